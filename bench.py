@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the HGQ2 quantizer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: the standalone fixed-point quantizer sweep -- 2^28 fp32 elements drawn from N(0, 4^2),
+per-element integer parameters k in {0,1}, i in [-2,6], f in [0,8], all six combinations of
+{RND,TRN} x {WRAP,SAT,SAT_SYM}, forward plus surrogate backward with an N(0,1) upstream
+gradient.  One step = one full sweep (6 forward + 6 backward passes over this rank's share of the
+element range).  With N > 1 (torchrun, one rank per GPU) the 2^28 elements are split contiguously
+over the ranks and no data crosses between them.
+
+Metric: achieved algorithmic bandwidth in GB/s, 46 bytes per element per (forward + backward)
+pass: forward reads x,i,f fp32 + k uint8 (13 B) and writes y (4 B); backward reads g,x,i,f,k (17 B)
+and writes dx,di,df (12 B).
+
+`--impl reference` times the reference's CPU formulation of the same sweep (the eager fp32 op
+sequence of oracle/fixed_point_ops.py on the host cores) on a bounded sample.
+
+Prints one JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+TOTAL_ELEMS = 1 << 28
+BYTES_FWD, BYTES_BWD = 17, 29
+MODES = [(rm, om) for rm in ('RND', 'TRN') for om in ('WRAP', 'SAT', 'SAT_SYM')]
+METRIC = 'quantizer_sweep_hbm_bandwidth'
+UNIT = 'GB/s'
+# DRAM bytes per element per launch (read + write) measured by ncu on a 2^25-element case of the
+# same kernels; traffic grows in proportion to the element count.  None until captured.
+NCU_TRAFFIC_BYTES_PER_ELEM = {'k_bwd_full': None, 'k_fwd_full': None}
+
+
+def measured_peaks():
+    p = ROOT / 'MEASURED_PEAKS.json'
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with NVML while a timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.05):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get('CUDA_VISIBLE_DEVICES')
+            phys = int(visible.split(',')[index]) if visible and visible.split(',')[index].isdigit() else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            'hw_slowdown': nv.nvmlClocksThrottleReasonHwSlowdown,
+            'hw_thermal_slowdown': nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+            'sw_thermal_slowdown': nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+            'sw_power_cap': nv.nvmlClocksThrottleReasonSwPowerCap,
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {'sm_mhz': None, 'sm_max_mhz': self.max_mhz, 'reasons': ['nvml unavailable']}
+        return {'sm_mhz': float(np.median(self.samples)), 'sm_max_mhz': self.max_mhz, 'reasons': sorted(self.reasons),
+                'samples': len(self.samples)}
+
+
+def make_inputs_np(n: int, seed: int):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(n, dtype=np.float32) * np.float32(4.0)
+    k = rng.integers(0, 2, n, dtype=np.uint8)
+    i = rng.integers(-2, 7, n).astype(np.float32)
+    f = rng.integers(0, 9, n).astype(np.float32)
+    g = rng.standard_normal(n, dtype=np.float32)
+    return x, k, i, f, g
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_sweep(sample: int, threads: int, steps: int, warmup: int):
+    """The reference formulation on the host: eager fp32 torch ops, materialised parameters."""
+    from oracle import fixed_point_ops as O
+
+    torch.set_num_threads(threads)
+    x, k, i, f, g = (torch.from_numpy(a) for a in make_inputs_np(sample, 1))
+    kf = k.float()
+
+    def one_step():
+        for rm, om in MODES:
+            O.quantize_fwd(x, kf, i, f, rm, om, training=False)
+            O.quantize_bwd(g, x, kf, i, f, rm, om)
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / steps
+    gbs = len(MODES) * (BYTES_FWD + BYTES_BWD) * sample / dt / 1e9
+    return gbs, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = 1 << 24
+    gbs, dt = cpu_sweep(sample, threads, max(1, args.steps), max(1, min(args.warmup, 2)))
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': round(gbs, 3), 'unit': UNIT, 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(dt * 1e3, 3), 'higher_is_better': True,
+        'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': workload_config(args.gpus),
+        'cpu_baseline': {'value': round(gbs, 3), 'unit': UNIT, 'cores': threads, 'kind': 'port',
+                         'sample': f'{sample} elements per pass (2^24 of the 2^28), 6 modes x (fwd+bwd) per step, '
+                                   'eager fp32 torch-CPU op sequence of the oracle'},
+        'e2e': {'value': round(gbs, 3), 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {
+        'workload': 'standalone fixed-point quantizer sweep: 2^28 fp32 elements N(0,16), per-element k/i/f, '
+                    '{RND,TRN}x{WRAP,SAT,SAT_SYM}, forward + surrogate backward',
+        'elements_total': TOTAL_ELEMS, 'elements_per_gpu': TOTAL_ELEMS // n_gpus,
+        'bytes_per_element': {'fwd': BYTES_FWD, 'bwd': BYTES_BWD},
+        'sharding': f'contiguous element range / {n_gpus}, no collective',
+        'l2': 'inputs larger than L2 (>= 1.5 GB touched per launch vs 126 MB L2)',
+    }
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+
+    from hgq2_b200 import kernels
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the product path has no CPU fallback')
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    n = TOTAL_ELEMS // world
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- inputs resident in HBM -----------------------------------------------------------------
+    gen = torch.Generator(device=dev).manual_seed(1 + rank)
+    x = torch.randn(n, device=dev, generator=gen) * 4.0
+    g = torch.randn(n, device=dev, generator=gen)
+    k = torch.randint(0, 2, (n,), device=dev, generator=gen, dtype=torch.uint8)
+    i = torch.randint(-2, 7, (n,), device=dev, generator=gen).float()
+    f = torch.randint(0, 9, (n,), device=dev, generator=gen).float()
+    y, dx, di, df = (torch.empty(n, device=dev) for _ in range(4))
+    L = kernels._lib.lib()
+    P = kernels.ptr
+    RM, OM = kernels._lib.ROUND_MODES, kernels._lib.OVERFLOW_MODES
+    st = torch.cuda.current_stream().cuda_stream
+
+    def fwd(rm, om):
+        kernels.check(L.hgq_quantize_fwd(P(x), P(k), P(i), P(f), P(y), None, n, n, RM[rm], OM[om], 0, st), 'fwd')
+
+    def bwd(rm, om):
+        kernels.check(L.hgq_quantize_bwd(P(g), P(x), P(k), P(i), P(f), P(dx), P(di), P(df), n, n, RM[rm], OM[om], 0,
+                                         None, 0, st), 'bwd')
+
+    def step():
+        for rm, om in MODES:
+            fwd(rm, om)
+            bwd(rm, om)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    launches0 = kernels.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    launches = kernels.launch_count() - launches0
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    bytes_per_step_total = len(MODES) * (BYTES_FWD + BYTES_BWD) * TOTAL_ELEMS
+    value = bytes_per_step_total / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel (backward, full layout), timed alone -------------------
+    def time_kernel(fn, reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    reps = max(6, args.steps)
+    t_bwd = time_kernel(lambda: bwd('RND', 'SAT'), reps)
+    t_fwd = time_kernel(lambda: fwd('RND', 'SAT'), reps)
+    peak, peak_kind = measured_peaks()
+    ach = BYTES_BWD * n / (t_bwd * 1e-3) / 1e9
+    tr = NCU_TRAFFIC_BYTES_PER_ELEM['k_bwd_full']
+    roofline = {
+        'bound': 'hbm', 'kernel': 'k_bwd_full (surrogate backward, full layout)', 'achieved': round(ach, 1),
+        'peak': peak, 'peak_source': f'{peak_kind} copy bandwidth (burst)', 'unit': 'GB/s', 'frac': round(ach / peak, 4),
+        'frac_of_8TBs_nominal': round(ach / 8000.0, 4),
+        'traffic': (tr * n if tr is not None else None),
+        'launch_ms': round(t_bwd, 4),
+        'fwd_kernel': {'achieved': round(BYTES_FWD * n / (t_fwd * 1e-3) / 1e9, 1), 'launch_ms': round(t_fwd, 4),
+                       'frac': round(BYTES_FWD * n / (t_fwd * 1e-3) / 1e9 / peak, 4)},
+    }
+
+    # ---- end to end through the host-buffer C-ABI entry ----------------------------------------
+    e2e = None
+    try:
+        e2e = run_e2e(args, kernels, n, dev, world, rank)
+    except Exception as exc:  # report, do not hide
+        e2e = {'value': None, 'unit': UNIT, 'error': repr(exc)[:300]}
+
+    # ---- CPU baseline on rank 0 at N = 1 --------------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        sample = 1 << 24
+        gbs, dt = cpu_sweep(sample, threads, 3, 1)
+        cpu = {'value': round(gbs, 3), 'unit': UNIT, 'cores': threads, 'kind': 'port',
+               'sample': f'{sample} elements per pass (2^24 of 2^28), 6 modes x (fwd+bwd), 3 steps; eager fp32 '
+                         'torch-CPU op sequence of the oracle'}
+
+    if rank == 0:
+        line = {
+            'metric': METRIC, 'value': round(value, 2), 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(3, args.warmup), 'ms_per_step': round(ms_per_step, 4), 'higher_is_better': True,
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+            'config': workload_config(world), 'roofline': roofline, 'cpu_baseline': cpu, 'e2e': e2e,
+            'gpu_launches': int(launches), 'clocks': clocks.summary(),
+            'frac_of_measured_copy_peak': round(value / world / peak, 4),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, kernels, n, dev, world, rank):
+    import torch.distributed as dist
+
+    chunk = 1 << 24
+    ws = torch.empty(kernels.quantize_host_workspace(chunk), dtype=torch.uint8, device=dev)
+    xs = make_inputs_np(n, 100 + rank)
+    hx, hk, hi, hf, hg = (torch.from_numpy(a).pin_memory() for a in xs)
+    hy, hdx, hdi, hdf = (torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(4))
+    steps = max(1, min(args.steps, 2))
+
+    def step():
+        for rm, om in MODES:
+            kernels.quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, hdi, hdf, rm, om, False, ws, chunk)
+
+    kernels.quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, hdi, hdf, 'RND', 'SAT', False, ws, chunk)  # warm-up
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    t = torch.tensor([dt], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt = float(t.item()) / steps
+    total = len(MODES) * (BYTES_FWD + BYTES_BWD) * TOTAL_ELEMS
+    return {
+        'value': round(total / dt / 1e9, 2), 'unit': UNIT, 'ms_per_step': round(dt * 1e3, 2), 'steps': steps,
+        'h2d_bytes_per_step': len(MODES) * 17 * n, 'd2h_bytes_per_step': len(MODES) * 16 * n,
+        'api': 'hgq_quantize_fwd_bwd_host: pinned host buffers, 3-stream chunked pipeline, synchronous return',
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=5)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--no-cpu', action='store_true', help='skip the cpu_baseline leg')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,101 @@
+"""ctypes binding of libhgq_b200.so, the C-ABI CUDA library of this package.
+
+The library is the only compute path of the package: there is no CPU or eager-PyTorch fallback.
+Loading fails loudly when the shared object is missing, and every call raises ``HGQError`` on a
+non-zero status.  PyTorch is used for device memory and streams only; the functions here take
+``torch.Tensor`` arguments and pass their raw device pointers across the ABI declared in
+``include/hgq_b200.h``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_uint, c_void_p
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / 'lib' / 'libhgq_b200.so'
+
+ROUND_MODES = {'TRN': 0, 'RND': 1, 'RND_CONV': 2}
+OVERFLOW_MODES = {'NONE': 0, 'WRAP': 1, 'SAT': 2, 'SAT_SYM': 3}
+FLAG_TRAINING = 1
+FLAG_ZERO_NONPOS = 2
+
+
+class HGQError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().hgq_status_string(status).decode() if _lib is not None else '?'
+        super().__init__(f'{where} failed with status {status}: {msg}')
+
+
+# name -> (restype, argtypes).  Every symbol declared in include/hgq_b200.h is listed here; the
+# CPU test-suite checks the two against each other.
+SIGNATURES: dict[str, tuple] = {
+    'hgq_status_string': (c_char_p, [c_int]),
+    'hgq_abi_version': (c_int, []),
+    'hgq_launch_count': (c_int64, []),
+    'hgq_quantize_fwd': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_uint, c_void_p],
+    ),
+    'hgq_quantize_bwd_workspace': (c_size_t, [c_int64, c_int64]),
+    'hgq_quantize_bwd': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,
+         c_uint, c_void_p, c_size_t, c_void_p],
+    ),
+    'hgq_quantize_host_workspace': (c_size_t, [c_int64]),
+    'hgq_quantize_fwd_bwd_host': (
+        c_int,
+        [c_void_p] * 9 + [c_int64, c_int, c_int, c_uint, c_void_p, c_size_t, c_int64],
+    ),
+}
+
+_lib: ctypes.CDLL | None = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library.  Raises if it has not been built (``python -m hgq2_b200.build``)."""
+    global _lib
+    if _lib is None:
+        path = Path(os.environ.get('HGQ_B200_LIB', LIB_PATH))
+        if not path.exists():
+            raise ImportError(
+                f'{path} is missing: build it with `python -m hgq2_b200.build` (needs nvcc). '
+                'hgq2_b200 has no CPU fallback.'
+            )
+        handle = ctypes.CDLL(str(path))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise HGQError(status, where)
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a tensor (None passes NULL)."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream_handle() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                'hgq2_b200 runs on CUDA tensors only (sm_100a kernels); got a tensor on ' + str(t.device)
+            )

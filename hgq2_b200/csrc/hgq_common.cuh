@@ -1,0 +1,68 @@
+// Host-side helpers shared by the translation units of the library: status codes, argument
+// checks, launch accounting and the launch geometry of the broadcast-layout kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/hgq_b200.h"
+
+namespace hgq {
+
+constexpr int kNumSMs = 148;        // B200: 2 dies x 74 SMs
+constexpr int kThreads = 256;       // CTA size of every streaming kernel
+constexpr int64_t kMaxParamAbs = 100;
+
+extern std::atomic<int64_t> g_launches;
+
+inline int check_launch() {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();  // clear the non-sticky error so the next call starts clean
+        return (int)e;
+    }
+    return HGQ_OK;
+}
+
+inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+inline int pow2ceil(int64_t v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+// Geometry of a broadcast-layout launch: x is [rows, P], parameters are [P].  A CTA is a
+// TX x TY arrangement of 256 threads; a thread owns VEC consecutive columns for the whole launch
+// (so the parameters live in registers and column reductions need no atomics) and walks rows
+// r0+ty, r0+ty+TY, ...  grid = (colTiles, rowBlocks).
+struct BcastGeom {
+    int vec;            // 4 (128-bit accesses) or 1
+    int64_t V;          // P / vec: vector columns
+    int TX, TY;         // TX * TY == kThreads, TX a power of two
+    int64_t colTiles;   // ceil(V / TX)
+    int rowBlocks;      // grid.y
+    int64_t rowsPerBlock;
+};
+
+inline BcastGeom bcast_geom(int64_t rows, int64_t P, bool can_vec, int unroll) {
+    BcastGeom g;
+    g.vec = (can_vec && P % 4 == 0) ? 4 : 1;
+    g.V = P / g.vec;
+    g.TX = (int)(g.V >= kThreads ? kThreads : pow2ceil(g.V));
+    g.TY = kThreads / g.TX;
+    g.colTiles = (g.V + g.TX - 1) / g.TX;
+    const int64_t target = (int64_t)kNumSMs * 8;
+    int64_t rb = (target + g.colTiles - 1) / g.colTiles;
+    const int64_t maxrb = (rows + (int64_t)g.TY * unroll - 1) / ((int64_t)g.TY * unroll);
+    if (rb > maxrb) rb = maxrb;
+    if (rb < 1) rb = 1;
+    if (rb > 65535) rb = 65535;
+    g.rowsPerBlock = (rows + rb - 1) / rb;
+    g.rowBlocks = (int)((rows + g.rowsPerBlock - 1) / g.rowsPerBlock);
+    return g;
+}
+
+}  // namespace hgq

@@ -1,0 +1,148 @@
+"""Tensor-level entry to the CUDA kernels: allocates outputs with torch, calls the C ABI.
+
+These functions are the seam between the Python mirror of the reference interface and
+``libhgq_b200.so``.  They do no arithmetic themselves.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import FLAG_TRAINING, FLAG_ZERO_NONPOS, OVERFLOW_MODES, ROUND_MODES, check, lib, ptr, require_cuda, stream_handle
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(nbytes: int, device: torch.device, slot: int = 0) -> torch.Tensor | None:
+    """A per-device scratch buffer that only ever grows (kept so steady-state steps allocate nothing)."""
+    if nbytes <= 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(), slot)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _modes(round_mode: str, overflow_mode: str) -> tuple[int, int]:
+    try:
+        return ROUND_MODES[round_mode.upper()], OVERFLOW_MODES[overflow_mode.upper()]
+    except KeyError as e:
+        raise ValueError(f'unsupported mode {e}; round modes {list(ROUND_MODES)}, overflow modes {list(OVERFLOW_MODES)}')
+
+
+def _period(x: torch.Tensor, p: torch.Tensor) -> int:
+    n, m = x.numel(), p.numel()
+    if m == n:
+        return n
+    if m == 0 or n % m != 0:
+        raise ValueError(f'parameter tensor with {m} entries cannot be broadcast over {n} elements')
+    return m
+
+
+def quantize_fwd(
+    x: torch.Tensor,
+    k: torch.Tensor | None,
+    i: torch.Tensor | None,
+    f: torch.Tensor,
+    round_mode: str,
+    overflow_mode: str,
+    training: bool = False,
+    zero_nonpos: bool = False,
+    want_absmax: bool = False,
+    out: torch.Tensor | None = None,
+):
+    """y = overflow(round(x, f), k, i, f); optionally also max_rows |round(x, f)| per parameter entry.
+
+    ``k`` is uint8, ``i``/``f`` fp32 with integer values.  Parameters either match ``x`` element
+    for element or hold ``period`` entries that repeat along the leading axes of ``x``.
+    """
+    require_cuda(x, k, i, f)
+    rm, om = _modes(round_mode, overflow_mode)
+    assert x.dtype == torch.float32 and f.dtype == torch.float32
+    x = x.contiguous()
+    f = f.contiguous()
+    k = k.contiguous() if k is not None else None
+    i = i.contiguous() if i is not None else None
+    if k is not None:
+        assert k.dtype == torch.uint8
+    period = _period(x, f)
+    y = out if out is not None else torch.empty_like(x)
+    absmax = torch.empty(period, dtype=torch.float32, device=x.device) if want_absmax else None
+    flags = (FLAG_TRAINING if training else 0) | (FLAG_ZERO_NONPOS if zero_nonpos else 0)
+    with torch.cuda.device(x.device):
+        st = lib().hgq_quantize_fwd(
+            ptr(x), ptr(k), ptr(i), ptr(f), ptr(y), ptr(absmax), x.numel(), period, rm, om, flags, stream_handle()
+        )
+    check(st, 'hgq_quantize_fwd')
+    return (y, absmax) if want_absmax else y
+
+
+def quantize_bwd(
+    g: torch.Tensor,
+    x: torch.Tensor,
+    k: torch.Tensor | None,
+    i: torch.Tensor | None,
+    f: torch.Tensor,
+    round_mode: str,
+    overflow_mode: str,
+    want_dx: bool = True,
+    want_di: bool = True,
+):
+    """Surrogate gradients (dx, di, df) of the training-mode quantizer; di/df are reduced to the parameter shape."""
+    require_cuda(g, x, k, i, f)
+    rm, om = _modes(round_mode, overflow_mode)
+    g = g.contiguous()
+    x = x.contiguous()
+    f = f.contiguous()
+    k = k.contiguous() if k is not None else None
+    i = i.contiguous() if i is not None else None
+    n = x.numel()
+    period = _period(x, f)
+    dx = torch.empty_like(x) if (want_dx or period == n) else None
+    di = torch.empty(period, dtype=torch.float32, device=x.device) if want_di else None
+    df = torch.empty(period, dtype=torch.float32, device=x.device)
+    nbytes = lib().hgq_quantize_bwd_workspace(n, period)
+    ws = workspace(nbytes, x.device)
+    with torch.cuda.device(x.device):
+        st = lib().hgq_quantize_bwd(
+            ptr(g), ptr(x), ptr(k), ptr(i), ptr(f), ptr(dx), ptr(di), ptr(df), n, period, rm, om, 0,
+            ptr(ws), ws.numel() if ws is not None else 0, stream_handle(),
+        )
+    check(st, 'hgq_quantize_bwd')
+    if period == n:
+        di = di.view(f.shape) if di is not None else None
+        df = df.view(f.shape)
+    else:
+        di = di.view(f.shape) if di is not None else None
+        df = df.view(f.shape)
+    return dx, di, df
+
+
+def launch_count() -> int:
+    return int(lib().hgq_launch_count())
+
+
+__all__ = ['quantize_fwd', 'quantize_bwd', 'launch_count', 'workspace', '_lib']
+
+
+def quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, hdi, hdf, round_mode: str, overflow_mode: str,
+                          training: bool, dev_ws: torch.Tensor, chunk_elems: int) -> None:
+    """Host-buffer sweep: CPU tensors in (ideally pinned), CPU tensors out; see hgq_quantize_fwd_bwd_host."""
+    rm, om = _modes(round_mode, overflow_mode)
+    for t in (hx, hk, hi, hf, hg, hy, hdx, hdi, hdf):
+        if t is not None and (t.is_cuda or not t.is_contiguous()):
+            raise ValueError('host entry takes contiguous CPU tensors')
+    require_cuda(dev_ws)
+    with torch.cuda.device(dev_ws.device):
+        st = lib().hgq_quantize_fwd_bwd_host(
+            ptr(hx), ptr(hk), ptr(hi), ptr(hf), ptr(hg), ptr(hy), ptr(hdx), ptr(hdi), ptr(hdf), hx.numel(), rm, om,
+            FLAG_TRAINING if training else 0, ptr(dev_ws), dev_ws.numel() * dev_ws.element_size(), chunk_elems,
+        )
+    check(st, 'hgq_quantize_fwd_bwd_host')
+
+
+def quantize_host_workspace(chunk_elems: int) -> int:
+    return int(lib().hgq_quantize_host_workspace(chunk_elems))

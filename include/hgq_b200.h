@@ -1,0 +1,144 @@
+/*
+ * hgq_b200.h -- C ABI of the B200 (sm_100a) kernels behind the HGQ2 quantised-training hot path.
+ *
+ * Every entry point takes raw device pointers (unless its name ends in _host), element counts,
+ * mode enums and a CUDA stream handle (a cudaStream_t passed as void*; NULL = the default
+ * stream).  Unless an entry says otherwise it allocates nothing, is asynchronous on the given
+ * stream and returns
+ *      0          success (the work has been enqueued),
+ *      negative   an HGQ_ERR_* argument error (nothing was enqueued),
+ *      positive   a cudaError_t raised by a launch or a runtime call.
+ * hgq_status_string() turns any of the three into text.
+ *
+ * The reference (calad0i/HGQ2) has no FFI of its own: it is pure Python on top of Keras and of
+ * the third-party `quantizers` package.  Each declaration below therefore cites the Python call
+ * site in the reference that it stands in for (path:line inside the HGQ2 tree).
+ *
+ * Conventions shared by all entries
+ *   - tensors are contiguous, row-major fp32 unless noted; `k` (keep_negative) is uint8 in {0,1},
+ *     the dtype of the reference variable (fixed_point_quantizer.py:218-224);
+ *   - `i` and `f` hold integer-valued floats (the reference passes round_conv()'ed variables,
+ *     fixed_point_quantizer.py:248-265,439-445); they are converted with round-to-nearest-even and
+ *     must lie in [-100, 100];
+ *   - parameter layout: `period` == n (or 0) means k/i/f have one entry per element of x
+ *     ("full"); otherwise they hold `period` entries and element e of x uses entry e % period
+ *     ("broadcast": the bitwidth tensor is x.shape with the leading homogeneous axes set to 1,
+ *     base.py:163-183).  n must be a multiple of period.
+ */
+#ifndef HGQ_B200_H_
+#define HGQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---------------------------------------------------------------------- */
+#define HGQ_OK 0
+#define HGQ_ERR_NULL (-1)      /* a required pointer is NULL                                  */
+#define HGQ_ERR_SIZE (-2)      /* a count/shape is negative, inconsistent or over a limit     */
+#define HGQ_ERR_MODE (-3)      /* unknown round / overflow mode or flag                       */
+#define HGQ_ERR_ALIGN (-4)     /* a pointer is not aligned to its element type                */
+#define HGQ_ERR_WORKSPACE (-5) /* the scratch buffer passed in is too small                   */
+#define HGQ_ERR_DEVICE (-6)    /* the current device is not an sm_100 part                    */
+#define HGQ_ERR_TIMEOUT (-7)   /* a bounded device-side wait gave up (status word non-zero)   */
+
+/* ---- modes (names follow the reference's round_mode / overflow_mode strings) ------------- */
+enum hgq_round_mode {
+    HGQ_ROUND_TRN = 0,      /* floor(x * 2^f) / 2^f                                            */
+    HGQ_ROUND_RND = 1,      /* floor(x * 2^f + 0.5) / 2^f                                      */
+    HGQ_ROUND_RND_CONV = 2  /* round-half-even(x * 2^f) / 2^f                                  */
+};
+
+enum hgq_overflow_mode {
+    HGQ_OVERFLOW_NONE = 0,    /* rounding only: stateless_quantizer.round(x, f, ...)            */
+    HGQ_OVERFLOW_WRAP = 1,    /* two's-complement wrap into [-k 2^i, 2^i - 2^-f]                */
+    HGQ_OVERFLOW_SAT = 2,     /* clip to [-k 2^i, 2^i - 2^-f]                                   */
+    HGQ_OVERFLOW_SAT_SYM = 3  /* clip to [-k (2^i - 2^-f), 2^i - 2^-f]                          */
+};
+
+/* flags (bit-or) */
+#define HGQ_FLAG_TRAINING 1u       /* training=True: WRAP leaves the rounded value unwrapped     */
+#define HGQ_FLAG_ZERO_NONPOS 2u    /* eval-only: y = 0 where k+i+f <= 0 (fixed_point_quantizer.py:148-149) */
+
+/* ---- library ------------------------------------------------------------------------------ */
+
+/* Text for a status returned by any entry point. Never NULL. */
+const char *hgq_status_string(int status);
+
+/* ABI version of this header (bumped on incompatible change). */
+int hgq_abi_version(void);
+
+/* Number of kernels this library has launched in the calling process (all entries, all
+ * streams).  Used by the benchmark to report how many launches a timed region made. */
+int64_t hgq_launch_count(void);
+
+/* ---- K1: elementwise fixed-point quantizer ------------------------------------------------ */
+
+/*
+ * Forward.  Stands in for stateless_quantizer(x, k, i, f, training, seed_gen)
+ * (call site fixed_point_quantizer.py:142-150) and stateless_quantizer.round(x, f, ...)
+ * (call sites fixed_point_quantizer.py:288,295,305,405) of quantizers.fixed_point.
+ *
+ *   y[e] = overflow(round(x[e], f), k, i, f)
+ *
+ * absmax (optional, may be NULL): `period` floats that receive max over the broadcast rows of
+ * |round(x, f)| -- the reduction x_to_bw_absmax (base.py:185-186) that the WRAP integer-bit
+ * tracking consumes (fixed_point_quantizer.py:405-413).  The entry clears it first.
+ * With overflow_mode NONE, `k` and `i` may be NULL.
+ */
+int hgq_quantize_fwd(const float *x, const uint8_t *k, const float *i, const float *f, float *y,
+                     float *absmax, int64_t n, int64_t period, int round_mode, int overflow_mode,
+                     unsigned flags, void *stream);
+
+/*
+ * Scratch bytes hgq_quantize_bwd needs for (n, period); 0 for the full layout.
+ */
+size_t hgq_quantize_bwd_workspace(int64_t n, int64_t period);
+
+/*
+ * Backward (surrogate gradients).  Stands in for the custom gradient of the same two callables.
+ * g is the upstream gradient dL/dy.
+ *
+ *   dx[e]  straight-through, zero where SAT / SAT_SYM clipped
+ *   df     -ln2 * (round(x,f) - x) * g on unclipped elements, +-ln2 2^-f g on clipped ones
+ *   di     ln2 2^i g on elements clipped at the top, -k ln2 2^i g at the bottom; 0 for WRAP/NONE
+ *
+ * Full layout: di/df have n entries.  Broadcast layout: di/df have `period` entries holding the
+ * sum over the broadcast rows (the backward of bw_to_x, base.py:182-183); partial sums are
+ * staged in `workspace` and reduced in a fixed order, so results do not depend on scheduling.
+ * di may be NULL (it is identically zero for WRAP / NONE).
+ */
+int hgq_quantize_bwd(const float *g, const float *x, const uint8_t *k, const float *i,
+                     const float *f, float *dx, float *di, float *df, int64_t n, int64_t period,
+                     int round_mode, int overflow_mode, unsigned flags, void *workspace,
+                     size_t workspace_bytes, void *stream);
+
+/* ---- standalone quantizer on host buffers ------------------------------------------------- */
+
+/*
+ * Device staging bytes hgq_quantize_fwd_bwd_host needs for a given chunk size (elements, a
+ * multiple of 4).  The caller allocates that much device memory, 256-byte aligned.
+ */
+size_t hgq_quantize_host_workspace(int64_t chunk_elems);
+
+/*
+ * The same computation as hgq_quantize_fwd followed by hgq_quantize_bwd (full layout), for a
+ * caller whose tensors live in host memory -- the situation of the reference's CPU path, where
+ * stateless_quantizer (fixed_point_quantizer.py:147) and its gradient run on host tensors.
+ * Inputs hx,hk,hi,hf (and hg) are read from host memory, outputs hy (and hdx,hdi,hdf) are written
+ * to host memory; pinned memory lets copies and kernels overlap.  hg == NULL runs the forward
+ * only; hdi may be NULL.  Synchronous: returns when every output byte has landed.  Uses three
+ * internal streams per device, created on first use; not re-entrant on one device.
+ */
+int hgq_quantize_fwd_bwd_host(const float *hx, const uint8_t *hk, const float *hi, const float *hf,
+                              const float *hg, float *hy, float *hdx, float *hdi, float *hdf,
+                              int64_t n, int round_mode, int overflow_mode, unsigned flags,
+                              void *dev_workspace, size_t dev_workspace_bytes, int64_t chunk_elems);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HGQ_B200_H_ */

@@ -1,0 +1,69 @@
+"""The C-ABI library builds, loads and exports exactly what include/hgq_b200.h declares (no GPU needed)."""
+
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope='module')
+def built_lib():
+    from hgq2_b200 import build
+
+    build.build()
+    from hgq2_b200 import _lib
+
+    return _lib.lib()
+
+
+def declared_symbols() -> set[str]:
+    text = (ROOT / 'include' / 'hgq_b200.h').read_text()
+    text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    return set(re.findall(r'\b(hgq_[a-z0-9_]+)\s*\(', text))
+
+
+def test_header_and_binding_agree(built_lib):
+    from hgq2_b200 import _lib
+
+    decl = declared_symbols()
+    assert decl, 'no declarations found'
+    assert decl == set(_lib.SIGNATURES), (decl ^ set(_lib.SIGNATURES))
+    for name in decl:
+        assert hasattr(built_lib, name), f'{name} is declared but not exported'
+
+
+def test_status_strings(built_lib):
+    assert built_lib.hgq_status_string(0) == b'ok'
+    for code in range(-7, 0):
+        assert built_lib.hgq_status_string(code) not in (b'', b'unknown status')
+    assert built_lib.hgq_abi_version() >= 1
+
+
+def test_argument_errors_need_no_gpu(built_lib):
+    # argument validation happens before any CUDA call
+    L = built_lib
+    assert L.hgq_quantize_fwd(None, None, None, None, None, None, 16, 0, 1, 2, 0, None) == -1
+    assert L.hgq_quantize_fwd(None, None, None, None, None, None, -1, 0, 1, 2, 0, None) == -2
+    assert L.hgq_quantize_fwd(None, None, None, None, None, None, 16, 5, 1, 2, 0, None) == -2
+    assert L.hgq_quantize_fwd(None, None, None, None, None, None, 16, 0, 7, 2, 0, None) == -3
+    assert L.hgq_quantize_fwd(None, None, None, None, None, None, 0, 0, 1, 2, 0, None) == 0
+    assert L.hgq_quantize_bwd_workspace(1 << 20, 1 << 20) == 0
+    assert L.hgq_quantize_bwd_workspace(1 << 20, 64) > 0
+
+
+def test_product_path_has_no_cpu_fallback():
+    import torch
+
+    from hgq2_b200 import kernels
+
+    x = torch.zeros(8)
+    with pytest.raises(RuntimeError, match='CUDA tensors only'):
+        kernels.quantize_fwd(x, torch.zeros(8, dtype=torch.uint8), x, x, 'RND', 'SAT')
+
+
+def test_package_never_imports_the_oracle():
+    for path in (ROOT / 'hgq2_b200').rglob('*.py'):
+        text = path.read_text()
+        assert not re.search(r'^\s*(from|import)\s+oracle\b', text, flags=re.M), path
