@@ -58,7 +58,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU with NVML while a timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None

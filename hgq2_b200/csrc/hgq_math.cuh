@@ -77,7 +77,8 @@ __device__ __forceinline__ float overflow(float xq, const Params &p) {
         const float minv = pow2i(-bk);
         const float bias = __fmul_rn(p.kf, pow2i(bk - 1));
         const float t = __fadd_rn(xq, bias);
-        const float r = __fsub_rn(t, __fmul_rn(m, floorf(__fmul_rn(t, minv))));
+        float r = __fsub_rn(t, __fmul_rn(m, floorf(__fmul_rn(t, minv))));
+        if (r == 0.f) r = copysignf(0.f, t);  // a zero remainder keeps the sign of the dividend
         return __fsub_rn(r, bias);
     }
     const float hi = __fsub_rn(p.p2i, p.inv);

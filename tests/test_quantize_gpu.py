@@ -12,7 +12,13 @@ MODES = [(rm, om) for rm in O.ROUND_MODES for om in O.OVERFLOW_MODES]
 
 
 def bits(t):
-    return t.detach().cpu().numpy().view(np.int32)
+    # canonical bit pattern: -0.0 is folded onto +0.0.  The sign of a zero produced by a clip is
+    # not defined by the reference (torch.clamp returns the bound or the value depending on the
+    # operand order of the SIMD max instruction it happens to be compiled to); every other value,
+    # NaN payloads included, must match bit for bit.
+    a = t.detach().cpu().numpy().astype(np.float32, copy=True).ravel()
+    a[a == 0] = 0.0
+    return a.view(np.int32)
 
 
 def assert_bit_equal(a, b, what=''):
@@ -162,5 +168,5 @@ def test_size_independent_properties_at_scale(K):
         assert torch.equal(y[nd], y2[nd]), (rm, om)
         hi = torch.exp2(i) - torch.exp2(-f)
         lo = -k.float() * (hi if om == 'SAT_SYM' else torch.exp2(i))
-        ok = (y <= hi) & (y >= lo) | (hi < lo)
+        ok = (y <= hi) & (y >= lo) | (hi < lo) | ~nd
         assert bool(ok.all()), (rm, om)
