@@ -43,8 +43,8 @@ MODES = [(rm, om) for rm in ('RND', 'TRN') for om in ('WRAP', 'SAT', 'SAT_SYM')]
 METRIC = 'quantizer_sweep_hbm_bandwidth'
 UNIT = 'GB/s'
 # DRAM bytes per element per launch (read + write) measured by ncu on a 2^25-element case of the
-# same kernels; traffic grows in proportion to the element count.  None until captured.
-NCU_TRAFFIC_BYTES_PER_ELEM = {'k_bwd_full': None, 'k_fwd_full': None}
+# same kernels (profiles/quantize_full_layout_sweep.md); traffic grows in proportion to the element count.
+NCU_TRAFFIC_BYTES_PER_ELEM = {'k_bwd_full': 27.56, 'k_fwd_full': 16.16}
 
 
 def measured_peaks():
@@ -277,10 +277,11 @@ def run_ours(args):
 
     # ---- end to end through the host-buffer C-ABI entry ----------------------------------------
     e2e = None
-    try:
-        e2e = run_e2e(args, kernels, n, dev, world, rank)
-    except Exception as exc:  # report, do not hide
-        e2e = {'value': None, 'unit': UNIT, 'error': repr(exc)[:300]}
+    if not args.no_e2e:
+        try:
+            e2e = run_e2e(args, kernels, n, dev, world, rank)
+        except Exception as exc:  # report, do not hide
+            e2e = {'value': None, 'unit': UNIT, 'error': repr(exc)[:300]}
 
     # ---- CPU baseline on rank 0 at N = 1 --------------------------------------------------------
     cpu = None
@@ -348,7 +349,11 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-cpu', action='store_true', help='skip the cpu_baseline leg')
+    ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer end-to-end leg')
+    ap.add_argument('--elements', type=int, default=1 << 28,
+                    help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
     args = ap.parse_args()
+    globals()['TOTAL_ELEMS'] = args.elements
     if args.impl == 'reference':
         run_reference(args)
     else:
