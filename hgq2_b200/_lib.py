@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_uint, c_void_p
+from ctypes import c_char_p, c_double, c_int, c_int64, c_size_t, c_uint, c_void_p
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
@@ -45,6 +45,15 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,
          c_uint, c_void_p, c_size_t, c_void_p],
+    ),
+    'hgq_ebops_dense': (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,
+    ),
+    'hgq_ebops_conv2d': (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_void_p] + [c_int] * 11 + [c_void_p, c_int64, c_double, c_double, c_double, c_void_p]
+        + [c_void_p] * 7,
     ),
     'hgq_quantize_host_workspace': (c_size_t, [c_int64]),
     'hgq_quantize_fwd_bwd_host': (

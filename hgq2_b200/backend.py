@@ -1,0 +1,367 @@
+"""The small slice of the Keras-3 layer protocol that the HGQ2 hot path relies on, on plain PyTorch.
+
+HGQ2's quantizers and layers are ``keras.layers.Layer`` subclasses; under the Keras torch backend
+such a layer *is* a ``torch.nn.Module`` whose variables wrap ``torch.nn.Parameter``s.  Keras is
+not a dependency of this package, so the few protocol pieces the path touches are provided here
+with Keras' names and meaning:
+
+    Layer.add_weight(name, shape, initializer, trainable, dtype, constraint, regularizer)
+    Layer.build(input_shape) / built, Layer.__call__(*args, training=None, **kw) with the
+    call-context propagation of ``training`` to nested layers, Layer.add_loss / losses,
+    Variable.assign / numpy / value / constraint / regularizer, trainable_variables, ...
+
+A model built from these layers trains with any torch optimizer; ``hgq2_b200.train`` has the step
+that also applies constraints and regularizers the way Keras' trainer does.
+"""
+
+from __future__ import annotations
+
+import math
+import threading
+from collections.abc import Callable, Sequence
+
+import numpy as np
+import torch
+from torch import nn
+
+_DTYPES = {
+    'float32': torch.float32, 'uint8': torch.uint8, 'int32': torch.int32, 'uint32': torch.uint32, 'bool': torch.bool,
+    'float64': torch.float64,
+}
+
+
+def epsilon() -> float:
+    """Keras' fuzz factor (keras.config.epsilon() default)."""
+    return 1e-7
+
+
+_default_device: torch.device | None = None
+
+
+def set_default_device(device) -> None:
+    global _default_device
+    _default_device = torch.device(device) if device is not None else None
+
+
+def default_device() -> torch.device:
+    if _default_device is not None:
+        return _default_device
+    if torch.cuda.is_available():
+        return torch.device('cuda', torch.cuda.current_device())
+    return torch.device('cpu')
+
+
+# ---- initializers ------------------------------------------------------------------------------
+class Initializer:
+    def __call__(self, shape, dtype=torch.float32, device=None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Constant(Initializer):
+    def __init__(self, value=0.0):
+        self.value = value
+
+    def __call__(self, shape, dtype=torch.float32, device=None):
+        return torch.full(tuple(shape), float(self.value), dtype=torch.float32, device=device).to(dtype)
+
+    def get_config(self):
+        return {'value': self.value}
+
+
+class Zeros(Constant):
+    def __init__(self):
+        super().__init__(0.0)
+
+
+class Ones(Constant):
+    def __init__(self):
+        super().__init__(1.0)
+
+
+def _fans(shape):
+    shape = tuple(shape)
+    if len(shape) < 1:
+        return 1, 1
+    if len(shape) == 1:
+        return shape[0], shape[0]
+    if len(shape) == 2:
+        return shape[0], shape[1]
+    receptive = int(np.prod(shape[:-2]))
+    return shape[-2] * receptive, shape[-1] * receptive
+
+
+class GlorotUniform(Initializer):
+    """U(-l, l), l = sqrt(6 / (fan_in + fan_out)); drawn with numpy so CPU and GPU models agree."""
+
+    def __init__(self, seed=None):
+        self.seed = seed
+
+    def __call__(self, shape, dtype=torch.float32, device=None):
+        fan_in, fan_out = _fans(shape)
+        limit = math.sqrt(6.0 / max(1.0, fan_in + fan_out))
+        rng = np.random.default_rng(self.seed)
+        w = rng.uniform(-limit, limit, size=tuple(shape)).astype(np.float32)
+        return torch.from_numpy(w).to(device=device, dtype=dtype)
+
+
+class RandomNormal(Initializer):
+    def __init__(self, mean=0.0, stddev=0.05, seed=None):
+        self.mean, self.stddev, self.seed = mean, stddev, seed
+
+    def __call__(self, shape, dtype=torch.float32, device=None):
+        rng = np.random.default_rng(self.seed)
+        w = (rng.standard_normal(tuple(shape)) * self.stddev + self.mean).astype(np.float32)
+        return torch.from_numpy(w).to(device=device, dtype=dtype)
+
+
+def get_initializer(spec) -> Initializer:
+    if isinstance(spec, Initializer):
+        return spec
+    if spec is None or spec == 'zeros':
+        return Zeros()
+    if spec == 'ones':
+        return Ones()
+    if spec == 'glorot_uniform':
+        return GlorotUniform()
+    if isinstance(spec, (int, float)):
+        return Constant(spec)
+    raise ValueError(f'unknown initializer {spec!r}')
+
+
+# ---- variables ---------------------------------------------------------------------------------
+class Variable:
+    """A named tensor owned by a layer.  Trainable float variables wrap an ``nn.Parameter``."""
+
+    def __init__(self, value: torch.Tensor, name: str, trainable: bool, dtype: str, constraint=None, regularizer=None):
+        self.name = name
+        self.path = name
+        self.dtype = dtype
+        self.constraint = constraint
+        self.regularizer = regularizer
+        self._trainable = bool(trainable) and value.is_floating_point()
+        self._p = nn.Parameter(value, requires_grad=self._trainable)
+
+    @property
+    def trainable(self) -> bool:
+        return self._trainable
+
+    @trainable.setter
+    def trainable(self, v: bool):
+        self._trainable = bool(v) and self._p.is_floating_point()
+        self._p.requires_grad_(self._trainable)
+
+    @property
+    def value(self) -> nn.Parameter:
+        return self._p
+
+    @property
+    def shape(self):
+        return tuple(self._p.shape)
+
+    def assign(self, value) -> None:
+        with torch.no_grad():
+            v = torch.as_tensor(value, device=self._p.device)
+            self._p.copy_(v.to(self._p.dtype).reshape(self._p.shape) if v.numel() == self._p.numel() else v.to(self._p.dtype).expand(self._p.shape))
+
+    def numpy(self) -> np.ndarray:
+        return self._p.detach().cpu().numpy()
+
+    def __repr__(self):
+        return f'<Variable {self.path} shape={self.shape} dtype={self.dtype} trainable={self.trainable}>'
+
+
+# ---- call context ------------------------------------------------------------------------------
+class _CallContext(threading.local):
+    def __init__(self):
+        self.depth = 0
+        self.training = None
+        self.root = None
+
+
+_ctx = _CallContext()
+
+
+class Layer(nn.Module):
+    _name_counters: dict[str, int] = {}
+
+    def __init__(self, name: str | None = None, trainable: bool = True, dtype: str = 'float32', **kwargs):
+        super().__init__()
+        if kwargs:
+            raise TypeError(f'unexpected arguments for {type(self).__name__}: {sorted(kwargs)}')
+        if name is None:
+            base = _snake(type(self).__name__)
+            n = Layer._name_counters.get(base, 0)
+            Layer._name_counters[base] = n + 1
+            name = base if n == 0 else f'{base}_{n}'
+        self.name = name
+        self._trainable = trainable
+        self._dtype = dtype
+        self.built = False
+        self._variables: list[Variable] = []
+        self._losses: list[torch.Tensor] = []
+        self.supports_masking = False
+
+    # -- keras-style attributes
+    @property
+    def dtype(self) -> str:
+        return self._dtype
+
+    @property
+    def trainable(self) -> bool:
+        return self._trainable
+
+    @trainable.setter
+    def trainable(self, v: bool):
+        self._trainable = v
+
+    def add_weight(self, shape=(), initializer=None, dtype=None, trainable=True, name=None, constraint=None,
+                   regularizer=None, autocast=True, **_ignored) -> Variable:
+        dtype = dtype or 'float32'
+        init = get_initializer(initializer)
+        value = init(tuple(shape), dtype=_DTYPES[dtype], device=default_device())
+        v = Variable(value, name or f'variable_{len(self._variables)}', trainable and self._trainable, dtype, constraint,
+                     regularizer)
+        v.path = f'{self.name}/{v.name}'
+        self._variables.append(v)
+        self.register_parameter(f'_v{len(self._variables) - 1}_{v.name}', v.value)
+        return v
+
+    def build(self, *args, **kwargs):
+        self.built = True
+
+    def compute_output_shape(self, input_shape):
+        return input_shape
+
+    def add_loss(self, loss) -> None:
+        (_ctx.root if _ctx.root is not None else self)._losses.append(loss)
+
+    @property
+    def losses(self) -> list[torch.Tensor]:
+        """Losses added during the last top-level call, plus the weight regularisers of every sublayer."""
+        out = list(self._losses)
+        for layer in self._flatten_layers():
+            for v in layer._variables:
+                if v.regularizer is not None and v.trainable:
+                    out.append(v.regularizer(v.value))
+        return out
+
+    def _flatten_layers(self, include_self: bool = True, recursive: bool = True):
+        seen = []
+        if include_self:
+            seen.append(self)
+        for m in (self.modules() if recursive else self.children()):
+            if m is not self and isinstance(m, Layer):
+                seen.append(m)
+        return seen
+
+    @property
+    def variables(self) -> list[Variable]:
+        return [v for layer in self._flatten_layers() for v in layer._variables]
+
+    @property
+    def trainable_variables(self) -> list[Variable]:
+        return [v for v in self.variables if v.trainable]
+
+    @property
+    def non_trainable_variables(self) -> list[Variable]:
+        return [v for v in self.variables if not v.trainable]
+
+    def _maybe_build(self, args):
+        if self.built:
+            return
+        shapes = [_shape_of(a) for a in args]
+        self.build(*shapes) if len(shapes) != 1 else self.build(shapes[0])
+        self.built = True
+
+    def __call__(self, *args, **kwargs):
+        top = _ctx.depth == 0
+        explicit = kwargs.get('training', None)
+        prev_training = _ctx.training
+        if explicit is not None:
+            _ctx.training = explicit
+        training = _ctx.training
+        if top:
+            _ctx.root = self
+            self._losses = []
+        if _accepts_training(self):
+            kwargs['training'] = training
+        else:
+            kwargs.pop('training', None)
+        _ctx.depth += 1
+        try:
+            self._maybe_build(args)
+            return self.call(*args, **kwargs)
+        finally:
+            _ctx.depth -= 1
+            _ctx.training = prev_training
+            if top:
+                _ctx.root = None
+
+    def call(self, *args, **kwargs):
+        raise NotImplementedError
+
+    def forward(self, *args, **kwargs):  # nn.Module protocol
+        return self.__call__(*args, **kwargs)
+
+    def get_config(self):
+        return {'name': self.name, 'trainable': self.trainable, 'dtype': self.dtype}
+
+
+_training_arg_cache: dict = {}
+
+
+def _accepts_training(layer: Layer) -> bool:
+    fn = type(layer).call  # keyed on the function: QLayerMeta swaps a class's call once
+    r = _training_arg_cache.get(fn)
+    if r is None:
+        import inspect
+
+        sig = inspect.signature(fn)
+        r = 'training' in sig.parameters or any(p.kind == p.VAR_KEYWORD for p in sig.parameters.values())
+        _training_arg_cache[fn] = r
+    return r
+
+
+def _shape_of(a):
+    if isinstance(a, (tuple, list)):
+        return [_shape_of(x) for x in a]
+    return tuple(a.shape)
+
+
+def _snake(name: str) -> str:
+    out = []
+    for i, ch in enumerate(name):
+        if ch.isupper() and i and (not name[i - 1].isupper() or (i + 1 < len(name) and name[i + 1].islower())):
+            out.append('_')
+        out.append(ch.lower())
+    return ''.join(out)
+
+
+# ---- activations -------------------------------------------------------------------------------
+def get_activation(spec) -> Callable | None:
+    if spec is None or spec == 'linear':
+        return None
+    if callable(spec):
+        return spec
+    if spec == 'relu':
+        return torch.relu
+    if spec == 'softmax':
+        return lambda x: torch.softmax(x, dim=-1)
+    if spec == 'tanh':
+        return torch.tanh
+    if spec == 'sigmoid':
+        return torch.sigmoid
+    raise ValueError(f'unknown activation {spec!r}')
+
+
+def activation_name(spec) -> str | None:
+    if spec is None or spec == 'linear':
+        return None
+    return spec if isinstance(spec, str) else getattr(spec, '__name__', 'custom')
+
+
+numbers = (int, float, np.integer, np.floating)
+
+__all__ = ['Layer', 'Variable', 'Initializer', 'Constant', 'Zeros', 'Ones', 'GlorotUniform', 'RandomNormal',
+           'get_initializer', 'get_activation', 'activation_name', 'epsilon', 'numbers', 'default_device',
+           'set_default_device', 'Sequence']

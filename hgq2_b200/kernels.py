@@ -125,7 +125,6 @@ def launch_count() -> int:
     return int(lib().hgq_launch_count())
 
 
-__all__ = ['quantize_fwd', 'quantize_bwd', 'launch_count', 'workspace', '_lib']
 
 
 def quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, hdi, hdf, round_mode: str, overflow_mode: str,
@@ -146,3 +145,52 @@ def quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, hdi, hdf, round_mode: str
 
 def quantize_host_workspace(chunk_elems: int) -> int:
     return int(lib().hgq_quantize_host_workspace(chunk_elems))
+
+
+def ebops_dense(bw_in, bw_w, bw_bias, out_size: float, scale: float, beta, want_grads: bool = True):
+    """K3 for a dense / einsum-dense layer.  bw_in [P, K], bw_w [K, N]; returns (ebops_u32, ebops_f, loss, d_in, d_w, d_bias)."""
+    require_cuda(bw_in, bw_w, bw_bias, beta)
+    bw_in, bw_w = bw_in.contiguous(), bw_w.contiguous()
+    P, K = bw_in.shape
+    K2, N = bw_w.shape
+    assert K == K2
+    dev = bw_in.device
+    nb = 0 if bw_bias is None else bw_bias.numel()
+    bw_bias = None if bw_bias is None else bw_bias.contiguous()
+    e_u = torch.empty((), dtype=torch.uint32, device=dev)
+    e_f = torch.empty((), dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    d_in = torch.empty_like(bw_in) if want_grads else None
+    d_w = torch.empty_like(bw_w) if want_grads else None
+    d_b = torch.empty_like(bw_bias) if (want_grads and nb) else None
+    with torch.cuda.device(dev):
+        st = lib().hgq_ebops_dense(ptr(bw_in), P, K, ptr(bw_w), N, ptr(bw_bias), nb, float(out_size), float(scale), ptr(beta),
+                                   ptr(e_u), ptr(e_f), ptr(loss), ptr(d_in), ptr(d_w), ptr(d_b), stream_handle())
+    check(st, 'hgq_ebops_dense')
+    return e_u, e_f, loss, d_in, d_w, d_b
+
+
+def ebops_conv2d(bw_in, bw_w, bw_bias, out_hw, strides, dilation, pad_tl, out_size: float, scale_main: float,
+                 scale_bias: float, beta, want_grads: bool = True):
+    """K3 for a channels-last conv2d.  bw_in [H, W, C], bw_w [KH, KW, C, N]."""
+    require_cuda(bw_in, bw_w, bw_bias, beta)
+    bw_in, bw_w = bw_in.contiguous(), bw_w.contiguous()
+    H, W, C = bw_in.shape
+    KH, KW, C2, N = bw_w.shape
+    assert C == C2
+    dev = bw_in.device
+    nb = 0 if bw_bias is None else bw_bias.numel()
+    bw_bias = None if bw_bias is None else bw_bias.contiguous()
+    e_u = torch.empty((), dtype=torch.uint32, device=dev)
+    e_f = torch.empty((), dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    d_in = torch.empty_like(bw_in) if want_grads else None
+    d_w = torch.empty_like(bw_w) if want_grads else None
+    d_b = torch.empty_like(bw_bias) if (want_grads and nb) else None
+    with torch.cuda.device(dev):
+        st = lib().hgq_ebops_conv2d(ptr(bw_in), H, W, C, ptr(bw_w), KH, KW, N, out_hw[0], out_hw[1], strides[0], strides[1],
+                                    dilation[0], dilation[1], pad_tl[0], pad_tl[1], ptr(bw_bias), nb, float(out_size),
+                                    float(scale_main), float(scale_bias), ptr(beta), ptr(e_u), ptr(e_f), ptr(loss),
+                                    ptr(d_in), ptr(d_w), ptr(d_b), stream_handle())
+    check(st, 'hgq_ebops_conv2d')
+    return e_u, e_f, loss, d_in, d_w, d_b

@@ -1,0 +1,160 @@
+"""QConv2D: act(conv2d(iq(x), kq(W)) + bq(b)) with EBOPs (mirror of src/hgq/layers/conv.py, rank 2, channels_last)."""
+
+from __future__ import annotations
+
+from math import ceil, prod
+
+import torch
+import torch.nn.functional as F
+
+from ..backend import activation_name, get_activation, get_initializer
+from ..quantizer import Quantizer
+from ..quantizer.config import QuantizerConfig
+from ._functions import EbopsConv2dFn
+from .core.base import QLayerBaseSingleInput
+
+
+def _pair(v):
+    return (int(v), int(v)) if isinstance(v, int) else tuple(int(a) for a in v)
+
+
+def same_padding(size: int, kernel: int, stride: int, dilation: int) -> tuple[int, int]:
+    """(before, after) zero padding of TensorFlow/Keras 'same' convolution along one axis."""
+    out = ceil(size / stride)
+    total = max((out - 1) * stride + (kernel - 1) * dilation + 1 - size, 0)
+    return total // 2, total - total // 2
+
+
+class QConv2D(QLayerBaseSingleInput):
+    rank = 2
+
+    def __init__(self, filters, kernel_size, strides=(1, 1), padding='valid', data_format=None, dilation_rate=(1, 1),
+                 groups=1, activation=None, use_bias=True, kernel_initializer='glorot_uniform', bias_initializer='zeros',
+                 kernel_regularizer=None, bias_regularizer=None, activity_regularizer=None, kernel_constraint=None,
+                 bias_constraint=None, kq_conf: None | QuantizerConfig = None, iq_conf: None | QuantizerConfig = None,
+                 bq_conf: None | QuantizerConfig = None, parallelization_factor=-1, **kwargs):
+        super().__init__(iq_conf=iq_conf, **kwargs)
+        if data_format not in (None, 'channels_last'):
+            raise NotImplementedError('only channels_last is supported')
+        if groups != 1:
+            raise NotImplementedError('grouped convolutions are not supported')
+        if padding not in ('valid', 'same'):
+            raise NotImplementedError(f'padding {padding!r} is not supported')
+        self.data_format = 'channels_last'
+        self.filters = int(filters)
+        self.kernel_size = _pair(kernel_size)
+        self.strides = _pair(strides)
+        self.dilation_rate = _pair(dilation_rate)
+        self.padding = padding
+        self.use_bias = use_bias
+        self._activation_spec = activation
+        self.activation = get_activation(activation)
+        self.kernel_initializer = get_initializer(kernel_initializer)
+        self.bias_initializer = get_initializer(bias_initializer)
+        self.kernel_regularizer, self.bias_regularizer = kernel_regularizer, bias_regularizer
+        self.kernel_constraint, self.bias_constraint = kernel_constraint, bias_constraint
+        kq_conf = kq_conf or QuantizerConfig('default', 'weight')
+        self._kq = Quantizer(kq_conf, name=f'{self.name}_kq')
+        bq_conf = bq_conf or QuantizerConfig('default', 'bias')
+        self._bq = Quantizer(bq_conf, name=f'{self.name}_bq') if use_bias else None
+        self.parallelization_factor = parallelization_factor
+        self.bias = None
+
+    @property
+    def kq(self):
+        return self._kq
+
+    @property
+    def bq(self):
+        return self._bq
+
+    @property
+    def kernel(self):
+        return self._kernel.value
+
+    def _pads(self, h, w):
+        if self.padding == 'valid':
+            return (0, 0), (0, 0)
+        return (same_padding(h, self.kernel_size[0], self.strides[0], self.dilation_rate[0]),
+                same_padding(w, self.kernel_size[1], self.strides[1], self.dilation_rate[1]))
+
+    def compute_output_shape(self, input_shape):
+        b, h, w, _ = input_shape
+        (pt, pb), (pl, pr) = self._pads(h, w)
+        oh = (h + pt + pb - (self.kernel_size[0] - 1) * self.dilation_rate[0] - 1) // self.strides[0] + 1
+        ow = (w + pl + pr - (self.kernel_size[1] - 1) * self.dilation_rate[1] - 1) // self.strides[1] + 1
+        return (b, oh, ow, self.filters)
+
+    def build(self, input_shape):
+        super().build(input_shape)
+        c = int(input_shape[-1])
+        self._kernel = self.add_weight(name='kernel', shape=self.kernel_size + (c, self.filters),
+                                       initializer=self.kernel_initializer, regularizer=self.kernel_regularizer,
+                                       constraint=self.kernel_constraint)
+        if self.use_bias:
+            self._bias = self.add_weight(name='bias', shape=(self.filters,), initializer=self.bias_initializer,
+                                         regularizer=self.bias_regularizer, constraint=self.bias_constraint)
+            self.bias = self._bias.value
+        self.kq.build(tuple(self._kernel.shape))
+        self.kq.built = True
+        if self.use_bias:
+            self.bq.build(tuple(self._bias.shape))
+            self.bq.built = True
+        self._built_hw = (int(input_shape[1]), int(input_shape[2]))
+        out = self.compute_output_shape(input_shape)
+        self.n_parallel = prod(int(d) for d in out[1:-1])
+        if self.parallelization_factor <= 0:
+            self.parallelization_factor = self.n_parallel
+
+    def convolution_op(self, inputs, kernel):
+        """channels_last 2-D convolution (library call; the fused kernel path replaces it)."""
+        (pt, pb), (pl, pr) = self._pads(inputs.shape[1], inputs.shape[2])
+        x = inputs.permute(0, 3, 1, 2)
+        if pt or pb or pl or pr:
+            x = F.pad(x, (pl, pr, pt, pb))
+        with torch.backends.cudnn.flags(allow_tf32=False):  # fp32 accumulate of fp32 operands, as the reference
+            y = F.conv2d(x, kernel.permute(3, 2, 0, 1), stride=self.strides, dilation=self.dilation_rate)
+        return y.permute(0, 2, 3, 1)
+
+    def call(self, inputs, training=None):
+        if self.enable_iq:
+            inputs = self.iq(inputs, training=training)
+        outputs = self.convolution_op(inputs, self.qkernel)
+        if self.use_bias:
+            outputs = outputs + self.qbias.reshape(1, 1, 1, self.filters)
+        if self.activation is not None:
+            return self.activation(outputs)
+        return outputs
+
+    def _compute_ebops(self, shape):
+        shape = tuple(shape)
+        _, h, w, _ = shape
+        bw_inp = self.iq.bits_(shape)[0]
+        bw_ker = self.kq.bits_(tuple(self._kernel.shape))
+        bw_bias = self.bq.bits_(tuple(self._bias.shape)) if self.bq is not None else None
+        (pt, _), (pl, _) = self._pads(h, w)
+        out = self.compute_output_shape(shape)
+        size = float(prod(shape[:-1]) * self.filters)
+        return EbopsConv2dFn.apply(bw_inp, bw_ker, bw_bias, (out[1], out[2]), self.strides, self.dilation_rate, (pt, pl),
+                                   size, self.parallelization_factor / self.n_parallel, 1.0)
+
+    def get_config(self):
+        config = super().get_config()
+        config.update({
+            'filters': self.filters, 'kernel_size': self.kernel_size, 'strides': self.strides, 'padding': self.padding,
+            'dilation_rate': self.dilation_rate, 'activation': activation_name(self._activation_spec),
+            'use_bias': self.use_bias, 'kq_conf': self.kq.config,
+            'bq_conf': self.bq.config if self.bq is not None else None,
+            'parallelization_factor': self.parallelization_factor,
+        })
+        return config
+
+    @property
+    def qkernel(self):
+        return self.kq(self._kernel.value)
+
+    @property
+    def qbias(self):
+        if self.bias is None:
+            return None
+        return self.bq(self._bias.value)

@@ -1,0 +1,107 @@
+"""QDense: act(iq(x) @ kq(W) + bq(b)) with EBOPs (mirror of src/hgq/layers/core/dense.py:13-102)."""
+
+from __future__ import annotations
+
+from math import prod
+
+import torch
+
+from ...backend import activation_name, get_activation, get_initializer
+from ...quantizer import Quantizer
+from ...quantizer.config import QuantizerConfig
+from .._functions import EbopsDenseFn
+from .base import QLayerBaseSingleInput
+
+
+class QDense(QLayerBaseSingleInput):
+    def __init__(self, units, activation=None, use_bias=True, kernel_initializer='glorot_uniform',
+                 bias_initializer='zeros', kernel_regularizer=None, bias_regularizer=None, activity_regularizer=None,
+                 kernel_constraint=None, bias_constraint=None, kq_conf: None | QuantizerConfig = None,
+                 iq_conf: None | QuantizerConfig = None, bq_conf: None | QuantizerConfig = None,
+                 parallelization_factor=-1, **kwargs):
+        super().__init__(iq_conf=iq_conf, **kwargs)
+        self.units = int(units)
+        self._activation_spec = activation
+        self.activation = get_activation(activation)
+        self.use_bias = use_bias
+        self.kernel_initializer = get_initializer(kernel_initializer)
+        self.bias_initializer = get_initializer(bias_initializer)
+        self.kernel_regularizer, self.bias_regularizer = kernel_regularizer, bias_regularizer
+        self.kernel_constraint, self.bias_constraint = kernel_constraint, bias_constraint
+        kq_conf = kq_conf or QuantizerConfig('default', 'weight')
+        self._kq = Quantizer(kq_conf, name=f'{self.name}_kq')
+        bq_conf = bq_conf or QuantizerConfig('default', 'bias')
+        self._bq = Quantizer(bq_conf, name=f'{self.name}_bq') if use_bias else None
+        self.parallelization_factor = parallelization_factor
+        self.bias = None
+
+    @property
+    def kq(self):
+        return self._kq
+
+    @property
+    def bq(self):
+        return self._bq
+
+    @property
+    def kernel(self):
+        return self._kernel.value
+
+    def build(self, input_shape):
+        super().build(input_shape)
+        in_dim = int(input_shape[-1])
+        self._kernel = self.add_weight(name='kernel', shape=(in_dim, self.units), initializer=self.kernel_initializer,
+                                       regularizer=self.kernel_regularizer, constraint=self.kernel_constraint)
+        if self.use_bias:
+            self._bias = self.add_weight(name='bias', shape=(self.units,), initializer=self.bias_initializer,
+                                         regularizer=self.bias_regularizer, constraint=self.bias_constraint)
+            self.bias = self._bias.value
+        self.n_parallel = prod(int(d) for d in input_shape[1:-1])
+        if self.parallelization_factor < 0:
+            self.parallelization_factor = self.n_parallel
+        self.kq.build(tuple(self._kernel.shape))
+        self.kq.built = True
+        if self.bias is not None:
+            self.bq.build(tuple(self._bias.shape))
+            self.bq.built = True
+
+    def compute_output_shape(self, input_shape):
+        return tuple(input_shape[:-1]) + (self.units,)
+
+    def call(self, inputs, training=None):
+        if self.enable_iq:
+            inputs = self.iq(inputs, training=training)
+        x = torch.matmul(inputs, self.qkernel)
+        if self.bias is not None:
+            x = x + self.qbias
+        if self.activation is not None:
+            x = self.activation(x)
+        return x
+
+    def _compute_ebops(self, shape):
+        shape = tuple(shape)
+        K = shape[-1]
+        bw_inp = self.iq.bits_(shape).reshape(-1, K)
+        bw_ker = self.kq.bits_(tuple(self._kernel.shape))
+        bw_bias = self.bq.bits_(tuple(self._bias.shape)) if self.bq is not None else None
+        out_size = prod(shape[:-1]) * self.units
+        return EbopsDenseFn.apply(bw_inp, bw_ker, bw_bias, float(out_size), self.parallelization_factor / self.n_parallel)
+
+    def get_config(self):
+        config = super().get_config()
+        config.update({
+            'units': self.units, 'activation': activation_name(self._activation_spec), 'use_bias': self.use_bias,
+            'kq_conf': self.kq.config, 'bq_conf': self.bq.config if self.bq is not None else None,
+            'parallelization_factor': self.parallelization_factor,
+        })
+        return config
+
+    @property
+    def qkernel(self):
+        return self.kq(self._kernel.value)
+
+    @property
+    def qbias(self):
+        if self.bias is None:
+            return None
+        return self.bq(self._bias.value)

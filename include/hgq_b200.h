@@ -116,6 +116,40 @@ int hgq_quantize_bwd(const float *g, const float *x, const uint8_t *k, const flo
                      int round_mode, int overflow_mode, unsigned flags, void *workspace,
                      size_t workspace_bytes, void *stream);
 
+/* ---- K3: EBOPs ---------------------------------------------------------------------------- */
+
+/*
+ * EBOPs of a dense / einsum-dense layer and the gradient of its loss term.  Stands in for
+ * QDense._compute_ebops (layers/core/dense.py:70-80), QEinsumDense._compute_ebops
+ * (layers/core/einsum_dense.py:85-93) and the wrapper's `_ebops.assign(cast(ebops, uint32));
+ * add_loss(ebops * beta)` (layers/core/base.py:95-104).
+ *
+ *   e = scale * ( sum_{p,k,n} bw_in[p,k] bw_w[k,n] + mean(bw_bias) * out_size )
+ *
+ * bw_in [P, K]: input bitwidths at batch 1 (P = product of the free input axes), bw_w [K, N],
+ * bw_bias [n_bias] (n_bias = 0: no bias), all integer-valued fp32.  `beta` is a device scalar.
+ * Outputs (each may be NULL): ebops = uint32(e); ebops_f = float(e); loss = ebops_f * beta;
+ * d_bw_in / d_bw_w / d_bw_bias = d loss / d (the three bitwidth tensors).  The integer sum is
+ * exact.  K <= 10240.  One CTA; latency-bound.
+ */
+int hgq_ebops_dense(const float *bw_in, int64_t P, int64_t K, const float *bw_w, int64_t N,
+                    const float *bw_bias, int64_t n_bias, double out_size, double scale,
+                    const float *beta, uint32_t *ebops, float *ebops_f, float *loss, float *d_bw_in,
+                    float *d_bw_w, float *d_bw_bias, void *stream);
+
+/*
+ * EBOPs of a channels-last 2-D convolution: sum(conv(bw_in, bw_w)) * scale_main +
+ * mean(bw_bias) * out_size * scale_bias (layers/conv.py:91-102).  bw_in [H, W, C],
+ * bw_w [KH, KW, C, N]; (OH, OW) is the output size, pad_top / pad_left the implicit zero padding
+ * ('valid': 0).  Outputs as for hgq_ebops_dense.  KH*KW*C <= 10240.
+ */
+int hgq_ebops_conv2d(const float *bw_in, int H, int W, int C, const float *bw_w, int KH, int KW,
+                     int N, int OH, int OW, int stride_h, int stride_w, int dil_h, int dil_w,
+                     int pad_top, int pad_left, const float *bw_bias, int64_t n_bias, double out_size,
+                     double scale_main, double scale_bias, const float *beta, uint32_t *ebops,
+                     float *ebops_f, float *loss, float *d_bw_in, float *d_bw_w, float *d_bw_bias,
+                     void *stream);
+
 /* ---- standalone quantizer on host buffers ------------------------------------------------- */
 
 /*

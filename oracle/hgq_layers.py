@@ -1,0 +1,357 @@
+"""CPU oracle for the stateful quantizers and quantised layers.  TEST INFRASTRUCTURE, not product code.
+
+Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / reference legs may import this.
+
+Plain-PyTorch fp32 CPU restatement of the reference's Python, one class per reference class, each
+method citing the lines it follows.  It keeps the reference's formulation on purpose -- bitwidths
+broadcast to the activation shape, abs-max as a separate reduction, EBOPs as an fp32
+matmul/einsum/conv of bitwidth tensors, torch autograd for everything -- so that it checks the fused
+CUDA path against the reference's own op sequence, and so that timing it is timing what the
+reference does on a CPU.
+
+PARITY UNPINNED for gradient values and for forward edge cases: see oracle/fixed_point_ops.py.
+"""
+
+from __future__ import annotations
+
+from math import prod
+
+import torch
+import torch.nn.functional as F
+
+from . import fixed_point_ops as O
+
+EPS = 1e-7  # keras.config.epsilon()
+
+
+def _leaf(t, requires_grad):
+    t = torch.as_tensor(t).detach().clone().float()
+    return t.requires_grad_(bool(requires_grad))
+
+
+def minimal_i_given_xb(x, b, symmetric=False):
+    """src/hgq/quantizer/internal/fixed_point_quantizer.py:16-22"""
+    if symmetric:
+        return torch.ceil(torch.log2((x + EPS) / (1 - 2.0**-b + EPS)))
+    i_pos = torch.ceil(torch.log2((x + EPS) / (1 - 2.0**-b + EPS)))
+    i_neg = torch.ceil(torch.log2(-x - EPS))
+    return torch.where(b > 0, torch.where(x >= 0, i_pos, i_neg), torch.full_like(i_pos, 32.0))
+
+
+def minimal_i_given_xf(x, f, symmetric=False):
+    """src/hgq/quantizer/internal/fixed_point_quantizer.py:25-31"""
+    if symmetric:
+        return torch.ceil(torch.log2(torch.abs(x) + 2.0**-f))
+    i_pos = torch.ceil(torch.log2(x + 2.0**-f))
+    i_neg = torch.ceil(torch.log2(-x - EPS))
+    return torch.where(x >= 0, i_pos, i_neg)
+
+
+class OracleFixedQuantizer:
+    """FixedPointQuantizerKBI / KIF (fixed_point_quantizer.py:153-459) with state held in leaf tensors."""
+
+    def __init__(self, kind, k, i, bf, round_mode, overflow_mode, homogeneous_axis, i_decay_speed=float('inf'),
+                 is_weight=False, trainable=True, i_constraint=None, scaler=None, affine=None, qnoise_factor=None):
+        assert kind in ('kbi', 'kif')
+        self.kind = kind
+        self.round_mode, self.overflow_mode = round_mode.upper(), overflow_mode.upper()
+        self.homogeneous_axis = tuple(homogeneous_axis)
+        self.is_weight, self.trainable = is_weight, trainable
+        self.i_constraint = i_constraint
+        self.scaler, self.affine, self.qnoise_factor = scaler, affine, qnoise_factor
+        self._k = torch.as_tensor(k).detach().clone().to(torch.uint8)
+        i_trainable = trainable and self.overflow_mode != 'WRAP'
+        self._i = _leaf(i, i_trainable)
+        if kind == 'kbi':
+            self._b = _leaf(bf, trainable)
+        else:
+            self._f = _leaf(bf, trainable)
+        self.i_decay_speed = torch.tensor(float(i_decay_speed))
+        self.q = O.get_fixed_quantizer(self.round_mode, self.overflow_mode)
+        self.symmetric = self.overflow_mode.endswith('SYM')
+
+    # -- properties (:244-265, :431-449)
+    @property
+    def k(self):
+        return self._k.float()
+
+    @property
+    def i(self):
+        return O.round_conv(self._i)
+
+    @property
+    def b(self):
+        return O.round_conv(self._b) if self.kind == 'kbi' else torch.relu(self.i + self.f)
+
+    @property
+    def f(self):
+        return self.b - self.i if self.kind == 'kbi' else O.round_conv(self._f)
+
+    @property
+    def kif(self):
+        return self.k, self.i, self.f
+
+    @property
+    def bits(self):  # :92-97
+        return self.b if self.overflow_mode != 'SAT' else self.b + self.k
+
+    def trainable_leaves(self):
+        out = {}
+        for name in ('_b', '_i', '_f'):
+            t = getattr(self, name, None)
+            if t is not None and t.requires_grad:
+                out[name[1:]] = t
+        return out
+
+    # -- bitwidth mapper (base.py:182-189)
+    def _absmax(self, x):
+        ax = self.homogeneous_axis
+        return torch.amax(torch.abs(x), dim=ax, keepdim=True) if ax else torch.abs(x)
+
+    def _anyneg(self, x):
+        ax = self.homogeneous_axis
+        return torch.amax(x < 0, dim=ax, keepdim=True) if ax else (x < 0)
+
+    def bits_(self, shape):  # quantizer.py:86-88
+        return torch.broadcast_to(self.bits, tuple(shape))
+
+    # -- calls
+    def _base_call(self, x, training):  # :142-150
+        k, i, f = self.kif
+        k, i, f = (torch.broadcast_to(t, x.shape) for t in (k, i, f))
+        ret = self.q(x, k, i, f, training is True, None)
+        if not training:
+            ret = torch.where(k + i + f > 0, ret, torch.zeros_like(ret))
+        return ret
+
+    def _internal_call(self, x, training):
+        wrap = self.overflow_mode == 'WRAP' and self.trainable
+        if self.kind == 'kbi':  # :277-307
+            if wrap:
+                if training or training == 'tracing':
+                    new_i = minimal_i_given_xb(self._absmax(x.detach()), self.b.detach(), self.symmetric)
+                    if training:
+                        new_i = torch.maximum(self._i.detach() - self.i_decay_speed, new_i)
+                        if self.i_constraint is not None:
+                            new_i = self.i_constraint(new_i)
+                        self._i.data.copy_(new_i)
+                        return self.q.round(x, torch.broadcast_to(self.f, x.shape), False, None)
+                    new_i = torch.maximum(self.i.detach(), new_i)
+                    if self.i_constraint is not None:
+                        new_i = self.i_constraint(new_i)
+                    f = torch.broadcast_to(self.b.detach() - new_i, x.shape)
+                    r = self.q.round(x, f, False, None)
+                    new_k = self._anyneg(r.detach()) & (self.b.detach() > 0)
+                    self._k = (self._k.bool() | new_k).to(torch.uint8)
+                    self._i.data.copy_(new_i)
+                    return r
+                if self.is_weight and self.round_mode == 'RND':
+                    return self.q.round(x, torch.broadcast_to(self.f, x.shape), False, None)
+            return self._base_call(x, training is True)
+        # kif :401-429
+        if wrap:
+            f = torch.broadcast_to(self.f, x.shape)
+            r = self.q.round(x, f, False, None)
+            if training or training == 'tracing':
+                _new_i = minimal_i_given_xf(self._absmax(r.detach()), self.f.detach(), self.symmetric)
+                if training:
+                    new_i = torch.maximum(self._i.detach() - self.i_decay_speed, _new_i)
+                    self._i.data.copy_(new_i)
+                else:
+                    if self.i_constraint is not None:
+                        _new_i = self.i_constraint(_new_i)
+                    new_i = torch.maximum(self.i.detach(), _new_i)
+                    self._k = (self._k.bool() | self._anyneg(r.detach())).to(torch.uint8)
+                    self._i.data.copy_(new_i)
+                return r
+            if self.is_weight:
+                return r
+        return self._base_call(x, training is True)
+
+    def __call__(self, x, training=None):  # Quantizer.call, quantizer.py:49-60
+        inputs = x / self.scaler if self.scaler is not None else x
+        out = self._internal_call(inputs, training)
+        if self.scaler is not None:
+            out = out * self.scaler
+        if self.qnoise_factor is not None and training:
+            out = inputs + self.qnoise_factor * (out - inputs)
+        if self.affine is not None:
+            out = out * self.affine[0] + self.affine[1]
+        return out
+
+
+class OracleQLayer:
+    """The EBOPs / output-quantizer wrapper of QLayerMeta (layers/core/base.py:88-110)."""
+
+    def __init__(self, iq, kq, bq, oq, beta, ebops_factor, enable_ebops, activation):
+        self.iq, self.kq, self.bq, self.oq = iq, kq, bq, oq
+        self.beta = torch.tensor(float(beta))
+        self.ebops_factor = ebops_factor
+        self.enable_ebops = enable_ebops
+        self.activation = activation
+        self.ebops = torch.zeros((), dtype=torch.uint32)
+        self.losses: list[torch.Tensor] = []
+
+    def quantizers(self):
+        return {n: q for n, q in (('iq', self.iq), ('kq', self.kq), ('bq', self.bq), ('oq', self.oq)) if q is not None}
+
+    def __call__(self, x, training=None):
+        self.losses = []
+        r = self.call(x, training)
+        if (training or training == 'tracing') and self.enable_ebops:
+            shape = (1,) + tuple(x.shape[1:])
+            ebops = self._compute_ebops(shape) * self.ebops_factor
+            self.ebops = ebops.detach().to(torch.uint32)
+            self.ebops_f = ebops.detach()
+            self.losses.append(ebops * self.beta)
+        if self.oq is not None:
+            r = self.oq(r, training)
+        return r
+
+    def _act(self, x):
+        if self.activation is None:
+            return x
+        if self.activation == 'relu':
+            return torch.relu(x)
+        raise NotImplementedError(self.activation)
+
+
+class OracleQDense(OracleQLayer):
+    """QDense (layers/core/dense.py:60-80)."""
+
+    def __init__(self, kernel, bias, n_parallel, parallelization_factor, **kw):
+        super().__init__(**kw)
+        self.kernel = _leaf(kernel, True)
+        self.bias = _leaf(bias, True) if bias is not None else None
+        self.n_parallel, self.pf = n_parallel, parallelization_factor
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        y = torch.matmul(x, self.kq(self.kernel, training))
+        if self.bias is not None:
+            y = y + self.bq(self.bias, training)
+        return self._act(y)
+
+    def _compute_ebops(self, shape):
+        bw_inp = self.iq.bits_(shape)
+        bw_ker = self.kq.bits_(self.kernel.shape)
+        ebops = torch.sum(torch.matmul(bw_inp, bw_ker))
+        if self.bq is not None:
+            bw_bias = self.bq.bits_(self.bias.shape)
+            size = float(prod(shape[:-1]) * self.kernel.shape[-1])
+            ebops = ebops + torch.mean(bw_bias) * size
+        return ebops * self.pf / self.n_parallel
+
+
+class OracleQEinsumDense(OracleQLayer):
+    """QEinsumDense (layers/core/einsum_dense.py:72-93)."""
+
+    def __init__(self, equation, kernel, bias, full_output_shape, n_parallel, parallelization_factor, **kw):
+        super().__init__(**kw)
+        self.equation = equation
+        self.kernel = _leaf(kernel, True)
+        self.bias = _leaf(bias, True) if bias is not None else None
+        self.full_output_shape = full_output_shape
+        self.n_parallel, self.pf = n_parallel, parallelization_factor
+
+    def call(self, x, training):
+        qk = self.kq(self.kernel, training)
+        if self.iq is not None:
+            x = self.iq(x, training)
+        y = torch.einsum(self.equation, x, qk)
+        if self.bias is not None:
+            y = y + self.bq(self.bias, training)
+        return self._act(y)
+
+    def _compute_ebops(self, shape):
+        bw_inp = self.iq.bits_(shape)
+        bw_ker = self.kq.bits_(self.kernel.shape)
+        ebops = torch.einsum(self.equation.split('->')[0] + '->', bw_inp, bw_ker)
+        if self.bq is not None:
+            bw_bias = self.bq.bits_(self.bias.shape)
+            size = float(prod(self.full_output_shape[1:]))
+            ebops = ebops + torch.mean(bw_bias) * size
+        return ebops * self.pf / self.n_parallel
+
+
+class OracleQConv2D(OracleQLayer):
+    """QConv2D (layers/conv.py:72-102), channels_last."""
+
+    def __init__(self, kernel, bias, strides, dilation, pads, n_parallel, parallelization_factor, **kw):
+        super().__init__(**kw)
+        self.kernel = _leaf(kernel, True)
+        self.bias = _leaf(bias, True) if bias is not None else None
+        self.strides, self.dilation, self.pads = strides, dilation, pads
+        self.n_parallel, self.pf = n_parallel, parallelization_factor
+
+    def conv(self, x, w):
+        (pt, pb), (pl, pr) = self.pads
+        x = x.permute(0, 3, 1, 2)
+        if pt or pb or pl or pr:
+            x = F.pad(x, (pl, pr, pt, pb))
+        return F.conv2d(x, w.permute(3, 2, 0, 1), stride=self.strides, dilation=self.dilation).permute(0, 2, 3, 1)
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        y = self.conv(x, self.kq(self.kernel, training))
+        if self.bias is not None:
+            y = y + self.bq(self.bias, training).reshape(1, 1, 1, -1)
+        return self._act(y)
+
+    def _compute_ebops(self, shape):
+        bw_inp = self.iq.bits_(shape)
+        bw_ker = self.kq.bits_(self.kernel.shape)
+        ebops = torch.sum(self.conv(bw_inp, bw_ker))
+        ebops = ebops * (self.pf / self.n_parallel)
+        if self.bq is not None:
+            size = float(prod(shape[:-1]) * self.kernel.shape[-1])
+            bw_bias = self.bq.bits_(self.bias.shape)
+            ebops = ebops + torch.mean(bw_bias) * size
+        return ebops
+
+
+# ---- building an oracle twin of a product object (reads variables by their reference names) ----
+def _np(v):
+    return v.value.detach().cpu()
+
+
+def mirror_quantizer(q):
+    """Oracle twin of a hgq2_b200 ``Quantizer`` (or None)."""
+    if q is None:
+        return None
+    iq = q.quantizer
+    if getattr(iq, '__dummy__', False):
+        raise NotImplementedError('dummy quantizer')
+    cfg = q.config
+    kind = cfg.q_type
+    bf = _np(iq._b) if kind == 'kbi' else _np(iq._f)
+    decay = float(_np(iq._i_decay_speed)) if iq.overflow_mode == 'WRAP' else float('inf')
+    return OracleFixedQuantizer(
+        kind, _np(iq._k), _np(iq._i), bf, iq.round_mode, iq.overflow_mode, iq.bw_mapper.homogeneous_axis, decay,
+        iq._is_weight, iq.trainable, iq.i_constraint, q.scaler, q.affine, q.qnoise_factor,
+    )
+
+
+def mirror_layer(layer):
+    """Oracle twin of a built hgq2_b200 QDense / QEinsumDense / QConv2D."""
+    name = type(layer).__name__
+    common = dict(
+        iq=mirror_quantizer(layer.iq) if layer.enable_iq else None, kq=mirror_quantizer(layer.kq),
+        bq=mirror_quantizer(layer.bq), oq=mirror_quantizer(layer.oq) if layer.enable_oq else None,
+        beta=float(layer.beta) if layer.enable_ebops else 0.0, ebops_factor=layer.ebops_factor,
+        enable_ebops=layer.enable_ebops, activation=layer.get_config()['activation'],
+    )
+    kernel = _np(layer._kernel)
+    bias = _np(layer._bias) if layer.bias is not None else None
+    if name == 'QDense':
+        return OracleQDense(kernel, bias, layer.n_parallel, layer.parallelization_factor, **common)
+    if name == 'QEinsumDense':
+        return OracleQEinsumDense(layer.equation, kernel, bias, layer.full_output_shape, layer.n_parallel,
+                                  layer.parallelization_factor, **common)
+    if name == 'QConv2D':
+        h, w = layer._built_hw
+        return OracleQConv2D(kernel, bias, layer.strides, layer.dilation_rate, layer._pads(h, w), layer.n_parallel,
+                             layer.parallelization_factor, **common)
+    raise NotImplementedError(name)
