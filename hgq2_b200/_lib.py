@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_double, c_int, c_int64, c_size_t, c_uint, c_void_p
+from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_size_t, c_uint, c_void_p
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
@@ -55,6 +55,7 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_int, c_int, c_int, c_void_p] + [c_int] * 11 + [c_void_p, c_int64, c_double, c_double, c_double, c_void_p]
         + [c_void_p] * 7,
     ),
+    'hgq_adam_step': (c_int, [c_void_p] * 7 + [c_int64] + [c_float] * 5 + [c_void_p, c_void_p]),
     'hgq_quantize_host_workspace': (c_size_t, [c_int64]),
     'hgq_quantize_fwd_bwd_host': (
         c_int,

@@ -307,6 +307,52 @@ class Layer(nn.Module):
         return {'name': self.name, 'trainable': self.trainable, 'dtype': self.dtype}
 
 
+class Lambda(Layer):
+    """Wraps a tensor function as a layer (keras.layers.Lambda)."""
+
+    def __init__(self, function, **kwargs):
+        super().__init__(**kwargs)
+        self.function = function
+
+    def call(self, inputs):
+        return self.function(inputs)
+
+
+class Flatten(Layer):
+    def call(self, inputs):
+        return inputs.reshape(inputs.shape[0], -1)
+
+
+class MaxPooling2D(Layer):
+    """channels_last 2-D max pooling, 'valid' padding."""
+
+    def __init__(self, pool_size=(2, 2), strides=None, **kwargs):
+        super().__init__(**kwargs)
+        self.pool_size = (pool_size, pool_size) if isinstance(pool_size, int) else tuple(pool_size)
+        self.strides = self.pool_size if strides is None else ((strides, strides) if isinstance(strides, int) else tuple(strides))
+
+    def call(self, inputs):
+        y = torch.nn.functional.max_pool2d(inputs.permute(0, 3, 1, 2), self.pool_size, self.strides)
+        return y.permute(0, 2, 3, 1).contiguous()
+
+
+class Sequential(Layer):
+    """A linear stack of layers (keras.Sequential)."""
+
+    def __init__(self, layers=(), **kwargs):
+        super().__init__(**kwargs)
+        self.layers = nn.ModuleList(layer if isinstance(layer, Layer) else Lambda(layer) for layer in layers)
+
+    def build(self, input_shape):
+        self.built = True
+
+    def call(self, inputs, training=None):
+        x = inputs
+        for layer in self.layers:
+            x = layer(x, training=training)
+        return x
+
+
 _training_arg_cache: dict = {}
 
 
@@ -362,6 +408,6 @@ def activation_name(spec) -> str | None:
 
 numbers = (int, float, np.integer, np.floating)
 
-__all__ = ['Layer', 'Variable', 'Initializer', 'Constant', 'Zeros', 'Ones', 'GlorotUniform', 'RandomNormal',
+__all__ = ['Layer', 'Sequential', 'Lambda', 'Flatten', 'MaxPooling2D', 'Variable', 'Initializer', 'Constant', 'Zeros', 'Ones', 'GlorotUniform', 'RandomNormal',
            'get_initializer', 'get_activation', 'activation_name', 'epsilon', 'numbers', 'default_device',
            'set_default_device', 'Sequence']

@@ -14,6 +14,11 @@ from ._functions import EbopsConv2dFn
 from .core.base import QLayerBaseSingleInput
 
 
+# The library convolution must multiply fp32 operands at full precision in forward *and* backward (the reference's
+# tests pin matmul precision to 'highest'); cuDNN's TF32 default would round operands to 10 mantissa bits.
+torch.backends.cudnn.allow_tf32 = False
+
+
 def _pair(v):
     return (int(v), int(v)) if isinstance(v, int) else tuple(int(a) for a in v)
 
@@ -112,8 +117,7 @@ class QConv2D(QLayerBaseSingleInput):
         x = inputs.permute(0, 3, 1, 2)
         if pt or pb or pl or pr:
             x = F.pad(x, (pl, pr, pt, pb))
-        with torch.backends.cudnn.flags(allow_tf32=False):  # fp32 accumulate of fp32 operands, as the reference
-            y = F.conv2d(x, kernel.permute(3, 2, 0, 1), stride=self.strides, dilation=self.dilation_rate)
+        y = F.conv2d(x, kernel.permute(3, 2, 0, 1), stride=self.strides, dilation=self.dilation_rate)
         return y.permute(0, 2, 3, 1)
 
     def call(self, inputs, training=None):

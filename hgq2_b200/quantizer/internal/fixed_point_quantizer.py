@@ -20,6 +20,17 @@ from ..fixed_point_ops import get_fixed_quantizer, round_conv
 from .base import DefaultBitwidthMapper, TrainableQuantizerBase, numbers
 
 
+# Set by hgq2_b200.train.DataParallel: a function applied to the abs-max statistics of *activations* before they
+# update the integer bits (a MAX all-reduce over the data-parallel ranks).  None = single process.
+absmax_sync_hook = None
+
+
+def _sync_absmax(absmax, inputs):
+    if absmax_sync_hook is not None and not isinstance(inputs, torch.nn.Parameter):
+        return absmax_sync_hook(absmax.contiguous())
+    return absmax
+
+
 def minimal_i_given_xb(x, b, symmetric=False):
     """Fewest integer bits that hold |x| with b total bits (reference :16-22)."""
     eps = epsilon()
@@ -218,7 +229,8 @@ class FixedPointQuantizerKBI(FixedPointQuantizerBase):
     def call(self, inputs, training=None):
         if self.overflow_mode == 'WRAP' and self.trainable:
             if training or training == 'tracing':  # noqa: E712 -- training may be a wrapper object
-                new_i = self.get_minimal_i(inputs.detach())
+                xr = _sync_absmax(self.bw_mapper.x_to_bw_absmax(inputs.detach()), inputs)
+                new_i = minimal_i_given_xb(xr, self.b.detach(), self.symmetric)
                 if training:
                     new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, new_i)
                     if self._i.constraint is not None:
@@ -294,7 +306,7 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
             f = self.f
             if training or training == 'tracing':  # noqa: E712
                 rinputs, absmax = self._round_and_absmax(inputs, f)
-                _new_i = minimal_i_given_xf(absmax, f.detach(), self.symmetric)
+                _new_i = minimal_i_given_xf(_sync_absmax(absmax, inputs), f.detach(), self.symmetric)
                 if training:
                     new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i)
                     self._i.assign(new_i)

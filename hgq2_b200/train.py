@@ -1,0 +1,186 @@
+"""The QAT training step: flat parameter bucket, fused Adam, data-parallel gradient exchange.
+
+What Keras' torch trainer does around the layers of the hot path (forward with ``training=True``,
+task loss + ``sum(model.losses)``, backward, optimizer update, constraints) is restated here on one
+flat fp32 bucket:
+
+* every trainable variable of the model becomes a view into ``params``; its ``.grad`` is a view into
+  ``grads``.  One memset clears the gradients, one NCCL all-reduce averages them over the ranks, one
+  fused kernel (``hgq_adam_step``) applies Adam, the MonoL1 regularisers and the MinMax constraints.
+* data parallelism shards the batch; the only other exchange is a MAX all-reduce of the per-column
+  abs-max statistics that drive the WRAP integer-bit tracking, so that every rank keeps identical
+  quantizer state (and therefore identical EBOPs).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .backend import Layer, Variable
+from .constraints import Constant as ConstantConstraint
+from .constraints import Max, Min, MinMax
+from .quantizer.internal import fixed_point_quantizer as _fpq
+from .regularizers import MonoL1
+
+
+class FlatState:
+    """Packs the trainable variables of ``model`` into one fp32 buffer (plus a matching gradient buffer and the
+    per-element constraint / regulariser tables the fused optimizer reads)."""
+
+    def __init__(self, model: Layer):
+        self.variables: list[Variable] = [v for v in model.trainable_variables]
+        if not self.variables:
+            raise ValueError('model has no trainable variables (is it built?)')
+        dev = self.variables[0].value.device
+        sizes = [v.value.numel() for v in self.variables]
+        # 4-element alignment keeps every view 16-byte aligned for the vectorised kernels
+        self.offsets, off = [], 0
+        for n in sizes:
+            self.offsets.append(off)
+            off += (n + 3) // 4 * 4
+        self.n = off
+        self.params = torch.zeros(self.n, dtype=torch.float32, device=dev)
+        self.grads = torch.zeros(self.n, dtype=torch.float32, device=dev)
+        lo = torch.full((self.n,), -math.inf, dtype=torch.float32)
+        hi = torch.full((self.n,), math.inf, dtype=torch.float32)
+        l1 = torch.zeros(self.n, dtype=torch.float32)
+        for v, o, n in zip(self.variables, self.offsets, sizes):
+            view = self.params[o:o + n].view(v.value.shape)
+            view.copy_(v.value.detach())
+            v.value.data = view
+            v.value.grad = self.grads[o:o + n].view(v.value.shape)
+            c = v.constraint
+            if c is None:
+                pass
+            elif isinstance(c, MinMax):
+                lo[o:o + n], hi[o:o + n] = c.min_value, c.max_value
+            elif isinstance(c, Min):
+                lo[o:o + n] = c.min_value
+            elif isinstance(c, Max):
+                hi[o:o + n] = c.max_value
+            elif isinstance(c, ConstantConstraint):
+                lo[o:o + n] = hi[o:o + n] = c.value
+            else:
+                raise NotImplementedError(f'constraint {type(c).__name__} on {v.path} cannot be fused')
+            r = v.regularizer
+            if r is None:
+                pass
+            elif isinstance(r, MonoL1):
+                l1[o:o + n] = r.l1
+            else:
+                raise NotImplementedError(f'regularizer {type(r).__name__} on {v.path} cannot be fused')
+        self.lo, self.hi, self.l1 = lo.to(dev), hi.to(dev), l1.to(dev)
+
+    def zero_grad(self) -> None:
+        self.grads.zero_()
+
+    def check_views(self) -> None:
+        """Autograd must have accumulated into the bucket views, not replaced them."""
+        base = self.grads.data_ptr()
+        for v, o in zip(self.variables, self.offsets):
+            g = v.value.grad
+            if g is None or g.data_ptr() != base + 4 * o:
+                raise RuntimeError(f'gradient of {v.path} left the flat bucket')
+
+    def regularization_loss(self) -> torch.Tensor:
+        return torch.dot(self.l1, self.params)
+
+
+class FusedAdam:
+    """Keras-flavoured Adam on a ``FlatState`` through the C-ABI kernel (regulariser and constraints included)."""
+
+    def __init__(self, state: FlatState, learning_rate=1e-3, beta_1=0.9, beta_2=0.999, epsilon=1e-7):
+        self.state = state
+        self.lr, self.b1, self.b2, self.eps = learning_rate, beta_1, beta_2, epsilon
+        dev = state.params.device
+        self.m = torch.zeros_like(state.params)
+        self.v = torch.zeros_like(state.params)
+        self.step_count = torch.zeros((), dtype=torch.int64, device=dev)
+
+    def step(self, grad_scale: float = 1.0) -> None:
+        s = self.state
+        _lib.require_cuda(s.params)
+        with torch.cuda.device(s.params.device):
+            st = _lib.lib().hgq_adam_step(
+                s.params.data_ptr(), s.grads.data_ptr(), self.m.data_ptr(), self.v.data_ptr(), s.lo.data_ptr(),
+                s.hi.data_ptr(), s.l1.data_ptr(), s.n, self.lr, self.b1, self.b2, self.eps, grad_scale,
+                self.step_count.data_ptr(), _lib.stream_handle(),
+            )
+        _lib.check(st, 'hgq_adam_step')
+
+
+def shard_batch(n: int, rank: int, world: int) -> slice:
+    """Contiguous, equal shard of a batch of n samples (n must divide evenly so per-rank means average correctly)."""
+    if n % world != 0:
+        raise ValueError(f'batch {n} does not divide over {world} ranks')
+    per = n // world
+    return slice(rank * per, (rank + 1) * per)
+
+
+class DataParallel:
+    """Batch-sharded training over the ranks of a torch.distributed process group (NCCL on GPUs).
+
+    ``sync_gradients`` averages the flat gradient bucket; ``absmax_sync`` is installed as the hook the WRAP
+    quantizers call on their abs-max statistics (a MAX all-reduce), which keeps ``i`` -- and with it the EBOPs
+    term -- identical on every rank and equal to what one rank would compute on the whole batch.
+    """
+
+    def __init__(self, group=None):
+        if not dist.is_initialized():
+            raise RuntimeError('torch.distributed is not initialised')
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def sync_gradients(self, grads: torch.Tensor) -> None:
+        if self.world > 1:
+            dist.all_reduce(grads, op=dist.ReduceOp.SUM, group=self.group)
+            grads.div_(self.world)
+
+    def absmax_sync(self, absmax: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(absmax, op=dist.ReduceOp.MAX, group=self.group)
+        return absmax
+
+    def __enter__(self):
+        self._prev = _fpq.absmax_sync_hook
+        _fpq.absmax_sync_hook = self.absmax_sync
+        return self
+
+    def __exit__(self, *exc):
+        _fpq.absmax_sync_hook = self._prev
+
+
+class Trainer:
+    """One model, one flat bucket, one fused optimizer; ``step(x, y)`` runs a full QAT step and returns the loss."""
+
+    def __init__(self, model: Layer, loss_fn, learning_rate=1e-3, dp: DataParallel | None = None):
+        self.model = model
+        self.loss_fn = loss_fn
+        self.dp = dp
+        self.state = FlatState(model)
+        self.opt = FusedAdam(self.state, learning_rate=learning_rate)
+
+    def forward_backward(self, x, y):
+        self.state.zero_grad()
+        pred = self.model(x, training=True)
+        task = self.loss_fn(pred, y)
+        total = task
+        for extra in self.model._losses:  # the beta * EBOPs terms; the weight regularisers are fused into the optimizer
+            total = total + extra
+        total.backward()
+        return task.detach(), total.detach() + self.state.regularization_loss()
+
+    def step(self, x, y):
+        if self.dp is not None:
+            with self.dp:
+                task, total = self.forward_backward(x, y)
+            self.dp.sync_gradients(self.state.grads)
+        else:
+            task, total = self.forward_backward(x, y)
+        self.opt.step()
+        return total

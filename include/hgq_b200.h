@@ -150,6 +150,23 @@ int hgq_ebops_conv2d(const float *bw_in, int H, int W, int C, const float *bw_w,
                      float *ebops_f, float *loss, float *d_bw_in, float *d_bw_w, float *d_bw_bias,
                      void *stream);
 
+/* ---- optimizer step ------------------------------------------------------------------------ */
+
+/*
+ * Adam over one flat bucket of n fp32 parameters, with the bitwidth regulariser and the variable
+ * constraints folded in.  Stands in for what Keras' trainer does after backward for the variables
+ * HGQ2 creates: optimizer.apply(grads, trainable_variables) followed by variable.constraint(...)
+ * (the constraints of src/hgq/constraints/__init__.py:11-69 are attached at
+ * fixed_point_quantizer.py:225-241,382-397), and the gradient of the MonoL1 regulariser
+ * (src/hgq/regularizers/__init__.py:8-17).
+ *   g' = g * grad_scale + l1;  Keras Adam update with (lr, beta1, beta2, eps);  w = clamp(w, lo, hi)
+ * lo / hi / l1 are per-element arrays and may be NULL.  `step` is a device counter (starts at 0)
+ * that the call reads for the bias correction and then increments.
+ */
+int hgq_adam_step(float *w, const float *g, float *m, float *v, const float *lo, const float *hi,
+                  const float *l1, int64_t n, float lr, float beta1, float beta2, float eps,
+                  float grad_scale, long long *step, void *stream);
+
 /* ---- standalone quantizer on host buffers ------------------------------------------------- */
 
 /*

@@ -1,0 +1,114 @@
+"""Full QAT steps (forward, backward, fused Adam, constraints) of the benchmark models against the CPU oracle."""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import train as OT
+
+pytestmark = pytest.mark.gpu
+
+
+def close(a, b, rtol, what):
+    a = a.detach().cpu().double().numpy()
+    b = b.detach().cpu().double().numpy()
+    scale = max(np.abs(b).max(), 1e-30)
+    err = np.abs(a - b).max() / scale
+    assert err <= rtol, f'{what}: error {err:.3e} (relative to max |ref| = {scale:.3e}) exceeds {rtol}'
+
+
+def ce(pred, y):
+    return F.cross_entropy(pred, y)
+
+
+def run_steps(builder, x_np, y_np, steps=3, beta0=1e-5, lr=1e-3):
+    from hgq2_b200 import workloads
+    from hgq2_b200.train import Trainer
+
+    model = workloads.build(builder(beta0=beta0))
+    twin, pairs = OT.mirror_model(model)
+    oopt = OT.OracleAdam(pairs, lr=lr)
+    tr = Trainer(model, ce, learning_rate=lr)
+    x, y = torch.from_numpy(x_np).cuda(), torch.from_numpy(y_np).cuda()
+    xc, yc = torch.from_numpy(x_np), torch.from_numpy(y_np)
+    for s in range(steps):
+        # forward + backward on both sides: loss, EBOPs and every gradient before the optimizer touches them
+        _, loss = tr.forward_backward(x, y)
+        tr.state.check_views()
+        pred = twin(xc, training=True)
+        oloss = ce(pred, yc) + sum(twin.losses) + oopt.regularization_loss()
+        oloss.backward()
+        close(loss, oloss, 1e-5, f'loss at step {s}')
+        for pl, ol in zip([l for l in model.layers if hasattr(l, '_ebops')], twin.qlayers()):
+            assert int(pl.ebops.item()) == int(ol.ebops.item()), f'EBOPs of {pl.name} at step {s}'
+        for leaf, var, _, _ in pairs:
+            g = var.value.grad
+            if var.regularizer is not None:  # the product adds the regulariser's constant gradient inside the optimizer
+                g = g + var.regularizer.l1
+            close(g, leaf.grad, 1e-4, f'gradient of {var.path} at step {s}')
+        tr.opt.step()
+        oopt.step()
+        # Adam normalises each element's step to ~lr whatever the gradient's size, so an element whose gradient is
+        # at the noise floor may move differently; all others must agree closely
+        for leaf, var, _, _ in pairs:
+            d = (var.value.detach().cpu() - leaf.detach()).abs()
+            scale = float(leaf.detach().abs().max()) + 1e-30
+            assert float(d.max()) <= 2.0 * lr * (s + 1), f'{var.path} after step {s}: {float(d.max())}'
+            frac_bad = float((d > 1e-5 * scale + 1e-7).float().mean())
+            assert frac_bad <= 5e-3, f'{var.path} after step {s}: {frac_bad:.4f} of the elements moved differently'
+    return model, twin
+
+
+def test_jet_tagger_mlp_steps():
+    from hgq2_b200 import workloads
+
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((2048, 16)).astype(np.float32)
+    y = np.random.default_rng(2).integers(0, 5, 2048)
+    run_steps(workloads.jet_tagger_mlp, x, y, steps=3, beta0=1e-5)
+
+
+def test_particle_tagger_steps():
+    from hgq2_b200 import workloads
+
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((96, 64, 16)).astype(np.float32)
+    y = np.random.default_rng(2).integers(0, 5, 96)
+    run_steps(workloads.particle_tagger, x, y, steps=2)
+
+
+def test_small_cnn_steps():
+    from hgq2_b200 import workloads
+
+    rng = np.random.default_rng(1)
+    x = rng.uniform(0, 1, (48, 32, 32, 3)).astype(np.float32)
+    y = np.random.default_rng(2).integers(0, 10, 48)
+    run_steps(workloads.small_cnn, x, y, steps=2)
+
+
+def test_adam_kernel_matches_keras_rule():
+    from hgq2_b200 import _lib
+
+    n = 1003
+    g = torch.Generator().manual_seed(0)
+    w0, gr = torch.randn(n, generator=g), torch.randn(n, generator=g)
+    lo, hi = torch.full((n,), -0.5), torch.full((n,), 0.7)
+    l1 = torch.full((n,), 1e-3)
+    w, m, v = w0.clone().cuda(), torch.zeros(n).cuda(), torch.zeros(n).cuda()
+    gd, lod, hid, l1d = gr.cuda(), lo.cuda(), hi.cuda(), l1.cuda()  # keep the device copies alive across the calls
+    step = torch.zeros((), dtype=torch.int64).cuda()
+    wr, mr, vr = w0.clone().double(), torch.zeros(n).double(), torch.zeros(n).double()
+    for t in range(1, 4):
+        st = _lib.lib().hgq_adam_step(w.data_ptr(), gd.data_ptr(), m.data_ptr(), v.data_ptr(), lod.data_ptr(),
+                                      hid.data_ptr(), l1d.data_ptr(), n, 1e-3, 0.9, 0.999, 1e-7, 0.5,
+                                      step.data_ptr(), _lib.stream_handle())
+        assert st == 0
+        ge = gr.double() * 0.5 + l1.double()
+        mr = 0.9 * mr + 0.1 * ge
+        vr = 0.999 * vr + 0.001 * ge * ge
+        alpha = 1e-3 * (1 - 0.999**t) ** 0.5 / (1 - 0.9**t)
+        wr = torch.clamp(wr - alpha * mr / (vr.sqrt() + 1e-7), -0.5, 0.7)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(w.cpu().numpy(), wr.numpy(), rtol=2e-5, atol=1e-7)
+    assert int(step.item()) == 3
