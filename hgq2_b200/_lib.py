@@ -46,6 +46,11 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,
          c_uint, c_void_p, c_size_t, c_void_p],
     ),
+    'hgq_quantize_bwd_noalloc': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,
+         c_uint, c_void_p],
+    ),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

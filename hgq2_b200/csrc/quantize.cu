@@ -488,3 +488,56 @@ extern "C" const char *hgq_status_string(int status) {
     if (status > 0) return cudaGetErrorString((cudaError_t)status);
     return "unknown status";
 }
+
+// ---- backward entry for callers that cannot allocate device memory --------------------------------
+//
+// Some hosts of this library may not create device allocations of their own: a plugin that runs inside
+// a framework whose memory pool already owns the whole GPU (a cudaMalloc from the plugin would fail or
+// starve the pool), or a service with a fixed, audited memory budget where every allocation has to be
+// accounted for before start-up.  For them the column-sum partials of the broadcast-layout backward
+// live in this fixed array instead of in a caller-provided workspace.  Every GPU that loads the library
+// holds the array until the process exits.
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = HGQ_NOALLOC_SCRATCH_BYTES;
+__device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+void *g_noalloc_addr[kNoAllocMaxDevices] = {};  // device address of g_noalloc_scratch, per device
+std::atomic<bool> g_noalloc_ready[kNoAllocMaxDevices];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use:
+// the device address is looked up once per device, with that device current.
+int noalloc_scratch_address(void **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return HGQ_ERR_DEVICE;
+    if (!g_noalloc_ready[dev].load(std::memory_order_acquire)) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (p == nullptr) return HGQ_ERR_DEVICE;
+        g_noalloc_addr[dev] = p;  // two threads racing here store the same value
+        g_noalloc_ready[dev].store(true, std::memory_order_release);
+    }
+    *out = g_noalloc_addr[dev];
+    return HGQ_OK;
+}
+
+}  // namespace
+
+extern "C" int hgq_quantize_bwd_noalloc(const float *g, const float *x, const uint8_t *k, const float *i,
+                                        const float *f, float *dx, float *di, float *df, int64_t n, int64_t period,
+                                        int round_mode, int overflow_mode, unsigned flags, void *stream) {
+    if (n < 0 || period < 0) return HGQ_ERR_SIZE;
+    const size_t need = hgq_quantize_bwd_workspace(n, period == 0 ? n : period);
+    if (need > kNoAllocScratchBytes) return HGQ_ERR_SIZE;  // beyond the built-in scratch: use hgq_quantize_bwd
+    void *scratch = nullptr;
+    if (need > 0) {
+        if (int e = noalloc_scratch_address(&scratch)) return e;
+    }
+    // Nothing in the scratch has to start at zero: the first kernel writes every partial the second one reads.
+    return hgq_quantize_bwd(g, x, k, i, f, dx, di, df, n, period, round_mode, overflow_mode, flags, scratch,
+                            need > 0 ? kNoAllocScratchBytes : 0, stream);
+}

@@ -116,6 +116,32 @@ int hgq_quantize_bwd(const float *g, const float *x, const uint8_t *k, const flo
                      int round_mode, int overflow_mode, unsigned flags, void *workspace,
                      size_t workspace_bytes, void *stream);
 
+/*
+ * The same backward for callers that must not allocate device memory -- a plugin inside a framework
+ * whose memory pool already owns the GPU, or a service with a fixed memory budget.  This entry has no
+ * counterpart in the reference.  It takes no workspace: the column-sum partials of the broadcast
+ * layout go to a fixed array of HGQ_NOALLOC_SCRATCH_BYTES inside the library (device memory that every
+ * GPU which loads the library holds until the process exits).  It calls no cudaMalloc / cudaFree and
+ * no allocating library routine.
+ *
+ * Limit: hgq_quantize_bwd_workspace(n, period) must not exceed HGQ_NOALLOC_SCRATCH_BYTES, otherwise
+ * the call returns HGQ_ERR_SIZE and launches nothing (use hgq_quantize_bwd with your own workspace).
+ * The full layout needs no scratch and is never limited.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with the
+ * calling thread's current device); make that first call before any stream capture begins.
+ * All calls on a device share the one array and it keeps the previous call's contents: nothing in it
+ * has to be cleared (each call overwrites every word it later reads), but two calls whose kernels
+ * overlap on the GPU -- different streams, no ordering between them -- race on it and corrupt each
+ * other's di / df.  Serialise them on one stream or with events.
+ * Outputs are identical to hgq_quantize_bwd's.
+ */
+#define HGQ_NOALLOC_SCRATCH_BYTES (8u << 20)
+int hgq_quantize_bwd_noalloc(const float *g, const float *x, const uint8_t *k, const float *i,
+                             const float *f, float *dx, float *di, float *df, int64_t n,
+                             int64_t period, int round_mode, int overflow_mode, unsigned flags,
+                             void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*
