@@ -10,9 +10,10 @@ gradient.  One step = one full sweep (6 forward + 6 backward passes over this ra
 element range).  With N > 1 (torchrun, one rank per GPU) the 2^28 elements are split contiguously
 over the ranks and no data crosses between them.
 
-Metric: achieved algorithmic bandwidth in GB/s, 46 bytes per element per (forward + backward)
-pass: forward reads x,i,f fp32 + k uint8 (13 B) and writes y (4 B); backward reads g,x,i,f,k (17 B)
-and writes dx,di,df (12 B).
+Metric: achieved algorithmic bandwidth in GB/s.  Bytes per element: forward reads x,i,f fp32 + k uint8
+(13 B) and writes y (4 B) = 17 B; SAT / SAT_SYM backward reads g,x,i,f,k (17 B) and writes dx,di,df (12 B)
+= 29 B; WRAP backward needs neither k nor i and its di is identically zero, so it reads g,x,f (12 B) and
+writes dx,df (8 B) = 20 B.  A full sweep is 2 x (17+20) + 4 x (17+29) = 258 B per element.
 
 `--impl reference` times the reference's CPU formulation of the same sweep (the eager fp32 op
 sequence of oracle/fixed_point_ops.py on the host cores) on a bounded sample.
@@ -39,7 +40,9 @@ if str(ROOT) not in sys.path:
 
 TOTAL_ELEMS = 1 << 28
 BYTES_FWD, BYTES_BWD = 17, 29
+BYTES_BWD_WRAP = 20
 MODES = [(rm, om) for rm in ('RND', 'TRN') for om in ('WRAP', 'SAT', 'SAT_SYM')]
+BYTES_PER_ELEM_SWEEP = sum(BYTES_FWD + (BYTES_BWD_WRAP if om == 'WRAP' else BYTES_BWD) for _, om in MODES)  # 258
 METRIC = 'quantizer_sweep_hbm_bandwidth'
 UNIT = 'GB/s'
 # DRAM bytes per element per launch (read + write) measured by ncu on a 2^25-element case of the
@@ -142,7 +145,7 @@ def cpu_sweep(sample: int, threads: int, steps: int, warmup: int):
     for _ in range(steps):
         one_step()
     dt = (time.perf_counter() - t0) / steps
-    gbs = len(MODES) * (BYTES_FWD + BYTES_BWD) * sample / dt / 1e9
+    gbs = BYTES_PER_ELEM_SWEEP * sample / dt / 1e9
     return gbs, dt
 
 
@@ -171,7 +174,7 @@ def workload_config(n_gpus: int):
         'workload': 'standalone fixed-point quantizer sweep: 2^28 fp32 elements N(0,16), per-element k/i/f, '
                     '{RND,TRN}x{WRAP,SAT,SAT_SYM}, forward + surrogate backward',
         'elements_total': TOTAL_ELEMS, 'elements_per_gpu': TOTAL_ELEMS // n_gpus,
-        'bytes_per_element': {'fwd': BYTES_FWD, 'bwd': BYTES_BWD},
+        'bytes_per_element': {'fwd': BYTES_FWD, 'bwd_sat': BYTES_BWD, 'bwd_wrap': BYTES_BWD_WRAP, 'sweep': BYTES_PER_ELEM_SWEEP},
         'sharding': f'contiguous element range / {n_gpus}, no collective',
         'l2': 'inputs larger than L2 (>= 1.5 GB touched per launch vs 126 MB L2)',
     }
@@ -216,7 +219,8 @@ def run_ours(args):
         kernels.check(L.hgq_quantize_fwd(P(x), P(k), P(i), P(f), P(y), None, n, n, RM[rm], OM[om], 0, st), 'fwd')
 
     def bwd(rm, om):
-        kernels.check(L.hgq_quantize_bwd(P(g), P(x), P(k), P(i), P(f), P(dx), P(di), P(df), n, n, RM[rm], OM[om], 0,
+        di_p = None if om == 'WRAP' else P(di)  # WRAP has no integer-bit gradient
+        kernels.check(L.hgq_quantize_bwd(P(g), P(x), P(k), P(i), P(f), P(dx), di_p, P(df), n, n, RM[rm], OM[om], 0,
                                          None, 0, st), 'bwd')
 
     def step():
@@ -243,7 +247,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     ms_per_step = ms / args.steps
-    bytes_per_step_total = len(MODES) * (BYTES_FWD + BYTES_BWD) * TOTAL_ELEMS
+    bytes_per_step_total = BYTES_PER_ELEM_SWEEP * TOTAL_ELEMS
     value = bytes_per_step_total / (ms_per_step * 1e-3) / 1e9
 
     # ---- roofline of the dominant kernel (backward, full layout), timed alone -------------------
@@ -293,18 +297,89 @@ def run_ours(args):
                'sample': f'{sample} elements per pass (2^24 of 2^28), 6 modes x (fwd+bwd), 3 steps; eager fp32 '
                          'torch-CPU op sequence of the oracle'}
 
+    # free the sweep's device arrays before the training workloads
+    del x, g, k, i, f, y, dx, di, df
+    torch.cuda.empty_cache()
+    qat = None if args.no_qat else run_qat(args, dev, world, rank, peak)
+
     if rank == 0:
         line = {
             'metric': METRIC, 'value': round(value, 2), 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': max(3, args.warmup), 'ms_per_step': round(ms_per_step, 4), 'higher_is_better': True,
             'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
             'config': workload_config(world), 'roofline': roofline, 'cpu_baseline': cpu, 'e2e': e2e,
-            'gpu_launches': int(launches), 'clocks': clocks.summary(),
+            'gpu_launches': int(launches), 'clocks': clocks.summary(), 'qat_step': qat,
             'frac_of_measured_copy_peak': round(value / world / peak, 4),
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+QAT_CONFIGS = {
+    # name: (builder, global batch, input maker, classes, modelled HBM bytes per sample for one QAT step)
+    'jet_tagger_mlp': ('jet_tagger_mlp', 16384, lambda rng, b: rng.standard_normal((b, 16), dtype=np.float32), 5, 3324),
+    'particle_tagger': ('particle_tagger', 65536, lambda rng, b: rng.standard_normal((b, 64, 16), dtype=np.float32), 5, 162108),
+    'small_cnn': ('small_cnn', 4096, lambda rng, b: rng.random((b, 32, 32, 3), dtype=np.float32), 10, 657144),
+}
+
+
+def run_qat(args, dev, world, rank, peak):
+    """Full QAT steps (forward, backward, gradient all-reduce, fused Adam) of the benchmark models; the global batch is
+    fixed and sharded over the ranks.  Reported beside the sweep: samples/s with the batch resident on the device, the
+    same with the batch copied from pinned host memory and the loss read back every step, and the fraction of the HBM
+    roofline under the model 'every layer-boundary activation crosses HBM once per use' (bytes per sample above)."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from hgq2_b200 import workloads
+    from hgq2_b200.train import DataParallel, Trainer, shard_batch
+
+    out = []
+    dp = DataParallel() if world > 1 else None
+    for name, (builder, batch, make_x, classes, bytes_per_sample) in QAT_CONFIGS.items():
+        try:
+            model = workloads.build(getattr(workloads, builder)(), device=dev)
+            tr = Trainer(model, F.cross_entropy, dp=dp)
+            sl = shard_batch(batch, rank, world)
+            hx = torch.from_numpy(make_x(np.random.default_rng(1), batch)[sl]).pin_memory()
+            hy = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch)[sl]).pin_memory()
+            x, y = hx.to(dev), hy.to(dev)
+            steps = max(3, args.steps)
+            for _ in range(3):
+                tr.step(x, y)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                tr.step(x, y)
+            b.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+            # end to end: host batch in, loss out, every step
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                loss = tr.step(hx.to(dev, non_blocking=True), hy.to(dev, non_blocking=True))
+                loss_host = float(loss.item())
+            e2e_ms = torch.tensor([(time.perf_counter() - t0) / steps * 1e3], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+                dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+            sps = batch / (float(ms.item()) * 1e-3)
+            out.append({
+                'model': name, 'global_batch': batch, 'ms_per_step': round(float(ms.item()), 4),
+                'samples_per_s': round(sps, 1), 'e2e_samples_per_s': round(batch / (float(e2e_ms.item()) * 1e-3), 1),
+                'h2d_bytes_per_step': int(hx.numel() * 4 + hy.numel() * 8), 'd2h_bytes_per_step': 4,
+                'hbm_roofline_frac': round(sps * bytes_per_sample / world / (peak * 1e9), 4),
+                'modelled_bytes_per_sample': bytes_per_sample, 'loss': round(loss_host, 5),
+            })
+            del model, tr, x, y, hx, hy
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            out.append({'model': name, 'error': repr(exc)[:300]})
+    return out
 
 
 def run_e2e(args, kernels, n, dev, world, rank):
@@ -319,7 +394,8 @@ def run_e2e(args, kernels, n, dev, world, rank):
 
     def step():
         for rm, om in MODES:
-            kernels.quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, hdi, hdf, rm, om, False, ws, chunk)
+            kernels.quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, None if om == 'WRAP' else hdi, hdf, rm, om, False,
+                                          ws, chunk)
 
     kernels.quantize_fwd_bwd_host(hx, hk, hi, hf, hg, hy, hdx, hdi, hdf, 'RND', 'SAT', False, ws, chunk)  # warm-up
     if world > 1:
@@ -334,10 +410,10 @@ def run_e2e(args, kernels, n, dev, world, rank):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dt = float(t.item()) / steps
-    total = len(MODES) * (BYTES_FWD + BYTES_BWD) * TOTAL_ELEMS
+    total = BYTES_PER_ELEM_SWEEP * TOTAL_ELEMS
     return {
         'value': round(total / dt / 1e9, 2), 'unit': UNIT, 'ms_per_step': round(dt * 1e3, 2), 'steps': steps,
-        'h2d_bytes_per_step': len(MODES) * 17 * n, 'd2h_bytes_per_step': len(MODES) * 16 * n,
+        'h2d_bytes_per_step': len(MODES) * 17 * n, 'd2h_bytes_per_step': (4 * 16 + 2 * 12) * n,
         'api': 'hgq_quantize_fwd_bwd_host: pinned host buffers, 3-stream chunked pipeline, synchronous return',
     }
 
@@ -349,6 +425,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-cpu', action='store_true', help='skip the cpu_baseline leg')
+    ap.add_argument('--no-qat', action='store_true', help='skip the QAT-step leg (training workloads)')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer end-to-end leg')
     ap.add_argument('--elements', type=int, default=1 << 28,
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
