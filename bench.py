@@ -346,6 +346,7 @@ def run_qat(args, dev, world, rank, peak):
             hy = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch)[sl]).pin_memory()
             x, y = hx.to(dev), hy.to(dev)
             steps = max(3, args.steps)
+            tr.capture(x, y, warmup=3)  # the whole step as one CUDA graph
             for _ in range(3):
                 tr.step(x, y)
             torch.cuda.synchronize()
@@ -373,7 +374,7 @@ def run_qat(args, dev, world, rank, peak):
                 'samples_per_s': round(sps, 1), 'e2e_samples_per_s': round(batch / (float(e2e_ms.item()) * 1e-3), 1),
                 'h2d_bytes_per_step': int(hx.numel() * 4 + hy.numel() * 8), 'd2h_bytes_per_step': 4,
                 'hbm_roofline_frac': round(sps * bytes_per_sample / world / (peak * 1e9), 4),
-                'modelled_bytes_per_sample': bytes_per_sample, 'loss': round(loss_host, 5),
+                'modelled_bytes_per_sample': bytes_per_sample, 'loss': round(loss_host, 5), 'cuda_graph': True,
             })
             del model, tr, x, y, hx, hy
             torch.cuda.empty_cache()

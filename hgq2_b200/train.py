@@ -156,7 +156,12 @@ class DataParallel:
 
 
 class Trainer:
-    """One model, one flat bucket, one fused optimizer; ``step(x, y)`` runs a full QAT step and returns the loss."""
+    """One model, one flat bucket, one fused optimizer; ``step(x, y)`` runs a full QAT step and returns the loss.
+
+    ``capture(x, y)`` records the whole step (forward, backward, gradient exchange, optimizer) into a CUDA graph over
+    static input buffers; afterwards ``step`` copies the batch into those buffers and replays the graph, which removes
+    the per-kernel launch and Python cost that dominates the small models.
+    """
 
     def __init__(self, model: Layer, loss_fn, learning_rate=1e-3, dp: DataParallel | None = None):
         self.model = model
@@ -164,6 +169,7 @@ class Trainer:
         self.dp = dp
         self.state = FlatState(model)
         self.opt = FusedAdam(self.state, learning_rate=learning_rate)
+        self._graph = None
 
     def forward_backward(self, x, y):
         self.state.zero_grad()
@@ -175,7 +181,7 @@ class Trainer:
         total.backward()
         return task.detach(), total.detach() + self.state.regularization_loss()
 
-    def step(self, x, y):
+    def _eager_step(self, x, y):
         if self.dp is not None:
             with self.dp:
                 task, total = self.forward_backward(x, y)
@@ -184,3 +190,26 @@ class Trainer:
             task, total = self.forward_backward(x, y)
         self.opt.step()
         return total
+
+    def capture(self, x, y, warmup: int = 3) -> None:
+        """Record the step as a CUDA graph for batches shaped like (x, y).  Runs ``warmup`` real steps first."""
+        self._sx, self._sy = x.clone(), y.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self._eager_step(self._sx, self._sy)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._sloss = self._eager_step(self._sx, self._sy)
+        self._graph = graph
+
+    def step(self, x, y):
+        if self._graph is not None and x.shape == self._sx.shape and y.shape == self._sy.shape:
+            self._sx.copy_(x, non_blocking=True)
+            self._sy.copy_(y, non_blocking=True)
+            self._graph.replay()
+            return self._sloss
+        return self._eager_step(x, y)

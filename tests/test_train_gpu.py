@@ -112,3 +112,31 @@ def test_adam_kernel_matches_keras_rule():
         torch.cuda.synchronize()
         np.testing.assert_allclose(w.cpu().numpy(), wr.numpy(), rtol=2e-5, atol=1e-7)
     assert int(step.item()) == 3
+
+
+def test_graph_captured_step_equals_eager_steps():
+    from hgq2_b200 import workloads
+    from hgq2_b200.train import Trainer
+
+    rng = np.random.default_rng(1)
+    xs = [torch.from_numpy(rng.standard_normal((512, 16)).astype(np.float32)).cuda() for _ in range(3)]
+    ys = [torch.from_numpy(rng.integers(0, 5, 512)).cuda() for _ in range(3)]
+    results = []
+    for graphed in (False, True):
+        model = workloads.build(workloads.jet_tagger_mlp())
+        tr = Trainer(model, ce)
+        if graphed:
+            snap = tr.state.params.clone()
+            m, v, t = tr.opt.m.clone(), tr.opt.v.clone(), tr.opt.step_count.clone()
+            qstate = [(var, var.value.detach().clone()) for var in model.non_trainable_variables]
+            tr.capture(xs[0], ys[0], warmup=2)
+            # undo the warm-up and capture-time updates so both runs start from the same state
+            tr.state.params.copy_(snap); tr.opt.m.copy_(m); tr.opt.v.copy_(v); tr.opt.step_count.copy_(t)
+            for var, val in qstate:
+                var.value.data.copy_(val)
+        losses = [float(tr.step(x, y)) for x, y in zip(xs, ys)]
+        results.append((losses, tr.state.params.clone(), [int(l.ebops.item()) for l in model.layers]))
+    (l0, p0, e0), (l1, p1, e1) = results
+    assert l0 == l1, (l0, l1)
+    assert torch.equal(p0, p1)
+    assert e0 == e1
