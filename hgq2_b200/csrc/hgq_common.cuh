@@ -26,7 +26,7 @@ inline int check_launch() {
     return HGQ_OK;
 }
 
-inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+__host__ __device__ inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 inline int pow2ceil(int64_t v) {
     int p = 1;

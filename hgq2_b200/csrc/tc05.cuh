@@ -1,0 +1,129 @@
+// Thin inline-PTX layer over the sm_100a tensor-core path: tcgen05.mma with operands in shared
+// memory and the accumulator in tensor memory (TMEM), mbarrier completion, tcgen05.ld read-back.
+// Every wait is bounded: a wait that runs out of iterations reports failure to its caller, which
+// records it in a status word and unwinds (freeing TMEM) instead of spinning for ever.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hgq {
+namespace tc {
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// ---- shared-memory matrix descriptor (no swizzle) ------------------------------------------------
+// Operands are stored as "core matrices": 8 rows x 16 bytes, 128 contiguous bytes.  For a K-major
+// operand a core matrix holds 8 rows (M or N index) x 8 bf16 along K; `lbo` is the byte distance
+// between the two core matrices that are adjacent along K inside one K=16 instruction step, `sbo`
+// the byte distance between core matrices of consecutive 8-row groups.  For an MN-major operand a
+// core matrix holds 8 K-indices x 8 bf16 along M/N; `sbo` is then the distance between consecutive
+// groups of 8 along M/N and `lbo` between consecutive groups of 8 along K.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);          // start address, 16-byte units        [0,14)
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;  // leading-dimension byte offset     [16,30)
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;  // stride-dimension byte offset      [32,46)
+    d |= (uint64_t)1 << 46;                           // descriptor version 1 (sm_100)      [46,48)
+    return d;                                         // base offset 0, layout type 0 = no swizzle
+}
+
+// ---- instruction descriptor: kind::f16, bf16 x bf16 -> fp32, M = 128 -------------------------------
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int n, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4)                       // accumulator format fp32
+           | (1u << 7)                     // A format bf16
+           | (1u << 10)                    // B format bf16
+           | ((a_mn_major ? 1u : 0u) << 15)
+           | ((b_mn_major ? 1u : 0u) << 16)
+           | ((uint32_t)(n >> 3) << 17)    // N / 8
+           | ((uint32_t)(128 >> 4) << 24); // M / 16
+}
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    const uint32_t acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Make generic-proxy writes to shared memory visible to the async proxy (the tensor core reads smem through it).
+__device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- mbarrier -------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+// Wait for the phase with the given parity; gives up after `max_polls` polls (each poll itself blocks for a
+// hardware-defined time slice).  Returns false on give-up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_polls = 1u << 22) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < max_polls; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// ---- tensor memory ------------------------------------------------------------------------------
+// One warp allocates `ncols` (power of two >= 32) columns; the base address lands in *slot (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// Read 8 consecutive fp32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + laneid).
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r0, r1, r2, r3, r4, r5, r6, r7;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3), "=r"(r4), "=r"(r5), "=r"(r6), "=r"(r7)
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
+    v[4] = __uint_as_float(r4); v[5] = __uint_as_float(r5); v[6] = __uint_as_float(r6); v[7] = __uint_as_float(r7);
+}
+
+// ---- exact bf16 splitting -------------------------------------------------------------------------
+// v = hi + lo + lo2 exactly (3 x 8 significant bits cover the 24 of an fp32); a term that is not
+// needed comes out as zero.
+__device__ __forceinline__ void split3(float v, __nv_bfloat16 &hi, __nv_bfloat16 &lo, __nv_bfloat16 &lo2) {
+    hi = __float2bfloat16_rn(v);
+    const float r1 = __fsub_rn(v, __bfloat162float(hi));
+    lo = __float2bfloat16_rn(r1);
+    const float r2 = __fsub_rn(r1, __bfloat162float(lo));
+    lo2 = __float2bfloat16_rn(r2);
+}
+
+__device__ __forceinline__ uint32_t pack2(__nv_bfloat16 a, __nv_bfloat16 b) {
+    return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+}
+
+}  // namespace tc
+}  // namespace hgq

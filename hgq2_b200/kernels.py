@@ -194,3 +194,51 @@ def ebops_conv2d(bw_in, bw_w, bw_bias, out_hw, strides, dilation, pad_tl, out_si
                                     ptr(d_in), ptr(d_w), ptr(d_b), stream_handle())
     check(st, 'hgq_ebops_conv2d')
     return e_u, e_f, loss, d_in, d_w, d_b
+
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device status word the tensor-core kernels set when a bounded device-side wait gives up."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = t
+    return t
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronising check of the status word (tests and debugging; the hot path does not call it)."""
+    v = int(status_word(device).item())
+    if v != 0:
+        raise _lib.HGQError(-7, f'device status word = {v}')
+
+
+def qdense_supported(M: int, K: int, N: int, rows_period: int) -> bool:
+    return M > 0 and lib().hgq_qdense_fwd_workspace(M, K, N, rows_period) > 0
+
+
+def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: str, training: bool, zero_nonpos: bool,
+               wq, bq, activation: str | None, want_absmax: bool):
+    """Fused y = act(iq(x) @ wq + bq); x is [..., K] and is treated as [M, K].  Returns (y, absmax or None)."""
+    require_cuda(x, qk, qi, qf, wq, bq)
+    rm, om = _modes(round_mode, overflow_mode)
+    x = x.contiguous()
+    K = x.shape[-1]
+    M = x.numel() // K
+    N = wq.shape[-1]
+    wq = wq.contiguous()
+    y = torch.empty(x.shape[:-1] + (N,), dtype=torch.float32, device=x.device)
+    absmax = torch.empty(rows_period * K, dtype=torch.float32, device=x.device) if want_absmax else None
+    ws = workspace(lib().hgq_qdense_fwd_workspace(M, K, N, rows_period), x.device, slot=1) if want_absmax else None
+    act = {None: 0, 'relu': 1}[activation]
+    flags = (FLAG_TRAINING if training else 0) | (FLAG_ZERO_NONPOS if zero_nonpos else 0)
+    with torch.cuda.device(x.device):
+        st = lib().hgq_qdense_fwd(
+            ptr(x), ptr(qk), ptr(qi), ptr(qf), rows_period, rm, om, flags, ptr(wq), ptr(bq), act, ptr(y), ptr(absmax), M, K, N,
+            ptr(ws), ws.numel() if ws is not None else 0, ptr(status_word(x.device)), stream_handle(),
+        )
+    check(st, 'hgq_qdense_fwd')
+    return y, absmax

@@ -142,6 +142,36 @@ int hgq_quantize_bwd_noalloc(const float *g, const float *x, const uint8_t *k, c
                              int64_t period, int round_mode, int overflow_mode, unsigned flags,
                              void *stream);
 
+/* ---- K2: fused quantised dense layer ------------------------------------------------------- */
+
+/*
+ * Scratch bytes hgq_qdense_fwd needs when the abs-max side output is requested (0 if the shape is not
+ * supported by the fused kernel).
+ */
+size_t hgq_qdense_fwd_workspace(int64_t M, int K, int N, int rows_period);
+
+/*
+ * y = act( iq(x) @ wq + bq ) in one pass.  Stands in for QDense.call (layers/core/dense.py:60-68) and for
+ * QEinsumDense.call (layers/core/einsum_dense.py:72-83) when the contraction is over the trailing input
+ * axis ('...k,kn->...n').
+ *
+ *   x [M, K] raw activations; qk/qi/qf: the input quantizer's tables, [rows_period, K] entries, row r of
+ *   x uses table row r % rows_period (qf == NULL: no input quantizer; qk/qi may be NULL when the overflow
+ *   mode is NONE, or WRAP with HGQ_FLAG_TRAINING); wq [K, N] and bq [N] (may be NULL) already quantised;
+ *   activation 0 none, 1 relu; y [M, N].
+ *   absmax (may be NULL): [rows_period, K] floats receiving max over rows of |round(x, f)| (the statistic
+ *   of x_to_bw_absmax, quantizer/internal/base.py:185-186); needs `workspace`.
+ *   status (may be NULL): device word; bit 0 is set if a bounded device-side wait gave up.
+ *
+ * The contraction runs on the tensor cores with every operand split exactly into bf16 terms and fp32
+ * accumulation, so y equals the fp32 result whenever that is exact, and is within fp32 rounding otherwise.
+ * Limits: K <= 256, N <= 128, rows_period * K <= 8192 when absmax is requested.
+ */
+int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi, const float *qf, int rows_period,
+                   int round_mode, int overflow_mode, unsigned flags, const float *wq, const float *bq,
+                   int activation, float *y, float *absmax, int64_t M, int K, int N, void *workspace,
+                   size_t workspace_bytes, unsigned *status, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*

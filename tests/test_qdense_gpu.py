@@ -1,0 +1,87 @@
+"""The fused quantise -> tensor-core GEMM -> bias/activation kernel against the oracle's op sequence."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fixed_point_ops as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(x, k, i, f, rm, om, training, w, b, act, rows_period):
+    M, K = x.shape
+    rep = M // rows_period + 1
+    kk, ii, ff = (t.repeat(rep, 1)[:M] for t in (k.float(), i, f))
+    xq = O.quantize_fwd(x, kk, ii, ff, rm, om, training)
+    y = (xq.double() @ w.double())
+    if b is not None:
+        y = y + b.double()
+    if act == 'relu':
+        y = torch.relu(y)
+    amax = torch.zeros(rows_period, K)
+    r = O.round_fwd(x, ff, rm).abs()
+    for p in range(rows_period):
+        amax[p] = r[p::rows_period].amax(0)
+    return y, amax
+
+
+@pytest.mark.parametrize('M,K,N,rows_period', [
+    (1000, 16, 64, 1), (128 * 37 + 5, 64, 64, 64), (4096, 64, 32, 1), (513, 32, 5, 1), (300, 27, 16, 1),
+    (2048, 128, 64, 64), (640, 64, 128, 8), (129, 64, 10, 3), (7, 16, 64, 1), (50000, 64, 64, 1), (3000, 144, 32, 1),
+])
+@pytest.mark.parametrize('rm,om,training', [('RND', 'WRAP', True), ('TRN', 'SAT', True), ('RND', 'WRAP', False)])
+def test_fused_dense_forward(M, K, N, rows_period, rm, om, training):
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(M + K + N)
+    x = torch.from_numpy((rng.standard_normal((M, K)) * 3).astype(np.float32))
+    k = torch.from_numpy(rng.integers(0, 2, (rows_period, K)).astype(np.uint8))
+    i = torch.from_numpy(rng.integers(0, 4, (rows_period, K)).astype(np.float32))
+    f = torch.from_numpy(rng.integers(1, 7, (rows_period, K)).astype(np.float32))
+    w = torch.from_numpy(np.round(rng.uniform(-2, 2, (K, N)) * 64) / 64).float()   # 8-bit weights
+    b = torch.from_numpy(np.round(rng.standard_normal(N) * 16) / 16).float()
+    for act in (None, 'relu'):
+        y, amax = kernels.qdense_fwd(x.cuda(), k.cuda(), i.cuda(), f.cuda(), rows_period, rm, om, training, False, w.cuda(),
+                                     b.cuda(), act, True)
+        kernels.check_status(y.device)
+        yr, ar = _ref(x, k, i, f, rm, om, training, w, b, act, rows_period)
+        err = (y.cpu().double() - yr).abs().max() / max(float(yr.abs().max()), 1e-30)
+        assert err <= 2e-7, f'act={act}: relative error {err:.3e}'
+        assert torch.equal(amax.cpu().view(rows_period, K), ar), 'absmax'
+
+
+def test_fused_dense_is_exact_for_wide_values():
+    # operands that need two and three bf16 terms: 14-bit activations, 12- and 20-bit weights
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(0)
+    M, K, N = 1024, 64, 64
+    x = torch.from_numpy((rng.standard_normal((M, K)) * 20).astype(np.float32))
+    f = torch.full((1, K), 8.0)
+    for wbits in (6, 12, 20):
+        w = torch.from_numpy(np.round(rng.uniform(-1, 1, (K, N)) * 2**wbits) / 2**wbits).float()
+        y, _ = kernels.qdense_fwd(x.cuda(), None, None, f.cuda(), 1, 'RND', 'WRAP', True, False, w.cuda(), None, None, False)
+        kernels.check_status(y.device)
+        xq = O.round_fwd(x, f.expand(M, K), 'RND')
+        yr = xq.double() @ w.double()
+        err = (y.cpu().double() - yr).abs().max() / float(yr.abs().max())
+        # 14-bit x wbits-bit products summed over 64 terms need more than fp32's 24 bits once wbits > 4: the sum is
+        # then rounded (by the reference too); the split operands themselves stay exact
+        assert err <= (2e-7 if wbits <= 6 else 1e-6), (wbits, float(err))
+
+
+def test_fused_dense_no_input_quantizer_and_limits():
+    from hgq2_b200 import _lib, kernels
+
+    rng = np.random.default_rng(1)
+    x = torch.from_numpy(rng.standard_normal((300, 48)).astype(np.float32))
+    w = torch.from_numpy(rng.standard_normal((48, 24)).astype(np.float32))
+    y, _ = kernels.qdense_fwd(x.cuda(), None, None, None, 1, 'RND', 'WRAP', True, False, w.cuda(), None, None, False)
+    kernels.check_status(y.device)
+    yr = x.double() @ w.double()
+    assert float((y.cpu().double() - yr).abs().max() / yr.abs().max()) <= 2e-7
+    assert not kernels.qdense_supported(100, 300, 64, 1)
+    assert not kernels.qdense_supported(100, 64, 200, 1)
+    L = _lib.lib()
+    assert L.hgq_qdense_fwd(1, None, None, None, 1, 1, 1, 0, 1, None, 0, 1, None, 100, 300, 64, None, 0, None, None) == -2
