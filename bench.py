@@ -419,6 +419,39 @@ def run_e2e(args, kernels, n, dev, world, rank):
     }
 
 
+def run_qdense(args):
+    """Kernel-level benchmark of the fused dense forward (quantise -> tcgen05 GEMM -> bias/ReLU) on the per-particle
+    layer shape of the particle tagger: M = batch x 64 rows, K = N = 64, input bitwidths [64, 64].  Algorithmic bytes
+    per row: 4 (K + N)."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    M, K, N, rp = args.rows, args.k, args.n, args.rows_period
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(M, K, device=dev, generator=gen)
+    f = torch.full((rp, K), 6.0, device=dev)
+    w = (torch.randint(-128, 128, (K, N), device=dev, generator=gen).float() / 64.0)
+    b = torch.zeros(N, device=dev)
+    fn = lambda: kernels.qdense_fwd(x, None, None, f, rp, 'RND', 'WRAP', True, False, w, b, 'relu', True)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    kernels.check_status(dev)
+    a, bb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        fn()
+    bb.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(bb) / args.steps
+    peak, kind = measured_peaks()
+    gbs = 4.0 * (K + N) * M / (ms * 1e-3) / 1e9
+    print(json.dumps({'kernel': 'k_qdense_fwd', 'M': M, 'K': K, 'N': N, 'rows_period': rp, 'ms': round(ms, 4),
+                      'achieved_GBs': round(gbs, 1), 'peak_GBs': peak, 'frac': round(gbs / peak, 4), 'peak_source': kind,
+                      'tflops': round(2.0 * M * K * N / (ms * 1e-3) / 1e12, 2)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -430,8 +463,16 @@ def main():
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer end-to-end leg')
     ap.add_argument('--elements', type=int, default=1 << 28,
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense'],
+                    help="'qdense' times the fused dense forward kernel alone (for profiler captures)")
+    ap.add_argument('--rows', type=int, default=1 << 22)
+    ap.add_argument('--k', type=int, default=64)
+    ap.add_argument('--n', type=int, default=64)
+    ap.add_argument('--rows-period', type=int, default=64)
     args = ap.parse_args()
     globals()['TOTAL_ELEMS'] = args.elements
+    if args.workload == 'qdense':
+        return run_qdense(args)
     if args.impl == 'reference':
         run_reference(args)
     else:

@@ -222,15 +222,17 @@ def qdense_supported(M: int, K: int, N: int, rows_period: int) -> bool:
 
 def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: str, training: bool, zero_nonpos: bool,
                wq, bq, activation: str | None, want_absmax: bool):
-    """Fused y = act(iq(x) @ wq + bq); x is [..., K] and is treated as [M, K].  Returns (y, absmax or None)."""
+    """Fused y = act(iq(x) @ wq + bq); x is treated as [M, K] with K = wq.shape[0].  Returns (y [M, N], absmax or None)."""
     require_cuda(x, qk, qi, qf, wq, bq)
     rm, om = _modes(round_mode, overflow_mode)
     x = x.contiguous()
-    K = x.shape[-1]
-    M = x.numel() // K
+    qk, qi, qf = (None if t is None else t.contiguous() for t in (qk, qi, qf))
+    bq = None if bq is None else bq.contiguous()
     N = wq.shape[-1]
+    K = wq.shape[0]
+    M = x.numel() // K
     wq = wq.contiguous()
-    y = torch.empty(x.shape[:-1] + (N,), dtype=torch.float32, device=x.device)
+    y = torch.empty((M, N), dtype=torch.float32, device=x.device)
     absmax = torch.empty(rows_period * K, dtype=torch.float32, device=x.device) if want_absmax else None
     ws = workspace(lib().hgq_qdense_fwd_workspace(M, K, N, rows_period), x.device, slot=1) if want_absmax else None
     act = {None: 0, 'relu': 1}[activation]

@@ -9,7 +9,7 @@ import torch
 from ...backend import activation_name, get_activation, get_initializer
 from ...quantizer import Quantizer
 from ...quantizer.config import QuantizerConfig
-from .._functions import EbopsDenseFn
+from .._functions import EbopsDenseFn, fused_dense_call
 from .base import QLayerBaseSingleInput
 
 
@@ -69,6 +69,9 @@ class QDense(QLayerBaseSingleInput):
         return tuple(input_shape[:-1]) + (self.units,)
 
     def call(self, inputs, training=None):
+        y = fused_dense_call(self, inputs, 1, self.qkernel, self.qbias if self.bias is not None else None, training)
+        if y is not None:
+            return y
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
         x = torch.matmul(inputs, self.qkernel)

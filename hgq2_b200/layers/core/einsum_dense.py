@@ -9,7 +9,7 @@ import torch
 from ...backend import activation_name, get_activation, get_initializer
 from ...quantizer import Quantizer
 from ...quantizer.config import QuantizerConfig
-from .._functions import EbopsDenseFn
+from .._functions import EbopsDenseFn, fused_dense_call
 from .base import QLayerBaseSingleInput
 
 
@@ -111,12 +111,49 @@ class QEinsumDense(QLayerBaseSingleInput):
             self.bq.build(tuple(self._bias.shape))
             self.bq.built = True
         self.ebops_equation = self.equation.split('->')[0] + '->'
+        self._matmul_form = self._analyze_matmul_form()
+
+    def _analyze_matmul_form(self):
+        """(number of trailing contracted input axes, K, N) if the equation is '<free><con>,<con><kfree>-><free><kfree>'
+        -- a plain [M, K] x [K, N] product after reshaping -- and the bias is a function of the kernel's free axes only."""
+        inp, rest = self.equation.split(',', 1)
+        ker, out = rest.split('->', 1)
+        con = [c for c in ker if c in inp]
+        n_con = len(con)
+        if n_con == 0 or len(set(inp)) != len(inp) or len(set(ker)) != len(ker):
+            return None
+        kfree = ker[n_con:]
+        if inp[-n_con:] != ''.join(con) or ker[:n_con] != ''.join(con) or any(c in inp for c in kfree):
+            return None
+        if out != inp[:-n_con] + kfree:
+            return None
+        kshape = tuple(self._kernel.shape)
+        K = 1
+        for d in kshape[:n_con]:
+            K *= d
+        N = 1
+        for d in kshape[n_con:]:
+            N *= d
+        if self.bias is not None:
+            spec = out[len(out) - len(self._bias.shape):]
+            if any(c not in kfree for c, d in zip(spec, self._bias.shape) if d != 1) or len(spec) > len(kfree):
+                return None
+        return n_con, K, N, kshape[n_con:]
 
     def compute_output_shape(self, input_shape):
         return (input_shape[0],) + tuple(self.full_output_shape[1:])
 
     def call(self, inputs, training=None):
         qkernel = self.kq(self._kernel.value, training=training)
+        if self._matmul_form is not None:
+            n_con, K, N, kfree_shape = self._matmul_form
+            qbias = None
+            if self.bias is not None:
+                qbias = self.bq(self._bias.value, training=training)
+                qbias = qbias.reshape((1,) * (len(kfree_shape) - qbias.dim()) + tuple(qbias.shape)).expand(kfree_shape).reshape(N)
+            y = fused_dense_call(self, inputs, n_con, qkernel.reshape(K, N), qbias, training)
+            if y is not None:
+                return y.reshape((inputs.shape[0],) + tuple(self.full_output_shape[1:]))
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
         x = torch.einsum(self.equation, inputs, qkernel)

@@ -144,6 +144,33 @@ class FixedPointQuantizerBase(TrainableQuantizerBase):
         zero = not training  # eval: where(k + i + f > 0, ret, 0), fused into the kernel
         return self.stateless_quantizer(inputs, self._k.value, i, f, training is True, self.seed_gen, zero_nonpos=zero)
 
+    # -- inline application by a consumer kernel ---------------------------------------------------
+    def fusion_plan(self, training):
+        """How a consuming kernel applies this quantizer to its input inline, mirroring the branches of ``call``.
+
+        Returns None when the call cannot be inlined (calibration mode, or a state update that must see the whole
+        tensor before any element is quantised); otherwise a dict with the stateless quantizer's modes and flags,
+        the bitwidth-shaped ``k``, ``i``, ``f`` tensors (differentiable), and ``track``: a function the caller
+        invokes with the abs-max of the rounded input to update the integer bits, or None.
+        """
+        if training == 'tracing':  # noqa: E712
+            return None
+        plan = dict(round_mode=self.round_mode, k=self._k.value, track=None)
+        if self.overflow_mode == 'WRAP' and self.trainable:
+            if training:
+                return self._wrap_training_plan(plan)
+            if self._is_weight and (self._kif_like or self.round_mode == 'RND'):
+                plan.update(overflow_mode='NONE', training=True, zero=False, i=None, f=self.f)
+                return plan
+        k, i, f = self.kif
+        plan.update(overflow_mode=self.overflow_mode, training=training is True, zero=not training, i=i, f=f)
+        return plan
+
+    _kif_like = False
+
+    def _wrap_training_plan(self, plan):
+        return None
+
 
 class FixedPointQuantizerKBI(FixedPointQuantizerBase):
     """Fixed-point quantizer parameterised by keep_negative, total bits and integer bits."""
@@ -321,6 +348,18 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
             if self._is_weight:
                 return self.stateless_quantizer.round(inputs, f, False, self.seed_gen)
         return super().call(inputs, training is True)
+
+    _kif_like = True
+
+    def _wrap_training_plan(self, plan):
+        f = self.f
+
+        def track(absmax, inputs=None):
+            _new_i = minimal_i_given_xf(_sync_absmax(absmax.view(f.shape), inputs), f.detach(), self.symmetric)
+            self._i.assign(torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i))
+
+        plan.update(overflow_mode='NONE', training=True, zero=False, i=None, f=f, track=track)
+        return plan
 
     @property
     def k(self):

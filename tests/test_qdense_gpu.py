@@ -80,7 +80,7 @@ def test_fused_dense_no_input_quantizer_and_limits():
     y, _ = kernels.qdense_fwd(x.cuda(), None, None, None, 1, 'RND', 'WRAP', True, False, w.cuda(), None, None, False)
     kernels.check_status(y.device)
     yr = x.double() @ w.double()
-    assert float((y.cpu().double() - yr).abs().max() / yr.abs().max()) <= 2e-7
+    assert float((y.cpu().double() - yr).abs().max() / yr.abs().max()) <= 1e-6  # full-width operands: fp32 rounding of the sum
     assert not kernels.qdense_supported(100, 300, 64, 1)
     assert not kernels.qdense_supported(100, 64, 200, 1)
     L = _lib.lib()
