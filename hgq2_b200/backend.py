@@ -56,6 +56,11 @@ class Initializer:
     def __call__(self, shape, dtype=torch.float32, device=None) -> torch.Tensor:
         raise NotImplementedError
 
+    def clone(self):
+        import copy
+
+        return copy.copy(self)
+
 
 class Constant(Initializer):
     def __init__(self, value=0.0):

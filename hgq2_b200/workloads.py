@@ -12,7 +12,8 @@ import torch
 
 from .backend import Flatten, Lambda, MaxPooling2D, Sequential
 from .config import LayerConfigScope, QuantizerConfigScope
-from .layers import QConv2D, QDense, QEinsumDense
+from .layers import QConv2D, QDense, QEinsumDense, QMultiHeadAttention
+from .quantizer import QuantizerConfig
 from .quantizer.internal import FixedPointQuantizerKBI
 
 
@@ -85,6 +86,32 @@ def small_cnn(beta0=1e-5):
     model = Sequential(layers, name='small_cnn')
     model.input_shape = (32, 32, 3)
     model.weight_bits = (3, 8)
+    return model
+
+
+def transformer_block(seq=64, d_model=64, heads=4, beta0=1e-5):
+    """Transformer block: QMultiHeadAttention (4 heads, key_dim 16, bit-accurate softmax with 10-bit exp / inverse
+    tables), QDense 64 -> 128 -> 64 feed-forward, mean over the sequence, QDense -> 5 classes.  Score and softmax
+    activations kif i=4 f=8."""
+    w, a, l = _scopes(4, 8, beta0)
+    t = QuantizerConfigScope(place='table', b0=10, i0=1)
+    with w, a, t, l:
+        table_in = dict(k0=0, i0=4, f0=6)  # 10-bit table index
+        mha = QMultiHeadAttention(
+            heads, d_model // heads,
+            softmax_exp_iq_conf=QuantizerConfig(place='datalane', overflow_mode='SAT', **table_in),
+            softmax_inv_iq_conf=QuantizerConfig(place='datalane', **dict(k0=0, i0=7, f0=3)),
+        )
+        layers = _seeded([
+            mha,
+            QDense(128, activation='relu'),
+            QDense(d_model),
+            Lambda(lambda x: x.mean(dim=1), name='mean_sequence'),
+            QDense(5),
+        ])
+    model = Sequential(layers, name='transformer_block')
+    model.input_shape = (seq, d_model)
+    model.weight_bits = (4, 8)
     return model
 
 

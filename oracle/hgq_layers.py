@@ -355,3 +355,131 @@ def mirror_layer(layer):
         return OracleQConv2D(kernel, bias, layer.strides, layer.dilation_rate, layer._pads(h, w), layer.n_parallel,
                              layer.parallelization_factor, **common)
     raise NotImplementedError(name)
+
+
+# ---- config 5: lookup-table activations, softmax, multi-head attention ---------------------------------------
+class OracleQUnaryLUT(OracleQLayer):
+    """QUnaryFunctionLUT (layers/activation.py:58-67)."""
+
+    def __init__(self, fn, **kw):
+        super().__init__(kq=None, bq=None, activation=None, **kw)
+        self.fn = fn
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        return self.fn(x)
+
+    def _compute_ebops(self, shape):
+        return torch.sum((2.0 ** self.iq.bits_(shape)) * self.oq.bits_(shape)) * 1e-4
+
+
+class OracleQSoftmax(OracleQLayer):
+    """QSoftmax (layers/softmax.py:114-161), stable form, no mask."""
+
+    def __init__(self, axes, exp_table, inv_table, stable, pf, **kw):
+        super().__init__(kq=None, bq=None, activation=None, **kw)
+        self.axes, self.exp_table, self.inv_table, self.stable, self.pf = tuple(axes), exp_table, inv_table, stable, pf
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        if self.stable:
+            x = torch.amax(x, dim=self.axes, keepdim=True) - x
+        e = self.exp_table(x, training)
+        s = torch.sum(e, dim=self.axes, keepdim=True)
+        d = self.inv_table(s, training)
+        self.sub_losses = self.exp_table.losses + self.inv_table.losses
+        return e * d
+
+    def __call__(self, x, training=None):
+        r = super().__call__(x, training)
+        self.losses = self.losses + self.sub_losses
+        return r
+
+    def _compute_ebops(self, shape):
+        accum_shape = tuple(1 if i in self.axes else s for i, s in enumerate(shape))
+        max_instance = prod(accum_shape)
+        factor = (self.pf if self.pf > 0 else max_instance) / max_instance
+        inp_bits = self.iq.bits_(shape) if self.iq is not None else 0
+        exp_bits = self.exp_table.oq.bits_(shape)
+        inv_bits = self.inv_table.oq.bits_(accum_shape)
+        if self.stable:
+            sub = torch.sum(inp_bits) if self.iq is not None else torch.sum(self.exp_table.iq.bits_(shape))
+        else:
+            sub = 0
+        accum = torch.sum(exp_bits) - torch.sum(torch.amin(exp_bits, dim=self.axes))
+        mult = torch.sum(exp_bits * inv_bits)
+        ebops = sub + accum + mult
+        if not self.stable:
+            ebops = ebops + torch.sum((2.0**inp_bits) * exp_bits) * 1e-4
+        return ebops * factor
+
+    def total_ebops(self):
+        return int(self.ebops.to(torch.int64) + self.exp_table.ebops.to(torch.int64) + self.inv_table.ebops.to(torch.int64))
+
+
+class OracleQMHA(OracleQLayer):
+    """QMultiHeadAttention (layers/attn/mha.py:386-537) for [B, T, D] inputs, no masks, no dropout."""
+
+    def __init__(self, q, k, v, o, softmax, pf, **kw):
+        super().__init__(iq=None, kq=None, bq=None, activation=None, **kw)
+        self.q, self.k, self.v, self.o, self.softmax, self.pf = q, k, v, o, softmax, pf
+
+    def __call__(self, x, training=None):
+        self.losses = []
+        query = self.q(x, training)
+        key = self.k(x, training)
+        value = self.v(x, training)
+        scores = torch.einsum('aecd,abcd->acbe', key, query)
+        scores = self.softmax(scores, training)
+        out = torch.einsum('acbe,aecd->abcd', scores, value)
+        out = self.o(out, training)
+        if self.oq is not None:
+            out = self.oq(out, training)
+        for sub in (self.q, self.k, self.v, self.softmax, self.o):
+            self.losses += sub.losses
+        if training and self.enable_ebops:
+            T, S = x.shape[1], x.shape[1]
+            N = self.q.full_output_shape[2]
+            bw_q = self.q.oq.bits_((1,) + tuple(self.q.full_output_shape[1:]))
+            bw_k = self.k.oq.bits_((1,) + tuple(self.k.full_output_shape[1:]))
+            bw_v = self.v.oq.bits_((1,) + tuple(self.v.full_output_shape[1:]))
+            bw_a = self.softmax.oq.bits_((1, N, T, S))
+            ebops = torch.einsum('aecd,abcd->', bw_q, bw_k) + torch.einsum('acbe,aecd->', bw_a, bw_v)
+            if self.pf > 0:
+                ebops = ebops * self.pf
+            ebops = ebops * self.ebops_factor
+            self.ebops = ebops.detach().to(torch.uint32)
+            self.losses.append(ebops * self.beta)
+        return out
+
+    def total_ebops(self):
+        return int(sum(int(p.ebops.to(torch.int64)) for p in (self.q, self.k, self.v, self.o)) + int(self.ebops.to(torch.int64))
+                   + self.softmax.total_ebops())
+
+    def qlayers(self):
+        return [self.q, self.k, self.v, self.o, self.softmax, self.softmax.exp_table, self.softmax.inv_table]
+
+
+def _common_kw(layer):
+    return dict(
+        iq=mirror_quantizer(layer.iq) if layer.enable_iq else None, oq=mirror_quantizer(layer.oq) if layer.enable_oq else None,
+        beta=float(layer.beta) if layer.enable_ebops else 0.0, ebops_factor=layer.ebops_factor, enable_ebops=layer.enable_ebops,
+    )
+
+
+def mirror_lut(layer):
+    return OracleQUnaryLUT(layer.activation, **_common_kw(layer))
+
+
+def mirror_softmax(layer):
+    return OracleQSoftmax(layer.axes, mirror_lut(layer.exp_table), mirror_lut(layer.inv_table), layer.stable,
+                          layer.parallelization_factor, **_common_kw(layer))
+
+
+def mirror_mha(layer):
+    kw = dict(oq=mirror_quantizer(layer.oq) if layer.enable_oq else None, beta=float(layer.beta) if layer.enable_ebops else 0.0,
+              ebops_factor=layer.ebops_factor, enable_ebops=layer.enable_ebops)
+    return OracleQMHA(mirror_layer(layer._query_dense), mirror_layer(layer._key_dense), mirror_layer(layer._value_dense),
+                      mirror_layer(layer._output_dense), mirror_softmax(layer._softmax), layer.parallelization_factor, **kw)

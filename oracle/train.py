@@ -41,6 +41,8 @@ def mirror_model(model):
         name = type(layer).__name__
         if name in ('QDense', 'QEinsumDense', 'QConv2D'):
             out.append(OL.mirror_layer(layer))
+        elif name == 'QMultiHeadAttention':
+            out.append(OL.mirror_mha(layer))
         elif name == 'Lambda':
             out.append(layer.function)
         elif name == 'Flatten':
@@ -52,8 +54,31 @@ def mirror_model(model):
             raise NotImplementedError(name)
     twin = OracleSequential(out)
     pairs = []
+
+    def quantizer_pairs(pl_q, ol_q):
+        iq = pl_q.quantizer
+        for vname, leaf in ol_q.trainable_leaves().items():
+            pairs.append((leaf, getattr(iq, '_' + vname), None, None))
+
     for pl, ol in zip(model.layers, out):
         if not isinstance(ol, OL.OracleQLayer):
+            continue
+        if isinstance(ol, OL.OracleQMHA):
+            for pd, od in ((pl._query_dense, ol.q), (pl._key_dense, ol.k), (pl._value_dense, ol.v), (pl._output_dense, ol.o)):
+                pairs.append((od.kernel, pd._kernel, None, None))
+                if od.bias is not None:
+                    pairs.append((od.bias, pd._bias, None, None))
+                for qname, oq in od.quantizers().items():
+                    if qname == 'iq' and any(oq is q2 for q2 in ()):
+                        continue
+                    quantizer_pairs(getattr(pd, qname), oq)
+            sm, osm = pl._softmax, ol.softmax
+            quantizer_pairs(sm.oq, osm.oq)
+            for tp, to in ((sm.exp_table, osm.exp_table), (sm.inv_table, osm.inv_table)):
+                quantizer_pairs(tp.iq, to.iq)
+                quantizer_pairs(tp.oq, to.oq)
+            if ol.oq is not None:
+                quantizer_pairs(pl.oq, ol.oq)
             continue
         pairs.append((ol.kernel, pl._kernel, None, None))
         if ol.bias is not None:

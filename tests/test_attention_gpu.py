@@ -1,0 +1,98 @@
+"""QSoftmax and QMultiHeadAttention (CUDA kernels for every quantizer and projection) against their CPU oracle twins."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hgq_layers as OL
+
+pytestmark = pytest.mark.gpu
+
+
+def close(a, b, rtol, what):
+    a = a.detach().cpu().double().numpy()
+    b = b.detach().cpu().double().numpy()
+    scale = max(np.abs(b).max(), 1e-30)
+    err = np.abs(a - b).max() / scale
+    assert err <= rtol, f'{what}: error {err:.3e} relative to max |ref| {scale:.3e} exceeds {rtol}'
+
+
+def compare_quantizer_grads(pairs):
+    """pairs: (product Quantizer, oracle quantizer, label)."""
+    for pq, oq, label in pairs:
+        iq = pq.quantizer
+        assert torch.equal(iq._i.value.detach().cpu(), oq._i.detach()), f'{label}._i'
+        assert torch.equal(iq.bits.detach().cpu(), oq.bits.detach()), f'{label}.bits'
+        for vname, leaf in oq.trainable_leaves().items():
+            g = getattr(iq, '_' + vname).value.grad
+            assert g is not None, f'{label}.{vname} got no gradient'
+            close(g, leaf.grad, 1e-4, f'd {label}.{vname}')
+
+
+def scopes(beta0=1e-3):
+    from hgq2_b200.config import LayerConfigScope, QuantizerConfigScope
+
+    a = QuantizerConfigScope(place='datalane', default_q_type='kif', overflow_mode='WRAP', round_mode='RND', i0=4, f0=8)
+    t = QuantizerConfigScope(place='table', b0=10, i0=1)
+    return a, t, LayerConfigScope(beta0=beta0, enable_ebops=True)
+
+
+def test_qsoftmax_matches_oracle():
+    from hgq2_b200.layers import QSoftmax
+    from hgq2_b200.quantizer import QuantizerConfig
+
+    rng = np.random.default_rng(0)
+    a, t, l = scopes()
+    with a, t, l:
+        layer = QSoftmax(axis=-1, enable_oq=True, exp_iq_conf=QuantizerConfig(place='datalane', overflow_mode='SAT', i0=4, f0=6),
+                         input_scaler=0.25)
+    x_np = (np.round(rng.standard_normal((64, 4, 16, 16)) * 3 * 64) / 64).astype(np.float32)
+    x = torch.from_numpy(x_np).cuda().requires_grad_()
+    layer(x.detach()[:2], training=False)
+    twin = OL.mirror_softmax(layer)
+    xc = torch.from_numpy(x_np).requires_grad_()
+    y, yc = layer(x, training=True), twin(xc, training=True)
+    close(y, yc, 1e-5, 'softmax output')
+    assert layer.ebops == twin.total_ebops()
+    w = torch.from_numpy(rng.standard_normal(tuple(yc.shape)).astype(np.float32))
+    ((y * w.cuda()).sum() + sum(layer.losses)).backward()
+    ((yc * w).sum() + sum(twin.losses)).backward()
+    close(x.grad, xc.grad, 1e-4, 'dx')
+    compare_quantizer_grads([(layer.oq, twin.oq, 'oq'), (layer.exp_table.iq, twin.exp_table.iq, 'exp.iq'),
+                             (layer.exp_table.oq, twin.exp_table.oq, 'exp.oq'), (layer.inv_table.iq, twin.inv_table.iq, 'inv.iq'),
+                             (layer.inv_table.oq, twin.inv_table.oq, 'inv.oq')])
+    close(layer(x.detach(), training=False), twin(torch.from_numpy(x_np), training=False), 1e-5, 'eval output')
+
+
+@pytest.mark.parametrize('fuse', ['none', 'qkv'])
+def test_qmha_matches_oracle(fuse):
+    from hgq2_b200.layers import QMultiHeadAttention
+    from hgq2_b200.workloads import randomize_weight_bits
+
+    rng = np.random.default_rng(1)
+    a, t, l = scopes()
+    with a, t, l:
+        layer = QMultiHeadAttention(2, 8, fuse=fuse, name=f'mha_{fuse}')
+    x_np = (np.round(rng.standard_normal((48, 12, 16)) * 64) / 64).astype(np.float32)
+    x = torch.from_numpy(x_np).cuda().requires_grad_()
+    layer(x.detach()[:2], training=False)
+    randomize_weight_bits(layer, 3, 7)
+    twin = OL.mirror_mha(layer)
+    xc = torch.from_numpy(x_np).requires_grad_()
+    y, yc = layer(x, training=True), twin(xc, training=True)
+    close(y, yc, 1e-5, 'attention output')
+    assert int(layer.ebops) == twin.total_ebops(), (int(layer.ebops), twin.total_ebops())
+    w = torch.from_numpy(rng.standard_normal(tuple(yc.shape)).astype(np.float32))
+    ((y * w.cuda()).sum() / 48 + sum(layer.losses)).backward()
+    ((yc * w).sum() / 48 + sum(twin.losses)).backward()
+    close(x.grad, xc.grad, 1e-4, 'dx')
+    for pl, ol, name in ((layer._query_dense, twin.q, 'q'), (layer._key_dense, twin.k, 'k'), (layer._value_dense, twin.v, 'v'),
+                         (layer._output_dense, twin.o, 'o')):
+        close(pl._kernel.value.grad, ol.kernel.grad, 1e-4, f'd {name}.kernel')
+        pairs = [(pl.kq, ol.kq, f'{name}.kq')]
+        if pl.enable_oq:
+            pairs.append((pl.oq, ol.oq, f'{name}.oq'))
+        if pl.enable_iq and not (fuse == 'qkv' and name in ('q', 'k')):
+            pairs.append((pl.iq, ol.iq, f'{name}.iq'))
+        compare_quantizer_grads(pairs)
+    close(layer(x.detach(), training=False), twin(torch.from_numpy(x_np), training=False), 1e-5, 'eval output')

@@ -41,7 +41,8 @@ def run_steps(builder, x_np, y_np, steps=3, beta0=1e-5, lr=1e-3):
         oloss.backward()
         close(loss, oloss, 1e-5, f'loss at step {s}')
         for pl, ol in zip([l for l in model.layers if hasattr(l, '_ebops')], twin.qlayers()):
-            assert int(pl.ebops.item()) == int(ol.ebops.item()), f'EBOPs of {pl.name} at step {s}'
+            want = ol.total_ebops() if hasattr(ol, 'total_ebops') else int(ol.ebops.item())
+            assert int(pl.ebops) == want, f'EBOPs of {pl.name} at step {s}'
         for leaf, var, _, _ in pairs:
             g = var.value.grad
             if var.regularizer is not None:  # the product adds the regulariser's constant gradient inside the optimizer
@@ -85,6 +86,15 @@ def test_small_cnn_steps():
     x = rng.uniform(0, 1, (48, 32, 32, 3)).astype(np.float32)
     y = np.random.default_rng(2).integers(0, 10, 48)
     run_steps(workloads.small_cnn, x, y, steps=2)
+
+
+def test_transformer_block_steps():
+    from hgq2_b200 import workloads
+
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((32, 16, 32)).astype(np.float32)
+    y = np.random.default_rng(2).integers(0, 5, 32)
+    run_steps(lambda beta0: workloads.transformer_block(seq=16, d_model=32, heads=2, beta0=beta0), x, y, steps=2)
 
 
 def test_adam_kernel_matches_keras_rule():
