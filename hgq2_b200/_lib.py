@@ -57,6 +57,12 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_uint, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
          c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    'hgq_qdense_bwd_workspace': (c_size_t, [c_int64, c_int, c_int, c_int]),
+    'hgq_qdense_bwd': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+         c_int, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

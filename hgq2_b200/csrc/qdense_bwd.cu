@@ -1,0 +1,470 @@
+// K2b (dense / einsum-dense backward): one pass over dY, y and x produces dX, dWq, dbq and the input quantizer's
+// fractional-bit gradient.
+//
+// Stands in for the autograd backward of QDense.call / QEinsumDense.call (src/hgq/layers/core/dense.py:60-68,
+// einsum_dense.py:72-83) with a rounding-only input quantizer (the training-mode WRAP activation quantizer,
+// src/hgq/quantizer/internal/fixed_point_quantizer.py:403-424):
+//     G   = dY * (y > 0)                      (ReLU mask; G = dY without activation)
+//     dXq = G @ Wq^T          dX = dXq        (straight-through rounding)
+//     df[p, k]  = sum over rows r = p (mod rows_period) of (-ln2 (xq - x)) * dXq
+//     dWq = xq^T @ G          dbq = sum_r G
+// Per 128-row tile the CTA converts G and the recomputed xq to bf16 terms in shared memory (two terms each: 16
+// significant bits, far inside the 1e-4 gradient tolerance; the weights are split exactly), then one thread issues
+//   MMA1  dXq [128 x K]   = G (K-major over n)      x  Wq rows (K-major over n)       accumulator 1 in TMEM
+//   MMA2  dWq [K+1 x N]  += xq^T (MN-major, + a row of ones that yields dbq)  x  G (MN-major)   accumulator 2 in TMEM,
+// the second accumulating over all tiles of the CTA.  The same G buffer serves as the A operand of MMA1 and as the B
+// operand of MMA2: a core matrix "8 rows x 8 columns, 16 bytes per row" is both a K-major and an MN-major core.
+// The epilogue reads dXq back, forms the df terms against x (re-read, L2-resident) and writes dX through a swizzled
+// staging block as full lines.  Per-CTA partials of dWq / dbq / df go to scratch and are reduced in a fixed order by a
+// second kernel, so results do not depend on scheduling.
+// HBM-bound: 4 (2N + 2K) bytes per row (dY, y, x in; dX out).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "hgq_common.cuh"
+#include "hgq_math.cuh"
+#include "tc05.cuh"
+
+namespace hgq {
+
+constexpr int kQbThreads = 512;
+constexpr int kQbTileM = 128;
+constexpr int kQbXTermBytes = 128 * 128 * 2;  // xq^T operand: 128 rows x 128 (padded) columns of bf16
+
+struct QbParams {
+    const float *gy, *y, *x, *qf, *wq;
+    float *dx;
+    float *part;        // per-CTA partials: [(K+1) x N] dWq|dbq, then [rows_period x K] df
+    unsigned *status;
+    int64_t M, num_tiles;
+    int K, N, Kp, Np, Kt;
+    int rows_period, rm, relu, want_df;
+};
+
+// two-term bf16 split of a pair: hi = RN(v), lo = RN(v - hi)
+__device__ __forceinline__ void split2_pair(float v0, float v1, uint32_t &hi, uint32_t &lo) {
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+    hi = *reinterpret_cast<const uint32_t *>(&h2);
+    const float r0 = __fsub_rn(v0, __uint_as_float(hi << 16));
+    const float r1 = __fsub_rn(v1, __uint_as_float(hi & 0xffff0000u));
+    const __nv_bfloat162 l2 = __floats2bfloat162_rn(r0, r1);
+    lo = *reinterpret_cast<const uint32_t *>(&l2);
+}
+
+template <bool CONV>
+__device__ __forceinline__ float round_e(float v, uint32_t ebyte, float rbias) {
+    const uint32_t sbits = ebyte << 23;  // 2^f
+    const float xs = __fmul_rn(v, __uint_as_float(sbits));
+    const float q = CONV ? rintf(xs) : floorf(__fadd_rn(xs, rbias));
+    return __fmul_rn(q, __uint_as_float(0x7F000000u - sbits));
+}
+
+template <bool CONV>
+__global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int K = P.K, N = P.N, Kp = P.Kp, Np = P.Np;
+    const int CGn = Np >> 3, CGk = Kp >> 3;              // 8-column groups of G and of x
+    const int g_term_bytes = kQbTileM * Np * 2;
+    const int w_term_bytes = Kp * Np * 2;
+    // carve: G terms (2) | xq^T terms (2) | W terms (3) | exponent table | barrier + tmem slot
+    unsigned char *G = smem;
+    unsigned char *X = G + 2 * g_term_bytes;
+    unsigned char *W = X + 2 * kQbXTermBytes;
+    const int Ke = P.Kt + 8;
+    unsigned char *etab = W + 3 * w_term_bytes;
+    const int tab_bytes = (P.qf != nullptr) ? (P.rows_period * Ke + 15) / 16 * 16 : 0;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(etab + tab_bytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < Kp + Np) tmem_cols <<= 1;
+
+    // ---- set-up -------------------------------------------------------------------------------------------------
+    if (tid == 0) {
+        tc::mbar_init(bar, 1);
+        tc::mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
+    if (P.qf != nullptr)
+        for (int e = tid; e < P.rows_period * P.Kt; e += kQbThreads) {
+            const int pr = e / P.Kt, k = e % P.Kt;
+            const int fi = (k < K) ? __float2int_rn(__ldg(P.qf + pr * K + k)) : 0;
+            etab[pr * Ke + k] = (unsigned char)(max(-126, min(127, fi)) + 127);
+        }
+    // xq^T operand: zero everywhere (padding rows k >= K stay zero for ever), ones in row k = K when no conversion
+    // group covers it (K % 8 == 0); otherwise the conversion loop writes that 1.0 itself
+    for (int e = tid; e < 2 * kQbXTermBytes / 16; e += kQbThreads) reinterpret_cast<uint4 *>(X)[e] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    if ((K & 7) == 0)
+        for (int r = tid; r < kQbTileM; r += kQbThreads)
+            *reinterpret_cast<unsigned short *>(X + ((r >> 3) * 16 + (K >> 3)) * 128 + (r & 7) * 16) = 0x3F80;  // bf16 1.0
+    // weights as the B operand of MMA1: rows k (the MMA's N index), contraction n; core (k/8, n/8)
+    int w_lo = 0, w_lo2 = 0;
+    for (int e = tid; e < Kp * Np; e += kQbThreads) {
+        const int n = e % Np, k = e / Np;
+        const float w = (k < K && n < N) ? __ldg(P.wq + (int64_t)k * N + n) : 0.f;
+        __nv_bfloat16 h, l, l2;
+        tc::split3(w, h, l, l2);
+        const int off = ((k >> 3) * CGn + (n >> 3)) * 128 + (k & 7) * 16 + (n & 7) * 2;
+        *reinterpret_cast<__nv_bfloat16 *>(W + off) = h;
+        *reinterpret_cast<__nv_bfloat16 *>(W + w_term_bytes + off) = l;
+        *reinterpret_cast<__nv_bfloat16 *>(W + 2 * w_term_bytes + off) = l2;
+        w_lo |= (__bfloat16_as_ushort(l) & 0x7fff) != 0;
+        w_lo2 |= (__bfloat16_as_ushort(l2) & 0x7fff) != 0;
+    }
+    const int any_w_lo = __syncthreads_or(w_lo);
+    const int any_w_lo2 = __syncthreads_or(w_lo2);
+    const int n_w = any_w_lo2 ? 3 : (any_w_lo ? 2 : 1);
+    tc::fence_smem_to_async();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t acc1 = tmem_base, acc2 = tmem_base + (uint32_t)Kp;
+    const uint32_t idesc1 = tc::make_idesc_bf16(Kp, false, false);
+    const uint32_t idesc2 = tc::make_idesc_bf16(Np, true, true);
+    const uint32_t g_base = tc::smem_u32(G), x_base = tc::smem_u32(X), w_base = tc::smem_u32(W);
+
+    const int r8 = lane & 7, q4 = lane >> 3;
+    const bool vec_n = (N % 4 == 0) && aligned(P.gy, 16) && (P.y == nullptr || aligned(P.y, 16));
+    const bool vec_k = (K % 4 == 0) && aligned(P.x, 16);
+    const float rbias = (P.rm == RM_RND) ? 0.5f : 0.f;
+    const uint32_t rp = (uint32_t)P.rows_period;  // divides 128 (checked on the host), so a tile starts at table row 0
+    uint32_t phase = 0;
+    bool ok = true;
+    bool first_tile = true;
+
+    // epilogue ownership: thread = (lane quarter q, column part cp): row r = 32 q + lane and the 8-column chunks
+    // cp and cp + 4 of the accumulator (Kp <= 64: at most 8 chunks)
+    const int qlane = (warp & 3) * 32, cpart = warp >> 2;
+    const int nchunk = Kp >> 3;
+    float df_r[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) df_r[j] = 0.f;
+
+    for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
+        const int64_t row0 = tile * kQbTileM;
+        // ---- G = dY (* relu mask), two bf16 terms, core (row/8, n/8) ------------------------------------------------
+        {
+            const int CG4 = (CGn + 3) >> 2;
+            for (int c = warp; c < 16 * CG4; c += kQbThreads / 32) {
+                const int mg = c / CG4, kg = (c - mg * CG4) * 4 + q4;
+                if (kg >= CGn) continue;
+                const int64_t row = row0 + mg * 8 + r8;
+                const int n0 = kg * 8;
+                float v[8];
+                if (row < P.M && vec_n && n0 + 8 <= N) {
+                    const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0));
+                    const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0 + 4));
+                    v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+                    if (P.relu) {
+                        const float4 y0 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0));
+                        const float4 y1 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0 + 4));
+                        v[0] = y0.x > 0.f ? v[0] : 0.f; v[1] = y0.y > 0.f ? v[1] : 0.f; v[2] = y0.z > 0.f ? v[2] : 0.f;
+                        v[3] = y0.w > 0.f ? v[3] : 0.f; v[4] = y1.x > 0.f ? v[4] : 0.f; v[5] = y1.y > 0.f ? v[5] : 0.f;
+                        v[6] = y1.z > 0.f ? v[6] : 0.f; v[7] = y1.w > 0.f ? v[7] : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const bool in = row < P.M && n0 + j < N;
+                        float t = in ? __ldcs(P.gy + row * N + n0 + j) : 0.f;
+                        if (in && P.relu && !(__ldcs(P.y + row * N + n0 + j) > 0.f)) t = 0.f;
+                        v[j] = t;
+                    }
+                }
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) split2_pair(v[j], v[j + 1], hi[j >> 1], lo[j >> 1]);
+                const int off = (mg * CGn + kg) * 128 + r8 * 16;
+                *reinterpret_cast<uint4 *>(G + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4 *>(G + g_term_bytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+        }
+        // ---- xq = round(x), two bf16 terms, transposed operand: core (row/8, k/8) in a 16-group-wide buffer ----------
+        {
+            const int groups = CGk;
+            const int CG4 = (groups + 3) >> 2;
+            for (int c = warp; c < 16 * CG4; c += kQbThreads / 32) {
+                const int mg = c / CG4, kg = (c - mg * CG4) * 4 + q4;
+                if (kg >= groups) continue;
+                const int64_t row = row0 + mg * 8 + r8;
+                const int k0 = kg * 8;
+                float v[8];
+                if (row < P.M && vec_k && k0 + 8 <= K) {
+                    const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0));
+                    const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0 + 4));
+                    v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = (row < P.M && k0 + j < K) ? __ldcs(P.x + row * K + k0 + j) : 0.f;
+                }
+                if (P.qf != nullptr) {
+                    const uint32_t pr = (uint32_t)(mg * 8 + r8) % rp;
+                    const uint2 eb = *reinterpret_cast<const uint2 *>(etab + pr * Ke + k0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = round_e<CONV>(v[j], ((j < 4 ? eb.x : eb.y) >> ((j & 3) * 8)) & 0xffu, rbias);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (k0 + j >= K) v[j] = (k0 + j == K) ? 1.f : 0.f;  // the row of ones that accumulates dbq
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) split2_pair(v[j], v[j + 1], hi[j >> 1], lo[j >> 1]);
+                const int off = (mg * 16 + kg) * 128 + r8 * 16;
+                *reinterpret_cast<uint4 *>(X + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4 *>(X + kQbXTermBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+        }
+        tc::fence_smem_to_async();
+        __syncthreads();
+        // ---- tensor cores -------------------------------------------------------------------------------------------
+        if (tid == 0) {
+            tc::fence_after_sync();
+            // MMA1: dXq = G x Wq^T, contraction over n in steps of 16
+            bool first = true;
+            for (int s = 0; s < Np / 16; ++s)
+                for (int tg = 0; tg < 2; ++tg) {
+                    const uint64_t da = tc::make_smem_desc(g_base + tg * g_term_bytes + s * 256, 128, (uint32_t)CGn * 128);
+                    for (int tw = 0; tw < n_w; ++tw) {
+                        const uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes + s * 256, 128, (uint32_t)CGn * 128);
+                        tc::mma_bf16(acc1, da, db, idesc1, !first);
+                        first = false;
+                    }
+                }
+            // MMA2: dWq (+ dbq row) += xq^T x G, contraction over the 128 rows in steps of 16; both operands MN-major:
+            // stride between 8-groups along M/N = 128 B (sbo), between 8-groups along the rows = one buffer row (lbo)
+            for (int s = 0; s < kQbTileM / 16; ++s)
+                for (int tx = 0; tx < 2; ++tx) {
+                    const uint64_t da = tc::make_smem_desc(x_base + tx * kQbXTermBytes + s * (2 * 16 * 128), 16 * 128, 128);
+                    for (int tg = 0; tg < 2; ++tg) {
+                        const uint64_t db = tc::make_smem_desc(g_base + tg * g_term_bytes + s * (2 * CGn * 128), (uint32_t)CGn * 128, 128);
+                        tc::mma_bf16(acc2, da, db, idesc2, !(first_tile && s == 0 && tx == 0 && tg == 0));
+                    }
+                }
+            tc::commit(bar);
+        }
+        first_tile = false;
+        const bool waited = (warp == 0) ? tc::mbar_wait(bar, phase) : true;
+        phase ^= 1u;
+        ok = __syncthreads_and(waited ? 1 : 0) != 0;
+        if (!ok) {
+            if (tid == 0 && P.status) atomicOr(P.status, 1u);
+            break;
+        }
+        // ---- epilogue: dXq -> df terms, dX ----------------------------------------------------------------------------
+        tc::fence_after_sync();
+        {
+            const int r = qlane + lane;
+            const int64_t row = row0 + r;
+            float v[16];
+#pragma unroll
+            for (int ci = 0; ci < 2; ++ci) {
+                const int chunk = cpart + 4 * ci;  // warp-uniform
+                if (chunk < nchunk) tc::tmem_ld8v(acc1 + ((uint32_t)qlane << 16) + (uint32_t)(chunk * 8), v + ci * 8);
+            }
+            if (P.want_df && P.qf != nullptr && row < P.M) {
+                const uint32_t pr = (uint32_t)r % rp;
+#pragma unroll
+                for (int ci = 0; ci < 2; ++ci) {
+                    const int kb = (cpart + 4 * ci) * 8;
+                    if (kb < K) {
+                        float xr[8];
+                        if (vec_k && kb + 8 <= K) {
+                            const float4 a0 = __ldg(reinterpret_cast<const float4 *>(P.x + row * K + kb));
+                            const float4 a1 = __ldg(reinterpret_cast<const float4 *>(P.x + row * K + kb + 4));
+                            xr[0] = a0.x; xr[1] = a0.y; xr[2] = a0.z; xr[3] = a0.w; xr[4] = a1.x; xr[5] = a1.y; xr[6] = a1.z; xr[7] = a1.w;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) xr[j] = (kb + j < K) ? __ldg(P.x + row * K + kb + j) : 0.f;
+                        }
+                        const uint2 eb = *reinterpret_cast<const uint2 *>(etab + pr * Ke + kb);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (kb + j < K) {
+                                const float xq = round_e<CONV>(xr[j], ((j < 4 ? eb.x : eb.y) >> ((j & 3) * 8)) & 0xffu, rbias);
+                                const float delta = __fsub_rn(xq, xr[j]);
+                                df_r[ci * 8 + j] = __fadd_rn(df_r[ci * 8 + j], __fmul_rn(__fmul_rn(delta, -kLn2), v[ci * 8 + j]));
+                            }
+                        }
+                    }
+                }
+            }
+            if (P.dx != nullptr) {
+                // Stage the [128 x Kp] block, then write full lines.  The staging floats are laid over exactly those
+                // 128-byte blocks of the xq^T buffers that the next tile's conversion rewrites (row groups x the first
+                // Kp/8 column groups of both terms), so the zero padding and the ones row are never disturbed.
+                const int C = Kp >> 2;                                   // 16-byte chunks per row
+                const int swm = ((C & -C) - 1) & 7;                      // XOR mask that stays inside the row
+                auto st_addr = [&](int rr, int c4s, int w) -> float * {  // float address of (row, swizzled chunk, word)
+                    const int L = rr * Kp + (c4s << 2) + w;
+                    const int b = L >> 5, within = L & 31;
+                    const int t = b / (16 * CGk), rem = b - t * (16 * CGk);
+                    const int rg = rem / CGk, kg = rem - rg * CGk;
+                    return reinterpret_cast<float *>(X + t * kQbXTermBytes + (rg * 16 + kg) * 128) + within;
+                };
+#pragma unroll
+                for (int ci = 0; ci < 2; ++ci) {
+                    const int chunk = cpart + 4 * ci;
+                    if (chunk < nchunk) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int c4 = chunk * 2 + h;
+                            *reinterpret_cast<float4 *>(st_addr(r, c4 ^ (r & swm), 0)) =
+                                make_float4(v[ci * 8 + 4 * h], v[ci * 8 + 4 * h + 1], v[ci * 8 + 4 * h + 2], v[ci * 8 + 4 * h + 3]);
+                        }
+                    }
+                }
+                __syncthreads();
+                const int64_t rows_here = (P.M - row0) < kQbTileM ? (P.M - row0) : kQbTileM;
+                if (vec_k) {
+                    const int cv = K >> 2;
+                    for (int g = tid; g < (int)rows_here * cv; g += kQbThreads) {
+                        const int rr = g / cv, c4 = g - rr * cv;
+                        const float4 o = *reinterpret_cast<const float4 *>(st_addr(rr, c4 ^ (rr & swm), 0));
+                        __stcs(reinterpret_cast<float4 *>(P.dx + (row0 + rr) * K) + c4, o);
+                    }
+                } else {
+                    for (int g = tid; g < (int)rows_here * K; g += kQbThreads) {
+                        const int rr = g / K, k = g - rr * K;
+                        __stcs(P.dx + (row0 + rr) * K + k, *st_addr(rr, (k >> 2) ^ (rr & swm), k & 3));
+                    }
+                }
+            }
+        }
+        tc::fence_before_sync();
+        __syncthreads();
+    }
+
+    // ---- per-CTA partials: dWq | dbq from accumulator 2, df from the registers ------------------------------------------
+    const bool did_work = (int64_t)blockIdx.x < P.num_tiles;
+    float *pw = P.part + (int64_t)blockIdx.x * ((int64_t)(K + 1) * N + (int64_t)P.rows_period * K);
+    float *pdf = pw + (int64_t)(K + 1) * N;
+    if (ok && did_work) {
+        tc::fence_after_sync();
+        const int r = qlane + lane;  // accumulator lane = k index (lane K holds dbq)
+        const int ncol = Np >> 2;    // columns per thread
+        for (int c0 = cpart * ncol; c0 < (cpart + 1) * ncol; c0 += 8) {
+            float v[8];
+            tc::tmem_ld8v(acc2 + ((uint32_t)qlane << 16) + (uint32_t)c0, v);
+            if (r <= K)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (c0 + j < N) pw[(int64_t)r * N + c0 + j] = v[j];
+        }
+    } else {
+        for (int e = tid; e < (K + 1) * N; e += kQbThreads) pw[e] = 0.f;
+    }
+    if (P.want_df && P.qf != nullptr) {
+        // rows of the tile that share a table row are summed in a fixed order through shared memory
+        __syncthreads();
+        float *st = reinterpret_cast<float *>(X);  // [128][Kp]
+        const int r = qlane + lane;
+#pragma unroll
+        for (int ci = 0; ci < 2; ++ci)
+            if (cpart + 4 * ci < nchunk)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) st[r * Kp + (cpart + 4 * ci) * 8 + j] = df_r[ci * 8 + j];
+        __syncthreads();
+        for (int e = tid; e < P.rows_period * K; e += kQbThreads) {
+            const int pr = e / K, k = e - pr * K;
+            float a = 0.f;
+            for (int rr = pr; rr < kQbTileM; rr += P.rows_period) a = __fadd_rn(a, st[rr * Kp + k]);
+            pdf[e] = a;
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// out[e] = sum over CTAs of part[cta * stride + offset + e], in double, fixed order
+__global__ void __launch_bounds__(kThreads) k_qb_stage2(const float *__restrict__ part, int64_t stride, int64_t offset,
+                                                       float *__restrict__ out, int64_t n, int nparts) {
+    const int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (e >= n) return;
+    double acc = 0.0;
+    for (int p = 0; p < nparts; ++p) acc += (double)part[(int64_t)p * stride + offset + e];
+    out[e] = (float)acc;
+}
+
+struct QbGeom {
+    int Kp, Np, Kt, grid;
+    size_t smem;
+    int64_t tiles, part_stride;
+};
+
+static int qb_geom(int64_t M, int K, int N, int rows_period, QbGeom &g) {
+    if (M <= 0 || K <= 0 || N <= 0 || rows_period <= 0) return HGQ_ERR_SIZE;
+    if (K > 64 || N > 128) return HGQ_ERR_SIZE;
+    if (kQbTileM % rows_period != 0) return HGQ_ERR_SIZE;
+    g.Kp = (K + 15) / 16 * 16;
+    g.Np = (N + 15) / 16 * 16;
+    g.Kt = (K + 7) / 8 * 8;
+    const size_t tab = ((size_t)rows_period * (g.Kt + 8) + 15) / 16 * 16;
+    g.smem = 2 * (size_t)kQbTileM * g.Np * 2 + 2 * (size_t)kQbXTermBytes + 3 * (size_t)g.Kp * g.Np * 2 + tab + 64;
+    if (g.smem > 226 * 1024) return HGQ_ERR_SIZE;
+    g.tiles = (M + kQbTileM - 1) / kQbTileM;
+    int64_t grid = kNumSMs;  // 512 threads, > 113 KB shared memory: one CTA per SM
+    if (grid > g.tiles) grid = g.tiles;
+    g.grid = (int)grid;
+    g.part_stride = (int64_t)(K + 1) * N + (int64_t)rows_period * K;
+    return HGQ_OK;
+}
+
+}  // namespace hgq
+
+using namespace hgq;
+
+extern "C" size_t hgq_qdense_bwd_workspace(int64_t M, int K, int N, int rows_period) {
+    QbGeom g;
+    if (qb_geom(M, K, N, rows_period, g) != HGQ_OK) return 0;
+    return (size_t)kNumSMs * g.part_stride * sizeof(float);
+}
+
+extern "C" int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float *qf, int rows_period,
+                              int round_mode, const float *wq, float *dx, float *dwq, float *dbq, float *df, int64_t M,
+                              int K, int N, void *workspace, size_t workspace_bytes, unsigned *status, void *stream) {
+    if (gy == nullptr || x == nullptr || wq == nullptr || dwq == nullptr) return HGQ_ERR_NULL;
+    if (round_mode < 0 || round_mode > 2) return HGQ_ERR_MODE;
+    if (df != nullptr && qf == nullptr) return HGQ_ERR_NULL;
+    QbGeom g;
+    if (int e = qb_geom(M, K, N, rows_period, g)) return e;
+    const size_t need = (size_t)g.grid * g.part_stride * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need) return HGQ_ERR_WORKSPACE;
+    if (!aligned(workspace, 16)) return HGQ_ERR_ALIGN;
+    QbParams p;
+    p.gy = gy; p.y = y; p.x = x; p.qf = qf; p.wq = wq; p.dx = dx;
+    p.part = (float *)workspace;
+    p.status = status;
+    p.M = M; p.num_tiles = g.tiles;
+    p.K = K; p.N = N; p.Kp = g.Kp; p.Np = g.Np; p.Kt = g.Kt;
+    p.rows_period = rows_period; p.rm = round_mode; p.relu = (y != nullptr) ? 1 : 0; p.want_df = (df != nullptr) ? 1 : 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t ce;
+    if (round_mode == RM_RND_CONV) {
+        ce = cudaFuncSetAttribute(k_qdense_bwd<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_qdense_bwd<true><<<g.grid, kQbThreads, g.smem, st>>>(p);
+    } else {
+        ce = cudaFuncSetAttribute(k_qdense_bwd<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_qdense_bwd<false><<<g.grid, kQbThreads, g.smem, st>>>(p);
+    }
+    if (int e = check_launch()) return e;
+    const int64_t nw = (int64_t)K * N;
+    k_qb_stage2<<<(unsigned)((nw + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, g.part_stride, 0, dwq, nw, g.grid);
+    if (int e = check_launch()) return e;
+    if (dbq != nullptr) {
+        k_qb_stage2<<<(unsigned)((N + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, g.part_stride, nw, dbq, N, g.grid);
+        if (int e = check_launch()) return e;
+    }
+    if (df != nullptr) {
+        const int64_t nf = (int64_t)rows_period * K;
+        k_qb_stage2<<<(unsigned)((nf + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, g.part_stride, (int64_t)(K + 1) * N, df,
+                                                                                  nf, g.grid);
+        if (int e = check_launch()) return e;
+    }
+    return HGQ_OK;
+}

@@ -244,3 +244,30 @@ def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: 
         )
     check(st, 'hgq_qdense_fwd')
     return y, absmax
+
+
+def qdense_bwd_supported(M: int, K: int, N: int, rows_period: int) -> bool:
+    return M > 0 and lib().hgq_qdense_bwd_workspace(M, K, N, rows_period) > 0
+
+
+def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: bool, want_db: bool, want_df: bool):
+    """Fused backward of qdense_fwd (rounding-only input quantizer or none).  gy/y are [M, N], x [M, K].
+    Returns (dx or None, dwq, dbq or None, df or None)."""
+    require_cuda(gy, y, x, qf, wq)
+    rm = ROUND_MODES[round_mode.upper()]
+    gy, x, wq = gy.contiguous(), x.contiguous(), wq.contiguous()
+    y = None if y is None else y.contiguous()
+    qf = None if qf is None else qf.contiguous()
+    K, N = wq.shape
+    M = x.numel() // K
+    dev = x.device
+    dx = torch.empty((M, K), dtype=torch.float32, device=dev) if want_dx else None
+    dwq = torch.empty((K, N), dtype=torch.float32, device=dev)
+    dbq = torch.empty(N, dtype=torch.float32, device=dev) if want_db else None
+    df = torch.empty(rows_period * K, dtype=torch.float32, device=dev) if (want_df and qf is not None) else None
+    ws = workspace(lib().hgq_qdense_bwd_workspace(M, K, N, rows_period), dev, slot=2)
+    with torch.cuda.device(dev):
+        st = lib().hgq_qdense_bwd(ptr(gy), ptr(y), ptr(x), ptr(qf), rows_period, rm, ptr(wq), ptr(dx), ptr(dwq), ptr(dbq), ptr(df),
+                                  M, K, N, ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
+    check(st, 'hgq_qdense_bwd')
+    return dx, dwq, dbq, df

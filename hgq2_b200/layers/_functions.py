@@ -71,11 +71,21 @@ class QDenseFusedFn(torch.autograd.Function):
         rows_period, rm, om, training, zero, activation, has_bias = ctx.meta
         K, N = wq.shape
         gy = gy.contiguous()
+        need_x, need_w, need_b, _, need_i, need_f = ctx.needs_input_grad[:6]
+        round_only = f is not None and (om == 'NONE' or (om == 'WRAP' and training)) and not zero
+        if fused_bwd_enabled and need_w and (f is None or round_only) and kernels.qdense_bwd_supported(x.numel() // K, K, N, rows_period):
+            dx, dwq, dbq, df = kernels.qdense_bwd(gy, y if activation == 'relu' else None, x, f, rows_period, rm, wq,
+                                                  want_dx=need_x, want_db=has_bias and need_b, want_df=bool(need_f))
+            if dx is not None:
+                dx = dx.view(x.shape)
+            if df is not None:
+                df = df.view(f.shape)
+            di = torch.zeros_like(i) if (need_i and i is not None) else None
+            return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None
         if activation == 'relu':
             gy = gy * (y > 0)
         g2 = gy.reshape(-1, N)
         x2 = x.reshape(-1, K)
-        need_x, need_w, need_b, _, need_i, need_f = ctx.needs_input_grad[:6]
         dbq = g2.sum(0) if (has_bias and need_b) else None
         dwq = None
         if need_w:
@@ -99,6 +109,7 @@ class QDenseFusedFn(torch.autograd.Function):
 
 # ---- dispatch of a dense-like layer onto the fused kernel ------------------------------------------------------
 fused_enabled = True  # module switch (tests compare the fused and the unfused formulation)
+fused_bwd_enabled = True
 
 
 def _amax_to_shape(t: torch.Tensor, shape) -> torch.Tensor:

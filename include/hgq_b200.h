@@ -172,6 +172,28 @@ int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi, const flo
                    int activation, float *y, float *absmax, int64_t M, int K, int N, void *workspace,
                    size_t workspace_bytes, unsigned *status, void *stream);
 
+/*
+ * Scratch bytes hgq_qdense_bwd needs (0 if the shape is not supported by the fused backward).
+ */
+size_t hgq_qdense_bwd_workspace(int64_t M, int K, int N, int rows_period);
+
+/*
+ * Backward of hgq_qdense_fwd for a rounding-only input quantizer (training-mode WRAP) or none, in one pass
+ * over gy, y and x.  Stands in for the autograd backward of QDense.call / QEinsumDense.call
+ * (layers/core/dense.py:60-68, einsum_dense.py:72-83) including the quantizer's surrogate gradient.
+ *
+ *   G = gy * (y > 0) if y != NULL (ReLU), else gy;   dx = G @ wq^T (straight-through);
+ *   dwq = round(x)^T @ G;   dbq = column sums of G;   df[p, k] = sum_{r = p mod rows_period} (-ln2 (round(x) - x)) dx
+ *
+ * gy, y [M, N]; x [M, K]; qf [rows_period, K] (NULL: no quantizer, then df must be NULL); wq [K, N];
+ * dx [M, K] (may be NULL); dwq [K, N]; dbq [N] (may be NULL); df [rows_period, K] (may be NULL).
+ * Operands enter the tensor cores as two bf16 terms (16 significant bits), the weights exactly; partial sums are
+ * reduced in a fixed order.  Limits: K <= 64, N <= 128, rows_period divides 128.
+ */
+int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float *qf, int rows_period,
+                   int round_mode, const float *wq, float *dx, float *dwq, float *dbq, float *df, int64_t M,
+                   int K, int N, void *workspace, size_t workspace_bytes, unsigned *status, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*

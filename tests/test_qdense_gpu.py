@@ -85,3 +85,56 @@ def test_fused_dense_no_input_quantizer_and_limits():
     assert not kernels.qdense_supported(100, 64, 200, 1)
     L = _lib.lib()
     assert L.hgq_qdense_fwd(1, None, None, None, 1, 1, 1, 0, 1, None, 0, 1, None, 100, 300, 64, None, 0, None, None) == -2
+
+
+@pytest.mark.parametrize('M,K,N,rows_period', [
+    (1000, 16, 64, 1), (128 * 21 + 5, 64, 64, 64), (4096, 64, 32, 1), (513, 32, 5, 1), (300, 24, 16, 8), (640, 64, 128, 32),
+    (129, 27, 10, 1), (7, 16, 64, 1), (60000, 64, 64, 64), (2000, 48, 40, 2),
+])
+@pytest.mark.parametrize('rm,relu,quant', [('RND', True, True), ('TRN', False, True), ('RND_CONV', True, True), ('RND', True, False)])
+def test_fused_dense_backward(M, K, N, rows_period, rm, relu, quant):
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(M + 3 * K + N)
+    x = torch.from_numpy((rng.standard_normal((M, K)) * 3).astype(np.float32))
+    f = torch.from_numpy(rng.integers(1, 7, (rows_period, K)).astype(np.float32))
+    w = torch.from_numpy(np.round(rng.uniform(-2, 2, (K, N)) * 64) / 64).float()
+    gy = torch.from_numpy(rng.standard_normal((M, N)).astype(np.float32))
+    y = torch.from_numpy(rng.standard_normal((M, N)).astype(np.float32)).clamp_min(0)
+    dx, dwq, dbq, df = kernels.qdense_bwd(gy.cuda(), y.cuda() if relu else None, x.cuda(), f.cuda() if quant else None, rows_period,
+                                          rm, w.cuda(), True, True, quant)
+    kernels.check_status(dx.device)
+    # reference in float64 from the oracle's definitions
+    g = (gy * (y > 0)) if relu else gy
+    rep = M // rows_period + 1
+    ff = f.repeat(rep, 1)[:M]
+    xq = O.round_fwd(x, ff, rm) if quant else x
+    dxr = g.double() @ w.double().t()
+    dwr = xq.double().t() @ g.double()
+    dbr = g.double().sum(0)
+
+    def rel(a, b):
+        return float((a.cpu().double() - b).abs().max() / max(float(b.abs().max()), 1e-30))
+
+    assert rel(dx, dxr) <= 2e-5, ('dx', rel(dx, dxr))
+    assert rel(dwq, dwr) <= 5e-5, ('dwq', rel(dwq, dwr))
+    assert rel(dbq, dbr) <= 5e-5, ('dbq', rel(dbq, dbr))
+    if quant:
+        t = ((xq - x).double() * (-O.LN2)) * dxr
+        dfr = torch.stack([t[p::rows_period].sum(0) for p in range(rows_period)])
+        assert rel(df.view(rows_period, K), dfr) <= 5e-5, ('df', rel(df.view(rows_period, K), dfr))
+
+
+def test_fused_dense_backward_is_deterministic():
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(0)
+    M, K, N = 50000, 64, 64
+    x = torch.from_numpy((rng.standard_normal((M, K)) * 3).astype(np.float32)).cuda()
+    f = torch.full((64, K), 5.0).cuda()
+    w = torch.from_numpy(np.round(rng.uniform(-2, 2, (K, N)) * 64) / 64).float().cuda()
+    gy = torch.from_numpy(rng.standard_normal((M, N)).astype(np.float32)).cuda()
+    a = kernels.qdense_bwd(gy, None, x, f, 64, 'RND', w, True, True, True)
+    b = kernels.qdense_bwd(gy, None, x, f, 64, 'RND', w, True, True, True)
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
