@@ -321,6 +321,8 @@ QAT_CONFIGS = {
     'jet_tagger_mlp': ('jet_tagger_mlp', 16384, lambda rng, b: rng.standard_normal((b, 16), dtype=np.float32), 5, 3324),
     'particle_tagger': ('particle_tagger', 65536, lambda rng, b: rng.standard_normal((b, 64, 16), dtype=np.float32), 5, 162108),
     'small_cnn': ('small_cnn', 4096, lambda rng, b: rng.random((b, 32, 32, 3), dtype=np.float32), 10, 657144),
+    'transformer_block': ('transformer_block', 8192, lambda rng, b: rng.standard_normal((b, 64, 64), dtype=np.float32), 5,
+                          1721916),
 }
 
 

@@ -481,5 +481,12 @@ def mirror_softmax(layer):
 def mirror_mha(layer):
     kw = dict(oq=mirror_quantizer(layer.oq) if layer.enable_oq else None, beta=float(layer.beta) if layer.enable_ebops else 0.0,
               ebops_factor=layer.ebops_factor, enable_ebops=layer.enable_ebops)
-    return OracleQMHA(mirror_layer(layer._query_dense), mirror_layer(layer._key_dense), mirror_layer(layer._value_dense),
-                      mirror_layer(layer._output_dense), mirror_softmax(layer._softmax), layer.parallelization_factor, **kw)
+    q, k, v = mirror_layer(layer._query_dense), mirror_layer(layer._key_dense), mirror_layer(layer._value_dense)
+    # fuse='qkv' / 'kv' share ONE input quantizer object between the projections (mha.py:201-206): its state then
+    # advances once per projection call, so the twin must share it too
+    if layer._query_dense.enable_iq and layer._query_dense._iq is layer._value_dense._iq:
+        q.iq = v.iq
+    if layer._key_dense.enable_iq and layer._key_dense._iq is layer._value_dense._iq:
+        k.iq = v.iq
+    return OracleQMHA(q, k, v, mirror_layer(layer._output_dense), mirror_softmax(layer._softmax), layer.parallelization_factor,
+                      **kw)

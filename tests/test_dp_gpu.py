@@ -1,0 +1,67 @@
+"""Data-parallel QAT on two GPUs (NCCL): two ranks on half batches must end up with the parameters, quantizer state and
+EBOPs of one rank on the whole batch."""
+
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist, torch.nn.functional as F
+sys.path.insert(0, os.environ['HGQ_ROOT'])
+from hgq2_b200 import workloads
+from hgq2_b200.train import DataParallel, Trainer, shard_batch
+
+rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
+torch.cuda.set_device(int(os.environ['LOCAL_RANK']))
+dist.init_process_group('nccl', device_id=torch.device('cuda', int(os.environ['LOCAL_RANK'])))
+rng = np.random.default_rng(1)
+X = torch.from_numpy(rng.standard_normal((4096, 16)).astype(np.float32)).cuda()
+Y = torch.from_numpy(np.random.default_rng(2).integers(0, 5, 4096)).cuda()
+
+def run(dp):
+    model = workloads.build(workloads.jet_tagger_mlp())
+    tr = Trainer(model, F.cross_entropy, dp=dp)
+    sl = shard_batch(4096, rank, world) if dp is not None else slice(None)
+    losses = [float(tr.step(X[sl], Y[sl])) for _ in range(3)]
+    state = [v.value.detach().clone() for v in model.variables]
+    return losses, tr.state.params.clone(), state, [int(l.ebops.item()) for l in model.layers]
+
+l_dp, p_dp, s_dp, e_dp = run(DataParallel())
+l_1, p_1, s_1, e_1 = run(None)
+assert e_dp == e_1, (e_dp, e_1)
+scale = float(p_1.abs().max())
+assert float((p_dp - p_1).abs().max()) <= 2e-3 * 3, float((p_dp - p_1).abs().max())
+frac_bad = float(((p_dp - p_1).abs() > 1e-5 * scale + 1e-7).float().mean())
+assert frac_bad <= 5e-3, frac_bad
+for a, b in zip(s_dp, s_1):
+    if not a.is_floating_point():
+        assert torch.equal(a, b)
+# every rank holds the same parameters
+q = p_dp.clone(); dist.all_reduce(q, op=dist.ReduceOp.MAX); assert torch.equal(q, p_dp)
+if rank == 0:
+    print('DP_OK', l_dp, l_1)
+dist.destroy_process_group()
+'''
+
+
+def test_two_rank_data_parallel_matches_single_rank(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    script = tmp_path / 'dp_worker.py'
+    script.write_text(WORKER)
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, HGQ_ROOT=str(ROOT), NCCL_NVLS_ENABLE='0')
+    r = subprocess.run([sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node=2', '--master-addr', '127.0.0.1',
+                        '--master-port', str(port), str(script)], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0 and 'DP_OK' in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]

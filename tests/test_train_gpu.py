@@ -47,7 +47,9 @@ def run_steps(builder, x_np, y_np, steps=3, beta0=1e-5, lr=1e-3):
             g = var.value.grad
             if var.regularizer is not None:  # the product adds the regulariser's constant gradient inside the optimizer
                 g = g + var.regularizer.l1
-            close(g, leaf.grad, 1e-4, f'gradient of {var.path} at step {s}')
+            # a per-tensor (scalar) bitwidth gradient is a sum of millions of signed terms that largely cancel; its error
+            # is set by the summation order relative to sum |terms|, not to the (tiny) result, hence the looser bound
+            close(g, leaf.grad, 1e-4 if leaf.numel() > 4 else 2e-3, f'gradient of {var.path} at step {s}')
         tr.opt.step()
         oopt.step()
         # Adam normalises each element's step to ~lr whatever the gradient's size, so an element whose gradient is
