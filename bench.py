@@ -326,6 +326,34 @@ QAT_CONFIGS = {
 }
 
 
+def run_qat_single(args):
+    """Eager (no CUDA graph) QAT steps of one benchmark model, for kernel-level profiling of a training step."""
+    import torch.nn.functional as F
+
+    from hgq2_b200 import workloads
+    from hgq2_b200.train import Trainer
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    builder, batch, make_x, classes, _ = QAT_CONFIGS[args.model]
+    batch = args.batch or batch
+    model = workloads.build(getattr(workloads, builder)(), device=dev)
+    tr = Trainer(model, F.cross_entropy)
+    x = torch.from_numpy(make_x(np.random.default_rng(1), batch)).to(dev)
+    y = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch)).to(dev)
+    for _ in range(max(1, args.warmup)):
+        tr.step(x, y)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        loss = tr.step(x, y)
+    b.record()
+    torch.cuda.synchronize()
+    print(json.dumps({'model': args.model, 'batch': batch, 'eager_ms_per_step': round(a.elapsed_time(b) / args.steps, 3),
+                      'loss': float(loss)}), flush=True)
+
+
 def run_qat(args, dev, world, rank, peak):
     """Full QAT steps (forward, backward, gradient all-reduce, fused Adam) of the benchmark models; the global batch is
     fixed and sharded over the ranks.  Reported beside the sweep: samples/s with the batch resident on the device, the
@@ -454,6 +482,38 @@ def run_qdense(args):
                       'tflops': round(2.0 * M * K * N / (ms * 1e-3) / 1e12, 2)}), flush=True)
 
 
+def run_qdense_bwd(args):
+    """Kernel-level benchmark of the fused dense backward (dX, dWq, dbq, df in one pass) on the particle-tagger layer
+    shape.  Algorithmic bytes per row: 4 (2 N + 2 K): dY, y and x in, dX out."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    M, K, N, rp = args.rows, args.k, args.n, args.rows_period
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(M, K, device=dev, generator=gen)
+    gy = torch.randn(M, N, device=dev, generator=gen)
+    y = torch.randn(M, N, device=dev, generator=gen).clamp_min(0)
+    f = torch.full((rp, K), 6.0, device=dev)
+    w = (torch.randint(-128, 128, (K, N), device=dev, generator=gen).float() / 64.0)
+    fn = lambda: kernels.qdense_bwd(gy, y, x, f, rp, 'RND', w, True, True, True)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    kernels.check_status(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    peak, kind = measured_peaks()
+    gbs = 4.0 * (2 * K + 2 * N) * M / (ms * 1e-3) / 1e9
+    print(json.dumps({'kernel': 'k_qdense_bwd', 'M': M, 'K': K, 'N': N, 'rows_period': rp, 'ms': round(ms, 4),
+                      'achieved_GBs': round(gbs, 1), 'peak_GBs': peak, 'frac': round(gbs / peak, 4), 'peak_source': kind}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -465,7 +525,9 @@ def main():
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer end-to-end leg')
     ap.add_argument('--elements', type=int, default=1 << 28,
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense'],
+    ap.add_argument('--model', default='particle_tagger', help='model of --workload qat')
+    ap.add_argument('--batch', type=int, default=0, help='batch of --workload qat (0 = the benchmark batch)')
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qat'],
                     help="'qdense' times the fused dense forward kernel alone (for profiler captures)")
     ap.add_argument('--rows', type=int, default=1 << 22)
     ap.add_argument('--k', type=int, default=64)
@@ -475,6 +537,10 @@ def main():
     globals()['TOTAL_ELEMS'] = args.elements
     if args.workload == 'qdense':
         return run_qdense(args)
+    if args.workload == 'qat':
+        return run_qat_single(args)
+    if args.workload == 'qdense_bwd':
+        return run_qdense_bwd(args)
     if args.impl == 'reference':
         run_reference(args)
     else:

@@ -66,12 +66,15 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
     const int CGn = Np >> 3, CGk = Kp >> 3;              // 8-column groups of G and of x
     const int g_term_bytes = kQbTileM * Np * 2;
     const int w_term_bytes = Kp * Np * 2;
-    // carve: G terms (2) | xq^T terms (2) | W terms (3) | exponent table | barrier + tmem slot
+    // carve: G terms (2) | xq^T terms (2) | W terms (3) | rounding-error stash | exponent table | barrier + tmem slot
     unsigned char *G = smem;
     unsigned char *X = G + 2 * g_term_bytes;
     unsigned char *W = X + 2 * kQbXTermBytes;
+    const int Kd = Kp + 4;                                          // stash row stride (floats): 16-byte accesses of 8 rows spread over the banks
+    float *dstash = reinterpret_cast<float *>(W + 3 * w_term_bytes);  // [128][Kd]: -ln2 * (round(x) - x), consumed by the epilogue
+    const int stash_bytes = (P.want_df && P.qf != nullptr) ? kQbTileM * Kd * 4 : 0;
     const int Ke = P.Kt + 8;
-    unsigned char *etab = W + 3 * w_term_bytes;
+    unsigned char *etab = reinterpret_cast<unsigned char *>(dstash) + stash_bytes;
     const int tab_bytes = (P.qf != nullptr) ? (P.rows_period * Ke + 15) / 16 * 16 : 0;
     uint64_t *bar = reinterpret_cast<uint64_t *>(etab + tab_bytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
@@ -143,79 +146,158 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) df_r[j] = 0.f;
 
+    // ---- per-thread constants of the dX staging (the same (row, chunk) pairs in every tile) -------------------------------
+    // The staging floats are laid over exactly those 128-byte blocks of the xq^T buffers that the next tile's conversion
+    // rewrites (row groups x the first Kp/8 column groups of both terms), so the zero padding and the ones row are never
+    // disturbed.  A 16-byte chunk index is XOR-swizzled with the row to spread the banks.
+    const int C = Kp >> 2;                  // 16-byte chunks per row
+    const int swm = ((C & -C) - 1) & 7;     // XOR mask that stays inside the row
+    auto st_off = [&](int rr, int c4s) -> int {  // byte offset inside X of the staged chunk (row, swizzled chunk)
+        const int L = rr * Kp + (c4s << 2);
+        const int b = L >> 5, within = L & 31;
+        const int t = b / (16 * CGk), rem = b - t * (16 * CGk);
+        const int rg = rem / CGk, kg = rem - rg * CGk;
+        return t * kQbXTermBytes + (rg * 16 + kg) * 128 + within * 4;
+    };
+    int st_w[4];                            // where this thread parks its up to 4 chunks of dXq (row qlane + lane)
+#pragma unroll
+    for (int ci = 0; ci < 2; ++ci)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c4 = (cpart + 4 * ci) * 2 + h, r = qlane + lane;
+            st_w[ci * 2 + h] = (cpart + 4 * ci < nchunk) ? st_off(r, c4 ^ (r & swm)) : -1;
+        }
+    const int cv = K >> 2;                  // valid chunks per row of dX (vector path)
+    int st_r[4], gl_r[4];                   // copy-out: staged chunk -> float4 index inside the tile's dX block
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int g = tid + kQbThreads * i;
+        if (vec_k && g < kQbTileM * cv) {
+            const int rr = g / cv, c4 = g - rr * cv;
+            st_r[i] = st_off(rr, c4 ^ (rr & swm));
+            gl_r[i] = rr * cv + c4;         // rows are contiguous in dX: chunk index relative to the tile start
+        } else {
+            st_r[i] = -1;
+            gl_r[i] = 0;
+        }
+    }
+
+    // ---- slab ownership (the same in every tile) and the register prefetch ----------------------------------------------
+    // G: unit u of a thread is combo c = u * 16 + warp -> row group mg = c / CG4g, column groups (c % CG4g) * 4 + q4;
+    // x: likewise with CG4k.  The raw values of the first two G units and of both x units of the NEXT tile are fetched
+    // into registers right after the MMAs of the current tile are issued, so their latency hides behind the wait and
+    // the epilogue.
+    const int CG4g = (CGn + 3) >> 2, combos_g = 16 * CG4g;  // <= 64
+    const int CG4k = (CGk + 3) >> 2, combos_k = 16 * CG4k;  // <= 32
+    float gv[2][8], yv[2][8], xv[2][8];
+    auto load_g = [&](int u, int slot, int64_t t_row0) {
+        const int c = u * 16 + warp;
+        const int mg = c / CG4g, kg = (c - mg * CG4g) * 4 + q4;
+        const bool act = c < combos_g && kg < CGn;
+        const int64_t row = t_row0 + mg * 8 + r8;
+        const int n0 = kg * 8;
+        if (act && row < P.M && vec_n && n0 + 8 <= N) {
+            const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0));
+            const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0 + 4));
+            gv[slot][0] = a0.x; gv[slot][1] = a0.y; gv[slot][2] = a0.z; gv[slot][3] = a0.w;
+            gv[slot][4] = a1.x; gv[slot][5] = a1.y; gv[slot][6] = a1.z; gv[slot][7] = a1.w;
+            if (P.relu) {
+                const float4 y0 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0));
+                const float4 y1 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0 + 4));
+                yv[slot][0] = y0.x; yv[slot][1] = y0.y; yv[slot][2] = y0.z; yv[slot][3] = y0.w;
+                yv[slot][4] = y1.x; yv[slot][5] = y1.y; yv[slot][6] = y1.z; yv[slot][7] = y1.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool in = act && row < P.M && n0 + j < N;
+                gv[slot][j] = in ? __ldcs(P.gy + row * N + n0 + j) : 0.f;
+                yv[slot][j] = (in && P.relu) ? __ldcs(P.y + row * N + n0 + j) : 1.f;
+            }
+        }
+    };
+    auto store_g = [&](int u, int slot) {
+        const int c = u * 16 + warp;
+        const int mg = c / CG4g, kg = (c - mg * CG4g) * 4 + q4;
+        if (!(c < combos_g && kg < CGn)) return;
+        if (P.relu) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gv[slot][j] = yv[slot][j] > 0.f ? gv[slot][j] : 0.f;
+        }
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) split2_pair(gv[slot][j], gv[slot][j + 1], hi[j >> 1], lo[j >> 1]);
+        const int off = (mg * CGn + kg) * 128 + r8 * 16;
+        *reinterpret_cast<uint4 *>(G + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4 *>(G + g_term_bytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    };
+    auto load_x = [&](int u, int64_t t_row0) {
+        const int c = u * 16 + warp;
+        const int mg = c / CG4k, kg = (c - mg * CG4k) * 4 + q4;
+        const bool act = c < combos_k && kg < CGk;
+        const int64_t row = t_row0 + mg * 8 + r8;
+        const int k0 = kg * 8;
+        if (act && row < P.M && vec_k && k0 + 8 <= K) {
+            const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0));
+            const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0 + 4));
+            xv[u][0] = a0.x; xv[u][1] = a0.y; xv[u][2] = a0.z; xv[u][3] = a0.w;
+            xv[u][4] = a1.x; xv[u][5] = a1.y; xv[u][6] = a1.z; xv[u][7] = a1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xv[u][j] = (act && row < P.M && k0 + j < K) ? __ldcs(P.x + row * K + k0 + j) : 0.f;
+        }
+    };
+    if ((int64_t)blockIdx.x < P.num_tiles) {
+        load_g(0, 0, (int64_t)blockIdx.x * kQbTileM);
+        load_g(1, 1, (int64_t)blockIdx.x * kQbTileM);
+        load_x(0, (int64_t)blockIdx.x * kQbTileM);
+        load_x(1, (int64_t)blockIdx.x * kQbTileM);
+    }
+
     for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
         const int64_t row0 = tile * kQbTileM;
         // ---- G = dY (* relu mask), two bf16 terms, core (row/8, n/8) ------------------------------------------------
-        {
-            const int CG4 = (CGn + 3) >> 2;
-            for (int c = warp; c < 16 * CG4; c += kQbThreads / 32) {
-                const int mg = c / CG4, kg = (c - mg * CG4) * 4 + q4;
-                if (kg >= CGn) continue;
-                const int64_t row = row0 + mg * 8 + r8;
-                const int n0 = kg * 8;
-                float v[8];
-                if (row < P.M && vec_n && n0 + 8 <= N) {
-                    const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0));
-                    const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0 + 4));
-                    v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
-                    if (P.relu) {
-                        const float4 y0 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0));
-                        const float4 y1 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0 + 4));
-                        v[0] = y0.x > 0.f ? v[0] : 0.f; v[1] = y0.y > 0.f ? v[1] : 0.f; v[2] = y0.z > 0.f ? v[2] : 0.f;
-                        v[3] = y0.w > 0.f ? v[3] : 0.f; v[4] = y1.x > 0.f ? v[4] : 0.f; v[5] = y1.y > 0.f ? v[5] : 0.f;
-                        v[6] = y1.z > 0.f ? v[6] : 0.f; v[7] = y1.w > 0.f ? v[7] : 0.f;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const bool in = row < P.M && n0 + j < N;
-                        float t = in ? __ldcs(P.gy + row * N + n0 + j) : 0.f;
-                        if (in && P.relu && !(__ldcs(P.y + row * N + n0 + j) > 0.f)) t = 0.f;
-                        v[j] = t;
-                    }
-                }
-                uint32_t hi[4], lo[4];
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) split2_pair(v[j], v[j + 1], hi[j >> 1], lo[j >> 1]);
-                const int off = (mg * CGn + kg) * 128 + r8 * 16;
-                *reinterpret_cast<uint4 *>(G + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4 *>(G + g_term_bytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            }
+        store_g(0, 0);
+        store_g(1, 1);
+        if (combos_g > 32) {  // wide outputs (N > 64): the remaining units are fetched here, not prefetched
+            load_g(2, 0, row0);
+            load_g(3, 1, row0);
+            store_g(2, 0);
+            store_g(3, 1);
         }
         // ---- xq = round(x), two bf16 terms, transposed operand: core (row/8, k/8) in a 16-group-wide buffer ----------
-        {
-            const int groups = CGk;
-            const int CG4 = (groups + 3) >> 2;
-            for (int c = warp; c < 16 * CG4; c += kQbThreads / 32) {
-                const int mg = c / CG4, kg = (c - mg * CG4) * 4 + q4;
-                if (kg >= groups) continue;
-                const int64_t row = row0 + mg * 8 + r8;
-                const int k0 = kg * 8;
-                float v[8];
-                if (row < P.M && vec_k && k0 + 8 <= K) {
-                    const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0));
-                    const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0 + 4));
-                    v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
-                } else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = (row < P.M && k0 + j < K) ? __ldcs(P.x + row * K + k0 + j) : 0.f;
-                }
-                if (P.qf != nullptr) {
-                    const uint32_t pr = (uint32_t)(mg * 8 + r8) % rp;
-                    const uint2 eb = *reinterpret_cast<const uint2 *>(etab + pr * Ke + k0);
+        for (int u = 0; u < 2; ++u) {
+            const int c = u * 16 + warp;
+            const int mg = c / CG4k, kg = (c - mg * CG4k) * 4 + q4;
+            if (!(c < combos_k && kg < CGk)) continue;
+            const int k0 = kg * 8, rl = mg * 8 + r8;
+            if (P.qf != nullptr) {
+                const uint32_t pr = (uint32_t)rl % rp;
+                const uint2 eb = *reinterpret_cast<const uint2 *>(etab + pr * Ke + k0);
+                float d[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = round_e<CONV>(v[j], ((j < 4 ? eb.x : eb.y) >> ((j & 3) * 8)) & 0xffu, rbias);
+                for (int j = 0; j < 8; ++j) {
+                    const float xq = round_e<CONV>(xv[u][j], ((j < 4 ? eb.x : eb.y) >> ((j & 3) * 8)) & 0xffu, rbias);
+                    d[j] = __fmul_rn(__fsub_rn(xq, xv[u][j]), -kLn2);
+                    xv[u][j] = xq;
                 }
+                if (stash_bytes) {
+                    *reinterpret_cast<float4 *>(dstash + rl * Kd + k0) = make_float4(d[0], d[1], d[2], d[3]);
+                    *reinterpret_cast<float4 *>(dstash + rl * Kd + k0 + 4) = make_float4(d[4], d[5], d[6], d[7]);
+                }
+            }
+            if (k0 + 8 > K) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                    if (k0 + j >= K) v[j] = (k0 + j == K) ? 1.f : 0.f;  // the row of ones that accumulates dbq
-                uint32_t hi[4], lo[4];
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) split2_pair(v[j], v[j + 1], hi[j >> 1], lo[j >> 1]);
-                const int off = (mg * 16 + kg) * 128 + r8 * 16;
-                *reinterpret_cast<uint4 *>(X + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4 *>(X + kQbXTermBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    if (k0 + j >= K) xv[u][j] = (k0 + j == K) ? 1.f : 0.f;  // the row of ones that accumulates dbq
             }
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) split2_pair(xv[u][j], xv[u][j + 1], hi[j >> 1], lo[j >> 1]);
+            const int off = (mg * 16 + kg) * 128 + r8 * 16;
+            *reinterpret_cast<uint4 *>(X + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4 *>(X + kQbXTermBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
         tc::fence_smem_to_async();
         __syncthreads();
@@ -246,6 +328,15 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
             tc::commit(bar);
         }
         first_tile = false;
+        {   // next tile's raw operands start their trip from HBM now
+            const int64_t ntile = tile + gridDim.x;
+            if (ntile < P.num_tiles) {
+                load_g(0, 0, ntile * kQbTileM);
+                load_g(1, 1, ntile * kQbTileM);
+                load_x(0, ntile * kQbTileM);
+                load_x(1, ntile * kQbTileM);
+            }
+        }
         const bool waited = (warp == 0) ? tc::mbar_wait(bar, phase) : true;
         phase ^= 1u;
         ok = __syncthreads_and(waited ? 1 : 0) != 0;
@@ -257,78 +348,43 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
         tc::fence_after_sync();
         {
             const int r = qlane + lane;
-            const int64_t row = row0 + r;
             float v[16];
 #pragma unroll
             for (int ci = 0; ci < 2; ++ci) {
                 const int chunk = cpart + 4 * ci;  // warp-uniform
                 if (chunk < nchunk) tc::tmem_ld8v(acc1 + ((uint32_t)qlane << 16) + (uint32_t)(chunk * 8), v + ci * 8);
             }
-            if (P.want_df && P.qf != nullptr && row < P.M) {
-                const uint32_t pr = (uint32_t)r % rp;
+            if (stash_bytes) {
 #pragma unroll
                 for (int ci = 0; ci < 2; ++ci) {
                     const int kb = (cpart + 4 * ci) * 8;
-                    if (kb < K) {
-                        float xr[8];
-                        if (vec_k && kb + 8 <= K) {
-                            const float4 a0 = __ldg(reinterpret_cast<const float4 *>(P.x + row * K + kb));
-                            const float4 a1 = __ldg(reinterpret_cast<const float4 *>(P.x + row * K + kb + 4));
-                            xr[0] = a0.x; xr[1] = a0.y; xr[2] = a0.z; xr[3] = a0.w; xr[4] = a1.x; xr[5] = a1.y; xr[6] = a1.z; xr[7] = a1.w;
-                        } else {
+                    if (cpart + 4 * ci < nchunk) {
+                        const float4 d0 = *reinterpret_cast<const float4 *>(dstash + r * Kd + kb);
+                        const float4 d1 = *reinterpret_cast<const float4 *>(dstash + r * Kd + kb + 4);
+                        const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) xr[j] = (kb + j < K) ? __ldg(P.x + row * K + kb + j) : 0.f;
-                        }
-                        const uint2 eb = *reinterpret_cast<const uint2 *>(etab + pr * Ke + kb);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            if (kb + j < K) {
-                                const float xq = round_e<CONV>(xr[j], ((j < 4 ? eb.x : eb.y) >> ((j & 3) * 8)) & 0xffu, rbias);
-                                const float delta = __fsub_rn(xq, xr[j]);
-                                df_r[ci * 8 + j] = __fadd_rn(df_r[ci * 8 + j], __fmul_rn(__fmul_rn(delta, -kLn2), v[ci * 8 + j]));
-                            }
-                        }
+                        for (int j = 0; j < 8; ++j) df_r[ci * 8 + j] = __fadd_rn(df_r[ci * 8 + j], __fmul_rn(d[j], v[ci * 8 + j]));
                     }
                 }
             }
             if (P.dx != nullptr) {
-                // Stage the [128 x Kp] block, then write full lines.  The staging floats are laid over exactly those
-                // 128-byte blocks of the xq^T buffers that the next tile's conversion rewrites (row groups x the first
-                // Kp/8 column groups of both terms), so the zero padding and the ones row are never disturbed.
-                const int C = Kp >> 2;                                   // 16-byte chunks per row
-                const int swm = ((C & -C) - 1) & 7;                      // XOR mask that stays inside the row
-                auto st_addr = [&](int rr, int c4s, int w) -> float * {  // float address of (row, swizzled chunk, word)
-                    const int L = rr * Kp + (c4s << 2) + w;
-                    const int b = L >> 5, within = L & 31;
-                    const int t = b / (16 * CGk), rem = b - t * (16 * CGk);
-                    const int rg = rem / CGk, kg = rem - rg * CGk;
-                    return reinterpret_cast<float *>(X + t * kQbXTermBytes + (rg * 16 + kg) * 128) + within;
-                };
 #pragma unroll
-                for (int ci = 0; ci < 2; ++ci) {
-                    const int chunk = cpart + 4 * ci;
-                    if (chunk < nchunk) {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int c4 = chunk * 2 + h;
-                            *reinterpret_cast<float4 *>(st_addr(r, c4 ^ (r & swm), 0)) =
-                                make_float4(v[ci * 8 + 4 * h], v[ci * 8 + 4 * h + 1], v[ci * 8 + 4 * h + 2], v[ci * 8 + 4 * h + 3]);
-                        }
-                    }
-                }
+                for (int q = 0; q < 4; ++q)
+                    if (st_w[q] >= 0)
+                        *reinterpret_cast<float4 *>(X + st_w[q]) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
                 __syncthreads();
                 const int64_t rows_here = (P.M - row0) < kQbTileM ? (P.M - row0) : kQbTileM;
                 if (vec_k) {
-                    const int cv = K >> 2;
-                    for (int g = tid; g < (int)rows_here * cv; g += kQbThreads) {
-                        const int rr = g / cv, c4 = g - rr * cv;
-                        const float4 o = *reinterpret_cast<const float4 *>(st_addr(rr, c4 ^ (rr & swm), 0));
-                        __stcs(reinterpret_cast<float4 *>(P.dx + (row0 + rr) * K) + c4, o);
-                    }
+                    float4 *dst = reinterpret_cast<float4 *>(P.dx + row0 * K);
+                    const int limit = (int)rows_here * cv;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (st_r[i] >= 0 && gl_r[i] < limit) __stcs(dst + gl_r[i], *reinterpret_cast<const float4 *>(X + st_r[i]));
                 } else {
                     for (int g = tid; g < (int)rows_here * K; g += kQbThreads) {
                         const int rr = g / K, k = g - rr * K;
-                        __stcs(P.dx + (row0 + rr) * K + k, *st_addr(rr, (k >> 2) ^ (rr & swm), k & 3));
+                        __stcs(P.dx + (row0 + rr) * K + k,
+                               *reinterpret_cast<const float *>(X + st_off(rr, (k >> 2) ^ (rr & swm)) + (k & 3) * 4));
                     }
                 }
             }
@@ -403,7 +459,8 @@ static int qb_geom(int64_t M, int K, int N, int rows_period, QbGeom &g) {
     g.Np = (N + 15) / 16 * 16;
     g.Kt = (K + 7) / 8 * 8;
     const size_t tab = ((size_t)rows_period * (g.Kt + 8) + 15) / 16 * 16;
-    g.smem = 2 * (size_t)kQbTileM * g.Np * 2 + 2 * (size_t)kQbXTermBytes + 3 * (size_t)g.Kp * g.Np * 2 + tab + 64;
+    g.smem = 2 * (size_t)kQbTileM * g.Np * 2 + 2 * (size_t)kQbXTermBytes + 3 * (size_t)g.Kp * g.Np * 2 +
+             (size_t)kQbTileM * (g.Kp + 4) * 4 + tab + 64;
     if (g.smem > 226 * 1024) return HGQ_ERR_SIZE;
     g.tiles = (M + kQbTileM - 1) / kQbTileM;
     int64_t grid = kNumSMs;  // 512 threads, > 113 KB shared memory: one CTA per SM

@@ -284,17 +284,21 @@ __global__ void __launch_bounds__(kThreads) k_bwd_bcast(const float *__restrict_
     }
 }
 
-// Stage 2: out[c] = sum over row blocks of ws[rb * P + c], in double, in a fixed order.
+// Stage 2: out[c] = sum over row blocks of ws[rb * P + c], in double, in a fixed order: one warp per column, lane l adds
+// the row blocks l, l + 32, ... in sequence, then the 32 lane sums are combined by a fixed shuffle tree.
 __global__ void __launch_bounds__(kThreads) k_colsum_stage2(const float *__restrict__ ws, float *__restrict__ di,
                                                             float *__restrict__ df, int64_t P, int rowBlocks) {
-    const int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int64_t c = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     if (c >= P) return;
     const float *src = blockIdx.y == 0 ? ws : ws + (int64_t)rowBlocks * P;
     float *dst = blockIdx.y == 0 ? di : df;
     if (dst == nullptr) return;
     double acc = 0.0;
-    for (int rb = 0; rb < rowBlocks; ++rb) acc += (double)src[(int64_t)rb * P + c];
-    dst[c] = (float)acc;
+    for (int rb = lane; rb < rowBlocks; rb += 32) acc += (double)src[(int64_t)rb * P + c];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) dst[c] = (float)acc;
 }
 
 // ---- dispatch --------------------------------------------------------------------------------
@@ -380,7 +384,7 @@ static int launch_bwd(const float *g, const float *x, const uint8_t *k, const fl
         cudaError_t e = cudaMemsetAsync(di, 0, sizeof(float) * period, st);
         if (e != cudaSuccess) return (int)e;
     }
-    dim3 g2((unsigned)((period + kThreads - 1) / kThreads), 2);
+    dim3 g2((unsigned)((period + kThreads / 32 - 1) / (kThreads / 32)), 2);
     k_colsum_stage2<<<g2, kThreads, 0, st>>>((const float *)ws, want_di ? di : nullptr, df, period, ge.rowBlocks);
     return check_launch();
 }
