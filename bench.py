@@ -316,6 +316,32 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# reduced batches for the CPU leg of the QAT step (the oracle's eager torch-CPU formulation), sized for a few seconds each
+QAT_CPU_BATCH = {'jet_tagger_mlp': 16384, 'particle_tagger': 512, 'small_cnn': 128, 'transformer_block': 64}
+
+
+def cpu_qat_step(name, builder_model, make_x, classes):
+    """samples/s of one QAT step (forward, backward, Adam, constraints) of the oracle twin on the host cores."""
+    import torch.nn.functional as F
+
+    from oracle import train as OT
+
+    batch = QAT_CPU_BATCH[name]
+    torch.set_num_threads(os.cpu_count() or 1)
+    twin, pairs = OT.mirror_model(builder_model)
+    opt = OT.OracleAdam(pairs)
+    x = torch.from_numpy(make_x(np.random.default_rng(1), batch))
+    y = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch))
+    OT.train_step(twin, opt, x, y, F.cross_entropy)  # warm-up
+    t0 = time.perf_counter()
+    n = 0
+    while n < 3 or (time.perf_counter() - t0 < 2.0 and n < 50):
+        OT.train_step(twin, opt, x, y, F.cross_entropy)
+        n += 1
+    dt = (time.perf_counter() - t0) / n
+    return {'samples_per_s': round(batch / dt, 1), 'batch': batch, 'steps': n, 'cores': os.cpu_count() or 1, 'kind': 'port'}
+
+
 QAT_CONFIGS = {
     # name: (builder, global batch, input maker, classes, modelled HBM bytes per sample for one QAT step)
     'jet_tagger_mlp': ('jet_tagger_mlp', 16384, lambda rng, b: rng.standard_normal((b, 16), dtype=np.float32), 5, 3324),
@@ -370,6 +396,9 @@ def run_qat(args, dev, world, rank, peak):
     for name, (builder, batch, make_x, classes, bytes_per_sample) in QAT_CONFIGS.items():
         try:
             model = workloads.build(getattr(workloads, builder)(), device=dev)
+            cpu = None
+            if rank == 0 and world == 1 and not args.no_cpu:
+                cpu = cpu_qat_step(name, model, make_x, classes)  # twin of the freshly built model, before any step
             tr = Trainer(model, F.cross_entropy, dp=dp)
             sl = shard_batch(batch, rank, world)
             hx = torch.from_numpy(make_x(np.random.default_rng(1), batch)[sl]).pin_memory()
@@ -405,6 +434,7 @@ def run_qat(args, dev, world, rank, peak):
                 'h2d_bytes_per_step': int(hx.numel() * 4 + hy.numel() * 8), 'd2h_bytes_per_step': 4,
                 'hbm_roofline_frac': round(sps * bytes_per_sample / world / (peak * 1e9), 4),
                 'modelled_bytes_per_sample': bytes_per_sample, 'loss': round(loss_host, 5), 'cuda_graph': True,
+                'cpu_baseline': cpu,
             })
             del model, tr, x, y, hx, hy
             torch.cuda.empty_cache()

@@ -63,6 +63,17 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
          c_int, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    'hgq_qsoftmax_fwd': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int64, c_int,
+         c_int, c_void_p],
+    ),
+    'hgq_qsoftmax_bwd_workspace': (c_size_t, [c_int64, c_int, c_int]),
+    'hgq_qsoftmax_bwd': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
+         c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p],
+    ),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

@@ -135,4 +135,44 @@ __device__ __forceinline__ void quantize_grad(float g, float x, const Params &p,
     }
 }
 
+// ---- runtime-mode variants (mode is uniform across a launch; used where a kernel applies several quantizers) ----------
+__device__ __forceinline__ float quantize_rt(float v, float kf, float i, float f, int rm, int om, bool zero, float &rounded) {
+    Params p = make_params(kf, i, f);
+    if (zero && ((kf != 0.f ? 1 : 0) + p.ii + p.fi <= 0)) {
+        rounded = 0.f;
+        return 0.f;
+    }
+    float xq;
+    switch (rm) {
+        case RM_TRN: xq = round_to_f<RM_TRN>(v, p); break;
+        case RM_RND: xq = round_to_f<RM_RND>(v, p); break;
+        default: xq = round_to_f<RM_RND_CONV>(v, p); break;
+    }
+    rounded = xq;
+    switch (om) {
+        case OM_WRAP: return overflow<OM_WRAP, false>(xq, p);
+        case OM_SAT: return overflow<OM_SAT, false>(xq, p);
+        case OM_SAT_SYM: return overflow<OM_SAT_SYM, false>(xq, p);
+        default: return xq;
+    }
+}
+
+// surrogate gradients of the training-mode quantizer with runtime modes (om: NONE / SAT / SAT_SYM; WRAP counts as NONE)
+__device__ __forceinline__ void quantize_grad_rt(float g, float x, float kf, float i, float f, int rm, int om, float &dx,
+                                                 float &di, float &df) {
+    const Params p = make_params(kf, i, f);
+#define HGQ_QG(RMV)                                                                                      \
+    switch (om) {                                                                                        \
+        case OM_SAT: quantize_grad<RMV, OM_SAT>(g, x, p, dx, di, df); break;                             \
+        case OM_SAT_SYM: quantize_grad<RMV, OM_SAT_SYM>(g, x, p, dx, di, df); break;                     \
+        default: quantize_grad<RMV, OM_NONE>(g, x, p, dx, di, df); break;                                \
+    }
+    switch (rm) {
+        case RM_TRN: HGQ_QG(RM_TRN) break;
+        case RM_RND: HGQ_QG(RM_RND) break;
+        default: HGQ_QG(RM_RND_CONV) break;
+    }
+#undef HGQ_QG
+}
+
 }  // namespace hgq

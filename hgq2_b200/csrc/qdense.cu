@@ -59,27 +59,6 @@ struct QdParams {
     int64_t num_tiles;
 };
 
-__device__ __forceinline__ float quantize_rt(float v, float kf, float i, float f, int rm, int om, bool zero, float &rounded) {
-    Params p = make_params(kf, i, f);
-    if (zero && ((kf != 0.f ? 1 : 0) + p.ii + p.fi <= 0)) {
-        rounded = 0.f;
-        return 0.f;
-    }
-    float xq;
-    switch (rm) {
-        case RM_TRN: xq = round_to_f<RM_TRN>(v, p); break;
-        case RM_RND: xq = round_to_f<RM_RND>(v, p); break;
-        default: xq = round_to_f<RM_RND_CONV>(v, p); break;
-    }
-    rounded = xq;
-    switch (om) {
-        case OM_WRAP: return overflow<OM_WRAP, false>(xq, p);
-        case OM_SAT: return overflow<OM_SAT, false>(xq, p);
-        case OM_SAT_SYM: return overflow<OM_SAT_SYM, false>(xq, p);
-        default: return xq;
-    }
-}
-
 // Abs-max bookkeeping variants (the statistic is max over rows of |round(x)| per quantizer-table entry):
 //   AMAX_NONE   not requested
 //   AMAX_REGS   rows_period == 1, one K slab: a thread's 8 columns never change, maxima live in registers

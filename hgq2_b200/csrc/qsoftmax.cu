@@ -1,0 +1,389 @@
+// K4: bit-accurate quantised softmax, forward and backward, one pass each.
+//
+// Stands in for QSoftmax.call (src/hgq/layers/softmax.py:114-132) in its stable form without mask, together with the
+// four table quantizers of its two QUnaryFunctionLUT sub-layers (src/hgq/layers/activation.py:58-61) and the layer's
+// own output quantizer (src/hgq/layers/core/base.py:105-110), in training mode:
+//     d = max_j(s) - s;  a = Q1(d);  e = exp(-a * scaler);  b = Q2(e);  S = sum_j b;  t = Q3(S);
+//     v = 1 / (t + eps);  u = Q4(v);  z = b * u;  y = Q5(z)
+// Q1..Q4 have one (k, i, f) each (heterogeneous_axis = ()), Q5 has a [rows_period, L] table (the bitwidth tensor of the
+// scores with the batch axis set to 1).  The reference runs this as ~25 eager element-wise passes over the score
+// tensor per direction; here a warp owns a row (L = 32 / 64 / 128 scores, 1 / 2 / 4 per lane), keeps it in registers,
+// and the score tensor is read once (forward) or twice (backward: s and dL/dy) and written once.
+// HBM-bound: 8 B per score forward, 12 B backward.
+//
+// Side outputs of the forward: the abs-max statistics the WRAP quantizers track (a scalar for Q3, a table for Q5).
+// The backward recomputes the chain from s and accumulates the surrogate gradients of all five quantizers: scalars are
+// summed per thread, then per CTA in a fixed order, then over CTAs by a second kernel; the Q5 table gradient is owned
+// by the warp lanes of the CTA that handles that table row for a range of batches.
+#include <cuda_runtime.h>
+
+#include "hgq_common.cuh"
+#include "hgq_math.cuh"
+
+namespace hgq {
+
+struct SQuant {            // one stateless quantizer with scalar parameters (device pointers to single elements)
+    const uint8_t *k;
+    const float *i, *f;
+    int rm, om;            // om: OM_NONE (rounding only), OM_SAT, OM_SAT_SYM
+};
+
+struct SmParams {
+    const float *s;        // [R, L] scores, R = batches * rows_period
+    const float *gy;       // backward: dL/dy
+    float *y;              // forward output / backward ds
+    SQuant q1, q2, q3, q4;
+    const uint8_t *k5;     // Q5 tables [rows_period, L]
+    const float *i5, *f5;
+    int rm5, om5;
+    float scaler, eps;
+    unsigned *amax3;       // forward: scalar abs-max of round(S) (as bits), or nullptr
+    unsigned *amax5;       // forward: [rows_period, L] abs-max of round(z), or nullptr
+    float *part;           // backward: per-CTA partials: 8 scalars (di1, df1, di2, df2, di3, df3, di4, df4), then per
+                           // (split, table row) L floats of df5 and L floats of di5
+    int64_t batches;
+    int rows_period, L, splits;
+};
+
+constexpr int kSmWarps = 8;
+constexpr float kNegInf = -3.402823466e38f;
+
+struct QS {  // scalar quantizer parameters in registers
+    float kf, i, f;
+};
+
+__device__ __forceinline__ QS load_q(const SQuant &q) {
+    QS r;
+    r.f = __ldg(q.f);
+    r.kf = (q.om == OM_NONE) ? 0.f : (float)__ldg(q.k);
+    r.i = (q.om == OM_NONE) ? 0.f : __ldg(q.i);
+    return r;
+}
+
+template <int VE>
+__device__ __forceinline__ void load_row(const float *p, int lane, float (&v)[VE]) {
+    if (VE == 4) {
+        const float4 t = __ldcs(reinterpret_cast<const float4 *>(p) + lane);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else if (VE == 2) {
+        const float2 t = __ldcs(reinterpret_cast<const float2 *>(p) + lane);
+        v[0] = t.x; v[1] = t.y;
+    } else {
+        v[0] = __ldcs(p + lane);
+    }
+}
+
+template <int VE>
+__device__ __forceinline__ void store_row(float *p, int lane, const float (&v)[VE]) {
+    if (VE == 4) __stcs(reinterpret_cast<float4 *>(p) + lane, make_float4(v[0], v[1], v[2], v[3]));
+    else if (VE == 2) __stcs(reinterpret_cast<float2 *>(p) + lane, make_float2(v[0], v[1]));
+    else __stcs(p + lane, v[0]);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {  // fixed butterfly: every lane ends with the same value
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Forward chain of one row.  Fills b[] (quantised exponentials), returns u and the intermediate scalars.
+template <int VE>
+__device__ __forceinline__ void chain_fwd(const SmParams &P, const QS &q1, const QS &q2, const QS &q3, const QS &q4,
+                                          const float (&s)[VE], float (&a)[VE], float (&e)[VE], float (&b)[VE], float &m,
+                                          float &S, float &t, float &t_rounded, float &v, float &u) {
+    float mx = kNegInf;
+#pragma unroll
+    for (int j = 0; j < VE; ++j) mx = fmaxf(mx, s[j]);
+    m = warp_max(mx);
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < VE; ++j) {
+        float r;
+        a[j] = quantize_rt(__fsub_rn(m, s[j]), q1.kf, q1.i, q1.f, P.q1.rm, P.q1.om, false, r);
+        e[j] = expf(__fmul_rn(-a[j], P.scaler));
+        b[j] = quantize_rt(e[j], q2.kf, q2.i, q2.f, P.q2.rm, P.q2.om, false, r);
+        part = __fadd_rn(part, b[j]);
+    }
+    S = warp_sum(part);
+    t = quantize_rt(S, q3.kf, q3.i, q3.f, P.q3.rm, P.q3.om, false, t_rounded);
+    v = __fdiv_rn(1.f, __fadd_rn(t, P.eps));
+    float r;
+    u = quantize_rt(v, q4.kf, q4.i, q4.f, P.q4.rm, P.q4.om, false, r);
+}
+
+// grid = (rows_period, splits); CTA (p, sp) handles table row p for the batches sp, sp + splits, ... (warp w takes every
+// 8th of those), so the Q5 statistics of row p are owned by this CTA's lanes.
+template <int VE>
+__global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p = blockIdx.x, sp = blockIdx.y, L = P.L;
+    const QS q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
+    float k5[VE], i5[VE], f5[VE];
+#pragma unroll
+    for (int j = 0; j < VE; ++j) {
+        const int c = p * L + lane * VE + j;
+        f5[j] = __ldg(P.f5 + c);
+        k5[j] = (P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c);
+        i5[j] = (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c);
+    }
+    float am5[VE], am3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < VE; ++j) am5[j] = 0.f;
+    for (int64_t bt = (int64_t)sp + (int64_t)warp * P.splits; bt < P.batches; bt += (int64_t)P.splits * kSmWarps) {
+        const int64_t row = bt * P.rows_period + p;
+        float s[VE], a[VE], e[VE], b[VE], y[VE];
+        load_row<VE>(P.s + row * L, lane, s);
+        float m, S, t, tr, v, u;
+        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u);
+        am3 = fmaxf(am3, fabsf(tr));
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+            float r;
+            y[j] = quantize_rt(__fmul_rn(b[j], u), k5[j], i5[j], f5[j], P.rm5, P.om5, false, r);
+            am5[j] = fmaxf(am5[j], fabsf(r));
+        }
+        store_row<VE>(P.y + row * L, lane, y);
+    }
+    if (P.amax5 != nullptr) {
+#pragma unroll
+        for (int j = 0; j < VE; ++j) atomicMax(P.amax5 + p * L + lane * VE + j, __float_as_uint(am5[j]));
+    }
+    if (P.amax3 != nullptr && lane == 0) atomicMax(P.amax3, __float_as_uint(am3));
+}
+
+template <int VE>
+__global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P) {
+    __shared__ float red[kSmWarps][8];
+    __shared__ float red5[kSmWarps][2][128];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p = blockIdx.x, sp = blockIdx.y, L = P.L;
+    const QS q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
+    float k5[VE], i5[VE], f5[VE];
+#pragma unroll
+    for (int j = 0; j < VE; ++j) {
+        const int c = p * L + lane * VE + j;
+        f5[j] = __ldg(P.f5 + c);
+        k5[j] = (P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c);
+        i5[j] = (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c);
+    }
+    float acc[8];  // di1, df1, di2, df2, di3, df3, di4, df4 (per thread; the per-row scalars are added by lane 0 only)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    float adf5[VE], adi5[VE];
+#pragma unroll
+    for (int j = 0; j < VE; ++j) adf5[j] = adi5[j] = 0.f;
+
+    for (int64_t bt = (int64_t)sp + (int64_t)warp * P.splits; bt < P.batches; bt += (int64_t)P.splits * kSmWarps) {
+        const int64_t row = bt * P.rows_period + p;
+        float s[VE], g[VE], a[VE], e[VE], b[VE];
+        load_row<VE>(P.s + row * L, lane, s);
+        load_row<VE>(P.gy + row * L, lane, g);
+        float m, S, t, tr, v, u;
+        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u);
+        // y = Q5(b u): gradient to z, Q5's own parameters
+        float gb[VE], gu_part = 0.f;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+            float gz, di, df;
+            quantize_grad_rt(g[j], __fmul_rn(b[j], u), k5[j], i5[j], f5[j], P.rm5, P.om5, gz, di, df);
+            adf5[j] = __fadd_rn(adf5[j], df);
+            adi5[j] = __fadd_rn(adi5[j], di);
+            gb[j] = __fmul_rn(gz, u);
+            gu_part = __fadd_rn(gu_part, __fmul_rn(gz, b[j]));
+        }
+        const float gu = warp_sum(gu_part);
+        // u = Q4(v), v = 1 / (t + eps), t = Q3(S): row scalars, identical on every lane
+        float gv, di4, df4, gS, di3, df3;
+        quantize_grad_rt(gu, v, q4.kf, q4.i, q4.f, P.q4.rm, P.q4.om, gv, di4, df4);
+        const float gt = __fmul_rn(-gv, __fmul_rn(v, v));
+        quantize_grad_rt(gt, S, q3.kf, q3.i, q3.f, P.q3.rm, P.q3.om, gS, di3, df3);
+        if (lane == 0) {
+            acc[4] = __fadd_rn(acc[4], di3); acc[5] = __fadd_rn(acc[5], df3);
+            acc[6] = __fadd_rn(acc[6], di4); acc[7] = __fadd_rn(acc[7], df4);
+        }
+        // b = Q2(e), e = exp(-a c), a = Q1(d), d = m - s
+        float gd[VE], gm_part = 0.f;
+        int ties_part = 0;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+            float ge, di2, df2, di1, df1;
+            quantize_grad_rt(__fadd_rn(gb[j], gS), e[j], q2.kf, q2.i, q2.f, P.q2.rm, P.q2.om, ge, di2, df2);
+            const float ga = __fmul_rn(ge, __fmul_rn(-P.scaler, e[j]));
+            quantize_grad_rt(ga, __fsub_rn(m, s[j]), q1.kf, q1.i, q1.f, P.q1.rm, P.q1.om, gd[j], di1, df1);
+            acc[0] = __fadd_rn(acc[0], di1); acc[1] = __fadd_rn(acc[1], df1);
+            acc[2] = __fadd_rn(acc[2], di2); acc[3] = __fadd_rn(acc[3], df2);
+            gm_part = __fadd_rn(gm_part, gd[j]);
+            ties_part += (s[j] == m) ? 1 : 0;
+        }
+        const float gm = warp_sum(gm_part);
+        int ties = ties_part;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ties += __shfl_xor_sync(0xffffffffu, ties, o);
+        const float share = __fdiv_rn(gm, (float)ties);  // the max spreads its gradient evenly over the tied maxima
+        float ds[VE];
+#pragma unroll
+        for (int j = 0; j < VE; ++j) ds[j] = __fadd_rn(-gd[j], (s[j] == m) ? share : 0.f);
+        store_row<VE>(P.y + row * L, lane, ds);
+    }
+    // ---- CTA partials, fixed order --------------------------------------------------------------------------------------
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float vsum = acc[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) vsum = __fadd_rn(vsum, __shfl_xor_sync(0xffffffffu, vsum, o));
+        if (lane == 0) red[warp][j] = vsum;
+    }
+#pragma unroll
+    for (int j = 0; j < VE; ++j) {
+        red5[warp][0][lane * VE + j] = adf5[j];
+        red5[warp][1][lane * VE + j] = adi5[j];
+    }
+    __syncthreads();
+    const int64_t cta = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
+    float *pc = P.part + cta * (8 + 2 * (int64_t)L);
+    if (threadIdx.x < 8) {
+        float a8 = 0.f;
+        for (int w = 0; w < kSmWarps; ++w) a8 = __fadd_rn(a8, red[w][threadIdx.x]);
+        pc[threadIdx.x] = a8;
+    }
+    for (int c = threadIdx.x; c < 2 * L; c += kSmWarps * 32) {
+        const int which = c / L, col = c - which * L;
+        float a5 = 0.f;
+        for (int w = 0; w < kSmWarps; ++w) a5 = __fadd_rn(a5, red5[w][which][col]);
+        pc[8 + c] = a5;
+    }
+}
+
+// tables: out[which][p * L + col] = sum over the splits of CTA (p, split); scalars: out8[j] = sum over all CTAs, one warp
+// per scalar (lanes stride over the CTAs, then a fixed shuffle tree), done by the last block
+__global__ void __launch_bounds__(kThreads) k_qsoftmax_stage2(const float *__restrict__ part, float *__restrict__ out8,
+                                                             float *__restrict__ df5, float *__restrict__ di5,
+                                                             int rows_period, int L, int splits) {
+    const int64_t stride = 8 + 2 * (int64_t)L;
+    const int64_t ncta = (int64_t)rows_period * splits;
+    if (blockIdx.x == gridDim.x - 1) {
+        const int j = threadIdx.x >> 5, lane = threadIdx.x & 31;  // kThreads = 256: warps 0..7 <-> the 8 scalars
+        double a = 0.0;
+        for (int64_t c = lane; c < ncta; c += 32) a += (double)part[c * stride + j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0) out8[j] = (float)a;
+        return;
+    }
+    const int64_t tbl = (int64_t)rows_period * L;
+    const int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (q < 2 * tbl) {
+        const int64_t which = q / tbl, idx = q - which * tbl;
+        const int64_t p = idx / L, col = idx - p * L;
+        double a = 0.0;
+        for (int sp = 0; sp < splits; ++sp) a += (double)part[((int64_t)sp * rows_period + p) * stride + 8 + which * L + col];
+        float *dst = which == 0 ? df5 : di5;
+        if (dst) dst[idx] = (float)a;
+    }
+}
+
+static int sm_splits(int64_t batches, int rows_period) {
+    int64_t s = ((int64_t)kNumSMs * 8 + rows_period - 1) / rows_period;
+    const int64_t maxs = (batches + kSmWarps - 1) / kSmWarps;
+    if (s > maxs) s = maxs;
+    if (s < 1) s = 1;
+    if (s > 65535) s = 65535;
+    return (int)s;
+}
+
+static int sm_check(const SmParams &p, int64_t R) {
+    if (R <= 0 || p.rows_period <= 0 || R % p.rows_period != 0) return HGQ_ERR_SIZE;
+    if (p.L != 32 && p.L != 64 && p.L != 128) return HGQ_ERR_SIZE;
+    if (!p.s || !p.y || !p.f5 || !p.q1.f || !p.q2.f || !p.q3.f || !p.q4.f) return HGQ_ERR_NULL;
+    const SQuant *qs[4] = {&p.q1, &p.q2, &p.q3, &p.q4};
+    for (const SQuant *q : qs) {
+        if (q->rm < 0 || q->rm > 2) return HGQ_ERR_MODE;
+        if (q->om != OM_NONE && q->om != OM_SAT && q->om != OM_SAT_SYM) return HGQ_ERR_MODE;
+        if (q->om != OM_NONE && (!q->k || !q->i)) return HGQ_ERR_NULL;
+    }
+    if (p.rm5 < 0 || p.rm5 > 2) return HGQ_ERR_MODE;
+    if (p.om5 != OM_NONE && p.om5 != OM_SAT && p.om5 != OM_SAT_SYM) return HGQ_ERR_MODE;
+    if (p.om5 != OM_NONE && (!p.k5 || !p.i5)) return HGQ_ERR_NULL;
+    if (!aligned(p.s, 16) || !aligned(p.y, 16) || (p.gy && !aligned(p.gy, 16))) return HGQ_ERR_ALIGN;
+    return HGQ_OK;
+}
+
+}  // namespace hgq
+
+using namespace hgq;
+
+// The C ABI passes the five quantizers as host arrays of five entries each: qk[5], qi[5], qf[5] hold device pointers
+// (entries 0..3 point at single elements, entry 4 at the [rows_period, L] tables), qrm[5], qom[5] the modes.
+static SmParams sm_make(const float *s, const float *gy, float *y, const uint8_t *const *qk, const float *const *qi,
+                        const float *const *qf, const int *qrm, const int *qom, float scaler, float eps, int64_t R, int L,
+                        int rows_period) {
+    SmParams p{};
+    p.s = s; p.gy = gy; p.y = y;
+    SQuant *qs[4] = {&p.q1, &p.q2, &p.q3, &p.q4};
+    for (int j = 0; j < 4; ++j) {
+        qs[j]->k = qk[j]; qs[j]->i = qi[j]; qs[j]->f = qf[j]; qs[j]->rm = qrm[j]; qs[j]->om = qom[j];
+    }
+    p.k5 = qk[4]; p.i5 = qi[4]; p.f5 = qf[4]; p.rm5 = qrm[4]; p.om5 = qom[4];
+    p.scaler = scaler; p.eps = eps;
+    p.rows_period = rows_period; p.L = L;
+    p.batches = rows_period > 0 ? R / rows_period : 0;
+    p.splits = sm_splits(p.batches, rows_period > 0 ? rows_period : 1);
+    return p;
+}
+
+extern "C" int hgq_qsoftmax_fwd(const float *s, float *y, const uint8_t *const *qk, const float *const *qi,
+                                const float *const *qf, const int *qrm, const int *qom, float scaler, float eps,
+                                float *absmax_inv_in, float *absmax_out, int64_t R, int L, int rows_period, void *stream) {
+    if (!qk || !qi || !qf || !qrm || !qom) return HGQ_ERR_NULL;
+    SmParams p = sm_make(s, nullptr, y, qk, qi, qf, qrm, qom, scaler, eps, R, L, rows_period);
+    if (int e = sm_check(p, R)) return e;
+    cudaStream_t st = (cudaStream_t)stream;
+    p.amax3 = (unsigned *)absmax_inv_in;
+    p.amax5 = (unsigned *)absmax_out;
+    if (absmax_inv_in) {
+        cudaError_t e = cudaMemsetAsync(absmax_inv_in, 0, sizeof(float), st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (absmax_out) {
+        cudaError_t e = cudaMemsetAsync(absmax_out, 0, sizeof(float) * (size_t)rows_period * L, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid((unsigned)rows_period, (unsigned)p.splits);
+    if (L == 128) k_qsoftmax_fwd<4><<<grid, kSmWarps * 32, 0, st>>>(p);
+    else if (L == 64) k_qsoftmax_fwd<2><<<grid, kSmWarps * 32, 0, st>>>(p);
+    else k_qsoftmax_fwd<1><<<grid, kSmWarps * 32, 0, st>>>(p);
+    return check_launch();
+}
+
+extern "C" size_t hgq_qsoftmax_bwd_workspace(int64_t R, int L, int rows_period) {
+    if (R <= 0 || rows_period <= 0 || R % rows_period != 0) return 0;
+    const int splits = sm_splits(R / rows_period, rows_period);
+    return (size_t)rows_period * splits * (8 + 2 * (size_t)L) * sizeof(float);
+}
+
+extern "C" int hgq_qsoftmax_bwd(const float *gy, const float *s, float *ds, const uint8_t *const *qk,
+                                const float *const *qi, const float *const *qf, const int *qrm, const int *qom,
+                                float scaler, float eps, float *dscalars8, float *df_out, float *di_out, int64_t R, int L,
+                                int rows_period, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!qk || !qi || !qf || !qrm || !qom || !gy || !dscalars8) return HGQ_ERR_NULL;
+    SmParams p = sm_make(s, gy, ds, qk, qi, qf, qrm, qom, scaler, eps, R, L, rows_period);
+    if (int e = sm_check(p, R)) return e;
+    const size_t need = hgq_qsoftmax_bwd_workspace(R, L, rows_period);
+    if (workspace == nullptr || workspace_bytes < need) return HGQ_ERR_WORKSPACE;
+    p.part = (float *)workspace;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((unsigned)rows_period, (unsigned)p.splits);
+    if (L == 128) k_qsoftmax_bwd<4><<<grid, kSmWarps * 32, 0, st>>>(p);
+    else if (L == 64) k_qsoftmax_bwd<2><<<grid, kSmWarps * 32, 0, st>>>(p);
+    else k_qsoftmax_bwd<1><<<grid, kSmWarps * 32, 0, st>>>(p);
+    if (int e = check_launch()) return e;
+    const int64_t n2 = 2 * (int64_t)rows_period * L;
+    k_qsoftmax_stage2<<<(unsigned)((n2 + kThreads - 1) / kThreads) + 1, kThreads, 0, st>>>(p.part, dscalars8, df_out, di_out, rows_period,
+                                                                                   L, p.splits);
+    return check_launch();
+}

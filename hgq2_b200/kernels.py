@@ -271,3 +271,61 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
                                   M, K, N, ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
     check(st, 'hgq_qdense_bwd')
     return dx, dwq, dbq, df
+
+
+def _quant_arrays(quants):
+    """quants: five (k, i, f, round_mode, overflow_mode) tuples -> ctypes arrays for the softmax entry points."""
+    import ctypes
+
+    def arr(vals):
+        return (ctypes.c_void_p * 5)(*[None if v is None else v.data_ptr() for v in vals])
+
+    ks = [None if q[0] is None else q[0].contiguous() for q in quants]
+    is_ = [None if q[1] is None else q[1].contiguous() for q in quants]
+    fs = [q[2].contiguous() for q in quants]
+    rms = (ctypes.c_int * 5)(*[ROUND_MODES[q[3]] for q in quants])
+    oms = (ctypes.c_int * 5)(*[OVERFLOW_MODES[q[4]] for q in quants])
+    keep = (ks, is_, fs)
+    return arr(ks), arr(is_), arr(fs), rms, oms, keep
+
+
+def qsoftmax_supported(L: int) -> bool:
+    return L in (32, 64, 128)
+
+
+def qsoftmax_fwd(s, quants, scaler: float, eps: float, rows_period: int, want_amax3: bool, want_amax5: bool):
+    """Fused training-mode QSoftmax forward over the last axis of s.  Returns (y, amax3 or None, amax5 or None)."""
+    require_cuda(s)
+    s = s.contiguous()
+    L = s.shape[-1]
+    R = s.numel() // L
+    y = torch.empty_like(s)
+    a3 = torch.empty(1, dtype=torch.float32, device=s.device) if want_amax3 else None
+    a5 = torch.empty(rows_period * L, dtype=torch.float32, device=s.device) if want_amax5 else None
+    qk, qi, qf, rms, oms, keep = _quant_arrays(quants)
+    with torch.cuda.device(s.device):
+        st = lib().hgq_qsoftmax_fwd(ptr(s), ptr(y), qk, qi, qf, rms, oms, float(scaler), float(eps), ptr(a3), ptr(a5), R, L,
+                                    rows_period, stream_handle())
+    check(st, 'hgq_qsoftmax_fwd')
+    del keep
+    return y, a3, a5
+
+
+def qsoftmax_bwd(gy, s, quants, scaler: float, eps: float, rows_period: int, want_di5: bool):
+    """Fused QSoftmax backward.  Returns (ds, scalars8, df5, di5 or None)."""
+    require_cuda(gy, s)
+    gy, s = gy.contiguous(), s.contiguous()
+    L = s.shape[-1]
+    R = s.numel() // L
+    ds = torch.empty_like(s)
+    sc = torch.empty(8, dtype=torch.float32, device=s.device)
+    df5 = torch.empty(rows_period * L, dtype=torch.float32, device=s.device)
+    di5 = torch.empty(rows_period * L, dtype=torch.float32, device=s.device) if want_di5 else None
+    ws = workspace(lib().hgq_qsoftmax_bwd_workspace(R, L, rows_period), s.device, slot=3)
+    qk, qi, qf, rms, oms, keep = _quant_arrays(quants)
+    with torch.cuda.device(s.device):
+        st = lib().hgq_qsoftmax_bwd(ptr(gy), ptr(s), ptr(ds), qk, qi, qf, rms, oms, float(scaler), float(eps), ptr(sc), ptr(df5),
+                                    ptr(di5), R, L, rows_period, ptr(ws), ws.numel(), stream_handle())
+    check(st, 'hgq_qsoftmax_bwd')
+    del keep
+    return ds, sc, df5, di5

@@ -172,3 +172,42 @@ def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training):
     if act_spec is not None and act_fused is None:
         y = layer.activation(y)
     return y
+
+
+class QSoftmaxFusedFn(torch.autograd.Function):
+    """Training-mode QSoftmax through the fused kernels.  ``params`` is a flat tuple of 15 tensors: (k, i, f) of the exp
+    table's input and output quantizers, of the inverse table's input and output quantizers (one element each) and of the
+    layer's output quantizer ([rows_period * L] tables); ``i`` / ``k`` are None for a rounding-only quantizer."""
+
+    @staticmethod
+    def forward(ctx, s, modes, scaler, eps, rows_period, want_amax3, want_amax5, *params):
+        quants = [(params[3 * j], params[3 * j + 1], params[3 * j + 2], modes[j][0], modes[j][1]) for j in range(5)]
+        quants = [(None if k is None else (k if k.dtype == torch.uint8 else k.to(torch.uint8)), i, f, rm, om)
+                  for k, i, f, rm, om in quants]
+        y, a3, a5 = kernels.qsoftmax_fwd(s, quants, scaler, eps, rows_period, want_amax3, want_amax5)
+        ctx.save_for_backward(s, *[t for q in quants for t in q[:3]])
+        ctx.meta = (modes, scaler, eps, rows_period, [None if t is None else tuple(t.shape) for t in params])
+        empty = torch.empty(0, device=s.device)
+        a3 = empty if a3 is None else a3
+        a5 = empty if a5 is None else a5
+        ctx.mark_non_differentiable(a3, a5)
+        return y, a3, a5
+
+    @staticmethod
+    def backward(ctx, gy, _g3, _g5):
+        s, *flat = ctx.saved_tensors
+        modes, scaler, eps, rows_period, shapes = ctx.meta
+        quants = [(flat[3 * j], flat[3 * j + 1], flat[3 * j + 2], modes[j][0], modes[j][1]) for j in range(5)]
+        want_di5 = modes[4][1] in ('SAT', 'SAT_SYM')
+        ds, sc, df5, di5 = kernels.qsoftmax_bwd(gy, s, quants, scaler, eps, rows_period, want_di5)
+        grads = []
+        for j in range(5):
+            k, i, f = flat[3 * j], flat[3 * j + 1], flat[3 * j + 2]
+            if j < 4:
+                gi = sc[2 * j].reshape(shapes[3 * j + 1]) if i is not None else None
+                gf = sc[2 * j + 1].reshape(shapes[3 * j + 2])
+            else:
+                gi = None if i is None else (di5.view(shapes[13]) if di5 is not None else torch.zeros(shapes[13], device=s.device))
+                gf = df5.view(shapes[14])
+            grads += [None, gi, gf]
+        return (ds, None, None, None, None, None, None, *grads)

@@ -46,10 +46,7 @@ class QLayerMeta(ABCMeta):
                     r = original_call(self, *args, **kwargs)
                     if (training or training == 'tracing') and self.enable_ebops:  # noqa: E712
                         tensors = args[0] if isinstance(args[0], (tuple, list)) else args
-                        shapes = ((1,) + tuple(t.shape[1:]) for t in tensors)
-                        ebops = self._compute_ebops(*shapes) * self.ebops_factor
-                        self._ebops.assign(ebops.detach().to(torch.uint32))
-                        self.add_loss(ebops * self.beta)
+                        self._account_ebops(*((1,) + tuple(t.shape[1:]) for t in tensors))
                     if not self.enable_oq or self.__output_quantizer_handled__:
                         return r
                     assert not isinstance(r, (tuple, list)), (
@@ -152,6 +149,12 @@ class QLayerBase(Layer, metaclass=QLayerMeta):
 
     def _compute_ebops(self, *args, **kwargs):
         raise NotImplementedError('This method is abstract and should be implemented in subclasses.')
+
+    def _account_ebops(self, *shapes):
+        """What the call wrapper does after a training forward: EBOPs at batch 1 -> uint32 variable and loss term."""
+        ebops = self._compute_ebops(*shapes) * self.ebops_factor
+        self._ebops.assign(ebops.detach().to(torch.uint32))
+        self.add_loss(ebops * self.beta)
 
 
 class QLayerBaseSingleInput(QLayerBase):

@@ -15,6 +15,7 @@ import torch
 from ..backend import epsilon
 from ..config.layer import global_config
 from ..quantizer import QuantizerConfig
+from . import _functions
 from .activation import QUnaryFunctionLUT
 from .core.base import QLayerBaseSingleInput
 
@@ -75,7 +76,71 @@ class QSoftmax(QLayerBaseSingleInput):
         self.inv_table.built = True
         super().build(input_shape)
 
+    def _fused_call(self, inputs, training):
+        """The whole chain (both tables, their quantizers and the output quantizer) in one kernel per direction, or None
+        when this call does not fit it: training forward only, stable form, softmax over the trailing axis, table
+        quantizers with one (k, i, f) each, every quantizer in a mode the kernel applies inline."""
+        from .. import kernels
+
+        if not (_functions.fused_enabled and training is True and self.stable and not self.enable_iq and self.enable_oq):
+            return None
+        if not inputs.is_cuda or inputs.dim() < 2 or self.axes != (inputs.dim() - 1,):
+            return None
+        L = inputs.shape[-1]
+        if not kernels.qsoftmax_supported(L):
+            return None
+        qs = (self.exp_table.iq, self.exp_table.oq, self.inv_table.iq, self.inv_table.oq, self.oq)
+        plans = []
+        for j, q in enumerate(qs):
+            if q.scaler is not None or q.affine is not None or q.qnoise_factor is not None:
+                return None
+            iq = q.quantizer
+            if getattr(iq, '__dummy__', False):
+                return None
+            plan = iq.fusion_plan(training)
+            if plan is None or plan['zero'] or plan['overflow_mode'] not in ('NONE', 'SAT', 'SAT_SYM'):
+                return None
+            if j < 4 and plan['f'].numel() != 1:
+                return None
+            plans.append(plan)
+        p5 = plans[4]
+        full = (1,) + tuple(inputs.shape[1:])
+        if len(p5['f'].shape) != len(full):
+            return None
+        rows_period = 1
+        for d in full[1:-1]:
+            rows_period *= d
+        if inputs.numel() % (rows_period * L) != 0:
+            return None
+        params = []
+        for j, plan in enumerate(plans):
+            for key in ('k', 'i', 'f'):
+                t = plan[key]
+                if t is not None and j == 4:
+                    t = t.expand(full).reshape(rows_period * L)
+                params.append(t)
+        modes = tuple((plan['round_mode'], plan['overflow_mode']) for plan in plans)
+        y, a3, a5 = _functions.QSoftmaxFusedFn.apply(inputs, modes, float(self.input_scaler), float(epsilon()), rows_period,
+                                                     plans[2]['track'] is not None, p5['track'] is not None, *params)
+        if plans[2]['track'] is not None:
+            plans[2]['track'](a3.view(plans[2]['f'].shape), None)
+        if p5['track'] is not None:
+            p5['track'](_functions._amax_to_shape(a5.view(full), tuple(p5['f'].shape)), None)
+        # the sub-layers' own bookkeeping that their wrapped call would have done
+        inv_shape = tuple(1 if ax in self.axes else d for ax, d in enumerate(full))
+        if self.exp_table.enable_ebops:
+            self.exp_table._account_ebops(full)
+        if self.inv_table.enable_ebops:
+            self.inv_table._account_ebops(inv_shape)
+        return y
+
     def call(self, inputs, training=None, mask=None):
+        self.__output_quantizer_handled__ = False
+        if mask is None:
+            y = self._fused_call(inputs, training)
+            if y is not None:
+                self.__output_quantizer_handled__ = True  # the kernel applied self.oq; the call wrapper must not repeat it
+                return y
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
         if self.stable:

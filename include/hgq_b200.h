@@ -194,6 +194,35 @@ int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float 
                    int round_mode, const float *wq, float *dx, float *dwq, float *dbq, float *df, int64_t M,
                    int K, int N, void *workspace, size_t workspace_bytes, unsigned *status, void *stream);
 
+/* ---- K4: quantised softmax ------------------------------------------------------------------ */
+
+/*
+ * Forward of the bit-accurate softmax in training mode.  Stands in for QSoftmax.call (layers/softmax.py:114-132,
+ * stable form, no mask) with the quantizers of its exp / inverse tables (layers/activation.py:58-61) and its own
+ * output quantizer (layers/core/base.py:105-110):
+ *   d = max(s) - s; a = Q1(d); e = exp(-a * scaler); b = Q2(e); S = sum b; t = Q3(S); u = Q4(1 / (t + eps)); y = Q5(b u)
+ * s, y [R, L] with the softmax over L (32, 64 or 128); R = batches * rows_period.  The quantizers come as HOST arrays
+ * of five entries: qk / qi / qf hold device pointers (Q1..Q4: one element each; Q5: [rows_period, L] tables; qk / qi
+ * entries may be NULL for a rounding-only quantizer), qrm the round modes, qom the overflow modes (NONE, SAT, SAT_SYM).
+ * absmax_inv_in (1 float) and absmax_out ([rows_period, L]) receive max |round(S)| and max |round(b u)| (may be NULL).
+ */
+int hgq_qsoftmax_fwd(const float *s, float *y, const uint8_t *const *qk, const float *const *qi,
+                     const float *const *qf, const int *qrm, const int *qom, float scaler, float eps,
+                     float *absmax_inv_in, float *absmax_out, int64_t R, int L, int rows_period, void *stream);
+
+size_t hgq_qsoftmax_bwd_workspace(int64_t R, int L, int rows_period);
+
+/*
+ * Backward of hgq_qsoftmax_fwd: recomputes the chain from s and returns ds [R, L], the surrogate gradients of Q1..Q4
+ * as dscalars8 = (di1, df1, di2, df2, di3, df3, di4, df4) and those of Q5 as df_out / di_out [rows_period, L]
+ * (di_out may be NULL).  The gradient of the row maximum is shared evenly among tied maxima.  Sums are reduced in a
+ * fixed order.
+ */
+int hgq_qsoftmax_bwd(const float *gy, const float *s, float *ds, const uint8_t *const *qk,
+                     const float *const *qi, const float *const *qf, const int *qrm, const int *qom,
+                     float scaler, float eps, float *dscalars8, float *df_out, float *di_out, int64_t R, int L,
+                     int rows_period, void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*
