@@ -544,6 +544,42 @@ def run_qdense_bwd(args):
                       'achieved_GBs': round(gbs, 1), 'peak_GBs': peak, 'frac': round(gbs / peak, 4), 'peak_source': kind}), flush=True)
 
 
+def run_qsoftmax(args):
+    """Kernel-level benchmark of the fused quantised softmax (forward and backward) on the attention-score tensor of the
+    transformer block: [batch, 4 heads, 64, 64] scores, softmax over the last axis, output bitwidth table [4 * 64, 64].
+    Algorithmic bytes per score: 8 forward (s in, y out), 12 backward (s, dL/dy in, ds out)."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    B, L, rp = args.batch or 8192, 64, 256
+    gen = torch.Generator(device=dev).manual_seed(0)
+    s = torch.randn(B, 4, 64, L, device=dev, generator=gen) * 4
+    gy = torch.randn(B, 4, 64, L, device=dev, generator=gen)
+    one = lambda v, dt=torch.float32: torch.full((1,), v, dtype=dt, device=dev)
+    k0, k1 = one(0, torch.uint8), one(1, torch.uint8)
+    quants = [(k0, one(4.0), one(6.0), 'RND', 'SAT'), (k0, one(1.0), one(9.0), 'RND_CONV', 'SAT'), (None, None, one(3.0), 'RND', 'NONE'),
+              (k0, one(1.0), one(9.0), 'RND_CONV', 'SAT'), (None, None, torch.full((rp * L,), 8.0, device=dev), 'RND', 'NONE')]
+    fwd = lambda: kernels.qsoftmax_fwd(s, quants, 0.25, 1e-7, rp, True, True)
+    bwd = lambda: kernels.qsoftmax_bwd(gy, s, quants, 0.25, 1e-7, rp, False)
+    peak, kind = measured_peaks()
+    out = {'kernel': 'k_qsoftmax', 'scores': s.numel(), 'peak_GBs': peak, 'peak_source': kind}
+    for name, fn, bpe in (('fwd', fwd, 8), ('bwd', bwd, 12)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        gbs = bpe * s.numel() / (ms * 1e-3) / 1e9
+        out[name] = {'ms': round(ms, 4), 'achieved_GBs': round(gbs, 1), 'frac': round(gbs / peak, 4)}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -557,7 +593,7 @@ def main():
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
     ap.add_argument('--model', default='particle_tagger', help='model of --workload qat')
     ap.add_argument('--batch', type=int, default=0, help='batch of --workload qat (0 = the benchmark batch)')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qat'],
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qsoftmax', 'qat'],
                     help="'qdense' times the fused dense forward kernel alone (for profiler captures)")
     ap.add_argument('--rows', type=int, default=1 << 22)
     ap.add_argument('--k', type=int, default=64)
@@ -571,6 +607,8 @@ def main():
         return run_qat_single(args)
     if args.workload == 'qdense_bwd':
         return run_qdense_bwd(args)
+    if args.workload == 'qsoftmax':
+        return run_qsoftmax(args)
     if args.impl == 'reference':
         run_reference(args)
     else:

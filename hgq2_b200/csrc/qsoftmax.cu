@@ -48,16 +48,63 @@ struct SmParams {
 constexpr int kSmWarps = 8;
 constexpr float kNegInf = -3.402823466e38f;
 
-struct QS {  // scalar quantizer parameters in registers
-    float kf, i, f;
+// A quantizer boiled down to launch-uniform constants, so that forward and backward are branch-free:
+// rounding-only quantizers get infinite clip bounds, SAT / SAT_SYM differ only in `lo` and in one select.
+struct QC {
+    float s, inv;      // 2^f, 2^-f
+    float lo, hi;      // clip bounds (+-inf when the quantizer only rounds)
+    float ci, cf;      // ln2 * 2^i, ln2 * 2^-f
+    float kf, rbias;   // keep_negative as float; 0.5 for RND, 0 for TRN
+    bool conv, sym;    // round-half-even; symmetric lower bound
 };
 
-__device__ __forceinline__ QS load_q(const SQuant &q) {
-    QS r;
-    r.f = __ldg(q.f);
-    r.kf = (q.om == OM_NONE) ? 0.f : (float)__ldg(q.k);
-    r.i = (q.om == OM_NONE) ? 0.f : __ldg(q.i);
-    return r;
+__device__ __forceinline__ QC make_qc(float kf, float i, float f, int rm, int om) {
+    QC c;
+    const Params p = make_params(kf, i, f);
+    c.s = p.s; c.inv = p.inv; c.kf = kf;
+    c.conv = (rm == RM_RND_CONV);
+    c.rbias = (rm == RM_RND) ? 0.5f : 0.f;
+    c.sym = (om == OM_SAT_SYM);
+    if (om == OM_NONE) {
+        c.lo = -INFINITY; c.hi = INFINITY; c.ci = 0.f; c.cf = 0.f;
+    } else {
+        c.hi = __fsub_rn(p.p2i, p.inv);
+        c.lo = (om == OM_SAT) ? __fmul_rn(-p.p2i, kf) : __fmul_rn(-c.hi, kf);
+        c.ci = __fmul_rn(p.p2i, kLn2);
+        c.cf = __fmul_rn(p.inv, kLn2);
+    }
+    return c;
+}
+
+__device__ __forceinline__ QC load_q(const SQuant &q) {
+    const float f = __ldg(q.f);
+    const float kf = (q.om == OM_NONE) ? 0.f : (float)__ldg(q.k);
+    const float i = (q.om == OM_NONE) ? 0.f : __ldg(q.i);
+    return make_qc(kf, i, f, q.rm, q.om);
+}
+
+__device__ __forceinline__ float qc_round(float x, const QC &c) {
+    const float xs = __fmul_rn(x, c.s);
+    const float q = c.conv ? rintf(xs) : floorf(__fadd_rn(xs, c.rbias));
+    return __fmul_rn(q, c.inv);
+}
+__device__ __forceinline__ float qc_fwd(float x, const QC &c, float &rounded) {
+    rounded = qc_round(x, c);
+    return clipf(rounded, c.lo, c.hi);
+}
+// same arithmetic as quantize_grad<> in hgq_math.cuh, with the mode folded into the constants
+__device__ __forceinline__ void qc_bwd(float g, float x, const QC &c, float &dx, float &di, float &df) {
+    const float xq = qc_round(x, c);
+    const float df_r = __fmul_rn(__fmul_rn(__fsub_rn(xq, x), -kLn2), g);
+    const bool pass = (xq >= c.lo) && (xq <= c.hi);
+    const bool to_hi = (xq > c.hi) || (c.hi < c.lo);
+    const bool to_lo = (xq < c.lo) && (c.lo < c.hi);
+    const float ghi = to_hi ? g : 0.f;
+    const float glo = to_lo ? -__fmul_rn(g, c.kf) : 0.f;
+    dx = pass ? g : 0.f;
+    const float m = __fadd_rn(ghi, glo);
+    di = c.sym ? __fmul_rn(m, c.ci) : __fadd_rn(__fmul_rn(ghi, c.ci), __fmul_rn(glo, c.ci));
+    df = __fadd_rn(pass ? df_r : 0.f, __fmul_rn(c.sym ? m : ghi, c.cf));
 }
 
 template <int VE>
@@ -93,7 +140,7 @@ __device__ __forceinline__ float warp_sum(float v) {  // fixed butterfly: every 
 
 // Forward chain of one row.  Fills b[] (quantised exponentials), returns u and the intermediate scalars.
 template <int VE>
-__device__ __forceinline__ void chain_fwd(const SmParams &P, const QS &q1, const QS &q2, const QS &q3, const QS &q4,
+__device__ __forceinline__ void chain_fwd(const SmParams &P, const QC &q1, const QC &q2, const QC &q3, const QC &q4,
                                           const float (&s)[VE], float (&a)[VE], float (&e)[VE], float (&b)[VE], float &m,
                                           float &S, float &t, float &t_rounded, float &v, float &u) {
     float mx = kNegInf;
@@ -104,16 +151,16 @@ __device__ __forceinline__ void chain_fwd(const SmParams &P, const QS &q1, const
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
         float r;
-        a[j] = quantize_rt(__fsub_rn(m, s[j]), q1.kf, q1.i, q1.f, P.q1.rm, P.q1.om, false, r);
+        a[j] = qc_fwd(__fsub_rn(m, s[j]), q1, r);
         e[j] = expf(__fmul_rn(-a[j], P.scaler));
-        b[j] = quantize_rt(e[j], q2.kf, q2.i, q2.f, P.q2.rm, P.q2.om, false, r);
+        b[j] = qc_fwd(e[j], q2, r);
         part = __fadd_rn(part, b[j]);
     }
     S = warp_sum(part);
-    t = quantize_rt(S, q3.kf, q3.i, q3.f, P.q3.rm, P.q3.om, false, t_rounded);
+    t = qc_fwd(S, q3, t_rounded);
     v = __fdiv_rn(1.f, __fadd_rn(t, P.eps));
     float r;
-    u = quantize_rt(v, q4.kf, q4.i, q4.f, P.q4.rm, P.q4.om, false, r);
+    u = qc_fwd(v, q4, r);
 }
 
 // grid = (rows_period, splits); CTA (p, sp) handles table row p for the batches sp, sp + splits, ... (warp w takes every
@@ -122,14 +169,13 @@ template <int VE>
 __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p = blockIdx.x, sp = blockIdx.y, L = P.L;
-    const QS q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
-    float k5[VE], i5[VE], f5[VE];
+    const QC q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
+    QC q5[VE];
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
         const int c = p * L + lane * VE + j;
-        f5[j] = __ldg(P.f5 + c);
-        k5[j] = (P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c);
-        i5[j] = (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c);
+        q5[j] = make_qc((P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c), (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c),
+                        __ldg(P.f5 + c), P.rm5, P.om5);
     }
     float am5[VE], am3 = 0.f;
 #pragma unroll
@@ -144,7 +190,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
             float r;
-            y[j] = quantize_rt(__fmul_rn(b[j], u), k5[j], i5[j], f5[j], P.rm5, P.om5, false, r);
+            y[j] = qc_fwd(__fmul_rn(b[j], u), q5[j], r);
             am5[j] = fmaxf(am5[j], fabsf(r));
         }
         store_row<VE>(P.y + row * L, lane, y);
@@ -162,14 +208,13 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P
     __shared__ float red5[kSmWarps][2][128];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p = blockIdx.x, sp = blockIdx.y, L = P.L;
-    const QS q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
-    float k5[VE], i5[VE], f5[VE];
+    const QC q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
+    QC q5[VE];
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
         const int c = p * L + lane * VE + j;
-        f5[j] = __ldg(P.f5 + c);
-        k5[j] = (P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c);
-        i5[j] = (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c);
+        q5[j] = make_qc((P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c), (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c),
+                        __ldg(P.f5 + c), P.rm5, P.om5);
     }
     float acc[8];  // di1, df1, di2, df2, di3, df3, di4, df4 (per thread; the per-row scalars are added by lane 0 only)
 #pragma unroll
@@ -190,7 +235,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
             float gz, di, df;
-            quantize_grad_rt(g[j], __fmul_rn(b[j], u), k5[j], i5[j], f5[j], P.rm5, P.om5, gz, di, df);
+            qc_bwd(g[j], __fmul_rn(b[j], u), q5[j], gz, di, df);
             adf5[j] = __fadd_rn(adf5[j], df);
             adi5[j] = __fadd_rn(adi5[j], di);
             gb[j] = __fmul_rn(gz, u);
@@ -199,9 +244,9 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P
         const float gu = warp_sum(gu_part);
         // u = Q4(v), v = 1 / (t + eps), t = Q3(S): row scalars, identical on every lane
         float gv, di4, df4, gS, di3, df3;
-        quantize_grad_rt(gu, v, q4.kf, q4.i, q4.f, P.q4.rm, P.q4.om, gv, di4, df4);
+        qc_bwd(gu, v, q4, gv, di4, df4);
         const float gt = __fmul_rn(-gv, __fmul_rn(v, v));
-        quantize_grad_rt(gt, S, q3.kf, q3.i, q3.f, P.q3.rm, P.q3.om, gS, di3, df3);
+        qc_bwd(gt, S, q3, gS, di3, df3);
         if (lane == 0) {
             acc[4] = __fadd_rn(acc[4], di3); acc[5] = __fadd_rn(acc[5], df3);
             acc[6] = __fadd_rn(acc[6], di4); acc[7] = __fadd_rn(acc[7], df4);
@@ -212,9 +257,9 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
             float ge, di2, df2, di1, df1;
-            quantize_grad_rt(__fadd_rn(gb[j], gS), e[j], q2.kf, q2.i, q2.f, P.q2.rm, P.q2.om, ge, di2, df2);
+            qc_bwd(__fadd_rn(gb[j], gS), e[j], q2, ge, di2, df2);
             const float ga = __fmul_rn(ge, __fmul_rn(-P.scaler, e[j]));
-            quantize_grad_rt(ga, __fsub_rn(m, s[j]), q1.kf, q1.i, q1.f, P.q1.rm, P.q1.om, gd[j], di1, df1);
+            qc_bwd(ga, __fsub_rn(m, s[j]), q1, gd[j], di1, df1);
             acc[0] = __fadd_rn(acc[0], di1); acc[1] = __fadd_rn(acc[1], df1);
             acc[2] = __fadd_rn(acc[2], di2); acc[3] = __fadd_rn(acc[3], df2);
             gm_part = __fadd_rn(gm_part, gd[j]);
