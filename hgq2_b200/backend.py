@@ -337,8 +337,8 @@ class MaxPooling2D(Layer):
         self.strides = self.pool_size if strides is None else ((strides, strides) if isinstance(strides, int) else tuple(strides))
 
     def call(self, inputs):
-        y = torch.nn.functional.max_pool2d(inputs.permute(0, 3, 1, 2), self.pool_size, self.strides)
-        return y.permute(0, 2, 3, 1).contiguous()
+        y = torch.nn.functional.max_pool2d(inputs.permute(0, 3, 1, 2), self.pool_size, self.strides)  # channels_last in, channels_last out
+        return y.permute(0, 2, 3, 1)
 
 
 class Sequential(Layer):

@@ -17,6 +17,9 @@ from .core.base import QLayerBaseSingleInput
 # The library convolution must multiply fp32 operands at full precision in forward *and* backward (the reference's
 # tests pin matmul precision to 'highest'); cuDNN's TF32 default would round operands to 10 mantissa bits.
 torch.backends.cudnn.allow_tf32 = False
+# Let cuDNN time its algorithms per shape: its heuristic picks FFT-based fp32 kernels (with layout transposes) for these
+# small 3x3 convolutions, which the direct NHWC kernels beat by a wide margin.
+torch.backends.cudnn.benchmark = True
 
 
 def _pair(v):
@@ -117,7 +120,10 @@ class QConv2D(QLayerBaseSingleInput):
         x = inputs.permute(0, 3, 1, 2)
         if pt or pb or pl or pr:
             x = F.pad(x, (pl, pr, pt, pb))
-        y = F.conv2d(x, kernel.permute(3, 2, 0, 1), stride=self.strides, dilation=self.dilation_rate)
+        # NHWC data viewed as NCHW is exactly torch's channels_last layout; giving the (tiny) kernel the same layout lets
+        # cuDNN run its NHWC kernels end to end, so no transposition of the activations happens on either side
+        w = kernel.permute(3, 2, 0, 1).contiguous(memory_format=torch.channels_last)
+        y = F.conv2d(x, w, stride=self.strides, dilation=self.dilation_rate)
         return y.permute(0, 2, 3, 1)
 
     def call(self, inputs, training=None):
