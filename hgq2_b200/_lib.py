@@ -74,6 +74,11 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
          c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p],
     ),
+    'hgq_qconv2d_supported': (c_int, [c_int64] + [c_int] * 8),
+    'hgq_qconv2d_fwd': (
+        c_int,
+        [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p] + [c_int] * 11 + [c_void_p, c_void_p],
+    ),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

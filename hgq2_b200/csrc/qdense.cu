@@ -57,6 +57,9 @@ struct QdParams {
     int rm, om, act, zero;
     int Kt;              // row stride of the packed parameter tables in shared memory (K rounded up to 8)
     int64_t num_tiles;
+    // implicit-GEMM convolution: x is a channels-last image [B, H, W, C] (C % 4 == 0), row m = (b, oh, ow), column
+    // k = ((kh * KW) + kw) * C + c reads x[b, oh*sh - pt + kh*dh, ow*sw - pl + kw*dw, c]; outside the image reads as zero
+    int conv, H, W, C, OH, OW, KH, KW, sh, sw, dh, dw, pt, pl;
 };
 
 // Abs-max bookkeeping variants (the statistic is max over rows of |round(x)| per quantizer-table entry):
@@ -78,11 +81,16 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
     unsigned char *B = stage + kQdStageBytes;                       // 3 x Kpad*Npad*2
     const int b_term_bytes = P.Kpad * P.Npad * 2;
     float *bias_s = reinterpret_cast<float *>(B + 3 * b_term_bytes);  // Npad floats
+    // convolution: per 4-column piece of the K axis its address offset and its tap displacement (dy, dx)
+    int *koff4 = reinterpret_cast<int *>(bias_s + P.Npad);
+    const int kp4 = P.conv ? (P.Kpad >> 2) : 0;
+    short *tap4 = reinterpret_cast<short *>(koff4 + kp4);          // (dy << 8) | (dx & 0xff), both int8
+    const int conv_bytes = P.conv ? ((kp4 * 6 + 15) / 16) * 16 : 0;
     // FASTQ: one byte per entry, the biased exponent of 2^f, row stride Kt + 8 (8-byte reads of 8 rows hit 8 bank pairs)
     // generic: f, i as int8 and k as uint8, row stride Kt
     const int Ke = P.Kt + 8;
     const int tab_bytes = (P.qf != nullptr) ? (P.rows_period * Ke + 15) / 16 * 16 : 0;
-    unsigned char *etab = reinterpret_cast<unsigned char *>(bias_s + P.Npad);
+    unsigned char *etab = reinterpret_cast<unsigned char *>(bias_s + P.Npad) + conv_bytes;
     signed char *ftab = reinterpret_cast<signed char *>(etab);
     signed char *itab = ftab + tab_bytes;
     unsigned char *ktab = reinterpret_cast<unsigned char *>(itab + tab_bytes);
@@ -104,6 +112,12 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
     if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
     for (int e = tid; e < Npad; e += kQdThreads) bias_s[e] = (P.bq != nullptr && e < N) ? __ldg(P.bq + e) : 0.f;
     for (int e = tid; e < amax_elems; e += kQdThreads) amax_t[e] = 0.f;
+    for (int e = tid; e < kp4; e += kQdThreads) {
+        const int k = e << 2, tap = k / P.C, c = k - tap * P.C, kh = tap / P.KW, kw = tap - kh * P.KW;
+        const int dy = kh * P.dh - P.pt, dx = kw * P.dw - P.pl;
+        koff4[e] = (dy * P.W + dx) * P.C + c;
+        tap4[e] = (short)(((dy & 0xff) << 8) | (dx & 0xff));
+    }
     if (P.qf != nullptr) {
         const bool need_ki = (P.om != OM_NONE);
         for (int e = tid; e < P.rows_period * P.Kt; e += kQdThreads) {
@@ -157,7 +171,7 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
     // 8-column groups kg = ((it*8 + w) & 1) * 4 + q4.  A quarter-warp (8 lanes, r8 = 0..7) fills one 128-byte core matrix.
     const int r8 = lane & 7, q4 = lane >> 3;
     const int n_chunks = (Kpad + kQdKC - 1) / kQdKC;
-    const bool vec_ok = (K % 4 == 0) && aligned(P.x, 16);
+    const bool vec_ok = (K % 4 == 0) && aligned(P.x, 16);  // convolution: C % 4 == 0 is checked on the host
     const float rbias = (P.rm == RM_RND) ? 0.5f : 0.f;
     const float act_lo = (P.act == ACT_RELU) ? 0.f : -INFINITY;
 
@@ -165,7 +179,23 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
     // on its way from HBM into the staging buffer (cp.async, 16 bytes per request, each thread fetching exactly the
     // pieces it will itself consume, so no barrier guards the staging area).
     const bool use_async = vec_ok;
+    // convolution: image offset of the patch origin and the origin's (ih, iw) for the four rows this thread serves in a
+    // tile; recomputed when the prefetch moves on to a new tile
+    int64_t cv_base[4];
+    int cv_ih[4], cv_iw[4];
     auto prefetch = [&](int64_t t_row0, int t_ch) {
+        if (P.conv && t_ch == 0) {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                const int64_t row = t_row0 + (((it * 8 + warp) >> 1) * 8) + r8;
+                const int64_t b = row / ((int64_t)P.OH * P.OW);
+                const int rem = (int)(row - b * ((int64_t)P.OH * P.OW));
+                const int oh = rem / P.OW, ow = rem - oh * P.OW;
+                cv_ih[it] = oh * P.sh;
+                cv_iw[it] = ow * P.sw;
+                cv_base[it] = ((b * P.H + cv_ih[it]) * P.W + cv_iw[it]) * P.C;
+            }
+        }
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
             const int c = it * 8 + warp, mg = c >> 1, kg = (c & 1) * 4 + q4;
@@ -173,8 +203,19 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
             const int k0 = t_ch * kQdKC + kg * 8;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const bool in = row < P.M && (k0 + 4 * h) < K;  // K % 4 == 0: a 16-byte piece is all inside or all outside
-                const float *src = in ? (P.x + row * K + k0 + 4 * h) : P.x;
+                bool in = row < P.M && (k0 + 4 * h) < K;  // K % 4 == 0: a 16-byte piece is all inside or all outside
+                const float *src = P.x;
+                if (P.conv) {
+                    if (in) {
+                        const int p4 = (k0 + 4 * h) >> 2;
+                        const int t = tap4[p4];
+                        const int ih = cv_ih[it] + (int)(signed char)(t >> 8), iw = cv_iw[it] + (int)(signed char)(t & 0xff);
+                        in = (unsigned)ih < (unsigned)P.H && (unsigned)iw < (unsigned)P.W;
+                        if (in) src = P.x + cv_base[it] + koff4[p4];
+                    }
+                } else if (in) {
+                    src = P.x + row * K + k0 + 4 * h;
+                }
                 const uint32_t dst = tc::smem_u32(stage) + (uint32_t)(((it * 2 + h) * kQdThreads + tid) * 16);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
             }
@@ -466,9 +507,9 @@ struct QdGeom {
     int64_t tiles;
 };
 
-static int qd_geom(int64_t M, int K, int N, int rows_period, bool want_amax, bool fastq, QdGeom &g) {
+static int qd_geom(int64_t M, int K, int N, int rows_period, bool want_amax, bool fastq, QdGeom &g, int kmax = 256) {
     if (M <= 0 || K <= 0 || N <= 0 || rows_period <= 0) return HGQ_ERR_SIZE;
-    if (K > 256 || N > 128) return HGQ_ERR_SIZE;
+    if (K > kmax || N > 128) return HGQ_ERR_SIZE;
     if (want_amax && (int64_t)rows_period * K > kQdMaxTable) return HGQ_ERR_SIZE;
     g.Kpad = (K + 15) / 16 * 16;
     g.Npad = pow2ceil(N < 16 ? 16 : N);
@@ -480,7 +521,7 @@ static int qd_geom(int64_t M, int K, int N, int rows_period, bool want_amax, boo
     // A terms (2), staging, B terms (3), bias, quantizer tables (3 byte planes), abs-max table, barrier + TMEM slot
     g.smem = 2 * (size_t)kQdATermBytes + kQdStageBytes + 3 * (size_t)g.Kpad * g.Npad * 2 + (size_t)g.Npad * 4 +
              (fastq ? 1 : 3) * tab_bytes +
-             (want_amax ? (size_t)rows_period * (g.Kt + 4) * 4 : 0) + 64;
+             (want_amax ? (size_t)rows_period * (g.Kt + 4) * 4 : 0) + 64 + (size_t)g.Kpad * 2 + 32;
     if (g.smem > 226 * 1024) return HGQ_ERR_SIZE;
     g.tiles = (M + kQdTileM - 1) / kQdTileM;
     int per_sm = (int)((228 * 1024) / (g.smem + 1024));  // 228 KB of shared memory per SM, 1 KB reserved per resident CTA
@@ -530,6 +571,7 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
     p.M = M; p.K = K; p.N = N; p.Kpad = g.Kpad; p.Npad = g.Npad; p.Kt = g.Kt;
     p.rows_period = rows_period; p.rm = round_mode; p.om = om; p.act = activation; p.zero = zero;
     p.num_tiles = g.tiles;
+    p.conv = 0;
     cudaStream_t st = (cudaStream_t)stream;
     const bool fastq = (qf != nullptr) && (om == OM_NONE);
     const bool conv = (round_mode == RM_RND_CONV);
@@ -573,4 +615,39 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
         return check_launch();
     }
     return HGQ_OK;
+}
+
+
+extern "C" int hgq_qconv2d_supported(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW) {
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || KH <= 0 || KW <= 0 || N <= 0 || OH <= 0 || OW <= 0) return 0;
+    if (C % 4 != 0) return 0;
+    QdGeom g;
+    return qd_geom(B * OH * OW, KH * KW * C, N, 1, false, false, g, 640) == HGQ_OK ? 1 : 0;
+}
+
+extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, const float *wq, const float *bq, int activation,
+                               float *y, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w, int dil_h,
+                               int dil_w, int pad_top, int pad_left, unsigned *status, void *stream) {
+    if (x == nullptr || wq == nullptr || y == nullptr) return HGQ_ERR_NULL;
+    if (activation != ACT_NONE && activation != ACT_RELU) return HGQ_ERR_MODE;
+    if (!hgq_qconv2d_supported(B, H, W, C, KH, KW, N, OH, OW)) return HGQ_ERR_SIZE;
+    if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0) return HGQ_ERR_SIZE;
+    if (pad_top < -127 || pad_top > 127 || pad_left < -127 || pad_left > 127 || KH * dil_h > 127 || KW * dil_w > 127) return HGQ_ERR_SIZE;
+    if (!aligned(x, 16) || !aligned(y, 4)) return HGQ_ERR_ALIGN;
+    const int64_t M = B * OH * OW;
+    const int K = KH * KW * C;
+    QdGeom g;
+    if (int e = qd_geom(M, K, N, 1, false, false, g, 640)) return e;
+    QdParams p{};
+    p.x = x; p.wq = wq; p.bq = bq; p.y = y; p.status = status;
+    p.M = M; p.K = K; p.N = N; p.Kpad = g.Kpad; p.Npad = g.Npad; p.Kt = g.Kt;
+    p.rows_period = 1; p.rm = RM_RND; p.om = OM_NONE; p.act = activation; p.zero = 0;
+    p.num_tiles = g.tiles;
+    p.conv = 1; p.H = H; p.W = W; p.C = C; p.OH = OH; p.OW = OW; p.KH = KH; p.KW = KW;
+    p.sh = stride_h; p.sw = stride_w; p.dh = dil_h; p.dw = dil_w; p.pt = pad_top; p.pl = pad_left;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t ce = cudaFuncSetAttribute(k_qdense_fwd<false, false, AMAX_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+    if (ce != cudaSuccess) return (int)ce;
+    k_qdense_fwd<false, false, AMAX_NONE><<<g.grid, kQdThreads, g.smem, st>>>(p);
+    return check_launch();
 }

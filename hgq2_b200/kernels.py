@@ -329,3 +329,24 @@ def qsoftmax_bwd(gy, s, quants, scaler: float, eps: float, rows_period: int, wan
     check(st, 'hgq_qsoftmax_bwd')
     del keep
     return ds, sc, df5, di5
+
+
+def qconv2d_supported(B, H, W, C, KH, KW, N, OH, OW) -> bool:
+    return bool(lib().hgq_qconv2d_supported(B, H, W, C, KH, KW, N, OH, OW))
+
+
+def qconv2d_fwd(x, wq2d, bq, activation, KH, KW, out_hw, strides, dilation, pad_tl):
+    """Implicit-GEMM conv2d forward.  x [B, H, W, C] (C % 4 == 0, already quantised), wq2d [KH*KW*C, N]."""
+    require_cuda(x, wq2d, bq)
+    x, wq2d = x.contiguous(), wq2d.contiguous()
+    bq = None if bq is None else bq.contiguous()
+    B, H, W, C = x.shape
+    N = wq2d.shape[1]
+    OH, OW = out_hw
+    y = torch.empty((B, OH, OW, N), dtype=torch.float32, device=x.device)
+    act = {None: 0, 'relu': 1}[activation]
+    with torch.cuda.device(x.device):
+        st = lib().hgq_qconv2d_fwd(ptr(x), B, H, W, C, ptr(wq2d), ptr(bq), act, ptr(y), KH, KW, N, OH, OW, strides[0], strides[1],
+                                   dilation[0], dilation[1], pad_tl[0], pad_tl[1], ptr(status_word(x.device)), stream_handle())
+    check(st, 'hgq_qconv2d_fwd')
+    return y

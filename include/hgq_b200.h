@@ -223,6 +223,22 @@ int hgq_qsoftmax_bwd(const float *gy, const float *s, float *ds, const uint8_t *
                      float scaler, float eps, float *dscalars8, float *df_out, float *di_out, int64_t R, int L,
                      int rows_period, void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * Implicit-GEMM 2-D convolution forward on the same tensor-core kernel as hgq_qdense_fwd:
+ *   y = act( conv2d(x, wq) + bq ),  channels-last.
+ * Stands in for the contraction of QBaseConv.call (layers/conv.py:72-89); the input quantizer is applied beforehand by
+ * hgq_quantize_fwd (x here is the already quantised image), because a pixel is shared by up to KH*KW patches.
+ *   x [B, H, W, C] with C % 4 == 0; wq [KH*KW*C, N] (the reference's [KH, KW, C, N] kernel flattened); bq [N] or NULL;
+ *   y [B, OH, OW, N]; output pixel (oh, ow) tap (kh, kw) reads x[b, oh*stride_h - pad_top + kh*dil_h,
+ *   ow*stride_w - pad_left + kw*dil_w, :], zero outside the image.  Patches are gathered straight from the image into
+ *   the operand staging (no im2col buffer).  Limits: KH*KW*C <= 640, N <= 128.
+ * The transposed convolution that yields dL/dx is the same call on dL/dy with the flipped, transposed kernel.
+ */
+int hgq_qconv2d_supported(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW);
+int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, const float *wq, const float *bq, int activation,
+                    float *y, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w, int dil_h,
+                    int dil_w, int pad_top, int pad_left, unsigned *status, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*
