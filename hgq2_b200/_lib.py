@@ -79,6 +79,11 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p] + [c_int] * 11 + [c_void_p, c_void_p],
     ),
+    'hgq_qconv2d_wgrad_workspace': (c_size_t, [c_int64] + [c_int] * 8),
+    'hgq_qconv2d_wgrad': (
+        c_int,
+        [c_void_p] * 6 + [c_int64] + [c_int] * 14 + [c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

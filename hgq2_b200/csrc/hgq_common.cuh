@@ -13,6 +13,7 @@ namespace hgq {
 constexpr int kNumSMs = 148;        // B200: 2 dies x 74 SMs
 constexpr int kThreads = 256;       // CTA size of every streaming kernel
 constexpr int64_t kMaxParamAbs = 100;
+enum : int { ACT_NONE = 0, ACT_RELU = 1 };  // fused output activations of the contraction kernels
 
 extern std::atomic<int64_t> g_launches;
 

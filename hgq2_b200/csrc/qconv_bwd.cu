@@ -1,0 +1,342 @@
+// K2c (convolution weight gradient): dWq = patches(xq)^T @ G and dbq = sum G over all output pixels, with
+// G = dY * (y > 0) written out once for the transposed convolution that yields dX.
+//
+// Stands in for the kernel/bias part of the autograd backward of QBaseConv.call (src/hgq/layers/conv.py:72-89).
+// The patch matrix [B*OH*OW, KH*KW*C] is never materialised: per 128-pixel tile and per block of 128 patch columns
+// the CTA gathers the image values straight into the transposed (MN-major) tensor-core operand as two bf16 terms
+// (16 significant bits: exact for quantised activations of up to 16 bits), G likewise, and one thread issues
+//   acc[kb] [128 k x N] += patches[:, kb]^T x G      (contraction over the tile's 128 pixels)
+// with one fp32 accumulator per column block in tensor memory, kept across all tiles of the CTA.  A constant column of
+// ones appended to the patch matrix makes row K of the product the bias gradient.  Per-CTA partials go to scratch and
+// are summed in a fixed order by a second kernel, so the result does not depend on scheduling.
+// Traffic: dY, y in and G out once (12 N bytes per pixel); the image is read through L1/L2 (each pixel serves up to
+// KH*KW patches).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "hgq_common.cuh"
+#include "tc05.cuh"
+
+namespace hgq {
+
+constexpr int kCwThreads = 256;
+constexpr int kCwTileM = 128;
+constexpr int kCwXTermBytes = 128 * 128 * 2;
+
+struct CwParams {
+    const float *x, *gy, *y;
+    float *gm;          // masked gradient out (NULL: no activation, G = dY is used as it is)
+    float *part;        // per-CTA partials [(K + 1) x N]
+    unsigned *status;
+    int64_t M, num_tiles;
+    int K, N, Np, nkb;
+    int H, W, C, OH, OW, KH, KW, sh, sw, dh, dw, pt, pl;
+};
+
+__device__ __forceinline__ void cw_split2(float v0, float v1, uint32_t &hi, uint32_t &lo) {
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+    hi = *reinterpret_cast<const uint32_t *>(&h2);
+    const float r0 = __fsub_rn(v0, __uint_as_float(hi << 16));
+    const float r1 = __fsub_rn(v1, __uint_as_float(hi & 0xffff0000u));
+    const __nv_bfloat162 l2 = __floats2bfloat162_rn(r0, r1);
+    lo = *reinterpret_cast<const uint32_t *>(&l2);
+}
+
+__global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad(const CwParams P) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int K = P.K, N = P.N, Np = P.Np, nkb = P.nkb;
+    const int CGn = Np >> 3;
+    const int g_term_bytes = kCwTileM * Np * 2;
+    unsigned char *G = smem;
+    unsigned char *X = G + 2 * g_term_bytes;
+    int *koff4 = reinterpret_cast<int *>(X + 2 * kCwXTermBytes);   // per 4-column piece: image offset, -1 = ones, -2 = zero
+    short *tap4 = reinterpret_cast<short *>(koff4 + nkb * 32);     // (dy << 8) | dx, tap displacement from the patch origin
+    uint64_t *bar = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(tap4) + (nkb * 64 + 15) / 16 * 16);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < nkb * Np) tmem_cols <<= 1;
+
+    if (tid == 0) {
+        tc::mbar_init(bar, 1);
+        tc::mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
+    for (int e = tid; e < nkb * 32; e += kCwThreads) {
+        const int k = e << 2;
+        if (k < K) {
+            const int tap = k / P.C, c = k - tap * P.C, kh = tap / P.KW, kw = tap - kh * P.KW;
+            const int dy = kh * P.dh, dx = kw * P.dw;
+            koff4[e] = (dy * P.W + dx) * P.C + c;
+            tap4[e] = (short)((dy << 8) | dx);
+        } else {
+            koff4[e] = (k == K) ? -1 : -2;
+            tap4[e] = 0;
+        }
+    }
+    for (int e = tid; e < 2 * kCwXTermBytes / 16; e += kCwThreads) reinterpret_cast<uint4 *>(X)[e] = make_uint4(0, 0, 0, 0);
+    tc::fence_smem_to_async();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t idesc = tc::make_idesc_bf16(Np, true, true);
+    const uint32_t g_base = tc::smem_u32(G), x_base = tc::smem_u32(X);
+
+    const int r8 = lane & 7, q4 = lane >> 3;
+    const bool vec_n = (N % 4 == 0) && aligned(P.gy, 16) && (P.y == nullptr || aligned(P.y, 16)) &&
+                       (P.gm == nullptr || aligned(P.gm, 16));
+    const bool relu = P.y != nullptr;
+    const int CG4g = (CGn + 3) >> 2, combos_g = 16 * CG4g;
+    const int64_t ohw = (int64_t)P.OH * P.OW;
+    // a single column block: groups that lie wholly in the zero padding stay zero for ever and are never rewritten
+    const int live_kg = (nkb == 1) ? ((K >> 2) + 2) >> 1 : 16;  // 8-column groups that hold data or the ones column
+
+    uint32_t phase = 0;
+    bool ok = true, issued = false, first_tile = true;
+
+    for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
+        const int64_t row0 = tile * kCwTileM;
+        // this thread's two pixel rows of the tile: local rows (h * 8 + warp) * 8 + r8
+        int64_t pbase[2];
+        int pih[2], piw[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t row = row0 + (h * 8 + warp) * 8 + r8;
+            if (row < P.M) {
+                const int64_t b = row / ohw;
+                const int rem = (int)(row - b * ohw);
+                const int oh = rem / P.OW, ow = rem - oh * P.OW;
+                pih[h] = oh * P.sh - P.pt;
+                piw[h] = ow * P.sw - P.pl;
+                pbase[h] = ((b * P.H + pih[h]) * P.W + piw[h]) * P.C;
+            } else {
+                pih[h] = -(1 << 20);  // every tap falls outside the image: the row gathers zeros
+                piw[h] = 0;
+                pbase[h] = 0;
+            }
+        }
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            // the previous product still reads both operand buffers
+            if (issued) {
+                const bool waited = (warp == 0) ? tc::mbar_wait(bar, phase) : true;
+                phase ^= 1u;
+                ok = __syncthreads_and(waited ? 1 : 0) != 0;
+                if (!ok) break;
+                issued = false;
+            }
+            if (kb == 0) {
+                // ---- G = dY (* relu mask): out to memory for the dX pass, two bf16 terms to shared memory ----------------
+                for (int u = 0; u * 8 < combos_g; ++u) {
+                    const int c = u * 8 + warp;
+                    const int mg = c / CG4g, kg = (c - mg * CG4g) * 4 + q4;
+                    if (!(c < combos_g && kg < CGn)) continue;
+                    const int64_t row = row0 + mg * 8 + r8;
+                    const int n0 = kg * 8;
+                    float g[8];
+                    if (row < P.M && vec_n && n0 + 8 <= N) {
+                        const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0));
+                        const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0 + 4));
+                        g[0] = a0.x; g[1] = a0.y; g[2] = a0.z; g[3] = a0.w; g[4] = a1.x; g[5] = a1.y; g[6] = a1.z; g[7] = a1.w;
+                        if (relu) {
+                            const float4 y0 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0));
+                            const float4 y1 = __ldcs(reinterpret_cast<const float4 *>(P.y + row * N + n0 + 4));
+                            const float yy[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) g[j] = yy[j] > 0.f ? g[j] : 0.f;
+                        }
+                        if (P.gm != nullptr) {
+                            *reinterpret_cast<float4 *>(P.gm + row * N + n0) = make_float4(g[0], g[1], g[2], g[3]);
+                            *reinterpret_cast<float4 *>(P.gm + row * N + n0 + 4) = make_float4(g[4], g[5], g[6], g[7]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const bool in = row < P.M && n0 + j < N;
+                            float v = in ? __ldcs(P.gy + row * N + n0 + j) : 0.f;
+                            if (in && relu) v = __ldcs(P.y + row * N + n0 + j) > 0.f ? v : 0.f;
+                            if (in && P.gm != nullptr) P.gm[row * N + n0 + j] = v;
+                            g[j] = v;
+                        }
+                    }
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) cw_split2(g[j], g[j + 1], hi[j >> 1], lo[j >> 1]);
+                    const int off = (mg * CGn + kg) * 128 + r8 * 16;
+                    *reinterpret_cast<uint4 *>(G + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4 *>(G + g_term_bytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                }
+            }
+            // ---- patches of column block kb, transposed operand: core (row/8, k/8) in a 16-group-wide buffer ------------
+            int lo_any = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int mg = h * 8 + warp;
+                float4 v[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int kg = i * 4 + q4;
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int p4 = kb * 32 + kg * 2 + hh;
+                        const int ko = koff4[p4];
+                        float4 t = make_float4(ko == -1 ? 1.f : 0.f, 0.f, 0.f, 0.f);
+                        if (ko >= 0) {
+                            const int tp = tap4[p4];
+                            const int ih = pih[h] + (tp >> 8), iw = piw[h] + (tp & 0xff);
+                            if ((unsigned)ih < (unsigned)P.H && (unsigned)iw < (unsigned)P.W)
+                                t = __ldg(reinterpret_cast<const float4 *>(P.x + pbase[h] + ko));
+                        }
+                        v[i * 2 + hh] = t;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int kg = i * 4 + q4;
+                    if (kg >= live_kg) continue;
+                    uint32_t hi[4], lo[4];
+                    cw_split2(v[i * 2].x, v[i * 2].y, hi[0], lo[0]);
+                    cw_split2(v[i * 2].z, v[i * 2].w, hi[1], lo[1]);
+                    cw_split2(v[i * 2 + 1].x, v[i * 2 + 1].y, hi[2], lo[2]);
+                    cw_split2(v[i * 2 + 1].z, v[i * 2 + 1].w, hi[3], lo[3]);
+                    lo_any |= ((lo[0] | lo[1] | lo[2] | lo[3]) & 0x7fff7fffu) != 0;
+                    const int off = (mg * 16 + kg) * 128 + r8 * 16;
+                    *reinterpret_cast<uint4 *>(X + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4 *>(X + kCwXTermBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                }
+            }
+            tc::fence_smem_to_async();
+            const int n_x = __syncthreads_or(lo_any) ? 2 : 1;
+            if (tid == 0) {
+                tc::fence_after_sync();
+                const uint32_t acc = tmem_base + (uint32_t)(kb * Np);
+                for (int s = 0; s < kCwTileM / 16; ++s)
+                    for (int tx = 0; tx < n_x; ++tx) {
+                        const uint64_t da = tc::make_smem_desc(x_base + tx * kCwXTermBytes + s * (2 * 16 * 128), 16 * 128, 128);
+                        for (int tg = 0; tg < 2; ++tg) {
+                            const uint64_t db =
+                                tc::make_smem_desc(g_base + tg * g_term_bytes + s * (2 * CGn * 128), (uint32_t)CGn * 128, 128);
+                            tc::mma_bf16(acc, da, db, idesc, !(first_tile && s == 0 && tx == 0 && tg == 0));
+                        }
+                    }
+                tc::commit(bar);
+            }
+            issued = true;
+        }
+        first_tile = false;
+    }
+    if (issued && ok) {
+        const bool waited = (warp == 0) ? tc::mbar_wait(bar, phase) : true;
+        ok = __syncthreads_and(waited ? 1 : 0) != 0;
+    }
+    if (!ok && tid == 0 && P.status) atomicOr(P.status, 1u);
+
+    // ---- per-CTA partial: rows k < K are dWq, row K is dbq ------------------------------------------------------------------
+    float *pw = P.part + (int64_t)blockIdx.x * ((int64_t)(K + 1) * N);
+    if (ok && (int64_t)blockIdx.x < P.num_tiles) {
+        tc::fence_after_sync();
+        const int qlane = (warp & 3) * 32, half = warp >> 2;
+        const int ncol = Np >> 1;
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int k = kb * 128 + qlane + lane;
+            for (int c0 = half * ncol; c0 < (half + 1) * ncol; c0 += 8) {
+                float v[8];
+                tc::tmem_ld8v(tmem_base + ((uint32_t)qlane << 16) + (uint32_t)(kb * Np + c0), v);
+                if (k <= K)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (c0 + j < N) pw[(int64_t)k * N + c0 + j] = v[j];
+            }
+        }
+    } else {
+        for (int e = tid; e < (K + 1) * N; e += kCwThreads) pw[e] = 0.f;
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+__global__ void __launch_bounds__(kThreads) k_cw_stage2(const float *__restrict__ part, int64_t stride, int64_t offset,
+                                                       float *__restrict__ out, int64_t n, int nparts) {
+    const int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (e >= n) return;
+    double acc = 0.0;
+    for (int p = 0; p < nparts; ++p) acc += (double)part[(int64_t)p * stride + offset + e];
+    out[e] = (float)acc;
+}
+
+struct CwGeom {
+    int Np, nkb, grid;
+    size_t smem;
+    int64_t tiles, M;
+};
+
+static int cw_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW, CwGeom &g) {
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || KH <= 0 || KW <= 0 || N <= 0 || OH <= 0 || OW <= 0) return HGQ_ERR_SIZE;
+    if (C % 4 != 0 || N > 128) return HGQ_ERR_SIZE;
+    if (B * H * W * C >= ((int64_t)1 << 31)) return HGQ_ERR_SIZE;
+    const int K = KH * KW * C;
+    g.Np = (N + 15) / 16 * 16;
+    g.nkb = (K + 1 + 127) / 128;
+    if (g.nkb * g.Np > 512) return HGQ_ERR_SIZE;
+    g.M = B * OH * OW;
+    g.tiles = (g.M + kCwTileM - 1) / kCwTileM;
+    g.smem = 2 * (size_t)kCwTileM * g.Np * 2 + 2 * (size_t)kCwXTermBytes + (size_t)g.nkb * 32 * 4 + ((size_t)g.nkb * 64 + 15) / 16 * 16 + 64;
+    int per_sm = (int)((228 * 1024) / (g.smem + 1024));
+    if (per_sm > 2) per_sm = 2;
+    if (per_sm == 2 && g.nkb * g.Np > 256) {  // two resident CTAs could not both hold their accumulators in tensor memory
+        g.smem = 120 * 1024;
+        per_sm = 1;
+    }
+    if (per_sm < 1 || g.smem > 226 * 1024) return HGQ_ERR_SIZE;
+    int64_t grid = (int64_t)kNumSMs * per_sm;
+    if (grid > g.tiles) grid = g.tiles;
+    g.grid = (int)grid;
+    return HGQ_OK;
+}
+
+}  // namespace hgq
+
+using namespace hgq;
+
+extern "C" size_t hgq_qconv2d_wgrad_workspace(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW) {
+    CwGeom g;
+    if (cw_geom(B, H, W, C, KH, KW, N, OH, OW, g) != HGQ_OK) return 0;
+    return (size_t)2 * kNumSMs * ((size_t)KH * KW * C + 1) * N * sizeof(float);
+}
+
+extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y, float *gm, float *dwq, float *dbq, int64_t B,
+                                 int H, int W, int C, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w,
+                                 int dil_h, int dil_w, int pad_top, int pad_left, void *workspace, size_t workspace_bytes,
+                                 unsigned *status, void *stream) {
+    if (x == nullptr || gy == nullptr || dwq == nullptr) return HGQ_ERR_NULL;
+    if ((y == nullptr) != (gm == nullptr)) return HGQ_ERR_NULL;
+    CwGeom g;
+    if (int e = cw_geom(B, H, W, C, KH, KW, N, OH, OW, g)) return e;
+    if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0) return HGQ_ERR_SIZE;
+    if (KH * dil_h > 127 || KW * dil_w > 127 || pad_top < 0 || pad_left < 0) return HGQ_ERR_SIZE;
+    if (!aligned(x, 16)) return HGQ_ERR_ALIGN;
+    const int K = KH * KW * C;
+    const int64_t stride = (int64_t)(K + 1) * N;
+    const size_t need = (size_t)g.grid * stride * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need) return HGQ_ERR_WORKSPACE;
+    CwParams p;
+    p.x = x; p.gy = gy; p.y = y; p.gm = gm; p.part = (float *)workspace; p.status = status;
+    p.M = g.M; p.num_tiles = g.tiles; p.K = K; p.N = N; p.Np = g.Np; p.nkb = g.nkb;
+    p.H = H; p.W = W; p.C = C; p.OH = OH; p.OW = OW; p.KH = KH; p.KW = KW;
+    p.sh = stride_h; p.sw = stride_w; p.dh = dil_h; p.dw = dil_w; p.pt = pad_top; p.pl = pad_left;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t ce = cudaFuncSetAttribute(k_qconv_wgrad, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+    if (ce != cudaSuccess) return (int)ce;
+    k_qconv_wgrad<<<g.grid, kCwThreads, g.smem, st>>>(p);
+    if (int e = check_launch()) return e;
+    const int64_t nw = (int64_t)K * N;
+    k_cw_stage2<<<(unsigned)((nw + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, stride, 0, dwq, nw, g.grid);
+    if (int e = check_launch()) return e;
+    if (dbq != nullptr) {
+        k_cw_stage2<<<(unsigned)((N + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, stride, nw, dbq, N, g.grid);
+        if (int e = check_launch()) return e;
+    }
+    return HGQ_OK;
+}

@@ -38,7 +38,6 @@ constexpr int kQdATermBytes = kQdTileM * kQdKC * 2;  // 16 KB per bf16 term
 constexpr int kQdStageBytes = kQdTileM * kQdKC * 4;  // 32 KB: one raw fp32 slab in flight
 constexpr int kQdMaxTable = 8192;              // abs-max table entries (rows_period * K)
 
-enum : int { ACT_NONE = 0, ACT_RELU = 1 };
 enum : unsigned { ST_TIMEOUT = 1u };
 
 struct QdParams {
@@ -618,19 +617,23 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
 }
 
 
-extern "C" int hgq_qconv2d_supported(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW) {
+namespace hgq {
+
+// Convolution by patch gather on the dense kernel (any stride); the extern "C" entry points that dispatch to it live with
+// the unit-stride kernel.
+int qconv2d_gather_supported(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW) {
     if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || KH <= 0 || KW <= 0 || N <= 0 || OH <= 0 || OW <= 0) return 0;
     if (C % 4 != 0) return 0;
     QdGeom g;
     return qd_geom(B * OH * OW, KH * KW * C, N, 1, false, false, g, 640) == HGQ_OK ? 1 : 0;
 }
 
-extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, const float *wq, const float *bq, int activation,
+int qconv2d_gather_launch(const float *x, int64_t B, int H, int W, int C, const float *wq, const float *bq, int activation,
                                float *y, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w, int dil_h,
                                int dil_w, int pad_top, int pad_left, unsigned *status, void *stream) {
     if (x == nullptr || wq == nullptr || y == nullptr) return HGQ_ERR_NULL;
     if (activation != ACT_NONE && activation != ACT_RELU) return HGQ_ERR_MODE;
-    if (!hgq_qconv2d_supported(B, H, W, C, KH, KW, N, OH, OW)) return HGQ_ERR_SIZE;
+    if (!qconv2d_gather_supported(B, H, W, C, KH, KW, N, OH, OW)) return HGQ_ERR_SIZE;
     if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0) return HGQ_ERR_SIZE;
     if (pad_top < -127 || pad_top > 127 || pad_left < -127 || pad_left > 127 || KH * dil_h > 127 || KW * dil_w > 127) return HGQ_ERR_SIZE;
     if (!aligned(x, 16) || !aligned(y, 4)) return HGQ_ERR_ALIGN;
@@ -651,3 +654,5 @@ extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, c
     k_qdense_fwd<false, false, AMAX_NONE><<<g.grid, kQdThreads, g.smem, st>>>(p);
     return check_launch();
 }
+
+}  // namespace hgq

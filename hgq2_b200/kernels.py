@@ -350,3 +350,31 @@ def qconv2d_fwd(x, wq2d, bq, activation, KH, KW, out_hw, strides, dilation, pad_
                                    dilation[0], dilation[1], pad_tl[0], pad_tl[1], ptr(status_word(x.device)), stream_handle())
     check(st, 'hgq_qconv2d_fwd')
     return y
+
+
+def qconv2d_wgrad_supported(B, H, W, C, KH, KW, N, OH, OW) -> bool:
+    return lib().hgq_qconv2d_wgrad_workspace(B, H, W, C, KH, KW, N, OH, OW) > 0
+
+
+def qconv2d_wgrad(x, gy, y, KH, KW, strides, dilation, pad_tl, want_db: bool):
+    """Weight / bias gradient of the implicit-GEMM convolution.  x [B, H, W, C] (C % 4 == 0), gy / y [B, OH, OW, N];
+    y is the forward output when the activation was ReLU, else None.  Returns (G, dwq [KH*KW*C, N], dbq or None) with
+    G the masked upstream gradient (gy itself without activation)."""
+    require_cuda(x, gy, y)
+    x, gy = x.contiguous(), gy.contiguous()
+    y = None if y is None else y.contiguous()
+    B, H, W, C = x.shape
+    _, OH, OW, N = gy.shape
+    dev = x.device
+    gm = torch.empty_like(gy) if y is not None else None
+    dwq = torch.empty((KH * KW * C, N), dtype=torch.float32, device=dev)
+    dbq = torch.empty(N, dtype=torch.float32, device=dev) if want_db else None
+    ws = workspace(lib().hgq_qconv2d_wgrad_workspace(B, H, W, C, KH, KW, N, OH, OW), dev, slot=4)
+    if ws is None:
+        raise _lib.HGQError(-2, 'hgq_qconv2d_wgrad: unsupported shape')
+    with torch.cuda.device(dev):
+        st = lib().hgq_qconv2d_wgrad(ptr(x), ptr(gy), ptr(y), ptr(gm), ptr(dwq), ptr(dbq), B, H, W, C, KH, KW, N, OH, OW, strides[0],
+                                     strides[1], dilation[0], dilation[1], pad_tl[0], pad_tl[1], ptr(ws), ws.numel(),
+                                     ptr(status_word(dev)), stream_handle())
+    check(st, 'hgq_qconv2d_wgrad')
+    return (gm if gm is not None else gy), dwq, dbq

@@ -174,6 +174,70 @@ def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training):
     return y
 
 
+class QConv2dFusedFn(torch.autograd.Function):
+    """act(conv2d(xq, wq) + bq), channels-last, on the implicit-GEMM tensor-core kernels (stride-1 input gradient).
+
+    ``xq`` is the already quantised image [B, H, W, C] and ``wq`` the quantised kernel [KH, KW, C, N].  Channels are
+    zero-padded to a multiple of four for the 16-byte patch gather.  Backward: one pass forms G = gy * (y > 0), the
+    kernel and bias gradients; the input gradient is the same forward kernel run over G with the flipped, transposed
+    kernel.
+    """
+
+    @staticmethod
+    def forward(ctx, xq, wq, bq, activation, strides, dilation, pad_tl, out_hw):
+        KH, KW, C, N = wq.shape
+        cp = (-C) % 4
+        if cp:
+            xq = torch.nn.functional.pad(xq, (0, cp))
+            wq = torch.nn.functional.pad(wq, (0, 0, 0, cp))
+        xq = xq.contiguous()
+        y = kernels.qconv2d_fwd(xq, wq.reshape(-1, N), bq, activation, KH, KW, out_hw, strides, dilation, pad_tl)
+        ctx.save_for_backward(xq, wq, y if activation == 'relu' else None)
+        ctx.geom = (KH, KW, C, N, cp, strides, dilation, pad_tl, bq is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        xq, wq, y = ctx.saved_tensors
+        KH, KW, C, N, cp, strides, dilation, pad_tl, has_bias = ctx.geom
+        need_x, need_w, need_b = ctx.needs_input_grad[:3]
+        g, dwq, dbq = kernels.qconv2d_wgrad(xq, gy, y, KH, KW, strides, dilation, pad_tl, has_bias and need_b)
+        dwq = dwq.view(KH, KW, C + cp, N)
+        if cp:
+            dwq = dwq[:, :, :C, :]
+        dx = None
+        if need_x:
+            B, H, W, Cp = xq.shape
+            wt = wq.flip(0, 1).permute(0, 1, 3, 2).reshape(KH * KW * N, Cp)
+            dx = kernels.qconv2d_fwd(g, wt, None, None, KH, KW, (H, W), (1, 1), dilation,
+                                     ((KH - 1) * dilation[0] - pad_tl[0], (KW - 1) * dilation[1] - pad_tl[1]))
+            if cp:
+                dx = dx[..., :C]
+        return dx, (dwq if need_w else None), dbq, None, None, None, None, None
+
+
+def fused_conv2d_call(layer, xq, qkernel, qbias):
+    """The fused convolution of a QConv2D layer on its quantised operands, or None when the shape is not covered."""
+    if not fused_enabled or not xq.is_cuda or xq.dtype != torch.float32 or xq.dim() != 4:
+        return None
+    act_spec = getattr(layer, '_activation_spec', None)
+    if act_spec not in (None, 'relu'):
+        return None
+    if tuple(layer.strides) != (1, 1):
+        return None  # the input gradient is written as a stride-1 convolution over the output gradient
+    B, H, W, C = xq.shape
+    KH, KW, _, N = qkernel.shape
+    (pt, _), (pl, _) = layer._pads(H, W)
+    _, OH, OW, _ = layer.compute_output_shape(tuple(xq.shape))
+    Cp = C + (-C) % 4
+    if N % 4 != 0 or KH * KW * N > 640 or Cp > 128:
+        return None
+    if not (kernels.qconv2d_supported(B, H, W, Cp, KH, KW, N, OH, OW) and kernels.qconv2d_supported(B, OH, OW, N, KH, KW, Cp, H, W)
+            and kernels.qconv2d_wgrad_supported(B, H, W, Cp, KH, KW, N, OH, OW)):
+        return None
+    return QConv2dFusedFn.apply(xq, qkernel, qbias, act_spec, tuple(layer.strides), tuple(layer.dilation_rate), (pt, pl), (OH, OW))
+
+
 class QSoftmaxFusedFn(torch.autograd.Function):
     """Training-mode QSoftmax through the fused kernels.  ``params`` is a flat tuple of 15 tensors: (k, i, f) of the exp
     table's input and output quantizers, of the inverse table's input and output quantizers (one element each) and of the

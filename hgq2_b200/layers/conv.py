@@ -10,7 +10,7 @@ import torch.nn.functional as F
 from ..backend import activation_name, get_activation, get_initializer
 from ..quantizer import Quantizer
 from ..quantizer.config import QuantizerConfig
-from ._functions import EbopsConv2dFn
+from ._functions import EbopsConv2dFn, fused_conv2d_call
 from .core.base import QLayerBaseSingleInput
 
 
@@ -115,7 +115,7 @@ class QConv2D(QLayerBaseSingleInput):
             self.parallelization_factor = self.n_parallel
 
     def convolution_op(self, inputs, kernel):
-        """channels_last 2-D convolution (library call; the fused kernel path replaces it)."""
+        """channels_last 2-D convolution through the library (shapes the implicit-GEMM kernels do not cover)."""
         (pt, pb), (pl, pr) = self._pads(inputs.shape[1], inputs.shape[2])
         x = inputs.permute(0, 3, 1, 2)
         if pt or pb or pl or pr:
@@ -129,9 +129,14 @@ class QConv2D(QLayerBaseSingleInput):
     def call(self, inputs, training=None):
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
-        outputs = self.convolution_op(inputs, self.qkernel)
+        qkernel = self.qkernel
+        qbias = self.qbias if self.use_bias else None
+        fused = fused_conv2d_call(self, inputs, qkernel, qbias)
+        if fused is not None:
+            return fused
+        outputs = self.convolution_op(inputs, qkernel)
         if self.use_bias:
-            outputs = outputs + self.qbias.reshape(1, 1, 1, self.filters)
+            outputs = outputs + qbias.reshape(1, 1, 1, self.filters)
         if self.activation is not None:
             return self.activation(outputs)
         return outputs

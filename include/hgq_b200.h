@@ -239,6 +239,21 @@ int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, const float 
                     float *y, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w, int dil_h,
                     int dil_w, int pad_top, int pad_left, unsigned *status, void *stream);
 
+/*
+ * Convolution weight / bias gradient (the kernel-side half of the autograd backward of QBaseConv.call,
+ * layers/conv.py:72-89), patches gathered from the image like hgq_qconv2d_fwd:
+ *   G = gy * (y > 0) when y != NULL (ReLU), else G = gy;   gm = G (written only when y != NULL; y and gm come together)
+ *   dwq [KH*KW*C, N] = patches(x)^T @ G,   dbq [N] = sum over pixels of G (dbq may be NULL).
+ * x [B, H, W, C] (C % 4 == 0, the quantised image the forward saw), gy / y / gm [B, OH, OW, N].
+ * Limits: N <= 128, ceil((KH*KW*C + 1) / 128) * roundup(N, 16) <= 512, B*H*W*C < 2^31, pads >= 0.
+ * Scratch: hgq_qconv2d_wgrad_workspace bytes (0 = unsupported shape).  Results do not depend on scheduling.
+ */
+size_t hgq_qconv2d_wgrad_workspace(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW);
+int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y, float *gm, float *dwq, float *dbq, int64_t B,
+                      int H, int W, int C, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w,
+                      int dil_h, int dil_w, int pad_top, int pad_left, void *workspace, size_t workspace_bytes,
+                      unsigned *status, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*

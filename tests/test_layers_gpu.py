@@ -136,17 +136,35 @@ def test_qeinsum_dense(q_type, overflow_mode, round_mode, equation, in_shape, ou
 
 @pytest.mark.parametrize('q_type,overflow_mode,round_mode', [('kbi', 'WRAP', 'RND'), ('kif', 'SAT', 'TRN'), ('kbi', 'SAT', 'RND')])
 @pytest.mark.parametrize('padding,strides', [('valid', 1), ('same', 1), ('valid', 2), ('same', 2)])
-def test_qconv2d(q_type, overflow_mode, round_mode, padding, strides):
+@pytest.mark.parametrize('filters', [5, 8])  # 8: the implicit-GEMM tensor-core kernels at stride 1; 5: the library path
+def test_qconv2d(q_type, overflow_mode, round_mode, padding, strides, filters):
     from hgq2_b200.layers import QConv2D
 
     rng = np.random.default_rng(9)
     sw, sa, sl = make_scopes(q_type, overflow_mode, round_mode, True)
     with sw, sa, sl:
-        layer = QConv2D(5, 3, strides=strides, padding=padding, activation='relu')
+        layer = QConv2D(filters, 3, strides=strides, padding=padding, activation='relu' if filters == 5 else None)
     x = grid_input(rng, (40, 9, 8, 3))
     layer(torch.from_numpy(x[:2]).cuda(), training=False)
     perturb(layer, rng, True)
     run_pair(layer, x, rng)
+
+
+def test_qconv2d_takes_the_fused_route():
+    from hgq2_b200 import _lib
+    from hgq2_b200.layers import QConv2D
+
+    rng = np.random.default_rng(3)
+    sw, sa, sl = make_scopes('kif', 'WRAP', 'RND', True)
+    with sw, sa, sl:
+        layer = QConv2D(16, 3, activation='relu')
+    x = grid_input(rng, (64, 12, 12, 4))
+    layer(torch.from_numpy(x[:2]).cuda(), training=False)
+    perturb(layer, rng, True)
+    before = _lib.lib().hgq_launch_count()
+    run_pair(layer, x, rng)
+    # forward + weight gradient (2 launches + reductions) + input gradient: the library convolution is not on this path
+    assert _lib.lib().hgq_launch_count() - before >= 6
 
 
 def test_dummy_quantizer_equals_plain_layer():

@@ -48,3 +48,57 @@ def test_implicit_gemm_conv_forward(B, H, W, C, KH, KW, N, stride, pads):
         assert tuple(y.shape) == tuple(yr.shape)
         err = float((y.cpu().double() - yr).abs().max() / max(float(yr.abs().max()), 1e-30))
         assert err <= 2e-7, err
+
+
+@pytest.mark.parametrize('B,H,W,C,KH,KW,N,stride,pads,relu', [
+    (9, 32, 32, 4, 3, 3, 16, (1, 1), ((0, 0), (0, 0)), True),
+    (5, 15, 15, 16, 3, 3, 32, (1, 1), ((0, 0), (0, 0)), True),
+    (37, 6, 6, 32, 3, 3, 64, (1, 1), ((0, 0), (0, 0)), True),
+    (4, 9, 8, 8, 3, 3, 5, (1, 1), ((1, 1), (1, 1)), False),
+    (3, 11, 10, 4, 3, 2, 12, (2, 2), ((0, 1), (0, 0)), True),
+    (2, 7, 7, 64, 3, 3, 32, (1, 1), ((2, 2), (2, 2)), False),
+    (600, 12, 12, 8, 3, 3, 16, (1, 1), ((0, 0), (0, 0)), True),
+])
+def test_implicit_gemm_conv_weight_gradient(B, H, W, C, KH, KW, N, stride, pads, relu):
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(B + H + C + N)
+    x = torch.from_numpy(grid(rng, (B, H, W, C)))
+    w = torch.from_numpy(grid(rng, (KH, KW, C, N), 5)).requires_grad_(True)
+    b = torch.from_numpy(grid(rng, (N,), 4)).requires_grad_(True)
+    (pt, pb), (pl, pr) = pads
+    y = ref_conv(x, w, b, stride, (1, 1), pads, relu)
+    gy = torch.from_numpy(rng.standard_normal(tuple(y.shape)).astype(np.float32))
+    (y * gy.double()).sum().backward()
+    assert kernels.qconv2d_wgrad_supported(B, H, W, C, KH, KW, N, y.shape[1], y.shape[2])
+    gm, dw, db = kernels.qconv2d_wgrad(x.cuda(), gy.cuda(), y.detach().float().cuda() if relu else None, KH, KW, stride, (1, 1),
+                                       (pt, pl), True)
+    kernels.check_status(gm.device)
+    g_ref = gy * (y.detach() > 0) if relu else gy
+    assert torch.equal(gm.cpu(), g_ref.float())
+    for got, ref in ((dw.cpu().reshape(KH, KW, C, N), w.grad), (db.cpu(), b.grad)):
+        err = float((got.double() - ref.double()).abs().max() / max(float(ref.abs().max()), 1e-30))
+        assert err <= 3e-5, err
+
+
+@pytest.mark.parametrize('B,H,W,C,KH,KW,N,pads', [
+    (9, 32, 32, 4, 3, 3, 16, ((0, 0), (0, 0))),
+    (5, 15, 15, 16, 3, 3, 32, ((0, 0), (0, 0))),
+    (7, 6, 6, 32, 3, 3, 64, ((0, 0), (0, 0))),
+    (4, 9, 8, 8, 3, 3, 8, ((1, 1), (1, 1))),
+])
+def test_input_gradient_as_flipped_convolution(B, H, W, C, KH, KW, N, pads):
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(B + H + C + N)
+    x = torch.from_numpy(grid(rng, (B, H, W, C))).requires_grad_(True)
+    w = torch.from_numpy(grid(rng, (KH, KW, C, N), 5))
+    (pt, pb), (pl, pr) = pads
+    y = ref_conv(x, w, None, (1, 1), (1, 1), pads, False)
+    gy = torch.from_numpy(rng.standard_normal(tuple(y.shape)).astype(np.float32))
+    (y * gy.double()).sum().backward()
+    wt = w.flip(0, 1).permute(0, 1, 3, 2).reshape(KH * KW * N, C).contiguous()
+    dx = kernels.qconv2d_fwd(gy.cuda(), wt.cuda(), None, None, KH, KW, (H, W), (1, 1), (1, 1), (KH - 1 - pt, KW - 1 - pl))
+    kernels.check_status(dx.device)
+    err = float((dx.cpu().double() - x.grad.double()).abs().max() / float(x.grad.abs().max()))
+    assert err <= 5e-6, err
