@@ -84,6 +84,8 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p] * 6 + [c_int64] + [c_int] * 14 + [c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    'hgq_maxpool2d_fwd': (c_int, [c_void_p, c_void_p, c_void_p, c_int64] + [c_int] * 9 + [c_void_p]),
+    'hgq_maxpool2d_bwd': (c_int, [c_void_p, c_void_p, c_void_p, c_int64] + [c_int] * 9 + [c_void_p]),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

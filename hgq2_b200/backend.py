@@ -337,8 +337,31 @@ class MaxPooling2D(Layer):
         self.strides = self.pool_size if strides is None else ((strides, strides) if isinstance(strides, int) else tuple(strides))
 
     def call(self, inputs):
+        if inputs.is_cuda and inputs.dtype == torch.float32 and self.pool_size[0] * self.pool_size[1] <= 255:
+            return _MaxPool2dFn.apply(inputs, self.pool_size, self.strides)
         y = torch.nn.functional.max_pool2d(inputs.permute(0, 3, 1, 2), self.pool_size, self.strides)  # channels_last in, channels_last out
         return y.permute(0, 2, 3, 1)
+
+
+class _MaxPool2dFn(torch.autograd.Function):
+    """Max pooling on the library's own kernels: one byte of arg-max per output element instead of an int64 index."""
+
+    @staticmethod
+    def forward(ctx, x, pool, strides):
+        from . import kernels
+
+        y, arg = kernels.maxpool2d_fwd(x, pool, strides)
+        ctx.save_for_backward(arg)
+        ctx.geom = (tuple(x.shape), pool, strides)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        from . import kernels
+
+        (arg,) = ctx.saved_tensors
+        shape, pool, strides = ctx.geom
+        return kernels.maxpool2d_bwd(gy, arg, shape, pool, strides), None, None
 
 
 class Sequential(Layer):

@@ -257,13 +257,18 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad(const CwParams P) {
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
+// out[e] = sum over CTAs of part[cta * stride + offset + e]: eight elements per warp, four lanes per element walking the
+// partials, combined in a fixed order (double accumulation), so the result does not depend on scheduling
 __global__ void __launch_bounds__(kThreads) k_cw_stage2(const float *__restrict__ part, int64_t stride, int64_t offset,
                                                        float *__restrict__ out, int64_t n, int nparts) {
-    const int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (e >= n) return;
+    const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
+    const int64_t e = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * 8 + j;
     double acc = 0.0;
-    for (int p = 0; p < nparts; ++p) acc += (double)part[(int64_t)p * stride + offset + e];
-    out[e] = (float)acc;
+    if (e < n)
+        for (int p = sub; p < nparts; p += 4) acc += (double)part[(int64_t)p * stride + offset + e];
+    acc += __shfl_down_sync(0xffffffffu, acc, 16);
+    acc += __shfl_down_sync(0xffffffffu, acc, 8);
+    if (sub == 0 && e < n) out[e] = (float)acc;
 }
 
 struct CwGeom {
@@ -332,10 +337,10 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
     k_qconv_wgrad<<<g.grid, kCwThreads, g.smem, st>>>(p);
     if (int e = check_launch()) return e;
     const int64_t nw = (int64_t)K * N;
-    k_cw_stage2<<<(unsigned)((nw + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, stride, 0, dwq, nw, g.grid);
+    k_cw_stage2<<<(unsigned)((nw + 63) / 64), kThreads, 0, st>>>(p.part, stride, 0, dwq, nw, g.grid);
     if (int e = check_launch()) return e;
     if (dbq != nullptr) {
-        k_cw_stage2<<<(unsigned)((N + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, stride, nw, dbq, N, g.grid);
+        k_cw_stage2<<<(unsigned)((N + 63) / 64), kThreads, 0, st>>>(p.part, stride, nw, dbq, N, g.grid);
         if (int e = check_launch()) return e;
     }
     return HGQ_OK;

@@ -378,3 +378,31 @@ def qconv2d_wgrad(x, gy, y, KH, KW, strides, dilation, pad_tl, want_db: bool):
                                      ptr(status_word(dev)), stream_handle())
     check(st, 'hgq_qconv2d_wgrad')
     return (gm if gm is not None else gy), dwq, dbq
+
+
+def maxpool2d_fwd(x, pool, strides):
+    """channels-last 'valid' max pooling.  Returns (y, argmax uint8)."""
+    require_cuda(x)
+    x = x.contiguous()
+    B, H, W, C = x.shape
+    OH, OW = (H - pool[0]) // strides[0] + 1, (W - pool[1]) // strides[1] + 1
+    y = torch.empty((B, OH, OW, C), dtype=torch.float32, device=x.device)
+    arg = torch.empty((B, OH, OW, C), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        st = lib().hgq_maxpool2d_fwd(ptr(x), ptr(y), ptr(arg), B, H, W, C, pool[0], pool[1], strides[0], strides[1], OH, OW,
+                                     stream_handle())
+    check(st, 'hgq_maxpool2d_fwd')
+    return y, arg
+
+
+def maxpool2d_bwd(gy, arg, in_shape, pool, strides):
+    require_cuda(gy, arg)
+    gy = gy.contiguous()
+    B, H, W, C = in_shape
+    _, OH, OW, _ = gy.shape
+    dx = torch.empty(in_shape, dtype=torch.float32, device=gy.device)
+    with torch.cuda.device(gy.device):
+        st = lib().hgq_maxpool2d_bwd(ptr(gy), ptr(arg), ptr(dx), B, H, W, C, pool[0], pool[1], strides[0], strides[1], OH, OW,
+                                     stream_handle())
+    check(st, 'hgq_maxpool2d_bwd')
+    return dx

@@ -254,6 +254,17 @@ int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y, float *gm
                       int dil_h, int dil_w, int pad_top, int pad_left, void *workspace, size_t workspace_bytes,
                       unsigned *status, void *stream);
 
+/* ---- K5: channels-last 2-D max pooling ('valid') ----------------------------------------------------------------
+ * The keras MaxPooling2D between the QConv2D layers of the reference's convolutional models (QMaxPooling2D,
+ * layers/pooling.py:146-167, delegates to the same keras op).  x [B, H, W, C] -> y [B, OH, OW, C] with
+ * OH = (H - pool_h) / stride_h + 1; argmax [B, OH, OW, C] holds the winning window position (ph * pool_w + pw, first
+ * maximum in scan order) as one byte.  The backward routes gy to those positions (summing where windows overlap).
+ */
+int hgq_maxpool2d_fwd(const float *x, float *y, unsigned char *argmax, int64_t B, int H, int W, int C, int pool_h,
+                      int pool_w, int stride_h, int stride_w, int OH, int OW, void *stream);
+int hgq_maxpool2d_bwd(const float *gy, const unsigned char *argmax, float *dx, int64_t B, int H, int W, int C,
+                      int pool_h, int pool_w, int stride_h, int stride_w, int OH, int OW, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*

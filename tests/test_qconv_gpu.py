@@ -102,3 +102,25 @@ def test_input_gradient_as_flipped_convolution(B, H, W, C, KH, KW, N, pads):
     kernels.check_status(dx.device)
     err = float((dx.cpu().double() - x.grad.double()).abs().max() / float(x.grad.abs().max()))
     assert err <= 5e-6, err
+
+
+@pytest.mark.parametrize('shape,pool,strides', [
+    ((5, 30, 30, 16), (2, 2), (2, 2)),
+    ((3, 13, 13, 32), (2, 2), (2, 2)),
+    ((4, 9, 11, 6), (3, 2), (2, 1)),
+    ((2, 8, 8, 3), (3, 3), (1, 1)),
+])
+def test_max_pooling_matches_torch_including_ties(shape, pool, strides):
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(11)
+    # a coarse grid after ReLU: many exact ties inside a window, so the arg-max rule is exercised
+    x = torch.from_numpy(np.maximum(np.round(rng.standard_normal(shape) * 2) / 2, 0).astype(np.float32))
+    xr = x.clone().requires_grad_()
+    yr = F.max_pool2d(xr.permute(0, 3, 1, 2), pool, strides).permute(0, 2, 3, 1)
+    gy = torch.from_numpy(rng.standard_normal(tuple(yr.shape)).astype(np.float32))
+    (yr * gy).sum().backward()
+    y, arg = kernels.maxpool2d_fwd(x.cuda(), pool, strides)
+    assert torch.equal(y.cpu(), yr.detach())
+    dx = kernels.maxpool2d_bwd(gy.cuda(), arg, shape, pool, strides)
+    assert float((dx.cpu() - xr.grad).abs().max()) <= 1e-6 * float(gy.abs().max()) * pool[0] * pool[1]
