@@ -393,7 +393,10 @@ def run_qat(args, dev, world, rank, peak):
 
     out = []
     dp = DataParallel() if world > 1 else None
+    only = [m for m in args.qat_models.split(',') if m]
     for name, (builder, batch, make_x, classes, bytes_per_sample) in QAT_CONFIGS.items():
+        if only and name not in only:
+            continue
         try:
             model = workloads.build(getattr(workloads, builder)(), device=dev)
             cpu = None
@@ -589,6 +592,7 @@ def main():
     ap.add_argument('--no-cpu', action='store_true', help='skip the cpu_baseline leg')
     ap.add_argument('--no-qat', action='store_true', help='skip the QAT-step leg (training workloads)')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer end-to-end leg')
+    ap.add_argument('--qat-models', default='', help='comma-separated subset of the QAT-step models (default: all)')
     ap.add_argument('--elements', type=int, default=1 << 28,
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
     ap.add_argument('--model', default='particle_tagger', help='model of --workload qat')
