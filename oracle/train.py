@@ -129,3 +129,52 @@ def train_step(twin: OracleSequential, opt: OracleAdam, x, y, loss_fn):
     total.backward()
     opt.step()
     return total.detach()
+
+
+class TracingFlag:
+    """Compares equal to 'tracing' and is falsy (utils/minmax_trace.py:25-33)."""
+
+    def __eq__(self, other):
+        return other == 'tracing'
+
+    def __hash__(self):
+        return hash('tracing')
+
+    def __bool__(self):
+        return False
+
+
+def _all_quantizers(obj, seen=None):
+    """Every OracleFixedQuantizer reachable from an oracle layer (attributes, nested oracle layers, lists/tuples)."""
+    seen = set() if seen is None else seen
+    if id(obj) in seen:
+        return
+    seen.add(id(obj))
+    if isinstance(obj, OL.OracleFixedQuantizer):
+        yield obj
+        return
+    if isinstance(obj, (list, tuple)):
+        for v in obj:
+            yield from _all_quantizers(v, seen)
+    elif isinstance(obj, (OL.OracleQLayer, OracleSequential)):
+        for v in vars(obj).values():
+            yield from _all_quantizers(v, seen)
+
+
+def trace_minmax(twin: OracleSequential, x: torch.Tensor, reset=True, batch_size=1024):
+    """utils/minmax_trace.py:35-99 on the oracle twin: reset i (-1e9) and k (0) of the trainable WRAP quantizers, run
+    the data in batches with training == 'tracing', return (total EBOPs, outputs)."""
+    if reset:
+        for q in _all_quantizers(twin):
+            if q.overflow_mode == 'WRAP' and q.trainable:
+                q._i.data.fill_(-1e9)
+                q._k = torch.zeros_like(q._k)
+    outs = []
+    with torch.no_grad():
+        for s in range(0, len(x), batch_size):
+            outs.append(twin(x[s:s + batch_size], training=TracingFlag()))
+    total = 0
+    for l in twin.qlayers():
+        if l.enable_ebops:
+            total += l.total_ebops() if hasattr(l, 'total_ebops') else int(l.ebops.item())
+    return total, torch.cat(outs)
