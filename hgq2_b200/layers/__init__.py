@@ -2,7 +2,20 @@ from .activation import QUnaryFunctionLUT
 from .attn.mha import QMultiHeadAttention
 from .conv import QConv2D
 from .core import QDense, QEinsumDense, QLayerBase, QLayerBaseMultiInputs, QLayerBaseSingleInput
+from .ops import QAdd, QAveragePow2, QMaximum, QMeanPow2, QMinimum, QMultiply, QSubtract, QSum
+from .pooling import (
+    QAveragePooling2D,
+    QGlobalAveragePooling1D,
+    QGlobalAveragePooling2D,
+    QGlobalMaxPooling1D,
+    QGlobalMaxPooling2D,
+    QMaxPooling2D,
+)
 from .softmax import QSoftmax
 
-__all__ = ['QDense', 'QEinsumDense', 'QConv2D', 'QSoftmax', 'QUnaryFunctionLUT', 'QMultiHeadAttention', 'QLayerBase',
-           'QLayerBaseSingleInput', 'QLayerBaseMultiInputs']
+__all__ = [
+    'QDense', 'QEinsumDense', 'QConv2D', 'QSoftmax', 'QUnaryFunctionLUT', 'QMultiHeadAttention', 'QLayerBase',
+    'QLayerBaseSingleInput', 'QLayerBaseMultiInputs', 'QSum', 'QMeanPow2', 'QAdd', 'QAveragePow2', 'QSubtract', 'QMultiply',
+    'QMaximum', 'QMinimum', 'QMaxPooling2D', 'QAveragePooling2D', 'QGlobalAveragePooling1D', 'QGlobalAveragePooling2D',
+    'QGlobalMaxPooling1D', 'QGlobalMaxPooling2D',
+]

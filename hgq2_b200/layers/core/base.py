@@ -38,7 +38,10 @@ class QLayerMeta(ABCMeta):
                 params['training'] = inspect.Parameter('training', inspect.Parameter.KEYWORD_ONLY, default=None)
                 new_signature = signature.replace(parameters=list(params.values()))
 
-            if not getattr(cls, '__no_wrap_call__', False):
+            # An inherited call that a parent class already wrapped is not wrapped again: the reference wraps it a second
+            # time when the parent was instantiated first (QMeanPow2 after QSum), which adds the EBOPs loss term twice
+            # depending on instantiation order; here the accounting happens once whatever the order.
+            if not getattr(cls, '__no_wrap_call__', False) and not getattr(original_call, '__ebops_wrapped__', False):
 
                 @wraps(original_call)
                 def call(self, *args, **kwargs):
@@ -55,6 +58,7 @@ class QLayerMeta(ABCMeta):
                     return self.oq(r, training=training)
 
                 call.__signature__ = new_signature
+                call.__ebops_wrapped__ = True
                 cls.call = call
         return super().__call__(*args, **kwargs)
 

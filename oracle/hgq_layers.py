@@ -490,3 +490,111 @@ def mirror_mha(layer):
         k.iq = v.iq
     return OracleQMHA(q, k, v, mirror_layer(layer._output_dense), mirror_softmax(layer._softmax), layer.parallelization_factor,
                       **kw)
+
+
+# ---- accumulation, merge and pooling layers (layers/ops/accum.py, layers/ops/merge.py, layers/pooling.py) --------------
+class OracleQSum(OracleQLayer):
+    """QSum / QMeanPow2 (layers/ops/accum.py:10-81): sum(iq(x), axes) * scale; EBOPs 0.65 (sum bits - sum min bits)."""
+
+    def __init__(self, axes, scale, keepdims, **kw):
+        super().__init__(kq=None, bq=None, activation=None, **kw)
+        self.axes, self.scale, self.keepdims = tuple(axes), scale, keepdims
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        return torch.sum(x, dim=self.axes, keepdim=self.keepdims) * self.scale
+
+    def _compute_ebops(self, shape):
+        bits = self.iq.bits_(shape)
+        return (torch.sum(bits) - torch.sum(torch.amin(bits, dim=self.axes))) * 0.65
+
+
+class OracleQPool(OracleQLayer):
+    """QBasePooling (layers/pooling.py:23-47): pool(iq(x)); EBOPs sum(bits) * parallelization_factor / n_parallel."""
+
+    def __init__(self, fn, n_parallel, parallelization_factor, **kw):
+        super().__init__(kq=None, bq=None, activation=None, **kw)
+        self.fn, self.n_parallel, self.pf = fn, n_parallel, parallelization_factor
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        return self.fn(x)
+
+    def _compute_ebops(self, shape):
+        return torch.sum(self.iq.bits_(shape)) * self.pf / self.n_parallel
+
+
+class OracleQMerge(OracleQLayer):
+    """QMerge and its subclasses (layers/ops/merge.py): one quantizer per input, then an element-wise merge."""
+
+    def __init__(self, kind, iqs, scale=1.0, **kw):
+        super().__init__(iq=None, kq=None, bq=None, activation=None, **kw)
+        self.kind, self.iqs, self.scale = kind, iqs, scale
+
+    def quantizers(self):
+        d = {f'iq{n}': q for n, q in enumerate(self.iqs or [])}
+        if self.oq is not None:
+            d['oq'] = self.oq
+        return d
+
+    def __call__(self, xs, training=None):
+        self.losses = []
+        if self.iqs is not None:
+            xs = [q(x, training) for q, x in zip(self.iqs, xs)]
+        out = xs[0]
+        for t in xs[1:]:
+            out = {'add': torch.add, 'sub': torch.sub, 'mul': torch.mul, 'max': torch.maximum, 'min': torch.minimum}[self.kind](out, t)
+        out = out * self.scale if self.scale != 1.0 else out
+        if (training or training == 'tracing') and self.enable_ebops:
+            bitss = [q.bits_((1,) + tuple(x.shape[1:])) for q, x in zip(self.iqs, xs)]
+            if self.kind == 'sub':
+                e = torch.sum(torch.maximum(bitss[0], bitss[1]))
+            elif self.kind == 'mul':
+                p = bitss[0]
+                for b in bitss[1:]:
+                    p = p * b
+                e = torch.sum(p)
+            else:
+                least = bitss[0]
+                for b in bitss[1:]:
+                    least = torch.minimum(least, b)
+                e = torch.sum(sum(bitss)) - torch.sum(least)
+                e = e * (0.65 if self.kind == 'add' else 1.0)
+            e = e * self.ebops_factor
+            self.ebops = e.detach().to(torch.uint32)
+            self.ebops_f = e.detach()
+            self.losses.append(e * self.beta)
+        if self.oq is not None:
+            out = self.oq(out, training)
+        return out
+
+
+def mirror_op_layer(layer):
+    """Oracle twin of a built hgq2_b200 accumulation / pooling / merge layer."""
+    import torch.nn.functional as F
+
+    name = type(layer).__name__
+    common = dict(
+        oq=mirror_quantizer(layer.oq) if layer.enable_oq else None, beta=float(layer.beta) if layer.enable_ebops else 0.0,
+        ebops_factor=layer.ebops_factor, enable_ebops=layer.enable_ebops,
+    )
+    if name in ('QSum', 'QMeanPow2'):
+        return OracleQSum(layer.axes, layer.scale, layer.keepdims, iq=mirror_quantizer(layer.iq) if layer.enable_iq else None, **common)
+    merges = {'QAdd': 'add', 'QAveragePow2': 'add', 'QSubtract': 'sub', 'QMultiply': 'mul', 'QMaximum': 'max', 'QMinimum': 'min'}
+    if name in merges:
+        iqs = [mirror_quantizer(q) for q in layer.iq] if layer.enable_iq else None
+        return OracleQMerge(merges[name], iqs, scale=getattr(layer, '_scale', 1.0), **common)
+    pools = {
+        'QMaxPooling2D': lambda l: (lambda t: F.max_pool2d(t.permute(0, 3, 1, 2), l.pool_size, l.strides).permute(0, 2, 3, 1)),
+        'QAveragePooling2D': lambda l: (lambda t: F.avg_pool2d(t.permute(0, 3, 1, 2), l.pool_size, l.strides).permute(0, 2, 3, 1)),
+        'QGlobalAveragePooling1D': lambda l: (lambda t: t.mean(dim=1, keepdim=l.keepdims)),
+        'QGlobalAveragePooling2D': lambda l: (lambda t: t.mean(dim=(1, 2), keepdim=l.keepdims)),
+        'QGlobalMaxPooling1D': lambda l: (lambda t: t.amax(dim=1, keepdim=l.keepdims)),
+        'QGlobalMaxPooling2D': lambda l: (lambda t: t.amax(dim=(1, 2), keepdim=l.keepdims)),
+    }
+    if name in pools:
+        return OracleQPool(pools[name](layer), layer.n_parallel, layer.parallelization_factor,
+                           iq=mirror_quantizer(layer.iq) if layer.enable_iq else None, **common)
+    raise NotImplementedError(name)
