@@ -411,6 +411,29 @@ def _snake(name: str) -> str:
     return ''.join(out)
 
 
+def moments(x: torch.Tensor, axes, keepdims: bool = False, synchronized: bool = False):
+    """Mean and variance over ``axes`` the way keras.ops.moments computes them on the torch backend
+    (Var = E[x^2] - E[x]^2).  ``synchronized``: average both statistics over the ranks of the default process group
+    (equal shard sizes), differentiably -- the torch backend of Keras refuses this flag; data-parallel training here
+    supports it."""
+    axes = tuple(axes) if not isinstance(axes, int) else (axes,)
+    mean = torch.mean(x, dim=axes, keepdim=True)
+    mean_sq = torch.mean(torch.square(x), dim=axes, keepdim=True)
+    if synchronized:
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            import torch.distributed.nn.functional as dfn
+
+            stats = dfn.all_reduce(torch.cat([mean.reshape(-1), mean_sq.reshape(-1)])) / dist.get_world_size()
+            mean, mean_sq = stats[:mean.numel()].view_as(mean), stats[mean.numel():].view_as(mean_sq)
+    variance = mean_sq - torch.square(mean)
+    if not keepdims:
+        mean = mean.squeeze(axes) if axes else mean
+        variance = variance.squeeze(axes) if axes else variance
+    return mean, variance
+
+
 # ---- activations -------------------------------------------------------------------------------
 def get_activation(spec) -> Callable | None:
     if spec is None or spec == 'linear':

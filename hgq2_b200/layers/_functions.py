@@ -118,11 +118,12 @@ def _amax_to_shape(t: torch.Tensor, shape) -> torch.Tensor:
     return torch.amax(t, dim=dims, keepdim=True) if dims else t
 
 
-def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training):
+def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training, apply_iq: bool = True):
     """act(iq(x) @ qkernel + qbias) through the fused kernel, or None if this call has to take the unfused route.
 
     ``inputs`` is [batch, free..., contracted...] with ``n_contract`` trailing contracted axes; ``qkernel`` is the
-    quantised kernel viewed as [K, N]; ``qbias`` the quantised bias as [N] or None.
+    quantised kernel viewed as [K, N]; ``qbias`` the quantised bias as [N] or None.  ``apply_iq=False``: the caller has
+    already quantised ``inputs`` (layers that need the quantised activations themselves, e.g. for batch moments).
     """
     if not fused_enabled or not inputs.is_cuda or inputs.dtype != torch.float32 or inputs.dim() < 2:
         return None
@@ -136,7 +137,7 @@ def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training):
     M = inputs.numel() // K
     k = i = f = None
     rows_period, rm, om, tr, zero, track, bw_shape, table_shape = 1, 'RND', 'NONE', True, False, None, None, None
-    if layer.enable_iq:
+    if layer.enable_iq and apply_iq:
         q = layer.iq
         if q.scaler is not None or q.affine is not None or (q.qnoise_factor is not None and training):
             return None

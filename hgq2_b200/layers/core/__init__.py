@@ -1,5 +1,6 @@
 from .base import MultipleQuantizers, QLayerBase, QLayerBaseMultiInputs, QLayerBaseSingleInput
-from .dense import QDense
+from .dense import QBatchNormDense, QDense
 from .einsum_dense import QEinsumDense
 
-__all__ = ['QLayerBase', 'QLayerBaseSingleInput', 'QLayerBaseMultiInputs', 'MultipleQuantizers', 'QDense', 'QEinsumDense']
+__all__ = ['QLayerBase', 'QLayerBaseSingleInput', 'QLayerBaseMultiInputs', 'MultipleQuantizers', 'QDense', 'QBatchNormDense',
+           'QEinsumDense']

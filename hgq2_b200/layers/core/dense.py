@@ -6,7 +6,7 @@ from math import prod
 
 import torch
 
-from ...backend import activation_name, get_activation, get_initializer
+from ...backend import activation_name, get_activation, get_initializer, moments
 from ...quantizer import Quantizer
 from ...quantizer.config import QuantizerConfig
 from .._functions import EbopsDenseFn, fused_dense_call
@@ -108,3 +108,97 @@ class QDense(QLayerBaseSingleInput):
         if self.bias is None:
             return None
         return self.bq(self._bias.value)
+
+
+class QBatchNormDense(QDense):
+    """Batch normalisation of the (quantised) input folded into the dense kernel before it is quantised
+    (mirror of src/hgq/layers/core/dense.py:105-254):
+
+        mean, var = moments(iq(x));  scaler = bn_gamma / sqrt(var + epsilon)
+        y = act( iq(x) @ kq(scaler[:, None] * W) + bq(b - mean @ W) )
+
+    Training uses the batch moments and updates the moving averages; otherwise the moving averages are used.
+    """
+
+    def __init__(self, units, activation=None, use_bias=True, kernel_initializer='glorot_uniform', bias_initializer='zeros',
+                 kernel_regularizer=None, bias_regularizer=None, activity_regularizer=None, kernel_constraint=None,
+                 bias_constraint=None, scale=True, momentum=0.99, epsilon=1e-3, bn_gamma_initializer='ones',
+                 moving_mean_initializer='zeros', moving_variance_initializer='ones', bn_gamma_regularizer=None,
+                 bn_gamma_constraint=None, synchronized=False, kq_conf: None | QuantizerConfig = None,
+                 iq_conf: None | QuantizerConfig = None, bq_conf: None | QuantizerConfig = None, **kwargs):
+        assert use_bias, 'BatchNormDense must have `use_bias=True`'
+        super().__init__(units=units, activation=activation, use_bias=use_bias, kernel_initializer=kernel_initializer,
+                         bias_initializer=bias_initializer, kernel_regularizer=kernel_regularizer,
+                         bias_regularizer=bias_regularizer, activity_regularizer=activity_regularizer,
+                         kernel_constraint=kernel_constraint, bias_constraint=bias_constraint, kq_conf=kq_conf,
+                         iq_conf=iq_conf, bq_conf=bq_conf, **kwargs)
+        self.scale = scale
+        self.momentum = float(momentum)
+        self.bn_gamma_initializer = get_initializer(bn_gamma_initializer)
+        self.moving_mean_initializer = get_initializer(moving_mean_initializer)
+        self.moving_variance_initializer = get_initializer(moving_variance_initializer)
+        self.bn_gamma_regularizer, self.bn_gamma_constraint = bn_gamma_regularizer, bn_gamma_constraint
+        self.epsilon = epsilon
+        self.synchronized = synchronized
+
+    def build(self, input_shape):
+        super().build(input_shape)
+        shape = (int(input_shape[-1]),)
+        self.reduction_axis = tuple(range(len(input_shape) - 1))
+        if self.scale:
+            self._bn_gamma = self.add_weight(shape=shape, name='bn_gamma', initializer=self.bn_gamma_initializer,
+                                             regularizer=self.bn_gamma_regularizer, constraint=self.bn_gamma_constraint)
+        self.moving_mean = self.add_weight(shape=shape, name='moving_mean', initializer=self.moving_mean_initializer,
+                                           trainable=False)
+        self.moving_variance = self.add_weight(shape=shape, name='moving_variance',
+                                               initializer=self.moving_variance_initializer, trainable=False)
+
+    @property
+    def bn_gamma(self):
+        return self._bn_gamma.value
+
+    def get_fused_qkernel_and_qbias(self, mean, var):
+        bn_gamma = self._bn_gamma.value if self.scale else 1
+        scaler = bn_gamma / torch.sqrt(var + self.epsilon)
+        kernel = self._kernel.value
+        fused_qkernel = self.kq(scaler[:, None] * kernel)
+        offset = -torch.matmul(mean, kernel)
+        fused_qbias = self.bq(self._bias.value + offset)
+        return fused_qkernel, fused_qbias
+
+    def call(self, inputs, training=None):
+        if self.enable_iq:
+            inputs = self.iq(inputs, training=training)
+        if training and self.trainable:
+            mean, var = moments(inputs, self.reduction_axis, synchronized=self.synchronized)
+            self.moving_mean.assign(self.moving_mean.value * self.momentum + mean.detach() * (1.0 - self.momentum))
+            self.moving_variance.assign(self.moving_variance.value * self.momentum + var.detach() * (1.0 - self.momentum))
+        else:
+            var, mean = self.moving_variance.value, self.moving_mean.value
+        qkernel, qbias = self.get_fused_qkernel_and_qbias(mean, var)
+        y = fused_dense_call(self, inputs, 1, qkernel, qbias, training, apply_iq=False)
+        if y is not None:
+            return y
+        x = torch.matmul(inputs, qkernel) + qbias
+        if self.activation is not None:
+            x = self.activation(x)
+        return x
+
+    def get_config(self):
+        config = super().get_config()
+        config.update({
+            'scale': self.scale, 'momentum': self.momentum, 'epsilon': self.epsilon,
+            'bn_gamma_initializer': self.bn_gamma_initializer, 'moving_mean_initializer': self.moving_mean_initializer,
+            'moving_variance_initializer': self.moving_variance_initializer,
+            'bn_gamma_regularizer': self.bn_gamma_regularizer, 'bn_gamma_constraint': self.bn_gamma_constraint,
+            'synchronized': self.synchronized,
+        })
+        return config
+
+    @property
+    def qkernel(self):
+        return self.get_fused_qkernel_and_qbias(self.moving_mean.value, self.moving_variance.value)[0]
+
+    @property
+    def qbias(self):
+        return self.get_fused_qkernel_and_qbias(self.moving_mean.value, self.moving_variance.value)[1]

@@ -145,20 +145,25 @@ class QEinsumDense(QLayerBaseSingleInput):
 
     def call(self, inputs, training=None):
         qkernel = self.kq(self._kernel.value, training=training)
+        qbias = self.bq(self._bias.value, training=training) if self.bias is not None else None
+        return self._contract(inputs, qkernel, qbias, training, apply_iq=True)
+
+    def _contract(self, inputs, qkernel, qbias, training, apply_iq: bool):
+        """act(einsum(eq, iq(x), qkernel) + qbias): the fused tensor-core kernel when the equation is a plain matrix
+        product, the library einsum otherwise.  ``apply_iq=False``: ``inputs`` are already quantised."""
         if self._matmul_form is not None:
             n_con, K, N, kfree_shape = self._matmul_form
-            qbias = None
-            if self.bias is not None:
-                qbias = self.bq(self._bias.value, training=training)
-                qbias = qbias.reshape((1,) * (len(kfree_shape) - qbias.dim()) + tuple(qbias.shape)).expand(kfree_shape).reshape(N)
-            y = fused_dense_call(self, inputs, n_con, qkernel.reshape(K, N), qbias, training)
+            qb = None
+            if qbias is not None:
+                qb = qbias.reshape((1,) * (len(kfree_shape) - qbias.dim()) + tuple(qbias.shape)).expand(kfree_shape).reshape(N)
+            y = fused_dense_call(self, inputs, n_con, qkernel.reshape(K, N), qb, training, apply_iq=apply_iq)
             if y is not None:
                 return y.reshape((inputs.shape[0],) + tuple(self.full_output_shape[1:]))
-        if self.enable_iq:
+        if self.enable_iq and apply_iq:
             inputs = self.iq(inputs, training=training)
         x = torch.einsum(self.equation, inputs, qkernel)
-        if self.bias is not None:
-            x = x + self.bq(self._bias.value, training=training)
+        if qbias is not None:
+            x = x + qbias
         if self.activation is not None:
             x = self.activation(x)
         return x

@@ -598,3 +598,126 @@ def mirror_op_layer(layer):
         return OracleQPool(pools[name](layer), layer.n_parallel, layer.parallelization_factor,
                            iq=mirror_quantizer(layer.iq) if layer.enable_iq else None, **common)
     raise NotImplementedError(name)
+
+
+# ---- batch-normalisation layers -----------------------------------------------------------------------------------------
+def _moments(x, axes):
+    """keras.ops.moments on the torch backend: Var = E[x^2] - E[x]^2, statistics squeezed."""
+    axes = tuple(axes)
+    mean = torch.mean(x, dim=axes, keepdim=True)
+    var = torch.mean(torch.square(x), dim=axes, keepdim=True) - torch.square(mean)
+    return mean.squeeze(axes), var.squeeze(axes)
+
+
+class OracleQBatchNormDense(OracleQDense):
+    """QBatchNormDense (layers/core/dense.py:105-254)."""
+
+    def __init__(self, bn_gamma, moving_mean, moving_variance, momentum, epsilon, trainable=True, **kw):
+        super().__init__(**kw)
+        self.bn_gamma = _leaf(bn_gamma, True) if bn_gamma is not None else None
+        self.moving_mean, self.moving_variance = moving_mean.detach().clone(), moving_variance.detach().clone()
+        self.momentum, self.epsilon, self.trainable = momentum, epsilon, trainable
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        if training and self.trainable:  # :206-214
+            mean, var = _moments(x, range(x.dim() - 1))
+            self.moving_mean = self.moving_mean * self.momentum + mean.detach() * (1.0 - self.momentum)
+            self.moving_variance = self.moving_variance * self.momentum + var.detach() * (1.0 - self.momentum)
+        else:
+            mean, var = self.moving_mean, self.moving_variance
+        gamma = self.bn_gamma if self.bn_gamma is not None else 1
+        scaler = gamma / torch.sqrt(var + self.epsilon)  # :186-198
+        qk = self.kq(scaler[:, None] * self.kernel, training)
+        qb = self.bq(self.bias + (-torch.matmul(mean, self.kernel)), training)
+        return self._act(torch.matmul(x, qk) + qb)
+
+
+class OracleQEinsumDenseBatchnorm(OracleQEinsumDense):
+    """QEinsumDenseBatchnorm (layers/einsum_dense_batchnorm.py:96-228)."""
+
+    def __init__(self, fused_kernel_equation, reduction_axes, cast_shape, bn_gamma, moving_mean, moving_variance, momentum,
+                 trainable=True, **kw):
+        super().__init__(**kw)
+        self.fused_kernel_equation, self.reduction_axes, self.cast_shape = fused_kernel_equation, reduction_axes, cast_shape
+        self.bn_gamma = _leaf(bn_gamma, True) if bn_gamma is not None else None
+        self.moving_mean, self.moving_variance = moving_mean.detach().clone(), moving_variance.detach().clone()
+        self.momentum, self.trainable = momentum, trainable
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        if training and self.trainable:  # :203-219
+            y0 = torch.einsum(self.equation, x, self.kernel)
+            mean, var = _moments(y0, self.reduction_axes)
+            self.moving_mean = self.moving_mean * self.momentum + mean.detach() * (1.0 - self.momentum)
+            self.moving_variance = self.moving_variance * self.momentum + var.detach() * (1.0 - self.momentum)
+        else:
+            mean, var = self.moving_mean, self.moving_variance
+        gamma = self.bn_gamma if self.bn_gamma is not None else 1
+        scaler = gamma / torch.sqrt(var + 1e-7)  # the backend fuzz factor, :172
+        qk = self.kq(torch.einsum(self.fused_kernel_equation, self.kernel, scaler), training)
+        qb = self.bq(self.bias + (-mean * scaler).reshape(self.cast_shape), training)
+        return self._act(torch.einsum(self.equation, x, qk) + qb)
+
+
+class OracleQBatchNorm(OracleQLayer):
+    """QBatchNormalization (layers/batch_normalization.py:123-207)."""
+
+    def __init__(self, axis, bn_gamma, bn_beta, moving_mean, moving_variance, momentum, epsilon, **kw):
+        super().__init__(activation=None, **kw)
+        self.axis = axis
+        self.bn_gamma = _leaf(bn_gamma, True) if bn_gamma is not None else None
+        self.bn_beta = _leaf(bn_beta, True) if bn_beta is not None else None
+        self.moving_mean, self.moving_variance = moving_mean.detach().clone(), moving_variance.detach().clone()
+        self.momentum, self.epsilon = momentum, epsilon
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        if training:
+            mean, var = _moments(x, [a for a in range(x.dim()) if a != self.axis])
+            self.moving_mean = self.moving_mean * self.momentum + mean.detach() * (1.0 - self.momentum)
+            self.moving_variance = self.moving_variance * self.momentum + var.detach() * (1.0 - self.momentum)
+        else:
+            mean, var = self.moving_mean, self.moving_variance
+        gamma = self.bn_gamma if self.bn_gamma is not None else 1
+        beta = self.bn_beta if self.bn_beta is not None else 1
+        scale = gamma / torch.sqrt(var + self.epsilon)
+        offset = beta - mean * scale
+        shape = [1] * x.dim()
+        shape[self.axis] = x.shape[self.axis]
+        return x * self.kq(scale, training).reshape(shape) + self.bq(offset, training).reshape(shape)
+
+    def _compute_ebops(self, shape):
+        bshape = [1] * len(shape)
+        bshape[self.axis] = shape[self.axis]
+        n = (shape[self.axis],)
+        bw_inp = self.iq.bits_(shape)
+        return torch.sum(bw_inp * self.kq.bits_(n).reshape(bshape)) + torch.mean(self.bq.bits_(n).reshape(bshape)) * float(prod(shape))
+
+
+def mirror_bn_layer(layer):
+    """Oracle twin of a built hgq2_b200 QBatchNormDense / QEinsumDenseBatchnorm / QBatchNormalization."""
+    name = type(layer).__name__
+    common = dict(
+        iq=mirror_quantizer(layer.iq) if layer.enable_iq else None, kq=mirror_quantizer(layer.kq), bq=mirror_quantizer(layer.bq),
+        oq=mirror_quantizer(layer.oq) if layer.enable_oq else None, beta=float(layer.beta) if layer.enable_ebops else 0.0,
+        ebops_factor=layer.ebops_factor, enable_ebops=layer.enable_ebops,
+    )
+    mm, mv = _np(layer.moving_mean), _np(layer.moving_variance)
+    if name == 'QBatchNormalization':
+        return OracleQBatchNorm(layer.axis, _np(layer._bn_gamma) if layer.scale else None, _np(layer._bn_beta) if layer.center else None,
+                                mm, mv, layer.momentum, layer.epsilon, **common)
+    common['activation'] = layer.get_config()['activation']
+    gamma = _np(layer._bn_gamma) if layer.scale else None
+    if name == 'QBatchNormDense':
+        return OracleQBatchNormDense(gamma, mm, mv, layer.momentum, layer.epsilon, kernel=_np(layer._kernel), bias=_np(layer._bias),
+                                     n_parallel=layer.n_parallel, parallelization_factor=layer.parallelization_factor, **common)
+    if name == 'QEinsumDenseBatchnorm':
+        return OracleQEinsumDenseBatchnorm(layer.fused_kernel_equation, layer._reduction_axes, layer._norm_offset_cast_shape, gamma,
+                                           mm, mv, layer.momentum, equation=layer.equation, kernel=_np(layer._kernel),
+                                           bias=_np(layer._bias), full_output_shape=layer.full_output_shape,
+                                           n_parallel=layer.n_parallel, parallelization_factor=layer.parallelization_factor, **common)
+    raise NotImplementedError(name)

@@ -75,6 +75,18 @@ def _worker(rank, world, port, out):
         assert fpq.absmax_sync_hook is None
         assert torch.equal(synced, X.abs().amax(0, keepdim=True))
         assert torch.equal(same, stat)
+        # synchronised batch moments: each rank's shard yields the moments of the whole batch, gradients included
+        from hgq2_b200.backend import moments
+
+        xs = X[sl].clone().requires_grad_()
+        m, v = moments(xs, (0,), synchronized=True)
+        (m.sum() + (v * torch.arange(1.0, 5.0)).sum()).backward()
+        xf = X.clone().requires_grad_()
+        mf, vf = moments(xf, (0,))
+        (mf.sum() + (vf * torch.arange(1.0, 5.0)).sum()).backward()
+        assert torch.allclose(m, mf, atol=1e-6) and torch.allclose(v, vf, atol=1e-6)
+        # the full-batch loss is counted once per rank here, hence the factor world on the shard's gradient
+        assert torch.allclose(xs.grad, xf.grad[sl] * world, atol=1e-6)
         out.put((rank, 'ok'))
     except Exception as e:  # surface the failure in the parent
         import traceback
