@@ -547,6 +547,52 @@ def run_qdense_bwd(args):
                       'achieved_GBs': round(gbs, 1), 'peak_GBs': peak, 'frac': round(gbs / peak, 4), 'peak_source': kind}), flush=True)
 
 
+def run_qconv(args):
+    """Kernel-level benchmark of the three convolution passes (forward, input gradient, weight gradient) on one layer of
+    the small CNN (--layer 1..3: 32x32x4 -> 16, 15x15x16 -> 32, 6x6x32 -> 64 filters, 3x3 'valid', ReLU).
+    Algorithmic bytes per output pixel: forward 4 (C' + N) with C' the input bytes per output pixel (H W C / (OH OW));
+    input gradient 4 (N + C'); weight gradient 4 (3 N + C') (dY, y in; masked gradient out; image in)."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    B = args.batch or 4096
+    H, C, N = {1: (32, 4, 16), 2: (15, 16, 32), 3: (6, 32, 64)}[args.layer]
+    OH = H - 2
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randint(0, 32, (B, H, H, C), device=dev, generator=gen).float() / 32.0  # 5-bit activations: exact in bf16
+    w = torch.randint(-64, 64, (3, 3, C, N), device=dev, generator=gen).float() / 64.0
+    bq = torch.randint(-8, 8, (N,), device=dev, generator=gen).float() / 8.0
+    gy = torch.randn(B, OH, OH, N, device=dev, generator=gen)
+    wt = w.flip(0, 1).permute(0, 1, 3, 2).reshape(9 * N, C).contiguous()
+    y = kernels.qconv2d_fwd(x, w.reshape(-1, N), bq, 'relu', 3, 3, (OH, OH), (1, 1), (1, 1), (0, 0))
+    passes = {
+        'forward': (lambda: kernels.qconv2d_fwd(x, w.reshape(-1, N), bq, 'relu', 3, 3, (OH, OH), (1, 1), (1, 1), (0, 0)),
+                    4.0 * (H * H * C + OH * OH * N)),
+        'input_gradient': (lambda: kernels.qconv2d_fwd(gy, wt, None, None, 3, 3, (H, H), (1, 1), (1, 1), (2, 2)),
+                           4.0 * (H * H * C + OH * OH * N)),
+        'weight_gradient': (lambda: kernels.qconv2d_wgrad(x, gy, y, 3, 3, (1, 1), (1, 1), (0, 0), True),
+                            4.0 * (H * H * C + 3 * OH * OH * N)),
+    }
+    peak, kind = measured_peaks()
+    out = {'kernel': 'qconv', 'layer': args.layer, 'batch': B, 'shape': [H, H, C, N], 'peak_GBs': peak, 'peak_source': kind}
+    for name, (fn, bytes_per_sample) in passes.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        kernels.check_status(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        gbs = bytes_per_sample * B / (ms * 1e-3) / 1e9
+        out[name] = {'ms': round(ms, 4), 'achieved_GBs': round(gbs, 1), 'frac': round(gbs / peak, 4)}
+    print(json.dumps(out), flush=True)
+
+
 def run_qsoftmax(args):
     """Kernel-level benchmark of the fused quantised softmax (forward and backward) on the attention-score tensor of the
     transformer block: [batch, 4 heads, 64, 64] scores, softmax over the last axis, output bitwidth table [4 * 64, 64].
@@ -597,8 +643,9 @@ def main():
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
     ap.add_argument('--model', default='particle_tagger', help='model of --workload qat')
     ap.add_argument('--batch', type=int, default=0, help='batch of --workload qat (0 = the benchmark batch)')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qsoftmax', 'qat'],
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qsoftmax', 'qconv', 'qat'],
                     help="'qdense' times the fused dense forward kernel alone (for profiler captures)")
+    ap.add_argument('--layer', type=int, default=1, choices=[1, 2, 3], help='convolution layer of --workload qconv')
     ap.add_argument('--rows', type=int, default=1 << 22)
     ap.add_argument('--k', type=int, default=64)
     ap.add_argument('--n', type=int, default=64)
@@ -611,6 +658,8 @@ def main():
         return run_qat_single(args)
     if args.workload == 'qdense_bwd':
         return run_qdense_bwd(args)
+    if args.workload == 'qconv':
+        return run_qconv(args)
     if args.workload == 'qsoftmax':
         return run_qsoftmax(args)
     if args.impl == 'reference':

@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
 
     // ---- set-up -------------------------------------------------------------------------------------------------------
     if (tid == 0) {
-        tc::mbar_init(bar, 1);
+        tc::mbar_init(bar, (uint32_t)MB);  // one issuing thread per 128-position block commits to it
         tc::mbar_init_fence();
     }
     if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
@@ -164,19 +164,21 @@ __global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
         tc::fence_smem_to_async();
         const int n_x = __syncthreads_or(lo_any) ? 2 : 1;
         // ---- tensor cores: every 128-position block x every K step x the term pairs ------------------------------------------
-        if (tid == 0) {
+        // lane 0 of warps 0 .. MB-1 each issue the MMAs of one 128-position block (its own accumulator): a single issuing
+        // thread would be the critical path while the whole CTA waits
+        if (lane == 0 && warp < MB) {
             tc::fence_after_sync();
-            for (int mb = 0; mb < MB; ++mb) {
-                bool first = true;
-                for (int s = 0; s < nsteps; ++s) {
-                    const int2 so = steps[s];
-                    for (int tx = 0; tx < n_x; ++tx) {
-                        const uint64_t da = tc::make_smem_desc(img_base + tx * img_term_bytes + so.x + mb * 2048, (uint32_t)so.y, 128);
-                        for (int tw = 0; tw < n_w; ++tw) {
-                            const uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes + s * w_step_bytes, 128, 256);
-                            tc::mma_bf16(tmem_base + (uint32_t)(mb * Np), da, db, idesc, !first);
-                            first = false;
-                        }
+            const int mb = warp;
+            const uint32_t acc = tmem_base + (uint32_t)(mb * Np);
+            bool first = true;
+            for (int s = 0; s < nsteps; ++s) {
+                const int2 so = steps[s];
+                for (int tx = 0; tx < n_x; ++tx) {
+                    const uint64_t da = tc::make_smem_desc(img_base + tx * img_term_bytes + so.x + mb * 2048, (uint32_t)so.y, 128);
+                    for (int tw = 0; tw < n_w; ++tw) {
+                        const uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes + s * w_step_bytes, 128, 256);
+                        tc::mma_bf16(acc, da, db, idesc, !first);
+                        first = false;
                     }
                 }
             }

@@ -271,6 +271,272 @@ __global__ void __launch_bounds__(kThreads) k_cw_stage2(const float *__restrict_
     if (sub == 0 && e < n) out[e] = (float)acc;
 }
 
+
+// ---- unit-stride variant: shifted windows of one staged image -------------------------------------------------------------
+// With the padded images of the batch viewed as one line of pixels q (row pitch Wp, see the forward kernel), the weight
+// gradient of tap (kh, kw) is  dW[kh, kw, c, n] = sum_q X[q + kh dil_h Wp + kw dil_w, c] * G[q, n]  with G zero at
+// positions that are not outputs.  X and G of Pt consecutive positions are staged once as [term][group of 8
+// channels][pixel] x 16 bytes, which is the MN-major core-matrix layout with the pixels as the contraction index.  The
+// 128 rows of one A operand are "16 consecutive horizontal shifts x 8 channels": the stride between row groups is one
+// pixel (16 dil_w bytes), so a single descriptor yields all KW taps of a kernel row at once (rows of shifts >= KW are
+// computed and ignored).  One accumulator per (kh, channel group) in tensor memory, kept across the tiles of the CTA.
+struct CsParams {
+    const float *x, *gy, *y;
+    float *gm, *part;
+    unsigned *status;
+    int64_t Q, num_tiles;
+    int H, W, C, N, Np, OH, OW, Hp, Wp, KH, KW, dh, dw, pt, pl;
+    int ncg, ng, Pt, npx, stack;
+};
+
+__global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int Np = P.Np, ncg = P.ncg, ng = P.ng, Pt = P.Pt, npx = P.npx, N = P.N;
+    const int cg_bytes = npx * 16, img_term = ncg * cg_bytes;
+    const int gg_bytes = Pt * 16, g_term = ng * gg_bytes;
+    unsigned char *IMG = smem;
+    unsigned char *GS = IMG + 2 * img_term;
+    float *red = reinterpret_cast<float *>(GS + 2 * g_term);           // [256][8] bias-gradient partials
+    uint64_t *bar = reinterpret_cast<uint64_t *>(red + kCwThreads * 8);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_acc = P.KH * ncg;
+    const int acc_cols = P.stack ? 2 * Np : Np;
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < n_acc * acc_cols) tmem_cols <<= 1;
+    if (tid == 0) {
+        tc::mbar_init(bar, (uint32_t)P.KH);  // one issuing thread per kernel row commits to it
+        tc::mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t idesc = tc::make_idesc_bf16(acc_cols, true, true);
+    const uint32_t img_base = tc::smem_u32(IMG), g_base = tc::smem_u32(GS);
+    const int HWp = P.Hp * P.Wp;
+    const bool half_group = (P.C & 7) != 0;
+    const bool relu = P.y != nullptr;
+    const int n_units_x = npx * ncg, n_units_g = Pt * ng;
+    const int my_g = tid % ng;  // kCwThreads is a multiple of ng: a thread always stages the same 8 output channels
+    float db_r[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) db_r[j] = 0.f;
+
+    uint32_t phase = 0;
+    bool ok = true, first_tile = true;
+    for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
+        const int64_t q0 = tile * Pt;
+        int lo_any = 0;
+        // ---- image pixels q0 .. q0 + npx ------------------------------------------------------------------------------------
+        for (int u0 = tid; u0 < n_units_x; u0 += 4 * kCwThreads) {
+            float4 v[4][2];
+            int dst[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int u = u0 + i * kCwThreads;
+                v[i][0] = v[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                dst[i] = -1;
+                if (u < n_units_x) {
+                    const int p = u / ncg, cg = u - p * ncg;
+                    dst[i] = cg * cg_bytes + p * 16;
+                    const int64_t q = q0 + p;
+                    if (q < P.Q) {
+                        const int b = (int)((uint32_t)q / (uint32_t)HWp);
+                        const int rem = (int)((uint32_t)q - (uint32_t)b * (uint32_t)HWp);
+                        const int yp = rem / P.Wp, xp = rem - yp * P.Wp;
+                        const int ih = yp - P.pt, iw = xp - P.pl;
+                        if ((unsigned)ih < (unsigned)P.H && (unsigned)iw < (unsigned)P.W) {
+                            const float *src = P.x + (((int64_t)b * P.H + ih) * P.W + iw) * P.C + cg * 8;
+                            v[i][0] = __ldg(reinterpret_cast<const float4 *>(src));
+                            if (!half_group || cg + 1 < ncg) v[i][1] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (dst[i] < 0) continue;
+                uint32_t hi[4], lo[4];
+                cw_split2(v[i][0].x, v[i][0].y, hi[0], lo[0]);
+                cw_split2(v[i][0].z, v[i][0].w, hi[1], lo[1]);
+                cw_split2(v[i][1].x, v[i][1].y, hi[2], lo[2]);
+                cw_split2(v[i][1].z, v[i][1].w, hi[3], lo[3]);
+                lo_any |= ((lo[0] | lo[1] | lo[2] | lo[3]) & 0x7fff7fffu) != 0;
+                *reinterpret_cast<uint4 *>(IMG + dst[i]) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4 *>(IMG + img_term + dst[i]) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+        }
+        // ---- G = dY (* relu mask) at the output positions, zero elsewhere; masked gradient out -----------------------------------
+        for (int u = tid; u < n_units_g; u += kCwThreads) {
+            const int p = u / ng;  // u % ng == my_g
+            const int64_t q = q0 + p;
+            float g[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] = 0.f;
+            const int n0 = my_g * 8;
+            if (q < P.Q && n0 < N) {
+                const int b = (int)((uint32_t)q / (uint32_t)HWp);
+                const int rem = (int)((uint32_t)q - (uint32_t)b * (uint32_t)HWp);
+                const int yp = rem / P.Wp, xp = rem - yp * P.Wp;
+                if (yp < P.OH && xp < P.OW) {
+                    const int64_t o = (((int64_t)b * P.OH + yp) * P.OW + xp) * N + n0;
+                    const bool second = n0 + 4 < N;  // N % 4 == 0 (checked on the host)
+                    const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.gy + o));
+                    const float4 a1 = second ? __ldcs(reinterpret_cast<const float4 *>(P.gy + o + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    g[0] = a0.x; g[1] = a0.y; g[2] = a0.z; g[3] = a0.w; g[4] = a1.x; g[5] = a1.y; g[6] = a1.z; g[7] = a1.w;
+                    if (relu) {
+                        const float4 y0 = __ldcs(reinterpret_cast<const float4 *>(P.y + o));
+                        const float4 y1 = second ? __ldcs(reinterpret_cast<const float4 *>(P.y + o + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        const float yy[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) g[j] = yy[j] > 0.f ? g[j] : 0.f;
+                        *reinterpret_cast<float4 *>(P.gm + o) = make_float4(g[0], g[1], g[2], g[3]);
+                        if (second) *reinterpret_cast<float4 *>(P.gm + o + 4) = make_float4(g[4], g[5], g[6], g[7]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) db_r[j] = __fadd_rn(db_r[j], g[j]);
+                }
+            }
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) cw_split2(g[j], g[j + 1], hi[j >> 1], lo[j >> 1]);
+            const int off = my_g * gg_bytes + p * 16;
+            *reinterpret_cast<uint4 *>(GS + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4 *>(GS + g_term + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+        tc::fence_smem_to_async();
+        const int n_x = __syncthreads_or(lo_any) ? 2 : 1;
+        // Issue is spread over KH threads (lane 0 of warps 0 .. KH-1, one kernel row each): a single thread building
+        // descriptors and issuing every MMA of the tile would be the critical path while the whole CTA waits.
+        // An MMA is bound by reading its 128-row A operand (4 KB) from shared memory whatever N is, so both bf16 terms of G
+        // go through ONE MMA as 2 Np columns when tensor memory allows (`stack`; the term planes are contiguous, so one
+        // uniform group stride covers them); the two halves of the accumulator are added in the final epilogue.
+        if (lane == 0 && warp < P.KH) {
+            tc::fence_after_sync();
+            const int kh = warp;
+            const int n_b = P.stack ? 1 : 2;
+            const uint64_t db0 = tc::make_smem_desc(g_base, 128, (uint32_t)gg_bytes);
+            for (int cg = 0; cg < ncg; ++cg) {
+                const uint32_t acc = tmem_base + (uint32_t)((kh * ncg + cg) * acc_cols);
+                const uint64_t da0 = tc::make_smem_desc(img_base + cg * cg_bytes + kh * P.dh * P.Wp * 16, 128, (uint32_t)(16 * P.dw));
+                bool first = first_tile;
+                for (int tx = 0; tx < n_x; ++tx)
+                    for (int tg = 0; tg < n_b; ++tg) {
+                        // the start-address field counts 16-byte units: + 16 per K step of 16 pixels (256 bytes)
+                        uint64_t da = da0 + (uint64_t)((tx * img_term) >> 4);
+                        uint64_t db = db0 + (uint64_t)((tg * g_term) >> 4);
+#pragma unroll 4
+                        for (int ks = 0; ks < Pt / 16; ++ks) {
+                            tc::mma_bf16(acc, da, db, idesc, !first);
+                            first = false;
+                            da += 16;
+                            db += 16;
+                        }
+                    }
+            }
+            tc::commit(bar);
+        }
+        first_tile = false;
+        const bool waited = (warp == 0) ? tc::mbar_wait(bar, phase) : true;
+        phase ^= 1u;
+        ok = __syncthreads_and(waited ? 1 : 0) != 0;
+    }
+    if (!ok && tid == 0 && P.status) atomicOr(P.status, 1u);
+
+    // ---- per-CTA partial: rows (tap, channel) of dWq, then dbq -----------------------------------------------------------------
+    const int K = P.KH * P.KW * P.C;
+    float *pw = P.part + (int64_t)blockIdx.x * ((int64_t)(K + 1) * N);
+    if (ok) {
+        tc::fence_after_sync();
+        const int qlane = (warp & 3) * 32, half = warp >> 2;
+        const int ncol = Np >> 1;
+        const int m = qlane + lane, kw = m >> 3, c8 = m & 7;  // accumulator row = (horizontal shift, channel in group)
+        for (int kh = 0; kh < P.KH; ++kh)
+            for (int cg = 0; cg < ncg; ++cg) {
+                const int c = cg * 8 + c8;
+                const bool live = kw < P.KW && c < P.C;
+                const int64_t krow = (int64_t)((kh * P.KW + kw) * P.C + c) * N;
+                for (int c0 = half * ncol; c0 < (half + 1) * ncol; c0 += 8) {
+                    float v[8];
+                    tc::tmem_ld8v(tmem_base + ((uint32_t)qlane << 16) + (uint32_t)((kh * ncg + cg) * acc_cols + c0), v);
+                    if (P.stack) {
+                        float v2[8];
+                        tc::tmem_ld8v(tmem_base + ((uint32_t)qlane << 16) + (uint32_t)((kh * ncg + cg) * acc_cols + Np + c0), v2);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = __fadd_rn(v[j], v2[j]);
+                    }
+                    if (live)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (c0 + j < N) pw[krow + c0 + j] = v[j];
+                }
+            }
+    } else {
+        for (int e = tid; e < K * N; e += kCwThreads) pw[e] = 0.f;
+    }
+    // bias gradient: threads with the same channel group are summed in a fixed order
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[tid * 8 + j] = db_r[j];
+    __syncthreads();
+    if (tid < ng * 8) {
+        const int g = tid >> 3, j = tid & 7;
+        float a = 0.f;
+        for (int t = g; t < kCwThreads; t += ng) a = __fadd_rn(a, red[t * 8 + j]);
+        if (g * 8 + j < N) pw[(int64_t)K * N + g * 8 + j] = a;
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+struct CsGeom {
+    int Np, Hp, Wp, ncg, ng, Pt, npx, grid, stack;
+    size_t smem;
+    int64_t Q, tiles;
+};
+
+static int cs_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW, int dh, int dw, CsGeom &g) {
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || KH <= 0 || KW <= 0 || N <= 0 || OH <= 0 || OW <= 0) return HGQ_ERR_SIZE;
+    if (C % 4 != 0 || N % 4 != 0 || N > 128 || KW > 16) return HGQ_ERR_SIZE;
+    g.Np = 16;
+    while (g.Np < N) g.Np <<= 1;
+    g.ng = g.Np / 8;
+    g.ncg = (C + 7) / 8;
+    if (KH * g.ncg * g.Np > 512) return HGQ_ERR_SIZE;
+    g.Hp = OH + (KH - 1) * dh;
+    g.Wp = OW + (KW - 1) * dw;
+    g.Q = B * g.Hp * g.Wp;
+    if (g.Q >= ((int64_t)1 << 31) || B * H * W * C >= ((int64_t)1 << 31)) return HGQ_ERR_SIZE;
+    const int reach = (KH - 1) * dh * g.Wp + 15 * dw;  // furthest pixel an operand row may read beyond its own position
+    g.Pt = 0;
+    for (int pt = 512; pt >= 128; pt >>= 1) {
+        const int npx = (pt + reach + 7) / 8 * 8;
+        const size_t sm = 2 * (size_t)g.ncg * npx * 16 + 2 * (size_t)g.ng * pt * 16 + (size_t)kCwThreads * 32 + 64;
+        if (sm <= 100 * 1024 || pt == 128) {
+            g.Pt = pt; g.npx = npx; g.smem = sm;
+            break;
+        }
+    }
+    if (g.smem > 226 * 1024) return HGQ_ERR_SIZE;
+    if (16 * dw >= (1 << 18)) return HGQ_ERR_SIZE;
+    g.tiles = (g.Q + g.Pt - 1) / g.Pt;
+    int per_sm = (int)((228 * 1024) / (g.smem + 1024));
+    if (per_sm > 3) per_sm = 3;
+    g.stack = (KH * g.ncg * 2 * g.Np <= 512 && 2 * g.Np <= 256) ? 1 : 0;
+    int tm = 32;
+    while (tm < KH * g.ncg * g.Np * (g.stack ? 2 : 1)) tm <<= 1;
+    if (per_sm * tm > 512) per_sm = 512 / tm;
+    if (per_sm < 1) return HGQ_ERR_SIZE;
+    int64_t grid = (int64_t)kNumSMs * per_sm;
+    if (grid > g.tiles) grid = g.tiles;
+    g.grid = (int)grid;
+    return HGQ_OK;
+}
+
 struct CwGeom {
     int Np, nkb, grid;
     size_t smem;
@@ -307,8 +573,9 @@ using namespace hgq;
 
 extern "C" size_t hgq_qconv2d_wgrad_workspace(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW) {
     CwGeom g;
-    if (cw_geom(B, H, W, C, KH, KW, N, OH, OW, g) != HGQ_OK) return 0;
-    return (size_t)2 * kNumSMs * ((size_t)KH * KW * C + 1) * N * sizeof(float);
+    CsGeom gs;
+    if (cw_geom(B, H, W, C, KH, KW, N, OH, OW, g) != HGQ_OK && cs_geom(B, H, W, C, KH, KW, N, OH, OW, 1, 1, gs) != HGQ_OK) return 0;
+    return (size_t)3 * kNumSMs * ((size_t)KH * KW * C + 1) * N * sizeof(float);
 }
 
 extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y, float *gm, float *dwq, float *dbq, int64_t B,
@@ -317,13 +584,38 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
                                  unsigned *status, void *stream) {
     if (x == nullptr || gy == nullptr || dwq == nullptr) return HGQ_ERR_NULL;
     if ((y == nullptr) != (gm == nullptr)) return HGQ_ERR_NULL;
-    CwGeom g;
-    if (int e = cw_geom(B, H, W, C, KH, KW, N, OH, OW, g)) return e;
     if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0) return HGQ_ERR_SIZE;
     if (KH * dil_h > 127 || KW * dil_w > 127 || pad_top < 0 || pad_left < 0) return HGQ_ERR_SIZE;
     if (!aligned(x, 16)) return HGQ_ERR_ALIGN;
     const int K = KH * KW * C;
     const int64_t stride = (int64_t)(K + 1) * N;
+    cudaStream_t st = (cudaStream_t)stream;
+    CsGeom gs;
+    if (stride_h == 1 && stride_w == 1 && aligned(gy, 16) && (y == nullptr || (aligned(y, 16) && aligned(gm, 16))) &&
+        cs_geom(B, H, W, C, KH, KW, N, OH, OW, dil_h, dil_w, gs) == HGQ_OK) {
+        const size_t need_s = (size_t)gs.grid * stride * sizeof(float);
+        if (workspace == nullptr || workspace_bytes < need_s) return HGQ_ERR_WORKSPACE;
+        CsParams q;
+        q.x = x; q.gy = gy; q.y = y; q.gm = gm; q.part = (float *)workspace; q.status = status;
+        q.Q = gs.Q; q.num_tiles = gs.tiles;
+        q.H = H; q.W = W; q.C = C; q.N = N; q.Np = gs.Np; q.OH = OH; q.OW = OW; q.Hp = gs.Hp; q.Wp = gs.Wp;
+        q.KH = KH; q.KW = KW; q.dh = dil_h; q.dw = dil_w; q.pt = pad_top; q.pl = pad_left;
+        q.ncg = gs.ncg; q.ng = gs.ng; q.Pt = gs.Pt; q.npx = gs.npx; q.stack = gs.stack;
+        cudaError_t ce = cudaFuncSetAttribute(k_qconv_wgrad_s1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_qconv_wgrad_s1<<<gs.grid, kCwThreads, gs.smem, st>>>(q);
+        if (int e = check_launch()) return e;
+        const int64_t nw = (int64_t)K * N;
+        k_cw_stage2<<<(unsigned)((nw + 63) / 64), kThreads, 0, st>>>(q.part, stride, 0, dwq, nw, gs.grid);
+        if (int e = check_launch()) return e;
+        if (dbq != nullptr) {
+            k_cw_stage2<<<(unsigned)((N + 63) / 64), kThreads, 0, st>>>(q.part, stride, nw, dbq, N, gs.grid);
+            if (int e = check_launch()) return e;
+        }
+        return HGQ_OK;
+    }
+    CwGeom g;
+    if (int e = cw_geom(B, H, W, C, KH, KW, N, OH, OW, g)) return e;
     const size_t need = (size_t)g.grid * stride * sizeof(float);
     if (workspace == nullptr || workspace_bytes < need) return HGQ_ERR_WORKSPACE;
     CwParams p;
@@ -331,7 +623,6 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
     p.M = g.M; p.num_tiles = g.tiles; p.K = K; p.N = N; p.Np = g.Np; p.nkb = g.nkb;
     p.H = H; p.W = W; p.C = C; p.OH = OH; p.OW = OW; p.KH = KH; p.KW = KW;
     p.sh = stride_h; p.sw = stride_w; p.dh = dil_h; p.dw = dil_w; p.pt = pad_top; p.pl = pad_left;
-    cudaStream_t st = (cudaStream_t)stream;
     cudaError_t ce = cudaFuncSetAttribute(k_qconv_wgrad, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
     if (ce != cudaSuccess) return (int)ce;
     k_qconv_wgrad<<<g.grid, kCwThreads, g.smem, st>>>(p);

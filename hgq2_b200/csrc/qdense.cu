@@ -278,8 +278,9 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const uint32_t sbits = (((j < 4 ? eb.x : eb.y) >> ((j & 3) * 8)) & 0xffu) << 23;  // 2^f
-                            const float xs = __fmul_rn(xv[it][j], __uint_as_float(sbits));
-                            const float q = CONV ? rintf(xs) : floorf(__fadd_rn(xs, rbias));
+                            // scaling by a power of two is exact, so one fused multiply-add gives RN(x * 2^f + bias) bit for bit
+                            const float q = CONV ? rintf(__fmul_rn(xv[it][j], __uint_as_float(sbits)))
+                                                 : floorf(__fmaf_rn(xv[it][j], __uint_as_float(sbits), rbias));
                             xv[it][j] = __fmul_rn(q, __uint_as_float(0x7F000000u - sbits));  // * 2^-f
                         }
                     } else {

@@ -54,8 +54,8 @@ __device__ __forceinline__ void split2_pair(float v0, float v1, uint32_t &hi, ui
 template <bool CONV>
 __device__ __forceinline__ float round_e(float v, uint32_t ebyte, float rbias) {
     const uint32_t sbits = ebyte << 23;  // 2^f
-    const float xs = __fmul_rn(v, __uint_as_float(sbits));
-    const float q = CONV ? rintf(xs) : floorf(__fadd_rn(xs, rbias));
+    // scaling by a power of two is exact, so one fused multiply-add gives RN(v * 2^f + bias) bit for bit
+    const float q = CONV ? rintf(__fmul_rn(v, __uint_as_float(sbits))) : floorf(__fmaf_rn(v, __uint_as_float(sbits), rbias));
     return __fmul_rn(q, __uint_as_float(0x7F000000u - sbits));
 }
 
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
 
     // ---- set-up -------------------------------------------------------------------------------------------------
     if (tid == 0) {
-        tc::mbar_init(bar, 1);
+        tc::mbar_init(bar, 2);  // two issuing threads (one per product) commit to it
         tc::mbar_init_fence();
     }
     if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
@@ -302,27 +302,39 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
         tc::fence_smem_to_async();
         __syncthreads();
         // ---- tensor cores -------------------------------------------------------------------------------------------
+        // The two products are issued by two threads (lane 0 of warps 0 and 1) with descriptors advanced by addition: one
+        // thread building every descriptor from scratch is a serial critical path while the CTA waits.
         if (tid == 0) {
             tc::fence_after_sync();
-            // MMA1: dXq = G x Wq^T, contraction over n in steps of 16
+            // MMA1: dXq = G x Wq^T, contraction over n in steps of 16 (start address + 256 bytes = + 16 units per step)
             bool first = true;
-            for (int s = 0; s < Np / 16; ++s)
-                for (int tg = 0; tg < 2; ++tg) {
-                    const uint64_t da = tc::make_smem_desc(g_base + tg * g_term_bytes + s * 256, 128, (uint32_t)CGn * 128);
-                    for (int tw = 0; tw < n_w; ++tw) {
-                        const uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes + s * 256, 128, (uint32_t)CGn * 128);
+            for (int tg = 0; tg < 2; ++tg)
+                for (int tw = 0; tw < n_w; ++tw) {
+                    uint64_t da = tc::make_smem_desc(g_base + tg * g_term_bytes, 128, (uint32_t)CGn * 128);
+                    uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes, 128, (uint32_t)CGn * 128);
+                    for (int s = 0; s < Np / 16; ++s) {
                         tc::mma_bf16(acc1, da, db, idesc1, !first);
                         first = false;
+                        da += 16;
+                        db += 16;
                     }
                 }
+            tc::commit(bar);
+        } else if (tid == 32) {
+            tc::fence_after_sync();
             // MMA2: dWq (+ dbq row) += xq^T x G, contraction over the 128 rows in steps of 16; both operands MN-major:
             // stride between 8-groups along M/N = 128 B (sbo), between 8-groups along the rows = one buffer row (lbo)
-            for (int s = 0; s < kQbTileM / 16; ++s)
-                for (int tx = 0; tx < 2; ++tx) {
-                    const uint64_t da = tc::make_smem_desc(x_base + tx * kQbXTermBytes + s * (2 * 16 * 128), 16 * 128, 128);
-                    for (int tg = 0; tg < 2; ++tg) {
-                        const uint64_t db = tc::make_smem_desc(g_base + tg * g_term_bytes + s * (2 * CGn * 128), (uint32_t)CGn * 128, 128);
-                        tc::mma_bf16(acc2, da, db, idesc2, !(first_tile && s == 0 && tx == 0 && tg == 0));
+            bool first = first_tile;
+            const uint32_t a_step = (2 * 16 * 128) >> 4, b_step = (uint32_t)(2 * CGn * 128) >> 4;
+            for (int tx = 0; tx < 2; ++tx)
+                for (int tg = 0; tg < 2; ++tg) {
+                    uint64_t da = tc::make_smem_desc(x_base + tx * kQbXTermBytes, 16 * 128, 128);
+                    uint64_t db = tc::make_smem_desc(g_base + tg * g_term_bytes, (uint32_t)CGn * 128, 128);
+                    for (int s = 0; s < kQbTileM / 16; ++s) {
+                        tc::mma_bf16(acc2, da, db, idesc2, !first);
+                        first = false;
+                        da += a_step;
+                        db += b_step;
                     }
                 }
             tc::commit(bar);
@@ -363,7 +375,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
                         const float4 d1 = *reinterpret_cast<const float4 *>(dstash + r * Kd + kb + 4);
                         const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) df_r[ci * 8 + j] = __fadd_rn(df_r[ci * 8 + j], __fmul_rn(d[j], v[ci * 8 + j]));
+                        for (int j = 0; j < 8; ++j) df_r[ci * 8 + j] = fmaf(d[j], v[ci * 8 + j], df_r[ci * 8 + j]);
                     }
                 }
             }
