@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < Kp + Np) tmem_cols <<= 1;
+    while ((int)tmem_cols < Kp + 2 * Np) tmem_cols <<= 1;  // dXq | dWq from the hi and the lo term of G
 
     // ---- set-up -------------------------------------------------------------------------------------------------
     if (tid == 0) {
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t acc1 = tmem_base, acc2 = tmem_base + (uint32_t)Kp;
     const uint32_t idesc1 = tc::make_idesc_bf16(Kp, false, false);
-    const uint32_t idesc2 = tc::make_idesc_bf16(Np, true, true);
+    const uint32_t idesc2 = tc::make_idesc_bf16(2 * Np, true, true);
     const uint32_t g_base = tc::smem_u32(G), x_base = tc::smem_u32(X), w_base = tc::smem_u32(W);
 
     const int r8 = lane & 7, q4 = lane >> 3;
@@ -227,9 +227,11 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
         uint32_t hi[4], lo[4];
 #pragma unroll
         for (int j = 0; j < 8; j += 2) split2_pair(gv[slot][j], gv[slot][j + 1], hi[j >> 1], lo[j >> 1]);
-        const int off = (mg * CGn + kg) * 128 + r8 * 16;
+        // core (row group, term, column group): the two terms of a row group are adjacent, so MMA2 takes both as one
+        // operand of 2 Np columns with a uniform 128-byte group stride
+        const int off = (mg * 2 * CGn + kg) * 128 + r8 * 16;
         *reinterpret_cast<uint4 *>(G + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4 *>(G + g_term_bytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4 *>(G + CGn * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     };
     auto load_x = [&](int u, int64_t t_row0) {
         const int c = u * 16 + warp;
@@ -310,7 +312,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
             bool first = true;
             for (int tg = 0; tg < 2; ++tg)
                 for (int tw = 0; tw < n_w; ++tw) {
-                    uint64_t da = tc::make_smem_desc(g_base + tg * g_term_bytes, 128, (uint32_t)CGn * 128);
+                    uint64_t da = tc::make_smem_desc(g_base + tg * CGn * 128, 128, (uint32_t)CGn * 256);
                     uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes, 128, (uint32_t)CGn * 128);
                     for (int s = 0; s < Np / 16; ++s) {
                         tc::mma_bf16(acc1, da, db, idesc1, !first);
@@ -325,18 +327,19 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
             // MMA2: dWq (+ dbq row) += xq^T x G, contraction over the 128 rows in steps of 16; both operands MN-major:
             // stride between 8-groups along M/N = 128 B (sbo), between 8-groups along the rows = one buffer row (lbo)
             bool first = first_tile;
-            const uint32_t a_step = (2 * 16 * 128) >> 4, b_step = (uint32_t)(2 * CGn * 128) >> 4;
-            for (int tx = 0; tx < 2; ++tx)
-                for (int tg = 0; tg < 2; ++tg) {
-                    uint64_t da = tc::make_smem_desc(x_base + tx * kQbXTermBytes, 16 * 128, 128);
-                    uint64_t db = tc::make_smem_desc(g_base + tg * g_term_bytes, (uint32_t)CGn * 128, 128);
-                    for (int s = 0; s < kQbTileM / 16; ++s) {
-                        tc::mma_bf16(acc2, da, db, idesc2, !first);
-                        first = false;
-                        da += a_step;
-                        db += b_step;
-                    }
+            // an MMA is bound by reading its 128-row A operand from shared memory whatever N is: both terms of G go through
+            // one MMA as 2 Np columns; the two halves of the accumulator are added when the partials are written
+            const uint32_t a_step = (2 * 16 * 128) >> 4, b_step = (uint32_t)(4 * CGn * 128) >> 4;
+            for (int tx = 0; tx < 2; ++tx) {
+                uint64_t da = tc::make_smem_desc(x_base + tx * kQbXTermBytes, 16 * 128, 128);
+                uint64_t db = tc::make_smem_desc(g_base, (uint32_t)CGn * 256, 128);
+                for (int s = 0; s < kQbTileM / 16; ++s) {
+                    tc::mma_bf16(acc2, da, db, idesc2, !first);
+                    first = false;
+                    da += a_step;
+                    db += b_step;
                 }
+            }
             tc::commit(bar);
         }
         first_tile = false;
@@ -414,8 +417,11 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
         const int r = qlane + lane;  // accumulator lane = k index (lane K holds dbq)
         const int ncol = Np >> 2;    // columns per thread
         for (int c0 = cpart * ncol; c0 < (cpart + 1) * ncol; c0 += 8) {
-            float v[8];
+            float v[8], v2[8];
             tc::tmem_ld8v(acc2 + ((uint32_t)qlane << 16) + (uint32_t)c0, v);
+            tc::tmem_ld8v(acc2 + ((uint32_t)qlane << 16) + (uint32_t)(Np + c0), v2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __fadd_rn(v[j], v2[j]);
             if (r <= K)
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
