@@ -453,14 +453,24 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-// out[e] = sum over CTAs of part[cta * stride + offset + e], in double, fixed order
-__global__ void __launch_bounds__(kThreads) k_qb_stage2(const float *__restrict__ part, int64_t stride, int64_t offset,
-                                                       float *__restrict__ out, int64_t n, int nparts) {
-    const int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (e >= n) return;
+// Sum of the per-CTA partials, in double and in a fixed order: element e of the partial vector [dWq | dbq | df] goes to
+// its own output array.  Eight elements per warp, four lanes per element walking the partials.
+__global__ void __launch_bounds__(kThreads) k_qb_stage2(const float *__restrict__ part, int64_t stride, int nparts,
+                                                       float *__restrict__ dw, int64_t nw, float *__restrict__ db, int64_t nb,
+                                                       float *__restrict__ df, int64_t nf) {
+    const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
+    const int64_t e = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * 8 + j;
+    const int64_t n = nw + nb + nf;
     double acc = 0.0;
-    for (int p = 0; p < nparts; ++p) acc += (double)part[(int64_t)p * stride + offset + e];
-    out[e] = (float)acc;
+    if (e < n)
+        for (int p = sub; p < nparts; p += 4) acc += (double)part[(int64_t)p * stride + e];
+    acc += __shfl_down_sync(0xffffffffu, acc, 16);
+    acc += __shfl_down_sync(0xffffffffu, acc, 8);
+    if (sub == 0 && e < n) {
+        if (e < nw) dw[e] = (float)acc;
+        else if (e < nw + nb) { if (db != nullptr) db[e - nw] = (float)acc; }
+        else if (df != nullptr) df[e - nw - nb] = (float)acc;
+    }
 }
 
 struct QbGeom {
@@ -528,18 +538,9 @@ extern "C" int hgq_qdense_bwd(const float *gy, const float *y, const float *x, c
         k_qdense_bwd<false><<<g.grid, kQbThreads, g.smem, st>>>(p);
     }
     if (int e = check_launch()) return e;
-    const int64_t nw = (int64_t)K * N;
-    k_qb_stage2<<<(unsigned)((nw + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, g.part_stride, 0, dwq, nw, g.grid);
+    const int64_t nw = (int64_t)K * N, nf = (int64_t)rows_period * K;
+    k_qb_stage2<<<(unsigned)((g.part_stride + 63) / 64), kThreads, 0, st>>>(p.part, g.part_stride, g.grid, dwq, nw, dbq, N,
+                                                                           df, df != nullptr ? nf : 0);
     if (int e = check_launch()) return e;
-    if (dbq != nullptr) {
-        k_qb_stage2<<<(unsigned)((N + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, g.part_stride, nw, dbq, N, g.grid);
-        if (int e = check_launch()) return e;
-    }
-    if (df != nullptr) {
-        const int64_t nf = (int64_t)rows_period * K;
-        k_qb_stage2<<<(unsigned)((nf + kThreads - 1) / kThreads), kThreads, 0, st>>>(p.part, g.part_stride, (int64_t)(K + 1) * N, df,
-                                                                                  nf, g.grid);
-        if (int e = check_launch()) return e;
-    }
     return HGQ_OK;
 }
