@@ -1,0 +1,250 @@
+// K6 (per-head products of multi-head attention on the tensor cores): the two activation-activation contractions of
+// QMultiHeadAttention._compute_attention (src/hgq/layers/attn/mha.py:434-470, einsum 'aecd,abcd->acbe' for the scores and
+// 'acbe,aecd->abcd' for the context) and the four products of their backward.
+//
+// Tensors: "SHD" = [B, L, H, D] (projections, context and their gradients: heads interleaved in memory), "HTS" =
+// [B, H, L, L] (scores, probabilities and their gradients), L = 64 positions, D = 16 or 32 per head.
+//   kind 0:  out_HTS[b,h,t,s] = sum_d  x_SHD[b,t,h,d] * y_SHD[b,s,h,d]        scores = Q K^T;   dP = dO V^T
+//   kind 1:  out_SHD[b,t,h,d] = sum_s  x_HTS[b,h,t,s] * y_SHD[b,s,h,d]        context = P V;    dQ = dS K
+//   kind 2:  out_SHD[b,s,h,d] = sum_t  x_HTS[b,h,t,s] * y_SHD[b,t,h,d]        dV = P^T dO;      dK = dS^T Q
+// A tile is one pair of heads of one sample: the A operand holds the 2 x 64 rows of both heads (the M = 128 of one
+// tcgen05.mma), and one product per head multiplies it with that head's B operand into its own accumulator; each
+// accumulator is valid in the 64 rows of its head (the other 64 rows are computed against the wrong head and dropped).
+// Operands are read strided straight from the [B, L, H, D] / [B, H, L, L] tensors (no transposed copies), split into
+// two bf16 terms (exact up to 16 significant bits: the quantised projections and probabilities; gradients are rounded
+// at 2^-17 relative) and stored as no-swizzle core matrices: K-major where the contraction index is contiguous in memory,
+// MN-major where the row / column index is.  HBM-bound: 4 (2 L D + L L) bytes per head and product.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "hgq_common.cuh"
+#include "tc05.cuh"
+
+namespace hgq {
+
+constexpr int kAtThreads = 256;
+constexpr int kAtL = 64;
+
+struct AtParams {
+    const float *x, *y;
+    float *out;
+    unsigned *status;
+    int64_t B, num_tiles;
+    int H, D;
+};
+
+__device__ __forceinline__ void at_split2(float v0, float v1, uint32_t &hi, uint32_t &lo) {
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+    hi = *reinterpret_cast<const uint32_t *>(&h2);
+    const float r0 = __fsub_rn(v0, __uint_as_float(hi << 16));
+    const float r1 = __fsub_rn(v1, __uint_as_float(hi & 0xffff0000u));
+    const __nv_bfloat162 l2 = __floats2bfloat162_rn(r0, r1);
+    lo = *reinterpret_cast<const uint32_t *>(&l2);
+}
+
+// eight consecutive floats -> one 16-byte row of a core matrix in each of the two term planes
+__device__ __forceinline__ int at_put8(const float *src, unsigned char *hi_plane, unsigned char *lo_plane, int off) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(src + 4));
+    uint32_t hi[4], lo[4];
+    at_split2(a.x, a.y, hi[0], lo[0]);
+    at_split2(a.z, a.w, hi[1], lo[1]);
+    at_split2(b.x, b.y, hi[2], lo[2]);
+    at_split2(b.z, b.w, hi[3], lo[3]);
+    *reinterpret_cast<uint4 *>(hi_plane + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4 *>(lo_plane + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    return ((lo[0] | lo[1] | lo[2] | lo[3]) & 0x7fff7fffu) != 0;
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int L = kAtL;
+    const int D = P.D, H = P.H, DG = D >> 3;
+    // operand geometry
+    const int Ka = (KIND == 0) ? D : L;          // contraction length
+    const int Nn = (KIND == 0) ? L : D;          // columns of a product
+    const int a_term = 128 * Ka * 2;             // A: 128 rows x Ka
+    const int b_term = Nn * Ka * 2;              // B of one head
+    unsigned char *A = smem;                     // [2 terms]
+    unsigned char *Bm = A + 2 * a_term;          // [2 heads][2 terms]
+    uint64_t *bar = reinterpret_cast<uint64_t *>(Bm + 4 * b_term);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < 2 * Nn) tmem_cols <<= 1;
+    if (tid == 0) {
+        tc::mbar_init(bar, 2);  // one issuing thread per head commits to it
+        tc::mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t a_base = tc::smem_u32(A), b_base = tc::smem_u32(Bm);
+    const uint32_t idesc = tc::make_idesc_bf16(Nn, KIND == 2, KIND != 0);
+    const int pairs = H >> 1;
+    const int64_t LL = (int64_t)L * L, row_shd = (int64_t)H * D;
+
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
+        const int64_t b = tile / pairs;
+        const int h0 = (int)(tile - b * pairs) * 2;
+        const float *x_shd = P.x + b * L * row_shd + (int64_t)h0 * D;   // kind 0: x[b, 0, h0, 0]
+        const float *x_hts = P.x + (b * H + h0) * LL;                   // kinds 1, 2: x[b, h0, 0, 0]
+        const float *y_shd = P.y + b * L * row_shd + (int64_t)h0 * D;
+        int lo_a = 0, lo_b = 0;
+        // ---- A operand: both heads ------------------------------------------------------------------------------------------
+        if (KIND == 0) {
+            // rows (hh, t), contraction d: K-major, core (row group, d group); unit = (t, hh, d group): a row of the pair is
+            // 2 D contiguous floats in memory
+            for (int u = tid; u < 128 * DG; u += kAtThreads) {
+                const int dg = u % DG, hh = (u / DG) & 1, t = u / (2 * DG);
+                const int row = hh * 64 + t;
+                lo_a |= at_put8(x_shd + t * row_shd + hh * D + dg * 8, A, A + a_term, ((row >> 3) * DG + dg) * 128 + (row & 7) * 16);
+            }
+        } else if (KIND == 1) {
+            // rows (hh, t), contraction s: K-major, core (row group, s group): a row is 64 contiguous floats
+            for (int u = tid; u < 128 * 8; u += kAtThreads) {
+                const int sg = u & 7, row = u >> 3;
+                lo_a |= at_put8(x_hts + (int64_t)row * L + sg * 8, A, A + a_term, ((row >> 3) * 8 + sg) * 128 + (row & 7) * 16);
+            }
+        } else {
+            // rows m = (hh, s), contraction t: MN-major, core (t group, m group) = 8 t x 8 m; a row t of a head is 64 contiguous s
+            for (int u = tid; u < 128 * 8; u += kAtThreads) {
+                const int sg = u & 7, t = (u >> 3) & 63, hh = u >> 9;
+                const int mg = hh * 8 + sg;
+                lo_a |= at_put8(x_hts + hh * LL + (int64_t)t * L + sg * 8, A, A + a_term, ((t >> 3) * 16 + mg) * 128 + (t & 7) * 16);
+            }
+        }
+        // ---- B operands: one per head -----------------------------------------------------------------------------------------
+        if (KIND == 0) {
+            // rows s (the product's columns), contraction d: K-major, core (s group, d group)
+            for (int u = tid; u < 128 * DG; u += kAtThreads) {
+                const int dg = u % DG, hh = (u / DG) & 1, s = u / (2 * DG);
+                unsigned char *base = Bm + hh * 2 * b_term;
+                lo_b |= at_put8(y_shd + s * row_shd + hh * D + dg * 8, base, base + b_term, ((s >> 3) * DG + dg) * 128 + (s & 7) * 16);
+            }
+        } else {
+            // columns d, contraction r (s or t): MN-major, core (r group, d group) = 8 r x 8 d
+            for (int u = tid; u < 128 * DG; u += kAtThreads) {
+                const int dg = u % DG, hh = (u / DG) & 1, r = u / (2 * DG);
+                unsigned char *base = Bm + hh * 2 * b_term;
+                lo_b |= at_put8(y_shd + r * row_shd + hh * D + dg * 8, base, base + b_term, ((r >> 3) * DG + dg) * 128 + (r & 7) * 16);
+            }
+        }
+        tc::fence_smem_to_async();
+        const int n_a = __syncthreads_or(lo_a) ? 2 : 1;
+        const int n_b = __syncthreads_or(lo_b) ? 2 : 1;
+        // ---- one issuing thread per head ------------------------------------------------------------------------------------------
+        if (lane == 0 && warp < 2) {
+            tc::fence_after_sync();
+            const int hh = warp;
+            const uint32_t acc = tmem_base + (uint32_t)(hh * Nn);
+            const uint32_t bb = b_base + hh * 2 * b_term;
+            bool first = true;
+            for (int ta = 0; ta < n_a; ++ta)
+                for (int tb = 0; tb < n_b; ++tb) {
+                    uint64_t da, db;
+                    uint32_t a_step, b_step;
+                    if (KIND == 0) {         // A, B K-major: cores adjacent along K 128 B apart, row groups DG * 128 apart
+                        da = tc::make_smem_desc(a_base + ta * a_term, 128, (uint32_t)DG * 128);
+                        db = tc::make_smem_desc(bb + tb * b_term, 128, (uint32_t)DG * 128);
+                        a_step = b_step = 256 >> 4;
+                    } else if (KIND == 1) {  // A K-major (8 s groups per row group); B MN-major: d groups 128 B apart, r groups DG * 128
+                        da = tc::make_smem_desc(a_base + ta * a_term, 128, 8 * 128);
+                        db = tc::make_smem_desc(bb + tb * b_term, (uint32_t)DG * 128, 128);
+                        a_step = 256 >> 4;
+                        b_step = (uint32_t)(2 * DG * 128) >> 4;
+                    } else {                 // A MN-major: m groups 128 B apart, t groups 16 * 128 apart
+                        da = tc::make_smem_desc(a_base + ta * a_term, 16 * 128, 128);
+                        db = tc::make_smem_desc(bb + tb * b_term, (uint32_t)DG * 128, 128);
+                        a_step = (2 * 16 * 128) >> 4;
+                        b_step = (uint32_t)(2 * DG * 128) >> 4;
+                    }
+                    for (int s = 0; s < Ka / 16; ++s) {
+                        tc::mma_bf16(acc, da, db, idesc, !first);
+                        first = false;
+                        da += a_step;
+                        db += b_step;
+                    }
+                }
+            tc::commit(bar);
+        }
+        const bool waited = (warp == 0) ? tc::mbar_wait(bar, phase) : true;
+        phase ^= 1u;
+        ok = __syncthreads_and(waited ? 1 : 0) != 0;
+        if (!ok) {
+            if (tid == 0 && P.status) atomicOr(P.status, 1u);
+            break;
+        }
+        // ---- epilogue: row r of the pair lives in accumulator r / 64 ------------------------------------------------------------
+        tc::fence_after_sync();
+        {
+            const int qlane = (warp & 3) * 32, half = warp >> 2;
+            const int r = qlane + lane, hh = r >> 6, i = r & 63;
+            const int ncol = Nn >> 1;  // columns per thread
+            float *dst = (KIND == 0) ? P.out + ((b * H + h0 + hh) * L + i) * L : P.out + (b * L + i) * row_shd + (int64_t)(h0 + hh) * D;
+            for (int c0 = half * ncol; c0 < (half + 1) * ncol; c0 += 8) {
+                float v[8];
+                tc::tmem_ld8v(tmem_base + ((uint32_t)qlane << 16) + (uint32_t)(hh * Nn + c0), v);
+                __stcs(reinterpret_cast<float4 *>(dst + c0), make_float4(v[0], v[1], v[2], v[3]));
+                __stcs(reinterpret_cast<float4 *>(dst + c0 + 4), make_float4(v[4], v[5], v[6], v[7]));
+            }
+        }
+        tc::fence_before_sync();
+        __syncthreads();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+static size_t at_smem(int kind, int D) {
+    const int Ka = kind == 0 ? D : kAtL, Nn = kind == 0 ? kAtL : D;
+    return 2 * (size_t)128 * Ka * 2 + 4 * (size_t)Nn * Ka * 2 + 64;
+}
+
+}  // namespace hgq
+
+using namespace hgq;
+
+extern "C" int hgq_attn_heads_supported(int64_t B, int L, int H, int D) {
+    return (B > 0 && L == kAtL && H > 0 && H % 2 == 0 && (D == 16 || D == 32)) ? 1 : 0;
+}
+
+extern "C" int hgq_attn_heads_matmul(int kind, const float *x, const float *y, float *out, int64_t B, int L, int H, int D,
+                                     unsigned *status, void *stream) {
+    if (x == nullptr || y == nullptr || out == nullptr) return HGQ_ERR_NULL;
+    if (kind < 0 || kind > 2) return HGQ_ERR_MODE;
+    if (!hgq_attn_heads_supported(B, L, H, D)) return HGQ_ERR_SIZE;
+    if (!aligned(x, 16) || !aligned(y, 16) || !aligned(out, 16)) return HGQ_ERR_ALIGN;
+    AtParams p;
+    p.x = x; p.y = y; p.out = out; p.status = status;
+    p.B = B; p.H = H; p.D = D;
+    p.num_tiles = B * (H / 2);
+    const size_t smem = at_smem(kind, D);
+    int per_sm = (int)((228 * 1024) / (smem + 1024));
+    if (per_sm > 4) per_sm = 4;  // 256 threads each; tensor memory: at most 128 columns per CTA
+    int64_t grid = (int64_t)kNumSMs * per_sm;
+    if (grid > p.num_tiles) grid = p.num_tiles;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t ce;
+    if (kind == 0) {
+        ce = cudaFuncSetAttribute(k_attn_heads<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_attn_heads<0><<<(unsigned)grid, kAtThreads, smem, st>>>(p);
+    } else if (kind == 1) {
+        ce = cudaFuncSetAttribute(k_attn_heads<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_attn_heads<1><<<(unsigned)grid, kAtThreads, smem, st>>>(p);
+    } else {
+        ce = cudaFuncSetAttribute(k_attn_heads<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_attn_heads<2><<<(unsigned)grid, kAtThreads, smem, st>>>(p);
+    }
+    return check_launch();
+}

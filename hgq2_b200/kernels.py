@@ -406,3 +406,20 @@ def maxpool2d_bwd(gy, arg, in_shape, pool, strides):
                                      stream_handle())
     check(st, 'hgq_maxpool2d_bwd')
     return dx
+
+
+def attn_heads_supported(B: int, L: int, H: int, D: int) -> bool:
+    return bool(lib().hgq_attn_heads_supported(B, L, H, D))
+
+
+def attn_heads_matmul(kind: int, x, y, B: int, L: int, H: int, D: int):
+    """Per-head attention products (see hgq_attn_heads_matmul).  kind 0: x, y [B, L, H, D] -> [B, H, L, L];
+    kinds 1, 2: x [B, H, L, L], y [B, L, H, D] -> [B, L, H, D]."""
+    require_cuda(x, y)
+    x, y = x.contiguous(), y.contiguous()
+    shape = (B, H, L, L) if kind == 0 else (B, L, H, D)
+    out = torch.empty(shape, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = lib().hgq_attn_heads_matmul(kind, ptr(x), ptr(y), ptr(out), B, L, H, D, ptr(status_word(x.device)), stream_handle())
+    check(st, 'hgq_attn_heads_matmul')
+    return out

@@ -239,6 +239,54 @@ def fused_conv2d_call(layer, xq, qkernel, qbias):
     return QConv2dFusedFn.apply(xq, qkernel, qbias, act_spec, tuple(layer.strides), tuple(layer.dilation_rate), (pt, pl), (OH, OW))
 
 
+class AttnScoresFn(torch.autograd.Function):
+    """scores[b, h, t, s] = sum_d q[b, t, h, d] k[b, s, h, d] on the per-head tensor-core kernel, with its backward."""
+
+    @staticmethod
+    def forward(ctx, key, query):
+        B, L, H, D = query.shape
+        ctx.save_for_backward(key, query)
+        return kernels.attn_heads_matmul(0, query, key, B, L, H, D)
+
+    @staticmethod
+    def backward(ctx, gs):
+        key, query = ctx.saved_tensors
+        B, L, H, D = query.shape
+        gs = gs.contiguous()
+        dq = kernels.attn_heads_matmul(1, gs, key, B, L, H, D) if ctx.needs_input_grad[1] else None     # dS K
+        dk = kernels.attn_heads_matmul(2, gs, query, B, L, H, D) if ctx.needs_input_grad[0] else None   # dS^T Q
+        return dk, dq
+
+
+class AttnContextFn(torch.autograd.Function):
+    """out[b, t, h, d] = sum_s p[b, h, t, s] v[b, s, h, d] on the per-head tensor-core kernel, with its backward."""
+
+    @staticmethod
+    def forward(ctx, probs, value):
+        B, L, H, D = value.shape
+        ctx.save_for_backward(probs, value)
+        return kernels.attn_heads_matmul(1, probs, value, B, L, H, D)
+
+    @staticmethod
+    def backward(ctx, go):
+        probs, value = ctx.saved_tensors
+        B, L, H, D = value.shape
+        go = go.contiguous()
+        dp = kernels.attn_heads_matmul(0, go, value, B, L, H, D) if ctx.needs_input_grad[0] else None   # dO V^T
+        dv = kernels.attn_heads_matmul(2, probs, go, B, L, H, D) if ctx.needs_input_grad[1] else None   # P^T dO
+        return dp, dv
+
+
+def attn_products_supported(query, key, value) -> bool:
+    """Self-attention shapes the per-head kernels cover: equal [B, 64, H, D] projections, D = 16 or 32, H even."""
+    if not fused_enabled or not query.is_cuda or query.dtype != torch.float32 or query.dim() != 4:
+        return False
+    if tuple(query.shape) != tuple(key.shape) or tuple(query.shape) != tuple(value.shape):
+        return False
+    B, L, H, D = query.shape
+    return kernels.attn_heads_supported(B, L, H, D)
+
+
 class QSoftmaxFusedFn(torch.autograd.Function):
     """Training-mode QSoftmax through the fused kernels.  ``params`` is a flat tuple of 15 tensors: (k, i, f) of the exp
     table's input and output quantizers, of the inverse table's input and output quantizers (one element each) and of the

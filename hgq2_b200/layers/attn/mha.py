@@ -14,7 +14,7 @@ import torch
 
 from ...backend import Constant
 from ...quantizer.config import QuantizerConfig
-from .._functions import EbopsDenseFn
+from .._functions import AttnContextFn, AttnScoresFn, EbopsDenseFn, attn_products_supported
 from ..core.base import QLayerBase
 from ..core.einsum_dense import QEinsumDense
 from ..softmax import QSoftmax
@@ -173,7 +173,11 @@ class QMultiHeadAttention(QLayerBase):
         return attention_output
 
     def _compute_attention(self, query, key, value, training=None):
-        query = query * self._inverse_sqrt_key_dim  # 1.0: the scale lives in the exp table's input
+        if self._inverse_sqrt_key_dim != 1.0:  # 1.0 after build: the scale lives in the exp table's input
+            query = query * self._inverse_sqrt_key_dim
+        if attn_products_supported(query, key, value):
+            scores = self._softmax(AttnScoresFn.apply(key, query))
+            return AttnContextFn.apply(scores, value), scores
         scores = torch.einsum(self._dot_product_equation, key, query)
         scores = self._softmax(scores)
         return torch.einsum(self._combine_equation, scores, value), scores

@@ -265,6 +265,19 @@ int hgq_maxpool2d_fwd(const float *x, float *y, unsigned char *argmax, int64_t B
 int hgq_maxpool2d_bwd(const float *gy, const unsigned char *argmax, float *dx, int64_t B, int H, int W, int C,
                       int pool_h, int pool_w, int stride_h, int stride_w, int OH, int OW, void *stream);
 
+/* ---- K6: per-head products of multi-head attention ---------------------------------------------------------------
+ * The two activation-activation contractions of QMultiHeadAttention._compute_attention (layers/attn/mha.py:434-470)
+ * and the four products of their backward, on the tensor cores, reading the head-interleaved projections in place.
+ * "SHD" = [B, L, H, D] fp32, "HTS" = [B, H, L, L] fp32; L = 64, D = 16 or 32, H even.
+ *   kind 0: out_HTS[b,h,t,s] = sum_d x_SHD[b,t,h,d] * y_SHD[b,s,h,d]     (scores = Q K^T;  dP = dO V^T)
+ *   kind 1: out_SHD[b,t,h,d] = sum_s x_HTS[b,h,t,s] * y_SHD[b,s,h,d]     (context = P V;   dQ = dS K)
+ *   kind 2: out_SHD[b,s,h,d] = sum_t x_HTS[b,h,t,s] * y_SHD[b,t,h,d]     (dV = P^T dO;     dK = dS^T Q)
+ * Operands go through two bf16 terms each (exact up to 16 significant bits), fp32 accumulation.
+ */
+int hgq_attn_heads_supported(int64_t B, int L, int H, int D);
+int hgq_attn_heads_matmul(int kind, const float *x, const float *y, float *out, int64_t B, int L, int H, int D,
+                          unsigned *status, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*

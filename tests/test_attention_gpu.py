@@ -96,3 +96,27 @@ def test_qmha_matches_oracle(fuse):
             pairs.append((pl.iq, ol.iq, f'{name}.iq'))
         compare_quantizer_grads(pairs)
     close(layer(x.detach(), training=False), twin(torch.from_numpy(x_np), training=False), 1e-5, 'eval output')
+
+
+@pytest.mark.parametrize('B,H,D', [(3, 4, 16), (5, 2, 32), (130, 4, 16)])
+def test_per_head_attention_products(B, H, D):
+    # the three product kinds of the per-head tensor-core kernel against float64 einsums
+    from hgq2_b200 import kernels
+
+    L = 64
+    rng = np.random.default_rng(B + H + D)
+    q = torch.from_numpy((np.round(rng.standard_normal((B, L, H, D)) * 64) / 64).astype(np.float32))
+    k = torch.from_numpy((np.round(rng.standard_normal((B, L, H, D)) * 64) / 64).astype(np.float32))
+    p = torch.from_numpy(rng.standard_normal((B, H, L, L)).astype(np.float32))
+    assert kernels.attn_heads_supported(B, L, H, D)
+    s = kernels.attn_heads_matmul(0, q.cuda(), k.cuda(), B, L, H, D)
+    kernels.check_status(s.device)
+    ref = torch.einsum('bthd,bshd->bhts', q.double(), k.double())
+    assert float((s.cpu().double() - ref).abs().max()) <= 1e-6 * float(ref.abs().max())
+    o = kernels.attn_heads_matmul(1, p.cuda(), k.cuda(), B, L, H, D)
+    ref = torch.einsum('bhts,bshd->bthd', p.double(), k.double())
+    assert float((o.cpu().double() - ref).abs().max()) <= 3e-5 * float(ref.abs().max())
+    g = kernels.attn_heads_matmul(2, p.cuda(), q.cuda(), B, L, H, D)
+    kernels.check_status(g.device)
+    ref = torch.einsum('bhts,bthd->bshd', p.double(), q.double())
+    assert float((g.cpu().double() - ref).abs().max()) <= 3e-5 * float(ref.abs().max())
