@@ -593,6 +593,41 @@ def run_qconv(args):
     print(json.dumps(out), flush=True)
 
 
+def run_attn(args):
+    """Kernel-level benchmark of the three per-head attention product kinds on the transformer block's shape:
+    [batch, 64, 4 heads, 16] projections, [batch, 4, 64, 64] scores.  Algorithmic bytes per head: 4 (2 L D + L L)."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    B, L, H, D = args.batch or 8192, 64, 4, 16
+    gen = torch.Generator(device=dev).manual_seed(0)
+    q = torch.randint(-512, 512, (B, L, H, D), device=dev, generator=gen).float() / 64.0   # 10-bit projections
+    k = torch.randint(-512, 512, (B, L, H, D), device=dev, generator=gen).float() / 64.0
+    p = torch.randint(0, 256, (B, H, L, L), device=dev, generator=gen).float() / 256.0     # 8-bit probabilities
+    g = torch.randn(B, H, L, L, device=dev, generator=gen)
+    peak, kind = measured_peaks()
+    out = {'kernel': 'k_attn_heads', 'batch': B, 'peak_GBs': peak, 'peak_source': kind}
+    cases = {'scores (kind 0)': (0, q, k), 'context (kind 1)': (1, p, k), 'context, fp32 lhs (kind 1)': (1, g, k),
+             'transposed (kind 2)': (2, g, q)}
+    for name, (kd, x, y) in cases.items():
+        fn = lambda: kernels.attn_heads_matmul(kd, x, y, B, L, H, D)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        kernels.check_status(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        gbs = 4.0 * (2 * L * D + L * L) * B * H / (ms * 1e-3) / 1e9
+        out[name] = {'ms': round(ms, 4), 'achieved_GBs': round(gbs, 1), 'frac': round(gbs / peak, 4)}
+    print(json.dumps(out), flush=True)
+
+
 def run_qsoftmax(args):
     """Kernel-level benchmark of the fused quantised softmax (forward and backward) on the attention-score tensor of the
     transformer block: [batch, 4 heads, 64, 64] scores, softmax over the last axis, output bitwidth table [4 * 64, 64].
@@ -643,7 +678,7 @@ def main():
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
     ap.add_argument('--model', default='particle_tagger', help='model of --workload qat')
     ap.add_argument('--batch', type=int, default=0, help='batch of --workload qat (0 = the benchmark batch)')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qsoftmax', 'qconv', 'qat'],
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qsoftmax', 'qconv', 'attn', 'qat'],
                     help="'qdense' times the fused dense forward kernel alone (for profiler captures)")
     ap.add_argument('--layer', type=int, default=1, choices=[1, 2, 3], help='convolution layer of --workload qconv')
     ap.add_argument('--rows', type=int, default=1 << 22)
@@ -660,6 +695,8 @@ def main():
         return run_qdense_bwd(args)
     if args.workload == 'qconv':
         return run_qconv(args)
+    if args.workload == 'attn':
+        return run_attn(args)
     if args.workload == 'qsoftmax':
         return run_qsoftmax(args)
     if args.impl == 'reference':
