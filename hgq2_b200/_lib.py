@@ -63,6 +63,11 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
          c_int, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    'hgq_qdense_bwd_strided': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+         c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
     'hgq_qsoftmax_fwd': (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int64, c_int,

@@ -36,7 +36,7 @@ struct QbParams {
     float *dx;
     float *part;        // per-CTA partials: [(K+1) x N] dWq|dbq, then [rows_period x K] df
     unsigned *status;
-    int64_t M, num_tiles;
+    int64_t M, num_tiles, ldx, lddx;  // row strides (floats) of x and dx: >= K, so a column slice of a wider matrix works
     int K, N, Kp, Np, Kt;
     int rows_period, rm, relu, want_df;
 };
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
 
     const int r8 = lane & 7, q4 = lane >> 3;
     const bool vec_n = (N % 4 == 0) && aligned(P.gy, 16) && (P.y == nullptr || aligned(P.y, 16));
-    const bool vec_k = (K % 4 == 0) && aligned(P.x, 16);
+    const bool vec_k = (K % 4 == 0) && aligned(P.x, 16) && (P.ldx % 4 == 0) && (P.lddx % 4 == 0) && (P.dx == nullptr || aligned(P.dx, 16));
     const float rbias = (P.rm == RM_RND) ? 0.5f : 0.f;
     const uint32_t rp = (uint32_t)P.rows_period;  // divides 128 (checked on the host), so a tile starts at table row 0
     uint32_t phase = 0;
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
         if (vec_k && g < kQbTileM * cv) {
             const int rr = g / cv, c4 = g - rr * cv;
             st_r[i] = st_off(rr, c4 ^ (rr & swm));
-            gl_r[i] = rr * cv + c4;         // rows are contiguous in dX: chunk index relative to the tile start
+            gl_r[i] = rr * (int)(P.lddx >> 2) + c4;  // chunk index relative to the tile start, rows lddx floats apart
         } else {
             st_r[i] = -1;
             gl_r[i] = 0;
@@ -240,13 +240,13 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
         const int64_t row = t_row0 + mg * 8 + r8;
         const int k0 = kg * 8;
         if (act && row < P.M && vec_k && k0 + 8 <= K) {
-            const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0));
-            const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * K + k0 + 4));
+            const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * P.ldx + k0));
+            const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.x + row * P.ldx + k0 + 4));
             xv[u][0] = a0.x; xv[u][1] = a0.y; xv[u][2] = a0.z; xv[u][3] = a0.w;
             xv[u][4] = a1.x; xv[u][5] = a1.y; xv[u][6] = a1.z; xv[u][7] = a1.w;
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) xv[u][j] = (act && row < P.M && k0 + j < K) ? __ldcs(P.x + row * K + k0 + j) : 0.f;
+            for (int j = 0; j < 8; ++j) xv[u][j] = (act && row < P.M && k0 + j < K) ? __ldcs(P.x + row * P.ldx + k0 + j) : 0.f;
         }
     };
     if ((int64_t)blockIdx.x < P.num_tiles) {
@@ -390,15 +390,15 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
                 __syncthreads();
                 const int64_t rows_here = (P.M - row0) < kQbTileM ? (P.M - row0) : kQbTileM;
                 if (vec_k) {
-                    float4 *dst = reinterpret_cast<float4 *>(P.dx + row0 * K);
-                    const int limit = (int)rows_here * cv;
+                    float4 *dst = reinterpret_cast<float4 *>(P.dx + row0 * P.lddx);
+                    const int limit = (int)rows_here * (int)(P.lddx >> 2);
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
                         if (st_r[i] >= 0 && gl_r[i] < limit) __stcs(dst + gl_r[i], *reinterpret_cast<const float4 *>(X + st_r[i]));
                 } else {
                     for (int g = tid; g < (int)rows_here * K; g += kQbThreads) {
                         const int rr = g / K, k = g - rr * K;
-                        __stcs(P.dx + (row0 + rr) * K + k,
+                        __stcs(P.dx + (row0 + rr) * P.lddx + k,
                                *reinterpret_cast<const float *>(X + st_off(rr, (k >> 2) ^ (rr & swm)) + (k & 3) * 4));
                     }
                 }
@@ -511,7 +511,16 @@ extern "C" size_t hgq_qdense_bwd_workspace(int64_t M, int K, int N, int rows_per
 extern "C" int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float *qf, int rows_period,
                               int round_mode, const float *wq, float *dx, float *dwq, float *dbq, float *df, int64_t M,
                               int K, int N, void *workspace, size_t workspace_bytes, unsigned *status, void *stream) {
+    return hgq_qdense_bwd_strided(gy, y, x, K, qf, rows_period, round_mode, wq, dx, K, dwq, dbq, df, M, K, N, workspace,
+                                  workspace_bytes, status, stream);
+}
+
+extern "C" int hgq_qdense_bwd_strided(const float *gy, const float *y, const float *x, int64_t ldx, const float *qf,
+                                      int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *dwq,
+                                      float *dbq, float *df, int64_t M, int K, int N, void *workspace, size_t workspace_bytes,
+                                      unsigned *status, void *stream) {
     if (gy == nullptr || x == nullptr || wq == nullptr || dwq == nullptr) return HGQ_ERR_NULL;
+    if (ldx < K || (dx != nullptr && lddx < K)) return HGQ_ERR_SIZE;
     if (round_mode < 0 || round_mode > 2) return HGQ_ERR_MODE;
     if (df != nullptr && qf == nullptr) return HGQ_ERR_NULL;
     QbGeom g;
@@ -523,7 +532,7 @@ extern "C" int hgq_qdense_bwd(const float *gy, const float *y, const float *x, c
     p.gy = gy; p.y = y; p.x = x; p.qf = qf; p.wq = wq; p.dx = dx;
     p.part = (float *)workspace;
     p.status = status;
-    p.M = M; p.num_tiles = g.tiles;
+    p.M = M; p.num_tiles = g.tiles; p.ldx = ldx; p.lddx = (dx != nullptr) ? lddx : K;
     p.K = K; p.N = N; p.Kp = g.Kp; p.Np = g.Np; p.Kt = g.Kt;
     p.rows_period = rows_period; p.rm = round_mode; p.relu = (y != nullptr) ? 1 : 0; p.want_df = (df != nullptr) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;

@@ -246,8 +246,17 @@ def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: 
     return y, absmax
 
 
+_QB_KBLOCK = 64  # input columns one backward launch covers
+
+
 def qdense_bwd_supported(M: int, K: int, N: int, rows_period: int) -> bool:
-    return M > 0 and lib().hgq_qdense_bwd_workspace(M, K, N, rows_period) > 0
+    if M <= 0:
+        return False
+    if K <= _QB_KBLOCK:
+        return lib().hgq_qdense_bwd_workspace(M, K, N, rows_period) > 0
+    # wider layers run as one launch per block of 64 input columns
+    return K % 4 == 0 and K <= 4 * _QB_KBLOCK and all(
+        lib().hgq_qdense_bwd_workspace(M, min(_QB_KBLOCK, K - k0), N, rows_period) > 0 for k0 in range(0, K, _QB_KBLOCK))
 
 
 def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: bool, want_db: bool, want_df: bool):
@@ -257,19 +266,32 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
     rm = ROUND_MODES[round_mode.upper()]
     gy, x, wq = gy.contiguous(), x.contiguous(), wq.contiguous()
     y = None if y is None else y.contiguous()
-    qf = None if qf is None else qf.contiguous()
     K, N = wq.shape
     M = x.numel() // K
     dev = x.device
+    want_df = want_df and qf is not None
     dx = torch.empty((M, K), dtype=torch.float32, device=dev) if want_dx else None
     dwq = torch.empty((K, N), dtype=torch.float32, device=dev)
     dbq = torch.empty(N, dtype=torch.float32, device=dev) if want_db else None
-    df = torch.empty(rows_period * K, dtype=torch.float32, device=dev) if (want_df and qf is not None) else None
-    ws = workspace(lib().hgq_qdense_bwd_workspace(M, K, N, rows_period), dev, slot=2)
+    dfs = []
+    x2 = x.view(M, K)
+    qf2 = None if qf is None else qf.reshape(rows_period, K)
     with torch.cuda.device(dev):
-        st = lib().hgq_qdense_bwd(ptr(gy), ptr(y), ptr(x), ptr(qf), rows_period, rm, ptr(wq), ptr(dx), ptr(dwq), ptr(dbq), ptr(df),
-                                  M, K, N, ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
-    check(st, 'hgq_qdense_bwd')
+        for k0 in range(0, K, _QB_KBLOCK):
+            kb = min(_QB_KBLOCK, K - k0)
+            qf_b = None if qf2 is None else qf2[:, k0:k0 + kb].contiguous()
+            df_b = torch.empty(rows_period * kb, dtype=torch.float32, device=dev) if want_df else None
+            ws = workspace(lib().hgq_qdense_bwd_workspace(M, kb, N, rows_period), dev, slot=2)
+            st = lib().hgq_qdense_bwd_strided(
+                ptr(gy), ptr(y), x2.data_ptr() + 4 * k0, K, ptr(qf_b), rows_period, rm, wq.data_ptr() + 4 * k0 * N,
+                (dx.data_ptr() + 4 * k0) if dx is not None else None, K, dwq.data_ptr() + 4 * k0 * N,
+                ptr(dbq) if k0 == 0 else None, ptr(df_b), M, kb, N, ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
+            check(st, 'hgq_qdense_bwd_strided')
+            if want_df:
+                dfs.append(df_b.view(rows_period, kb))
+    df = None
+    if want_df:
+        df = (dfs[0] if len(dfs) == 1 else torch.cat(dfs, dim=1)).reshape(-1)
     return dx, dwq, dbq, df
 
 
