@@ -29,6 +29,24 @@ inline int check_launch() {
 
 __host__ __device__ inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// Division of a non-negative 31-bit number by an invariant divisor through one 64-bit multiply: n / d == (n * mul) >> shift
+// for every 0 <= n < 2^31 with shift = 31 + ceil(log2 d), mul = ceil(2^shift / d).
+struct FastDiv {
+    uint64_t mul;
+    int shift;
+    uint32_t d;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    int l = 0;
+    while ((1u << l) < d) ++l;
+    f.shift = 31 + l;
+    f.mul = ((((uint64_t)1) << f.shift) + d - 1) / d;
+    f.d = d;
+    return f;
+}
+__host__ __device__ inline uint32_t fastdiv(uint32_t n, const FastDiv &f) { return (uint32_t)(((uint64_t)n * f.mul) >> f.shift); }
+
 inline int pow2ceil(int64_t v) {
     int p = 1;
     while (p < v) p <<= 1;

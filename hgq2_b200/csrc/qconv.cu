@@ -39,6 +39,7 @@ struct ClParams {
     int H, W, C, N, Np, OH, OW, Hp, Wp, KH, KW, dh, dw, pt, pl;
     int ncg, nsteps, MB, npx;  // channel groups, MMA K-steps, 128-row blocks per tile, staged pixels per tile
     int act;
+    FastDiv div_img, div_row, div_cg;  // by Hp * Wp, by Wp and by the number of channel groups
 };
 
 __device__ __forceinline__ void cl_split2(float v0, float v1, uint32_t &hi, uint32_t &lo) {
@@ -132,13 +133,13 @@ __global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
                 v[i][0] = v[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                 dst[i] = -1;
                 if (u < n_units) {
-                    const int p = u / ncg, cg = u - p * ncg;
+                    const int p = (int)fastdiv((uint32_t)u, P.div_cg), cg = u - p * ncg;
                     dst[i] = cg * cg_bytes + p * 16;
                     const int64_t q = q0 + p;
                     if (q < P.Q) {
-                        const int b = (int)((uint32_t)q / (uint32_t)HWp);   // Q < 2^31 (checked on the host)
+                        const int b = (int)fastdiv((uint32_t)q, P.div_img);   // Q < 2^31 (checked on the host)
                         const int rem = (int)((uint32_t)q - (uint32_t)b * (uint32_t)HWp);
-                        const int yp = rem / P.Wp, xp = rem - yp * P.Wp;
+                        const int yp = (int)fastdiv((uint32_t)rem, P.div_row), xp = rem - yp * P.Wp;
                         const int ih = yp - P.pt, iw = xp - P.pl;
                         if ((unsigned)ih < (unsigned)P.H && (unsigned)iw < (unsigned)P.W) {
                             const float *src = P.x + (((int64_t)b * P.H + ih) * P.W + iw) * P.C + cg * 8;
@@ -200,9 +201,9 @@ __global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
                 const int64_t q = q0 + mb * 128 + qlane + lane;
                 float *dst = nullptr;
                 if (q < P.Q) {
-                    const int b = (int)((uint32_t)q / (uint32_t)HWp);
+                    const int b = (int)fastdiv((uint32_t)q, P.div_img);
                     const int rem = (int)((uint32_t)q - (uint32_t)b * (uint32_t)HWp);
-                    const int yp = rem / P.Wp, xp = rem - yp * P.Wp;
+                    const int yp = (int)fastdiv((uint32_t)rem, P.div_row), xp = rem - yp * P.Wp;
                     if (yp < P.OH && xp < P.OW) dst = P.y + (((int64_t)b * P.OH + yp) * P.OW + xp) * P.N;
                 }
                 for (int c0 = half * ncol; c0 < (half + 1) * ncol; c0 += 8) {
@@ -307,6 +308,9 @@ extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, c
     p.H = H; p.W = W; p.C = C; p.N = N; p.Np = g.Np; p.OH = OH; p.OW = OW; p.Hp = g.Hp; p.Wp = g.Wp;
     p.KH = KH; p.KW = KW; p.dh = dil_h; p.dw = dil_w; p.pt = pad_top; p.pl = pad_left;
     p.ncg = g.ncg; p.nsteps = g.nsteps; p.MB = g.MB; p.npx = g.npx; p.act = activation;
+    p.div_img = make_fastdiv((uint32_t)(g.Hp * g.Wp));
+    p.div_row = make_fastdiv((uint32_t)g.Wp);
+    p.div_cg = make_fastdiv((uint32_t)g.ncg);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t ce = cudaFuncSetAttribute(k_qconv_s1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
     if (ce != cudaSuccess) return (int)ce;

@@ -287,6 +287,7 @@ struct CsParams {
     int64_t Q, num_tiles;
     int H, W, C, N, Np, OH, OW, Hp, Wp, KH, KW, dh, dw, pt, pl;
     int ncg, ng, Pt, npx, stack;
+    FastDiv div_img, div_row, div_cg;  // by Hp * Wp, by Wp and by the number of channel groups
 };
 
 __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P) {
@@ -320,6 +321,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
     const bool half_group = (P.C & 7) != 0;
     const bool relu = P.y != nullptr;
     const int n_units_x = npx * ncg, n_units_g = Pt * ng;
+    const int ng_shift = 31 - __clz(ng);
     const int my_g = tid % ng;  // kCwThreads is a multiple of ng: a thread always stages the same 8 output channels
     float db_r[8];
 #pragma unroll
@@ -340,13 +342,13 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
                 v[i][0] = v[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                 dst[i] = -1;
                 if (u < n_units_x) {
-                    const int p = u / ncg, cg = u - p * ncg;
+                    const int p = (int)fastdiv((uint32_t)u, P.div_cg), cg = u - p * ncg;
                     dst[i] = cg * cg_bytes + p * 16;
                     const int64_t q = q0 + p;
                     if (q < P.Q) {
-                        const int b = (int)((uint32_t)q / (uint32_t)HWp);
+                        const int b = (int)fastdiv((uint32_t)q, P.div_img);
                         const int rem = (int)((uint32_t)q - (uint32_t)b * (uint32_t)HWp);
-                        const int yp = rem / P.Wp, xp = rem - yp * P.Wp;
+                        const int yp = (int)fastdiv((uint32_t)rem, P.div_row), xp = rem - yp * P.Wp;
                         const int ih = yp - P.pt, iw = xp - P.pl;
                         if ((unsigned)ih < (unsigned)P.H && (unsigned)iw < (unsigned)P.W) {
                             const float *src = P.x + (((int64_t)b * P.H + ih) * P.W + iw) * P.C + cg * 8;
@@ -371,16 +373,16 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
         }
         // ---- G = dY (* relu mask) at the output positions, zero elsewhere; masked gradient out -----------------------------------
         for (int u = tid; u < n_units_g; u += kCwThreads) {
-            const int p = u / ng;  // u % ng == my_g
+            const int p = u >> ng_shift;  // ng is a power of two; u % ng == my_g
             const int64_t q = q0 + p;
             float g[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) g[j] = 0.f;
             const int n0 = my_g * 8;
             if (q < P.Q && n0 < N) {
-                const int b = (int)((uint32_t)q / (uint32_t)HWp);
+                const int b = (int)fastdiv((uint32_t)q, P.div_img);
                 const int rem = (int)((uint32_t)q - (uint32_t)b * (uint32_t)HWp);
-                const int yp = rem / P.Wp, xp = rem - yp * P.Wp;
+                const int yp = (int)fastdiv((uint32_t)rem, P.div_row), xp = rem - yp * P.Wp;
                 if (yp < P.OH && xp < P.OW) {
                     const int64_t o = (((int64_t)b * P.OH + yp) * P.OW + xp) * N + n0;
                     const bool second = n0 + 4 < N;  // N % 4 == 0 (checked on the host)
@@ -601,6 +603,9 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
         q.H = H; q.W = W; q.C = C; q.N = N; q.Np = gs.Np; q.OH = OH; q.OW = OW; q.Hp = gs.Hp; q.Wp = gs.Wp;
         q.KH = KH; q.KW = KW; q.dh = dil_h; q.dw = dil_w; q.pt = pad_top; q.pl = pad_left;
         q.ncg = gs.ncg; q.ng = gs.ng; q.Pt = gs.Pt; q.npx = gs.npx; q.stack = gs.stack;
+        q.div_img = make_fastdiv((uint32_t)(gs.Hp * gs.Wp));
+        q.div_row = make_fastdiv((uint32_t)gs.Wp);
+        q.div_cg = make_fastdiv((uint32_t)gs.ncg);
         cudaError_t ce = cudaFuncSetAttribute(k_qconv_wgrad_s1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);
         if (ce != cudaSuccess) return (int)ce;
         k_qconv_wgrad_s1<<<gs.grid, kCwThreads, gs.smem, st>>>(q);
