@@ -228,7 +228,8 @@ extern "C" int hgq_attn_heads_matmul(int kind, const float *x, const float *y, f
     p.num_tiles = B * (H / 2);
     const size_t smem = at_smem(kind, D);
     int per_sm = (int)((228 * 1024) / (smem + 1024));
-    if (per_sm > 4) per_sm = 4;  // 256 threads each; tensor memory: at most 128 columns per CTA
+    const int cap = 4;  // measured optimum for all three kinds (3 and 5 resident CTAs are both slower)
+    if (per_sm > cap) per_sm = cap;
     int64_t grid = (int64_t)kNumSMs * per_sm;
     if (grid > p.num_tiles) grid = p.num_tiles;
     cudaStream_t st = (cudaStream_t)stream;
