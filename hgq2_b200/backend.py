@@ -175,6 +175,58 @@ class Variable:
         return f'<Variable {self.path} shape={self.shape} dtype={self.dtype} trainable={self.trainable}>'
 
 
+# ---- bookkeeping stream ------------------------------------------------------------------------
+# The integer-bit tracking of the WRAP quantizers and the EBOPs terms are long chains of tiny kernels on bitwidth-shaped
+# tensors.  They depend on a layer's abs-max statistics but nothing downstream in the forward pass depends on them (until
+# the losses are summed), so they run on a second stream, forked from and later joined to the stream that carries the
+# activations: in the captured step graph this becomes a parallel branch, and autograd replays the backward of those
+# nodes on the same second stream.
+overlap_bookkeeping = True
+_side_streams: dict = {}
+
+
+class bookkeeping:
+    """``with bookkeeping(t1, t2, ...):`` -- run the body on the device's bookkeeping stream, ordered after everything
+    queued so far on the current stream.  The tensors named are inputs of the body that were allocated on the current
+    stream; they are marked as in use by the second stream so that their memory is not handed out again early."""
+
+    def __init__(self, *tensors):
+        self.tensors = tensors
+        self._ctx = None
+
+    def __enter__(self):
+        if not overlap_bookkeeping or not torch.cuda.is_available():
+            return self
+        dev = torch.cuda.current_device()
+        main = torch.cuda.current_stream()
+        side = _side_streams.get(dev)
+        if side is None:
+            side = _side_streams[dev] = torch.cuda.Stream(device=dev)
+        if main == side:  # nested region
+            return self
+        side.wait_stream(main)
+        for t in self.tensors:
+            if t is not None and t.is_cuda:
+                t.record_stream(side)
+        self._ctx = torch.cuda.stream(side)
+        self._ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self._ctx is not None:
+            self._ctx.__exit__(*exc)
+        return False
+
+
+def join_bookkeeping() -> None:
+    """Make the current stream wait for the bookkeeping stream (before its results -- loss terms -- are consumed)."""
+    if not torch.cuda.is_available():
+        return
+    side = _side_streams.get(torch.cuda.current_device())
+    if side is not None and torch.cuda.current_stream() != side:
+        torch.cuda.current_stream().wait_stream(side)
+
+
 # ---- call context ------------------------------------------------------------------------------
 class _CallContext(threading.local):
     def __init__(self):
@@ -298,6 +350,8 @@ class Layer(nn.Module):
             return self.call(*args, **kwargs)
         finally:
             _ctx.depth -= 1
+            if _ctx.depth == 0:
+                join_bookkeeping()  # state, EBOPs and loss terms written on the second stream are visible to the caller
             _ctx.training = prev_training
             if top:
                 _ctx.root = None

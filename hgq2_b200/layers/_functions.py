@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from ..backend import bookkeeping
 
 _ones: dict = {}
 
@@ -169,7 +170,8 @@ def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training, a
     y, amax = QDenseFusedFn.apply(inputs, qkernel, qbias, k, i, f, rows_period, rm, om, tr, zero, act_fused, want_amax)
     y = y.view(shape[:len(shape) - n_contract] + (N,))
     if want_amax:
-        track(_amax_to_shape(amax.view(table_shape), bw_shape), inputs)
+        with bookkeeping(amax):
+            track(_amax_to_shape(amax.view(table_shape), bw_shape), inputs)
     if act_spec is not None and act_fused is None:
         y = layer.activation(y)
     return y

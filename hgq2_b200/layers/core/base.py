@@ -15,7 +15,7 @@ from functools import wraps
 
 import torch
 
-from ...backend import Constant, Initializer, Layer
+from ...backend import Constant, Initializer, Layer, bookkeeping
 from ...config.layer import global_config
 from ...quantizer import Quantizer, QuantizerConfig
 
@@ -49,7 +49,8 @@ class QLayerMeta(ABCMeta):
                     r = original_call(self, *args, **kwargs)
                     if (training or training == 'tracing') and self.enable_ebops:  # noqa: E712
                         tensors = args[0] if isinstance(args[0], (tuple, list)) else args
-                        self._account_ebops(*((1,) + tuple(t.shape[1:]) for t in tensors))
+                        with bookkeeping():
+                            self._account_ebops(*((1,) + tuple(t.shape[1:]) for t in tensors))
                     if not self.enable_oq or self.__output_quantizer_handled__:
                         return r
                     assert not isinstance(r, (tuple, list)), (

@@ -12,7 +12,7 @@ from math import prod
 
 import torch
 
-from ..backend import epsilon
+from ..backend import bookkeeping, epsilon
 from ..config.layer import global_config
 from ..quantizer import QuantizerConfig
 from . import _functions
@@ -122,16 +122,17 @@ class QSoftmax(QLayerBaseSingleInput):
         modes = tuple((plan['round_mode'], plan['overflow_mode']) for plan in plans)
         y, a3, a5 = _functions.QSoftmaxFusedFn.apply(inputs, modes, float(self.input_scaler), float(epsilon()), rows_period,
                                                      plans[2]['track'] is not None, p5['track'] is not None, *params)
-        if plans[2]['track'] is not None:
-            plans[2]['track'](a3.view(plans[2]['f'].shape), None)
-        if p5['track'] is not None:
-            p5['track'](_functions._amax_to_shape(a5.view(full), tuple(p5['f'].shape)), None)
-        # the sub-layers' own bookkeeping that their wrapped call would have done
-        inv_shape = tuple(1 if ax in self.axes else d for ax, d in enumerate(full))
-        if self.exp_table.enable_ebops:
-            self.exp_table._account_ebops(full)
-        if self.inv_table.enable_ebops:
-            self.inv_table._account_ebops(inv_shape)
+        with bookkeeping(a3, a5):
+            if plans[2]['track'] is not None:
+                plans[2]['track'](a3.view(plans[2]['f'].shape), None)
+            if p5['track'] is not None:
+                p5['track'](_functions._amax_to_shape(a5.view(full), tuple(p5['f'].shape)), None)
+            # the sub-layers' own bookkeeping that their wrapped call would have done
+            inv_shape = tuple(1 if ax in self.axes else d for ax, d in enumerate(full))
+            if self.exp_table.enable_ebops:
+                self.exp_table._account_ebops(full)
+            if self.inv_table.enable_ebops:
+                self.inv_table._account_ebops(inv_shape)
         return y
 
     def call(self, inputs, training=None, mask=None):

@@ -12,7 +12,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from ...backend import Constant, Initializer, epsilon
+from ...backend import Constant, Initializer, bookkeeping, epsilon
 from ...constraints import Constraint, MinMax
 from ...regularizers import Regularizer
 from .. import fixed_point_ops
@@ -333,17 +333,20 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
             f = self.f
             if training or training == 'tracing':  # noqa: E712
                 rinputs, absmax = self._round_and_absmax(inputs, f)
-                _new_i = minimal_i_given_xf(_sync_absmax(absmax, inputs), f.detach(), self.symmetric)
                 if training:
-                    new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i)
-                    self._i.assign(new_i)
-                else:
-                    if self._i.constraint is not None:
-                        _new_i = self._i.constraint(_new_i)
-                    new_i = torch.maximum(self.i.detach(), _new_i)
-                    new_k = self.get_any_k(rinputs.detach())
-                    self._k.assign((self._k.value.bool() | new_k).to(torch.uint8))
-                    self._i.assign(new_i)
+                    with bookkeeping(absmax):  # nothing downstream in this forward pass reads the updated integer bits
+                        _new_i = minimal_i_given_xf(_sync_absmax(absmax, inputs), f.detach(), self.symmetric)
+                        new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i)
+                        self._i.assign(new_i)
+                    return rinputs
+                # tracing
+                _new_i = minimal_i_given_xf(_sync_absmax(absmax, inputs), f.detach(), self.symmetric)
+                if self._i.constraint is not None:
+                    _new_i = self._i.constraint(_new_i)
+                new_i = torch.maximum(self.i.detach(), _new_i)
+                new_k = self.get_any_k(rinputs.detach())
+                self._k.assign((self._k.value.bool() | new_k).to(torch.uint8))
+                self._i.assign(new_i)
                 return rinputs
             if self._is_weight:
                 return self.stateless_quantizer.round(inputs, f, False, self.seed_gen)

@@ -20,7 +20,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .backend import Layer, Variable
+from .backend import Layer, Variable, join_bookkeeping
 from .constraints import Constant as ConstantConstraint
 from .constraints import Max, Min, MinMax
 from .quantizer.internal import fixed_point_quantizer as _fpq
@@ -175,6 +175,7 @@ class Trainer:
         self.state.zero_grad()
         pred = self.model(x, training=True)
         task = self.loss_fn(pred, y)
+        join_bookkeeping()  # the EBOPs terms were computed on the bookkeeping stream
         total = task
         for extra in self.model._losses:  # the beta * EBOPs terms; the weight regularisers are fused into the optimizer
             total = total + extra
