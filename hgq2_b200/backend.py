@@ -218,6 +218,36 @@ class bookkeeping:
         return False
 
 
+def queue_params(layers) -> None:
+    """Queue the parameter-only part of the coming calls of ``layers`` (their quantised kernels and biases) on the second
+    stream, where it runs beside the first layers' activation kernels; each layer picks its result up with
+    ``take_prepared``."""
+    if not overlap_bookkeeping or not torch.cuda.is_available():
+        return
+    for layer in layers:
+        prep = getattr(layer, 'prepare_params', None)
+        if prep is not None and layer.built:
+            with bookkeeping():
+                layer._prepared = prep()
+                layer._prepared_event = torch.cuda.Event()
+                layer._prepared_event.record()
+
+
+def take_prepared(layer):
+    """The (quantised kernel, quantised bias) a ``Sequential`` queued ahead for this call of ``layer``, or None.  The current
+    stream is made to wait for them."""
+    p = getattr(layer, '_prepared', None)
+    if p is None:
+        return None
+    layer._prepared = None
+    main = torch.cuda.current_stream()
+    main.wait_event(layer._prepared_event)
+    for t in p:
+        if t is not None:
+            t.record_stream(main)
+    return p
+
+
 def join_bookkeeping() -> None:
     """Make the current stream wait for the bookkeeping stream (before its results -- loss terms -- are consumed)."""
     if not torch.cuda.is_available():
@@ -429,6 +459,8 @@ class Sequential(Layer):
         self.built = True
 
     def call(self, inputs, training=None):
+        if training and torch.is_tensor(inputs) and inputs.is_cuda:
+            queue_params(self.layers)
         x = inputs
         for layer in self.layers:
             x = layer(x, training=training)

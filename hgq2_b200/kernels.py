@@ -11,14 +11,16 @@ import torch
 from . import _lib
 from ._lib import FLAG_TRAINING, FLAG_ZERO_NONPOS, OVERFLOW_MODES, ROUND_MODES, check, lib, ptr, require_cuda, stream_handle
 
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_workspaces: dict[tuple[int, int, int], torch.Tensor] = {}
 
 
 def workspace(nbytes: int, device: torch.device, slot: int = 0) -> torch.Tensor | None:
-    """A per-device scratch buffer that only ever grows (kept so steady-state steps allocate nothing)."""
+    """A scratch buffer that only ever grows (kept so steady-state steps allocate nothing), one per device, purpose
+    (``slot``) and stream: kernels queued on different streams may run at the same time and must not share scratch."""
     if nbytes <= 0:
         return None
-    key = (device.index if device.index is not None else torch.cuda.current_device(), slot)
+    dev = device.index if device.index is not None else torch.cuda.current_device()
+    key = (dev, slot, torch.cuda.current_stream(dev).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)

@@ -12,7 +12,7 @@ import math
 
 import torch
 
-from ...backend import Constant
+from ...backend import Constant, queue_params
 from ...quantizer.config import QuantizerConfig
 from .._functions import AttnContextFn, AttnScoresFn, EbopsDenseFn, attn_products_supported
 from ..core.base import QLayerBase
@@ -161,6 +161,8 @@ class QMultiHeadAttention(QLayerBase):
             value = query
         if key is None:
             key = value
+        if training and query.is_cuda:
+            queue_params((self._query_dense, self._key_dense, self._value_dense, self._output_dense))
         query = self._query_dense(query)
         key = self._key_dense(key)
         value = self._value_dense(value)

@@ -7,7 +7,7 @@ from math import ceil, prod
 import torch
 import torch.nn.functional as F
 
-from ..backend import activation_name, get_activation, get_initializer
+from ..backend import activation_name, get_activation, get_initializer, take_prepared
 from ..quantizer import Quantizer
 from ..quantizer.config import QuantizerConfig
 from ._functions import EbopsConv2dFn, fused_conv2d_call
@@ -126,11 +126,14 @@ class QConv2D(QLayerBaseSingleInput):
         y = F.conv2d(x, w, stride=self.strides, dilation=self.dilation_rate)
         return y.permute(0, 2, 3, 1)
 
+    def prepare_params(self):
+        """The parameter-only part of a call: (quantised kernel, quantised bias)."""
+        return self.qkernel, (self.qbias if self.use_bias else None)
+
     def call(self, inputs, training=None):
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
-        qkernel = self.qkernel
-        qbias = self.qbias if self.use_bias else None
+        qkernel, qbias = take_prepared(self) or self.prepare_params()
         fused = fused_conv2d_call(self, inputs, qkernel, qbias)
         if fused is not None:
             return fused

@@ -6,7 +6,7 @@ from math import prod
 
 import torch
 
-from ...backend import activation_name, get_activation, get_initializer, moments
+from ...backend import activation_name, get_activation, get_initializer, moments, take_prepared
 from ...quantizer import Quantizer
 from ...quantizer.config import QuantizerConfig
 from .._functions import EbopsDenseFn, fused_dense_call
@@ -68,15 +68,20 @@ class QDense(QLayerBaseSingleInput):
     def compute_output_shape(self, input_shape):
         return tuple(input_shape[:-1]) + (self.units,)
 
+    def prepare_params(self):
+        """The parameter-only part of a call: (quantised kernel, quantised bias)."""
+        return self.qkernel, (self.qbias if self.bias is not None else None)
+
     def call(self, inputs, training=None):
-        y = fused_dense_call(self, inputs, 1, self.qkernel, self.qbias if self.bias is not None else None, training)
+        qkernel, qbias = take_prepared(self) or self.prepare_params()
+        y = fused_dense_call(self, inputs, 1, qkernel, qbias, training)
         if y is not None:
             return y
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
-        x = torch.matmul(inputs, self.qkernel)
-        if self.bias is not None:
-            x = x + self.qbias
+        x = torch.matmul(inputs, qkernel)
+        if qbias is not None:
+            x = x + qbias
         if self.activation is not None:
             x = self.activation(x)
         return x
@@ -152,6 +157,8 @@ class QBatchNormDense(QDense):
                                            trainable=False)
         self.moving_variance = self.add_weight(shape=shape, name='moving_variance',
                                                initializer=self.moving_variance_initializer, trainable=False)
+
+    prepare_params = None  # kernel and bias depend on the batch statistics: nothing to queue ahead
 
     @property
     def bn_gamma(self):

@@ -6,7 +6,7 @@ from math import prod
 
 import torch
 
-from ...backend import activation_name, get_activation, get_initializer
+from ...backend import activation_name, get_activation, get_initializer, take_prepared
 from ...quantizer import Quantizer
 from ...quantizer.config import QuantizerConfig
 from .._functions import EbopsDenseFn, fused_dense_call
@@ -143,9 +143,12 @@ class QEinsumDense(QLayerBaseSingleInput):
     def compute_output_shape(self, input_shape):
         return (input_shape[0],) + tuple(self.full_output_shape[1:])
 
+    def prepare_params(self):
+        """The parameter-only part of a call: (quantised kernel, quantised bias)."""
+        return self.kq(self._kernel.value), (self.bq(self._bias.value) if self.bias is not None else None)
+
     def call(self, inputs, training=None):
-        qkernel = self.kq(self._kernel.value, training=training)
-        qbias = self.bq(self._bias.value, training=training) if self.bias is not None else None
+        qkernel, qbias = take_prepared(self) or self.prepare_params()
         return self._contract(inputs, qkernel, qbias, training, apply_iq=True)
 
     def _contract(self, inputs, qkernel, qbias, training, apply_iq: bool):

@@ -43,6 +43,8 @@ class QEinsumDenseBatchnorm(QEinsumDense):
         self.normalize_axes = normalize_axes
         self._check_normalize_axes()
 
+    prepare_params = None  # kernel and bias depend on the batch statistics: nothing to queue ahead
+
     def _check_normalize_axes(self):
         kernel_axes, output_axes = self.equation.split(',')[1].split('->')
         for c in self.normalize_axes:
