@@ -55,10 +55,16 @@ class QMultiHeadAttention(QLayerBase):
         self._output_shape = output_shape
         self._kernel_initializer, self._bias_initializer = kernel_initializer, bias_initializer
         self._inverse_sqrt_key_dim = 1.0 / math.sqrt(float(key_dim))
+        self._n_projections = 0
         super().__init__(**kwargs)
 
     def _common(self):
-        return dict(kernel_initializer=self._kernel_initializer, bias_initializer=self._bias_initializer,
+        init = self._kernel_initializer
+        if getattr(init, 'seed', None) is not None:  # a seeded initializer: each projection gets its own stream
+            init = init.clone()
+            init.seed = init.seed + self._n_projections
+            self._n_projections += 1
+        return dict(kernel_initializer=init, bias_initializer=self._bias_initializer,
                     iq_conf=self._qkvo_iq_conf, kq_conf=self._qkvo_kq_conf, bq_conf=self._qkvo_bq_conf,
                     oq_conf=self._qkvo_oq_conf, enable_ebops=self.enable_ebops, beta0=self._beta0.clone(),
                     parallelization_factor=self.parallelization_factor)

@@ -41,6 +41,8 @@ def _seeded(layers, seed=0):
     for j, layer in enumerate(layers):
         if hasattr(layer, 'kernel_initializer'):
             layer.kernel_initializer = GlorotUniform(seed + j)
+        elif hasattr(layer, '_kernel_initializer'):  # attention: its four projections draw from seed, seed + 1, ...
+            layer._kernel_initializer = GlorotUniform(1000 * (seed + j + 1))
     return layers
 
 
