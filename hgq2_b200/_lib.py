@@ -65,8 +65,8 @@ SIGNATURES: dict[str, tuple] = {
     ),
     'hgq_qdense_bwd_strided': (
         c_int,
-        [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-         c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
+        [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+         c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
     'hgq_qsoftmax_fwd': (
         c_int,

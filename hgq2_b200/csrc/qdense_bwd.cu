@@ -39,6 +39,8 @@ struct QbParams {
     int64_t M, num_tiles, ldx, lddx;  // row strides (floats) of x and dx: >= K, so a column slice of a wider matrix works
     int K, N, Kp, Np, Kt;
     int rows_period, rm, relu, want_df;
+    int gy_repeat;     // each row of gy serves gy_repeat consecutive rows (the gradient of a sum over an axis); 1 = one each
+    FastDiv gy_div;
 };
 
 // two-term bf16 split of a pair: hi = RN(v), lo = RN(v - hi)
@@ -196,9 +198,10 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
         const bool act = c < combos_g && kg < CGn;
         const int64_t row = t_row0 + mg * 8 + r8;
         const int n0 = kg * 8;
+        const int64_t grow = (P.gy_repeat > 1) ? (int64_t)fastdiv((uint32_t)row, P.gy_div) : row;  // M < 2^31 when repeating
         if (act && row < P.M && vec_n && n0 + 8 <= N) {
-            const float4 a0 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0));
-            const float4 a1 = __ldcs(reinterpret_cast<const float4 *>(P.gy + row * N + n0 + 4));
+            const float4 a0 = __ldg(reinterpret_cast<const float4 *>(P.gy + grow * N + n0));
+            const float4 a1 = __ldg(reinterpret_cast<const float4 *>(P.gy + grow * N + n0 + 4));
             gv[slot][0] = a0.x; gv[slot][1] = a0.y; gv[slot][2] = a0.z; gv[slot][3] = a0.w;
             gv[slot][4] = a1.x; gv[slot][5] = a1.y; gv[slot][6] = a1.z; gv[slot][7] = a1.w;
             if (P.relu) {
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const bool in = act && row < P.M && n0 + j < N;
-                gv[slot][j] = in ? __ldcs(P.gy + row * N + n0 + j) : 0.f;
+                gv[slot][j] = in ? __ldg(P.gy + grow * N + n0 + j) : 0.f;
                 yv[slot][j] = (in && P.relu) ? __ldcs(P.y + row * N + n0 + j) : 1.f;
             }
         }
@@ -511,16 +514,17 @@ extern "C" size_t hgq_qdense_bwd_workspace(int64_t M, int K, int N, int rows_per
 extern "C" int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float *qf, int rows_period,
                               int round_mode, const float *wq, float *dx, float *dwq, float *dbq, float *df, int64_t M,
                               int K, int N, void *workspace, size_t workspace_bytes, unsigned *status, void *stream) {
-    return hgq_qdense_bwd_strided(gy, y, x, K, qf, rows_period, round_mode, wq, dx, K, dwq, dbq, df, M, K, N, workspace,
+    return hgq_qdense_bwd_strided(gy, 1, y, x, K, qf, rows_period, round_mode, wq, dx, K, dwq, dbq, df, M, K, N, workspace,
                                   workspace_bytes, status, stream);
 }
 
-extern "C" int hgq_qdense_bwd_strided(const float *gy, const float *y, const float *x, int64_t ldx, const float *qf,
+extern "C" int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const float *y, const float *x, int64_t ldx, const float *qf,
                                       int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *dwq,
                                       float *dbq, float *df, int64_t M, int K, int N, void *workspace, size_t workspace_bytes,
                                       unsigned *status, void *stream) {
     if (gy == nullptr || x == nullptr || wq == nullptr || dwq == nullptr) return HGQ_ERR_NULL;
     if (ldx < K || (dx != nullptr && lddx < K)) return HGQ_ERR_SIZE;
+    if (gy_repeat < 1 || (gy_repeat > 1 && M >= ((int64_t)1 << 31))) return HGQ_ERR_SIZE;
     if (round_mode < 0 || round_mode > 2) return HGQ_ERR_MODE;
     if (df != nullptr && qf == nullptr) return HGQ_ERR_NULL;
     QbGeom g;
@@ -532,6 +536,7 @@ extern "C" int hgq_qdense_bwd_strided(const float *gy, const float *y, const flo
     p.gy = gy; p.y = y; p.x = x; p.qf = qf; p.wq = wq; p.dx = dx;
     p.part = (float *)workspace;
     p.status = status;
+    p.gy_repeat = gy_repeat; p.gy_div = make_fastdiv((uint32_t)gy_repeat);
     p.M = M; p.num_tiles = g.tiles; p.ldx = ldx; p.lddx = (dx != nullptr) ? lddx : K;
     p.K = K; p.N = N; p.Kp = g.Kp; p.Np = g.Np; p.Kt = g.Kt;
     p.rows_period = rows_period; p.rm = round_mode; p.relu = (y != nullptr) ? 1 : 0; p.want_df = (df != nullptr) ? 1 : 0;

@@ -261,8 +261,10 @@ def qdense_bwd_supported(M: int, K: int, N: int, rows_period: int) -> bool:
         lib().hgq_qdense_bwd_workspace(M, min(_QB_KBLOCK, K - k0), N, rows_period) > 0 for k0 in range(0, K, _QB_KBLOCK))
 
 
-def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: bool, want_db: bool, want_df: bool):
-    """Fused backward of qdense_fwd (rounding-only input quantizer or none).  gy/y are [M, N], x [M, K].
+def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: bool, want_db: bool, want_df: bool,
+               gy_repeat: int = 1):
+    """Fused backward of qdense_fwd (rounding-only input quantizer or none).  gy/y are [M, N], x [M, K]; with
+    ``gy_repeat`` > 1, gy is [M / gy_repeat, N] and each of its rows serves gy_repeat consecutive rows.
     Returns (dx or None, dwq, dbq or None, df or None)."""
     require_cuda(gy, y, x, qf, wq)
     rm = ROUND_MODES[round_mode.upper()]
@@ -285,7 +287,7 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
             df_b = torch.empty(rows_period * kb, dtype=torch.float32, device=dev) if want_df else None
             ws = workspace(lib().hgq_qdense_bwd_workspace(M, kb, N, rows_period), dev, slot=2)
             st = lib().hgq_qdense_bwd_strided(
-                ptr(gy), ptr(y), x2.data_ptr() + 4 * k0, K, ptr(qf_b), rows_period, rm, wq.data_ptr() + 4 * k0 * N,
+                ptr(gy), gy_repeat, ptr(y), x2.data_ptr() + 4 * k0, K, ptr(qf_b), rows_period, rm, wq.data_ptr() + 4 * k0 * N,
                 (dx.data_ptr() + 4 * k0) if dx is not None else None, K, dwq.data_ptr() + 4 * k0 * N,
                 ptr(dbq) if k0 == 0 else None, ptr(df_b), M, kb, N, ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
             check(st, 'hgq_qdense_bwd_strided')

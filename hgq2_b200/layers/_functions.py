@@ -56,9 +56,14 @@ class QDenseFusedFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, wq, bq, k, i, f, rows_period, round_mode, overflow_mode, training, zero, activation, want_absmax):
+    def forward(ctx, x, wq, bq, k, i, f, rows_period, round_mode, overflow_mode, training, zero, activation, want_absmax,
+                out_shape=None):
         y, amax = kernels.qdense_fwd(x, k, i, f, rows_period, round_mode, overflow_mode, training, zero, wq, bq, activation,
                                      want_absmax)
+        if out_shape is not None:
+            # the layer's output shape is given here, not by a view outside: the incoming gradient then arrives as autograd
+            # made it (e.g. the stride-0 expansion of a sum's gradient), not reshaped into a dense copy
+            y = y.view(out_shape)
         ctx.save_for_backward(x, wq, k, i, f, y if activation == 'relu' else None)
         ctx.meta = (rows_period, round_mode, overflow_mode, training, zero, activation, bq is not None)
         if amax is None:
@@ -71,20 +76,28 @@ class QDenseFusedFn(torch.autograd.Function):
         x, wq, k, i, f, y = ctx.saved_tensors
         rows_period, rm, om, training, zero, activation, has_bias = ctx.meta
         K, N = wq.shape
-        gy = gy.contiguous()
+        gy_repeat = 1
+        if (gy.dim() == 3 and gy.stride(1) == 0 and gy.stride(2) == 1 and gy.stride(0) == N and gy.size(1) > 1
+                and x.numel() // K < (1 << 31)):
+            gy_repeat, gy = gy.size(1), gy[:, 0, :]  # gradient of a sum over axis 1: one stored row per sample
+        else:
+            gy = gy.contiguous()
         need_x, need_w, need_b, _, need_i, need_f = ctx.needs_input_grad[:6]
         round_only = f is not None and (om == 'NONE' or (om == 'WRAP' and training)) and not zero
         if fused_bwd_enabled and need_w and (f is None or round_only) and kernels.qdense_bwd_supported(x.numel() // K, K, N, rows_period):
             dx, dwq, dbq, df = kernels.qdense_bwd(gy, y if activation == 'relu' else None, x, f, rows_period, rm, wq,
-                                                  want_dx=need_x, want_db=has_bias and need_b, want_df=bool(need_f))
+                                                  want_dx=need_x, want_db=has_bias and need_b, want_df=bool(need_f),
+                                                  gy_repeat=gy_repeat)
             if dx is not None:
                 dx = dx.view(x.shape)
             if df is not None:
                 df = df.view(f.shape)
             di = torch.zeros_like(i) if (need_i and i is not None) else None
-            return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None
+            return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None, None
+        if gy_repeat > 1:
+            gy = gy.unsqueeze(1).expand(-1, gy_repeat, -1)
         if activation == 'relu':
-            gy = gy * (y > 0)
+            gy = gy * (y > 0).view(gy.shape)
         g2 = gy.reshape(-1, N)
         x2 = x.reshape(-1, K)
         dbq = g2.sum(0) if (has_bias and need_b) else None
@@ -105,7 +118,7 @@ class QDenseFusedFn(torch.autograd.Function):
                     di = torch.zeros_like(i)
             if dx is not None:
                 dx = dx.view(x.shape)
-        return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None
+        return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None, None
 
 
 # ---- dispatch of a dense-like layer onto the fused kernel ------------------------------------------------------
@@ -167,8 +180,8 @@ def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training, a
     if not kernels.qdense_supported(M, K, N, rows_period):
         return None
     want_amax = track is not None
-    y, amax = QDenseFusedFn.apply(inputs, qkernel, qbias, k, i, f, rows_period, rm, om, tr, zero, act_fused, want_amax)
-    y = y.view(shape[:len(shape) - n_contract] + (N,))
+    y, amax = QDenseFusedFn.apply(inputs, qkernel, qbias, k, i, f, rows_period, rm, om, tr, zero, act_fused, want_amax,
+                                  shape[:len(shape) - n_contract] + (N,))
     if want_amax:
         with bookkeeping(amax):
             track(_amax_to_shape(amax.view(table_shape), bw_shape), inputs)

@@ -195,8 +195,10 @@ int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float 
                    int K, int N, void *workspace, size_t workspace_bytes, unsigned *status, void *stream);
 /* The same with x and dx as column slices of wider row-major matrices (row strides ldx, lddx >= K, in floats): a layer
  * with K > 64 runs as one call per block of 64 input columns, each producing its columns of dx, its rows of dwq and its
- * columns of df (dbq is the same in every call). */
-int hgq_qdense_bwd_strided(const float *gy, const float *y, const float *x, int64_t ldx, const float *qf,
+ * columns of df (dbq is the same in every call).  gy_repeat > 1: gy has M / gy_repeat rows, each serving gy_repeat
+ * consecutive rows of x -- the gradient of a sum over an axis (e.g. over the particles of a set), read in place instead
+ * of being expanded in memory. */
+int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const float *y, const float *x, int64_t ldx, const float *qf,
                            int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *dwq,
                            float *dbq, float *df, int64_t M, int K, int N, void *workspace, size_t workspace_bytes,
                            unsigned *status, void *stream);

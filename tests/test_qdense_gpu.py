@@ -138,3 +138,23 @@ def test_fused_dense_backward_is_deterministic():
     b = kernels.qdense_bwd(gy, None, x, f, 64, 'RND', w, True, True, True)
     for u, v in zip(a, b):
         assert torch.equal(u, v)
+
+
+def test_fused_dense_backward_with_repeated_gradient_rows():
+    # the gradient of a sum over an axis: one stored row of dY per group of 64 rows, read in place
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(5)
+    B, P, K, N = 37, 64, 64, 64
+    M = B * P
+    x = torch.from_numpy((rng.standard_normal((M, K)) * 3).astype(np.float32)).cuda()
+    f = torch.from_numpy(rng.integers(1, 7, (P, K)).astype(np.float32)).cuda()
+    w = torch.from_numpy(np.round(rng.uniform(-2, 2, (K, N)) * 64) / 64).float().cuda()
+    g = torch.from_numpy(rng.standard_normal((B, N)).astype(np.float32)).cuda()
+    y = torch.from_numpy(rng.standard_normal((M, N)).astype(np.float32)).cuda()
+    full = g.unsqueeze(1).expand(B, P, N).reshape(M, N).contiguous()
+    ref = kernels.qdense_bwd(full, y, x, f, P, 'RND', w, True, True, True)
+    got = kernels.qdense_bwd(g, y, x, f, P, 'RND', w, True, True, True, gy_repeat=P)
+    kernels.check_status(x.device)
+    for a, b in zip(got, ref):
+        assert torch.equal(a, b)
