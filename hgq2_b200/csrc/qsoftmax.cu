@@ -56,6 +56,7 @@ struct QC {
     float ci, cf;      // ln2 * 2^i, ln2 * 2^-f
     float kf, rbias;   // keep_negative as float; 0.5 for RND, 0 for TRN
     bool conv, sym;    // round-half-even; symmetric lower bound
+    bool clips;        // false: the quantizer only rounds (launch-uniform, so branching on it does not diverge)
 };
 
 __device__ __forceinline__ QC make_qc(float kf, float i, float f, int rm, int om) {
@@ -65,6 +66,7 @@ __device__ __forceinline__ QC make_qc(float kf, float i, float f, int rm, int om
     c.conv = (rm == RM_RND_CONV);
     c.rbias = (rm == RM_RND) ? 0.5f : 0.f;
     c.sym = (om == OM_SAT_SYM);
+    c.clips = (om != OM_NONE);
     if (om == OM_NONE) {
         c.lo = -INFINITY; c.hi = INFINITY; c.ci = 0.f; c.cf = 0.f;
     } else {
@@ -92,10 +94,16 @@ __device__ __forceinline__ float qc_fwd(float x, const QC &c, float &rounded) {
     rounded = qc_round(x, c);
     return clipf(rounded, c.lo, c.hi);
 }
-// same arithmetic as quantize_grad<> in hgq_math.cuh, with the mode folded into the constants
-__device__ __forceinline__ void qc_bwd(float g, float x, const QC &c, float &dx, float &di, float &df) {
-    const float xq = qc_round(x, c);
+// same arithmetic as quantize_grad<> in hgq_math.cuh, with the mode folded into the constants; xq = qc_round(x, c) is
+// passed in by callers that already have it from the forward chain
+__device__ __forceinline__ void qc_bwd_r(float g, float x, float xq, const QC &c, float &dx, float &di, float &df) {
     const float df_r = __fmul_rn(__fmul_rn(__fsub_rn(xq, x), -kLn2), g);
+    if (!c.clips) {  // rounding only: straight-through value gradient, no integer-bit gradient
+        dx = g;
+        di = 0.f;
+        df = df_r;
+        return;
+    }
     const bool pass = (xq >= c.lo) && (xq <= c.hi);
     const bool to_hi = (xq > c.hi) || (c.hi < c.lo);
     const bool to_lo = (xq < c.lo) && (c.lo < c.hi);
@@ -105,6 +113,9 @@ __device__ __forceinline__ void qc_bwd(float g, float x, const QC &c, float &dx,
     const float m = __fadd_rn(ghi, glo);
     di = c.sym ? __fmul_rn(m, c.ci) : __fadd_rn(__fmul_rn(ghi, c.ci), __fmul_rn(glo, c.ci));
     df = __fadd_rn(pass ? df_r : 0.f, __fmul_rn(c.sym ? m : ghi, c.cf));
+}
+__device__ __forceinline__ void qc_bwd(float g, float x, const QC &c, float &dx, float &di, float &df) {
+    qc_bwd_r(g, x, qc_round(x, c), c, dx, di, df);
 }
 
 template <int VE>
@@ -142,7 +153,8 @@ __device__ __forceinline__ float warp_sum(float v) {  // fixed butterfly: every 
 template <int VE>
 __device__ __forceinline__ void chain_fwd(const SmParams &P, const QC &q1, const QC &q2, const QC &q3, const QC &q4,
                                           const float (&s)[VE], float (&a)[VE], float (&e)[VE], float (&b)[VE], float &m,
-                                          float &S, float &t, float &t_rounded, float &v, float &u) {
+                                          float &S, float &t, float &t_rounded, float &v, float &u, float (&ra)[VE],
+                                          float (&rb)[VE], float &u_rounded) {
     float mx = kNegInf;
 #pragma unroll
     for (int j = 0; j < VE; ++j) mx = fmaxf(mx, s[j]);
@@ -150,17 +162,15 @@ __device__ __forceinline__ void chain_fwd(const SmParams &P, const QC &q1, const
     float part = 0.f;
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
-        float r;
-        a[j] = qc_fwd(__fsub_rn(m, s[j]), q1, r);
+        a[j] = qc_fwd(__fsub_rn(m, s[j]), q1, ra[j]);
         e[j] = expf(__fmul_rn(-a[j], P.scaler));
-        b[j] = qc_fwd(e[j], q2, r);
+        b[j] = qc_fwd(e[j], q2, rb[j]);
         part = __fadd_rn(part, b[j]);
     }
     S = warp_sum(part);
     t = qc_fwd(S, q3, t_rounded);
     v = __fdiv_rn(1.f, __fadd_rn(t, P.eps));
-    float r;
-    u = qc_fwd(v, q4, r);
+    u = qc_fwd(v, q4, u_rounded);
 }
 
 // grid = (rows_period, splits); CTA (p, sp) handles table row p for the batches sp, sp + splits, ... (warp w takes every
@@ -184,8 +194,8 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P
         const int64_t row = bt * P.rows_period + p;
         float s[VE], a[VE], e[VE], b[VE], y[VE];
         load_row<VE>(P.s + row * L, lane, s);
-        float m, S, t, tr, v, u;
-        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u);
+        float m, S, t, tr, v, u, ur, ra[VE], rb[VE];
+        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u, ra, rb, ur);
         am3 = fmaxf(am3, fabsf(tr));
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
@@ -202,8 +212,10 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P
     if (P.amax3 != nullptr && lane == 0) atomicMax(P.amax3, __float_as_uint(am3));
 }
 
+// Four resident CTAs (64 registers per thread): the per-row dependency chains (five warp reductions, exp, divide) need
+// many warps to hide; measured 1.46 ms at two CTAs, 1.22 at three, 1.16 at four for 134 M scores.
 template <int VE>
-__global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P) {
+__global__ void __launch_bounds__(kSmWarps * 32, 4) k_qsoftmax_bwd(const SmParams P) {
     __shared__ float red[kSmWarps][8];
     __shared__ float red5[kSmWarps][2][128];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -228,8 +240,8 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P
         float s[VE], g[VE], a[VE], e[VE], b[VE];
         load_row<VE>(P.s + row * L, lane, s);
         load_row<VE>(P.gy + row * L, lane, g);
-        float m, S, t, tr, v, u;
-        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u);
+        float m, S, t, tr, v, u, ur, ra[VE], rb[VE];
+        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u, ra, rb, ur);
         // y = Q5(b u): gradient to z, Q5's own parameters
         float gb[VE], gu_part = 0.f;
 #pragma unroll
@@ -244,9 +256,9 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P
         const float gu = warp_sum(gu_part);
         // u = Q4(v), v = 1 / (t + eps), t = Q3(S): row scalars, identical on every lane
         float gv, di4, df4, gS, di3, df3;
-        qc_bwd(gu, v, q4, gv, di4, df4);
+        qc_bwd_r(gu, v, ur, q4, gv, di4, df4);
         const float gt = __fmul_rn(-gv, __fmul_rn(v, v));
-        qc_bwd(gt, S, q3, gS, di3, df3);
+        qc_bwd_r(gt, S, tr, q3, gS, di3, df3);
         if (lane == 0) {
             acc[4] = __fadd_rn(acc[4], di3); acc[5] = __fadd_rn(acc[5], df3);
             acc[6] = __fadd_rn(acc[6], di4); acc[7] = __fadd_rn(acc[7], df4);
@@ -257,9 +269,9 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_bwd(const SmParams P
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
             float ge, di2, df2, di1, df1;
-            qc_bwd(__fadd_rn(gb[j], gS), e[j], q2, ge, di2, df2);
+            qc_bwd_r(__fadd_rn(gb[j], gS), e[j], rb[j], q2, ge, di2, df2);
             const float ga = __fmul_rn(ge, __fmul_rn(-P.scaler, e[j]));
-            qc_bwd(ga, __fsub_rn(m, s[j]), q1, gd[j], di1, df1);
+            qc_bwd_r(ga, __fsub_rn(m, s[j]), ra[j], q1, gd[j], di1, df1);
             acc[0] = __fadd_rn(acc[0], di1); acc[1] = __fadd_rn(acc[1], df1);
             acc[2] = __fadd_rn(acc[2], di2); acc[3] = __fadd_rn(acc[3], df2);
             gm_part = __fadd_rn(gm_part, gd[j]);
