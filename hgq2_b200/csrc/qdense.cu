@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
                 tc::commit(bar);
             }
             // every thread waits: the slab buffers are rewritten next and the epilogue reads TMEM
-            // one warp polls the mbarrier, the others park at the CTA barrier; the verdict is CTA-wide so that nobody is left
+            // one warp polls the mbarrier, the others park at the CTA barrier; the outcome is CTA-wide so that nobody is left
             // behind at a later barrier
             bool waited = (warp == 0) ? tc::mbar_wait(bar, phase) : true;
             phase ^= 1u;
