@@ -80,6 +80,7 @@ SIGNATURES: dict[str, tuple] = {
          c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p],
     ),
     'hgq_qconv2d_supported': (c_int, [c_int64] + [c_int] * 8),
+    'hgq_qconv2d_unit_stride_supported': (c_int, [c_int64] + [c_int] * 10),
     'hgq_qconv2d_fwd': (
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p] + [c_int] * 11 + [c_void_p, c_void_p],

@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
     const uint32_t idesc = tc::make_idesc_bf16(Np, false, false);
     const uint32_t img_base = tc::smem_u32(IMG), w_base = tc::smem_u32(WT);
     const int HWp = P.Hp * P.Wp;
+    const bool vec_c = (P.C & 3) == 0;
     const bool half_group = (P.C & 7) != 0;  // C % 8 == 4: the last channel group holds four channels
     const float act_lo = (P.act == ACT_RELU) ? 0.f : -INFINITY;
     const bool vec_out = (P.N % 4 == 0) && aligned(P.y, 16);
@@ -143,8 +144,17 @@ __global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
                         const int ih = yp - P.pt, iw = xp - P.pl;
                         if ((unsigned)ih < (unsigned)P.H && (unsigned)iw < (unsigned)P.W) {
                             const float *src = P.x + (((int64_t)b * P.H + ih) * P.W + iw) * P.C + cg * 8;
-                            v[i][0] = __ldg(reinterpret_cast<const float4 *>(src));
-                            if (!half_group || cg + 1 < ncg) v[i][1] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+                            if (vec_c) {
+                                v[i][0] = __ldg(reinterpret_cast<const float4 *>(src));
+                                if (!half_group || cg + 1 < ncg) v[i][1] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+                            } else {  // channel count not a multiple of four (an RGB image): pixels are not 16-byte aligned
+                                const int nc = min(8, P.C - cg * 8);
+                                float t8[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) t8[j] = (j < nc) ? __ldg(src + j) : 0.f;
+                                v[i][0] = make_float4(t8[0], t8[1], t8[2], t8[3]);
+                                v[i][1] = make_float4(t8[4], t8[5], t8[6], t8[7]);
+                            }
                         }
                     }
                 }
@@ -244,7 +254,7 @@ static size_t cl_smem(int MB, int halo, int ncg, int nsteps, int Np, int &npx) {
 
 static int cl_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW, int dh, int dw, ClGeom &g) {
     if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || KH <= 0 || KW <= 0 || N <= 0 || OH <= 0 || OW <= 0) return HGQ_ERR_SIZE;
-    if (C % 4 != 0 || N > 128) return HGQ_ERR_SIZE;
+    if (N > 128) return HGQ_ERR_SIZE;
     g.Np = 16;
     while (g.Np < N) g.Np <<= 1;
     g.Hp = OH + (KH - 1) * dh;
@@ -289,6 +299,12 @@ extern "C" int hgq_qconv2d_supported(int64_t B, int H, int W, int C, int KH, int
     return qconv2d_gather_supported(B, H, W, C, KH, KW, N, OH, OW);
 }
 
+extern "C" int hgq_qconv2d_unit_stride_supported(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW,
+                                                 int dil_h, int dil_w) {
+    ClGeom g;
+    return (dil_h > 0 && dil_w > 0 && cl_geom(B, H, W, C, KH, KW, N, OH, OW, dil_h, dil_w, g) == HGQ_OK) ? 1 : 0;
+}
+
 extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, const float *wq, const float *bq, int activation,
                                float *y, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w, int dil_h,
                                int dil_w, int pad_top, int pad_left, unsigned *status, void *stream) {
@@ -301,7 +317,7 @@ extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, c
     if (!unit)
         return qconv2d_gather_launch(x, B, H, W, C, wq, bq, activation, y, KH, KW, N, OH, OW, stride_h, stride_w, dil_h, dil_w,
                                      pad_top, pad_left, status, stream);
-    if (!aligned(x, 16) || !aligned(y, 4)) return HGQ_ERR_ALIGN;
+    if (!aligned(x, (C % 4 == 0) ? 16 : 4) || !aligned(y, 4)) return HGQ_ERR_ALIGN;
     ClParams p;
     p.x = x; p.wq = wq; p.bq = bq; p.y = y; p.status = status;
     p.Q = g.Q; p.num_tiles = g.tiles;

@@ -318,6 +318,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
     const uint32_t idesc = tc::make_idesc_bf16(acc_cols, true, true);
     const uint32_t img_base = tc::smem_u32(IMG), g_base = tc::smem_u32(GS);
     const int HWp = P.Hp * P.Wp;
+    const bool vec_c = (P.C & 3) == 0;
     const bool half_group = (P.C & 7) != 0;
     const bool relu = P.y != nullptr;
     const int n_units_x = npx * ncg, n_units_g = Pt * ng;
@@ -352,8 +353,17 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
                         const int ih = yp - P.pt, iw = xp - P.pl;
                         if ((unsigned)ih < (unsigned)P.H && (unsigned)iw < (unsigned)P.W) {
                             const float *src = P.x + (((int64_t)b * P.H + ih) * P.W + iw) * P.C + cg * 8;
-                            v[i][0] = __ldg(reinterpret_cast<const float4 *>(src));
-                            if (!half_group || cg + 1 < ncg) v[i][1] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+                            if (vec_c) {
+                                v[i][0] = __ldg(reinterpret_cast<const float4 *>(src));
+                                if (!half_group || cg + 1 < ncg) v[i][1] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+                            } else {  // channel count not a multiple of four (an RGB image): pixels are not 16-byte aligned
+                                const int nc = min(8, P.C - cg * 8);
+                                float t8[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) t8[j] = (j < nc) ? __ldg(src + j) : 0.f;
+                                v[i][0] = make_float4(t8[0], t8[1], t8[2], t8[3]);
+                                v[i][1] = make_float4(t8[4], t8[5], t8[6], t8[7]);
+                            }
                         }
                     }
                 }
@@ -503,7 +513,7 @@ struct CsGeom {
 
 static int cs_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW, int dh, int dw, CsGeom &g) {
     if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || KH <= 0 || KW <= 0 || N <= 0 || OH <= 0 || OW <= 0) return HGQ_ERR_SIZE;
-    if (C % 4 != 0 || N % 4 != 0 || N > 128 || KW > 16) return HGQ_ERR_SIZE;
+    if (N % 4 != 0 || N > 128 || KW > 16) return HGQ_ERR_SIZE;
     g.Np = 16;
     while (g.Np < N) g.Np <<= 1;
     g.ng = g.Np / 8;
@@ -577,6 +587,7 @@ extern "C" size_t hgq_qconv2d_wgrad_workspace(int64_t B, int H, int W, int C, in
     CwGeom g;
     CsGeom gs;
     if (cw_geom(B, H, W, C, KH, KW, N, OH, OW, g) != HGQ_OK && cs_geom(B, H, W, C, KH, KW, N, OH, OW, 1, 1, gs) != HGQ_OK) return 0;
+    if (C % 4 != 0 && cs_geom(B, H, W, C, KH, KW, N, OH, OW, 1, 1, gs) != HGQ_OK) return 0;  // only the unit-stride kernel takes such images
     return (size_t)3 * kNumSMs * ((size_t)KH * KW * C + 1) * N * sizeof(float);
 }
 
@@ -588,7 +599,7 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
     if ((y == nullptr) != (gm == nullptr)) return HGQ_ERR_NULL;
     if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0) return HGQ_ERR_SIZE;
     if (KH * dil_h > 127 || KW * dil_w > 127 || pad_top < 0 || pad_left < 0) return HGQ_ERR_SIZE;
-    if (!aligned(x, 16)) return HGQ_ERR_ALIGN;
+    if (!aligned(x, (C % 4 == 0) ? 16 : 4)) return HGQ_ERR_ALIGN;
     const int K = KH * KW * C;
     const int64_t stride = (int64_t)(K + 1) * N;
     cudaStream_t st = (cudaStream_t)stream;

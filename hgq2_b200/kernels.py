@@ -361,8 +361,13 @@ def qconv2d_supported(B, H, W, C, KH, KW, N, OH, OW) -> bool:
     return bool(lib().hgq_qconv2d_supported(B, H, W, C, KH, KW, N, OH, OW))
 
 
+def qconv2d_unit_stride_supported(B, H, W, C, KH, KW, N, OH, OW, dilation=(1, 1)) -> bool:
+    return bool(lib().hgq_qconv2d_unit_stride_supported(B, H, W, C, KH, KW, N, OH, OW, dilation[0], dilation[1]))
+
+
 def qconv2d_fwd(x, wq2d, bq, activation, KH, KW, out_hw, strides, dilation, pad_tl):
-    """Implicit-GEMM conv2d forward.  x [B, H, W, C] (C % 4 == 0, already quantised), wq2d [KH*KW*C, N]."""
+    """Implicit-GEMM conv2d forward.  x [B, H, W, C] (already quantised; C % 4 == 0 unless the unit-stride kernel takes the
+    shape), wq2d [KH*KW*C, N]."""
     require_cuda(x, wq2d, bq)
     x, wq2d = x.contiguous(), wq2d.contiguous()
     bq = None if bq is None else bq.contiguous()

@@ -193,16 +193,16 @@ def fused_dense_call(layer, inputs, n_contract: int, qkernel, qbias, training, a
 class QConv2dFusedFn(torch.autograd.Function):
     """act(conv2d(xq, wq) + bq), channels-last, on the implicit-GEMM tensor-core kernels (stride-1 input gradient).
 
-    ``xq`` is the already quantised image [B, H, W, C] and ``wq`` the quantised kernel [KH, KW, C, N].  Channels are
-    zero-padded to a multiple of four for the 16-byte patch gather.  Backward: one pass forms G = gy * (y > 0), the
+    ``xq`` is the already quantised image [B, H, W, C] and ``wq`` the quantised kernel [KH, KW, C, N].  ``cp`` channels of
+    zero padding are appended first when the kernels at hand need 16-byte pixels (0 when they read the image as it is).
+    Backward: one pass forms G = gy * (y > 0), the
     kernel and bias gradients; the input gradient is the same forward kernel run over G with the flipped, transposed
     kernel.
     """
 
     @staticmethod
-    def forward(ctx, xq, wq, bq, activation, strides, dilation, pad_tl, out_hw):
+    def forward(ctx, xq, wq, bq, activation, strides, dilation, pad_tl, out_hw, cp=0):
         KH, KW, C, N = wq.shape
-        cp = (-C) % 4
         if cp:
             xq = torch.nn.functional.pad(xq, (0, cp))
             wq = torch.nn.functional.pad(wq, (0, 0, 0, cp))
@@ -229,7 +229,7 @@ class QConv2dFusedFn(torch.autograd.Function):
                                      ((KH - 1) * dilation[0] - pad_tl[0], (KW - 1) * dilation[1] - pad_tl[1]))
             if cp:
                 dx = dx[..., :C]
-        return dx, (dwq if need_w else None), dbq, None, None, None, None, None
+        return dx, (dwq if need_w else None), dbq, None, None, None, None, None, None
 
 
 def fused_conv2d_call(layer, xq, qkernel, qbias):
@@ -245,13 +245,25 @@ def fused_conv2d_call(layer, xq, qkernel, qbias):
     KH, KW, _, N = qkernel.shape
     (pt, _), (pl, _) = layer._pads(H, W)
     _, OH, OW, _ = layer.compute_output_shape(tuple(xq.shape))
-    Cp = C + (-C) % 4
-    if N % 4 != 0 or KH * KW * N > 640 or Cp > 128:
+    dil = tuple(layer.dilation_rate)
+    if N % 4 != 0 or KH * KW * N > 640:
         return None
-    if not (kernels.qconv2d_supported(B, H, W, Cp, KH, KW, N, OH, OW) and kernels.qconv2d_supported(B, OH, OW, N, KH, KW, Cp, H, W)
-            and kernels.qconv2d_wgrad_supported(B, H, W, Cp, KH, KW, N, OH, OW)):
+
+    def covered(c):
+        if c > 128:
+            return False
+        if c % 4 == 0:
+            return (kernels.qconv2d_supported(B, H, W, c, KH, KW, N, OH, OW) and kernels.qconv2d_supported(B, OH, OW, N, KH, KW, c, H, W)
+                    and kernels.qconv2d_wgrad_supported(B, H, W, c, KH, KW, N, OH, OW))
+        # unaligned pixels (an RGB image): only the unit-stride kernels read them in place
+        return (kernels.qconv2d_unit_stride_supported(B, H, W, c, KH, KW, N, OH, OW, dil)
+                and kernels.qconv2d_unit_stride_supported(B, OH, OW, N, KH, KW, c, H, W, dil)
+                and kernels.qconv2d_wgrad_supported(B, H, W, c, KH, KW, N, OH, OW))
+
+    cp = 0 if covered(C) else (-C) % 4
+    if cp and not covered(C + cp):
         return None
-    return QConv2dFusedFn.apply(xq, qkernel, qbias, act_spec, tuple(layer.strides), tuple(layer.dilation_rate), (pt, pl), (OH, OW))
+    return QConv2dFusedFn.apply(xq, qkernel, qbias, act_spec, tuple(layer.strides), dil, (pt, pl), (OH, OW), cp)
 
 
 class AttnScoresFn(torch.autograd.Function):

@@ -47,7 +47,7 @@ class QBatchNormalization(QLayerBaseSingleInput):
         return self._bq
 
     def build(self, input_shape):
-        super().build(input_shape)
+        # the normalisation variables first, then the base classes' beta / ebops: the reference's variable order
         if self.axis < 0:
             self.axis += len(input_shape)
         dim = (int(input_shape[self.axis]),)
@@ -59,6 +59,7 @@ class QBatchNormalization(QLayerBaseSingleInput):
         self.moving_variance = self.add_weight(shape=dim, name='moving_variance', initializer=self.moving_variance_initializer,
                                                trainable=False)
         self._reduction_axes = tuple(a for a in range(len(input_shape)) if a != self.axis)
+        super().build(input_shape)
         self.bq.build(dim)
         self.bq.built = True
         self.kq.build(dim)

@@ -94,7 +94,7 @@ class QConv2D(QLayerBaseSingleInput):
         return (b, oh, ow, self.filters)
 
     def build(self, input_shape):
-        super().build(input_shape)
+        # kernel and bias before the base classes' beta / ebops: the reference's variable order
         c = int(input_shape[-1])
         self._kernel = self.add_weight(name='kernel', shape=self.kernel_size + (c, self.filters),
                                        initializer=self.kernel_initializer, regularizer=self.kernel_regularizer,
@@ -103,6 +103,7 @@ class QConv2D(QLayerBaseSingleInput):
             self._bias = self.add_weight(name='bias', shape=(self.filters,), initializer=self.bias_initializer,
                                          regularizer=self.bias_regularizer, constraint=self.bias_constraint)
             self.bias = self._bias.value
+        super().build(input_shape)
         self.kq.build(tuple(self._kernel.shape))
         self.kq.built = True
         if self.use_bias:

@@ -48,7 +48,8 @@ class QDense(QLayerBaseSingleInput):
         return self._kernel.value
 
     def build(self, input_shape):
-        super().build(input_shape)
+        # kernel and bias first, then the base classes' beta / ebops: the variable order of the reference, whose Keras base
+        # layer builds before QLayerBase adds its own (src/hgq/layers/core/base.py:186-203)
         in_dim = int(input_shape[-1])
         self._kernel = self.add_weight(name='kernel', shape=(in_dim, self.units), initializer=self.kernel_initializer,
                                        regularizer=self.kernel_regularizer, constraint=self.kernel_constraint)
@@ -56,6 +57,7 @@ class QDense(QLayerBaseSingleInput):
             self._bias = self.add_weight(name='bias', shape=(self.units,), initializer=self.bias_initializer,
                                          regularizer=self.bias_regularizer, constraint=self.bias_constraint)
             self.bias = self._bias.value
+        super().build(input_shape)
         self.n_parallel = prod(int(d) for d in input_shape[1:-1])
         if self.parallelization_factor < 0:
             self.parallelization_factor = self.n_parallel

@@ -93,7 +93,7 @@ class QEinsumDense(QLayerBaseSingleInput):
         return self._kernel.value
 
     def build(self, input_shape):
-        super().build(input_shape)
+        # kernel and bias before the base classes' beta / ebops: the reference's variable order
         kshape, bshape, full_out = analyze_einsum(self.equation, self.bias_axes, tuple(input_shape), self.partial_output_shape)
         self.full_output_shape = full_out
         self._kernel = self.add_weight(name='kernel', shape=kshape, initializer=self.kernel_initializer,
@@ -102,6 +102,7 @@ class QEinsumDense(QLayerBaseSingleInput):
             self._bias = self.add_weight(name='bias', shape=bshape, initializer=self.bias_initializer,
                                          regularizer=self.bias_regularizer, constraint=self.bias_constraint)
             self.bias = self._bias.value
+        super().build(input_shape)
         self.n_parallel = _einsum_free0_size(self.equation, input_shape)
         if self.parallelization_factor < 0:
             self.parallelization_factor = self.n_parallel

@@ -244,6 +244,10 @@ int hgq_qsoftmax_bwd(const float *gy, const float *s, float *ds, const uint8_t *
  * The transposed convolution that yields dL/dx is the same call on dL/dy with the flipped, transposed kernel.
  */
 int hgq_qconv2d_supported(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW);
+/* Shapes the unit-stride kernel takes (any channel count: an image whose C is not a multiple of 4 is read with scalar
+ * loads instead of being padded in memory). */
+int hgq_qconv2d_unit_stride_supported(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW, int dil_h,
+                                      int dil_w);
 int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, const float *wq, const float *bq, int activation,
                     float *y, int KH, int KW, int N, int OH, int OW, int stride_h, int stride_w, int dil_h,
                     int dil_w, int pad_top, int pad_left, unsigned *status, void *stream);

@@ -124,3 +124,28 @@ def test_max_pooling_matches_torch_including_ties(shape, pool, strides):
     assert torch.equal(y.cpu(), yr.detach())
     dx = kernels.maxpool2d_bwd(gy.cuda(), arg, shape, pool, strides)
     assert float((dx.cpu() - xr.grad).abs().max()) <= 1e-6 * float(gy.abs().max()) * pool[0] * pool[1]
+
+
+def test_rgb_image_is_read_in_place():
+    # C = 3: pixels are 12 bytes apart; the unit-stride kernels read them with scalar loads instead of a padded copy
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(3)
+    B, H, W, C, N = 6, 32, 32, 3, 16
+    x = torch.from_numpy(grid(rng, (B, H, W, C)))
+    w = torch.from_numpy(grid(rng, (3, 3, C, N), 5)).requires_grad_(True)
+    b = torch.from_numpy(grid(rng, (N,), 4)).requires_grad_(True)
+    xr = x.clone().requires_grad_()
+    y = ref_conv(xr, w, b, (1, 1), (1, 1), ((0, 0), (0, 0)), True)
+    gy = torch.from_numpy(rng.standard_normal(tuple(y.shape)).astype(np.float32))
+    (y * gy.double()).sum().backward()
+    assert kernels.qconv2d_unit_stride_supported(B, H, W, C, 3, 3, N, 30, 30)
+    yk = kernels.qconv2d_fwd(x.cuda(), w.detach().reshape(-1, N).cuda(), b.detach().cuda(), 'relu', 3, 3, (30, 30), (1, 1), (1, 1), (0, 0))
+    assert float((yk.cpu().double() - y.detach()).abs().max()) <= 2e-7 * float(y.abs().max())
+    gm, dw, db = kernels.qconv2d_wgrad(x.cuda(), gy.cuda(), yk, 3, 3, (1, 1), (1, 1), (0, 0), True)
+    assert float((dw.cpu().reshape(3, 3, C, N).double() - w.grad).abs().max()) <= 3e-5 * float(w.grad.abs().max())
+    assert float((db.cpu().double() - b.grad).abs().max()) <= 3e-5 * float(b.grad.abs().max())
+    wt = w.detach().flip(0, 1).permute(0, 1, 3, 2).reshape(9 * N, C).contiguous()
+    dx = kernels.qconv2d_fwd(gm, wt.cuda(), None, None, 3, 3, (H, W), (1, 1), (1, 1), (2, 2))
+    kernels.check_status(dx.device)
+    assert float((dx.cpu().double() - xr.grad).abs().max()) <= 5e-6 * float(xr.grad.abs().max())
