@@ -18,15 +18,16 @@ struct PoolParams {
 
 template <int VEC>
 __global__ void __launch_bounds__(kThreads) k_maxpool_fwd(const float *__restrict__ x, float *__restrict__ y,
-                                                         unsigned char *__restrict__ idx, const PoolParams P, int64_t n_units) {
+                                                         unsigned char *__restrict__ idx, const PoolParams P, int64_t n_units,
+                                                         const FastDiv div_cv, const FastDiv div_ow, const FastDiv div_oh) {
     const int CV = P.C / VEC;
     for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < n_units; u += (int64_t)gridDim.x * kThreads) {
-        const int cv = (int)(u % CV);
-        int64_t r = u / CV;
-        const int ow = (int)(r % P.OW);
-        r /= P.OW;
-        const int oh = (int)(r % P.OH);
-        const int64_t b = r / P.OH;
+        const uint32_t r0 = fastdiv((uint32_t)u, div_cv);  // n_units < 2^31 (checked on the host)
+        const int cv = (int)((uint32_t)u - r0 * (uint32_t)CV);
+        const uint32_t r1 = fastdiv(r0, div_ow);
+        const int ow = (int)(r0 - r1 * (uint32_t)P.OW);
+        const int64_t b = fastdiv(r1, div_oh);
+        const int oh = (int)(r1 - (uint32_t)b * (uint32_t)P.OH);
         const float *src = x + ((b * P.H + (int64_t)oh * P.SH) * P.W + (int64_t)ow * P.SW) * P.C + cv * VEC;
         float best[VEC];
         unsigned char arg[VEC];
@@ -106,6 +107,48 @@ __global__ void __launch_bounds__(kThreads) k_maxpool_bwd(const float *__restric
     }
 }
 
+
+// Non-overlapping windows (stride == pool size): one thread per output element group scatters its gradient to the
+// PH x PW positions of its window (the winner gets gy, the others zero), so every covered input element is written exactly
+// once and no search over windows is needed.  Rows / columns beyond the last full window are zeroed by the caller.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) k_maxpool_bwd_tiled(const float *__restrict__ gy, const unsigned char *__restrict__ idx,
+                                                               float *__restrict__ dx, const PoolParams P, int64_t n_units,
+                                                               const FastDiv div_cv, const FastDiv div_ow, const FastDiv div_oh) {
+    const int CV = P.C / VEC;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < n_units; u += (int64_t)gridDim.x * kThreads) {
+        const uint32_t r0 = fastdiv((uint32_t)u, div_cv);
+        const int cv = (int)((uint32_t)u - r0 * (uint32_t)CV);
+        const uint32_t r1 = fastdiv(r0, div_ow);
+        const int ow = (int)(r0 - r1 * (uint32_t)P.OW);
+        const uint32_t b = fastdiv(r1, div_oh);
+        const int oh = (int)(r1 - b * (uint32_t)P.OH);
+        const int64_t o = u * VEC;
+        float g[VEC];
+        unsigned char a[VEC];
+        if (VEC == 4) {
+            const float4 t = __ldcs(reinterpret_cast<const float4 *>(gy + o));
+            const uchar4 c = *reinterpret_cast<const uchar4 *>(idx + o);
+            g[0] = t.x; g[1 % VEC] = t.y; g[2 % VEC] = t.z; g[3 % VEC] = t.w;
+            a[0] = c.x; a[1 % VEC] = c.y; a[2 % VEC] = c.z; a[3 % VEC] = c.w;
+        } else {
+            g[0] = __ldcs(gy + o);
+            a[0] = idx[o];
+        }
+        float *dst = dx + (((int64_t)b * P.H + (int64_t)oh * P.PH) * P.W + (int64_t)ow * P.PW) * P.C + cv * VEC;
+        for (int ph = 0; ph < P.PH; ++ph)
+            for (int pw = 0; pw < P.PW; ++pw) {
+                const unsigned char code = (unsigned char)(ph * P.PW + pw);
+                float *q = dst + ((int64_t)ph * P.W + pw) * P.C;
+                if (VEC == 4)
+                    __stcs(reinterpret_cast<float4 *>(q), make_float4(a[0] == code ? g[0] : 0.f, a[1 % VEC] == code ? g[1 % VEC] : 0.f,
+                                                                       a[2 % VEC] == code ? g[2 % VEC] : 0.f, a[3 % VEC] == code ? g[3 % VEC] : 0.f));
+                else
+                    *q = a[0] == code ? g[0] : 0.f;
+            }
+    }
+}
+
 static int pool_check(const PoolParams &p) {
     if (p.B <= 0 || p.H <= 0 || p.W <= 0 || p.C <= 0 || p.PH <= 0 || p.PW <= 0 || p.SH <= 0 || p.SW <= 0) return HGQ_ERR_SIZE;
     if (p.PH * p.PW > 255 || p.PH > p.H || p.PW > p.W) return HGQ_ERR_SIZE;
@@ -130,11 +173,14 @@ extern "C" int hgq_maxpool2d_fwd(const float *x, float *y, unsigned char *argmax
     if (int e = pool_check(p)) return e;
     cudaStream_t st = (cudaStream_t)stream;
     const bool vec = (C % 4 == 0) && aligned(x, 16) && aligned(y, 16) && aligned(argmax, 4);
-    const int64_t n_units = B * OH * OW * (vec ? C / 4 : C);
+    const int cvn = vec ? C / 4 : C;
+    const int64_t n_units = B * OH * OW * cvn;
+    if (n_units >= ((int64_t)1 << 31)) return HGQ_ERR_SIZE;
+    const FastDiv d_cv = make_fastdiv((uint32_t)cvn), d_ow = make_fastdiv((uint32_t)OW), d_oh = make_fastdiv((uint32_t)OH);
     if (vec)
-        k_maxpool_fwd<4><<<pool_grid(n_units), kThreads, 0, st>>>(x, y, argmax, p, n_units);
+        k_maxpool_fwd<4><<<pool_grid(n_units), kThreads, 0, st>>>(x, y, argmax, p, n_units, d_cv, d_ow, d_oh);
     else
-        k_maxpool_fwd<1><<<pool_grid(n_units), kThreads, 0, st>>>(x, y, argmax, p, n_units);
+        k_maxpool_fwd<1><<<pool_grid(n_units), kThreads, 0, st>>>(x, y, argmax, p, n_units, d_cv, d_ow, d_oh);
     return check_launch();
 }
 
@@ -145,6 +191,21 @@ extern "C" int hgq_maxpool2d_bwd(const float *gy, const unsigned char *argmax, f
     if (int e = pool_check(p)) return e;
     cudaStream_t st = (cudaStream_t)stream;
     const bool vec = (C % 4 == 0) && aligned(gy, 16) && aligned(dx, 16) && aligned(argmax, 4);
+    if (stride_h == pool_h && stride_w == pool_w && B * OH * OW * (int64_t)C < ((int64_t)1 << 31)) {
+        // non-overlapping windows: scatter per window; input rows / columns behind the last full window get no gradient
+        if (OH * pool_h != H || OW * pool_w != W) {
+            cudaError_t ce = cudaMemsetAsync(dx, 0, (size_t)B * H * W * C * sizeof(float), st);
+            if (ce != cudaSuccess) return (int)ce;
+        }
+        const int cvn = vec ? C / 4 : C;
+        const int64_t n_out = B * OH * OW * cvn;
+        const FastDiv d_cv = make_fastdiv((uint32_t)cvn), d_ow = make_fastdiv((uint32_t)OW), d_oh = make_fastdiv((uint32_t)OH);
+        if (vec)
+            k_maxpool_bwd_tiled<4><<<pool_grid(n_out), kThreads, 0, st>>>(gy, argmax, dx, p, n_out, d_cv, d_ow, d_oh);
+        else
+            k_maxpool_bwd_tiled<1><<<pool_grid(n_out), kThreads, 0, st>>>(gy, argmax, dx, p, n_out, d_cv, d_ow, d_oh);
+        return check_launch();
+    }
     const int64_t n_units = B * H * W * (vec ? C / 4 : C);
     if (vec)
         k_maxpool_bwd<4><<<pool_grid(n_units), kThreads, 0, st>>>(gy, argmax, dx, p, n_units);
