@@ -628,6 +628,45 @@ def run_attn(args):
     print(json.dumps(out), flush=True)
 
 
+def run_bcast(args):
+    """Kernel-level benchmark of the broadcast-layout quantizer kernels (bitwidths per activation position, shared over
+    the batch): x [rows, P] with P = 4096 parameters (64 particles x 64 features), kif WRAP-training (round + abs-max)
+    forward and SAT forward / backward.  Algorithmic bytes per element: forward 8, backward 12 (g, x in; dx out)."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    rows, Pn = (args.batch or 65536), 4096
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(rows, Pn, device=dev, generator=gen) * 4
+    g = torch.randn(rows, Pn, device=dev, generator=gen)
+    k = torch.randint(0, 2, (1, Pn), device=dev, generator=gen).to(torch.uint8)
+    i = torch.randint(-2, 7, (1, Pn), device=dev, generator=gen).float()
+    f = torch.randint(0, 9, (1, Pn), device=dev, generator=gen).float()
+    peak, kind = measured_peaks()
+    out = {'kernel': 'k_fwd_bcast / k_bwd_bcast', 'rows': rows, 'params': Pn, 'peak_GBs': peak, 'peak_source': kind}
+    cases = {
+        'fwd round + abs-max (WRAP training)': (lambda: kernels.quantize_fwd(x, None, None, f, 'RND', 'NONE', training=True, want_absmax=True), 8.0),
+        'fwd SAT': (lambda: kernels.quantize_fwd(x, k, i, f, 'RND', 'SAT', training=True), 8.0),
+        'bwd round only (dx, df)': (lambda: kernels.quantize_bwd(g, x, None, None, f, 'RND', 'NONE', want_di=False), 12.0),
+        'bwd SAT (dx, di, df)': (lambda: kernels.quantize_bwd(g, x, k, i, f, 'RND', 'SAT'), 12.0),
+    }
+    for name, (fn, bpe) in cases.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        gbs = bpe * rows * Pn / (ms * 1e-3) / 1e9
+        out[name] = {'ms': round(ms, 4), 'achieved_GBs': round(gbs, 1), 'frac': round(gbs / peak, 4)}
+    print(json.dumps(out), flush=True)
+
+
 def run_qsoftmax(args):
     """Kernel-level benchmark of the fused quantised softmax (forward and backward) on the attention-score tensor of the
     transformer block: [batch, 4 heads, 64, 64] scores, softmax over the last axis, output bitwidth table [4 * 64, 64].
@@ -678,7 +717,7 @@ def main():
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
     ap.add_argument('--model', default='particle_tagger', help='model of --workload qat')
     ap.add_argument('--batch', type=int, default=0, help='batch of --workload qat (0 = the benchmark batch)')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'qdense', 'qdense_bwd', 'qsoftmax', 'qconv', 'attn', 'qat'],
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'bcast', 'qdense', 'qdense_bwd', 'qsoftmax', 'qconv', 'attn', 'qat'],
                     help="'qdense' times the fused dense forward kernel alone (for profiler captures)")
     ap.add_argument('--layer', type=int, default=1, choices=[1, 2, 3], help='convolution layer of --workload qconv')
     ap.add_argument('--rows', type=int, default=1 << 22)
@@ -693,6 +732,8 @@ def main():
         return run_qat_single(args)
     if args.workload == 'qdense_bwd':
         return run_qdense_bwd(args)
+    if args.workload == 'bcast':
+        return run_bcast(args)
     if args.workload == 'qconv':
         return run_qconv(args)
     if args.workload == 'attn':
