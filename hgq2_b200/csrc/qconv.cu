@@ -51,7 +51,10 @@ __device__ __forceinline__ void cl_split2(float v0, float v1, uint32_t &hi, uint
     lo = *reinterpret_cast<const uint32_t *>(&l2);
 }
 
-__global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
+// VEC_C: the channel count is a multiple of four (16-byte pixels, 128-bit loads); the other instantiation reads images
+// such as RGB with scalar loads and is kept apart so that the common case stays at 64 registers (four resident CTAs).
+template <bool VEC_C>
+__global__ void __launch_bounds__(kClThreads, VEC_C ? 4 : 3) k_qconv_s1(const ClParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int Np = P.Np, ncg = P.ncg, nsteps = P.nsteps, MB = P.MB, npx = P.npx;
     const int Pt = MB * 128;
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(kClThreads) k_qconv_s1(const ClParams P) {
     const uint32_t idesc = tc::make_idesc_bf16(Np, false, false);
     const uint32_t img_base = tc::smem_u32(IMG), w_base = tc::smem_u32(WT);
     const int HWp = P.Hp * P.Wp;
-    const bool vec_c = (P.C & 3) == 0;
+    constexpr bool vec_c = VEC_C;
     const bool half_group = (P.C & 7) != 0;  // C % 8 == 4: the last channel group holds four channels
     const float act_lo = (P.act == ACT_RELU) ? 0.f : -INFINITY;
     const bool vec_out = (P.N % 4 == 0) && aligned(P.y, 16);
@@ -328,8 +331,15 @@ extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, c
     p.div_row = make_fastdiv((uint32_t)g.Wp);
     p.div_cg = make_fastdiv((uint32_t)g.ncg);
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t ce = cudaFuncSetAttribute(k_qconv_s1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
-    if (ce != cudaSuccess) return (int)ce;
-    k_qconv_s1<<<g.grid, kClThreads, g.smem, st>>>(p);
+    cudaError_t ce;
+    if (C % 4 == 0) {
+        ce = cudaFuncSetAttribute(k_qconv_s1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_qconv_s1<true><<<g.grid, kClThreads, g.smem, st>>>(p);
+    } else {
+        ce = cudaFuncSetAttribute(k_qconv_s1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+        if (ce != cudaSuccess) return (int)ce;
+        k_qconv_s1<false><<<g.grid, kClThreads, g.smem, st>>>(p);
+    }
     return check_launch();
 }

@@ -290,6 +290,7 @@ struct CsParams {
     FastDiv div_img, div_row, div_cg;  // by Hp * Wp, by Wp and by the number of channel groups
 };
 
+template <bool VEC_C>  // see k_qconv_s1: scalar image loads live in their own instantiation
 __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int Np = P.Np, ncg = P.ncg, ng = P.ng, Pt = P.Pt, npx = P.npx, N = P.N;
@@ -318,7 +319,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
     const uint32_t idesc = tc::make_idesc_bf16(acc_cols, true, true);
     const uint32_t img_base = tc::smem_u32(IMG), g_base = tc::smem_u32(GS);
     const int HWp = P.Hp * P.Wp;
-    const bool vec_c = (P.C & 3) == 0;
+    constexpr bool vec_c = VEC_C;
     const bool half_group = (P.C & 7) != 0;
     const bool relu = P.y != nullptr;
     const int n_units_x = npx * ncg, n_units_g = Pt * ng;
@@ -617,9 +618,16 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
         q.div_img = make_fastdiv((uint32_t)(gs.Hp * gs.Wp));
         q.div_row = make_fastdiv((uint32_t)gs.Wp);
         q.div_cg = make_fastdiv((uint32_t)gs.ncg);
-        cudaError_t ce = cudaFuncSetAttribute(k_qconv_wgrad_s1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);
-        if (ce != cudaSuccess) return (int)ce;
-        k_qconv_wgrad_s1<<<gs.grid, kCwThreads, gs.smem, st>>>(q);
+        cudaError_t ce;
+        if (C % 4 == 0) {
+            ce = cudaFuncSetAttribute(k_qconv_wgrad_s1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);
+            if (ce != cudaSuccess) return (int)ce;
+            k_qconv_wgrad_s1<true><<<gs.grid, kCwThreads, gs.smem, st>>>(q);
+        } else {
+            ce = cudaFuncSetAttribute(k_qconv_wgrad_s1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);
+            if (ce != cudaSuccess) return (int)ce;
+            k_qconv_wgrad_s1<false><<<gs.grid, kCwThreads, gs.smem, st>>>(q);
+        }
         if (int e = check_launch()) return e;
         const int64_t nw = (int64_t)K * N;
         k_cw_stage2<<<(unsigned)((nw + 63) / 64), kThreads, 0, st>>>(q.part, stride, 0, dwq, nw, gs.grid);
