@@ -207,6 +207,33 @@ class Trainer:
             self._sloss = self._eager_step(self._sx, self._sy)
         self._graph = graph
 
+    def prefetch(self, hx, hy):
+        """Start the host-to-device copy of a (pinned) host batch on a copy stream of its own and return a handle for
+        ``step_prefetched``.  Two device staging slots alternate, so the copy of batch n + 1 overlaps step n."""
+        if not hasattr(self, '_copy_stream'):
+            self._copy_stream = torch.cuda.Stream()
+            self._slots = [None, None]
+            self._slot = 0
+        j = self._slot
+        self._slot ^= 1
+        dev = self.state.params.device
+        if self._slots[j] is None or self._slots[j][0].shape != hx.shape or self._slots[j][1].shape != hy.shape:
+            self._slots[j] = (torch.empty(hx.shape, dtype=hx.dtype, device=dev), torch.empty(hy.shape, dtype=hy.dtype, device=dev))
+        dx, dy = self._slots[j]
+        self._copy_stream.wait_stream(torch.cuda.current_stream())  # the slot's previous batch has been consumed
+        with torch.cuda.stream(self._copy_stream):
+            dx.copy_(hx, non_blocking=True)
+            dy.copy_(hy, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        return dx, dy, done
+
+    def step_prefetched(self, handle):
+        """``step`` on a batch started with ``prefetch``."""
+        dx, dy, done = handle
+        torch.cuda.current_stream().wait_event(done)
+        return self.step(dx, dy)
+
     def step(self, x, y):
         if self._graph is not None and x.shape == self._sx.shape and y.shape == self._sy.shape:
             self._sx.copy_(x, non_blocking=True)
