@@ -183,6 +183,9 @@ class Variable:
 # nodes on the same second stream.
 overlap_bookkeeping = True
 _side_streams: dict = {}
+# gradients of parameters first touched on the second stream are accumulated there on purpose
+if hasattr(torch.autograd.graph, 'set_warn_on_accumulate_grad_stream_mismatch'):
+    torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
 
 
 class bookkeeping:
