@@ -94,6 +94,8 @@ SIGNATURES: dict[str, tuple] = {
     'hgq_maxpool2d_bwd': (c_int, [c_void_p, c_void_p, c_void_p, c_int64] + [c_int] * 9 + [c_void_p]),
     'hgq_attn_heads_supported': (c_int, [c_int64, c_int, c_int, c_int]),
     'hgq_attn_heads_matmul': (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),
+    'hgq_track_kif': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    'hgq_track_kbi': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_int64, c_void_p]),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

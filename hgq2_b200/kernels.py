@@ -454,3 +454,23 @@ def attn_heads_matmul(kind: int, x, y, B: int, L: int, H: int, D: int):
         st = lib().hgq_attn_heads_matmul(kind, ptr(x), ptr(y), ptr(out), B, L, H, D, ptr(status_word(x.device)), stream_handle())
     check(st, 'hgq_attn_heads_matmul')
     return out
+
+
+def track_supported(*tensors) -> bool:
+    return all(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() for t in tensors) and \
+        len({t.numel() for t in tensors}) == 1
+
+
+def track_kif(absmax, f_raw, i_state, decay) -> None:
+    """In place: i_state <- max(i_state - decay, ceil(log2(absmax + 2^-rint(f_raw))))."""
+    with torch.cuda.device(absmax.device):
+        st = lib().hgq_track_kif(ptr(absmax), ptr(f_raw), ptr(i_state), ptr(decay), absmax.numel(), stream_handle())
+    check(st, 'hgq_track_kif')
+
+
+def track_kbi(absmax, b_raw, i_state, decay, symmetric: bool, lo: float, hi: float) -> None:
+    """In place: i_state <- clamp(max(i_state - decay, minimal_i_given_xb(absmax, rint(b_raw))), lo, hi)."""
+    with torch.cuda.device(absmax.device):
+        st = lib().hgq_track_kbi(ptr(absmax), ptr(b_raw), ptr(i_state), ptr(decay), 1 if symmetric else 0, float(lo), float(hi),
+                                 absmax.numel(), stream_handle())
+    check(st, 'hgq_track_kbi')

@@ -31,6 +31,34 @@ def _sync_absmax(absmax, inputs):
     return absmax
 
 
+def _fused_track_kif(absmax, f_var, i_var, decay_var) -> bool:
+    """i <- max(i - decay, minimal_i_given_xf(absmax, round(f))) in one kernel launch; False if the tensors do not qualify."""
+    from ... import kernels
+
+    am = absmax.reshape(i_var.value.shape)
+    if not (am.is_cuda and kernels.track_supported(am.contiguous(), f_var.value, i_var.value)):
+        return False
+    kernels.track_kif(am.contiguous(), f_var.value.detach(), i_var.value.detach(), decay_var.value)
+    return True
+
+
+def _fused_track_kbi(absmax, b_var, i_var, decay_var, symmetric) -> bool:
+    from ... import kernels
+
+    c = i_var.constraint
+    if c is None:
+        lo, hi = float('-inf'), float('inf')
+    elif isinstance(c, MinMax):
+        lo, hi = c.min_value, c.max_value
+    else:
+        return False
+    am = absmax.reshape(i_var.value.shape)
+    if not (am.is_cuda and kernels.track_supported(am.contiguous(), b_var.value, i_var.value)):
+        return False
+    kernels.track_kbi(am.contiguous(), b_var.value.detach(), i_var.value.detach(), decay_var.value, symmetric, lo, hi)
+    return True
+
+
 def minimal_i_given_xb(x, b, symmetric=False):
     """Fewest integer bits that hold |x| with b total bits (reference :16-22)."""
     eps = epsilon()
@@ -257,6 +285,8 @@ class FixedPointQuantizerKBI(FixedPointQuantizerBase):
         if self.overflow_mode == 'WRAP' and self.trainable:
             if training or training == 'tracing':  # noqa: E712 -- training may be a wrapper object
                 xr = _sync_absmax(self.bw_mapper.x_to_bw_absmax(inputs.detach()), inputs)
+                if training and _fused_track_kbi(xr, self._b, self._i, self._i_decay_speed, self.symmetric):
+                    return self.stateless_quantizer.round(inputs, self.f, False, self.seed_gen)
                 new_i = minimal_i_given_xb(xr, self.b.detach(), self.symmetric)
                 if training:
                     new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, new_i)
@@ -335,9 +365,11 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
                 rinputs, absmax = self._round_and_absmax(inputs, f)
                 if training:
                     with bookkeeping(absmax):  # nothing downstream in this forward pass reads the updated integer bits
-                        _new_i = minimal_i_given_xf(_sync_absmax(absmax, inputs), f.detach(), self.symmetric)
-                        new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i)
-                        self._i.assign(new_i)
+                        am = _sync_absmax(absmax, inputs)
+                        if not _fused_track_kif(am, self._f, self._i, self._i_decay_speed):
+                            _new_i = minimal_i_given_xf(am, f.detach(), self.symmetric)
+                            new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i)
+                            self._i.assign(new_i)
                     return rinputs
                 # tracing
                 _new_i = minimal_i_given_xf(_sync_absmax(absmax, inputs), f.detach(), self.symmetric)
@@ -358,7 +390,10 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
         f = self.f
 
         def track(absmax, inputs=None):
-            _new_i = minimal_i_given_xf(_sync_absmax(absmax.view(f.shape), inputs), f.detach(), self.symmetric)
+            am = _sync_absmax(absmax.view(f.shape), inputs)
+            if _fused_track_kif(am, self._f, self._i, self._i_decay_speed):
+                return
+            _new_i = minimal_i_given_xf(am, f.detach(), self.symmetric)
             self._i.assign(torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i))
 
         plan.update(overflow_mode='NONE', training=True, zero=False, i=None, f=f, track=track)

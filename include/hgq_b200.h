@@ -291,6 +291,17 @@ int hgq_attn_heads_supported(int64_t B, int L, int H, int D);
 int hgq_attn_heads_matmul(int kind, const float *x, const float *y, float *out, int64_t B, int L, int H, int D,
                           unsigned *status, void *stream);
 
+/* ---- integer-bit tracking of WRAP quantizers (training) ------------------------------------------------------------
+ * i_state <- max(i_state - decay, fewest integer bits that hold absmax), in place, one launch:
+ *   hgq_track_kif: minimal_i_given_xf, FixedPointQuantizerKIF.call (fixed_point_quantizer.py:25-31, 401-411);
+ *   hgq_track_kbi: minimal_i_given_xb, FixedPointQuantizerKBI.call (:16-22, 277-288), then the clamp [lo, hi] of the
+ *                  variable's MinMax constraint (pass -INFINITY / INFINITY for none).
+ * absmax >= 0 and the raw (unrounded) f / b variables have n elements each; decay is a device scalar.
+ */
+int hgq_track_kif(const float *absmax, const float *f_raw, float *i_state, const float *decay, int64_t n, void *stream);
+int hgq_track_kbi(const float *absmax, const float *b_raw, float *i_state, const float *decay, int symmetric, float lo,
+                  float hi, int64_t n, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*

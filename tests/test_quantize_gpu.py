@@ -170,3 +170,30 @@ def test_size_independent_properties_at_scale(K):
         lo = -k.float() * (hi if om == 'SAT_SYM' else torch.exp2(i))
         ok = (y <= hi) & (y >= lo) | (hi < lo) | ~nd
         assert bool(ok.all()), (rm, om)
+
+
+def test_fused_integer_bit_tracking_matches_the_elementwise_formulation():
+    # one-launch tracking kernels against minimal_i_given_xf / minimal_i_given_xb + max(i - decay, .), bit for bit
+    from hgq2_b200 import kernels
+    from hgq2_b200.quantizer.internal.fixed_point_quantizer import minimal_i_given_xb, minimal_i_given_xf
+
+    rng = np.random.default_rng(8)
+    n = 5000
+    absmax = torch.from_numpy(np.abs(rng.standard_normal(n) * 10 ** rng.uniform(-4, 3, n)).astype(np.float32)).cuda()
+    absmax[::97] = 0.0
+    absmax[1::97] = 2.0 ** torch.from_numpy(rng.integers(-6, 7, absmax[1::97].numel()).astype(np.float32)).cuda()  # exact powers of two
+    raw = torch.from_numpy((rng.integers(-3, 10, n) + rng.uniform(-0.4, 0.4, n)).astype(np.float32)).cuda()
+    i0 = torch.from_numpy(rng.uniform(-4, 8, n).astype(np.float32)).cuda()
+    decay = torch.tensor(0.01, device='cuda')
+    # kif
+    want = torch.maximum(i0 - decay, minimal_i_given_xf(absmax, torch.round(raw)))
+    got = i0.clone()
+    kernels.track_kif(absmax, raw, got, decay)
+    assert torch.equal(got, want)
+    # kbi, plain and symmetric, with and without a clamp
+    for sym in (False, True):
+        for lo, hi in ((float('-inf'), float('inf')), (-2.0, 5.0)):
+            want = torch.clamp(torch.maximum(i0 - decay, minimal_i_given_xb(absmax, torch.round(raw), sym)), lo, hi)
+            got = i0.clone()
+            kernels.track_kbi(absmax, raw, got, decay, sym, lo, hi)
+            assert torch.equal(torch.nan_to_num(got, nan=-777.0), torch.nan_to_num(want, nan=-777.0)), (sym, lo, hi)
