@@ -251,6 +251,11 @@ def take_prepared(layer):
     return p
 
 
+def current_pass() -> int:
+    """Number of the top-level layer call in progress (0 outside any call)."""
+    return _ctx.pass_id if _ctx.depth > 0 else 0
+
+
 def join_bookkeeping() -> None:
     """Make the current stream wait for the bookkeeping stream (before its results -- loss terms -- are consumed)."""
     if not torch.cuda.is_available():
@@ -266,6 +271,7 @@ class _CallContext(threading.local):
         self.depth = 0
         self.training = None
         self.root = None
+        self.pass_id = 0  # number of the current top-level call: per-pass memos (rounded bitwidths) are keyed on it
 
 
 _ctx = _CallContext()
@@ -372,6 +378,7 @@ class Layer(nn.Module):
         training = _ctx.training
         if top:
             _ctx.root = self
+            _ctx.pass_id += 1
             self._losses = []
         if _accepts_training(self):
             kwargs['training'] = training

@@ -9,10 +9,12 @@ tensors themselves (a few hundred elements).
 
 from __future__ import annotations
 
+import weakref
+
 import numpy as np
 import torch
 
-from ...backend import Constant, Initializer, bookkeeping, epsilon
+from ...backend import Constant, Initializer, bookkeeping, current_pass, epsilon
 from ...constraints import Constraint, MinMax
 from ...regularizers import Regularizer
 from .. import fixed_point_ops
@@ -110,6 +112,28 @@ class FixedPointQuantizerBase(TrainableQuantizerBase):
     @property
     def symmetric(self):
         return self._symmetric
+
+    def _rounded(self, var):
+        """round_conv(variable), computed once per forward pass and variable state: the properties b / i / f / bits are
+        read several times in one pass (quantizer call, fused-kernel plan, EBOPs), each read otherwise costing a launch
+        forward and a gradient sum backward."""
+        p = var.value
+        tag = (current_pass(), p._version, torch.is_grad_enabled(), p.requires_grad)
+        memo = self.__dict__.setdefault('_round_memo', {})
+        hit = memo.get(var.name)
+        if tag[0] != 0 and hit is not None and hit[0] == tag:
+            r = hit[1]()
+            if r is not None:
+                return r
+        r = round_conv(p)
+        # a weak reference: the result lives as long as the pass's autograd graph uses it and no longer (a strong one would
+        # keep the variable's gradient accumulator alive across steps, pinned to the stream of the step that made it)
+        memo[var.name] = (tag, weakref.ref(r))
+        return r
+
+    def _state_written(self, var) -> None:
+        """A kernel wrote the variable in place (no version bump): drop its memo."""
+        self.__dict__.get('_round_memo', {}).pop(var.name, None)
 
     @property
     def i_decay_speed(self):
@@ -256,11 +280,11 @@ class FixedPointQuantizerKBI(FixedPointQuantizerBase):
 
     @property
     def b(self):
-        return round_conv(self._b.value)
+        return self._rounded(self._b)
 
     @property
     def i(self):
-        return round_conv(self._i.value)
+        return self._rounded(self._i)
 
     @property
     def f(self):
@@ -286,6 +310,7 @@ class FixedPointQuantizerKBI(FixedPointQuantizerBase):
             if training or training == 'tracing':  # noqa: E712 -- training may be a wrapper object
                 xr = _sync_absmax(self.bw_mapper.x_to_bw_absmax(inputs.detach()), inputs)
                 if training and _fused_track_kbi(xr, self._b, self._i, self._i_decay_speed, self.symmetric):
+                    self._state_written(self._i)
                     return self.stateless_quantizer.round(inputs, self.f, False, self.seed_gen)
                 new_i = minimal_i_given_xb(xr, self.b.detach(), self.symmetric)
                 if training:
@@ -366,7 +391,9 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
                 if training:
                     with bookkeeping(absmax):  # nothing downstream in this forward pass reads the updated integer bits
                         am = _sync_absmax(absmax, inputs)
-                        if not _fused_track_kif(am, self._f, self._i, self._i_decay_speed):
+                        if _fused_track_kif(am, self._f, self._i, self._i_decay_speed):
+                            self._state_written(self._i)
+                        else:
                             _new_i = minimal_i_given_xf(am, f.detach(), self.symmetric)
                             new_i = torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i)
                             self._i.assign(new_i)
@@ -392,6 +419,7 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
         def track(absmax, inputs=None):
             am = _sync_absmax(absmax.view(f.shape), inputs)
             if _fused_track_kif(am, self._f, self._i, self._i_decay_speed):
+                self._state_written(self._i)
                 return
             _new_i = minimal_i_given_xf(am, f.detach(), self.symmetric)
             self._i.assign(torch.maximum(self._i.value.detach() - self.i_decay_speed, _new_i))
@@ -409,11 +437,11 @@ class FixedPointQuantizerKIF(FixedPointQuantizerBase):
 
     @property
     def i(self):
-        return round_conv(self._i.value)
+        return self._rounded(self._i)
 
     @property
     def f(self):
-        return round_conv(self._f.value)
+        return self._rounded(self._f)
 
     @property
     def kif(self):
