@@ -1,6 +1,13 @@
-"""Post-update clamps for bitwidth variables (mirror of src/hgq/constraints/__init__.py:11-69)."""
+"""Clamps applied to bitwidth variables after every optimizer update.
+
+Interface of src/hgq/constraints/__init__.py:11-69 (``MinMax``, ``Min``, ``Max``, ``Constant`` with Keras'
+``__call__`` / ``get_config`` protocol).  All four are one class of clamp with optional bounds; the fused optimizer
+kernel reads ``min_value`` / ``max_value`` straight from the instances.
+"""
 
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -8,61 +15,61 @@ __all__ = ['Constraint', 'MinMax', 'Min', 'Max', 'Constant']
 
 
 class Constraint:
+    """Identity; subclasses set the bounds they enforce."""
+
+    _fields: tuple = ()
+
     def __call__(self, w: torch.Tensor) -> torch.Tensor:
         return w
 
-    def get_config(self):
-        return {}
+    def get_config(self) -> dict:
+        return {name: getattr(self, name) for name in self._fields}
 
 
-class MinMax(Constraint):
-    """Constrains the weights to between min_value and max_value."""
-
-    def __init__(self, min_value, max_value):
-        self.min_value = float(min_value)
-        self.max_value = float(max_value)
+class _Clamp(Constraint):
+    min_value = -math.inf
+    max_value = math.inf
 
     def __call__(self, w):
-        return torch.clamp(w, self.min_value, self.max_value)
+        lo = None if self.min_value == -math.inf else self.min_value
+        hi = None if self.max_value == math.inf else self.max_value
+        return w if lo is None and hi is None else torch.clamp(w, min=lo, max=hi)
 
-    def get_config(self):
-        return {'min_value': self.min_value, 'max_value': self.max_value}
+
+class MinMax(_Clamp):
+    """min_value <= w <= max_value."""
+
+    _fields = ('min_value', 'max_value')
+
+    def __init__(self, min_value, max_value):
+        self.min_value, self.max_value = float(min_value), float(max_value)
+
+
+class Min(_Clamp):
+    """w >= min_value."""
+
+    _fields = ('min_value',)
+
+    def __init__(self, min_value):
+        self.min_value = float(min_value)
+
+
+class Max(_Clamp):
+    """w <= max_value."""
+
+    _fields = ('max_value',)
+
+    def __init__(self, max_value):
+        self.max_value = float(max_value)
 
 
 class Constant(Constraint):
-    """Constrains the weights to a constant value."""
+    """w == value everywhere."""
+
+    _fields = ('value',)
 
     def __init__(self, value):
         self.value = float(value)
 
     def __call__(self, w):
         return torch.full_like(w, self.value)
-
-    def get_config(self):
-        return {'value': self.value}
-
-
-class Min(Constraint):
-    """Constrains the weights to greater or equal than min_value."""
-
-    def __init__(self, min_value):
-        self.min_value = float(min_value)
-
-    def __call__(self, w):
-        return torch.clamp(w, min=self.min_value)
-
-    def get_config(self):
-        return {'min_value': self.min_value}
-
-
-class Max(Constraint):
-    """Constrains the weights to less or equal than max_value."""
-
-    def __init__(self, max_value):
-        self.max_value = float(max_value)
-
-    def __call__(self, w):
-        return torch.clamp(w, max=self.max_value)
-
-    def get_config(self):
-        return {'max_value': self.max_value}

@@ -127,26 +127,19 @@ class QBatchNormDense(QDense):
     Training uses the batch moments and updates the moving averages; otherwise the moving averages are used.
     """
 
-    def __init__(self, units, activation=None, use_bias=True, kernel_initializer='glorot_uniform', bias_initializer='zeros',
-                 kernel_regularizer=None, bias_regularizer=None, activity_regularizer=None, kernel_constraint=None,
-                 bias_constraint=None, scale=True, momentum=0.99, epsilon=1e-3, bn_gamma_initializer='ones',
-                 moving_mean_initializer='zeros', moving_variance_initializer='ones', bn_gamma_regularizer=None,
-                 bn_gamma_constraint=None, synchronized=False, kq_conf: None | QuantizerConfig = None,
-                 iq_conf: None | QuantizerConfig = None, bq_conf: None | QuantizerConfig = None, **kwargs):
-        assert use_bias, 'BatchNormDense must have `use_bias=True`'
-        super().__init__(units=units, activation=activation, use_bias=use_bias, kernel_initializer=kernel_initializer,
-                         bias_initializer=bias_initializer, kernel_regularizer=kernel_regularizer,
-                         bias_regularizer=bias_regularizer, activity_regularizer=activity_regularizer,
-                         kernel_constraint=kernel_constraint, bias_constraint=bias_constraint, kq_conf=kq_conf,
-                         iq_conf=iq_conf, bq_conf=bq_conf, **kwargs)
-        self.scale = scale
-        self.momentum = float(momentum)
+    def __init__(self, units, activation=None, use_bias=True, *, scale=True, momentum=0.99, epsilon=1e-3,
+                 bn_gamma_initializer='ones', moving_mean_initializer='zeros', moving_variance_initializer='ones',
+                 bn_gamma_regularizer=None, bn_gamma_constraint=None, synchronized=False, **dense_kwargs):
+        # every other argument (initializers, regularizers, constraints, kq_conf / iq_conf / bq_conf, ...) is QDense's
+        if not use_bias:
+            raise AssertionError('BatchNormDense must have `use_bias=True`')
+        super().__init__(units, activation=activation, use_bias=True, **dense_kwargs)
+        self.scale, self.synchronized = scale, synchronized
+        self.momentum, self.epsilon = float(momentum), epsilon
         self.bn_gamma_initializer = get_initializer(bn_gamma_initializer)
         self.moving_mean_initializer = get_initializer(moving_mean_initializer)
         self.moving_variance_initializer = get_initializer(moving_variance_initializer)
         self.bn_gamma_regularizer, self.bn_gamma_constraint = bn_gamma_regularizer, bn_gamma_constraint
-        self.epsilon = epsilon
-        self.synchronized = synchronized
 
     def build(self, input_shape):
         super().build(input_shape)

@@ -17,30 +17,21 @@ class QEinsumDenseBatchnorm(QEinsumDense):
     Otherwise the moving moments are used.  ``eps`` is the backend's fuzz factor (1e-7), as in the reference
     (einsum_dense_batchnorm.py:172), not the ``epsilon`` argument."""
 
-    def __init__(self, equation, output_shape, activation=None, bias_axes=None, kernel_initializer='glorot_uniform',
-                 bias_initializer='zeros', kernel_regularizer=None, bias_regularizer=None, kernel_constraint=None,
-                 bias_constraint=None, kq_conf: None | QuantizerConfig = None, iq_conf: None | QuantizerConfig = None,
-                 bq_conf: None | QuantizerConfig = None, normalize_axes: str | None = None, momentum=0.99, epsilon=1e-3,
-                 center=True, scale=True, beta_initializer='zeros', gamma_initializer='ones',
+    def __init__(self, equation, output_shape, activation=None, bias_axes=None, *, normalize_axes: str | None = None,
+                 momentum=0.99, epsilon=1e-3, center=True, scale=True, beta_initializer='zeros', gamma_initializer='ones',
                  moving_mean_initializer='zeros', moving_variance_initializer='ones', beta_regularizer=None,
-                 gamma_regularizer=None, beta_constraint=None, gamma_constraint=None, synchronized=False, **kwargs):
-        super().__init__(equation=equation, output_shape=output_shape, activation=activation, bias_axes=bias_axes,
-                         kernel_initializer=kernel_initializer, bias_initializer=bias_initializer,
-                         kernel_regularizer=kernel_regularizer, bias_regularizer=bias_regularizer,
-                         kernel_constraint=kernel_constraint, bias_constraint=bias_constraint, iq_conf=iq_conf,
-                         kq_conf=kq_conf, bq_conf=bq_conf, **kwargs)
-        self.synchronized = synchronized
-        self.momentum = float(momentum)
-        self.epsilon = float(epsilon)
-        self.center = center
-        self.scale = scale
+                 gamma_regularizer=None, beta_constraint=None, gamma_constraint=None, synchronized=False, **einsum_kwargs):
+        # every other argument (initializers, regularizers, constraints, kq_conf / iq_conf / bq_conf, ...) is QEinsumDense's
+        super().__init__(equation, output_shape, activation=activation, bias_axes=bias_axes, **einsum_kwargs)
+        self.synchronized, self.center, self.scale = synchronized, center, scale
+        self.momentum, self.epsilon = float(momentum), float(epsilon)
         self.gamma_initializer = get_initializer(gamma_initializer)
         self.moving_mean_initializer = get_initializer(moving_mean_initializer)
         self.moving_variance_initializer = get_initializer(moving_variance_initializer)
         self.gamma_regularizer, self.gamma_constraint = gamma_regularizer, gamma_constraint
-        normalize_axes = normalize_axes or bias_axes
-        assert normalize_axes is not None, 'Either normalize_axes or bias_axes must be provided.'
-        self.normalize_axes = normalize_axes
+        self.normalize_axes = normalize_axes or bias_axes
+        if self.normalize_axes is None:
+            raise AssertionError('Either normalize_axes or bias_axes must be provided.')
         self._check_normalize_axes()
 
     prepare_params = None  # kernel and bias depend on the batch statistics: nothing to queue ahead
