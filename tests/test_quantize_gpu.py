@@ -197,3 +197,21 @@ def test_fused_integer_bit_tracking_matches_the_elementwise_formulation():
             got = i0.clone()
             kernels.track_kbi(absmax, raw, got, decay, sym, lo, hi)
             assert torch.equal(torch.nan_to_num(got, nan=-777.0), torch.nan_to_num(want, nan=-777.0)), (sym, lo, hi)
+
+
+def test_empty_inputs_are_no_ops():
+    # zero elements (an empty batch): nothing is launched, empty results come back, reductions are zero
+    from hgq2_b200 import kernels
+
+    dev = 'cuda'
+    f = torch.full((1, 7), 3.0, device=dev)
+    k = torch.ones((1, 7), dtype=torch.uint8, device=dev)
+    i = torch.full((1, 7), 2.0, device=dev)
+    x = torch.empty((0, 7), device=dev)
+    y = kernels.quantize_fwd(x, k, i, f, 'RND', 'SAT', training=True)
+    assert tuple(y.shape) == (0, 7)
+    dx, di, df = kernels.quantize_bwd(x.clone(), x, k, i, f, 'RND', 'SAT')
+    assert tuple(dx.shape) == (0, 7) and float(di.abs().sum()) == 0.0 and float(df.abs().sum()) == 0.0
+    e = torch.empty(0, device=dev)
+    ye = kernels.quantize_fwd(e, torch.empty(0, dtype=torch.uint8, device=dev), e, e, 'TRN', 'WRAP')
+    assert ye.numel() == 0
