@@ -357,14 +357,14 @@ def run_qat_single(args):
     import torch.nn.functional as F
 
     from hgq2_b200 import workloads
-    from hgq2_b200.train import Trainer
+    from hgq2_b200.train import Trainer, sparse_categorical_crossentropy
 
     dev = torch.device('cuda', 0)
     torch.cuda.set_device(dev)
     builder, batch, make_x, classes, _ = QAT_CONFIGS[args.model]
     batch = args.batch or batch
     model = workloads.build(getattr(workloads, builder)(), device=dev)
-    tr = Trainer(model, F.cross_entropy)
+    tr = Trainer(model, sparse_categorical_crossentropy)
     x = torch.from_numpy(make_x(np.random.default_rng(1), batch)).to(dev)
     y = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch)).to(dev)
     for _ in range(max(1, args.warmup)):
@@ -389,7 +389,7 @@ def run_qat(args, dev, world, rank, peak):
     import torch.nn.functional as F
 
     from hgq2_b200 import workloads
-    from hgq2_b200.train import DataParallel, Trainer, shard_batch
+    from hgq2_b200.train import DataParallel, Trainer, shard_batch, sparse_categorical_crossentropy
 
     out = []
     dp = DataParallel() if world > 1 else None
@@ -402,7 +402,7 @@ def run_qat(args, dev, world, rank, peak):
             cpu = None
             if rank == 0 and world == 1 and not args.no_cpu:
                 cpu = cpu_qat_step(name, model, make_x, classes)  # twin of the freshly built model, before any step
-            tr = Trainer(model, F.cross_entropy, dp=dp)
+            tr = Trainer(model, sparse_categorical_crossentropy, dp=dp)
             sl = shard_batch(batch, rank, world)
             hx = torch.from_numpy(make_x(np.random.default_rng(1), batch)[sl]).pin_memory()
             hy = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch)[sl]).pin_memory()
@@ -438,6 +438,9 @@ def run_qat(args, dev, world, rank, peak):
                 dist.all_reduce(ms, op=dist.ReduceOp.MAX)
                 dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
             sps = batch / (float(ms.item()) * 1e-3)
+            from hgq2_b200 import kernels as _k
+
+            _k.check_status(dev)  # a bounded tensor-core wait that gave up would have left its mark here
             out.append({
                 'model': name, 'global_batch': batch, 'ms_per_step': round(float(ms.item()), 4),
                 'samples_per_s': round(sps, 1), 'e2e_samples_per_s': round(batch / (float(e2e_ms.item()) * 1e-3), 1),

@@ -96,6 +96,8 @@ SIGNATURES: dict[str, tuple] = {
     'hgq_attn_heads_matmul': (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),
     'hgq_track_kif': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     'hgq_track_kbi': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_int64, c_void_p]),
+    'hgq_softmax_xent_workspace': (c_size_t, [c_int64]),
+    'hgq_softmax_xent': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     'hgq_ebops_dense': (
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,

@@ -416,7 +416,13 @@ extern "C" int hgq_quantize_fwd(const float *x, const uint8_t *k, const float *i
                                 float *absmax, int64_t n, int64_t period, int round_mode, int overflow_mode,
                                 unsigned flags, void *stream) {
     if (int e = check_common(x, f, n, period, round_mode, overflow_mode, flags)) return e;
-    if (n == 0) return HGQ_OK;
+    if (n == 0) {
+        if (absmax != nullptr && period > 0) {  // the maximum over zero rows of |.|
+            const cudaError_t ce = cudaMemsetAsync(absmax, 0, (size_t)period * sizeof(float), (cudaStream_t)stream);
+            if (ce != cudaSuccess) return (int)ce;
+        }
+        return HGQ_OK;
+    }
     if (y == nullptr) return HGQ_ERR_NULL;
     // WRAP leaves the value unwrapped while training (the integer bits are tracked instead).
     int om = overflow_mode;
@@ -453,7 +459,16 @@ extern "C" int hgq_quantize_bwd(const float *g, const float *x, const uint8_t *k
                                 void *stream) {
     if (int e = check_common(x, f, n, period, round_mode, overflow_mode, flags)) return e;
     if (flags & HGQ_FLAG_ZERO_NONPOS) return HGQ_ERR_MODE;  // the backward exists for training only
-    if (n == 0) return HGQ_OK;
+    if (n == 0) {
+        // an empty batch: the sums over zero rows are zero
+        cudaStream_t st0 = (cudaStream_t)stream;
+        for (float *out : {df, di}) {
+            if (out == nullptr || period <= 0) continue;
+            const cudaError_t ce = cudaMemsetAsync(out, 0, (size_t)period * sizeof(float), st0);
+            if (ce != cudaSuccess) return (int)ce;
+        }
+        return HGQ_OK;
+    }
     if (g == nullptr || df == nullptr) return HGQ_ERR_NULL;
     if (dx == nullptr && period == n) return HGQ_ERR_NULL;
     int om = overflow_mode;

@@ -474,3 +474,17 @@ def track_kbi(absmax, b_raw, i_state, decay, symmetric: bool, lo: float, hi: flo
         st = lib().hgq_track_kbi(ptr(absmax), ptr(b_raw), ptr(i_state), ptr(decay), 1 if symmetric else 0, float(lo), float(hi),
                                  absmax.numel(), stream_handle())
     check(st, 'hgq_track_kbi')
+
+
+def softmax_xent(logits, labels):
+    """Mean softmax cross-entropy of [B, C] logits against int64 labels.  Returns (loss scalar, dloss/dlogits)."""
+    require_cuda(logits, labels)
+    logits, labels = logits.contiguous(), labels.contiguous()
+    B, C = logits.shape
+    loss = torch.empty((), dtype=torch.float32, device=logits.device)
+    dlogits = torch.empty_like(logits)
+    ws = workspace(lib().hgq_softmax_xent_workspace(B), logits.device, slot=5)
+    with torch.cuda.device(logits.device):
+        st = lib().hgq_softmax_xent(ptr(logits), ptr(labels), ptr(loss), ptr(dlogits), B, C, ptr(ws), ws.numel(), stream_handle())
+    check(st, 'hgq_softmax_xent')
+    return loss, dlogits

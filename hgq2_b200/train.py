@@ -155,6 +155,29 @@ class DataParallel:
         _fpq.absmax_sync_hook = self._prev
 
 
+class _SoftmaxXentFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels):
+        from . import kernels
+
+        loss, dlogits = kernels.softmax_xent(logits, labels)
+        ctx.save_for_backward(dlogits)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits * g, None
+
+
+def sparse_categorical_crossentropy(logits, labels):
+    """Mean softmax cross-entropy from logits with integer labels (what the reference's models are compiled with), on the
+    fused kernel when the logits are a CUDA [B, C <= 64] fp32 matrix with int64 labels; torch's otherwise."""
+    if logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.shape[1] <= 64 and labels.dtype == torch.int64:
+        return _SoftmaxXentFn.apply(logits, labels)
+    return torch.nn.functional.cross_entropy(logits, labels)
+
+
 class Trainer:
     """One model, one flat bucket, one fused optimizer; ``step(x, y)`` runs a full QAT step and returns the loss.
 

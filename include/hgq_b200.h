@@ -302,6 +302,15 @@ int hgq_track_kif(const float *absmax, const float *f_raw, float *i_state, const
 int hgq_track_kbi(const float *absmax, const float *b_raw, float *i_state, const float *decay, int symmetric, float lo,
                   float hi, int64_t n, void *stream);
 
+/* ---- softmax cross-entropy from logits, integer labels, mean over the batch ------------------------------------------
+ * The task loss the reference's models are compiled with (keras SparseCategoricalCrossentropy(from_logits=True); Keras,
+ * not HGQ2, owns it).  loss (device scalar) and dlogits = (softmax - onehot) / B in one pass; C <= 64;
+ * workspace: hgq_softmax_xent_workspace(B) bytes.  Deterministic (fixed-order reduction).
+ */
+size_t hgq_softmax_xent_workspace(int64_t B);
+int hgq_softmax_xent(const float *logits, const int64_t *labels, float *loss, float *dlogits, int64_t B, int C,
+                     void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- K3: EBOPs ---------------------------------------------------------------------------- */
 
 /*

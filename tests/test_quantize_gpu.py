@@ -208,8 +208,8 @@ def test_empty_inputs_are_no_ops():
     k = torch.ones((1, 7), dtype=torch.uint8, device=dev)
     i = torch.full((1, 7), 2.0, device=dev)
     x = torch.empty((0, 7), device=dev)
-    y = kernels.quantize_fwd(x, k, i, f, 'RND', 'SAT', training=True)
-    assert tuple(y.shape) == (0, 7)
+    y, amax = kernels.quantize_fwd(x, k, i, f, 'RND', 'SAT', training=True, want_absmax=True)
+    assert tuple(y.shape) == (0, 7) and float(amax.abs().sum()) == 0.0
     dx, di, df = kernels.quantize_bwd(x.clone(), x, k, i, f, 'RND', 'SAT')
     assert tuple(dx.shape) == (0, 7) and float(di.abs().sum()) == 0.0 and float(df.abs().sum()) == 0.0
     e = torch.empty(0, device=dev)

@@ -152,3 +152,43 @@ def test_graph_captured_step_equals_eager_steps():
     assert l0 == l1, (l0, l1)
     assert torch.equal(p0, p1)
     assert e0 == e1
+
+
+@pytest.mark.parametrize('B,C', [(1, 5), (777, 5), (65536, 10), (300, 64)])
+def test_fused_softmax_cross_entropy(B, C):
+    from hgq2_b200.train import sparse_categorical_crossentropy
+
+    rng = np.random.default_rng(B + C)
+    z = torch.from_numpy((rng.standard_normal((B, C)) * 3).astype(np.float32))
+    y = torch.from_numpy(rng.integers(0, C, B))
+    zc = z.clone().double().requires_grad_()
+    ref = F.cross_entropy(zc, y)
+    (ref * 1.7).backward()
+    zg = z.cuda().requires_grad_()
+    loss = sparse_categorical_crossentropy(zg, y.cuda())
+    (loss * 1.7).backward()
+    assert abs(float(loss) - float(ref)) <= 1e-6 * max(abs(float(ref)), 1.0)
+    err = float((zg.grad.cpu().double() - zc.grad).abs().max() / zc.grad.abs().max())
+    assert err <= 1e-5, err
+
+
+def test_steps_with_the_fused_loss_match_the_oracle():
+    from hgq2_b200 import workloads
+    from hgq2_b200.train import Trainer, sparse_categorical_crossentropy
+
+    rng = np.random.default_rng(1)
+    x_np = rng.standard_normal((2048, 16)).astype(np.float32)
+    y_np = np.random.default_rng(2).integers(0, 5, 2048)
+    model = workloads.build(workloads.jet_tagger_mlp())
+    twin, pairs = OT.mirror_model(model)
+    oopt = OT.OracleAdam(pairs, lr=1e-3)
+    tr = Trainer(model, sparse_categorical_crossentropy)
+    _, loss = tr.forward_backward(torch.from_numpy(x_np).cuda(), torch.from_numpy(y_np).cuda())
+    oloss = ce(twin(torch.from_numpy(x_np), training=True), torch.from_numpy(y_np)) + sum(twin.losses) + oopt.regularization_loss()
+    oloss.backward()
+    close(loss, oloss, 1e-5, 'loss')
+    for leaf, var, _, _ in pairs:
+        g = var.value.grad
+        if var.regularizer is not None:
+            g = g + var.regularizer.l1
+        close(g, leaf.grad, 1e-4 if leaf.numel() > 4 else 2e-3, f'gradient of {var.path}')
