@@ -24,6 +24,7 @@
 // Several CTAs are resident per SM, so one CTA's loads overlap another's MMA and epilogue.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include "hgq_common.cuh"
 #include "hgq_math.cuh"
@@ -501,6 +502,19 @@ __global__ void __launch_bounds__(kThreads) k_amax_stage2(const unsigned *__rest
     out[e] = __uint_as_float(m);
 }
 
+int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round_mode, const float *wq, const float *bq,
+                     int activation, float *y, unsigned *amax_part, int64_t M, int K, int N, int Kpad, int Npad, int Kt,
+                     unsigned *status, cudaStream_t st, int *grid);
+
+// HGQ_QDENSE_WS=0 in the environment keeps every call on the general kernel (for comparisons).
+static bool ws_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("HGQ_QDENSE_WS");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
+}
+
 struct QdGeom {
     int Kpad, Npad, Kt, grid;
     size_t smem;
@@ -575,6 +589,22 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
     cudaStream_t st = (cudaStream_t)stream;
     const bool fastq = (qf != nullptr) && (om == OM_NONE);
     const bool conv = (round_mode == RM_RND_CONV);
+    if (fastq && ws_enabled()) {
+        // the common training case has a warp-specialised kernel of its own
+        int ws_grid = 0;
+        const int r = qdense_ws_launch(x, qf, rows_period, round_mode, wq, bq, activation, y, p.amax_part, M, K, N, g.Kpad,
+                                       g.Npad, g.Kt, status, st, &ws_grid);
+        if (r < 0) return -r;
+        if (r == 1) {
+            if (int e = check_launch()) return e;
+            if (absmax) {
+                const int table = rows_period * K;
+                k_amax_stage2<<<(table + kThreads - 1) / kThreads, kThreads, 0, st>>>((const unsigned *)workspace, absmax, table, ws_grid);
+                return check_launch();
+            }
+            return HGQ_OK;
+        }
+    }
     int amax_mode = AMAX_NONE;
     if (absmax) {
         if (!fastq) amax_mode = AMAX_ATOMIC;

@@ -1,0 +1,515 @@
+// K2w (dense / einsum-dense forward, warp-specialised): y = act( iq(x) @ Wq + bq ) for the training-mode case in which
+// the input quantizer only rounds (WRAP overflow in training), the contract of k_qdense_fwd in qdense.cu.
+//
+// Stands in for QDense.call (src/hgq/layers/core/dense.py:60-68) and QEinsumDense.call
+// (src/hgq/layers/core/einsum_dense.py:72-83); the per-entry max |round(x)| of the WRAP integer-bit tracking
+// (fixed_point_quantizer.py:405-413) is a side output.
+//
+// One persistent CTA per SM with three roles that meet only at mbarriers, never at a CTA-wide barrier:
+//   warps 0-7   producers: fetch a 128 x 64 fp32 slab (cp.async into thread-private slots, two slabs ahead), quantise it in
+//               registers, split every value exactly into bf16 terms and store them as no-swizzle K-major core matrices
+//               into one of two operand stages; arrive on full[stage];
+//   warp 16     waits for full[stage] and for a free accumulator, issues tcgen05.mma (M = 128, N = padded N, K = 16) for
+//               every pair of terms, commits to empty[stage] and, after the last slab of a tile, to acc_full[acc];
+//   warps 8-15  epilogue: wait for acc_full[acc], read their 32 rows x half of the columns with tcgen05.ld, release the
+//               accumulator (acc_empty[acc]), add bias, apply the activation, transpose through a warp-private 4 KB
+//               buffer and write whole 128-byte row pieces.
+// With two operand stages and two accumulators in tensor memory the conversion of tile t + 1 overlaps the products of
+// tile t and the write-out of tile t - 1.  HBM-bound: 4 (K + N) bytes per row.
+// Every wait is bounded (polls and wall time); a wait that gives up sets an abort word that ends every role's loop, the
+// status word tells the host, and the CTA still frees its tensor memory.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "hgq_common.cuh"
+#include "hgq_math.cuh"
+#include "tc05.cuh"
+
+namespace hgq {
+
+constexpr int kWsProd = 256;                         // producer threads
+constexpr int kWsThreads = 544;                      // 8 producer warps, 8 epilogue warps, 1 issuing warp
+constexpr int kWsTileM = 128;
+constexpr int kWsKC = 64;                            // K slab of one operand stage
+constexpr int kWsTermBytes = kWsTileM * kWsKC * 2;   // 16 KB per bf16 term
+constexpr int kWsStageBytes = 3 * kWsTermBytes;      // hi, lo and (rarely non-zero) third term
+constexpr int kWsFetchBytes = kWsTileM * kWsKC * 4;  // raw fp32 slab in flight
+constexpr int kWsOutBytes = 8 * 4096;                // one transposition buffer per epilogue warp
+constexpr unsigned kWsTimeout = 1u;                  // status bit, same meaning as in the other tensor-core kernels
+
+// Abs-max bookkeeping (max over rows of |round(x)| per entry of the quantizer table):
+//   REGS   rows_period == 1, one K slab: a thread's 8 columns never change; maxima in registers, merged through a one-row
+//          table in shared memory at the end
+//   ROWS1  rows_period == 32, ROWS2 rows_period == 64, one K slab: every table entry belongs to exactly one thread, which
+//          keeps it in a register and writes it out at the end
+//   PLAIN  rows_period == 128 or several K slabs with rows_period in {32, 64, 128}: rows that share a table entry fall to
+//          the same thread, plain read-modify-write of a table in shared memory
+enum : int { WS_AMAX_NONE = 0, WS_AMAX_REGS = 1, WS_AMAX_PLAIN = 2, WS_AMAX_ROWS1 = 3, WS_AMAX_ROWS2 = 4 };
+
+struct WsParams {
+    const float *x, *qf, *wq, *bq;
+    float *y;
+    unsigned *amax_part;  // [gridDim.x, rows_period * K] abs-max partials, or nullptr
+    unsigned *status;
+    int64_t M, num_tiles;
+    int K, N, Kpad, Npad, Kt, rows_period;
+    int rm, act;
+    int depth;            // raw slabs in flight ahead of the conversion: 1 or 2
+};
+
+__device__ __forceinline__ void ws_arrive(uint64_t *bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 st;\n\t"
+        "mbarrier.arrive.shared::cta.b64 st, [%0];\n\t"
+        "}\n" ::"r"(tc::smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ unsigned long long ws_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Wait for a phase of an mbarrier; gives up when another role has raised the abort word, after 2 s of wall time or
+// after 2^24 polls, whichever comes first.
+__device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word) {
+    if (tc::mbar_wait(bar, parity, 64)) return true;
+    const unsigned long long t0 = ws_now();
+    for (uint32_t it = 0; it < (1u << 16); ++it) {
+        if (tc::mbar_wait(bar, parity, 256)) return true;
+        if (*abort_word) return false;
+        if (ws_now() - t0 > 2000000000ull) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ int ws_swz(int r, int C) { return C == 8 ? (r & 7) : (C == 4 ? ((r >> 1) & 3) : ((r >> 2) & 1)); }
+
+template <bool RCONV, int AMAX>
+__global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams P) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    // carve: operand stages | raw-slab slots | transposition buffers | B terms | bias | exponent table | abs-max table |
+    // barriers, TMEM slot, flags
+    unsigned char *A = smem;
+    unsigned char *fetch = A + 2 * kWsStageBytes;
+    unsigned char *outst = fetch + P.depth * kWsFetchBytes;
+    unsigned char *B = outst + kWsOutBytes;
+    const int b_term_bytes = P.Kpad * P.Npad * 2;
+    float *bias_s = reinterpret_cast<float *>(B + 3 * b_term_bytes);
+    const int Ke = P.Kt + 8;  // row stride of the exponent table: 8-byte reads of 8 rows hit 8 bank pairs
+    const int tab_bytes = (P.rows_period * Ke + 15) / 16 * 16;
+    unsigned char *etab = reinterpret_cast<unsigned char *>(bias_s + P.Npad);
+    const int Ks = P.Kt + 4;  // abs-max table row: 16-byte accesses of 8 rows hit 8 bank groups
+    float *amax_t = reinterpret_cast<float *>(etab + tab_bytes);
+    const int amax_elems = (AMAX == WS_AMAX_REGS || AMAX == WS_AMAX_PLAIN) ? P.rows_period * Ks : 0;
+    uint64_t *full = reinterpret_cast<uint64_t *>(amax_t + amax_elems);
+    uint64_t *empty = full + 2, *acc_full = full + 4, *acc_empty = full + 6;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(full + 8);
+    int *dirty3 = reinterpret_cast<int *>(tmem_slot + 1);  // per stage: some tile needed the third term (sticky)
+    int *abort_word = dirty3 + 2;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = P.K, N = P.N, Kpad = P.Kpad, Npad = P.Npad;
+    const uint32_t tmem_cols = 2 * Npad < 32 ? 32u : (uint32_t)(2 * Npad);  // two accumulators; Npad is a power of two
+
+    // ---- one-time set-up (all threads) -------------------------------------------------------------------------------
+    if (tid == 0) {
+        for (int s = 0; s < 2; ++s) {
+            tc::mbar_init(full + s, 8);       // one arrival per producer warp
+            tc::mbar_init(empty + s, 1);      // tcgen05.commit
+            tc::mbar_init(acc_full + s, 1);   // tcgen05.commit
+            tc::mbar_init(acc_empty + s, 8);  // one arrival per epilogue warp
+            dirty3[s] = 0;
+        }
+        *abort_word = 0;
+        tc::mbar_init_fence();
+    }
+    if (warp == 16) tc::tmem_alloc(tmem_slot, tmem_cols);
+    for (int e = tid; e < Npad; e += kWsThreads) bias_s[e] = (P.bq != nullptr && e < N) ? __ldg(P.bq + e) : 0.f;
+    for (int e = tid; e < amax_elems; e += kWsThreads) amax_t[e] = 0.f;
+    for (int e = tid; e < P.rows_period * P.Kt; e += kWsThreads) {
+        const int pr = e / P.Kt, k = e % P.Kt;
+        const int fi = (k < K) ? __float2int_rn(__ldg(P.qf + pr * K + k)) : 0;
+        etab[pr * Ke + k] = (unsigned char)(max(-126, min(127, fi)) + 127);
+    }
+    // the third-term buffers hold zeros until a tile needs them
+    for (int s = 0; s < 2; ++s)
+        for (int e = tid; e < kWsTermBytes / 16; e += kWsThreads)
+            reinterpret_cast<uint4 *>(A + s * kWsStageBytes + 2 * kWsTermBytes)[e] = make_uint4(0, 0, 0, 0);
+    // weights: fp32 [K, N] -> up to three bf16 terms, K-major core matrices: (n/8, k/8) -> 128-byte block
+    int w_lo = 0, w_lo2 = 0;
+    for (int e = tid; e < Kpad * Npad; e += kWsThreads) {
+        const int n = e % Npad, k = e / Npad;
+        const float w = (k < K && n < N) ? __ldg(P.wq + (int64_t)k * N + n) : 0.f;
+        __nv_bfloat16 h, l, l2;
+        tc::split3(w, h, l, l2);
+        const int off = ((n >> 3) * (Kpad >> 3) + (k >> 3)) * 128 + (n & 7) * 16 + (k & 7) * 2;
+        *reinterpret_cast<__nv_bfloat16 *>(B + off) = h;
+        *reinterpret_cast<__nv_bfloat16 *>(B + b_term_bytes + off) = l;
+        *reinterpret_cast<__nv_bfloat16 *>(B + 2 * b_term_bytes + off) = l2;
+        w_lo |= (__bfloat16_as_ushort(l) & 0x7fff) != 0;
+        w_lo2 |= (__bfloat16_as_ushort(l2) & 0x7fff) != 0;
+    }
+    const int any_w_lo = __syncthreads_or(w_lo);
+    const int any_w_lo2 = __syncthreads_or(w_lo2);
+    const int n_w = any_w_lo2 ? 3 : (any_w_lo ? 2 : 1);
+    tc::fence_smem_to_async();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const int n_chunks = (Kpad + kWsKC - 1) / kWsKC;
+
+    if (warp < 8) {
+        // ================================ producers ==================================================================
+        // slab mapping: lane = (q4, r8); warp w in iteration it handles row group mg = (it*8 + w) / 2 and the 8-column
+        // group kg = (w & 1) * 4 + q4.  A quarter-warp (r8 = 0..7) fills one 128-byte core matrix.
+        const int r8 = lane & 7, q4 = lane >> 3;
+        const int kg = (warp & 1) * 4 + q4;
+        const float rbias = (P.rm == RM_RND) ? 0.5f : 0.f;
+        const uint32_t fetch_base = tc::smem_u32(fetch);
+        // Requests run `depth` slabs ahead of the conversion; every request closes one cp.async group (an empty one past
+        // the last slab), so "all but the newest depth - 1 groups have landed" always means "this slab has landed".
+        const int depth = P.depth;
+        int64_t pf_tile = blockIdx.x;
+        int pf_ch = 0;
+        uint32_t pf_n = 0;
+        auto request = [&]() {
+            if (pf_tile < P.num_tiles) {
+                const int k0 = pf_ch * kWsKC + kg * 8;
+                const uint32_t buf = fetch_base + (depth == 2 ? (pf_n & 1u) : 0u) * kWsFetchBytes;
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int64_t row = pf_tile * kWsTileM + (((it * 8 + warp) >> 1) * 8) + r8;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const bool in = row < P.M && (k0 + 4 * h) < K;  // K % 4 == 0: a 16-byte piece is all inside or all outside
+                        const float *src = in ? P.x + row * K + k0 + 4 * h : P.x;
+                        const uint32_t dst = buf + (uint32_t)(((it * 2 + h) * kWsProd + tid) * 16);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (++pf_ch == n_chunks) { pf_ch = 0; pf_tile += gridDim.x; }
+            ++pf_n;
+        };
+        for (int d = 0; d < depth; ++d) request();
+
+        const uint32_t rp = (uint32_t)P.rows_period;
+        const bool rp_pow2 = (rp & (rp - 1)) == 0;
+        uint32_t base_pr = (uint32_t)(((int64_t)blockIdx.x * kWsTileM) % P.rows_period);
+        const uint32_t step_pr = (uint32_t)(((int64_t)gridDim.x * kWsTileM) % P.rows_period);
+        float amax_r[2][8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax_r[0][j] = amax_r[1][j] = 0.f;
+
+        uint32_t n = 0;  // slabs produced so far
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, base_pr = (base_pr + step_pr) % rp) {
+            for (int ch = 0; ch < n_chunks && ok; ++ch, ++n) {
+                const int s = (int)(n & 1u);
+                const uint32_t use = n >> 1;
+                unsigned char *As = A + s * kWsStageBytes;
+                float xv[4][8];
+                if (depth == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
+                else asm volatile("cp.async.wait_group 0;" ::: "memory");
+                {
+                    const unsigned char *buf = fetch + (depth == 2 ? (n & 1u) : 0u) * kWsFetchBytes;
+#pragma unroll
+                    for (int it = 0; it < 4; ++it) {
+                        const float4 v0 = *reinterpret_cast<const float4 *>(buf + ((it * 2 + 0) * kWsProd + tid) * 16);
+                        const float4 v1 = *reinterpret_cast<const float4 *>(buf + ((it * 2 + 1) * kWsProd + tid) * 16);
+                        xv[it][0] = v0.x; xv[it][1] = v0.y; xv[it][2] = v0.z; xv[it][3] = v0.w;
+                        xv[it][4] = v1.x; xv[it][5] = v1.y; xv[it][6] = v1.z; xv[it][7] = v1.w;
+                    }
+                }
+                request();  // the slots just read are free again (their contents sit in registers)
+                // the products that read this stage two slabs ago must have completed (they were issued a whole slab ago)
+                if (use > 0) {
+                    const bool w = ws_wait(empty + s, (use - 1) & 1u, abort_word);
+                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                }
+                // third term: values with more than 16 significant bits.  Once a stage has carried one, every thread
+                // rewrites its part of the stage's third buffer on every slab (zeros where it has none); until then the
+                // buffer holds the zeros of the set-up and the issuing warp skips it.
+                int d3 = *reinterpret_cast<volatile int *>(dirty3 + s);
+                const int k0 = ch * kWsKC + kg * 8;
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int lrow = ((it * 8 + warp) >> 1) * 8 + r8;
+                    const bool valid = (tile * kWsTileM + lrow) < P.M && k0 < K;
+                    if (valid) {
+                        const uint32_t lr = base_pr + (uint32_t)lrow;
+                        const int pr = (int)(rp_pow2 ? (lr & (rp - 1)) : (lr % rp));
+                        const uint2 eb = *reinterpret_cast<const uint2 *>(etab + pr * Ke + k0);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t sbits = (((j < 4 ? eb.x : eb.y) >> ((j & 3) * 8)) & 0xffu) << 23;  // 2^f
+                            // scaling by a power of two is exact, so one fused multiply-add gives RN(x * 2^f + bias) bit for bit
+                            const float q = RCONV ? rintf(__fmul_rn(xv[it][j], __uint_as_float(sbits)))
+                                                  : floorf(__fmaf_rn(xv[it][j], __uint_as_float(sbits), rbias));
+                            xv[it][j] = __fmul_rn(q, __uint_as_float(0x7F000000u - sbits));  // * 2^-f
+                        }
+                        if (AMAX == WS_AMAX_REGS || AMAX == WS_AMAX_ROWS1 || AMAX == WS_AMAX_ROWS2) {
+                            const int ri = (AMAX == WS_AMAX_ROWS2) ? (it & 1) : 0;  // rows it * 32 + c: residue mod 64 alternates
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) amax_r[ri][j] = fmaxf(amax_r[ri][j], fabsf(xv[it][j]));
+                        } else if (AMAX == WS_AMAX_PLAIN) {
+                            const int te = pr * Ks + k0;
+                            float4 m0 = *reinterpret_cast<float4 *>(amax_t + te), m1 = *reinterpret_cast<float4 *>(amax_t + te + 4);
+                            m0.x = fmaxf(m0.x, fabsf(xv[it][0])); m0.y = fmaxf(m0.y, fabsf(xv[it][1]));
+                            m0.z = fmaxf(m0.z, fabsf(xv[it][2])); m0.w = fmaxf(m0.w, fabsf(xv[it][3]));
+                            m1.x = fmaxf(m1.x, fabsf(xv[it][4])); m1.y = fmaxf(m1.y, fabsf(xv[it][5]));
+                            m1.z = fmaxf(m1.z, fabsf(xv[it][6])); m1.w = fmaxf(m1.w, fabsf(xv[it][7]));
+                            *reinterpret_cast<float4 *>(amax_t + te) = m0;
+                            *reinterpret_cast<float4 *>(amax_t + te + 4) = m1;
+                        }
+                    }
+                    // exact bf16 terms: a float whose low 16 bits are zero *is* a bf16 (top 16 bits), the common case
+                    uint32_t hi[4], lo[4] = {0u, 0u, 0u, 0u}, t3[4] = {0u, 0u, 0u, 0u};
+                    uint32_t lowbits = 0u;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) lowbits |= __float_as_uint(xv[it][j]);
+                    if ((lowbits & 0xFFFFu) == 0u) {
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2)
+                            hi[j >> 1] = __byte_perm(__float_as_uint(xv[it][j]), __float_as_uint(xv[it][j + 1]), 0x7632);
+                    } else {
+                        int need3 = 0;
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) {
+                            __nv_bfloat16 h0, l0, m0, h1, l1, m1;
+                            tc::split3(xv[it][j], h0, l0, m0);
+                            tc::split3(xv[it][j + 1], h1, l1, m1);
+                            hi[j >> 1] = tc::pack2(h0, h1);
+                            lo[j >> 1] = tc::pack2(l0, l1);
+                            t3[j >> 1] = tc::pack2(m0, m1);
+                            need3 |= (t3[j >> 1] & 0x7fff7fffu) != 0;
+                        }
+                        if (need3 && !d3) { atomicOr(dirty3 + s, 1); d3 = 1; }
+                    }
+                    const int off = (lrow >> 3) * 1024 + kg * 128 + r8 * 16;
+                    *reinterpret_cast<uint4 *>(As + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4 *>(As + kWsTermBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    if (d3) *reinterpret_cast<uint4 *>(As + 2 * kWsTermBytes + off) = make_uint4(t3[0], t3[1], t3[2], t3[3]);
+                }
+                tc::fence_smem_to_async();
+                __syncwarp();
+                if (lane == 0) ws_arrive(full + s);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (!ok) {
+            *reinterpret_cast<volatile int *>(abort_word) = 1;
+            if (lane == 0 && P.status) atomicOr(P.status, kWsTimeout);
+        }
+        // ---- abs-max partials of this CTA -----------------------------------------------------------------------------
+        if (AMAX == WS_AMAX_ROWS1 || AMAX == WS_AMAX_ROWS2) {
+            // a tile starts at a multiple of 128 rows, so this thread's table rows are the same in every tile
+            unsigned *dst = P.amax_part + (int64_t)blockIdx.x * P.rows_period * K;
+#pragma unroll
+            for (int ri = 0; ri < (AMAX == WS_AMAX_ROWS2 ? 2 : 1); ++ri) {
+                const int pr = (warp >> 1) * 8 + r8 + ri * 32;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (kg * 8 + j < K) dst[pr * K + kg * 8 + j] = __float_as_uint(amax_r[ri][j]);
+            }
+        } else if (AMAX != WS_AMAX_NONE) {
+            if (AMAX == WS_AMAX_REGS) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (kg * 8 + j < K) atomicMax(reinterpret_cast<unsigned *>(amax_t) + kg * 8 + j, __float_as_uint(amax_r[0][j]));
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const int table = P.rows_period * K;
+            unsigned *dst = P.amax_part + (int64_t)blockIdx.x * table;
+            for (int e = tid; e < table; e += kWsProd) dst[e] = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
+        }
+    } else if (warp == 16) {
+        // ================================ tensor-core issue ==========================================================
+        // The whole warp walks the loop (so that it stays converged for the barriers of the tear-down); lane 0 issues.
+        const uint32_t idesc = tc::make_idesc_bf16(Npad, false, false);
+        const uint32_t a_base = tc::smem_u32(A), b_base = tc::smem_u32(B);
+        const uint32_t sbo_a = (kWsKC / 8) * 128, sbo_b = (uint32_t)(Kpad >> 3) * 128;
+        uint32_t n = 0, ti = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++ti) {
+            const uint32_t a = ti & 1u, ause = ti >> 1;
+            for (int ch = 0; ch < n_chunks && ok; ++ch, ++n) {
+                const uint32_t s = n & 1u, use = n >> 1;
+                bool w = ws_wait(full + s, use & 1u, abort_word);
+                // the epilogue must have drained this accumulator (tile ti - 2) before the first product overwrites it
+                if (w && ch == 0 && ause > 0) w = ws_wait(acc_empty + a, (ause - 1) & 1u, abort_word);
+                if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                tc::fence_after_sync();
+                if (lane == 0) {
+                    const int n_a = *reinterpret_cast<volatile int *>(dirty3 + s) ? 3 : 2;
+                    const int kleft = Kpad - ch * kWsKC;
+                    const int ksteps = (kleft < kWsKC ? kleft : kWsKC) / 16;
+                    const uint32_t tacc = tmem_base + a * (uint32_t)Npad;
+                    bool first = (ch == 0);
+                    for (int ks = 0; ks < ksteps; ++ks) {
+                        uint64_t da = tc::make_smem_desc(a_base + s * kWsStageBytes + ks * 256, 128, sbo_a);
+                        for (int ta = 0; ta < n_a; ++ta, da += (uint64_t)(kWsTermBytes >> 4)) {
+                            uint64_t db = tc::make_smem_desc(b_base + (ch * (kWsKC / 16) + ks) * 256, 128, sbo_b);
+                            for (int tw = 0; tw < n_w; ++tw, db += (uint64_t)(b_term_bytes >> 4)) {
+                                tc::mma_bf16(tacc, da, db, idesc, !first);
+                                first = false;
+                            }
+                        }
+                    }
+                    tc::commit(empty + s);
+                    if (ch == n_chunks - 1) tc::commit(acc_full + a);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok) {
+            *reinterpret_cast<volatile int *>(abort_word) = 1;
+            if (lane == 0 && P.status) atomicOr(P.status, kWsTimeout);
+        }
+    } else {
+        // ================================ epilogue ===================================================================
+        // Warp e reads TMEM lanes 32 (e & 3) .. + 31 (the rows of the tile it owns) and the half e >> 2 of every block of
+        // W = min(Npad, 64) columns: wc = W / 2 columns per thread in one tcgen05.ld.
+        const int e = warp - 8, q = e & 3, half = e >> 2;
+        float *ost = reinterpret_cast<float *>(outst + e * 4096);  // 32 rows x wc floats
+        const int W = Npad < 64 ? Npad : 64, wc = W >> 1, C = wc >> 2;
+        const float act_lo = (P.act == ACT_RELU) ? 0.f : -INFINITY;
+        const bool vec_out = (N % 4 == 0) && aligned(P.y, 16);
+        const int swz_w = ws_swz(lane, C);
+        uint32_t ti = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++ti) {
+            const uint32_t a = ti & 1u, ause = ti >> 1;
+            const bool w = ws_wait(acc_full + a, ause & 1u, abort_word);
+            if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+            tc::fence_after_sync();
+            const int64_t wrow0 = tile * kWsTileM + q * 32;  // first row of this warp
+            const int rows_w = (int)((P.M - wrow0) < 32 ? ((P.M - wrow0) < 0 ? 0 : (P.M - wrow0)) : 32);
+            for (int cb = 0; cb < Npad; cb += W) {
+                float v[32];
+                const int c0 = cb + half * wc;  // first column of this thread's piece
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * (uint32_t)Npad + (uint32_t)c0;
+                if (wc == 32) tc::tmem_ld32v(taddr, v);
+                else if (wc == 16) tc::tmem_ld16v(taddr, v);
+                else tc::tmem_ld8v(taddr, v);
+                if (cb + W >= Npad) {  // the accumulator is in registers: hand it back to the issuing warp
+                    tc::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ws_arrive(acc_empty + a);
+                }
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    if (j < wc) {
+                        const float4 b = *reinterpret_cast<const float4 *>(bias_s + c0 + j);
+                        float4 o;
+                        o.x = fmaxf(__fadd_rn(v[j], b.x), act_lo); o.y = fmaxf(__fadd_rn(v[j + 1], b.y), act_lo);
+                        o.z = fmaxf(__fadd_rn(v[j + 2], b.z), act_lo); o.w = fmaxf(__fadd_rn(v[j + 3], b.w), act_lo);
+                        *reinterpret_cast<float4 *>(ost + lane * wc + (((j >> 2) ^ swz_w) << 2)) = o;
+                    }
+                }
+                __syncwarp();
+                const int my_n = (N - c0) < wc ? ((N - c0) < 0 ? 0 : (N - c0)) : wc;  // valid columns of the piece
+                float *ydst = P.y + wrow0 * N + c0;
+                if (vec_out) {
+                    const int cv = my_n >> 2;
+                    const int total = rows_w * cv;
+                    if (cv == 8) {
+                        for (int g = lane; g < total; g += 32) {
+                            const int rr = g >> 3, c4 = g & 7;
+                            const float4 o = *reinterpret_cast<const float4 *>(ost + rr * wc + ((c4 ^ ws_swz(rr, C)) << 2));
+                            __stcs(reinterpret_cast<float4 *>(ydst + (int64_t)rr * N) + c4, o);
+                        }
+                    } else {
+                        for (int g = lane; g < total; g += 32) {
+                            const int rr = g / cv, c4 = g - rr * cv;
+                            const float4 o = *reinterpret_cast<const float4 *>(ost + rr * wc + ((c4 ^ ws_swz(rr, C)) << 2));
+                            __stcs(reinterpret_cast<float4 *>(ydst + (int64_t)rr * N) + c4, o);
+                        }
+                    }
+                } else {
+                    const int total = rows_w * my_n;
+                    for (int g = lane; g < total; g += 32) {
+                        const int rr = g / my_n, c = g - rr * my_n;
+                        __stcs(ydst + (int64_t)rr * N + c, ost[rr * wc + ((((c >> 2) ^ ws_swz(rr, C)) << 2) | (c & 3))]);
+                    }
+                }
+                __syncwarp();  // the transposition buffer is reused by the next block / the next tile
+            }
+        }
+        if (!ok) {
+            *reinterpret_cast<volatile int *>(abort_word) = 1;
+            if (lane == 0 && P.status) atomicOr(P.status, kWsTimeout);
+        }
+    }
+
+    // ---- tear-down ----------------------------------------------------------------------------------------------------
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 16) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+static size_t qdense_ws_smem(int Kpad, int Npad, int Kt, int rows_period, bool amax_table, int depth) {
+    const size_t tab_bytes = ((size_t)rows_period * (Kt + 8) + 15) / 16 * 16;
+    return 2 * (size_t)kWsStageBytes + (size_t)depth * kWsFetchBytes + kWsOutBytes + 3 * (size_t)Kpad * Npad * 2 +
+           (size_t)Npad * 4 + tab_bytes + (amax_table ? (size_t)rows_period * (Kt + 4) * 4 : 0) + 8 * 8 + 32;
+}
+
+// Launches the warp-specialised kernel when it covers the call; returns 1 with the grid size in *grid, 0 when the call is
+// not covered (the caller then takes the general kernel), or a negative CUDA error code.
+int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round_mode, const float *wq, const float *bq,
+                     int activation, float *y, unsigned *amax_part, int64_t M, int K, int N, int Kpad, int Npad, int Kt,
+                     unsigned *status, cudaStream_t st, int *grid) {
+    if (qf == nullptr || K % 4 != 0 || !aligned(x, 16) || !aligned(y, 4)) return 0;
+    if (2 * Npad > 512) return 0;
+    const bool want_amax = amax_part != nullptr;
+    const bool one_slab = Kpad <= kWsKC;
+    int amax_mode = WS_AMAX_NONE;
+    if (want_amax) {
+        if (rows_period == 1 && one_slab) amax_mode = WS_AMAX_REGS;
+        else if (rows_period == 32 && one_slab) amax_mode = WS_AMAX_ROWS1;
+        else if (rows_period == 64 && one_slab) amax_mode = WS_AMAX_ROWS2;
+        else if (rows_period == 32 || rows_period == 64 || rows_period == 128) amax_mode = WS_AMAX_PLAIN;
+        else return 0;
+    }
+    const bool amax_table = amax_mode == WS_AMAX_REGS || amax_mode == WS_AMAX_PLAIN;
+    int depth = 2;
+    size_t smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth);
+    if (smem > 227 * 1024) {
+        depth = 1;
+        smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth);
+    }
+    if (smem > 227 * 1024) return 0;
+    WsParams p;
+    p.x = x; p.qf = qf; p.wq = wq; p.bq = bq; p.y = y; p.amax_part = amax_part; p.status = status;
+    p.M = M; p.num_tiles = (M + kWsTileM - 1) / kWsTileM;
+    p.K = K; p.N = N; p.Kpad = Kpad; p.Npad = Npad; p.Kt = Kt; p.rows_period = rows_period;
+    p.rm = round_mode; p.act = activation; p.depth = depth;
+    const int g = (int)(p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs);
+    *grid = g;
+#define HGQ_WS_LAUNCH(CV, AM)                                                                                           \
+    do {                                                                                                                \
+        cudaError_t ce = cudaFuncSetAttribute(k_qdense_fwd_ws<CV, AM>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                              (int)smem);                                                               \
+        if (ce != cudaSuccess) return -(int)ce;                                                                         \
+        k_qdense_fwd_ws<CV, AM><<<g, kWsThreads, smem, st>>>(p);                                                        \
+    } while (0)
+#define HGQ_WS_MODES(CV)                                                              \
+    switch (amax_mode) {                                                              \
+        case WS_AMAX_NONE: HGQ_WS_LAUNCH(CV, WS_AMAX_NONE); break;                    \
+        case WS_AMAX_REGS: HGQ_WS_LAUNCH(CV, WS_AMAX_REGS); break;                    \
+        case WS_AMAX_ROWS1: HGQ_WS_LAUNCH(CV, WS_AMAX_ROWS1); break;                  \
+        case WS_AMAX_ROWS2: HGQ_WS_LAUNCH(CV, WS_AMAX_ROWS2); break;                  \
+        default: HGQ_WS_LAUNCH(CV, WS_AMAX_PLAIN); break;                             \
+    }
+    if (round_mode == RM_RND_CONV) { HGQ_WS_MODES(true); } else { HGQ_WS_MODES(false); }
+#undef HGQ_WS_MODES
+#undef HGQ_WS_LAUNCH
+    return 1;
+}
+
+}  // namespace hgq

@@ -71,6 +71,31 @@ def test_fused_dense_is_exact_for_wide_values():
         assert err <= (2e-7 if wbits <= 6 else 1e-6), (wbits, float(err))
 
 
+def test_fused_dense_activations_beyond_two_terms():
+    # quantised activations with more than 16 significant bits appear only in some tiles, late in a CTA's sequence of
+    # tiles and in single elements: the third bf16 term must be picked up exactly where it is needed.  Every sum here
+    # is exact in fp32 (one wide value per row, weights are powers of two), so the comparison is bit for bit.
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(5)
+    M, K, N = 128 * 400 + 17, 64, 32
+    x = torch.from_numpy(np.round(rng.standard_normal((M, K)) * 4).astype(np.float32))  # integers: few bits
+    wide = torch.from_numpy((rng.standard_normal(M) * 20).astype(np.float32))
+    col = torch.from_numpy(rng.integers(0, K, M))
+    rows = torch.cat([torch.arange(128 * 200, 128 * 260), torch.tensor([128 * 300 + 5, M - 3])])
+    x[rows] = 0.0
+    x[rows, col[rows]] = wide[rows]
+    f = torch.full((1, K), 20.0)
+    w = torch.from_numpy(rng.choice([-1.0, 1.0], (K, N)) * 2.0 ** -rng.integers(0, 7, (K, N))).float()
+    y, amax = kernels.qdense_fwd(x.cuda(), None, None, f.cuda(), 1, 'RND', 'WRAP', True, False, w.cuda(), None, None, True)
+    kernels.check_status(y.device)
+    xq = O.round_fwd(x, f.expand(M, K), 'RND')
+    assert int((xq[rows].view(torch.int32) & 0xff).ne(0).sum()) > 1000  # the wide rows do need a third term
+    yr = (xq.double() @ w.double()).float()
+    assert torch.equal(y.cpu(), yr)
+    assert torch.equal(amax.cpu().view(1, K), xq.abs().amax(0, keepdim=True))
+
+
 def test_fused_dense_no_input_quantizer_and_limits():
     from hgq2_b200 import _lib, kernels
 
