@@ -6,14 +6,14 @@
 // (fixed_point_quantizer.py:405-413) is a side output.
 //
 // One persistent CTA per SM with three roles that meet only at mbarriers, never at a CTA-wide barrier:
-//   warps 0-7   producers: fetch a 128 x 64 fp32 slab (cp.async into thread-private slots, two slabs ahead), quantise it in
+//   warps 0-15  producers: fetch a 128 x 64 fp32 slab (cp.async into thread-private slots, two slabs ahead), quantise it in
 //               registers, split every value exactly into bf16 terms and store them as no-swizzle K-major core matrices
 //               into one of two operand stages; arrive on full[stage];
-//   warp 16     waits for full[stage] and for a free accumulator, issues tcgen05.mma (M = 128, N = padded N, K = 16) for
+//   warp 20     waits for full[stage] and for a free accumulator, issues tcgen05.mma (M = 128, N = padded N, K = 16) for
 //               every pair of terms, commits to empty[stage] and, after the last slab of a tile, to acc_full[acc];
-//   warps 8-15  epilogue: wait for acc_full[acc], read their 32 rows x half of the columns with tcgen05.ld, release the
-//               accumulator (acc_empty[acc]), add bias, apply the activation, transpose through a warp-private 4 KB
-//               buffer and write whole 128-byte row pieces.
+//   warps 16-19 epilogue: wait for acc_full[acc], read their 32 rows of the accumulator with tcgen05.ld (32 columns at a
+//               time), release the accumulator (acc_empty[acc]), add bias, apply the activation, transpose through a
+//               warp-private 4 KB buffer and write whole 128-byte row pieces.
 // With two operand stages and two accumulators in tensor memory the conversion of tile t + 1 overlaps the products of
 // tile t and the write-out of tile t - 1.  HBM-bound: 4 (K + N) bytes per row.
 // Every wait is bounded (polls and wall time); a wait that gives up sets an abort word that ends every role's loop, the
@@ -27,24 +27,22 @@
 
 namespace hgq {
 
-constexpr int kWsProd = 256;                         // producer threads
-constexpr int kWsThreads = 544;                      // 8 producer warps, 8 epilogue warps, 1 issuing warp
+// The kernel is a template on its warp split: NPW producer warps (8 or 16), EW epilogue warps (4 or 8), one issuing warp.
 constexpr int kWsTileM = 128;
 constexpr int kWsKC = 64;                            // K slab of one operand stage
 constexpr int kWsTermBytes = kWsTileM * kWsKC * 2;   // 16 KB per bf16 term
 constexpr int kWsStageBytes = 3 * kWsTermBytes;      // hi, lo and (rarely non-zero) third term
 constexpr int kWsFetchBytes = kWsTileM * kWsKC * 4;  // raw fp32 slab in flight
-constexpr int kWsOutBytes = 8 * 4096;                // one transposition buffer per epilogue warp
+constexpr int kWsOutWarpBytes = 4096;                // transposition buffer of one epilogue warp: 32 rows x 32 floats
 constexpr unsigned kWsTimeout = 1u;                  // status bit, same meaning as in the other tensor-core kernels
 
 // Abs-max bookkeeping (max over rows of |round(x)| per entry of the quantizer table):
-//   REGS   rows_period == 1, one K slab: a thread's 8 columns never change; maxima in registers, merged through a one-row
-//          table in shared memory at the end
-//   ROWS1  rows_period == 32, ROWS2 rows_period == 64, one K slab: every table entry belongs to exactly one thread, which
-//          keeps it in a register and writes it out at the end
-//   PLAIN  rows_period == 128 or several K slabs with rows_period in {32, 64, 128}: rows that share a table entry fall to
-//          the same thread, plain read-modify-write of a table in shared memory
-enum : int { WS_AMAX_NONE = 0, WS_AMAX_REGS = 1, WS_AMAX_PLAIN = 2, WS_AMAX_ROWS1 = 3, WS_AMAX_ROWS2 = 4 };
+//   REGS1 / REGS2  one K slab and a period that divides 128: a tile starts at table row 0, so the table rows (one when the
+//          period divides 64, else two) and the 8 columns of a thread never change; maxima live in registers and are merged
+//          through a table in shared memory (atomic max on the bit patterns) when the CTA is done
+//   PLAIN  period 64 or 128, several K slabs: rows that share a table entry fall to the same thread, plain
+//          read-modify-write of the table in shared memory
+enum : int { WS_AMAX_NONE = 0, WS_AMAX_REGS1 = 1, WS_AMAX_PLAIN = 2, WS_AMAX_REGS2 = 3 };
 
 struct WsParams {
     const float *x, *qf, *wq, *bq;
@@ -87,24 +85,31 @@ __device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, volatile
 
 __device__ __forceinline__ int ws_swz(int r, int C) { return C == 8 ? (r & 7) : (C == 4 ? ((r >> 1) & 3) : ((r >> 2) & 1)); }
 
-template <bool RCONV, int AMAX>
-__global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams P) {
+template <bool RCONV, int AMAX, int NPW, int EW>
+__global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const WsParams P) {
+    constexpr int kWsProdWarps = NPW, kWsProd = NPW * 32, kWsEpiWarps = EW, kWsIssueWarp = NPW + EW;
+    constexpr int kWsThreads = (NPW + EW + 1) * 32;
+    constexpr int ITS = 32 / NPW;       // 8-row groups a producer thread converts per slab
+    constexpr int ROWSTEP = NPW * 4;    // their distance in rows
     extern __shared__ __align__(128) unsigned char smem[];
     // carve: operand stages | raw-slab slots | transposition buffers | B terms | bias | exponent table | abs-max table |
     // barriers, TMEM slot, flags
     unsigned char *A = smem;
     unsigned char *fetch = A + 2 * kWsStageBytes;
     unsigned char *outst = fetch + P.depth * kWsFetchBytes;
-    unsigned char *B = outst + kWsOutBytes;
+    unsigned char *B = outst + EW * kWsOutWarpBytes;
     const int b_term_bytes = P.Kpad * P.Npad * 2;
     float *bias_s = reinterpret_cast<float *>(B + 3 * b_term_bytes);
     const int Ke = P.Kt + 8;  // row stride of the exponent table: 8-byte reads of 8 rows hit 8 bank pairs
     const int tab_bytes = (P.rows_period * Ke + 15) / 16 * 16;
     unsigned char *etab = reinterpret_cast<unsigned char *>(bias_s + P.Npad);
     const int Ks = P.Kt + 4;  // abs-max table row: 16-byte accesses of 8 rows hit 8 bank groups
-    float *amax_t = reinterpret_cast<float *>(etab + tab_bytes);
-    const int amax_elems = (AMAX == WS_AMAX_REGS || AMAX == WS_AMAX_PLAIN) ? P.rows_period * Ks : 0;
-    uint64_t *full = reinterpret_cast<uint64_t *>(amax_t + amax_elems);
+    // PLAIN keeps the abs-max table beside the exponent table; the register modes merge through the raw-slab slots, which
+    // are idle by then
+    constexpr bool amax_regs = (AMAX == WS_AMAX_REGS1 || AMAX == WS_AMAX_REGS2);
+    const int amax_elems = (AMAX == WS_AMAX_PLAIN) ? P.rows_period * Ks : 0;
+    float *amax_t = amax_regs ? reinterpret_cast<float *>(fetch) : reinterpret_cast<float *>(etab + tab_bytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(etab + tab_bytes + amax_elems * 4);
     uint64_t *empty = full + 2, *acc_full = full + 4, *acc_empty = full + 6;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(full + 8);
     int *dirty3 = reinterpret_cast<int *>(tmem_slot + 1);  // per stage: some tile needed the third term (sticky)
@@ -117,16 +122,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
     // ---- one-time set-up (all threads) -------------------------------------------------------------------------------
     if (tid == 0) {
         for (int s = 0; s < 2; ++s) {
-            tc::mbar_init(full + s, 8);       // one arrival per producer warp
+            tc::mbar_init(full + s, kWsProdWarps);  // one arrival per producer warp
             tc::mbar_init(empty + s, 1);      // tcgen05.commit
             tc::mbar_init(acc_full + s, 1);   // tcgen05.commit
-            tc::mbar_init(acc_empty + s, 8);  // one arrival per epilogue warp
+            tc::mbar_init(acc_empty + s, kWsEpiWarps);  // one arrival per epilogue warp
             dirty3[s] = 0;
         }
         *abort_word = 0;
         tc::mbar_init_fence();
     }
-    if (warp == 16) tc::tmem_alloc(tmem_slot, tmem_cols);
+    if (warp == kWsIssueWarp) tc::tmem_alloc(tmem_slot, tmem_cols);
     for (int e = tid; e < Npad; e += kWsThreads) bias_s[e] = (P.bq != nullptr && e < N) ? __ldg(P.bq + e) : 0.f;
     for (int e = tid; e < amax_elems; e += kWsThreads) amax_t[e] = 0.f;
     for (int e = tid; e < P.rows_period * P.Kt; e += kWsThreads) {
@@ -162,9 +167,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
     const uint32_t tmem_base = *tmem_slot;
     const int n_chunks = (Kpad + kWsKC - 1) / kWsKC;
 
-    if (warp < 8) {
+    if (warp < kWsProdWarps) {
         // ================================ producers ==================================================================
-        // slab mapping: lane = (q4, r8); warp w in iteration it handles row group mg = (it*8 + w) / 2 and the 8-column
+        // slab mapping: lane = (q4, r8); warp w in iteration it handles row group mg = (it * NPW + w) / 2 and the 8-column
         // group kg = (w & 1) * 4 + q4.  A quarter-warp (r8 = 0..7) fills one 128-byte core matrix.
         const int r8 = lane & 7, q4 = lane >> 3;
         const int kg = (warp & 1) * 4 + q4;
@@ -181,8 +186,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
                 const int k0 = pf_ch * kWsKC + kg * 8;
                 const uint32_t buf = fetch_base + (depth == 2 ? (pf_n & 1u) : 0u) * kWsFetchBytes;
 #pragma unroll
-                for (int it = 0; it < 4; ++it) {
-                    const int64_t row = pf_tile * kWsTileM + (((it * 8 + warp) >> 1) * 8) + r8;
+                for (int it = 0; it < ITS; ++it) {
+                    const int64_t row = pf_tile * kWsTileM + it * ROWSTEP + (warp >> 1) * 8 + r8;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const bool in = row < P.M && (k0 + 4 * h) < K;  // K % 4 == 0: a 16-byte piece is all inside or all outside
@@ -213,13 +218,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
                 const int s = (int)(n & 1u);
                 const uint32_t use = n >> 1;
                 unsigned char *As = A + s * kWsStageBytes;
-                float xv[4][8];
+                float xv[ITS][8];
                 if (depth == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
                 else asm volatile("cp.async.wait_group 0;" ::: "memory");
                 {
                     const unsigned char *buf = fetch + (depth == 2 ? (n & 1u) : 0u) * kWsFetchBytes;
 #pragma unroll
-                    for (int it = 0; it < 4; ++it) {
+                    for (int it = 0; it < ITS; ++it) {
                         const float4 v0 = *reinterpret_cast<const float4 *>(buf + ((it * 2 + 0) * kWsProd + tid) * 16);
                         const float4 v1 = *reinterpret_cast<const float4 *>(buf + ((it * 2 + 1) * kWsProd + tid) * 16);
                         xv[it][0] = v0.x; xv[it][1] = v0.y; xv[it][2] = v0.z; xv[it][3] = v0.w;
@@ -238,8 +243,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
                 int d3 = *reinterpret_cast<volatile int *>(dirty3 + s);
                 const int k0 = ch * kWsKC + kg * 8;
 #pragma unroll
-                for (int it = 0; it < 4; ++it) {
-                    const int lrow = ((it * 8 + warp) >> 1) * 8 + r8;
+                for (int it = 0; it < ITS; ++it) {
+                    const int lrow = it * ROWSTEP + (warp >> 1) * 8 + r8;
                     const bool valid = (tile * kWsTileM + lrow) < P.M && k0 < K;
                     if (valid) {
                         const uint32_t lr = base_pr + (uint32_t)lrow;
@@ -253,8 +258,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
                                                   : floorf(__fmaf_rn(xv[it][j], __uint_as_float(sbits), rbias));
                             xv[it][j] = __fmul_rn(q, __uint_as_float(0x7F000000u - sbits));  // * 2^-f
                         }
-                        if (AMAX == WS_AMAX_REGS || AMAX == WS_AMAX_ROWS1 || AMAX == WS_AMAX_ROWS2) {
-                            const int ri = (AMAX == WS_AMAX_ROWS2) ? (it & 1) : 0;  // rows it * 32 + c: residue mod 64 alternates
+                        if (AMAX == WS_AMAX_REGS1 || AMAX == WS_AMAX_REGS2) {
+                            const int ri = (AMAX == WS_AMAX_REGS2) ? (it & 1) : 0;  // REGS2: the table row alternates with it
 #pragma unroll
                             for (int j = 0; j < 8; ++j) amax_r[ri][j] = fmaxf(amax_r[ri][j], fabsf(xv[it][j]));
                         } else if (AMAX == WS_AMAX_PLAIN) {
@@ -307,28 +312,25 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
             if (lane == 0 && P.status) atomicOr(P.status, kWsTimeout);
         }
         // ---- abs-max partials of this CTA -----------------------------------------------------------------------------
-        if (AMAX == WS_AMAX_ROWS1 || AMAX == WS_AMAX_ROWS2) {
-            // a tile starts at a multiple of 128 rows, so this thread's table rows are the same in every tile
-            unsigned *dst = P.amax_part + (int64_t)blockIdx.x * P.rows_period * K;
+        if (AMAX != WS_AMAX_NONE) {
+            if (amax_regs) {
+                asm volatile("bar.sync 1, %0;" ::"n"(kWsProd) : "memory");  // every producer is done with the raw-slab slots
+                for (int e = tid; e < P.rows_period * Ks; e += kWsProd) amax_t[e] = 0.f;
+                asm volatile("bar.sync 1, %0;" ::"n"(kWsProd) : "memory");
 #pragma unroll
-            for (int ri = 0; ri < (AMAX == WS_AMAX_ROWS2 ? 2 : 1); ++ri) {
-                const int pr = (warp >> 1) * 8 + r8 + ri * 32;
+                for (int ri = 0; ri < (AMAX == WS_AMAX_REGS2 ? 2 : 1); ++ri) {
+                    const int pr = (ri * ROWSTEP + (warp >> 1) * 8 + r8) % P.rows_period;
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (kg * 8 + j < K) dst[pr * K + kg * 8 + j] = __float_as_uint(amax_r[ri][j]);
+                    for (int j = 0; j < 8; ++j)
+                        if (kg * 8 + j < K) atomicMax(reinterpret_cast<unsigned *>(amax_t) + pr * Ks + kg * 8 + j, __float_as_uint(amax_r[ri][j]));
+                }
             }
-        } else if (AMAX != WS_AMAX_NONE) {
-            if (AMAX == WS_AMAX_REGS) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (kg * 8 + j < K) atomicMax(reinterpret_cast<unsigned *>(amax_t) + kg * 8 + j, __float_as_uint(amax_r[0][j]));
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kWsProd) : "memory");
             const int table = P.rows_period * K;
             unsigned *dst = P.amax_part + (int64_t)blockIdx.x * table;
             for (int e = tid; e < table; e += kWsProd) dst[e] = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
         }
-    } else if (warp == 16) {
+    } else if (warp == kWsIssueWarp) {
         // ================================ tensor-core issue ==========================================================
         // The whole warp walks the loop (so that it stays converged for the barriers of the tear-down); lane 0 issues.
         const uint32_t idesc = tc::make_idesc_bf16(Npad, false, false);
@@ -373,14 +375,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
         }
     } else {
         // ================================ epilogue ===================================================================
-        // Warp e reads TMEM lanes 32 (e & 3) .. + 31 (the rows of the tile it owns) and the half e >> 2 of every block of
-        // W = min(Npad, 64) columns: wc = W / 2 columns per thread in one tcgen05.ld.
-        const int e = warp - 8, q = e & 3, half = e >> 2;
-        float *ost = reinterpret_cast<float *>(outst + e * 4096);  // 32 rows x wc floats
-        const int W = Npad < 64 ? Npad : 64, wc = W >> 1, C = wc >> 2;
+        // Warp e reads TMEM lanes 32 (e & 3) .. + 31 (the rows of the tile it owns); with eight warps the column pieces
+        // alternate between the two warps of a lane quarter.  wc columns per tcgen05.ld.
+        const int e = warp - kWsProdWarps, q = e & 3, part = e >> 2;
+        constexpr int NPARTS = EW / 4;
+        float *ost = reinterpret_cast<float *>(outst + e * kWsOutWarpBytes);  // 32 rows x wc floats
+        const int wc = (Npad / NPARTS) < 32 ? (Npad / NPARTS) : 32, C = wc >> 2;
+        const int swz_w = ws_swz(lane, C);
+        const int last_c0 = Npad - wc * (NPARTS - part);  // this warp's last piece
         const float act_lo = (P.act == ACT_RELU) ? 0.f : -INFINITY;
         const bool vec_out = (N % 4 == 0) && aligned(P.y, 16);
-        const int swz_w = ws_swz(lane, C);
         uint32_t ti = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++ti) {
@@ -390,14 +394,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
             tc::fence_after_sync();
             const int64_t wrow0 = tile * kWsTileM + q * 32;  // first row of this warp
             const int rows_w = (int)((P.M - wrow0) < 32 ? ((P.M - wrow0) < 0 ? 0 : (P.M - wrow0)) : 32);
-            for (int cb = 0; cb < Npad; cb += W) {
+            for (int c0 = part * wc; c0 < Npad; c0 += NPARTS * wc) {
                 float v[32];
-                const int c0 = cb + half * wc;  // first column of this thread's piece
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * (uint32_t)Npad + (uint32_t)c0;
                 if (wc == 32) tc::tmem_ld32v(taddr, v);
                 else if (wc == 16) tc::tmem_ld16v(taddr, v);
                 else tc::tmem_ld8v(taddr, v);
-                if (cb + W >= Npad) {  // the accumulator is in registers: hand it back to the issuing warp
+                if (c0 == last_c0) {  // the accumulator is in registers: hand it back to the issuing warp
                     tc::fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ws_arrive(acc_empty + a);
@@ -438,7 +441,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
                         __stcs(ydst + (int64_t)rr * N + c, ost[rr * wc + ((((c >> 2) ^ ws_swz(rr, C)) << 2) | (c & 3))]);
                     }
                 }
-                __syncwarp();  // the transposition buffer is reused by the next block / the next tile
+                __syncwarp();  // the transposition buffer is reused by the next piece / the next tile
             }
         }
         if (!ok) {
@@ -450,12 +453,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) k_qdense_fwd_ws(const WsParams 
     // ---- tear-down ----------------------------------------------------------------------------------------------------
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 16) tc::tmem_dealloc(tmem_base, tmem_cols);
+    if (warp == kWsIssueWarp) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-static size_t qdense_ws_smem(int Kpad, int Npad, int Kt, int rows_period, bool amax_table, int depth) {
+static size_t qdense_ws_smem(int Kpad, int Npad, int Kt, int rows_period, bool amax_table, int depth, int ew) {
     const size_t tab_bytes = ((size_t)rows_period * (Kt + 8) + 15) / 16 * 16;
-    return 2 * (size_t)kWsStageBytes + (size_t)depth * kWsFetchBytes + kWsOutBytes + 3 * (size_t)Kpad * Npad * 2 +
+    return 2 * (size_t)kWsStageBytes + (size_t)depth * kWsFetchBytes + (size_t)ew * kWsOutWarpBytes + 3 * (size_t)Kpad * Npad * 2 +
            (size_t)Npad * 4 + tab_bytes + (amax_table ? (size_t)rows_period * (Kt + 4) * 4 : 0) + 8 * 8 + 32;
 }
 
@@ -466,22 +469,27 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
                      unsigned *status, cudaStream_t st, int *grid) {
     if (qf == nullptr || K % 4 != 0 || !aligned(x, 16) || !aligned(y, 4)) return 0;
     if (2 * Npad > 512) return 0;
+    // Warp split: 8 producer and 8 epilogue warps.  Measured on the particle-layer shape (ms per launch): 8/8 0.53,
+    // 16/8 0.63, 8/4 0.77, 16/4 0.80 -- more producer warps cost registers and add per-warp overhead, fewer epilogue warps
+    // fall behind.
+    constexpr int npw = 8, ew = 8;
     const bool want_amax = amax_part != nullptr;
     const bool one_slab = Kpad <= kWsKC;
+    const int rowstep = npw * 4;
+    int depth = 2;
     int amax_mode = WS_AMAX_NONE;
     if (want_amax) {
-        if (rows_period == 1 && one_slab) amax_mode = WS_AMAX_REGS;
-        else if (rows_period == 32 && one_slab) amax_mode = WS_AMAX_ROWS1;
-        else if (rows_period == 64 && one_slab) amax_mode = WS_AMAX_ROWS2;
-        else if (rows_period == 32 || rows_period == 64 || rows_period == 128) amax_mode = WS_AMAX_PLAIN;
+        const bool plain_ok = (rows_period % rowstep == 0) && (kWsTileM % rows_period == 0);
+        if (one_slab && rowstep % rows_period == 0) amax_mode = WS_AMAX_REGS1;
+        else if (one_slab && (2 * rowstep) % rows_period == 0 && (size_t)rows_period * (Kt + 4) * 4 <= kWsFetchBytes) amax_mode = WS_AMAX_REGS2;
+        else if (plain_ok) amax_mode = WS_AMAX_PLAIN;
         else return 0;
     }
-    const bool amax_table = amax_mode == WS_AMAX_REGS || amax_mode == WS_AMAX_PLAIN;
-    int depth = 2;
-    size_t smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth);
+    const bool amax_table = amax_mode == WS_AMAX_PLAIN;
+    size_t smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth, ew);
     if (smem > 227 * 1024) {
         depth = 1;
-        smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth);
+        smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth, ew);
     }
     if (smem > 227 * 1024) return 0;
     WsParams p;
@@ -491,22 +499,21 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
     p.rm = round_mode; p.act = activation; p.depth = depth;
     const int g = (int)(p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs);
     *grid = g;
-#define HGQ_WS_LAUNCH(CV, AM)                                                                                           \
-    do {                                                                                                                \
-        cudaError_t ce = cudaFuncSetAttribute(k_qdense_fwd_ws<CV, AM>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
-                                              (int)smem);                                                               \
-        if (ce != cudaSuccess) return -(int)ce;                                                                         \
-        k_qdense_fwd_ws<CV, AM><<<g, kWsThreads, smem, st>>>(p);                                                        \
+#define HGQ_WS_LAUNCH(CV, AM, PW, EWW)                                                                                      \
+    do {                                                                                                                    \
+        cudaError_t ce = cudaFuncSetAttribute(k_qdense_fwd_ws<CV, AM, PW, EWW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                              (int)smem);                                                                   \
+        if (ce != cudaSuccess) return -(int)ce;                                                                             \
+        k_qdense_fwd_ws<CV, AM, PW, EWW><<<g, (PW + EWW + 1) * 32, smem, st>>>(p);                                           \
     } while (0)
-#define HGQ_WS_MODES(CV)                                                              \
+#define HGQ_WS_MODES(CV, PW, EWW)                                                     \
     switch (amax_mode) {                                                              \
-        case WS_AMAX_NONE: HGQ_WS_LAUNCH(CV, WS_AMAX_NONE); break;                    \
-        case WS_AMAX_REGS: HGQ_WS_LAUNCH(CV, WS_AMAX_REGS); break;                    \
-        case WS_AMAX_ROWS1: HGQ_WS_LAUNCH(CV, WS_AMAX_ROWS1); break;                  \
-        case WS_AMAX_ROWS2: HGQ_WS_LAUNCH(CV, WS_AMAX_ROWS2); break;                  \
-        default: HGQ_WS_LAUNCH(CV, WS_AMAX_PLAIN); break;                             \
+        case WS_AMAX_NONE: HGQ_WS_LAUNCH(CV, WS_AMAX_NONE, PW, EWW); break;           \
+        case WS_AMAX_REGS1: HGQ_WS_LAUNCH(CV, WS_AMAX_REGS1, PW, EWW); break;         \
+        case WS_AMAX_REGS2: HGQ_WS_LAUNCH(CV, WS_AMAX_REGS2, PW, EWW); break;         \
+        default: HGQ_WS_LAUNCH(CV, WS_AMAX_PLAIN, PW, EWW); break;                    \
     }
-    if (round_mode == RM_RND_CONV) { HGQ_WS_MODES(true); } else { HGQ_WS_MODES(false); }
+    if (round_mode == RM_RND_CONV) { HGQ_WS_MODES(true, npw, ew) } else { HGQ_WS_MODES(false, npw, ew) }
 #undef HGQ_WS_MODES
 #undef HGQ_WS_LAUNCH
     return 1;
