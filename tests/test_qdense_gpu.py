@@ -183,3 +183,18 @@ def test_fused_dense_backward_with_repeated_gradient_rows():
     kernels.check_status(x.device)
     for a, b in zip(got, ref):
         assert torch.equal(a, b)
+
+
+def test_general_forward_kernel_on_the_same_cases():
+    # HGQ_QDENSE_WS=0 (read once per process) keeps every forward call on the general kernel: the forward cases above are
+    # run again in a child process so that both kernels stay covered by the same references
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, HGQ_QDENSE_WS='0')
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, '-m', 'pytest', os.path.join(root, 'tests', 'test_qdense_gpu.py'), '-q', '-x', '-m', 'gpu',
+                        '-k', 'test_fused_dense_forward or beyond_two_terms or wide_values', '-p', 'no:cacheprovider'],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
