@@ -6,14 +6,15 @@
 // (fixed_point_quantizer.py:405-413) is a side output.
 //
 // One persistent CTA per SM with three roles that meet only at mbarriers, never at a CTA-wide barrier:
-//   warps 0-15  producers: fetch a 128 x 64 fp32 slab (cp.async into thread-private slots, two slabs ahead), quantise it in
-//               registers, split every value exactly into bf16 terms and store them as no-swizzle K-major core matrices
-//               into one of two operand stages; arrive on full[stage];
-//   warp 20     waits for full[stage] and for a free accumulator, issues tcgen05.mma (M = 128, N = padded N, K = 16) for
-//               every pair of terms, commits to empty[stage] and, after the last slab of a tile, to acc_full[acc];
-//   warps 16-19 epilogue: wait for acc_full[acc], read their 32 rows of the accumulator with tcgen05.ld (32 columns at a
-//               time), release the accumulator (acc_empty[acc]), add bias, apply the activation, transpose through a
-//               warp-private 4 KB buffer and write whole 128-byte row pieces.
+//   NPW producer warps (8): fetch a 128 x 64 fp32 slab (cp.async into thread-private slots, two slabs ahead), quantise it
+//               in registers, split every value exactly into bf16 terms and store them as no-swizzle K-major core
+//               matrices into one of two operand stages; arrive on full[stage];
+//   EW epilogue warps (8): wait for acc_full[acc], read their 32 rows of the accumulator with tcgen05.ld (up to 32 columns
+//               at a time; the two warps of a lane quarter take alternate column pieces), release the accumulator
+//               (acc_empty[acc]), add bias, apply the activation, transpose through a warp-private 4 KB buffer and write
+//               whole 128-byte row pieces;
+//   the last warp waits for full[stage] and for a free accumulator, issues tcgen05.mma (M = 128, N = padded N, K = 16)
+//               for every pair of terms, commits to empty[stage] and, after the last slab of a tile, to acc_full[acc].
 // With two operand stages and two accumulators in tensor memory the conversion of tile t + 1 overlaps the products of
 // tile t and the write-out of tile t - 1.  HBM-bound: 4 (K + N) bytes per row.
 // Every wait is bounded (polls and wall time); a wait that gives up sets an abort word that ends every role's loop, the
