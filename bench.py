@@ -160,7 +160,9 @@ def run_reference(args):
         'impl': 'reference', 'metric': METRIC, 'value': round(gbs, 3), 'unit': UNIT, 'n_gpus': args.gpus,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(dt * 1e3, 3), 'higher_is_better': True,
         'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': workload_config(args.gpus),
+        'config': dict(workload_config(args.gpus), elements_timed_per_pass=sample,
+                       note='the CPU arm times a 2^24-element sample of the 2^28-element workload; GB/s is per byte, so the '
+                            'figures compare'),
         'cpu_baseline': {'value': round(gbs, 3), 'unit': UNIT, 'cores': threads, 'kind': 'port',
                          'sample': f'{sample} elements per pass (2^24 of the 2^28), 6 modes x (fwd+bwd) per step, '
                                    'eager fp32 torch-CPU op sequence of the oracle'},
@@ -388,7 +390,7 @@ def run_qat(args, dev, world, rank, peak):
     import torch.distributed as dist
     import torch.nn.functional as F
 
-    from hgq2_b200 import workloads
+    from hgq2_b200 import routes, workloads
     from hgq2_b200.train import DataParallel, Trainer, shard_batch, sparse_categorical_crossentropy
 
     out = []
@@ -408,7 +410,12 @@ def run_qat(args, dev, world, rank, peak):
             hy = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch)[sl]).pin_memory()
             x, y = hx.to(dev), hy.to(dev)
             steps = max(3, args.steps)
-            tr.capture(x, y, warmup=3)  # the whole step as one CUDA graph
+            routes.reset()
+            # the whole step as one CUDA graph, recorded over two sets of static input buffers so that a host batch can be
+            # copied straight into the set the step after next reads
+            tr.capture(x, y, warmup=3, double_buffer=True)
+            fallbacks = routes.fallbacks()  # library routines a layer fell back to while the step was recorded (none expected)
+            x, y = tr.static_inputs  # the batch is resident where the captured step reads it
             for _ in range(3):
                 tr.step(x, y)
             torch.cuda.synchronize()
@@ -423,8 +430,8 @@ def run_qat(args, dev, world, rank, peak):
             ms = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
             # end to end: host batch in, loss out, every step
             # every step copies its batch from pinned host memory and reads its loss back; the copy of batch n + 1 is
-            # started before step n is launched, so it overlaps the step (two device staging slots)
-            for _ in range(2):  # untimed: the two staging slots are allocated on first use
+            # started before step n is launched, so it overlaps the step (it lands in the other set of static buffers)
+            for _ in range(2):  # untimed warm-up of the copy stream
                 tr.step_prefetched(tr.prefetch(hx, hy))
             torch.cuda.synchronize()
             t0 = time.perf_counter()
@@ -449,7 +456,7 @@ def run_qat(args, dev, world, rank, peak):
                 'h2d_bytes_per_step': int(hx.numel() * 4 + hy.numel() * 8), 'd2h_bytes_per_step': 4,
                 'hbm_roofline_frac': round(sps * bytes_per_sample / world / (peak * 1e9), 4),
                 'modelled_bytes_per_sample': bytes_per_sample, 'loss': round(loss_host, 5), 'cuda_graph': True,
-                'cpu_baseline': cpu,
+                'library_fallbacks': fallbacks, 'cpu_baseline': cpu,
             })
             del model, tr, x, y, hx, hy
             torch.cuda.empty_cache()

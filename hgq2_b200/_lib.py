@@ -70,8 +70,8 @@ SIGNATURES: dict[str, tuple] = {
     ),
     'hgq_qsoftmax_fwd': (
         c_int,
-        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int64, c_int,
-         c_int, c_void_p],
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p,
+         c_int64, c_int, c_int, c_void_p],
     ),
     'hgq_qsoftmax_bwd_workspace': (c_size_t, [c_int64, c_int, c_int]),
     'hgq_qsoftmax_bwd': (
@@ -115,10 +115,10 @@ SIGNATURES: dict[str, tuple] = {
     ),
 }
 
-_lib: ctypes.CDLL | None = None
+_lib = None  # the loaded library behind a call-counting proxy (hgq2_b200.routes)
 
 
-def lib() -> ctypes.CDLL:
+def lib():
     """The loaded library.  Raises if it has not been built (``python -m hgq2_b200.build``)."""
     global _lib
     if _lib is None:
@@ -133,7 +133,9 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)  # AttributeError if the symbol is not exported
             fn.restype = res
             fn.argtypes = args
-        _lib = handle
+        from .routes import CountingLibrary
+
+        _lib = CountingLibrary(handle)
     return _lib
 
 

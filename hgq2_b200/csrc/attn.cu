@@ -230,7 +230,7 @@ extern "C" int hgq_attn_heads_matmul(int kind, const float *x, const float *y, f
     int per_sm = (int)((228 * 1024) / (smem + 1024));
     const int cap = 4;  // measured optimum for all three kinds (3 and 5 resident CTAs are both slower)
     if (per_sm > cap) per_sm = cap;
-    int64_t grid = (int64_t)kNumSMs * per_sm;
+    int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > p.num_tiles) grid = p.num_tiles;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t ce;

@@ -10,12 +10,31 @@
 
 namespace hgq {
 
-constexpr int kNumSMs = 148;        // B200: 2 dies x 74 SMs
 constexpr int kThreads = 256;       // CTA size of every streaming kernel
 constexpr int64_t kMaxParamAbs = 100;
 enum : int { ACT_NONE = 0, ACT_RELU = 1 };  // fused output activations of the contraction kernels
 
 extern std::atomic<int64_t> g_launches;
+
+// Number of SMs of the current device (148 on a B200: 2 dies x 74), asked of the runtime once per device.  Grid sizes and
+// the workspace sizes that follow from them both come from here, so they agree on whatever part the library runs on.
+inline int num_sms() {
+    static std::atomic<int> cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return 148;  // no device in this process (host-only use of the size queries)
+    }
+    int v = cache[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+            cudaGetLastError();
+            v = 148;
+        }
+        cache[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
 
 inline int check_launch() {
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -73,7 +92,7 @@ inline BcastGeom bcast_geom(int64_t rows, int64_t P, bool can_vec, int unroll) {
     g.TX = (int)(g.V >= kThreads ? kThreads : pow2ceil(g.V));
     g.TY = kThreads / g.TX;
     g.colTiles = (g.V + g.TX - 1) / g.TX;
-    const int64_t target = (int64_t)kNumSMs * 8;
+    const int64_t target = (int64_t)num_sms() * 8;
     int64_t rb = (target + g.colTiles - 1) / g.colTiles;
     const int64_t maxrb = (rows + (int64_t)g.TY * unroll - 1) / ((int64_t)g.TY * unroll);
     if (rb > maxrb) rb = maxrb;

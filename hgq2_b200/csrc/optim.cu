@@ -52,7 +52,7 @@ extern "C" int hgq_adam_step(float *w, const float *g, float *m, float *v, const
     if (n == 0) return HGQ_OK;
     if (!w || !g || !m || !v || !step) return HGQ_ERR_NULL;
     int64_t blocks = (n + kThreads - 1) / kThreads;
-    if (blocks > (int64_t)kNumSMs * 8) blocks = (int64_t)kNumSMs * 8;
+    if (blocks > (int64_t)num_sms() * 8) blocks = (int64_t)num_sms() * 8;
     cudaStream_t st = (cudaStream_t)stream;
     k_adam<<<(unsigned)blocks, kThreads, 0, st>>>(w, g, m, v, lo, hi, l1, n, lr, beta1, beta2, eps, grad_scale, step);
     if (int e = check_launch()) return e;

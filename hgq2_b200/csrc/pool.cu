@@ -158,7 +158,7 @@ static int pool_check(const PoolParams &p) {
 
 static unsigned pool_grid(int64_t n_units) {
     int64_t g = (n_units + kThreads - 1) / kThreads;
-    const int64_t cap = (int64_t)kNumSMs * 32;
+    const int64_t cap = (int64_t)num_sms() * 32;
     return (unsigned)(g < cap ? g : cap);
 }
 

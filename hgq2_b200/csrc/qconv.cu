@@ -288,7 +288,7 @@ static int cl_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH
     while (tm < g.MB * g.Np) tm <<= 1;
     if (per_sm * tm > 512) per_sm = 512 / tm;
     if (per_sm < 1) return HGQ_ERR_SIZE;
-    int64_t grid = (int64_t)kNumSMs * per_sm;
+    int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > g.tiles) grid = g.tiles;
     g.grid = (int)grid;
     return HGQ_OK;

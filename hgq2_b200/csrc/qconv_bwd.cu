@@ -544,7 +544,7 @@ static int cs_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH
     while (tm < KH * g.ncg * g.Np * (g.stack ? 2 : 1)) tm <<= 1;
     if (per_sm * tm > 512) per_sm = 512 / tm;
     if (per_sm < 1) return HGQ_ERR_SIZE;
-    int64_t grid = (int64_t)kNumSMs * per_sm;
+    int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > g.tiles) grid = g.tiles;
     g.grid = (int)grid;
     return HGQ_OK;
@@ -574,7 +574,7 @@ static int cw_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH
         per_sm = 1;
     }
     if (per_sm < 1 || g.smem > 226 * 1024) return HGQ_ERR_SIZE;
-    int64_t grid = (int64_t)kNumSMs * per_sm;
+    int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > g.tiles) grid = g.tiles;
     g.grid = (int)grid;
     return HGQ_OK;
@@ -589,7 +589,7 @@ extern "C" size_t hgq_qconv2d_wgrad_workspace(int64_t B, int H, int W, int C, in
     CsGeom gs;
     if (cw_geom(B, H, W, C, KH, KW, N, OH, OW, g) != HGQ_OK && cs_geom(B, H, W, C, KH, KW, N, OH, OW, 1, 1, gs) != HGQ_OK) return 0;
     if (C % 4 != 0 && cs_geom(B, H, W, C, KH, KW, N, OH, OW, 1, 1, gs) != HGQ_OK) return 0;  // only the unit-stride kernel takes such images
-    return (size_t)3 * kNumSMs * ((size_t)KH * KW * C + 1) * N * sizeof(float);
+    return (size_t)3 * num_sms() * ((size_t)KH * KW * C + 1) * N * sizeof(float);
 }
 
 extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y, float *gm, float *dwq, float *dbq, int64_t B,

@@ -544,7 +544,7 @@ static int qd_geom(int64_t M, int K, int N, int rows_period, bool want_amax, boo
     // TMEM: 512 columns per SM
     const int cols = g.Npad < 32 ? 32 : g.Npad;
     if (per_sm * cols > 512) per_sm = 512 / cols;
-    int64_t grid = (int64_t)kNumSMs * per_sm;
+    int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > g.tiles) grid = g.tiles;
     g.grid = (int)grid;
     return HGQ_OK;
@@ -557,7 +557,7 @@ using namespace hgq;
 extern "C" size_t hgq_qdense_fwd_workspace(int64_t M, int K, int N, int rows_period) {
     QdGeom g;
     if (qd_geom(M, K, N, rows_period, true, false, g) != HGQ_OK) return 0;
-    return (size_t)kNumSMs * 4 * rows_period * K * sizeof(unsigned);  // room for the largest grid any variant launches
+    return (size_t)num_sms() * 4 * rows_period * K * sizeof(unsigned);  // room for the largest grid any variant launches
 }
 
 extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi, const float *qf, int rows_period,

@@ -494,7 +494,7 @@ static int qb_geom(int64_t M, int K, int N, int rows_period, QbGeom &g) {
              (size_t)kQbTileM * (g.Kp + 4) * 4 + tab + 64;
     if (g.smem > 226 * 1024) return HGQ_ERR_SIZE;
     g.tiles = (M + kQbTileM - 1) / kQbTileM;
-    int64_t grid = kNumSMs;  // 512 threads, > 113 KB shared memory: one CTA per SM
+    int64_t grid = num_sms();  // 512 threads, > 113 KB shared memory: one CTA per SM
     if (grid > g.tiles) grid = g.tiles;
     g.grid = (int)grid;
     g.part_stride = (int64_t)(K + 1) * N + (int64_t)rows_period * K;
@@ -508,7 +508,7 @@ using namespace hgq;
 extern "C" size_t hgq_qdense_bwd_workspace(int64_t M, int K, int N, int rows_period) {
     QbGeom g;
     if (qb_geom(M, K, N, rows_period, g) != HGQ_OK) return 0;
-    return (size_t)kNumSMs * g.part_stride * sizeof(float);
+    return (size_t)num_sms() * g.part_stride * sizeof(float);
 }
 
 extern "C" int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float *qf, int rows_period,

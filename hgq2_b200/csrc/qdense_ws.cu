@@ -498,7 +498,7 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
     p.M = M; p.num_tiles = (M + kWsTileM - 1) / kWsTileM;
     p.K = K; p.N = N; p.Kpad = Kpad; p.Npad = Npad; p.Kt = Kt; p.rows_period = rows_period;
     p.rm = round_mode; p.act = activation; p.depth = depth;
-    const int g = (int)(p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs);
+    const int g = (int)(p.num_tiles < num_sms() ? p.num_tiles : num_sms());
     *grid = g;
 #define HGQ_WS_LAUNCH(CV, AM, PW, EWW)                                                                                      \
     do {                                                                                                                    \

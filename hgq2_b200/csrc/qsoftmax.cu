@@ -11,7 +11,8 @@
 // and the score tensor is read once (forward) or twice (backward: s and dL/dy) and written once.
 // HBM-bound: 8 B per score forward, 12 B backward.
 //
-// Side outputs of the forward: the abs-max statistics the WRAP quantizers track (a scalar for Q3, a table for Q5).
+// Side outputs of the forward: the abs-max statistics the WRAP quantizers track (scalars for Q1 and Q3, a table for Q5;
+// Q2 and Q4 are table outputs, which the layer forces to SAT).
 // The backward recomputes the chain from s and accumulates the surrogate gradients of all five quantizers: scalars are
 // summed per thread, then per CTA in a fixed order, then over CTAs by a second kernel; the Q5 table gradient is owned
 // by the warp lanes of the CTA that handles that table row for a range of batches.
@@ -37,6 +38,7 @@ struct SmParams {
     const float *i5, *f5;
     int rm5, om5;
     float scaler, eps;
+    unsigned *amax1;       // forward: scalar abs-max of round(d) (as bits), or nullptr
     unsigned *amax3;       // forward: scalar abs-max of round(S) (as bits), or nullptr
     unsigned *amax5;       // forward: [rows_period, L] abs-max of round(z), or nullptr
     float *part;           // backward: per-CTA partials: 8 scalars (di1, df1, di2, df2, di3, df3, di4, df4), then per
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P
         q5[j] = make_qc((P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c), (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c),
                         __ldg(P.f5 + c), P.rm5, P.om5);
     }
-    float am5[VE], am3 = 0.f;
+    float am5[VE], am3 = 0.f, am1 = 0.f;
 #pragma unroll
     for (int j = 0; j < VE; ++j) am5[j] = 0.f;
     for (int64_t bt = (int64_t)sp + (int64_t)warp * P.splits; bt < P.batches; bt += (int64_t)P.splits * kSmWarps) {
@@ -200,6 +202,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
             float r;
+            am1 = fmaxf(am1, fabsf(ra[j]));
             y[j] = qc_fwd(__fmul_rn(b[j], u), q5[j], r);
             am5[j] = fmaxf(am5[j], fabsf(r));
         }
@@ -210,6 +213,10 @@ __global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P
         for (int j = 0; j < VE; ++j) atomicMax(P.amax5 + p * L + lane * VE + j, __float_as_uint(am5[j]));
     }
     if (P.amax3 != nullptr && lane == 0) atomicMax(P.amax3, __float_as_uint(am3));
+    if (P.amax1 != nullptr) {
+        am1 = warp_max(am1);
+        if (lane == 0) atomicMax(P.amax1, __float_as_uint(am1));
+    }
 }
 
 // Four resident CTAs (64 registers per thread): the per-row dependency chains (five warp reductions, exp, divide) need
@@ -345,7 +352,7 @@ __global__ void __launch_bounds__(kThreads) k_qsoftmax_stage2(const float *__res
 }
 
 static int sm_splits(int64_t batches, int rows_period) {
-    int64_t s = ((int64_t)kNumSMs * 8 + rows_period - 1) / rows_period;
+    int64_t s = ((int64_t)num_sms() * 8 + rows_period - 1) / rows_period;
     const int64_t maxs = (batches + kSmWarps - 1) / kSmWarps;
     if (s > maxs) s = maxs;
     if (s < 1) s = 1;
@@ -395,13 +402,19 @@ static SmParams sm_make(const float *s, const float *gy, float *y, const uint8_t
 
 extern "C" int hgq_qsoftmax_fwd(const float *s, float *y, const uint8_t *const *qk, const float *const *qi,
                                 const float *const *qf, const int *qrm, const int *qom, float scaler, float eps,
-                                float *absmax_inv_in, float *absmax_out, int64_t R, int L, int rows_period, void *stream) {
+                                float *absmax_exp_in, float *absmax_inv_in, float *absmax_out, int64_t R, int L,
+                                int rows_period, void *stream) {
     if (!qk || !qi || !qf || !qrm || !qom) return HGQ_ERR_NULL;
     SmParams p = sm_make(s, nullptr, y, qk, qi, qf, qrm, qom, scaler, eps, R, L, rows_period);
     if (int e = sm_check(p, R)) return e;
     cudaStream_t st = (cudaStream_t)stream;
+    p.amax1 = (unsigned *)absmax_exp_in;
     p.amax3 = (unsigned *)absmax_inv_in;
     p.amax5 = (unsigned *)absmax_out;
+    if (absmax_exp_in) {
+        cudaError_t e = cudaMemsetAsync(absmax_exp_in, 0, sizeof(float), st);
+        if (e != cudaSuccess) return (int)e;
+    }
     if (absmax_inv_in) {
         cudaError_t e = cudaMemsetAsync(absmax_inv_in, 0, sizeof(float), st);
         if (e != cudaSuccess) return (int)e;

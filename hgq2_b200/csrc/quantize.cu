@@ -522,8 +522,7 @@ constexpr size_t kNoAllocScratchBytes = HGQ_NOALLOC_SCRATCH_BYTES;
 __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 constexpr int kNoAllocMaxDevices = 64;
-void *g_noalloc_addr[kNoAllocMaxDevices] = {};  // device address of g_noalloc_scratch, per device
-std::atomic<bool> g_noalloc_ready[kNoAllocMaxDevices];
+std::atomic<void *> g_noalloc_addr[kNoAllocMaxDevices];  // device address of g_noalloc_scratch, per device (null: not looked up yet)
 
 // In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use:
 // the device address is looked up once per device, with that device current.
@@ -532,15 +531,14 @@ int noalloc_scratch_address(void **out) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= kNoAllocMaxDevices) return HGQ_ERR_DEVICE;
-    if (!g_noalloc_ready[dev].load(std::memory_order_acquire)) {
-        void *p = nullptr;
+    void *p = g_noalloc_addr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess) return (int)e;
         if (p == nullptr) return HGQ_ERR_DEVICE;
-        g_noalloc_addr[dev] = p;  // two threads racing here store the same value
-        g_noalloc_ready[dev].store(true, std::memory_order_release);
+        g_noalloc_addr[dev].store(p, std::memory_order_release);  // first callers that race here store the same address
     }
-    *out = g_noalloc_addr[dev];
+    *out = p;
     return HGQ_OK;
 }
 

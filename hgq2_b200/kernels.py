@@ -319,22 +319,25 @@ def qsoftmax_supported(L: int) -> bool:
     return L in (32, 64, 128)
 
 
-def qsoftmax_fwd(s, quants, scaler: float, eps: float, rows_period: int, want_amax3: bool, want_amax5: bool):
-    """Fused training-mode QSoftmax forward over the last axis of s.  Returns (y, amax3 or None, amax5 or None)."""
+def qsoftmax_fwd(s, quants, scaler: float, eps: float, rows_period: int, want_amax3: bool, want_amax5: bool,
+                 want_amax1: bool = False):
+    """Fused training-mode QSoftmax forward over the last axis of s.  Returns (y, amax3 or None, amax5 or None, amax1 or
+    None): the abs-max statistics of the inverse table's input, the layer output and the exp table's input."""
     require_cuda(s)
     s = s.contiguous()
     L = s.shape[-1]
     R = s.numel() // L
     y = torch.empty_like(s)
+    a1 = torch.empty(1, dtype=torch.float32, device=s.device) if want_amax1 else None
     a3 = torch.empty(1, dtype=torch.float32, device=s.device) if want_amax3 else None
     a5 = torch.empty(rows_period * L, dtype=torch.float32, device=s.device) if want_amax5 else None
     qk, qi, qf, rms, oms, keep = _quant_arrays(quants)
     with torch.cuda.device(s.device):
-        st = lib().hgq_qsoftmax_fwd(ptr(s), ptr(y), qk, qi, qf, rms, oms, float(scaler), float(eps), ptr(a3), ptr(a5), R, L,
-                                    rows_period, stream_handle())
+        st = lib().hgq_qsoftmax_fwd(ptr(s), ptr(y), qk, qi, qf, rms, oms, float(scaler), float(eps), ptr(a1), ptr(a3), ptr(a5),
+                                    R, L, rows_period, stream_handle())
     check(st, 'hgq_qsoftmax_fwd')
     del keep
-    return y, a3, a5
+    return y, a3, a5, a1
 
 
 def qsoftmax_bwd(gy, s, quants, scaler: float, eps: float, rows_period: int, want_di5: bool):

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from .. import kernels
+from .. import kernels, routes
 from ..backend import bookkeeping
 
 _ones: dict = {}
@@ -94,6 +94,7 @@ class QDenseFusedFn(torch.autograd.Function):
                 df = df.view(f.shape)
             di = torch.zeros_like(i) if (need_i and i is not None) else None
             return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None, None
+        routes.fallback('cuBLAS backward of a dense layer', f'M={x.numel() // K} K={K} N={N} period={rows_period} {rm}/{om}')
         if gy_repeat > 1:
             gy = gy.unsqueeze(1).expand(-1, gy_repeat, -1)
         if activation == 'relu':
@@ -320,21 +321,22 @@ class QSoftmaxFusedFn(torch.autograd.Function):
     layer's output quantizer ([rows_period * L] tables); ``i`` / ``k`` are None for a rounding-only quantizer."""
 
     @staticmethod
-    def forward(ctx, s, modes, scaler, eps, rows_period, want_amax3, want_amax5, *params):
+    def forward(ctx, s, modes, scaler, eps, rows_period, want_amax3, want_amax5, want_amax1, *params):
         quants = [(params[3 * j], params[3 * j + 1], params[3 * j + 2], modes[j][0], modes[j][1]) for j in range(5)]
         quants = [(None if k is None else (k if k.dtype == torch.uint8 else k.to(torch.uint8)), i, f, rm, om)
                   for k, i, f, rm, om in quants]
-        y, a3, a5 = kernels.qsoftmax_fwd(s, quants, scaler, eps, rows_period, want_amax3, want_amax5)
+        y, a3, a5, a1 = kernels.qsoftmax_fwd(s, quants, scaler, eps, rows_period, want_amax3, want_amax5, want_amax1)
         ctx.save_for_backward(s, *[t for q in quants for t in q[:3]])
         ctx.meta = (modes, scaler, eps, rows_period, [None if t is None else tuple(t.shape) for t in params])
         empty = torch.empty(0, device=s.device)
+        a1 = empty if a1 is None else a1
         a3 = empty if a3 is None else a3
         a5 = empty if a5 is None else a5
-        ctx.mark_non_differentiable(a3, a5)
-        return y, a3, a5
+        ctx.mark_non_differentiable(a3, a5, a1)
+        return y, a3, a5, a1
 
     @staticmethod
-    def backward(ctx, gy, _g3, _g5):
+    def backward(ctx, gy, _g3, _g5, _g1):
         s, *flat = ctx.saved_tensors
         modes, scaler, eps, rows_period, shapes = ctx.meta
         quants = [(flat[3 * j], flat[3 * j + 1], flat[3 * j + 2], modes[j][0], modes[j][1]) for j in range(5)]
@@ -350,4 +352,4 @@ class QSoftmaxFusedFn(torch.autograd.Function):
                 gi = None if i is None else (di5.view(shapes[13]) if di5 is not None else torch.zeros(shapes[13], device=s.device))
                 gf = df5.view(shapes[14])
             grads += [None, gi, gf]
-        return (ds, None, None, None, None, None, None, *grads)
+        return (ds, None, None, None, None, None, None, None, *grads)

@@ -12,6 +12,7 @@ import math
 
 import torch
 
+from ... import routes
 from ...backend import Constant, queue_params
 from ...quantizer.config import QuantizerConfig
 from .._functions import AttnContextFn, AttnScoresFn, EbopsDenseFn, attn_products_supported
@@ -186,6 +187,7 @@ class QMultiHeadAttention(QLayerBase):
         if attn_products_supported(query, key, value):
             scores = self._softmax(AttnScoresFn.apply(key, query))
             return AttnContextFn.apply(scores, value), scores
+        routes.fallback('torch.einsum', f'attention products of {self.name}')
         scores = torch.einsum(self._dot_product_equation, key, query)
         scores = self._softmax(scores)
         return torch.einsum(self._combine_equation, scores, value), scores

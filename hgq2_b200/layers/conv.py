@@ -7,19 +7,12 @@ from math import ceil, prod
 import torch
 import torch.nn.functional as F
 
+from .. import routes
 from ..backend import activation_name, get_activation, get_initializer, take_prepared
 from ..quantizer import Quantizer
 from ..quantizer.config import QuantizerConfig
 from ._functions import EbopsConv2dFn, fused_conv2d_call
 from .core.base import QLayerBaseSingleInput
-
-
-# The library convolution must multiply fp32 operands at full precision in forward *and* backward (the reference's
-# tests pin matmul precision to 'highest'); cuDNN's TF32 default would round operands to 10 mantissa bits.
-torch.backends.cudnn.allow_tf32 = False
-# Let cuDNN time its algorithms per shape: its heuristic picks FFT-based fp32 kernels (with layout transposes) for these
-# small 3x3 convolutions, which the direct NHWC kernels beat by a wide margin.
-torch.backends.cudnn.benchmark = True
 
 
 def _pair(v):
@@ -31,6 +24,26 @@ def same_padding(size: int, kernel: int, stride: int, dilation: int) -> tuple[in
     out = ceil(size / stride)
     total = max((out - 1) * stride + (kernel - 1) * dilation + 1 - size, 0)
     return total // 2, total - total // 2
+
+
+class _Conv2dFullPrecision(torch.autograd.Function):
+    """torch's conv2d with the cuDNN flags of the forward call (fp32 operands, no TF32) applied to its backward too:
+    autograd runs the backward outside the ``with`` block of the forward, so the flags are set again around it."""
+
+    @staticmethod
+    def forward(ctx, x, w, strides, dilation):
+        ctx.save_for_backward(x, w)
+        ctx.geom = (strides, dilation)
+        return F.conv2d(x, w, stride=strides, dilation=dilation)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        strides, dilation = ctx.geom
+        with torch.backends.cudnn.flags(enabled=True, benchmark=True, deterministic=False, allow_tf32=False):
+            gx = torch.nn.grad.conv2d_input(x.shape, w, gy, stride=strides, dilation=dilation) if ctx.needs_input_grad[0] else None
+            gw = torch.nn.grad.conv2d_weight(x, w.shape, gy, stride=strides, dilation=dilation) if ctx.needs_input_grad[1] else None
+        return gx, gw, None, None
 
 
 class QConv2D(QLayerBaseSingleInput):
@@ -124,7 +137,12 @@ class QConv2D(QLayerBaseSingleInput):
         # NHWC data viewed as NCHW is exactly torch's channels_last layout; giving the (tiny) kernel the same layout lets
         # cuDNN run its NHWC kernels end to end, so no transposition of the activations happens on either side
         w = kernel.permute(3, 2, 0, 1).contiguous(memory_format=torch.channels_last)
-        y = F.conv2d(x, w, stride=self.strides, dilation=self.dilation_rate)
+        # The library convolution must multiply fp32 operands at full precision in forward *and* backward (the reference's
+        # tests pin matmul precision to 'highest'; cuDNN's TF32 default would round operands to 10 mantissa bits), and is
+        # left to time its algorithms per shape (its heuristic picks FFT-based kernels with layout transposes for these
+        # small 3x3 cases).  Both settings are scoped to this call: the process-wide cuDNN flags are the host's.
+        with torch.backends.cudnn.flags(enabled=True, benchmark=True, deterministic=False, allow_tf32=False):
+            y = _Conv2dFullPrecision.apply(x, w, self.strides, self.dilation_rate)
         return y.permute(0, 2, 3, 1)
 
     def prepare_params(self):
@@ -138,6 +156,7 @@ class QConv2D(QLayerBaseSingleInput):
         fused = fused_conv2d_call(self, inputs, qkernel, qbias)
         if fused is not None:
             return fused
+        routes.fallback('cudnn.conv2d', f'QConv2D {self.name}')
         outputs = self.convolution_op(inputs, qkernel)
         if self.use_bias:
             outputs = outputs + qbias.reshape(1, 1, 1, self.filters)

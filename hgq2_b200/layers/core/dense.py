@@ -6,6 +6,7 @@ from math import prod
 
 import torch
 
+from ... import routes
 from ...backend import activation_name, get_activation, get_initializer, moments, take_prepared
 from ...quantizer import Quantizer
 from ...quantizer.config import QuantizerConfig
@@ -79,6 +80,7 @@ class QDense(QLayerBaseSingleInput):
         y = fused_dense_call(self, inputs, 1, qkernel, qbias, training)
         if y is not None:
             return y
+        routes.fallback('torch.matmul', f'QDense {self.name}')
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
         x = torch.matmul(inputs, qkernel)
@@ -181,6 +183,7 @@ class QBatchNormDense(QDense):
         y = fused_dense_call(self, inputs, 1, qkernel, qbias, training, apply_iq=False)
         if y is not None:
             return y
+        routes.fallback('torch.matmul', f'QBatchNormDense {self.name}')
         x = torch.matmul(inputs, qkernel) + qbias
         if self.activation is not None:
             x = self.activation(x)

@@ -6,6 +6,7 @@ from math import prod
 
 import torch
 
+from ... import routes
 from ...backend import activation_name, get_activation, get_initializer, take_prepared
 from ...quantizer import Quantizer
 from ...quantizer.config import QuantizerConfig
@@ -163,6 +164,7 @@ class QEinsumDense(QLayerBaseSingleInput):
             y = fused_dense_call(self, inputs, n_con, qkernel.reshape(K, N), qb, training, apply_iq=apply_iq)
             if y is not None:
                 return y.reshape((inputs.shape[0],) + tuple(self.full_output_shape[1:]))
+        routes.fallback('torch.einsum', f'QEinsumDense {self.name} "{self.equation}"')
         if self.enable_iq and apply_iq:
             inputs = self.iq(inputs, training=training)
         x = torch.einsum(self.equation, inputs, qkernel)

@@ -12,6 +12,7 @@ from math import prod
 
 import torch
 
+from .. import routes
 from ..backend import bookkeeping, epsilon
 from ..config.layer import global_config
 from ..quantizer import QuantizerConfig
@@ -120,9 +121,14 @@ class QSoftmax(QLayerBaseSingleInput):
                     t = t.expand(full).reshape(rows_period * L)
                 params.append(t)
         modes = tuple((plan['round_mode'], plan['overflow_mode']) for plan in plans)
-        y, a3, a5 = _functions.QSoftmaxFusedFn.apply(inputs, modes, float(self.input_scaler), float(epsilon()), rows_period,
-                                                     plans[2]['track'] is not None, p5['track'] is not None, *params)
-        with bookkeeping(a3, a5):
+        if plans[1]['track'] is not None or plans[3]['track'] is not None:
+            return None  # a table output that tracks its integer bits (the layer forces them to SAT, so this is a custom setup)
+        y, a3, a5, a1 = _functions.QSoftmaxFusedFn.apply(inputs, modes, float(self.input_scaler), float(epsilon()), rows_period,
+                                                         plans[2]['track'] is not None, p5['track'] is not None,
+                                                         plans[0]['track'] is not None, *params)
+        with bookkeeping(a1, a3, a5):
+            if plans[0]['track'] is not None:  # the exp table's input quantizer in WRAP mode (the layer's default)
+                plans[0]['track'](a1.view(plans[0]['f'].shape), None)
             if plans[2]['track'] is not None:
                 plans[2]['track'](a3.view(plans[2]['f'].shape), None)
             if p5['track'] is not None:
@@ -142,6 +148,8 @@ class QSoftmax(QLayerBaseSingleInput):
             if y is not None:
                 self.__output_quantizer_handled__ = True  # the kernel applied self.oq; the call wrapper must not repeat it
                 return y
+        if training is True and inputs.is_cuda:
+            routes.fallback('softmax chain in torch', f'QSoftmax {self.name}')
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
         if self.stable:

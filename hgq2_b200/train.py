@@ -136,10 +136,13 @@ class DataParallel:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
 
-    def sync_gradients(self, grads: torch.Tensor) -> None:
+    def sync_gradients(self, grads: torch.Tensor, average: bool = True) -> None:
+        """Sum the gradient bucket over the ranks; ``average=False`` leaves the division by the number of ranks to the
+        caller (the trainer folds it into the optimizer kernel's gradient scale instead of a pass of its own)."""
         if self.world > 1:
             dist.all_reduce(grads, op=dist.ReduceOp.SUM, group=self.group)
-            grads.div_(self.world)
+            if average:
+                grads.div_(self.world)
 
     def absmax_sync(self, absmax: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
@@ -192,7 +195,13 @@ class Trainer:
         self.dp = dp
         self.state = FlatState(model)
         self.opt = FusedAdam(self.state, learning_rate=learning_rate)
-        self._graph = None
+        self._graphs = []      # captured steps, one per set of static input buffers
+        self._sbuf = []        # the static (x, y) buffers the graphs read
+        self._next_buf = 0
+        # status word of the tensor-core kernels (set when a bounded device-side wait gives up), read back without a sync
+        self._status_dev = None
+        self._status_host = None
+        self._status_event = None
 
     def forward_backward(self, x, y):
         self.state.zero_grad()
@@ -209,58 +218,134 @@ class Trainer:
         if self.dp is not None:
             with self.dp:
                 task, total = self.forward_backward(x, y)
-            self.dp.sync_gradients(self.state.grads)
+            self.dp.sync_gradients(self.state.grads, average=False)
+            self.opt.step(grad_scale=1.0 / self.dp.world)  # the mean over the ranks, folded into the optimizer kernel
         else:
             task, total = self.forward_backward(x, y)
-        self.opt.step()
+            self.opt.step()
+        self._queue_status_read()
         return total
 
-    def capture(self, x, y, warmup: int = 3) -> None:
-        """Record the step as a CUDA graph for batches shaped like (x, y).  Runs ``warmup`` real steps first."""
-        self._sx, self._sy = x.clone(), y.clone()
+    # -- device status ---------------------------------------------------------------------------------------------------
+    def _queue_status_read(self) -> None:
+        """Copy the device status word to pinned host memory behind the step (no synchronisation; part of a captured
+        step like any other node)."""
+        if not self.state.params.is_cuda:
+            return
+        from . import kernels
+
+        if self._status_dev is None:
+            self._status_dev = kernels.status_word(self.state.params.device)
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_host.copy_(self._status_dev, non_blocking=True)
+        if not torch.cuda.is_current_stream_capturing():
+            self._status_event = torch.cuda.Event()
+            self._status_event.record()
+
+    def check_status(self, wait: bool = False) -> None:
+        """Raise ``HGQError`` (HGQ_ERR_TIMEOUT) if a kernel of an earlier step reported that one of its bounded waits gave
+        up: that step's outputs, gradients and the update made from them are garbage.  Without ``wait`` only a read-back
+        that has already landed is looked at, so calling this at the start of every step costs no synchronisation; the
+        word is cleared once reported."""
+        if self._status_host is None:
+            return
+        ev = self._status_event
+        if ev is not None:
+            if wait:
+                ev.synchronize()
+            elif not ev.query():
+                return
+        if int(self._status_host[0]) != 0:
+            v = int(self._status_host[0])
+            self._status_host.zero_()
+            self._status_dev.zero_()
+            raise _lib.HGQError(-7, f'training step (device status word = {v})')
+
+    def capture(self, x, y, warmup: int = 3, double_buffer: bool = False) -> None:
+        """Record the step as a CUDA graph for batches shaped like (x, y).  Runs ``warmup`` real steps first.
+
+        ``double_buffer``: record the step twice, over two sets of static input buffers that share one memory pool;
+        ``prefetch`` then copies a host batch straight into the set the step after next will read, with no staging copy
+        on the device."""
+        self._sbuf = [(x.clone(), y.clone()) for _ in range(2 if double_buffer else 1)]
+        self._graphs, self._next_buf = [], 0
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(warmup):
-                self._eager_step(self._sx, self._sy)
+                self._eager_step(*self._sbuf[0])
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            self._sloss = self._eager_step(self._sx, self._sy)
-        self._graph = graph
+        self.check_status(wait=True)
+        pool = None
+        for sx, sy in self._sbuf:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=pool):
+                loss = self._eager_step(sx, sy)
+            pool = graph.pool()
+            self._graphs.append((graph, loss))
 
     def prefetch(self, hx, hy):
         """Start the host-to-device copy of a (pinned) host batch on a copy stream of its own and return a handle for
-        ``step_prefetched``.  Two device staging slots alternate, so the copy of batch n + 1 overlaps step n."""
+        ``step_prefetched``; the copy of batch n + 1 overlaps step n.  After ``capture(..., double_buffer=True)`` the
+        batch lands directly in the static buffers of the graph that will consume it; otherwise two device staging
+        slots alternate."""
         if not hasattr(self, '_copy_stream'):
             self._copy_stream = torch.cuda.Stream()
             self._slots = [None, None]
             self._slot = 0
-        j = self._slot
-        self._slot ^= 1
-        dev = self.state.params.device
-        if self._slots[j] is None or self._slots[j][0].shape != hx.shape or self._slots[j][1].shape != hy.shape:
-            self._slots[j] = (torch.empty(hx.shape, dtype=hx.dtype, device=dev), torch.empty(hy.shape, dtype=hy.dtype, device=dev))
-        dx, dy = self._slots[j]
-        self._copy_stream.wait_stream(torch.cuda.current_stream())  # the slot's previous batch has been consumed
+        direct = len(self._graphs) == 2 and hx.shape == self._sbuf[0][0].shape and hy.shape == self._sbuf[0][1].shape
+        if direct:
+            j = self._next_buf
+            self._next_buf ^= 1
+            dx, dy = self._sbuf[j]
+        else:
+            j = self._slot
+            self._slot ^= 1
+            dev = self.state.params.device
+            if self._slots[j] is None or self._slots[j][0].shape != hx.shape or self._slots[j][1].shape != hy.shape:
+                self._slots[j] = (torch.empty(hx.shape, dtype=hx.dtype, device=dev), torch.empty(hy.shape, dtype=hy.dtype, device=dev))
+            dx, dy = self._slots[j]
+        # everything queued so far has consumed the buffer's previous batch (two steps back; the step that overlaps this
+        # copy is launched after this call and reads the other buffer)
+        self._copy_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self._copy_stream):
             dx.copy_(hx, non_blocking=True)
             dy.copy_(hy, non_blocking=True)
             done = torch.cuda.Event()
             done.record()
-        return dx, dy, done
+        return dx, dy, done, (j if direct else None)
 
     def step_prefetched(self, handle):
         """``step`` on a batch started with ``prefetch``."""
-        dx, dy, done = handle
+        dx, dy, done, buf = handle
         torch.cuda.current_stream().wait_event(done)
+        if buf is not None:
+            self.check_status()
+            return self._replay(buf)
         return self.step(dx, dy)
 
     def step(self, x, y):
-        if self._graph is not None and x.shape == self._sx.shape and y.shape == self._sy.shape:
-            self._sx.copy_(x, non_blocking=True)
-            self._sy.copy_(y, non_blocking=True)
-            self._graph.replay()
-            return self._sloss
+        """One QAT step on a device batch; returns the loss (a device scalar, valid until the next step)."""
+        self.check_status()
+        if self._graphs and x.shape == self._sbuf[0][0].shape and y.shape == self._sbuf[0][1].shape:
+            sx, sy = self._sbuf[0]
+            if x.data_ptr() != sx.data_ptr():
+                sx.copy_(x, non_blocking=True)
+            if y.data_ptr() != sy.data_ptr():
+                sy.copy_(y, non_blocking=True)
+            return self._replay(0)
         return self._eager_step(x, y)
+
+    def _replay(self, buf: int):
+        graph, loss = self._graphs[buf]
+        graph.replay()
+        self._status_event = torch.cuda.Event()  # behind the replay, whose last node is the status read-back
+        self._status_event.record()
+        return loss
+
+    @property
+    def static_inputs(self):
+        """The static (x, y) buffers of the captured step: a caller that writes its batch there itself (and passes these
+        very tensors to ``step``) saves the device-to-device copy."""
+        return self._sbuf[0] if self._sbuf else None

@@ -130,6 +130,9 @@ int hgq_quantize_bwd(const float *g, const float *x, const uint8_t *k, const flo
  *
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with the
  * calling thread's current device); make that first call before any stream capture begins.
+ * The array used is the CURRENT device's: the calling thread's current device must be the device
+ * `stream` belongs to (cudaSetDevice before the call), otherwise the kernels would be handed another
+ * GPU's scratch address.
  * All calls on a device share the one array and it keeps the previous call's contents: nothing in it
  * has to be cleared (each call overwrites every word it later reads), but two calls whose kernels
  * overlap on the GPU -- different streams, no ordering between them -- race on it and corrupt each
@@ -213,11 +216,14 @@ int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const float *y, const
  * s, y [R, L] with the softmax over L (32, 64 or 128); R = batches * rows_period.  The quantizers come as HOST arrays
  * of five entries: qk / qi / qf hold device pointers (Q1..Q4: one element each; Q5: [rows_period, L] tables; qk / qi
  * entries may be NULL for a rounding-only quantizer), qrm the round modes, qom the overflow modes (NONE, SAT, SAT_SYM).
- * absmax_inv_in (1 float) and absmax_out ([rows_period, L]) receive max |round(S)| and max |round(b u)| (may be NULL).
+ * absmax_exp_in (1 float), absmax_inv_in (1 float) and absmax_out ([rows_period, L]) receive max |round(d)|,
+ * max |round(S)| and max |round(b u)|: the statistics the integer-bit tracking of a WRAP quantizer in those three places
+ * needs (fixed_point_quantizer.py:401-424); each may be NULL.
  */
 int hgq_qsoftmax_fwd(const float *s, float *y, const uint8_t *const *qk, const float *const *qi,
                      const float *const *qf, const int *qrm, const int *qom, float scaler, float eps,
-                     float *absmax_inv_in, float *absmax_out, int64_t R, int L, int rows_period, void *stream);
+                     float *absmax_exp_in, float *absmax_inv_in, float *absmax_out, int64_t R, int L, int rows_period,
+                     void *stream);
 
 size_t hgq_qsoftmax_bwd_workspace(int64_t R, int L, int rows_period);
 

@@ -23,32 +23,36 @@ from hgq2_b200.train import DataParallel, Trainer, shard_batch
 rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
 torch.cuda.set_device(int(os.environ['LOCAL_RANK']))
 dist.init_process_group('nccl', device_id=torch.device('cuda', int(os.environ['LOCAL_RANK'])))
-rng = np.random.default_rng(1)
-X = torch.from_numpy(rng.standard_normal((4096, 16)).astype(np.float32)).cuda()
-Y = torch.from_numpy(np.random.default_rng(2).integers(0, 5, 4096)).cuda()
 
-def run(dp):
-    model = workloads.build(workloads.jet_tagger_mlp())
+def run(builder, X, Y, dp):
+    model = workloads.build(builder())
     tr = Trainer(model, F.cross_entropy, dp=dp)
-    sl = shard_batch(4096, rank, world) if dp is not None else slice(None)
+    n = X.shape[0]
+    sl = shard_batch(n, rank, world) if dp is not None else slice(None)
     losses = [float(tr.step(X[sl], Y[sl])) for _ in range(3)]
-    state = [v.value.detach().clone() for v in model.variables]
-    return losses, tr.state.params.clone(), state, [int(l.ebops.item()) for l in model.layers]
+    state = [(v.path, v.value.detach().clone()) for v in model.non_trainable_variables]
+    return losses, tr.state.params.clone(), state, [int(l.ebops.item()) for l in model.layers if hasattr(l, '_ebops')]
 
-l_dp, p_dp, s_dp, e_dp = run(DataParallel())
-l_1, p_1, s_1, e_1 = run(None)
-assert e_dp == e_1, (e_dp, e_1)
-scale = float(p_1.abs().max())
-assert float((p_dp - p_1).abs().max()) <= 2e-3 * 3, float((p_dp - p_1).abs().max())
-frac_bad = float(((p_dp - p_1).abs() > 1e-5 * scale + 1e-7).float().mean())
-assert frac_bad <= 5e-3, frac_bad
-for a, b in zip(s_dp, s_1):
-    if not a.is_floating_point():
-        assert torch.equal(a, b)
-# every rank holds the same parameters
-q = p_dp.clone(); dist.all_reduce(q, op=dist.ReduceOp.MAX); assert torch.equal(q, p_dp)
-if rank == 0:
-    print('DP_OK', l_dp, l_1)
+# the small MLP ([1, F] abs-max tables) and the particle-set tagger ([1, 64, C] tables, a gradient that arrives as the
+# expansion of a sum over the particles)
+CASES = (('jet_tagger_mlp', workloads.jet_tagger_mlp, (4096, 16)), ('particle_tagger', workloads.particle_tagger, (512, 64, 16)))
+for name, builder, shape in CASES:
+    X = torch.from_numpy(np.random.default_rng(1).standard_normal(shape).astype(np.float32)).cuda()
+    Y = torch.from_numpy(np.random.default_rng(2).integers(0, 5, shape[0])).cuda()
+    l_dp, p_dp, s_dp, e_dp = run(builder, X, Y, DataParallel())
+    l_1, p_1, s_1, e_1 = run(builder, X, Y, None)
+    assert e_dp == e_1, (name, e_dp, e_1)
+    scale = float(p_1.abs().max())
+    assert float((p_dp - p_1).abs().max()) <= 2e-3 * 3, (name, float((p_dp - p_1).abs().max()))
+    frac_bad = float(((p_dp - p_1).abs() > 1e-5 * scale + 1e-7).float().mean())
+    assert frac_bad <= 5e-3, (name, frac_bad)
+    for (path, a), (_, b) in zip(s_dp, s_1):  # quantizer state (tracked integer bits, keep-negative flags) and EBOPs: identical
+        assert torch.equal(a, b), (name, path)
+    # every rank holds the same parameters
+    q = p_dp.clone(); dist.all_reduce(q, op=dist.ReduceOp.MAX); assert torch.equal(q, p_dp), name
+    if rank == 0:
+        print('DP_OK', name, 'world', world, 'losses dp', [round(v, 6) for v in l_dp], 'single', [round(v, 6) for v in l_1],
+              'ebops', e_dp, 'max |dparam|', float((p_dp - p_1).abs().max()), flush=True)
 dist.destroy_process_group()
 '''
 
@@ -64,4 +68,5 @@ def test_two_rank_data_parallel_matches_single_rank(tmp_path):
     env = dict(os.environ, HGQ_ROOT=str(ROOT), NCCL_NVLS_ENABLE='0')
     r = subprocess.run([sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node=2', '--master-addr', '127.0.0.1',
                         '--master-port', str(port), str(script)], capture_output=True, text=True, env=env, timeout=600)
-    assert r.returncode == 0 and 'DP_OK' in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+    assert r.returncode == 0 and r.stdout.count('DP_OK') == 2, r.stdout[-2000:] + r.stderr[-4000:]
+    print(r.stdout)
