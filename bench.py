@@ -382,6 +382,12 @@ def run_qat_single(args):
                       'loss': float(loss)}), flush=True)
 
 
+def progress(msg: str) -> None:
+    """Phase marker on stderr (rank 0): tells where a run stopped if it does not reach its JSON line."""
+    if int(os.environ.get('RANK', '0')) == 0:
+        print(f'[bench {time.strftime("%H:%M:%S")}] {msg}', file=sys.stderr, flush=True)
+
+
 def run_qat(args, dev, world, rank, peak):
     """Full QAT steps (forward, backward, gradient all-reduce, fused Adam) of the benchmark models; the global batch is
     fixed and sharded over the ranks.  Reported beside the sweep: samples/s with the batch resident on the device, the
@@ -400,6 +406,7 @@ def run_qat(args, dev, world, rank, peak):
         if only and name not in only:
             continue
         try:
+            progress(f'qat {name}: build')
             model = workloads.build(getattr(workloads, builder)(), device=dev)
             cpu = None
             if rank == 0 and world == 1 and not args.no_cpu:
@@ -410,12 +417,14 @@ def run_qat(args, dev, world, rank, peak):
             hy = torch.from_numpy(np.random.default_rng(2).integers(0, classes, batch)[sl]).pin_memory()
             x, y = hx.to(dev), hy.to(dev)
             steps = max(3, args.steps)
+            progress(f'qat {name}: capture')
             routes.reset()
             # the whole step as one CUDA graph, recorded over two sets of static input buffers so that a host batch can be
             # copied straight into the set the step after next reads
             tr.capture(x, y, warmup=3, double_buffer=True)
             fallbacks = routes.fallbacks()  # library routines a layer fell back to while the step was recorded (none expected)
             x, y = tr.static_inputs  # the batch is resident where the captured step reads it
+            progress(f'qat {name}: timed steps')
             for _ in range(3):
                 tr.step(x, y)
             torch.cuda.synchronize()
@@ -431,6 +440,7 @@ def run_qat(args, dev, world, rank, peak):
             # end to end: host batch in, loss out, every step
             # every step copies its batch from pinned host memory and reads its loss back; the copy of batch n + 1 is
             # started before step n is launched, so it overlaps the step (it lands in the other set of static buffers)
+            progress(f'qat {name}: end-to-end steps')
             for _ in range(2):  # untimed warm-up of the copy stream
                 tr.step_prefetched(tr.prefetch(hx, hy))
             torch.cuda.synchronize()
@@ -458,6 +468,7 @@ def run_qat(args, dev, world, rank, peak):
                 'modelled_bytes_per_sample': bytes_per_sample, 'loss': round(loss_host, 5), 'cuda_graph': True,
                 'library_fallbacks': fallbacks, 'cpu_baseline': cpu,
             })
+            progress(f'qat {name}: done')
             del model, tr, x, y, hx, hy
             torch.cuda.empty_cache()
         except Exception as exc:

@@ -108,12 +108,36 @@ SIGNATURES: dict[str, tuple] = {
         + [c_void_p] * 7,
     ),
     'hgq_adam_step': (c_int, [c_void_p] * 7 + [c_int64] + [c_float] * 5 + [c_void_p, c_void_p]),
+    'hgq_tables_forward': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
+    'hgq_tables_track_bits': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
+    'hgq_tables_backward': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
+    'hgq_weights_forward': (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+    'hgq_weights_backward': (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     'hgq_quantize_host_workspace': (c_size_t, [c_int64]),
     'hgq_quantize_fwd_bwd_host': (
         c_int,
         [c_void_p] * 9 + [c_int64, c_int, c_int, c_uint, c_void_p, c_size_t, c_int64],
     ),
 }
+
+
+
+class SlotDesc(ctypes.Structure):
+    """hgq_slot_desc of include/hgq_b200.h."""
+
+    _fields_ = [('a_raw', c_void_p), ('i_raw', c_void_p), ('k', c_void_p), ('I', c_void_p), ('F', c_void_p), ('BITS', c_void_p),
+                ('dI', c_void_p), ('dF', c_void_p), ('dBITS', c_void_p), ('g_a', c_void_p), ('g_i', c_void_p),
+                ('absmax', c_void_p), ('decay', c_void_p), ('n', c_int64), ('kind', ctypes.c_int32), ('om', ctypes.c_int32),
+                ('rm', ctypes.c_int32), ('symmetric', ctypes.c_int32), ('tracked_weight', ctypes.c_int32), ('i_lo', c_float),
+                ('i_hi', c_float)]
+
+
+class WeightDesc(ctypes.Structure):
+    """hgq_weight_desc of include/hgq_b200.h."""
+
+    _fields_ = [('w_raw', c_void_p), ('wq', c_void_p), ('dwq', c_void_p), ('g_w', c_void_p), ('n', c_int64),
+                ('slot', ctypes.c_int32), ('mode', ctypes.c_int32)]
+
 
 _lib = None  # the loaded library behind a call-counting proxy (hgq2_b200.routes)
 

@@ -19,6 +19,12 @@ def workspace(nbytes: int, device: torch.device, slot: int = 0) -> torch.Tensor 
     (``slot``) and stream: kernels queued on different streams may run at the same time and must not share scratch."""
     if nbytes <= 0:
         return None
+    if torch.cuda.is_current_stream_capturing():
+        # Inside a graph capture the scratch is a temporary of the graph's own memory pool, like any other tensor of the
+        # captured step.  A cached buffer must not be used here: one that an earlier capture allocated belongs to that
+        # graph's pool, and once it is replaced (a later call needs a larger one) and that graph is gone, the pool hands
+        # its memory back to the driver while this graph's kernels still hold the address.
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
     dev = device.index if device.index is not None else torch.cuda.current_device()
     key = (dev, slot, torch.cuda.current_stream(dev).cuda_stream)
     ws = _workspaces.get(key)
@@ -55,8 +61,10 @@ def quantize_fwd(
     zero_nonpos: bool = False,
     want_absmax: bool = False,
     out: torch.Tensor | None = None,
+    absmax_out: torch.Tensor | None = None,
 ):
-    """y = overflow(round(x, f), k, i, f); optionally also max_rows |round(x, f)| per parameter entry.
+    """y = overflow(round(x, f), k, i, f); optionally also max_rows |round(x, f)| per parameter entry (into ``absmax_out``
+    when given).
 
     ``k`` is uint8, ``i``/``f`` fp32 with integer values.  Parameters either match ``x`` element
     for element or hold ``period`` entries that repeat along the leading axes of ``x``.
@@ -72,7 +80,7 @@ def quantize_fwd(
         assert k.dtype == torch.uint8
     period = _period(x, f)
     y = out if out is not None else torch.empty_like(x)
-    absmax = torch.empty(period, dtype=torch.float32, device=x.device) if want_absmax else None
+    absmax = (absmax_out if absmax_out is not None else torch.empty(period, dtype=torch.float32, device=x.device)) if want_absmax else None
     flags = (FLAG_TRAINING if training else 0) | (FLAG_ZERO_NONPOS if zero_nonpos else 0)
     with torch.cuda.device(x.device):
         st = lib().hgq_quantize_fwd(
@@ -92,8 +100,11 @@ def quantize_bwd(
     overflow_mode: str,
     want_dx: bool = True,
     want_di: bool = True,
+    out_df: torch.Tensor | None = None,
+    out_di: torch.Tensor | None = None,
 ):
-    """Surrogate gradients (dx, di, df) of the training-mode quantizer; di/df are reduced to the parameter shape."""
+    """Surrogate gradients (dx, di, df) of the training-mode quantizer; di/df are reduced to the parameter shape (and
+    written to ``out_di`` / ``out_df`` when given)."""
     require_cuda(g, x, k, i, f)
     rm, om = _modes(round_mode, overflow_mode)
     g = g.contiguous()
@@ -104,8 +115,8 @@ def quantize_bwd(
     n = x.numel()
     period = _period(x, f)
     dx = torch.empty_like(x) if (want_dx or period == n) else None
-    di = torch.empty(period, dtype=torch.float32, device=x.device) if want_di else None
-    df = torch.empty(period, dtype=torch.float32, device=x.device)
+    di = (out_di if out_di is not None else torch.empty(period, dtype=torch.float32, device=x.device)) if want_di else None
+    df = out_df if out_df is not None else torch.empty(period, dtype=torch.float32, device=x.device)
     nbytes = lib().hgq_quantize_bwd_workspace(n, period)
     ws = workspace(nbytes, x.device)
     with torch.cuda.device(x.device):
@@ -149,8 +160,9 @@ def quantize_host_workspace(chunk_elems: int) -> int:
     return int(lib().hgq_quantize_host_workspace(chunk_elems))
 
 
-def ebops_dense(bw_in, bw_w, bw_bias, out_size: float, scale: float, beta, want_grads: bool = True):
-    """K3 for a dense / einsum-dense layer.  bw_in [P, K], bw_w [K, N]; returns (ebops_u32, ebops_f, loss, d_in, d_w, d_bias)."""
+def ebops_dense(bw_in, bw_w, bw_bias, out_size: float, scale: float, beta, want_grads: bool = True, out=None):
+    """K3 for a dense / einsum-dense layer.  bw_in [P, K], bw_w [K, N]; returns (ebops_u32, ebops_f, loss, d_in, d_w, d_bias).
+    ``out``: caller-owned (ebops_u32, loss, d_in, d_w, d_bias) destinations instead of fresh tensors."""
     require_cuda(bw_in, bw_w, bw_bias, beta)
     bw_in, bw_w = bw_in.contiguous(), bw_w.contiguous()
     P, K = bw_in.shape
@@ -159,12 +171,16 @@ def ebops_dense(bw_in, bw_w, bw_bias, out_size: float, scale: float, beta, want_
     dev = bw_in.device
     nb = 0 if bw_bias is None else bw_bias.numel()
     bw_bias = None if bw_bias is None else bw_bias.contiguous()
-    e_u = torch.empty((), dtype=torch.uint32, device=dev)
-    e_f = torch.empty((), dtype=torch.float32, device=dev)
-    loss = torch.empty((), dtype=torch.float32, device=dev)
-    d_in = torch.empty_like(bw_in) if want_grads else None
-    d_w = torch.empty_like(bw_w) if want_grads else None
-    d_b = torch.empty_like(bw_bias) if (want_grads and nb) else None
+    if out is not None:
+        e_u, loss, d_in, d_w, d_b = out
+        e_f = None
+    else:
+        e_u = torch.empty((), dtype=torch.uint32, device=dev)
+        e_f = torch.empty((), dtype=torch.float32, device=dev)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        d_in = torch.empty_like(bw_in) if want_grads else None
+        d_w = torch.empty_like(bw_w) if want_grads else None
+        d_b = torch.empty_like(bw_bias) if (want_grads and nb) else None
     with torch.cuda.device(dev):
         st = lib().hgq_ebops_dense(ptr(bw_in), P, K, ptr(bw_w), N, ptr(bw_bias), nb, float(out_size), float(scale), ptr(beta),
                                    ptr(e_u), ptr(e_f), ptr(loss), ptr(d_in), ptr(d_w), ptr(d_b), stream_handle())
@@ -173,7 +189,7 @@ def ebops_dense(bw_in, bw_w, bw_bias, out_size: float, scale: float, beta, want_
 
 
 def ebops_conv2d(bw_in, bw_w, bw_bias, out_hw, strides, dilation, pad_tl, out_size: float, scale_main: float,
-                 scale_bias: float, beta, want_grads: bool = True):
+                 scale_bias: float, beta, want_grads: bool = True, out=None):
     """K3 for a channels-last conv2d.  bw_in [H, W, C], bw_w [KH, KW, C, N]."""
     require_cuda(bw_in, bw_w, bw_bias, beta)
     bw_in, bw_w = bw_in.contiguous(), bw_w.contiguous()
@@ -183,12 +199,16 @@ def ebops_conv2d(bw_in, bw_w, bw_bias, out_hw, strides, dilation, pad_tl, out_si
     dev = bw_in.device
     nb = 0 if bw_bias is None else bw_bias.numel()
     bw_bias = None if bw_bias is None else bw_bias.contiguous()
-    e_u = torch.empty((), dtype=torch.uint32, device=dev)
-    e_f = torch.empty((), dtype=torch.float32, device=dev)
-    loss = torch.empty((), dtype=torch.float32, device=dev)
-    d_in = torch.empty_like(bw_in) if want_grads else None
-    d_w = torch.empty_like(bw_w) if want_grads else None
-    d_b = torch.empty_like(bw_bias) if (want_grads and nb) else None
+    if out is not None:
+        e_u, loss, d_in, d_w, d_b = out
+        e_f = None
+    else:
+        e_u = torch.empty((), dtype=torch.uint32, device=dev)
+        e_f = torch.empty((), dtype=torch.float32, device=dev)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        d_in = torch.empty_like(bw_in) if want_grads else None
+        d_w = torch.empty_like(bw_w) if want_grads else None
+        d_b = torch.empty_like(bw_bias) if (want_grads and nb) else None
     with torch.cuda.device(dev):
         st = lib().hgq_ebops_conv2d(ptr(bw_in), H, W, C, ptr(bw_w), KH, KW, N, out_hw[0], out_hw[1], strides[0], strides[1],
                                     dilation[0], dilation[1], pad_tl[0], pad_tl[1], ptr(bw_bias), nb, float(out_size),
@@ -223,7 +243,7 @@ def qdense_supported(M: int, K: int, N: int, rows_period: int) -> bool:
 
 
 def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: str, training: bool, zero_nonpos: bool,
-               wq, bq, activation: str | None, want_absmax: bool):
+               wq, bq, activation: str | None, want_absmax: bool, absmax_out=None):
     """Fused y = act(iq(x) @ wq + bq); x is treated as [M, K] with K = wq.shape[0].  Returns (y [M, N], absmax or None)."""
     require_cuda(x, qk, qi, qf, wq, bq)
     rm, om = _modes(round_mode, overflow_mode)
@@ -235,7 +255,7 @@ def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: 
     M = x.numel() // K
     wq = wq.contiguous()
     y = torch.empty((M, N), dtype=torch.float32, device=x.device)
-    absmax = torch.empty(rows_period * K, dtype=torch.float32, device=x.device) if want_absmax else None
+    absmax = (absmax_out if absmax_out is not None else torch.empty(rows_period * K, dtype=torch.float32, device=x.device)) if want_absmax else None
     ws = workspace(lib().hgq_qdense_fwd_workspace(M, K, N, rows_period), x.device, slot=1) if want_absmax else None
     act = {None: 0, 'relu': 1}[activation]
     flags = (FLAG_TRAINING if training else 0) | (FLAG_ZERO_NONPOS if zero_nonpos else 0)
@@ -262,7 +282,7 @@ def qdense_bwd_supported(M: int, K: int, N: int, rows_period: int) -> bool:
 
 
 def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: bool, want_db: bool, want_df: bool,
-               gy_repeat: int = 1):
+               gy_repeat: int = 1, out_dwq=None, out_dbq=None, out_df=None):
     """Fused backward of qdense_fwd (rounding-only input quantizer or none).  gy/y are [M, N], x [M, K]; with
     ``gy_repeat`` > 1, gy is [M / gy_repeat, N] and each of its rows serves gy_repeat consecutive rows.
     Returns (dx or None, dwq, dbq or None, df or None)."""
@@ -275,8 +295,9 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
     dev = x.device
     want_df = want_df and qf is not None
     dx = torch.empty((M, K), dtype=torch.float32, device=dev) if want_dx else None
-    dwq = torch.empty((K, N), dtype=torch.float32, device=dev)
-    dbq = torch.empty(N, dtype=torch.float32, device=dev) if want_db else None
+    dwq = out_dwq if out_dwq is not None else torch.empty((K, N), dtype=torch.float32, device=dev)
+    dbq = (out_dbq if out_dbq is not None else torch.empty(N, dtype=torch.float32, device=dev)) if want_db else None
+    direct_df = want_df and out_df is not None and K <= _QB_KBLOCK  # one launch: the kernel writes the caller's table
     dfs = []
     x2 = x.view(M, K)
     qf2 = None if qf is None else qf.reshape(rows_period, K)
@@ -284,7 +305,7 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
         for k0 in range(0, K, _QB_KBLOCK):
             kb = min(_QB_KBLOCK, K - k0)
             qf_b = None if qf2 is None else qf2[:, k0:k0 + kb].contiguous()
-            df_b = torch.empty(rows_period * kb, dtype=torch.float32, device=dev) if want_df else None
+            df_b = (out_df if direct_df else torch.empty(rows_period * kb, dtype=torch.float32, device=dev)) if want_df else None
             ws = workspace(lib().hgq_qdense_bwd_workspace(M, kb, N, rows_period), dev, slot=2)
             st = lib().hgq_qdense_bwd_strided(
                 ptr(gy), gy_repeat, ptr(y), x2.data_ptr() + 4 * k0, K, ptr(qf_b), rows_period, rm, wq.data_ptr() + 4 * k0 * N,
@@ -295,7 +316,13 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
                 dfs.append(df_b.view(rows_period, kb))
     df = None
     if want_df:
-        df = (dfs[0] if len(dfs) == 1 else torch.cat(dfs, dim=1)).reshape(-1)
+        if direct_df:
+            df = out_df
+        elif out_df is not None:
+            torch.cat(dfs, dim=1, out=out_df.view(rows_period, K))
+            df = out_df
+        else:
+            df = (dfs[0] if len(dfs) == 1 else torch.cat(dfs, dim=1)).reshape(-1)
     return dx, dwq, dbq, df
 
 
@@ -320,7 +347,7 @@ def qsoftmax_supported(L: int) -> bool:
 
 
 def qsoftmax_fwd(s, quants, scaler: float, eps: float, rows_period: int, want_amax3: bool, want_amax5: bool,
-                 want_amax1: bool = False):
+                 want_amax1: bool = False, out_amax=(None, None, None)):
     """Fused training-mode QSoftmax forward over the last axis of s.  Returns (y, amax3 or None, amax5 or None, amax1 or
     None): the abs-max statistics of the inverse table's input, the layer output and the exp table's input."""
     require_cuda(s)
@@ -328,9 +355,10 @@ def qsoftmax_fwd(s, quants, scaler: float, eps: float, rows_period: int, want_am
     L = s.shape[-1]
     R = s.numel() // L
     y = torch.empty_like(s)
-    a1 = torch.empty(1, dtype=torch.float32, device=s.device) if want_amax1 else None
-    a3 = torch.empty(1, dtype=torch.float32, device=s.device) if want_amax3 else None
-    a5 = torch.empty(rows_period * L, dtype=torch.float32, device=s.device) if want_amax5 else None
+    o1, o3, o5 = out_amax  # caller-owned destinations of the three statistics (None: allocate)
+    a1 = (o1 if o1 is not None else torch.empty(1, dtype=torch.float32, device=s.device)) if want_amax1 else None
+    a3 = (o3 if o3 is not None else torch.empty(1, dtype=torch.float32, device=s.device)) if want_amax3 else None
+    a5 = (o5 if o5 is not None else torch.empty(rows_period * L, dtype=torch.float32, device=s.device)) if want_amax5 else None
     qk, qi, qf, rms, oms, keep = _quant_arrays(quants)
     with torch.cuda.device(s.device):
         st = lib().hgq_qsoftmax_fwd(ptr(s), ptr(y), qk, qi, qf, rms, oms, float(scaler), float(eps), ptr(a1), ptr(a3), ptr(a5),
@@ -390,7 +418,7 @@ def qconv2d_wgrad_supported(B, H, W, C, KH, KW, N, OH, OW) -> bool:
     return lib().hgq_qconv2d_wgrad_workspace(B, H, W, C, KH, KW, N, OH, OW) > 0
 
 
-def qconv2d_wgrad(x, gy, y, KH, KW, strides, dilation, pad_tl, want_db: bool):
+def qconv2d_wgrad(x, gy, y, KH, KW, strides, dilation, pad_tl, want_db: bool, out_dwq=None, out_dbq=None):
     """Weight / bias gradient of the implicit-GEMM convolution.  x [B, H, W, C] (C % 4 == 0), gy / y [B, OH, OW, N];
     y is the forward output when the activation was ReLU, else None.  Returns (G, dwq [KH*KW*C, N], dbq or None) with
     G the masked upstream gradient (gy itself without activation)."""
@@ -401,8 +429,8 @@ def qconv2d_wgrad(x, gy, y, KH, KW, strides, dilation, pad_tl, want_db: bool):
     _, OH, OW, N = gy.shape
     dev = x.device
     gm = torch.empty_like(gy) if y is not None else None
-    dwq = torch.empty((KH * KW * C, N), dtype=torch.float32, device=dev)
-    dbq = torch.empty(N, dtype=torch.float32, device=dev) if want_db else None
+    dwq = out_dwq if out_dwq is not None else torch.empty((KH * KW * C, N), dtype=torch.float32, device=dev)
+    dbq = (out_dbq if out_dbq is not None else torch.empty(N, dtype=torch.float32, device=dev)) if want_db else None
     ws = workspace(lib().hgq_qconv2d_wgrad_workspace(B, H, W, C, KH, KW, N, OH, OW), dev, slot=4)
     if ws is None:
         raise _lib.HGQError(-2, 'hgq_qconv2d_wgrad: unsupported shape')
@@ -491,3 +519,29 @@ def softmax_xent(logits, labels):
         st = lib().hgq_softmax_xent(ptr(logits), ptr(labels), ptr(loss), ptr(dlogits), B, C, ptr(ws), ws.numel(), stream_handle())
     check(st, 'hgq_softmax_xent')
     return loss, dlogits
+
+
+# ---- batched parameter-side kernels (descriptor tables in device memory, see hgq2_b200.engine) -------------------------
+def tables_forward(slots_dev, n_slots: int, max_n: int) -> None:
+    with torch.cuda.device(slots_dev.device):
+        check(lib().hgq_tables_forward(ptr(slots_dev), n_slots, max_n, stream_handle()), 'hgq_tables_forward')
+
+
+def tables_track_bits(slots_dev, n_slots: int, max_n: int) -> None:
+    with torch.cuda.device(slots_dev.device):
+        check(lib().hgq_tables_track_bits(ptr(slots_dev), n_slots, max_n, stream_handle()), 'hgq_tables_track_bits')
+
+
+def tables_backward(slots_dev, n_slots: int, max_n: int) -> None:
+    with torch.cuda.device(slots_dev.device):
+        check(lib().hgq_tables_backward(ptr(slots_dev), n_slots, max_n, stream_handle()), 'hgq_tables_backward')
+
+
+def weights_forward(weights_dev, n_weights: int, max_n: int, slots_dev) -> None:
+    with torch.cuda.device(slots_dev.device):
+        check(lib().hgq_weights_forward(ptr(weights_dev), n_weights, max_n, ptr(slots_dev), stream_handle()), 'hgq_weights_forward')
+
+
+def weights_backward(weights_dev, n_weights: int, max_n: int, slots_dev) -> None:
+    with torch.cuda.device(slots_dev.device):
+        check(lib().hgq_weights_backward(ptr(weights_dev), n_weights, max_n, ptr(slots_dev), stream_handle()), 'hgq_weights_backward')

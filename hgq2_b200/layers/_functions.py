@@ -233,20 +233,9 @@ class QConv2dFusedFn(torch.autograd.Function):
         return dx, (dwq if need_w else None), dbq, None, None, None, None, None, None
 
 
-def fused_conv2d_call(layer, xq, qkernel, qbias):
-    """The fused convolution of a QConv2D layer on its quantised operands, or None when the shape is not covered."""
-    if not fused_enabled or not xq.is_cuda or xq.dtype != torch.float32 or xq.dim() != 4:
-        return None
-    act_spec = getattr(layer, '_activation_spec', None)
-    if act_spec not in (None, 'relu'):
-        return None
-    if tuple(layer.strides) != (1, 1):
-        return None  # the input gradient is written as a stride-1 convolution over the output gradient
-    B, H, W, C = xq.shape
-    KH, KW, _, N = qkernel.shape
-    (pt, _), (pl, _) = layer._pads(H, W)
-    _, OH, OW, _ = layer.compute_output_shape(tuple(xq.shape))
-    dil = tuple(layer.dilation_rate)
+def conv_padding_channels(B, H, W, C, KH, KW, N, OH, OW, dil):
+    """How many zero channels must be appended to the image so that the unit-stride implicit-GEMM kernels (forward, input
+    gradient, weight gradient) cover the convolution: 0 when they read it as it is, None when they do not cover it."""
     if N % 4 != 0 or KH * KW * N > 640:
         return None
 
@@ -263,6 +252,26 @@ def fused_conv2d_call(layer, xq, qkernel, qbias):
 
     cp = 0 if covered(C) else (-C) % 4
     if cp and not covered(C + cp):
+        return None
+    return cp
+
+
+def fused_conv2d_call(layer, xq, qkernel, qbias):
+    """The fused convolution of a QConv2D layer on its quantised operands, or None when the shape is not covered."""
+    if not fused_enabled or not xq.is_cuda or xq.dtype != torch.float32 or xq.dim() != 4:
+        return None
+    act_spec = getattr(layer, '_activation_spec', None)
+    if act_spec not in (None, 'relu'):
+        return None
+    if tuple(layer.strides) != (1, 1):
+        return None  # the input gradient is written as a stride-1 convolution over the output gradient
+    B, H, W, C = xq.shape
+    KH, KW, _, N = qkernel.shape
+    (pt, _), (pl, _) = layer._pads(H, W)
+    _, OH, OW, _ = layer.compute_output_shape(tuple(xq.shape))
+    dil = tuple(layer.dilation_rate)
+    cp = conv_padding_channels(B, H, W, C, KH, KW, N, OH, OW, dil)
+    if cp is None:
         return None
     return QConv2dFusedFn.apply(xq, qkernel, qbias, act_spec, tuple(layer.strides), dil, (pt, pl), (OH, OW), cp)
 

@@ -145,6 +145,9 @@ class FixedPointQuantizerBase(TrainableQuantizerBase):
 
     @property
     def bits(self):
+        planned = self.__dict__.get('_engine_bits')
+        if planned is not None:  # a step engine holds this quantizer's bit counts as a table of its own (hgq2_b200.engine)
+            return planned
         if self.overflow_mode != 'SAT':
             return self.b
         return self.b + self.k

@@ -15,6 +15,7 @@ flat fp32 bucket:
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -189,12 +190,29 @@ class Trainer:
     the per-kernel launch and Python cost that dominates the small models.
     """
 
-    def __init__(self, model: Layer, loss_fn, learning_rate=1e-3, dp: DataParallel | None = None):
+    def __init__(self, model: Layer, loss_fn, learning_rate=1e-3, dp: DataParallel | None = None, engine: bool | None = None):
+        """``engine``: run forward and backward through the static step plan of ``hgq2_b200.engine`` (batched bitwidth
+        arithmetic, no autograd graph).  None (default): use it when it covers the model, else the autograd path; True:
+        require it (raises ``engine.Unsupported`` otherwise); False: always the autograd path.  The environment variable
+        ``HGQ_ENGINE=0`` turns the default off."""
         self.model = model
         self.loss_fn = loss_fn
         self.dp = dp
         self.state = FlatState(model)
         self.opt = FusedAdam(self.state, learning_rate=learning_rate)
+        self.engine = None
+        if engine is None:
+            engine = None if os.environ.get('HGQ_ENGINE', '1') != '0' else False
+        if engine is not False and self.state.params.is_cuda:
+            from .engine import Engine, Unsupported
+
+            try:
+                self.engine = Engine(model, self.state)
+                self.engine.dp = dp
+            except Unsupported as why:
+                if engine is True:
+                    raise
+                self.engine_refusal = str(why)
         self._graphs = []      # captured steps, one per set of static input buffers
         self._sbuf = []        # the static (x, y) buffers the graphs read
         self._next_buf = 0
@@ -204,6 +222,15 @@ class Trainer:
         self._status_event = None
 
     def forward_backward(self, x, y):
+        if self.engine is not None:
+            from .engine import Unsupported
+
+            try:
+                self.engine.check(int(x.shape[0]))
+            except Unsupported as why:  # this batch size is outside some kernel: the autograd path takes over for good
+                self.engine, self.engine_refusal = None, str(why)
+            else:
+                return self.engine.forward_backward(x, y, self.loss_fn)
         self.state.zero_grad()
         pred = self.model(x, training=True)
         task = self.loss_fn(pred, y)

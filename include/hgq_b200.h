@@ -368,6 +368,82 @@ int hgq_adam_step(float *w, const float *g, float *m, float *v, const float *lo,
                   const float *l1, int64_t n, float lr, float beta1, float beta2, float eps,
                   float grad_scale, long long *step, void *stream);
 
+/* ---- batched parameter-side work of a training step ------------------------------------------ */
+
+/*
+ * Descriptor tables.  A model's quantizers and weight tensors are described once, in arrays of these structs held in
+ * DEVICE memory (all pointers inside are device pointers); each entry point below then handles every quantizer / every
+ * weight tensor of the model in one launch.  The reference does the same work as eager element-wise operations on each
+ * bitwidth-shaped tensor separately.
+ */
+#define HGQ_SLOT_KIF 0 /* variables (k, i, f): FixedPointQuantizerKIF, fixed_point_quantizer.py:310-458 */
+#define HGQ_SLOT_KBI 1 /* variables (k, b, i): FixedPointQuantizerKBI, fixed_point_quantizer.py:153-307 */
+
+typedef struct hgq_slot_desc {
+    const float *a_raw;   /* the variable `f` (KIF) or `b` (KBI), n entries                                   */
+    float *i_raw;         /* the variable `i` (trainable, or the tracked state of a WRAP quantizer)           */
+    const uint8_t *k;     /* the variable `k`                                                                 */
+    float *I, *F, *BITS;  /* derived tables: round_conv(i); round_conv(f) or round_conv(b) - round_conv(i);    */
+                          /* the `bits` property (fixed_point_quantizer.py:92-97)                             */
+    float *dI, *dF, *dBITS; /* gradients of the loss w.r.t. the three derived tables                          */
+    float *g_a, *g_i;     /* where the gradients of a_raw / i_raw go (NULL: not trainable)                    */
+    const float *absmax;  /* a tracked activation quantizer: max |round(x, f)| per entry; else NULL           */
+    const float *decay;   /* the scalar variable i_decay_speed (WRAP), else NULL                              */
+    int64_t n;
+    int32_t kind;         /* HGQ_SLOT_KIF / HGQ_SLOT_KBI                                                      */
+    int32_t om, rm;       /* hgq_overflow_mode, hgq_round_mode of the quantizer                               */
+    int32_t symmetric;    /* overflow mode ends in _SYM                                                       */
+    int32_t tracked_weight; /* the weights pass tracks this quantizer's integer bits                          */
+    float i_lo, i_hi;     /* MinMax constraint of `i` applied while tracking (KBI; +-inf: none)               */
+} hgq_slot_desc;
+
+#define HGQ_WEIGHT_QUANTIZE 0    /* wq = stateless_quantizer(w, k, i, f, training=True)                       */
+#define HGQ_WEIGHT_ROUND 1       /* wq = stateless_quantizer.round(w, f)                                      */
+#define HGQ_WEIGHT_TRACK_ROUND 2 /* WRAP quantizer in training: track the integer bits, then round            */
+
+typedef struct hgq_weight_desc {
+    const float *w_raw;  /* the kernel or bias variable, n entries                                            */
+    float *wq;           /* its quantised value                                                               */
+    const float *dwq;    /* dL/dwq (written by the layer's backward kernel)                                   */
+    float *g_w;          /* where dL/dw goes                                                                  */
+    int64_t n;
+    int32_t slot;        /* index of the quantizer's hgq_slot_desc; its tables have one entry per weight      */
+    int32_t mode;        /* HGQ_WEIGHT_*                                                                      */
+} hgq_weight_desc;
+
+/*
+ * I = round_conv(i), F = round_conv(f) (KIF) or round_conv(b) - round_conv(i) (KBI) for every slot: the properties
+ * `i`, `f` of fixed_point_quantizer.py:244-265,431-449.  max_n = the largest n of any slot.
+ */
+int hgq_tables_forward(const hgq_slot_desc *slots, int n_slots, int64_t max_n, void *stream);
+
+/*
+ * After the forward pass: for every slot with `absmax`, the training branch of FixedPointQuantizerKIF.call
+ * (fixed_point_quantizer.py:401-411): i <- max(i - decay, ceil(log2(absmax + 2^-f))); then for every slot
+ * BITS = relu(I + F) (KIF) or round_conv(b) (KBI), plus k for overflow mode SAT (fixed_point_quantizer.py:92-97,435-437).
+ */
+int hgq_tables_track_bits(const hgq_slot_desc *slots, int n_slots, int64_t max_n, void *stream);
+
+/*
+ * Backward of the two calls above with straight-through rounding: (dI, dF, dBITS) -> gradients of the raw variables.
+ * KIF: g_f = dF + dBITS [i + f > 0], g_i = dI + dBITS [i + f > 0];  KBI: g_b = dF + dBITS, g_i = dI - dF.
+ */
+int hgq_tables_backward(const hgq_slot_desc *slots, int n_slots, int64_t max_n, void *stream);
+
+/*
+ * The quantised kernel / bias of every layer (qkernel / qbias, src/hgq/layers/core/dense.py:93-102 and the like),
+ * reading the tables hgq_tables_forward made.  HGQ_WEIGHT_TRACK_ROUND entries also run the integer-bit tracking of
+ * FixedPointQuantizerKBI.call / KIF.call in training (fixed_point_quantizer.py:277-288,401-411) on the weight itself.
+ */
+int hgq_weights_forward(const hgq_weight_desc *weights, int n_weights, int64_t max_n, const hgq_slot_desc *slots,
+                        void *stream);
+
+/*
+ * Surrogate backward of hgq_weights_forward: g_w = dL/dw, and the slot's dI / dF (one entry per weight) are written.
+ */
+int hgq_weights_backward(const hgq_weight_desc *weights, int n_weights, int64_t max_n, const hgq_slot_desc *slots,
+                         void *stream);
+
 /* ---- standalone quantizer on host buffers ------------------------------------------------- */
 
 /*
