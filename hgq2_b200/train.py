@@ -201,6 +201,7 @@ class Trainer:
         self.state = FlatState(model)
         self.opt = FusedAdam(self.state, learning_rate=learning_rate)
         self.engine = None
+        self.engine_refusal = None  # why the static step plan is not in use (None: it is, or it was not asked for)
         if engine is None:
             engine = None if os.environ.get('HGQ_ENGINE', '1') != '0' else False
         if engine is not False and self.state.params.is_cuda:

@@ -67,3 +67,29 @@ def test_package_never_imports_the_oracle():
     for path in (ROOT / 'hgq2_b200').rglob('*.py'):
         text = path.read_text()
         assert not re.search(r'^\s*(from|import)\s+oracle\b', text, flags=re.M), path
+
+
+def test_descriptor_structs_match_the_header(tmp_path):
+    """hgq_slot_desc / hgq_weight_desc as the C compiler lays them out equal their ctypes mirrors field by field."""
+    import ctypes
+    import shutil
+    import subprocess
+
+    from hgq2_b200._lib import SlotDesc, WeightDesc
+
+    gcc = shutil.which('gcc')
+    if gcc is None:
+        pytest.skip('no C compiler')
+    fields = [('hgq_slot_desc', SlotDesc), ('hgq_weight_desc', WeightDesc)]
+    body = ''.join(f'printf("%zu\\n", sizeof({c}));' + ''.join(f'printf("%zu\\n", offsetof({c}, {name}));' for name, _ in s._fields_)
+                   for c, s in fields)
+    src = tmp_path / 'layout.c'
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "hgq_b200.h"\nint main(void){' + body + 'return 0;}\n')
+    exe = tmp_path / 'layout'
+    subprocess.run([gcc, '-I', str(ROOT / 'include'), str(src), '-o', str(exe)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    want = []
+    for _, s in fields:
+        want.append(ctypes.sizeof(s))
+        want += [getattr(s, name).offset for name, _ in s._fields_]
+    assert got == want

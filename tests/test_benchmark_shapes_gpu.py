@@ -185,12 +185,15 @@ def test_transformer_block_steps_at_the_benchmark_shape():
     rng = np.random.default_rng(1)
     x = rng.standard_normal((16, 64, 64)).astype(np.float32)
     y = np.random.default_rng(2).integers(0, 5, 16)
-    routes.reset()
-    with routes.strict_mode():
-        run_steps(workloads.transformer_block, x, y, steps=2)
-    assert routes.counts['hgq_attn_heads_matmul'] == 12, dict(routes.counts)
-    assert routes.counts['hgq_qsoftmax_bwd'] == 2
-    assert not routes.fallbacks(), routes.fallbacks()
+    for engine in (True, False):  # the static step plan and the autograd path launch the same kernels here
+        routes.reset()
+        with routes.strict_mode():
+            run_steps(workloads.transformer_block, x, y, steps=2, engine=engine)
+        # two training steps: 2 forward + 4 backward products each on the per-head kernel (+ 2 of the build-time forward)
+        assert routes.counts['hgq_attn_heads_matmul'] == 12 + 2, dict(routes.counts)
+        assert routes.counts['hgq_qsoftmax_bwd'] == 2
+        assert routes.counts['hgq_qdense_bwd_strided'] >= 2 * 8
+        assert not routes.fallbacks(), routes.fallbacks()
 
 
 @pytest.mark.parametrize('name,shape,classes,draw', [
@@ -210,14 +213,43 @@ def test_every_benchmark_model_steps_without_a_library_fallback(name, shape, cla
     y_np = np.random.default_rng(2).integers(0, classes, shape[0])
     model = workloads.build(getattr(workloads, name)())
     tr = Trainer(model, sparse_categorical_crossentropy)
+    assert tr.engine is not None, tr.engine_refusal  # the static step plan covers every benchmark model
     x, y = torch.from_numpy(x_np).cuda(), torch.from_numpy(y_np).cuda()
     routes.reset()
     with routes.strict_mode():
-        tr.capture(x, y, warmup=2)
+        tr.capture(x, y, warmup=2, double_buffer=True)
         loss = float(tr.step(x, y))
+        loss2 = float(tr.step_prefetched(tr.prefetch(torch.from_numpy(x_np).pin_memory(), torch.from_numpy(y_np).pin_memory())))
     tr.check_status(wait=True)
-    assert np.isfinite(loss)
+    assert tr.engine is not None, tr.engine_refusal
+    assert np.isfinite(loss) and np.isfinite(loss2)
     assert not routes.fallbacks(), routes.fallbacks()
+    at_launches = routes.counts  # every launch of this package's own kernels is counted; none may be a library contraction
+    assert at_launches['hgq_tables_forward'] >= 1 and at_launches['hgq_tables_backward'] >= 1
+
+
+def test_static_step_plan_equals_the_autograd_path():
+    """Three steps of the small MLP through the static plan and through the layers' autograd path: same losses, same
+    parameters, same quantizer state and EBOPs (both run the same kernels on the same operands; only the order of a few
+    fp32 additions differs)."""
+    from hgq2_b200 import workloads
+    from hgq2_b200.train import Trainer, sparse_categorical_crossentropy
+
+    rng = np.random.default_rng(3)
+    xs = [torch.from_numpy(rng.standard_normal((1024, 16)).astype(np.float32)).cuda() for _ in range(3)]
+    ys = [torch.from_numpy(rng.integers(0, 5, 1024)).cuda() for _ in range(3)]
+    out = []
+    for engine in (True, False):
+        model = workloads.build(workloads.jet_tagger_mlp())
+        tr = Trainer(model, sparse_categorical_crossentropy, engine=engine)
+        losses = [float(tr.step(x, y)) for x, y in zip(xs, ys)]
+        state = [v.value.detach().clone() for v in model.non_trainable_variables]
+        out.append((losses, tr.state.params.clone(), state))
+    (l_e, p_e, s_e), (l_a, p_a, s_a) = out
+    assert np.allclose(l_e, l_a, rtol=1e-6), (l_e, l_a)
+    assert float((p_e - p_a).abs().max()) <= 1e-5, float((p_e - p_a).abs().max())
+    for a, b in zip(s_e, s_a):
+        assert torch.equal(a, b)
 
 
 def test_strict_mode_refuses_a_fallback():

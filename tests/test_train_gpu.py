@@ -22,14 +22,14 @@ def ce(pred, y):
     return F.cross_entropy(pred, y)
 
 
-def run_steps(builder, x_np, y_np, steps=3, beta0=1e-5, lr=1e-3):
+def run_steps(builder, x_np, y_np, steps=3, beta0=1e-5, lr=1e-3, engine=True):
     from hgq2_b200 import workloads
     from hgq2_b200.train import Trainer
 
     model = workloads.build(builder(beta0=beta0))
     twin, pairs = OT.mirror_model(model)
     oopt = OT.OracleAdam(pairs, lr=lr)
-    tr = Trainer(model, ce, learning_rate=lr)
+    tr = Trainer(model, ce, learning_rate=lr, engine=engine)  # engine=True: the static step plan must cover the model
     x, y = torch.from_numpy(x_np).cuda(), torch.from_numpy(y_np).cuda()
     xc, yc = torch.from_numpy(x_np), torch.from_numpy(y_np)
     for s in range(steps):
@@ -65,40 +65,44 @@ def run_steps(builder, x_np, y_np, steps=3, beta0=1e-5, lr=1e-3):
     return model, twin
 
 
-def test_jet_tagger_mlp_steps():
+@pytest.mark.parametrize('engine', [True, False])
+def test_jet_tagger_mlp_steps(engine):
     from hgq2_b200 import workloads
 
     rng = np.random.default_rng(1)
     x = rng.standard_normal((2048, 16)).astype(np.float32)
     y = np.random.default_rng(2).integers(0, 5, 2048)
-    run_steps(workloads.jet_tagger_mlp, x, y, steps=3, beta0=1e-5)
+    run_steps(workloads.jet_tagger_mlp, x, y, steps=3, beta0=1e-5, engine=engine)
 
 
-def test_particle_tagger_steps():
+@pytest.mark.parametrize('engine', [True, False])
+def test_particle_tagger_steps(engine):
     from hgq2_b200 import workloads
 
     rng = np.random.default_rng(1)
     x = rng.standard_normal((96, 64, 16)).astype(np.float32)
     y = np.random.default_rng(2).integers(0, 5, 96)
-    run_steps(workloads.particle_tagger, x, y, steps=2)
+    run_steps(workloads.particle_tagger, x, y, steps=2, engine=engine)
 
 
-def test_small_cnn_steps():
+@pytest.mark.parametrize('engine', [True, False])
+def test_small_cnn_steps(engine):
     from hgq2_b200 import workloads
 
     rng = np.random.default_rng(1)
     x = rng.uniform(0, 1, (48, 32, 32, 3)).astype(np.float32)
     y = np.random.default_rng(2).integers(0, 10, 48)
-    run_steps(workloads.small_cnn, x, y, steps=2)
+    run_steps(workloads.small_cnn, x, y, steps=2, engine=engine)
 
 
 def test_transformer_block_steps():
+    # sequence 16: outside the per-head attention kernel, so this model takes the autograd path (torch.einsum products)
     from hgq2_b200 import workloads
 
     rng = np.random.default_rng(1)
     x = rng.standard_normal((32, 16, 32)).astype(np.float32)
     y = np.random.default_rng(2).integers(0, 5, 32)
-    run_steps(lambda beta0: workloads.transformer_block(seq=16, d_model=32, heads=2, beta0=beta0), x, y, steps=2)
+    run_steps(lambda beta0: workloads.transformer_block(seq=16, d_model=32, heads=2, beta0=beta0), x, y, steps=2, engine=None)
 
 
 def test_adam_kernel_matches_keras_rule():
