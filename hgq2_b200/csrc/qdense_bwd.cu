@@ -21,6 +21,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "hgq_common.cuh"
 #include "hgq_math.cuh"
 #include "tc05.cuh"
@@ -476,6 +478,19 @@ __global__ void __launch_bounds__(kThreads) k_qb_stage2(const float *__restrict_
     }
 }
 
+int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const float *x, int64_t ldx, const float *qf,
+                         int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *part, bool want_df,
+                         int64_t M, int K, int N, unsigned *status, cudaStream_t st, int *records);
+
+// HGQ_QDENSE_BWD_WS=0 in the environment keeps every call on the general kernel (for comparisons).
+static bool bwd_ws_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("HGQ_QDENSE_BWD_WS");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
+}
+
 struct QbGeom {
     int Kp, Np, Kt, grid;
     size_t smem;
@@ -508,7 +523,7 @@ using namespace hgq;
 extern "C" size_t hgq_qdense_bwd_workspace(int64_t M, int K, int N, int rows_period) {
     QbGeom g;
     if (qb_geom(M, K, N, rows_period, g) != HGQ_OK) return 0;
-    return (size_t)num_sms() * g.part_stride * sizeof(float);
+    return (size_t)2 * num_sms() * g.part_stride * sizeof(float);  // the warp-specialised kernel writes two records per CTA
 }
 
 extern "C" int hgq_qdense_bwd(const float *gy, const float *y, const float *x, const float *qf, int rows_period,
@@ -529,9 +544,22 @@ extern "C" int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const floa
     if (df != nullptr && qf == nullptr) return HGQ_ERR_NULL;
     QbGeom g;
     if (int e = qb_geom(M, K, N, rows_period, g)) return e;
-    const size_t need = (size_t)g.grid * g.part_stride * sizeof(float);
+    const size_t need = (size_t)2 * g.grid * g.part_stride * sizeof(float);
     if (workspace == nullptr || workspace_bytes < need) return HGQ_ERR_WORKSPACE;
     if (!aligned(workspace, 16)) return HGQ_ERR_ALIGN;
+    const int64_t nw_ = (int64_t)K * N, nf_ = (int64_t)rows_period * K;
+    if (bwd_ws_enabled()) {
+        int records = 0;
+        const int r = qdense_bwd_ws_launch(gy, gy_repeat, y, x, ldx, qf, rows_period, round_mode, wq, dx, lddx, (float *)workspace,
+                                           df != nullptr, M, K, N, status, (cudaStream_t)stream, &records);
+        if (r < 0) return -r;
+        if (r == 1) {
+            if (int e = check_launch()) return e;
+            k_qb_stage2<<<(unsigned)((g.part_stride + 63) / 64), kThreads, 0, (cudaStream_t)stream>>>(
+                (const float *)workspace, g.part_stride, records, dwq, nw_, dbq, N, df, df != nullptr ? nf_ : 0);
+            return check_launch();
+        }
+    }
     QbParams p;
     p.gy = gy; p.y = y; p.x = x; p.qf = qf; p.wq = wq; p.dx = dx;
     p.part = (float *)workspace;

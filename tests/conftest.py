@@ -34,3 +34,16 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope='session')
 def golden_dir():
     return ROOT / 'tests' / 'golden'
+
+
+@pytest.fixture(scope='session')
+def quantizer_golden(golden_dir):
+    """The stateless quantizer's golden arrays: the file made by the real ``quantizers`` package
+    (tests/golden/make_reference_golden.py) when someone has produced it, else the oracle-made one.  Returns
+    (arrays, pinned): ``pinned`` says whether the arrays come from the reference itself."""
+    import numpy as np
+
+    ref = golden_dir / 'quantizer_golden_reference.npz'
+    if ref.exists():
+        return np.load(ref), True
+    return np.load(golden_dir / 'quantizer_golden.npz'), False

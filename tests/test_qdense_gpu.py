@@ -198,3 +198,54 @@ def test_general_forward_kernel_on_the_same_cases():
                         '-k', 'test_fused_dense_forward or beyond_two_terms or wide_values', '-p', 'no:cacheprovider'],
                        cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize('M,K,N,rows_period,relu,want_dx', [
+    (128 * 300 + 77, 32, 64, 128, True, True), (5000, 64, 16, 4, False, True), (128 * 150, 16, 32, 16, True, False),
+    (9, 64, 64, 1, True, True), (128 * 149 + 1, 20, 28, 2, True, True),
+])
+def test_warp_specialised_backward_shapes(M, K, N, rows_period, relu, want_dx):
+    """Shapes inside the warp-specialised backward kernel's cover (K, N multiples of 4 padding to 16 / 32 / 64): several
+    tiles per CTA, a ragged last tile, padded columns, no input gradient wanted."""
+    from hgq2_b200 import kernels
+
+    rng = np.random.default_rng(M + K + N)
+    x = torch.from_numpy((rng.standard_normal((M, K)) * 3).astype(np.float32))
+    f = torch.from_numpy(rng.integers(1, 7, (rows_period, K)).astype(np.float32))
+    w = torch.from_numpy(np.round(rng.uniform(-2, 2, (K, N)) * 64) / 64).float()
+    gy = torch.from_numpy(rng.standard_normal((M, N)).astype(np.float32))
+    y = torch.from_numpy(rng.standard_normal((M, N)).astype(np.float32)).clamp_min(0)
+    dx, dwq, dbq, df = kernels.qdense_bwd(gy.cuda(), y.cuda() if relu else None, x.cuda(), f.cuda(), rows_period, 'RND', w.cuda(),
+                                          want_dx, True, True)
+    kernels.check_status(dwq.device)
+    g = (gy * (y > 0)) if relu else gy
+    ff = f.repeat(M // rows_period + 1, 1)[:M]
+    xq = O.round_fwd(x, ff, 'RND')
+    dxr = g.double() @ w.double().t()
+
+    def rel(a, b):
+        return float((a.cpu().double() - b).abs().max() / max(float(b.abs().max()), 1e-30))
+
+    assert (dx is None) == (not want_dx)
+    if want_dx:
+        assert rel(dx, dxr) <= 2e-5
+    assert rel(dwq, xq.double().t() @ g.double()) <= 5e-5
+    assert rel(dbq, g.double().sum(0)) <= 5e-5
+    t = ((xq - x).double() * (-O.LN2)) * dxr
+    dfr = torch.stack([t[p::rows_period].sum(0) for p in range(rows_period)])
+    assert rel(df.view(rows_period, K), dfr) <= 5e-5
+
+
+def test_general_backward_kernel_on_the_same_cases():
+    # HGQ_QDENSE_BWD_WS=0 (read once per process) keeps every backward call on the general kernel: the backward cases
+    # above run again in a child process so that both kernels stay covered by the same references
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, HGQ_QDENSE_BWD_WS='0')
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, '-m', 'pytest', os.path.join(root, 'tests', 'test_qdense_gpu.py'), '-q', '-x', '-m', 'gpu',
+                        '-k', 'backward and not general', '-p', 'no:cacheprovider'],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
