@@ -103,22 +103,26 @@ __device__ __forceinline__ void bw_cp16(uint32_t dst, const float *src, bool in)
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
 }
 
-template <bool CONV>
+// The kernel is a template on the padded widths (CGN = Np / 8 and CGK = Kp / 8 column groups: 2, 4 or 8 each), on the
+// ReLU mask and on the rounding flavour, so that every loop below has a constant trip count and every shared-memory offset
+// is an immediate: the kernel is bound by the number of instructions it issues, not by bytes.
+template <bool CONV, int CGN, int CGK, bool RELU>
 __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams P) {
+    constexpr int Np = CGN * 8, Kp = CGK * 8;
+    constexpr int ITG = CGN / 2, ITX = CGK / 2;  // units (8 rows x 8 columns) a producer thread converts per tile
+    constexpr int UNITS = ITG + ITX;
+    constexpr int g_bytes = 2 * kBwTileM * Np * 2;  // both bf16 terms
+    constexpr int w_term_bytes = Kp * Np * 2;
+    constexpr int n_raw_units = ITG * (RELU ? 2 : 1) + ITX;
     extern __shared__ __align__(128) unsigned char smem[];
-    const int K = P.K, N = P.N, Kp = P.Kp, Np = P.Np;
-    const int CGn = Np >> 3, CGk = Kp >> 3;  // 8-column groups of G and of x: 2, 4 or 8 each
-    const int ITG = CGn >> 1, ITX = CGk >> 1;  // units (8 rows x 8 columns) a producer thread converts per tile
+    const int K = P.K, N = P.N;
     const bool has_q = P.qf != nullptr;
-    const int g_bytes = 2 * kBwTileM * Np * 2;  // both bf16 terms
-    const int w_term_bytes = Kp * Np * 2;
     // carve: G operand | xq^T operand | W terms (3) | raw slots (dY, y, x) | transposition buffers | exponent table |
     // barriers, TMEM slot, abort word
     unsigned char *G = smem;
     unsigned char *X = G + g_bytes;
     unsigned char *W = X + kBwXBytes;
     unsigned char *raw = W + 3 * w_term_bytes;
-    const int n_raw_units = ITG * (P.relu ? 2 : 1) + ITX;
     unsigned char *outst = raw + n_raw_units * kBwProd * 32;
     const int Ke = P.Kt + 8;
     unsigned char *etab = outst + kBwEpiWarps * kBwOutWarpBytes;
@@ -129,8 +133,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
     int *abort_word = reinterpret_cast<int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < 2 * Kp + 2 * Np) tmem_cols <<= 1;  // two dXq accumulators | dWq from both terms of G
+    constexpr uint32_t tmem_cols = (2 * Kp + 2 * Np) <= 32 ? 32u : (2 * Kp + 2 * Np) <= 64 ? 64u : (2 * Kp + 2 * Np) <= 128 ? 128u : 256u;
 
     // ---- one-time set-up (all threads) -------------------------------------------------------------------------------
     if (tid == 0) {
@@ -159,7 +162,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
         const float w = (k < K && n < N) ? __ldg(P.wq + (int64_t)k * N + n) : 0.f;
         __nv_bfloat16 h, l, l2;
         tc::split3(w, h, l, l2);
-        const int off = ((k >> 3) * CGn + (n >> 3)) * 128 + (k & 7) * 16 + (n & 7) * 2;
+        const int off = ((k >> 3) * CGN + (n >> 3)) * 128 + (k & 7) * 16 + (n & 7) * 2;
         *reinterpret_cast<__nv_bfloat16 *>(W + off) = h;
         *reinterpret_cast<__nv_bfloat16 *>(W + w_term_bytes + off) = l;
         *reinterpret_cast<__nv_bfloat16 *>(W + 2 * w_term_bytes + off) = l2;
@@ -176,8 +179,10 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t acc2 = tmem_base + 2u * (uint32_t)Kp;
     const bool did_work = (int64_t)blockIdx.x < P.num_tiles;
-    float *rec_hi = P.part + (int64_t)(2 * blockIdx.x) * ((int64_t)(K + 1) * N + (int64_t)P.rows_period * K);
-    float *rec_lo = rec_hi + ((int64_t)(K + 1) * N + (int64_t)P.rows_period * K);
+    const int64_t rec_stride = (int64_t)(K + 1) * N + (int64_t)P.rows_period * K;
+    float *rec_hi = P.part + (int64_t)(2 * blockIdx.x) * rec_stride;
+    float *rec_lo = rec_hi + rec_stride;
+    const int64_t tile_step = (int64_t)gridDim.x * kBwTileM;  // rows between two tiles of this CTA
 
     if (warp < kBwProdWarps) {
         // ================================ producers ==================================================================
@@ -185,45 +190,83 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
         // divides 32); a quarter-warp (r8 = 0..7) fills one 128-byte core matrix.
         const int r8 = lane & 7, q4 = lane >> 3;
         const int ubase = warp * 4 + q4;
-        const int kg_g = ubase % CGn, kg_x = ubase % CGk;
+        const int kg_g = ubase % CGN, kg_x = ubase % CGK;
+        const int mg_g0 = ubase / CGN, mg_x0 = ubase / CGK;  // row group of unit `it`: mg0 + it * (32 / CG)
         const float rbias = (P.rm == RM_RND) ? 0.5f : 0.f;
-        const uint32_t raw_base = tc::smem_u32(raw);
-        // slot s of this thread: raw + (s * 256 + tid) * 32 bytes; slots: [0, ITG) dY, [ITG, 2 ITG) y (if relu), then x
-        const int y_slot0 = ITG, x_slot0 = ITG * (P.relu ? 2 : 1);
-        auto fetch_g = [&](int it, int64_t tile) {
-            const int mg = (it * 32 + ubase) / CGn;
-            const int64_t row = tile * kBwTileM + mg * 8 + r8;
-            const int n0 = kg_g * 8;
-            const bool row_in = tile < P.num_tiles && row < P.M;
-            const int64_t grow = (P.gy_repeat > 1) ? (int64_t)fastdiv((uint32_t)(row_in ? row : 0), P.gy_div) : row;
+        // Raw data travel in WARP-private 1 KB slots, filled cooperatively: the four units a warp converts in one iteration
+        // are 8 (or 16) consecutive rows x 128 (or 64) contiguous bytes, and one cp.async instruction of the warp copies
+        // whole 128-byte (64-byte) row segments -- every 32-byte sector it asks L2 for is used in full.  (With one private
+        // slot per thread, a thread's two 16-byte copies sit in two instructions that each touch half of 32 sectors: the
+        // L2 request rate, not HBM, then sets the pace.)  A 16-byte piece lands at an XOR-swizzled place in its row so that
+        // the quarter-warp that later reads one unit (8 rows, same piece) hits 8 different bank groups.
+        // slot s of this warp: raw + (s * 8 + warp) * 1024 bytes; slots: [0, ITG) dY, [ITG, 2 ITG) y (if RELU), then x
+        constexpr int y_slot0 = ITG, x_slot0 = ITG * (RELU ? 2 : 1);
+        constexpr int SEG_G = CGN >= 4 ? 8 : 4, SEG_X = CGK >= 4 ? 8 : 4;  // 16-byte pieces per row of a slot
+        auto swz_of = [](int row_local, int segs) { return segs == 8 ? (row_local & 7) : ((row_local >> 1) & 3); };
+        const uint32_t raw_warp = tc::smem_u32(raw) + (uint32_t)warp * 1024u;
+        const unsigned char *raw_warp_p = raw + (size_t)warp * 1024;
+        // copy geometry of this lane (two pieces per slot: c = lane and c = 32 + lane)
+        int g_src[2], g_dst[2], x_src[2], x_dst[2];
+        bool g_col[2], x_col[2];
+        const int kg0_g = (warp * 4) % CGN, kg0_x = (warp * 4) % CGK;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const bool in = row_in && (n0 + 4 * h) < N;  // N % 4 == 0: a 16-byte piece is all inside or all outside
-                bw_cp16(raw_base + (uint32_t)(((it * kBwProd + tid) * 2 + h) * 16), in ? P.gy + grow * N + n0 + 4 * h : P.gy, in);
-                if (P.relu)
-                    bw_cp16(raw_base + (uint32_t)((((y_slot0 + it) * kBwProd + tid) * 2 + h) * 16),
-                            in ? P.y + row * N + n0 + 4 * h : P.gy, in);
+        for (int j2 = 0; j2 < 2; ++j2) {
+            const int c = j2 * 32 + lane;
+            const int rl_g = c / SEG_G, sg_g = c % SEG_G, rl_x = c / SEG_X, sg_x = c % SEG_X;
+            g_src[j2] = rl_g * N + kg0_g * 8 + sg_g * 4;  // floats from the first row of the slot (row stride N)
+            g_col[j2] = kg0_g * 8 + sg_g * 4 < N;          // N % 4 == 0: a 16-byte piece is all inside or all outside
+            g_dst[j2] = rl_g * SEG_G * 16 + ((sg_g ^ swz_of(rl_g, SEG_G)) * 16);
+            x_src[j2] = rl_x;                               // row only: the row stride of x is a runtime value
+            x_col[j2] = kg0_x * 8 + sg_x * 4 < K;
+            x_dst[j2] = rl_x * SEG_X * 16 + ((sg_x ^ swz_of(rl_x, SEG_X)) * 16);
+        }
+        const int x_colf = kg0_x * 8 + (lane % SEG_X) * 4;  // c % SEG_X is the same for both pieces (32 % SEG_X == 0)
+        // where this thread finds the two 16-byte halves of the unit it converts
+        const int rl_gu = CGN >= 4 ? r8 : ((q4 >> 1) * 8 + r8), sg_gu = CGN >= 4 ? q4 * 2 : (q4 & 1) * 2;
+        const int rl_xu = CGK >= 4 ? r8 : ((q4 >> 1) * 8 + r8), sg_xu = CGK >= 4 ? q4 * 2 : (q4 & 1) * 2;
+        const int g_rd0 = rl_gu * SEG_G * 16 + ((sg_gu ^ swz_of(rl_gu, SEG_G)) * 16);
+        const int g_rd1 = rl_gu * SEG_G * 16 + (((sg_gu + 1) ^ swz_of(rl_gu, SEG_G)) * 16);
+        const int x_rd0 = rl_xu * SEG_X * 16 + ((sg_xu ^ swz_of(rl_xu, SEG_X)) * 16);
+        const int x_rd1 = rl_xu * SEG_X * 16 + (((sg_xu + 1) ^ swz_of(rl_xu, SEG_X)) * 16);
+        const bool linear_gy = P.gy_repeat <= 1;
+        // first row of the tile being FETCHED (one tile ahead of the one being converted)
+        int64_t f_row0 = (int64_t)blockIdx.x * kBwTileM;
+        auto fetch_g = [&](int it) {
+            const int64_t row_first = f_row0 + ((it * 32 + warp * 4) / CGN) * 8;
+            const uint32_t dst = raw_warp + (uint32_t)(it * 8 * 1024), dsty = raw_warp + (uint32_t)((y_slot0 + it) * 8 * 1024);
+#pragma unroll
+            for (int j2 = 0; j2 < 2; ++j2) {
+                const int rl = (j2 * 32 + lane) / SEG_G;
+                const int64_t row = row_first + rl;
+                const bool in = row < P.M && g_col[j2];
+                if (linear_gy) {
+                    bw_cp16(dst + (uint32_t)g_dst[j2], in ? P.gy + row_first * N + g_src[j2] : P.gy, in);
+                } else {
+                    const int64_t grow = (int64_t)fastdiv((uint32_t)(in ? row : 0), P.gy_div);
+                    bw_cp16(dst + (uint32_t)g_dst[j2], in ? P.gy + grow * N + (g_src[j2] - rl * N) : P.gy, in);
+                }
+                if (RELU) bw_cp16(dsty + (uint32_t)g_dst[j2], in ? P.y + row_first * N + g_src[j2] : P.gy, in);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        auto fetch_x = [&](int it, int64_t tile) {
-            const int mg = (it * 32 + ubase) / CGk;
-            const int64_t row = tile * kBwTileM + mg * 8 + r8;
-            const int k0 = kg_x * 8;
-            const bool row_in = tile < P.num_tiles && row < P.M;
+        auto fetch_x = [&](int it) {
+            const int64_t row_first = f_row0 + ((it * 32 + warp * 4) / CGK) * 8;
+            const uint32_t dst = raw_warp + (uint32_t)((x_slot0 + it) * 8 * 1024);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const bool in = row_in && (k0 + 4 * h) < K;
-                bw_cp16(raw_base + (uint32_t)((((x_slot0 + it) * kBwProd + tid) * 2 + h) * 16),
-                        in ? P.x + row * P.ldx + k0 + 4 * h : P.x, in);
+            for (int j2 = 0; j2 < 2; ++j2) {
+                const int64_t row = row_first + x_src[j2];
+                const bool in = row < P.M && x_col[j2];
+                bw_cp16(dst + (uint32_t)x_dst[j2], in ? P.x + row * P.ldx + x_colf : P.x, in);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        // one commit group per unit, in unit order; past the last tile the groups are empty, so "all but the newest
-        // (units - 1) groups have landed" always means "this unit has landed"
-        for (int it = 0; it < ITG; ++it) fetch_g(it, blockIdx.x);
-        for (int it = 0; it < ITX; ++it) fetch_x(it, blockIdx.x);
-        const int units = ITG + ITX;
+        // one commit group per unit, in unit order; past the last tile every row is out of range and the copies fetch
+        // nothing, so "all but the newest UNITS - 1 groups have landed" always means "this unit has landed"
+#pragma unroll
+        for (int it = 0; it < ITG; ++it) fetch_g(it);
+#pragma unroll
+        for (int it = 0; it < ITX; ++it) fetch_x(it);
+        f_row0 += tile_step;
 
         float dbq_r[8];
 #pragma unroll
@@ -232,55 +275,48 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
         uint32_t n = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++n) {
-            const int64_t next = tile + gridDim.x;
             // the products of the previous tile must have finished reading the operand stage
             if (n > 0) {
                 const bool w = bw_wait(stage_free, (n - 1) & 1u, abort_word);
                 if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
             }
             // ---- G = dY (* relu mask): two bf16 terms, core (row group, term, column group) -----------------------------
+#pragma unroll
             for (int it = 0; it < ITG; ++it) {
-                // units - 1 newer groups may still be in flight
-                if (units == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
-                else if (units == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
-                else if (units == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
-                else if (units == 5) asm volatile("cp.async.wait_group 4;" ::: "memory");
-                else if (units == 6) asm volatile("cp.async.wait_group 5;" ::: "memory");
-                else asm volatile("cp.async.wait_group 7;" ::: "memory");
-                const unsigned char *sg = raw + (size_t)((it * kBwProd + tid) * 32);
-                const float4 a0 = *reinterpret_cast<const float4 *>(sg), a1 = *reinterpret_cast<const float4 *>(sg + 16);
+                asm volatile("cp.async.wait_group %0;" ::"n"(UNITS - 1) : "memory");
+                __syncwarp();  // every lane's copies of this slot have landed
+                const unsigned char *sg = raw_warp_p + it * 8 * 1024;
+                const float4 a0 = *reinterpret_cast<const float4 *>(sg + g_rd0), a1 = *reinterpret_cast<const float4 *>(sg + g_rd1);
                 float gv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                if (P.relu) {
-                    const unsigned char *sy = raw + (size_t)(((y_slot0 + it) * kBwProd + tid) * 32);
-                    const float4 y0 = *reinterpret_cast<const float4 *>(sy), y1 = *reinterpret_cast<const float4 *>(sy + 16);
+                if (RELU) {
+                    const unsigned char *sy = raw_warp_p + (y_slot0 + it) * 8 * 1024;
+                    const float4 y0 = *reinterpret_cast<const float4 *>(sy + g_rd0), y1 = *reinterpret_cast<const float4 *>(sy + g_rd1);
                     const float yv[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
 #pragma unroll
                     for (int j = 0; j < 8; ++j) gv[j] = yv[j] > 0.f ? gv[j] : 0.f;
                 }
-                fetch_g(it, next);  // the slots just read are free again
+                __syncwarp();  // every lane has read its part: the slot is free
+                fetch_g(it);   // the next tile's data for this slot start their trip
 #pragma unroll
                 for (int j = 0; j < 8; ++j) dbq_r[j] = __fadd_rn(dbq_r[j], gv[j]);
                 uint32_t hi[4], lo[4];
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) bw_split2_pair(gv[j], gv[j + 1], hi[j >> 1], lo[j >> 1]);
-                const int mg = (it * 32 + ubase) / CGn;
-                const int off = (mg * 2 * CGn + kg_g) * 128 + r8 * 16;
+                const int off = ((mg_g0 + it * (32 / CGN)) * 2 * CGN + kg_g) * 128 + r8 * 16;
                 *reinterpret_cast<uint4 *>(G + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4 *>(G + CGn * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4 *>(G + CGN * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
             // ---- xq = round(x): two bf16 terms stacked along M of the transposed operand ---------------------------------
+#pragma unroll
             for (int it = 0; it < ITX; ++it) {
-                if (units == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
-                else if (units == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
-                else if (units == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
-                else if (units == 5) asm volatile("cp.async.wait_group 4;" ::: "memory");
-                else if (units == 6) asm volatile("cp.async.wait_group 5;" ::: "memory");
-                else asm volatile("cp.async.wait_group 7;" ::: "memory");
-                const unsigned char *sx = raw + (size_t)(((x_slot0 + it) * kBwProd + tid) * 32);
-                const float4 a0 = *reinterpret_cast<const float4 *>(sx), a1 = *reinterpret_cast<const float4 *>(sx + 16);
+                asm volatile("cp.async.wait_group %0;" ::"n"(UNITS - 1) : "memory");
+                __syncwarp();
+                const unsigned char *sx = raw_warp_p + (x_slot0 + it) * 8 * 1024;
+                const float4 a0 = *reinterpret_cast<const float4 *>(sx + x_rd0), a1 = *reinterpret_cast<const float4 *>(sx + x_rd1);
                 float xv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                fetch_x(it, next);
-                const int mg = (it * 32 + ubase) / CGk;
+                __syncwarp();
+                fetch_x(it);
+                const int mg = mg_x0 + it * (32 / CGK);
                 if (has_q) {
                     const uint32_t pr = (uint32_t)(mg * 8 + r8) % rp;
                     const uint2 eb = *reinterpret_cast<const uint2 *>(etab + pr * Ke + kg_x * 8);
@@ -295,6 +331,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
                 *reinterpret_cast<uint4 *>(X + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                 *reinterpret_cast<uint4 *>(X + 8 * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
+            f_row0 += tile_step;
             tc::fence_smem_to_async();
             __syncwarp();
             if (lane == 0) bw_arrive(full);
@@ -315,15 +352,15 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
             float a = 0.f;
             for (int t = 0; t < kBwProd; ++t) {
                 const int tub = (t >> 5) * 4 + ((t & 31) >> 3);
-                if (tub % CGn == kg) a = __fadd_rn(a, red[t * 8 + j]);
+                if (tub % CGN == kg) a = __fadd_rn(a, red[t * 8 + j]);
             }
             rec_hi[(int64_t)K * N + nn] = did_work ? a : 0.f;
             rec_lo[(int64_t)K * N + nn] = 0.f;
         }
     } else if (warp == kBwIssueWarp) {
         // ================================ tensor-core issue ==========================================================
-        const uint32_t idesc1 = tc::make_idesc_bf16(Kp, false, false);
-        const uint32_t idesc2 = tc::make_idesc_bf16(2 * Np, true, true);
+        constexpr uint32_t idesc1 = tc::make_idesc_bf16(Kp, false, false);
+        constexpr uint32_t idesc2 = tc::make_idesc_bf16(2 * Np, true, true);
         const uint32_t g_base = tc::smem_u32(G), x_base = tc::smem_u32(X), w_base = tc::smem_u32(W);
         uint32_t n = 0;
         bool ok = true;
@@ -340,8 +377,9 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
                 bool first = true;
                 for (int tg = 0; tg < 2; ++tg)
                     for (int tw = 0; tw < n_w; ++tw) {
-                        uint64_t da = tc::make_smem_desc(g_base + tg * CGn * 128, 128, (uint32_t)CGn * 256);
-                        uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes, 128, (uint32_t)CGn * 128);
+                        uint64_t da = tc::make_smem_desc(g_base + tg * CGN * 128, 128, (uint32_t)CGN * 256);
+                        uint64_t db = tc::make_smem_desc(w_base + tw * w_term_bytes, 128, (uint32_t)CGN * 128);
+#pragma unroll
                         for (int s = 0; s < Np / 16; ++s) {
                             tc::mma_bf16(acc1, da, db, idesc1, !first);
                             first = false;
@@ -352,8 +390,9 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
                 // MMA2: dWq += xq^T x G, contraction over the 128 rows in steps of 16; both operands MN-major: stride between
                 // 8-groups along M / N = 128 bytes, between 8-groups along the rows = one buffer row
                 uint64_t da = tc::make_smem_desc(x_base, 16 * 128, 128);
-                uint64_t db = tc::make_smem_desc(g_base, (uint32_t)CGn * 256, 128);
-                const uint32_t a_step = (2 * 16 * 128) >> 4, b_step = (uint32_t)(4 * CGn * 128) >> 4;
+                uint64_t db = tc::make_smem_desc(g_base, (uint32_t)CGN * 256, 128);
+                constexpr uint32_t a_step = (2 * 16 * 128) >> 4, b_step = (uint32_t)(4 * CGN * 128) >> 4;
+#pragma unroll
                 for (int s = 0; s < kBwTileM / 16; ++s) {
                     tc::mma_bf16(acc2, da, db, idesc2, !(n == 0 && s == 0));
                     da += a_step;
@@ -372,78 +411,83 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
         // ================================ epilogue ===================================================================
         // Warp e reads TMEM lanes 32 (e & 3) .. + 31 (the rows of the tile it owns) and the column half e >> 2.
         const int e = warp - kBwProdWarps, q = e & 3, part = e >> 2;
-        float *ost = reinterpret_cast<float *>(outst + e * kBwOutWarpBytes);  // 32 rows x wc floats
-        const int wc = Kp >> 1;          // 8, 16 or 32 columns per warp
-        const int cv = wc >> 2;          // float4 chunks per row piece: 2, 4 or 8
-        const int rows_it = 32 / cv;     // rows one copy-out iteration covers
-        const int c0 = part * wc;
-        const int my_rr = lane / cv, my_c4 = lane % cv;  // this lane's piece in iteration i: row my_rr + rows_it * i
+        float *ost = reinterpret_cast<float *>(outst + e * kBwOutWarpBytes);  // 32 rows x WC floats
+        constexpr int WC = Kp / 2;        // 8, 16 or 32 columns per warp
+        constexpr int CV = WC / 4;        // float4 chunks per row piece: 2, 4 or 8
+        constexpr int ROWS_IT = 32 / CV;  // rows one copy-out iteration covers
+        const int c0 = part * WC;
+        const int my_rr = lane / CV, my_c4 = lane % CV;  // this lane's piece in iteration i: row my_rr + ROWS_IT * i
         const int my_col = c0 + my_c4 * 4;               // its 4 columns (the same in every iteration and tile)
         const bool col_in = my_col < K;                  // K % 4 == 0
         const float rbias = (P.rm == RM_RND) ? 0.5f : 0.f;
         const bool do_df = P.want_df && has_q;
-        float acc_df[32];
+        const bool load_x = do_df && col_in;
+        const bool store_dx = P.dx != nullptr && col_in;
+        float acc_df[CV * 4];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc_df[j] = 0.f;
+        for (int j = 0; j < CV * 4; ++j) acc_df[j] = 0.f;
+        // table bytes of this lane's pieces: row (q * 32 + my_rr + ROWS_IT * i) % rows_period, columns my_col .. + 3 -- the same
+        // in every tile (tiles start at multiples of 128, which rows_period divides)
+        const unsigned char *etab_my = etab + my_col;
+        const uint32_t swz_w = (uint32_t)bw_swz(lane, CV);
+        const float *x_my = P.x + ((int64_t)blockIdx.x * kBwTileM + q * 32 + my_rr) * P.ldx + my_col;
+        float *dx_my = P.dx + ((int64_t)blockIdx.x * kBwTileM + q * 32 + my_rr) * P.lddx + my_col;
+        const int64_t x_it = (int64_t)ROWS_IT * P.ldx, dx_it = (int64_t)ROWS_IT * P.lddx;
+        const int64_t x_tile = tile_step * P.ldx, dx_tile = tile_step * P.lddx;
         uint32_t n = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++n) {
+        for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++n, x_my += x_tile, dx_my += dx_tile) {
             const uint32_t a = n & 1u, ause = n >> 1;
-            const int64_t wrow0 = tile * kBwTileM + q * 32;
-            // x pieces of this tile (L2 hits: the producers fetched the lines a moment ago): the first four start their trip
+            const int64_t rows_left = P.M - (tile * kBwTileM + q * 32 + my_rr);  // row of piece i is in range iff ROWS_IT * i < rows_left
+            // x pieces of this tile (L2 hits: the producers fetched the lines a moment ago): the first half starts its trip
             // before the accumulator is waited for, the rest once the accumulator's registers are free again
-            auto load_x = [&](int i) -> float4 {
-                const int64_t row = wrow0 + my_rr + rows_it * i;
-                if (do_df && i < cv && row < P.M && col_in) return __ldg(reinterpret_cast<const float4 *>(P.x + row * P.ldx + my_col));
-                return make_float4(0.f, 0.f, 0.f, 0.f);
-            };
-            float4 xa[4], xb[4];
+            float4 xa[(CV + 1) / 2], xb[(CV + 1) / 2];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) xa[i] = load_x(i);
+            for (int i = 0; i < (CV + 1) / 2; ++i)
+                xa[i] = (load_x && ROWS_IT * i < rows_left) ? __ldg(reinterpret_cast<const float4 *>(x_my + i * x_it)) : make_float4(0.f, 0.f, 0.f, 0.f);
             const bool w = bw_wait(acc_full + a, ause & 1u, abort_word);
             if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
             tc::fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * (uint32_t)Kp + (uint32_t)c0;
-            const int swz_w = bw_swz(lane, cv);
-            for (int cb = 0; cb < wc; cb += 16) {  // 16 columns at a time keeps the register footprint down
+#pragma unroll
+            for (int cb = 0; cb < WC; cb += 16) {  // 16 columns at a time keeps the register footprint down
                 float v[16];
-                if (wc >= 16) tc::tmem_ld16v(taddr + (uint32_t)cb, v);
+                if (WC >= 16) tc::tmem_ld16v(taddr + (uint32_t)cb, v);
                 else tc::tmem_ld8v(taddr, v);
-                if (cb + 16 >= wc) {  // the accumulator is in registers: hand it back to the issuing warp
+                if (cb + 16 >= WC) {  // the accumulator is in registers: hand it back to the issuing warp
                     tc::fence_before_sync();
                     __syncwarp();
                     if (lane == 0) bw_arrive(acc_empty + a);
                 }
 #pragma unroll
                 for (int j = 0; j < 16; j += 4)
-                    if (cb + j < wc)
-                        *reinterpret_cast<float4 *>(ost + lane * wc + ((((cb + j) >> 2) ^ swz_w) << 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    if (cb + j < WC)
+                        *reinterpret_cast<float4 *>(ost + lane * WC + ((((cb + j) >> 2) ^ swz_w) << 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) xb[i] = load_x(4 + i);
+            for (int i = 0; i < CV / 2; ++i) {
+                const int ii = (CV + 1) / 2 + i;
+                xb[i] = (load_x && ROWS_IT * ii < rows_left) ? __ldg(reinterpret_cast<const float4 *>(x_my + ii * x_it)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (i < cv) {
-                    const int rr = my_rr + rows_it * i;
-                    const int64_t row = wrow0 + rr;
-                    const float4 o = *reinterpret_cast<const float4 *>(ost + rr * wc + ((my_c4 ^ bw_swz(rr, cv)) << 2));
-                    if (do_df) {
-                        const uint32_t pr = (uint32_t)(q * 32 + rr) % (uint32_t)P.rows_period;
-                        const uint32_t eb = *reinterpret_cast<const uint32_t *>(etab + pr * Ke + my_col);
-                        const float4 xp = (i < 4) ? xa[i & 3] : xb[i & 3];
-                        const float xs[4] = {xp.x, xp.y, xp.z, xp.w};
-                        const float os[4] = {o.x, o.y, o.z, o.w};
+            for (int i = 0; i < CV; ++i) {
+                const int rr = my_rr + ROWS_IT * i;
+                const float4 o = *reinterpret_cast<const float4 *>(ost + rr * WC + ((my_c4 ^ bw_swz(rr, CV)) << 2));
+                if (do_df) {
+                    const uint32_t pr = (uint32_t)(q * 32 + rr) % (uint32_t)P.rows_period;
+                    const uint32_t eb = *reinterpret_cast<const uint32_t *>(etab_my + pr * Ke);
+                    const float4 xp = (i < (CV + 1) / 2) ? xa[i < (CV + 1) / 2 ? i : 0] : xb[i >= (CV + 1) / 2 ? i - (CV + 1) / 2 : 0];
+                    const float xs[4] = {xp.x, xp.y, xp.z, xp.w};
+                    const float os[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float xq = bw_round_e<CONV>(xs[j], (eb >> (j * 8)) & 0xffu, rbias);
-                            const float d = __fmul_rn(__fsub_rn(xq, xs[j]), -kLn2);
-                            acc_df[i * 4 + j] = fmaf(d, os[j], acc_df[i * 4 + j]);
-                        }
+                    for (int j = 0; j < 4; ++j) {
+                        const float xq = bw_round_e<CONV>(xs[j], (eb >> (j * 8)) & 0xffu, rbias);
+                        const float d = __fmul_rn(__fsub_rn(xq, xs[j]), -kLn2);
+                        acc_df[i * 4 + j] = fmaf(d, os[j], acc_df[i * 4 + j]);
                     }
-                    if (P.dx != nullptr && row < P.M && col_in)
-                        __stcs(reinterpret_cast<float4 *>(P.dx + row * P.lddx + my_col), o);
                 }
+                if (store_dx && ROWS_IT * i < rows_left) __stcs(reinterpret_cast<float4 *>(dx_my + i * dx_it), o);
             }
             __syncwarp();  // the transposition buffer is reused by the next tile
         }
@@ -458,7 +502,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
             const int m = q * 32 + lane;          // accumulator lane
             const int k = m & 63;
             float *rec = (m < 64) ? rec_hi : rec_lo;
-            const int ncol = Np >> 1;             // columns per warp of a lane quarter
+            constexpr int ncol = Np / 2;          // columns per warp of a lane quarter
             for (int cc = part * ncol; cc < (part + 1) * ncol; cc += 8) {
                 float v1[8], v2[8];
                 tc::tmem_ld8v(acc2 + ((uint32_t)(q * 32) << 16) + (uint32_t)cc, v1);
@@ -480,12 +524,11 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
             asm volatile("bar.sync 2, %0;" ::"n"(kBwEpiWarps * 32) : "memory");
             float *st = reinterpret_cast<float *>(X);  // [128][Kp] floats <= 32 KB, the size of the xq^T operand
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                if (i < cv) {
-                    const int rr = q * 32 + my_rr + rows_it * i;
+            for (int i = 0; i < CV; ++i) {
+                const int rr = q * 32 + my_rr + ROWS_IT * i;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) st[rr * Kp + my_col + j] = acc_df[i * 4 + j];
-                }
+                for (int j = 0; j < 4; ++j) st[rr * Kp + my_col + j] = acc_df[i * 4 + j];
+            }
             asm volatile("bar.sync 2, %0;" ::"n"(kBwEpiWarps * 32) : "memory");
             float *pdf_hi = rec_hi + (int64_t)(K + 1) * N, *pdf_lo = rec_lo + (int64_t)(K + 1) * N;
             for (int idx = (warp - kBwProdWarps) * 32 + lane; idx < P.rows_period * K; idx += kBwEpiWarps * 32) {
@@ -533,16 +576,29 @@ int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const f
     p.gy_repeat = gy_repeat; p.gy_div = make_fastdiv((uint32_t)gy_repeat);
     const int g = (int)(p.num_tiles < num_sms() ? p.num_tiles : num_sms());
     *records = 2 * g;
-    cudaError_t ce;
-    if (round_mode == RM_RND_CONV) {
-        ce = cudaFuncSetAttribute(k_qdense_bwd_ws<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (ce != cudaSuccess) return -(int)ce;
-        k_qdense_bwd_ws<true><<<g, kBwThreads, smem, st>>>(p);
-    } else {
-        ce = cudaFuncSetAttribute(k_qdense_bwd_ws<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (ce != cudaSuccess) return -(int)ce;
-        k_qdense_bwd_ws<false><<<g, kBwThreads, smem, st>>>(p);
+    const int cgn = Np / 8, cgk = Kp / 8;
+    const bool relu = y != nullptr, conv = round_mode == RM_RND_CONV;
+    cudaError_t ce = cudaSuccess;
+    bool launched = false;
+#define HGQ_BW_CASE(CV_, CGN_, CGK_, RELU_)                                                                                  \
+    if (!launched && conv == CV_ && cgn == CGN_ && cgk == CGK_ && relu == RELU_) {                                           \
+        ce = cudaFuncSetAttribute(k_qdense_bwd_ws<CV_, CGN_, CGK_, RELU_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                  (int)smem);                                                                               \
+        if (ce != cudaSuccess) return -(int)ce;                                                                             \
+        k_qdense_bwd_ws<CV_, CGN_, CGK_, RELU_><<<g, kBwThreads, smem, st>>>(p);                                            \
+        launched = true;                                                                                                    \
     }
+#define HGQ_BW_SHAPES(CV_, RELU_)                                                                                           \
+    HGQ_BW_CASE(CV_, 2, 2, RELU_) HGQ_BW_CASE(CV_, 2, 4, RELU_) HGQ_BW_CASE(CV_, 2, 8, RELU_)                               \
+    HGQ_BW_CASE(CV_, 4, 2, RELU_) HGQ_BW_CASE(CV_, 4, 4, RELU_) HGQ_BW_CASE(CV_, 4, 8, RELU_)                               \
+    HGQ_BW_CASE(CV_, 8, 2, RELU_) HGQ_BW_CASE(CV_, 8, 4, RELU_) HGQ_BW_CASE(CV_, 8, 8, RELU_)
+    HGQ_BW_SHAPES(false, false)
+    HGQ_BW_SHAPES(false, true)
+    HGQ_BW_SHAPES(true, false)
+    HGQ_BW_SHAPES(true, true)
+#undef HGQ_BW_SHAPES
+#undef HGQ_BW_CASE
+    if (!launched) return 0;
     return 1;
 }
 
