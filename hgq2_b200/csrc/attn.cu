@@ -44,13 +44,13 @@ __device__ __forceinline__ void at_split2(float v0, float v1, uint32_t &hi, uint
 
 // eight consecutive floats -> one 16-byte row of a core matrix in each of the two term planes
 __device__ __forceinline__ int at_put8(const float *src, unsigned char *hi_plane, unsigned char *lo_plane, int off) {
-    const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
-    const float4 b = __ldg(reinterpret_cast<const float4 *>(src + 4));
+    float v[8];
+    ldcs8(src, v);  // one 32-byte sector per thread and instruction; every operand element is read once per product
     uint32_t hi[4], lo[4];
-    at_split2(a.x, a.y, hi[0], lo[0]);
-    at_split2(a.z, a.w, hi[1], lo[1]);
-    at_split2(b.x, b.y, hi[2], lo[2]);
-    at_split2(b.z, b.w, hi[3], lo[3]);
+    at_split2(v[0], v[1], hi[0], lo[0]);
+    at_split2(v[2], v[3], hi[1], lo[1]);
+    at_split2(v[4], v[5], hi[2], lo[2]);
+    at_split2(v[6], v[7], hi[3], lo[3]);
     *reinterpret_cast<uint4 *>(hi_plane + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
     *reinterpret_cast<uint4 *>(lo_plane + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     return ((lo[0] | lo[1] | lo[2] | lo[3]) & 0x7fff7fffu) != 0;
@@ -191,8 +191,7 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
             for (int c0 = half * ncol; c0 < (half + 1) * ncol; c0 += 8) {
                 float v[8];
                 tc::tmem_ld8v(tmem_base + ((uint32_t)qlane << 16) + (uint32_t)(hh * Nn + c0), v);
-                __stcs(reinterpret_cast<float4 *>(dst + c0), make_float4(v[0], v[1], v[2], v[3]));
-                __stcs(reinterpret_cast<float4 *>(dst + c0 + 4), make_float4(v[4], v[5], v[6], v[7]));
+                stcs8(dst + c0, v);
             }
         }
         tc::fence_before_sync();
@@ -221,7 +220,7 @@ extern "C" int hgq_attn_heads_matmul(int kind, const float *x, const float *y, f
     if (x == nullptr || y == nullptr || out == nullptr) return HGQ_ERR_NULL;
     if (kind < 0 || kind > 2) return HGQ_ERR_MODE;
     if (!hgq_attn_heads_supported(B, L, H, D)) return HGQ_ERR_SIZE;
-    if (!aligned(x, 16) || !aligned(y, 16) || !aligned(out, 16)) return HGQ_ERR_ALIGN;
+    if (!aligned(x, 32) || !aligned(y, 32) || !aligned(out, 32)) return HGQ_ERR_ALIGN;  // 256-bit accesses
     AtParams p;
     p.x = x; p.y = y; p.out = out; p.status = status;
     p.B = B; p.H = H; p.D = D;

@@ -46,6 +46,28 @@ inline int check_launch() {
     return HGQ_OK;
 }
 
+// 256-bit global accesses (sm_100): one instruction moves a whole 32-byte sector per thread.  Two 128-bit accesses to the
+// two halves of a sector are two requests for that sector wherever the first level cache does not merge them (streaming
+// stores, cache-bypassing loads), and the rate of sector requests between an SM and L2 is what bounds several of the
+// kernels here well before HBM does.  Addresses must be 32-byte aligned.
+#ifdef __CUDACC__
+__device__ __forceinline__ void ldg8(const float *p, float (&v)[8]) {  // read-only data, kept in L1 like __ldg
+    asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void ldcs8(const float *p, float (&v)[8]) {  // streaming: read once
+    asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void stcs8(float *p, const float (&v)[8]) {  // streaming store of a whole sector
+    asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]),
+                 "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                 : "memory");
+}
+#endif
+
 __host__ __device__ inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // Division of a non-negative 31-bit number by an invariant divisor through one 64-bit multiply: n / d == (n * mul) >> shift
