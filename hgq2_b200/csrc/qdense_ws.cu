@@ -17,10 +17,18 @@
 //               for every pair of terms, commits to empty[stage] and, after the last slab of a tile, to acc_full[acc].
 // With two operand stages and two accumulators in tensor memory the conversion of tile t + 1 overlaps the products of
 // tile t and the write-out of tile t - 1.  HBM-bound: 4 (K + N) bytes per row.
+// Raw slabs reach shared memory in one of two ways (template parameter TMA): every producer thread copies its own pieces
+// with cp.async into thread-private slots, or an extra loader warp has the copy engine fetch the whole 128 x 64 slab as
+// two tiled bulk-tensor copies (cp.async.bulk.tensor.2d, 128 rows x 32 floats each, 128-byte swizzle, completion counted
+// on an mbarrier), from a tensor map over this GPU's x alone.  Rows past the end of x and columns past K arrive as zeros.
 // Every wait is bounded (polls and wall time); a wait that gives up sets an abort word that ends every role's loop, the
 // status word tells the host, and the CTA still frees its tensor memory.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
 
 #include "hgq_common.cuh"
 #include "hgq_math.cuh"
@@ -84,15 +92,34 @@ __device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, volatile
     return false;
 }
 
+__device__ __forceinline__ void ws_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 st;\n\t"
+        "mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t"
+        "}\n" ::"r"(tc::smem_u32(bar)), "r"(bytes)
+        : "memory");
+}
+
+// One tiled 2-D bulk copy global -> shared (this CTA's own shared memory), completion bytes counted on `bar`.
+__device__ __forceinline__ void ws_tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(tc::smem_u32(bar))
+                 : "memory");
+}
+
 __device__ __forceinline__ int ws_swz(int r, int C) { return C == 8 ? (r & 7) : (C == 4 ? ((r >> 1) & 3) : ((r >> 2) & 1)); }
 
-template <bool RCONV, int AMAX, int NPW, int EW>
-__global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const WsParams P) {
+template <bool RCONV, int AMAX, int NPW, int EW, bool TMA>
+__global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qdense_fwd_ws(const WsParams P,
+                                                                                       const __grid_constant__ CUtensorMap tmap) {
     constexpr int kWsProdWarps = NPW, kWsProd = NPW * 32, kWsEpiWarps = EW, kWsIssueWarp = NPW + EW;
-    constexpr int kWsThreads = (NPW + EW + 1) * 32;
+    constexpr int kWsLoadWarp = NPW + EW + 1;  // TMA only
+    constexpr int kWsThreads = (NPW + EW + 1 + (TMA ? 1 : 0)) * 32;
     constexpr int ITS = 32 / NPW;       // 8-row groups a producer thread converts per slab
     constexpr int ROWSTEP = NPW * 4;    // their distance in rows
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);  // the carve starts on a 1 KB boundary
     // carve: operand stages | raw-slab slots | transposition buffers | B terms | bias | exponent table | abs-max table |
     // barriers, TMEM slot, flags
     unsigned char *A = smem;
@@ -112,7 +139,8 @@ __global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const 
     float *amax_t = amax_regs ? reinterpret_cast<float *>(fetch) : reinterpret_cast<float *>(etab + tab_bytes);
     uint64_t *full = reinterpret_cast<uint64_t *>(etab + tab_bytes + amax_elems * 4);
     uint64_t *empty = full + 2, *acc_full = full + 4, *acc_empty = full + 6;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(full + 8);
+    uint64_t *raw_full = full + 8, *raw_empty = full + 10;  // TMA only: a raw slab has landed / has been read by every producer
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(full + 12);
     int *dirty3 = reinterpret_cast<int *>(tmem_slot + 1);  // per stage: some tile needed the third term (sticky)
     int *abort_word = dirty3 + 2;
 
@@ -127,10 +155,16 @@ __global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const 
             tc::mbar_init(empty + s, 1);      // tcgen05.commit
             tc::mbar_init(acc_full + s, 1);   // tcgen05.commit
             tc::mbar_init(acc_empty + s, kWsEpiWarps);  // one arrival per epilogue warp
+            tc::mbar_init(raw_full + s, 1);             // the loader's expect_tx arrival (+ the copies' bytes)
+            tc::mbar_init(raw_empty + s, kWsProdWarps);
             dirty3[s] = 0;
         }
         *abort_word = 0;
         tc::mbar_init_fence();
+        if (TMA && (tc::smem_u32(fetch) & 1023u) != 0) {  // the swizzled copies need a 1 KB aligned destination
+            *abort_word = 1;
+            if (P.status) atomicOr(P.status, kWsTimeout);
+        }
     }
     if (warp == kWsIssueWarp) tc::tmem_alloc(tmem_slot, tmem_cols);
     for (int e = tid; e < Npad; e += kWsThreads) bias_s[e] = (P.bq != nullptr && e < N) ? __ldg(P.bq + e) : 0.f;
@@ -202,7 +236,12 @@ __global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const 
             if (++pf_ch == n_chunks) { pf_ch = 0; pf_tile += gridDim.x; }
             ++pf_n;
         };
-        for (int d = 0; d < depth; ++d) request();
+        if (!TMA)
+            for (int d = 0; d < depth; ++d) request();
+        // where this thread finds its unit of iteration it in a slab the copy engine wrote: column half kg / 4 (one 16 KB
+        // copy each), row it * ROWSTEP + (warp / 2) * 8 + r8 of 128 bytes, 16-byte chunk XOR (row & 7) = r8 (128-byte swizzle)
+        const int tma_rd0 = (kg >> 2) * (kWsFetchBytes / 2) + ((warp >> 1) * 8 + r8) * 128 + ((((kg & 3) * 2) ^ r8) * 16);
+        const int tma_rd1 = (kg >> 2) * (kWsFetchBytes / 2) + ((warp >> 1) * 8 + r8) * 128 + ((((kg & 3) * 2 + 1) ^ r8) * 16);
 
         const uint32_t rp = (uint32_t)P.rows_period;
         const bool rp_pow2 = (rp & (rp - 1)) == 0;
@@ -220,9 +259,25 @@ __global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const 
                 const uint32_t use = n >> 1;
                 unsigned char *As = A + s * kWsStageBytes;
                 float xv[ITS][8];
-                if (depth == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
-                else asm volatile("cp.async.wait_group 0;" ::: "memory");
-                {
+                if (TMA) {
+                    const uint32_t rb = depth == 2 ? (n & 1u) : 0u, ruse = depth == 2 ? (n >> 1) : n;
+                    const bool w = ws_wait(raw_full + rb, ruse & 1u, abort_word);
+                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    const unsigned char *buf = fetch + rb * kWsFetchBytes;
+                    const bool col_in = ch * kWsKC + kg * 8 < K;  // a column half the loader did not fetch holds nothing
+#pragma unroll
+                    for (int it = 0; it < ITS; ++it) {
+                        const float4 v0 = *reinterpret_cast<const float4 *>(buf + it * ROWSTEP * 128 + tma_rd0);
+                        const float4 v1 = *reinterpret_cast<const float4 *>(buf + it * ROWSTEP * 128 + tma_rd1);
+                        xv[it][0] = col_in ? v0.x : 0.f; xv[it][1] = col_in ? v0.y : 0.f; xv[it][2] = col_in ? v0.z : 0.f;
+                        xv[it][3] = col_in ? v0.w : 0.f; xv[it][4] = col_in ? v1.x : 0.f; xv[it][5] = col_in ? v1.y : 0.f;
+                        xv[it][6] = col_in ? v1.z : 0.f; xv[it][7] = col_in ? v1.w : 0.f;
+                    }
+                    __syncwarp();  // every lane holds its units in registers: the slab buffer may be refilled
+                    if (lane == 0) ws_arrive(raw_empty + rb);
+                } else {
+                    if (depth == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    else asm volatile("cp.async.wait_group 0;" ::: "memory");
                     const unsigned char *buf = fetch + (depth == 2 ? (n & 1u) : 0u) * kWsFetchBytes;
 #pragma unroll
                     for (int it = 0; it < ITS; ++it) {
@@ -231,8 +286,8 @@ __global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const 
                         xv[it][0] = v0.x; xv[it][1] = v0.y; xv[it][2] = v0.z; xv[it][3] = v0.w;
                         xv[it][4] = v1.x; xv[it][5] = v1.y; xv[it][6] = v1.z; xv[it][7] = v1.w;
                     }
+                    request();  // the slots just read are free again (their contents sit in registers)
                 }
-                request();  // the slots just read are free again (their contents sit in registers)
                 // the products that read this stage two slabs ago must have completed (they were issued a whole slab ago)
                 if (use > 0) {
                     const bool w = ws_wait(empty + s, (use - 1) & 1u, abort_word);
@@ -374,6 +429,37 @@ __global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const 
             *reinterpret_cast<volatile int *>(abort_word) = 1;
             if (lane == 0 && P.status) atomicOr(P.status, kWsTimeout);
         }
+    } else if (TMA && warp == kWsLoadWarp) {
+        // ================================ bulk-copy loader (TMA variant) ===========================================
+        // One thread keeps `depth` raw slabs in flight: it waits until every producer warp has taken its units out of a slab
+        // buffer, then has the copy engine fetch the next slab into it.  The whole warp walks the loop (it stays converged
+        // for the tear-down barrier); lane 0 issues.
+        const int depth = P.depth;
+        const uint32_t fetch_base = tc::smem_u32(fetch);
+        uint32_t n = 0;
+        bool ok = *reinterpret_cast<volatile int *>(abort_word) == 0;
+        for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
+            for (int ch = 0; ch < n_chunks && ok; ++ch, ++n) {
+                const uint32_t rb = depth == 2 ? (n & 1u) : 0u, ruse = depth == 2 ? (n >> 1) : n;
+                if (ruse > 0) {
+                    const bool w = ws_wait(raw_empty + rb, (ruse - 1) & 1u, abort_word);
+                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                }
+                if (lane == 0) {
+                    const int c0 = ch * kWsKC;
+                    const int halves = (K - c0 > 32) ? 2 : 1;  // a column half that lies past K is not fetched at all
+                    ws_expect_tx(raw_full + rb, (uint32_t)(halves * (kWsFetchBytes / 2)));
+                    const uint32_t dst = fetch_base + rb * kWsFetchBytes;
+                    for (int hcol = 0; hcol < halves; ++hcol)
+                        ws_tma_load_2d(dst + hcol * (kWsFetchBytes / 2), &tmap, c0 + hcol * 32, (int)(tile * kWsTileM), raw_full + rb);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok) {
+            *reinterpret_cast<volatile int *>(abort_word) = 1;
+            if (lane == 0 && P.status) atomicOr(P.status, kWsTimeout);
+        }
     } else {
         // ================================ epilogue ===================================================================
         // Warp e reads TMEM lanes 32 (e & 3) .. + 31 (the rows of the tile it owns); with eight warps the column pieces
@@ -460,7 +546,46 @@ __global__ void __launch_bounds__((NPW + EW + 1) * 32, 1) k_qdense_fwd_ws(const 
 static size_t qdense_ws_smem(int Kpad, int Npad, int Kt, int rows_period, bool amax_table, int depth, int ew) {
     const size_t tab_bytes = ((size_t)rows_period * (Kt + 8) + 15) / 16 * 16;
     return 2 * (size_t)kWsStageBytes + (size_t)depth * kWsFetchBytes + (size_t)ew * kWsOutWarpBytes + 3 * (size_t)Kpad * Npad * 2 +
-           (size_t)Npad * 4 + tab_bytes + (amax_table ? (size_t)rows_period * (Kt + 4) * 4 : 0) + 8 * 8 + 32;
+           (size_t)Npad * 4 + tab_bytes + (amax_table ? (size_t)rows_period * (Kt + 4) * 4 : 0) + 12 * 8 + 32;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point query (the library does not link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static const EncodeTiledFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return (EncodeTiledFn) nullptr;
+        }
+        return (EncodeTiledFn)ptr;
+    }();
+    return fn;
+}
+
+// HGQ_QDENSE_TMA=0 / 1 in the environment picks how raw slabs are fetched (thread-private cp.async / bulk tensor copies).
+static bool ws_tma_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("HGQ_QDENSE_TMA");
+        return v != nullptr ? v[0] != '0' : true;  // measured faster on every layer shape of the training workloads
+    }();
+    return on;
+}
+
+// A tensor map over x [M, K] fp32 (this GPU's memory only): boxes of 128 rows x 32 floats, 128-byte swizzle, zeros outside.
+static bool ws_make_tmap(CUtensorMap *map, const float *x, int64_t M, int K) {
+    const EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 4};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kWsTileM};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Launches the warp-specialised kernel when it covers the call; returns 1 with the grid size in *grid, 0 when the call is
@@ -500,12 +625,23 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
     p.rm = round_mode; p.act = activation; p.depth = depth;
     const int g = (int)(p.num_tiles < num_sms() ? p.num_tiles : num_sms());
     *grid = g;
-#define HGQ_WS_LAUNCH(CV, AM, PW, EWW)                                                                                      \
-    do {                                                                                                                    \
-        cudaError_t ce = cudaFuncSetAttribute(k_qdense_fwd_ws<CV, AM, PW, EWW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                              (int)smem);                                                                   \
-        if (ce != cudaSuccess) return -(int)ce;                                                                             \
-        k_qdense_fwd_ws<CV, AM, PW, EWW><<<g, (PW + EWW + 1) * 32, smem, st>>>(p);                                           \
+    CUtensorMap tmap;
+    memset(&tmap, 0, sizeof(tmap));
+    // the bulk copies want x 16-byte aligned with rows a multiple of 16 bytes (K % 4 == 0, checked above)
+    const bool tma = ws_tma_enabled() && M < ((int64_t)1 << 31) && ws_make_tmap(&tmap, x, M, K);
+    smem += 1024;  // room to start the carve on a 1 KB boundary whatever the base of dynamic shared memory is
+    if (smem > 227 * 1024) return 0;
+#define HGQ_WS_LAUNCH1(CV, AM, PW, EWW, TM)                                                                                      \
+    do {                                                                                                                        \
+        cudaError_t ce = cudaFuncSetAttribute(k_qdense_fwd_ws<CV, AM, PW, EWW, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                              (int)smem);                                                                       \
+        if (ce != cudaSuccess) return -(int)ce;                                                                                 \
+        k_qdense_fwd_ws<CV, AM, PW, EWW, TM><<<g, (PW + EWW + 1 + (TM ? 1 : 0)) * 32, smem, st>>>(p, tmap);                      \
+    } while (0)
+#define HGQ_WS_LAUNCH(CV, AM, PW, EWW)                 \
+    do {                                               \
+        if (tma) HGQ_WS_LAUNCH1(CV, AM, PW, EWW, true); \
+        else HGQ_WS_LAUNCH1(CV, AM, PW, EWW, false);    \
     } while (0)
 #define HGQ_WS_MODES(CV, PW, EWW)                                                     \
     switch (amax_mode) {                                                              \
@@ -517,6 +653,7 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
     if (round_mode == RM_RND_CONV) { HGQ_WS_MODES(true, npw, ew) } else { HGQ_WS_MODES(false, npw, ew) }
 #undef HGQ_WS_MODES
 #undef HGQ_WS_LAUNCH
+#undef HGQ_WS_LAUNCH1
     return 1;
 }
 
