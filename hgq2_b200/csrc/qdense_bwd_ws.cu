@@ -18,12 +18,20 @@
 //                     buffer and, piece by piece in coalesced order, re-read x (an L2 hit: the producers fetched it a few
 //                     microseconds earlier), form the fractional-bit gradient terms and write dX.  The df sums live in
 //                     registers across tiles (a lane meets the same table rows and columns in every tile).
+// With the template parameter TMA the raw tiles are fetched by the copy engine instead: an extra loader warp issues tiled
+// bulk-tensor copies (cp.async.bulk.tensor.2d, 128 rows x 32 floats, 128-byte swizzle; tensor maps over this GPU's dY, y
+// and x only) as soon as every producer warp has taken its units out of a buffer, and the producers issue no copies at
+// all.  (A dY that repeats rows -- the gradient of a sum -- has no tiled description and keeps the cp.async route.)
 // Per-CTA partials (two records: the rows of the accumulator that hold the high and the low terms of xq) are reduced in a
 // fixed order by k_qb_stage2.  HBM-bound: 4 (2N + 2K) bytes per row.
 // Every wait is bounded (polls and wall time); a role that gives up raises an abort word that ends the other roles' loops,
 // the status word tells the host, and the CTA still frees its tensor memory.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
 
 #include "hgq_common.cuh"
 #include "hgq_math.cuh"
@@ -36,6 +44,7 @@ constexpr int kBwProdWarps = 8, kBwProd = kBwProdWarps * 32;
 constexpr int kBwEpiWarps = 8;
 constexpr int kBwIssueWarp = kBwProdWarps + kBwEpiWarps;
 constexpr int kBwThreads = (kBwProdWarps + kBwEpiWarps + 1) * 32;
+constexpr int kBwLoadWarp = kBwIssueWarp + 1;  // bulk-copy loader (TMA variant only)
 constexpr int kBwXBytes = 128 * 128 * 2;      // xq^T operand: 128 rows x (64 high-term + 64 low-term) columns of bf16
 constexpr int kBwOutWarpBytes = 4096;         // transposition buffer of one epilogue warp: 32 rows x 32 floats
 constexpr unsigned kBwTimeout = 1u;
@@ -97,6 +106,22 @@ __device__ __forceinline__ float bw_round_e(float v, uint32_t ebyte, float rbias
     return __fmul_rn(q, __uint_as_float(0x7F000000u - sbits));
 }
 
+__device__ __forceinline__ void bw_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 st;\n\t"
+        "mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t"
+        "}\n" ::"r"(tc::smem_u32(bar)), "r"(bytes)
+        : "memory");
+}
+
+// One tiled 2-D bulk copy global -> shared (this CTA's own shared memory), completion bytes counted on `bar`.
+__device__ __forceinline__ void bw_tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(tc::smem_u32(bar))
+                 : "memory");
+}
+
 __device__ __forceinline__ int bw_swz(int r, int C) { return C == 8 ? (r & 7) : (C == 4 ? ((r >> 1) & 3) : ((r >> 2) & 1)); }
 
 __device__ __forceinline__ void bw_cp16(uint32_t dst, const float *src, bool in) {
@@ -106,15 +131,19 @@ __device__ __forceinline__ void bw_cp16(uint32_t dst, const float *src, bool in)
 // The kernel is a template on the padded widths (CGN = Np / 8 and CGK = Kp / 8 column groups: 2, 4 or 8 each), on the
 // ReLU mask and on the rounding flavour, so that every loop below has a constant trip count and every shared-memory offset
 // is an immediate: the kernel is bound by the number of instructions it issues, not by bytes.
-template <bool CONV, int CGN, int CGK, bool RELU>
-__global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams P) {
+template <bool CONV, int CGN, int CGK, bool RELU, bool TMA>
+__global__ void __launch_bounds__(kBwThreads + (TMA ? 32 : 0), 1) k_qdense_bwd_ws(const BwParams P, const __grid_constant__ CUtensorMap map_g,
+                                                                                 const __grid_constant__ CUtensorMap map_y,
+                                                                                 const __grid_constant__ CUtensorMap map_x) {
+    constexpr int kThreadsAll = kBwThreads + (TMA ? 32 : 0);
     constexpr int Np = CGN * 8, Kp = CGK * 8;
     constexpr int ITG = CGN / 2, ITX = CGK / 2;  // units (8 rows x 8 columns) a producer thread converts per tile
     constexpr int UNITS = ITG + ITX;
     constexpr int g_bytes = 2 * kBwTileM * Np * 2;  // both bf16 terms
     constexpr int w_term_bytes = Kp * Np * 2;
     constexpr int n_raw_units = ITG * (RELU ? 2 : 1) + ITX;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);  // the carve starts on a 1 KB boundary
     const int K = P.K, N = P.N;
     const bool has_q = P.qf != nullptr;
     // carve: G operand | xq^T operand | W terms (3) | raw slots (dY, y, x) | transposition buffers | exponent table |
@@ -122,14 +151,16 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
     unsigned char *G = smem;
     unsigned char *X = G + g_bytes;
     unsigned char *W = X + kBwXBytes;
-    unsigned char *raw = W + 3 * w_term_bytes;
+    constexpr int raw_off = (g_bytes + kBwXBytes + 3 * w_term_bytes + 1023) / 1024 * 1024;  // bulk copies land on a 1 KB boundary
+    unsigned char *raw = smem + raw_off;
     unsigned char *outst = raw + n_raw_units * kBwProd * 32;
     const int Ke = P.Kt + 8;
     unsigned char *etab = outst + kBwEpiWarps * kBwOutWarpBytes;
     const int tab_bytes = has_q ? (P.rows_period * Ke + 15) / 16 * 16 : 0;
     uint64_t *full = reinterpret_cast<uint64_t *>(etab + tab_bytes);
     uint64_t *stage_free = full + 1, *acc_full = full + 2, *acc_empty = full + 4;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(full + 6);
+    uint64_t *rawg_full = full + 6, *rawg_empty = full + 7, *rawx_full = full + 8, *rawx_empty = full + 9;  // TMA variant
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(full + 10);
     int *abort_word = reinterpret_cast<int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -143,21 +174,25 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
             tc::mbar_init(acc_full + a, 1);
             tc::mbar_init(acc_empty + a, kBwEpiWarps);
         }
+        tc::mbar_init(rawg_full, 1);   // the loader's expect_tx arrival (+ the copies' bytes)
+        tc::mbar_init(rawx_full, 1);
+        tc::mbar_init(rawg_empty, kBwProdWarps);
+        tc::mbar_init(rawx_empty, kBwProdWarps);
         *abort_word = 0;
         tc::mbar_init_fence();
     }
     if (warp == kBwIssueWarp) tc::tmem_alloc(tmem_slot, tmem_cols);
     if (has_q)
-        for (int e = tid; e < P.rows_period * P.Kt; e += kBwThreads) {
+        for (int e = tid; e < P.rows_period * P.Kt; e += kThreadsAll) {
             const int pr = e / P.Kt, k = e % P.Kt;
             const int fi = (k < K) ? __float2int_rn(__ldg(P.qf + pr * K + k)) : 0;
             etab[pr * Ke + k] = (unsigned char)(max(-126, min(127, fi)) + 127);
         }
     // the xq^T operand: column groups that no conversion unit writes (k >= Kp of either term) stay zero for ever
-    for (int e = tid; e < kBwXBytes / 16; e += kBwThreads) reinterpret_cast<uint4 *>(X)[e] = make_uint4(0, 0, 0, 0);
+    for (int e = tid; e < kBwXBytes / 16; e += kThreadsAll) reinterpret_cast<uint4 *>(X)[e] = make_uint4(0, 0, 0, 0);
     // weights as the B operand of MMA1: rows k (the product's N index), contraction n; core (k/8, n/8)
     int w_lo = 0, w_lo2 = 0;
-    for (int e = tid; e < Kp * Np; e += kBwThreads) {
+    for (int e = tid; e < Kp * Np; e += kThreadsAll) {
         const int n = e % Np, k = e / Np;
         const float w = (k < K && n < N) ? __ldg(P.wq + (int64_t)k * N + n) : 0.f;
         __nv_bfloat16 h, l, l2;
@@ -262,11 +297,24 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
         };
         // one commit group per unit, in unit order; past the last tile every row is out of range and the copies fetch
         // nothing, so "all but the newest UNITS - 1 groups have landed" always means "this unit has landed"
+        if (!TMA) {
 #pragma unroll
-        for (int it = 0; it < ITG; ++it) fetch_g(it);
+            for (int it = 0; it < ITG; ++it) fetch_g(it);
 #pragma unroll
-        for (int it = 0; it < ITX; ++it) fetch_x(it);
-        f_row0 += tile_step;
+            for (int it = 0; it < ITX; ++it) fetch_x(it);
+            f_row0 += tile_step;
+        }
+        // where this thread finds its unit (row group mg, column group kg) in a tile the copy engine wrote: one 128-row copy
+        // per 32 columns (column half kg / 4), rows of IB = min(32, columns) * 4 bytes, 16-byte chunks XOR-swizzled with
+        // the row (128-byte rows: chunk ^ (row & 7); 64-byte rows: chunk ^ ((row >> 1) & 3)); row & 7 = r8 here
+        constexpr int IBG = (CGN >= 4 ? 128 : 64), IBX = (CGK >= 4 ? 128 : 64);
+        const int swg = (IBG == 128) ? r8 : ((r8 >> 1) & 3), swx = (IBX == 128) ? r8 : ((r8 >> 1) & 3);
+        const int tg_rd0 = (kg_g >> 2) * (128 * IBG) + r8 * IBG + ((((kg_g & 3) * 2) ^ swg) * 16);
+        const int tg_rd1 = (kg_g >> 2) * (128 * IBG) + r8 * IBG + ((((kg_g & 3) * 2 + 1) ^ swg) * 16);
+        const int tx_rd0 = (kg_x >> 2) * (128 * IBX) + r8 * IBX + ((((kg_x & 3) * 2) ^ swx) * 16);
+        const int tx_rd1 = (kg_x >> 2) * (128 * IBX) + r8 * IBX + ((((kg_x & 3) * 2 + 1) ^ swx) * 16);
+        constexpr int g_stream_bytes = 128 * Np * 4, x_stream_bytes = 128 * Kp * 4;  // one raw tile of dY (or y) / of x
+        const unsigned char *raw_y = raw + g_stream_bytes, *raw_x = raw + g_stream_bytes * (RELU ? 2 : 1);
 
         float dbq_r[8];
 #pragma unroll
@@ -283,20 +331,43 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
             // ---- G = dY (* relu mask): two bf16 terms, core (row group, term, column group) -----------------------------
 #pragma unroll
             for (int it = 0; it < ITG; ++it) {
-                asm volatile("cp.async.wait_group %0;" ::"n"(UNITS - 1) : "memory");
-                __syncwarp();  // every lane's copies of this slot have landed
-                const unsigned char *sg = raw_warp_p + it * 8 * 1024;
-                const float4 a0 = *reinterpret_cast<const float4 *>(sg + g_rd0), a1 = *reinterpret_cast<const float4 *>(sg + g_rd1);
+                float4 a0, a1, y0, y1;
+                if (TMA) {
+                    if (it == 0) {
+                        const bool w = bw_wait(rawg_full, n & 1u, abort_word);
+                        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    }
+                    const int ro = (mg_g0 + it * (32 / CGN)) * 8 * IBG;
+                    a0 = *reinterpret_cast<const float4 *>(raw + ro + tg_rd0);
+                    a1 = *reinterpret_cast<const float4 *>(raw + ro + tg_rd1);
+                    if (RELU) {
+                        y0 = *reinterpret_cast<const float4 *>(raw_y + ro + tg_rd0);
+                        y1 = *reinterpret_cast<const float4 *>(raw_y + ro + tg_rd1);
+                    }
+                    if (it == ITG - 1) {  // every lane holds its last unit of dY / y in registers: the buffers may be refilled
+                        __syncwarp();
+                        if (lane == 0) bw_arrive(rawg_empty);
+                    }
+                } else {
+                    asm volatile("cp.async.wait_group %0;" ::"n"(UNITS - 1) : "memory");
+                    __syncwarp();  // every lane's copies of this slot have landed
+                    const unsigned char *sg = raw_warp_p + it * 8 * 1024;
+                    a0 = *reinterpret_cast<const float4 *>(sg + g_rd0);
+                    a1 = *reinterpret_cast<const float4 *>(sg + g_rd1);
+                    if (RELU) {
+                        const unsigned char *sy = raw_warp_p + (y_slot0 + it) * 8 * 1024;
+                        y0 = *reinterpret_cast<const float4 *>(sy + g_rd0);
+                        y1 = *reinterpret_cast<const float4 *>(sy + g_rd1);
+                    }
+                    __syncwarp();  // every lane has read its part: the slot is free
+                    fetch_g(it);   // the next tile's data for this slot start their trip
+                }
                 float gv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
                 if (RELU) {
-                    const unsigned char *sy = raw_warp_p + (y_slot0 + it) * 8 * 1024;
-                    const float4 y0 = *reinterpret_cast<const float4 *>(sy + g_rd0), y1 = *reinterpret_cast<const float4 *>(sy + g_rd1);
                     const float yv[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
 #pragma unroll
                     for (int j = 0; j < 8; ++j) gv[j] = yv[j] > 0.f ? gv[j] : 0.f;
                 }
-                __syncwarp();  // every lane has read its part: the slot is free
-                fetch_g(it);   // the next tile's data for this slot start their trip
 #pragma unroll
                 for (int j = 0; j < 8; ++j) dbq_r[j] = __fadd_rn(dbq_r[j], gv[j]);
                 uint32_t hi[4], lo[4];
@@ -309,13 +380,29 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
             // ---- xq = round(x): two bf16 terms stacked along M of the transposed operand ---------------------------------
 #pragma unroll
             for (int it = 0; it < ITX; ++it) {
-                asm volatile("cp.async.wait_group %0;" ::"n"(UNITS - 1) : "memory");
-                __syncwarp();
-                const unsigned char *sx = raw_warp_p + (x_slot0 + it) * 8 * 1024;
-                const float4 a0 = *reinterpret_cast<const float4 *>(sx + x_rd0), a1 = *reinterpret_cast<const float4 *>(sx + x_rd1);
+                float4 a0, a1;
+                if (TMA) {
+                    if (it == 0) {
+                        const bool w = bw_wait(rawx_full, n & 1u, abort_word);
+                        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    }
+                    const int ro = (mg_x0 + it * (32 / CGK)) * 8 * IBX;
+                    a0 = *reinterpret_cast<const float4 *>(raw_x + ro + tx_rd0);
+                    a1 = *reinterpret_cast<const float4 *>(raw_x + ro + tx_rd1);
+                    if (it == ITX - 1) {
+                        __syncwarp();
+                        if (lane == 0) bw_arrive(rawx_empty);
+                    }
+                } else {
+                    asm volatile("cp.async.wait_group %0;" ::"n"(UNITS - 1) : "memory");
+                    __syncwarp();
+                    const unsigned char *sx = raw_warp_p + (x_slot0 + it) * 8 * 1024;
+                    a0 = *reinterpret_cast<const float4 *>(sx + x_rd0);
+                    a1 = *reinterpret_cast<const float4 *>(sx + x_rd1);
+                    __syncwarp();
+                    fetch_x(it);
+                }
                 float xv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                __syncwarp();
-                fetch_x(it);
                 const int mg = mg_x0 + it * (32 / CGK);
                 if (has_q) {
                     const uint32_t pr = (uint32_t)(mg * 8 + r8) % rp;
@@ -331,6 +418,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
                 *reinterpret_cast<uint4 *>(X + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                 *reinterpret_cast<uint4 *>(X + 8 * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
+            if (!ok) break;  // a wait inside the unit loops gave up
             f_row0 += tile_step;
             tc::fence_smem_to_async();
             __syncwarp();
@@ -400,6 +488,46 @@ __global__ void __launch_bounds__(kBwThreads, 1) k_qdense_bwd_ws(const BwParams 
                 }
                 tc::commit(stage_free);
                 tc::commit(acc_full + a);
+            }
+            __syncwarp();
+        }
+        if (!ok) {
+            *reinterpret_cast<volatile int *>(abort_word) = 1;
+            if (lane == 0 && P.status) atomicOr(P.status, kBwTimeout);
+        }
+    } else if (TMA && warp == kBwLoadWarp) {
+        // ================================ bulk-copy loader (TMA variant) ===========================================
+        // Keeps one raw tile in flight per stream: as soon as every producer warp has taken its units of dY / y (of x) out
+        // of the buffer, the copy engine fetches the next tile's into it.  The whole warp walks the loop (it stays
+        // converged for the tear-down barrier); lane 0 issues.
+        constexpr int IBG = (CGN >= 4 ? 128 : 64), IBX = (CGK >= 4 ? 128 : 64);
+        constexpr int g_stream_bytes = 128 * Np * 4, x_stream_bytes = 128 * Kp * 4;
+        const uint32_t raw_u = tc::smem_u32(raw);
+        const uint32_t rawy_u = raw_u + g_stream_bytes, rawx_u = raw_u + g_stream_bytes * (RELU ? 2 : 1);
+        const int g_boxes = (N + 31) / 32, x_boxes = (K + 31) / 32;  // a column half that lies past N / K is not fetched
+        uint32_t n = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++n) {
+            const int row0 = (int)(tile * kBwTileM);
+            if (n > 0) {
+                const bool w = bw_wait(rawg_empty, (n - 1) & 1u, abort_word);
+                if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+            }
+            if (lane == 0) {
+                bw_expect_tx(rawg_full, (uint32_t)(g_boxes * 128 * IBG * (RELU ? 2 : 1)));
+                for (int b = 0; b < g_boxes; ++b) {
+                    bw_tma_load_2d(raw_u + b * 128 * IBG, &map_g, b * 32, row0, rawg_full);
+                    if (RELU) bw_tma_load_2d(rawy_u + b * 128 * IBG, &map_y, b * 32, row0, rawg_full);
+                }
+            }
+            __syncwarp();
+            if (n > 0) {
+                const bool w = bw_wait(rawx_empty, (n - 1) & 1u, abort_word);
+                if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+            }
+            if (lane == 0) {
+                bw_expect_tx(rawx_full, (uint32_t)(x_boxes * 128 * IBX));
+                for (int b = 0; b < x_boxes; ++b) bw_tma_load_2d(rawx_u + b * 128 * IBX, &map_x, b * 32, row0, rawx_full);
             }
             __syncwarp();
         }
@@ -552,7 +680,50 @@ static size_t qdense_bwd_ws_smem(int Kp, int Np, int Kt, int rows_period, bool r
     const size_t g_bytes = 2 * (size_t)kBwTileM * Np * 2;
     const size_t raw = (size_t)(ITG * (relu ? 2 : 1) + ITX) * kBwProd * 32;
     const size_t tab = has_q ? ((size_t)rows_period * (Kt + 8) + 15) / 16 * 16 : 0;
-    return g_bytes + kBwXBytes + 3 * (size_t)Kp * Np * 2 + raw + (size_t)kBwEpiWarps * kBwOutWarpBytes + tab + 6 * 8 + 32;
+    const size_t operands = (g_bytes + kBwXBytes + 3 * (size_t)Kp * Np * 2 + 1023) / 1024 * 1024;  // the raw tiles start on a 1 KB boundary
+    return 1024 + operands + raw + (size_t)kBwEpiWarps * kBwOutWarpBytes + tab + 10 * 8 + 32;  // + room to align the carve itself
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point query (the library does not link against libcuda)
+typedef CUresult (*BwEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static BwEncodeTiledFn bw_encode_tiled_fn() {
+    static const BwEncodeTiledFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return (BwEncodeTiledFn) nullptr;
+        }
+        return (BwEncodeTiledFn)ptr;
+    }();
+    return fn;
+}
+
+// HGQ_QDENSE_BWD_TMA=0 / 1 in the environment picks how raw tiles are fetched (cooperative cp.async / bulk tensor copies).
+static bool bw_tma_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("HGQ_QDENSE_BWD_TMA");
+        return v != nullptr ? v[0] != '0' : true;
+    }();
+    return on;
+}
+
+// A tensor map over a row-major fp32 matrix [rows, cols] with row stride ld floats (this GPU's memory only): boxes of 128
+// rows x min(32, padded columns) floats, swizzled over the box's row length (128 or 64 bytes), zeros outside.
+static bool bw_make_tmap(CUtensorMap *map, const float *base, int64_t rows, int cols, int64_t ld, int padded_cols) {
+    const BwEncodeTiledFn enc = bw_encode_tiled_fn();
+    if (enc == nullptr || base == nullptr) return false;
+    const cuuint32_t inner = padded_cols >= 32 ? 32u : 16u;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    const cuuint32_t box[2] = {inner, (cuuint32_t)kBwTileM};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               inner == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Launches the warp-specialised backward when it covers the call: returns 1 with the number of partial records in
@@ -578,15 +749,25 @@ int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const f
     *records = 2 * g;
     const int cgn = Np / 8, cgk = Kp / 8;
     const bool relu = y != nullptr, conv = round_mode == RM_RND_CONV;
+    // bulk tensor copies: not for a dY that repeats rows (no tiled description), and rows must fit a 32-bit coordinate
+    CUtensorMap map_g, map_y, map_x;
+    memset(&map_g, 0, sizeof(map_g)); memset(&map_y, 0, sizeof(map_y)); memset(&map_x, 0, sizeof(map_x));
+    const bool tma = bw_tma_enabled() && gy_repeat == 1 && M < ((int64_t)1 << 31) && bw_make_tmap(&map_g, gy, M, N, N, Np) &&
+                     (!relu || bw_make_tmap(&map_y, y, M, N, N, Np)) && bw_make_tmap(&map_x, x, M, K, ldx, Kp);
     cudaError_t ce = cudaSuccess;
     bool launched = false;
-#define HGQ_BW_CASE(CV_, CGN_, CGK_, RELU_)                                                                                  \
-    if (!launched && conv == CV_ && cgn == CGN_ && cgk == CGK_ && relu == RELU_) {                                           \
-        ce = cudaFuncSetAttribute(k_qdense_bwd_ws<CV_, CGN_, CGK_, RELU_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+#define HGQ_BW_CASE1(CV_, CGN_, CGK_, RELU_, TMA_)                                                                           \
+    do {                                                                                                                    \
+        ce = cudaFuncSetAttribute(k_qdense_bwd_ws<CV_, CGN_, CGK_, RELU_, TMA_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                   (int)smem);                                                                               \
         if (ce != cudaSuccess) return -(int)ce;                                                                             \
-        k_qdense_bwd_ws<CV_, CGN_, CGK_, RELU_><<<g, kBwThreads, smem, st>>>(p);                                            \
+        k_qdense_bwd_ws<CV_, CGN_, CGK_, RELU_, TMA_><<<g, kBwThreads + (TMA_ ? 32 : 0), smem, st>>>(p, map_g, map_y, map_x); \
         launched = true;                                                                                                    \
+    } while (0)
+#define HGQ_BW_CASE(CV_, CGN_, CGK_, RELU_)                                                                                  \
+    if (!launched && conv == CV_ && cgn == CGN_ && cgk == CGK_ && relu == RELU_) {                                           \
+        if (tma) HGQ_BW_CASE1(CV_, CGN_, CGK_, RELU_, true);                                                                 \
+        else HGQ_BW_CASE1(CV_, CGN_, CGK_, RELU_, false);                                                                    \
     }
 #define HGQ_BW_SHAPES(CV_, RELU_)                                                                                           \
     HGQ_BW_CASE(CV_, 2, 2, RELU_) HGQ_BW_CASE(CV_, 2, 4, RELU_) HGQ_BW_CASE(CV_, 2, 8, RELU_)                               \
@@ -598,6 +779,7 @@ int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const f
     HGQ_BW_SHAPES(true, true)
 #undef HGQ_BW_SHAPES
 #undef HGQ_BW_CASE
+#undef HGQ_BW_CASE1
     if (!launched) return 0;
     return 1;
 }
