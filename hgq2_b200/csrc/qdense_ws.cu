@@ -62,6 +62,7 @@ struct WsParams {
     int K, N, Kpad, Npad, Kt, rows_period;
     int rm, act;
     int depth;            // raw slabs in flight ahead of the conversion: 1 or 2
+    int tma_store;        // the epilogue hands finished 128 x 32 blocks to the copy engine (tiled bulk-tensor stores)
 };
 
 __device__ __forceinline__ void ws_arrive(uint64_t *bar) {
@@ -108,11 +109,35 @@ __device__ __forceinline__ void ws_tma_load_2d(uint32_t dst, const CUtensorMap *
                  : "memory");
 }
 
+// One tiled 2-D bulk copy shared -> global; rows / columns outside the tensor are not written.
+__device__ __forceinline__ void ws_tma_store_2d(const CUtensorMap *map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1), "r"(src)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// Barrier of `count` threads that also ANDs a predicate over them: every participant learns whether all of them are fine.
+__device__ __forceinline__ bool ws_bar_and(int id, int count, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %3, 0;\n\t"
+        "bar.red.and.pred q, %1, %2, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t"
+        "}\n"
+        : "=r"(r)
+        : "r"(id), "r"(count), "r"(pred ? 1u : 0u)
+        : "memory");
+    return r != 0;
+}
+
 __device__ __forceinline__ int ws_swz(int r, int C) { return C == 8 ? (r & 7) : (C == 4 ? ((r >> 1) & 3) : ((r >> 2) & 1)); }
 
 template <bool RCONV, int AMAX, int NPW, int EW, bool TMA>
 __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qdense_fwd_ws(const WsParams P,
-                                                                                       const __grid_constant__ CUtensorMap tmap) {
+                                                                                       const __grid_constant__ CUtensorMap tmap,
+                                                                                       const __grid_constant__ CUtensorMap tmap_y) {
     constexpr int kWsProdWarps = NPW, kWsProd = NPW * 32, kWsEpiWarps = EW, kWsIssueWarp = NPW + EW;
     constexpr int kWsLoadWarp = NPW + EW + 1;  // TMA only
     constexpr int kWsThreads = (NPW + EW + 1 + (TMA ? 1 : 0)) * 32;
@@ -474,10 +499,23 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
         const bool vec_out = (N % 4 == 0) && aligned(P.y, 16);
         uint32_t ti = 0;
         bool ok = true;
+        // With bulk stores (tma_store, wc = 32): the four warps that share `part` fill one 128-row x 32-column block in
+        // shared memory (128-byte rows, 16-byte chunks XOR-swizzled with the row) and one of their threads hands it to the
+        // copy engine; a block is reused once the previous store has read it.  The four warps meet at a named barrier that
+        // also carries each warp's wait outcome, so that all of them leave the loop together if a wait gave up.
+        const bool tstore = P.tma_store != 0;
+        unsigned char *box = outst + part * 16384;
+        const bool leader = (q == 0 && lane == 0);
+        const int row_t = q * 32 + lane;
         for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++ti) {
             const uint32_t a = ti & 1u, ause = ti >> 1;
-            const bool w = ws_wait(acc_full + a, ause & 1u, abort_word);
-            if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+            bool w = ws_wait(acc_full + a, ause & 1u, abort_word);
+            w = __all_sync(0xffffffffu, w);
+            if (tstore) {
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the block's last store has read it
+                w = ws_bar_and(3 + part, 128, w);
+            }
+            if (!w) { ok = false; break; }
             tc::fence_after_sync();
             const int64_t wrow0 = tile * kWsTileM + q * 32;  // first row of this warp
             const int rows_w = (int)((P.M - wrow0) < 32 ? ((P.M - wrow0) < 0 ? 0 : (P.M - wrow0)) : 32);
@@ -491,6 +529,24 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
                     tc::fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ws_arrive(acc_empty + a);
+                }
+                if (tstore) {
+                    if (c0 != part * wc) {  // a later piece of the same tile: wait for the store of the previous one
+                        if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        asm volatile("bar.sync %0, 128;" ::"r"(3 + part) : "memory");
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 b = *reinterpret_cast<const float4 *>(bias_s + c0 + j);
+                        float4 o;
+                        o.x = fmaxf(__fadd_rn(v[j], b.x), act_lo); o.y = fmaxf(__fadd_rn(v[j + 1], b.y), act_lo);
+                        o.z = fmaxf(__fadd_rn(v[j + 2], b.z), act_lo); o.w = fmaxf(__fadd_rn(v[j + 3], b.w), act_lo);
+                        *reinterpret_cast<float4 *>(box + row_t * 128 + (((j >> 2) ^ (lane & 7)) << 4)) = o;
+                    }
+                    tc::fence_smem_to_async();
+                    asm volatile("bar.sync %0, 128;" ::"r"(3 + part) : "memory");
+                    if (leader) ws_tma_store_2d(&tmap_y, c0, (int)(tile * kWsTileM), tc::smem_u32(box));
+                    continue;
                 }
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
@@ -531,6 +587,7 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
                 __syncwarp();  // the transposition buffer is reused by the next piece / the next tile
             }
         }
+        if (tstore && leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every store of this CTA has landed
         if (!ok) {
             *reinterpret_cast<volatile int *>(abort_word) = 1;
             if (lane == 0 && P.status) atomicOr(P.status, kWsTimeout);
@@ -571,6 +628,15 @@ static EncodeTiledFn encode_tiled_fn() {
 static bool ws_tma_enabled() {
     static const bool on = [] {
         const char *v = getenv("HGQ_QDENSE_TMA");
+        return v != nullptr ? v[0] != '0' : true;  // measured faster on every layer shape of the training workloads
+    }();
+    return on;
+}
+
+// HGQ_QDENSE_TMA_STORE=0 / 1: the epilogue writes y through its transposition buffers / through bulk tensor stores.
+static bool ws_tma_store_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("HGQ_QDENSE_TMA_STORE");
         return v != nullptr ? v[0] != '0' : true;  // measured faster on every layer shape of the training workloads
     }();
     return on;
@@ -629,6 +695,12 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
     memset(&tmap, 0, sizeof(tmap));
     // the bulk copies want x 16-byte aligned with rows a multiple of 16 bytes (K % 4 == 0, checked above)
     const bool tma = ws_tma_enabled() && M < ((int64_t)1 << 31) && ws_make_tmap(&tmap, x, M, K);
+    CUtensorMap tmap_y;
+    memset(&tmap_y, 0, sizeof(tmap_y));
+    // bulk stores of 128 x 32 blocks: y rows a multiple of 16 bytes, 32 columns per epilogue warp (padded N >= 64)
+    const bool tstore = ws_tma_store_enabled() && N % 4 == 0 && aligned(y, 16) && Npad / (ew / 4) >= 32 && M < ((int64_t)1 << 31) &&
+                        ws_make_tmap(&tmap_y, y, M, N);
+    p.tma_store = tstore ? 1 : 0;
     smem += 1024;  // room to start the carve on a 1 KB boundary whatever the base of dynamic shared memory is
     if (smem > 227 * 1024) return 0;
 #define HGQ_WS_LAUNCH1(CV, AM, PW, EWW, TM)                                                                                      \
@@ -636,7 +708,7 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
         cudaError_t ce = cudaFuncSetAttribute(k_qdense_fwd_ws<CV, AM, PW, EWW, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                               (int)smem);                                                                       \
         if (ce != cudaSuccess) return -(int)ce;                                                                                 \
-        k_qdense_fwd_ws<CV, AM, PW, EWW, TM><<<g, (PW + EWW + 1 + (TM ? 1 : 0)) * 32, smem, st>>>(p, tmap);                      \
+        k_qdense_fwd_ws<CV, AM, PW, EWW, TM><<<g, (PW + EWW + 1 + (TM ? 1 : 0)) * 32, smem, st>>>(p, tmap, tmap_y);                      \
     } while (0)
 #define HGQ_WS_LAUNCH(CV, AM, PW, EWW)                 \
     do {                                               \

@@ -249,3 +249,19 @@ def test_general_backward_kernel_on_the_same_cases():
                         '-k', 'backward and not general', '-p', 'no:cacheprovider'],
                        cwd=root, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_cp_async_variants_on_the_same_cases():
+    # HGQ_QDENSE_TMA=0 / HGQ_QDENSE_BWD_TMA=0 / HGQ_QDENSE_TMA_STORE=0 (read once per process) keep the warp-specialised kernels
+    # on their cp.async fetch and their transposition-buffer stores instead of the bulk tensor copies: forward and backward cases run again in a child process, so that both ways
+    # of fetching stay covered by the same references
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, HGQ_QDENSE_TMA='0', HGQ_QDENSE_BWD_TMA='0', HGQ_QDENSE_TMA_STORE='0')
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, '-m', 'pytest', os.path.join(root, 'tests', 'test_qdense_gpu.py'), '-q', '-x', '-m', 'gpu',
+                        '-k', 'not general and not cp_async', '-p', 'no:cacheprovider'],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
