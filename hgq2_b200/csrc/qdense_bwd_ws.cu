@@ -59,6 +59,7 @@ struct BwParams {
     int rows_period, rm, relu, want_df;
     int gy_repeat;
     FastDiv gy_div;
+    int g_box_rows;     // TMA variant: rows of dY one tile needs (128, or 128 / gy_repeat, at least 1, when dY repeats rows)
 };
 
 __device__ __forceinline__ void bw_arrive(uint64_t *bar) {
@@ -338,8 +339,19 @@ __global__ void __launch_bounds__(kBwThreads + (TMA ? 32 : 0), 1) k_qdense_bwd_w
                         if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
                     }
                     const int ro = (mg_g0 + it * (32 / CGN)) * 8 * IBG;
-                    a0 = *reinterpret_cast<const float4 *>(raw + ro + tg_rd0);
-                    a1 = *reinterpret_cast<const float4 *>(raw + ro + tg_rd1);
+                    if (P.gy_repeat > 1) {
+                        // dY repeats rows (gy_repeat is a multiple of 8): the 8 rows of a unit share one stored row, jr of the
+                        // g_box_rows rows fetched for this tile; every lane of a quarter-warp reads the same 32 bytes
+                        const int jr = ((mg_g0 + it * (32 / CGN)) * 8 / P.gy_repeat) % P.g_box_rows;
+                        const int base = (kg_g >> 2) * (P.g_box_rows * IBG) + jr * IBG;
+                        // the swizzle is a function of the shared-memory address (the raw tiles start on a 1 KB boundary)
+                        const int sw = (IBG == 128) ? ((base >> 7) & 7) : ((base >> 7) & 3);
+                        a0 = *reinterpret_cast<const float4 *>(raw + base + ((((kg_g & 3) * 2) ^ sw) * 16));
+                        a1 = *reinterpret_cast<const float4 *>(raw + base + ((((kg_g & 3) * 2 + 1) ^ sw) * 16));
+                    } else {
+                        a0 = *reinterpret_cast<const float4 *>(raw + ro + tg_rd0);
+                        a1 = *reinterpret_cast<const float4 *>(raw + ro + tg_rd1);
+                    }
                     if (RELU) {
                         y0 = *reinterpret_cast<const float4 *>(raw_y + ro + tg_rd0);
                         y1 = *reinterpret_cast<const float4 *>(raw_y + ro + tg_rd1);
@@ -514,9 +526,11 @@ __global__ void __launch_bounds__(kBwThreads + (TMA ? 32 : 0), 1) k_qdense_bwd_w
                 if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
             }
             if (lane == 0) {
-                bw_expect_tx(rawg_full, (uint32_t)(g_boxes * 128 * IBG * (RELU ? 2 : 1)));
+                const int R = P.g_box_rows;  // 128 unless dY repeats rows
+                const int grow0 = (P.gy_repeat > 1) ? (int)(tile * kBwTileM / P.gy_repeat) : row0;
+                bw_expect_tx(rawg_full, (uint32_t)(g_boxes * IBG * (R + (RELU ? 128 : 0))));
                 for (int b = 0; b < g_boxes; ++b) {
-                    bw_tma_load_2d(raw_u + b * 128 * IBG, &map_g, b * 32, row0, rawg_full);
+                    bw_tma_load_2d(raw_u + b * R * IBG, &map_g, b * 32, grow0, rawg_full);
                     if (RELU) bw_tma_load_2d(rawy_u + b * 128 * IBG, &map_y, b * 32, row0, rawg_full);
                 }
             }
@@ -713,13 +727,14 @@ static bool bw_tma_enabled() {
 
 // A tensor map over a row-major fp32 matrix [rows, cols] with row stride ld floats (this GPU's memory only): boxes of 128
 // rows x min(32, padded columns) floats, swizzled over the box's row length (128 or 64 bytes), zeros outside.
-static bool bw_make_tmap(CUtensorMap *map, const float *base, int64_t rows, int cols, int64_t ld, int padded_cols) {
+static bool bw_make_tmap(CUtensorMap *map, const float *base, int64_t rows, int cols, int64_t ld, int padded_cols,
+                         int box_rows = kBwTileM) {
     const BwEncodeTiledFn enc = bw_encode_tiled_fn();
     if (enc == nullptr || base == nullptr) return false;
     const cuuint32_t inner = padded_cols >= 32 ? 32u : 16u;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-    const cuuint32_t box[2] = {inner, (cuuint32_t)kBwTileM};
+    const cuuint32_t box[2] = {inner, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                inner == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -749,10 +764,15 @@ int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const f
     *records = 2 * g;
     const int cgn = Np / 8, cgk = Kp / 8;
     const bool relu = y != nullptr, conv = round_mode == RM_RND_CONV;
-    // bulk tensor copies: not for a dY that repeats rows (no tiled description), and rows must fit a 32-bit coordinate
+    // bulk tensor copies: rows must fit a 32-bit coordinate; a dY that repeats rows (the gradient of a sum over an axis) has a
+    // tiled description when a group of 8 rows shares one stored row and a tile covers whole stored rows
     CUtensorMap map_g, map_y, map_x;
     memset(&map_g, 0, sizeof(map_g)); memset(&map_y, 0, sizeof(map_y)); memset(&map_x, 0, sizeof(map_x));
-    const bool tma = bw_tma_enabled() && gy_repeat == 1 && M < ((int64_t)1 << 31) && bw_make_tmap(&map_g, gy, M, N, N, Np) &&
+    const bool rep_ok = gy_repeat == 1 || (gy_repeat % 8 == 0 && M % gy_repeat == 0 &&
+                                           ((gy_repeat <= kBwTileM && kBwTileM % gy_repeat == 0) || gy_repeat % kBwTileM == 0));
+    p.g_box_rows = gy_repeat == 1 ? kBwTileM : (gy_repeat >= kBwTileM ? 1 : kBwTileM / gy_repeat);
+    const bool tma = bw_tma_enabled() && rep_ok && M < ((int64_t)1 << 31) &&
+                     bw_make_tmap(&map_g, gy, M / gy_repeat, N, N, Np, p.g_box_rows) &&
                      (!relu || bw_make_tmap(&map_y, y, M, N, N, Np)) && bw_make_tmap(&map_x, x, M, K, ldx, Kp);
     cudaError_t ce = cudaSuccess;
     bool launched = false;
