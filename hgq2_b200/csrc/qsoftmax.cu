@@ -18,6 +18,8 @@
 // by the warp lanes of the CTA that handles that table row for a range of batches.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "hgq_common.cuh"
 #include "hgq_math.cuh"
 
@@ -87,20 +89,27 @@ __device__ __forceinline__ QC load_q(const SQuant &q) {
     return make_qc(kf, i, f, q.rm, q.om);
 }
 
+// Mode knowledge at compile time.  CL: 0 = the quantizer only rounds, 1 = it clips, 2 = decided at run time (launch-uniform
+// flag).  FL: every quantizer rounds by floor(x 2^f + bias) (RND: bias 1/2, TRN: bias 0); otherwise round-half-even is
+// selected at run time.
+template <bool FL>
 __device__ __forceinline__ float qc_round(float x, const QC &c) {
     const float xs = __fmul_rn(x, c.s);
-    const float q = c.conv ? rintf(xs) : floorf(__fadd_rn(xs, c.rbias));
+    const float q = (!FL && c.conv) ? rintf(xs) : floorf(__fadd_rn(xs, c.rbias));
     return __fmul_rn(q, c.inv);
 }
+template <int CL, bool FL>
 __device__ __forceinline__ float qc_fwd(float x, const QC &c, float &rounded) {
-    rounded = qc_round(x, c);
-    return clipf(rounded, c.lo, c.hi);
+    rounded = qc_round<FL>(x, c);
+    if (CL == 0) return rounded;
+    return clipf(rounded, c.lo, c.hi);  // +-inf bounds when a run-time quantizer only rounds
 }
 // same arithmetic as quantize_grad<> in hgq_math.cuh, with the mode folded into the constants; xq = qc_round(x, c) is
 // passed in by callers that already have it from the forward chain
+template <int CL>
 __device__ __forceinline__ void qc_bwd_r(float g, float x, float xq, const QC &c, float &dx, float &di, float &df) {
     const float df_r = __fmul_rn(__fmul_rn(__fsub_rn(xq, x), -kLn2), g);
-    if (!c.clips) {  // rounding only: straight-through value gradient, no integer-bit gradient
+    if (CL == 0 || (CL == 2 && !c.clips)) {  // rounding only: straight-through value gradient, no integer-bit gradient
         dx = g;
         di = 0.f;
         df = df_r;
@@ -116,13 +125,27 @@ __device__ __forceinline__ void qc_bwd_r(float g, float x, float xq, const QC &c
     di = c.sym ? __fmul_rn(m, c.ci) : __fadd_rn(__fmul_rn(ghi, c.ci), __fmul_rn(glo, c.ci));
     df = __fadd_rn(pass ? df_r : 0.f, __fmul_rn(c.sym ? m : ghi, c.cf));
 }
-__device__ __forceinline__ void qc_bwd(float g, float x, const QC &c, float &dx, float &di, float &df) {
-    qc_bwd_r(g, x, qc_round(x, c), c, dx, di, df);
-}
+
+// Kernel variants: 0 = every mode decided at run time; 1 / 2 = the training set-up of the layer (every quantizer rounds
+// by floor; the two table outputs Q2 and Q4 saturate; Q3 and Q5, WRAP quantizers, only round), with Q1 only rounding (1)
+// or saturating (2).
+template <int V> struct Modes {
+    static constexpr bool FL = V != 0;
+    static constexpr int C1 = V == 0 ? 2 : (V == 2 ? 1 : 0);
+    static constexpr int C2 = V == 0 ? 2 : 1;
+    static constexpr int C3 = V == 0 ? 2 : 0;
+    static constexpr int C4 = C2;
+    static constexpr int C5 = C3;
+};
 
 template <int VE>
 __device__ __forceinline__ void load_row(const float *p, int lane, float (&v)[VE]) {
-    if (VE == 4) {
+    if (VE == 8) {
+        float t[8];
+        ldcs8(p + lane * 8, t);
+#pragma unroll
+        for (int j = 0; j < VE; ++j) v[j] = t[j];
+    } else if (VE == 4) {
         const float4 t = __ldcs(reinterpret_cast<const float4 *>(p) + lane);
         v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     } else if (VE == 2) {
@@ -135,138 +158,176 @@ __device__ __forceinline__ void load_row(const float *p, int lane, float (&v)[VE
 
 template <int VE>
 __device__ __forceinline__ void store_row(float *p, int lane, const float (&v)[VE]) {
-    if (VE == 4) __stcs(reinterpret_cast<float4 *>(p) + lane, make_float4(v[0], v[1], v[2], v[3]));
+    if (VE == 8) {
+        float t[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = v[j < VE ? j : 0];
+        stcs8(p + lane * 8, t);
+    } else if (VE == 4) __stcs(reinterpret_cast<float4 *>(p) + lane, make_float4(v[0], v[1], v[2], v[3]));
     else if (VE == 2) __stcs(reinterpret_cast<float2 *>(p) + lane, make_float2(v[0], v[1]));
     else __stcs(p + lane, v[0]);
 }
 
-__device__ __forceinline__ float warp_max(float v) {
+// Reductions over the LPR lanes that share a row (LPR = 32: the warp; 16: each half of it holds a row of its own).
+// Fixed butterflies: every lane of the row ends with the same value.
+template <int LPR>
+__device__ __forceinline__ float row_max(float v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    for (int o = LPR / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
-__device__ __forceinline__ float warp_sum(float v) {  // fixed butterfly: every lane ends with the same value
+template <int LPR>
+__device__ __forceinline__ float row_sum(float v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    for (int o = LPR / 2; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+template <int LPR>
+__device__ __forceinline__ int row_sum_int(int v) {
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
 
 // Forward chain of one row.  Fills b[] (quantised exponentials), returns u and the intermediate scalars.
-template <int VE>
+template <int VE, int LPR, int V>
 __device__ __forceinline__ void chain_fwd(const SmParams &P, const QC &q1, const QC &q2, const QC &q3, const QC &q4,
-                                          const float (&s)[VE], float (&a)[VE], float (&e)[VE], float (&b)[VE], float &m,
-                                          float &S, float &t, float &t_rounded, float &v, float &u, float (&ra)[VE],
-                                          float (&rb)[VE], float &u_rounded) {
+                                          const float (&s)[VE], float (&e)[VE], float (&b)[VE], float &m, float &S,
+                                          float &t_rounded, float &v, float &u, float (&ra)[VE], float (&rb)[VE],
+                                          float &u_rounded) {
+    using Mo = Modes<V>;
     float mx = kNegInf;
 #pragma unroll
     for (int j = 0; j < VE; ++j) mx = fmaxf(mx, s[j]);
-    m = warp_max(mx);
+    m = row_max<LPR>(mx);
     float part = 0.f;
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
-        a[j] = qc_fwd(__fsub_rn(m, s[j]), q1, ra[j]);
-        e[j] = expf(__fmul_rn(-a[j], P.scaler));
-        b[j] = qc_fwd(e[j], q2, rb[j]);
+        const float a = qc_fwd<Mo::C1, Mo::FL>(__fsub_rn(m, s[j]), q1, ra[j]);
+        e[j] = expf(__fmul_rn(-a, P.scaler));
+        b[j] = qc_fwd<Mo::C2, Mo::FL>(e[j], q2, rb[j]);
         part = __fadd_rn(part, b[j]);
     }
-    S = warp_sum(part);
-    t = qc_fwd(S, q3, t_rounded);
+    S = row_sum<LPR>(part);
+    const float t = qc_fwd<Mo::C3, Mo::FL>(S, q3, t_rounded);
     v = __fdiv_rn(1.f, __fadd_rn(t, P.eps));
-    u = qc_fwd(v, q4, u_rounded);
+    u = qc_fwd<Mo::C4, Mo::FL>(v, q4, u_rounded);
 }
 
-// grid = (rows_period, splits); CTA (p, sp) handles table row p for the batches sp, sp + splits, ... (warp w takes every
-// 8th of those), so the Q5 statistics of row p are owned by this CTA's lanes.
 template <int VE>
-__global__ void __launch_bounds__(kSmWarps * 32) k_qsoftmax_fwd(const SmParams P) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int p = blockIdx.x, sp = blockIdx.y, L = P.L;
-    const QC q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
-    QC q5[VE];
+__device__ __forceinline__ void load_q5(const SmParams &P, int p, int col0, QC (&q5)[VE]) {
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
-        const int c = p * L + lane * VE + j;
+        const int c = p * P.L + col0 + j;
         q5[j] = make_qc((P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c), (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c),
                         __ldg(P.f5 + c), P.rm5, P.om5);
     }
+}
+
+// grid = (rows_period, splits); CTA (p, sp) handles table row p for the batches sp, sp + splits, ...: row-group g of the CTA
+// (8 warps x 32 / LPR rows per warp) takes every (8 * 32 / LPR)-th of those, so the Q5 statistics of table row p are owned
+// by this CTA's lanes.  A row-group without a batch left repeats the first group's row of its warp and discards the result.
+template <int VE, int LPR, int V>
+__global__ void __launch_bounds__(kSmWarps * 32, VE == 8 ? 3 : 1) k_qsoftmax_fwd(const SmParams P) {
+    using Mo = Modes<V>;
+    constexpr int RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rl = lane % LPR, sub = lane / LPR;
+    const int p = blockIdx.x, sp = blockIdx.y, L = P.L;
+    const QC q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
+    QC q5[VE];
+    load_q5<VE>(P, p, rl * VE, q5);
     float am5[VE], am3 = 0.f, am1 = 0.f;
 #pragma unroll
     for (int j = 0; j < VE; ++j) am5[j] = 0.f;
-    for (int64_t bt = (int64_t)sp + (int64_t)warp * P.splits; bt < P.batches; bt += (int64_t)P.splits * kSmWarps) {
-        const int64_t row = bt * P.rows_period + p;
-        float s[VE], a[VE], e[VE], b[VE], y[VE];
-        load_row<VE>(P.s + row * L, lane, s);
-        float m, S, t, tr, v, u, ur, ra[VE], rb[VE];
-        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u, ra, rb, ur);
-        am3 = fmaxf(am3, fabsf(tr));
+    const int64_t step = (int64_t)P.splits * kSmWarps * RPW;
+    for (int64_t bt0 = (int64_t)sp + (int64_t)(warp * RPW) * P.splits; bt0 < P.batches; bt0 += step) {
+        const int64_t mine = bt0 + (int64_t)sub * P.splits;
+        const bool valid = mine < P.batches;
+        const int64_t row = (valid ? mine : bt0) * P.rows_period + p;
+        float s[VE], e[VE], b[VE], y[VE];
+        load_row<VE>(P.s + row * L, rl, s);
+        float m, S, tr, v, u, ur, ra[VE], rb[VE];
+        chain_fwd<VE, LPR, V>(P, q1, q2, q3, q4, s, e, b, m, S, tr, v, u, ra, rb, ur);
+        if (valid) {
+            am3 = fmaxf(am3, fabsf(tr));
 #pragma unroll
-        for (int j = 0; j < VE; ++j) {
-            float r;
-            am1 = fmaxf(am1, fabsf(ra[j]));
-            y[j] = qc_fwd(__fmul_rn(b[j], u), q5[j], r);
-            am5[j] = fmaxf(am5[j], fabsf(r));
+            for (int j = 0; j < VE; ++j) {
+                float r;
+                am1 = fmaxf(am1, fabsf(ra[j]));
+                y[j] = qc_fwd<Mo::C5, Mo::FL>(__fmul_rn(b[j], u), q5[j], r);
+                am5[j] = fmaxf(am5[j], fabsf(r));
+            }
+            store_row<VE>(P.y + row * L, rl, y);
         }
-        store_row<VE>(P.y + row * L, lane, y);
     }
     if (P.amax5 != nullptr) {
 #pragma unroll
-        for (int j = 0; j < VE; ++j) atomicMax(P.amax5 + p * L + lane * VE + j, __float_as_uint(am5[j]));
+        for (int j = 0; j < VE; ++j) atomicMax(P.amax5 + p * L + rl * VE + j, __float_as_uint(am5[j]));
     }
-    if (P.amax3 != nullptr && lane == 0) atomicMax(P.amax3, __float_as_uint(am3));
+    if (P.amax3 != nullptr && rl == 0) atomicMax(P.amax3, __float_as_uint(am3));
     if (P.amax1 != nullptr) {
-        am1 = warp_max(am1);
+        am1 = row_max<32>(am1);
         if (lane == 0) atomicMax(P.amax1, __float_as_uint(am1));
     }
 }
 
-// Four resident CTAs (64 registers per thread): the per-row dependency chains (five warp reductions, exp, divide) need
-// many warps to hide; measured 1.46 ms at two CTAs, 1.22 at three, 1.16 at four for 134 M scores.
-template <int VE>
-__global__ void __launch_bounds__(kSmWarps * 32, 4) k_qsoftmax_bwd(const SmParams P) {
+// Resident CTAs: the per-row dependency chains (reductions, exp, divide) need many warps to hide; measured on 134 M
+// scores with a warp per row: 1.46 ms at two CTAs per SM, 1.22 at three, 1.16 at four.  With eight scores per lane the
+// chain of a lane is long enough by itself: two CTAs without spills (0.69 ms) beat three with spills (0.70).
+template <int VE, int LPR, int V>
+__global__ void __launch_bounds__(kSmWarps * 32, VE == 8 ? 2 : 4) k_qsoftmax_bwd(const SmParams P) {
+    using Mo = Modes<V>;
+    constexpr int RPW = 32 / LPR;
+    constexpr int LL = VE * LPR;  // = L
     __shared__ float red[kSmWarps][8];
-    __shared__ float red5[kSmWarps][2][128];
+    __shared__ float red5[kSmWarps * RPW][2][LL];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rl = lane % LPR, sub = lane / LPR;
     const int p = blockIdx.x, sp = blockIdx.y, L = P.L;
     const QC q1 = load_q(P.q1), q2 = load_q(P.q2), q3 = load_q(P.q3), q4 = load_q(P.q4);
     QC q5[VE];
-#pragma unroll
-    for (int j = 0; j < VE; ++j) {
-        const int c = p * L + lane * VE + j;
-        q5[j] = make_qc((P.om5 == OM_NONE) ? 0.f : (float)__ldg(P.k5 + c), (P.om5 == OM_NONE) ? 0.f : __ldg(P.i5 + c),
-                        __ldg(P.f5 + c), P.rm5, P.om5);
-    }
-    float acc[8];  // di1, df1, di2, df2, di3, df3, di4, df4 (per thread; the per-row scalars are added by lane 0 only)
+    load_q5<VE>(P, p, rl * VE, q5);
+    float acc[8];  // di1, df1, di2, df2, di3, df3, di4, df4 (per thread; the per-row scalars are added by one lane per row)
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     float adf5[VE], adi5[VE];
 #pragma unroll
     for (int j = 0; j < VE; ++j) adf5[j] = adi5[j] = 0.f;
 
-    for (int64_t bt = (int64_t)sp + (int64_t)warp * P.splits; bt < P.batches; bt += (int64_t)P.splits * kSmWarps) {
-        const int64_t row = bt * P.rows_period + p;
-        float s[VE], g[VE], a[VE], e[VE], b[VE];
-        load_row<VE>(P.s + row * L, lane, s);
-        load_row<VE>(P.gy + row * L, lane, g);
-        float m, S, t, tr, v, u, ur, ra[VE], rb[VE];
-        chain_fwd<VE>(P, q1, q2, q3, q4, s, a, e, b, m, S, t, tr, v, u, ra, rb, ur);
+    const int64_t step = (int64_t)P.splits * kSmWarps * RPW;
+    for (int64_t bt0 = (int64_t)sp + (int64_t)(warp * RPW) * P.splits; bt0 < P.batches; bt0 += step) {
+        const int64_t mine = bt0 + (int64_t)sub * P.splits;
+        const bool valid = mine < P.batches;
+        const int64_t row = (valid ? mine : bt0) * P.rows_period + p;
+        float s[VE], g[VE], e[VE], b[VE];
+        load_row<VE>(P.s + row * L, rl, s);
+        load_row<VE>(P.gy + row * L, rl, g);
+        if (!valid) {
+#pragma unroll
+            for (int j = 0; j < VE; ++j) g[j] = 0.f;  // a zero upstream gradient: every contribution below is +-0
+        }
+        float m, S, tr, v, u, ur, ra[VE], rb[VE];
+        chain_fwd<VE, LPR, V>(P, q1, q2, q3, q4, s, e, b, m, S, tr, v, u, ra, rb, ur);
         // y = Q5(b u): gradient to z, Q5's own parameters
         float gb[VE], gu_part = 0.f;
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
             float gz, di, df;
-            qc_bwd(g[j], __fmul_rn(b[j], u), q5[j], gz, di, df);
+            const float z = __fmul_rn(b[j], u);
+            qc_bwd_r<Mo::C5>(g[j], z, qc_round<Mo::FL>(z, q5[j]), q5[j], gz, di, df);
             adf5[j] = __fadd_rn(adf5[j], df);
-            adi5[j] = __fadd_rn(adi5[j], di);
+            if (Mo::C5 != 0) adi5[j] = __fadd_rn(adi5[j], di);
             gb[j] = __fmul_rn(gz, u);
-            gu_part = __fadd_rn(gu_part, __fmul_rn(gz, b[j]));
+            gu_part = fmaf(gz, b[j], gu_part);
         }
-        const float gu = warp_sum(gu_part);
-        // u = Q4(v), v = 1 / (t + eps), t = Q3(S): row scalars, identical on every lane
+        const float gu = row_sum<LPR>(gu_part);
+        // u = Q4(v), v = 1 / (t + eps), t = Q3(S): row scalars, identical on every lane of the row
         float gv, di4, df4, gS, di3, df3;
-        qc_bwd_r(gu, v, ur, q4, gv, di4, df4);
+        qc_bwd_r<Mo::C4>(gu, v, ur, q4, gv, di4, df4);
         const float gt = __fmul_rn(-gv, __fmul_rn(v, v));
-        qc_bwd_r(gt, S, tr, q3, gS, di3, df3);
-        if (lane == 0) {
+        qc_bwd_r<Mo::C3>(gt, S, tr, q3, gS, di3, df3);
+        if (rl == 0) {
             acc[4] = __fadd_rn(acc[4], di3); acc[5] = __fadd_rn(acc[5], df3);
             acc[6] = __fadd_rn(acc[6], di4); acc[7] = __fadd_rn(acc[7], df4);
         }
@@ -276,36 +337,33 @@ __global__ void __launch_bounds__(kSmWarps * 32, 4) k_qsoftmax_bwd(const SmParam
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
             float ge, di2, df2, di1, df1;
-            qc_bwd_r(__fadd_rn(gb[j], gS), e[j], rb[j], q2, ge, di2, df2);
+            qc_bwd_r<Mo::C2>(__fadd_rn(gb[j], gS), e[j], rb[j], q2, ge, di2, df2);
             const float ga = __fmul_rn(ge, __fmul_rn(-P.scaler, e[j]));
-            qc_bwd_r(ga, __fsub_rn(m, s[j]), ra[j], q1, gd[j], di1, df1);
-            acc[0] = __fadd_rn(acc[0], di1); acc[1] = __fadd_rn(acc[1], df1);
+            qc_bwd_r<Mo::C1>(ga, __fsub_rn(m, s[j]), ra[j], q1, gd[j], di1, df1);
+            if (Mo::C1 != 0) acc[0] = __fadd_rn(acc[0], di1);
+            acc[1] = __fadd_rn(acc[1], df1);
             acc[2] = __fadd_rn(acc[2], di2); acc[3] = __fadd_rn(acc[3], df2);
             gm_part = __fadd_rn(gm_part, gd[j]);
             ties_part += (s[j] == m) ? 1 : 0;
         }
-        const float gm = warp_sum(gm_part);
-        int ties = ties_part;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ties += __shfl_xor_sync(0xffffffffu, ties, o);
+        const float gm = row_sum<LPR>(gm_part);
+        const int ties = row_sum_int<LPR>(ties_part);
         const float share = __fdiv_rn(gm, (float)ties);  // the max spreads its gradient evenly over the tied maxima
         float ds[VE];
 #pragma unroll
         for (int j = 0; j < VE; ++j) ds[j] = __fadd_rn(-gd[j], (s[j] == m) ? share : 0.f);
-        store_row<VE>(P.y + row * L, lane, ds);
+        if (valid) store_row<VE>(P.y + row * L, rl, ds);
     }
     // ---- CTA partials, fixed order --------------------------------------------------------------------------------------
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        float vsum = acc[j];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) vsum = __fadd_rn(vsum, __shfl_xor_sync(0xffffffffu, vsum, o));
+        const float vsum = row_sum<32>(acc[j]);
         if (lane == 0) red[warp][j] = vsum;
     }
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
-        red5[warp][0][lane * VE + j] = adf5[j];
-        red5[warp][1][lane * VE + j] = adi5[j];
+        red5[warp * RPW + sub][0][rl * VE + j] = adf5[j];
+        red5[warp * RPW + sub][1][rl * VE + j] = adi5[j];
     }
     __syncthreads();
     const int64_t cta = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
@@ -318,7 +376,7 @@ __global__ void __launch_bounds__(kSmWarps * 32, 4) k_qsoftmax_bwd(const SmParam
     for (int c = threadIdx.x; c < 2 * L; c += kSmWarps * 32) {
         const int which = c / L, col = c - which * L;
         float a5 = 0.f;
-        for (int w = 0; w < kSmWarps; ++w) a5 = __fadd_rn(a5, red5[w][which][col]);
+        for (int w = 0; w < kSmWarps * RPW; ++w) a5 = __fadd_rn(a5, red5[w][which][col]);
         pc[8 + c] = a5;
     }
 }
@@ -377,6 +435,50 @@ static int sm_check(const SmParams &p, int64_t R) {
     return HGQ_OK;
 }
 
+// Kernel variant of a launch (see Modes<>): 1 / 2 when the modes are those of the layer in training, else 0.
+static int sm_variant(const SmParams &p) {
+    const SQuant *qs[4] = {&p.q1, &p.q2, &p.q3, &p.q4};
+    for (const SQuant *q : qs)
+        if (q->rm == RM_RND_CONV) return 0;
+    if (p.rm5 == RM_RND_CONV) return 0;
+    if (p.q2.om == OM_NONE || p.q4.om == OM_NONE || p.q3.om != OM_NONE || p.om5 != OM_NONE) return 0;
+    return p.q1.om == OM_NONE ? 1 : 2;
+}
+
+// Lanes per row of 64 scores: 8 (eight scores per lane, four rows per warp) unless HGQ_QSOFTMAX_LANES in the environment says
+// 16 or 32 (for comparisons).  Measured on 134 M scores, forward / backward: 32 lanes 0.46 / 1.02 ms, 16 lanes 0.38 / 0.75,
+// 8 lanes 0.29 / 0.69: fewer lanes per row mean fewer shuffle steps and less per-row scalar work repeated on every lane.
+static int sm_lanes() {
+    static const int lanes = [] {
+        const char *v = getenv("HGQ_QSOFTMAX_LANES");
+        const int n = v != nullptr ? atoi(v) : 8;
+        return (n == 16 || n == 32) ? n : 8;
+    }();
+    return lanes;
+}
+
+// the 8-lane organisation moves 32 bytes per lane at a time
+static bool sm_aligned32(const SmParams &p) { return aligned(p.s, 32) && aligned(p.y, 32) && (!p.gy || aligned(p.gy, 32)); }
+
+#define HGQ_SM_LAUNCH(KERN, ...)                                                          \
+    do {                                                                                  \
+        switch (sm_variant(p)) {                                                          \
+            case 1: KERN<__VA_ARGS__, 1><<<grid, kSmWarps * 32, 0, st>>>(p); break;       \
+            case 2: KERN<__VA_ARGS__, 2><<<grid, kSmWarps * 32, 0, st>>>(p); break;       \
+            default: KERN<__VA_ARGS__, 0><<<grid, kSmWarps * 32, 0, st>>>(p); break;      \
+        }                                                                                 \
+    } while (0)
+// L = 128: a warp per row, four scores per lane; L = 64: 8 lanes per row (or 16 / 32); L = 32: 16 lanes, two scores per lane
+#define HGQ_SM_DISPATCH(KERN)                                                             \
+    do {                                                                                  \
+        const int lanes = sm_lanes();                                                     \
+        if (L == 128) HGQ_SM_LAUNCH(KERN, 4, 32);                                         \
+        else if (L == 64 && lanes == 8 && sm_aligned32(p)) HGQ_SM_LAUNCH(KERN, 8, 8);     \
+        else if (L == 64 && lanes != 32) HGQ_SM_LAUNCH(KERN, 4, 16);                      \
+        else if (L == 64) HGQ_SM_LAUNCH(KERN, 2, 32);                                     \
+        else HGQ_SM_LAUNCH(KERN, 2, 16);                                                  \
+    } while (0)
+
 }  // namespace hgq
 
 using namespace hgq;
@@ -424,9 +526,7 @@ extern "C" int hgq_qsoftmax_fwd(const float *s, float *y, const uint8_t *const *
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid((unsigned)rows_period, (unsigned)p.splits);
-    if (L == 128) k_qsoftmax_fwd<4><<<grid, kSmWarps * 32, 0, st>>>(p);
-    else if (L == 64) k_qsoftmax_fwd<2><<<grid, kSmWarps * 32, 0, st>>>(p);
-    else k_qsoftmax_fwd<1><<<grid, kSmWarps * 32, 0, st>>>(p);
+    HGQ_SM_DISPATCH(k_qsoftmax_fwd);
     return check_launch();
 }
 
@@ -448,9 +548,7 @@ extern "C" int hgq_qsoftmax_bwd(const float *gy, const float *s, float *ds, cons
     p.part = (float *)workspace;
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid((unsigned)rows_period, (unsigned)p.splits);
-    if (L == 128) k_qsoftmax_bwd<4><<<grid, kSmWarps * 32, 0, st>>>(p);
-    else if (L == 64) k_qsoftmax_bwd<2><<<grid, kSmWarps * 32, 0, st>>>(p);
-    else k_qsoftmax_bwd<1><<<grid, kSmWarps * 32, 0, st>>>(p);
+    HGQ_SM_DISPATCH(k_qsoftmax_bwd);
     if (int e = check_launch()) return e;
     const int64_t n2 = 2 * (int64_t)rows_period * L;
     k_qsoftmax_stage2<<<(unsigned)((n2 + kThreads - 1) / kThreads) + 1, kThreads, 0, st>>>(p.part, dscalars8, df_out, di_out, rows_period,

@@ -86,6 +86,83 @@ def test_qsoftmax_rows_of_64_with_a_256_row_table(exp_iq_mode):
     assert not routes.fallbacks()
 
 
+@pytest.mark.parametrize('B,T,L,table_round,exp_iq_mode', [
+    (13, 64, 64, 'RND', 'SAT'),        # half a warp per row; the last row-group of a CTA has no batch left
+    (13, 64, 64, 'RND', 'WRAP'),       # ... with a rounding-only table index
+    (13, 64, 64, 'RND_CONV', 'SAT'),   # round-half-even tables: the kernel variant with every mode decided at run time
+    (21, 8, 32, 'RND', 'SAT'),         # rows of 32: half a warp per row, two scores per lane
+    (7, 4, 128, 'RND', 'WRAP'),        # rows of 128: a warp per row, four scores per lane
+    (7, 4, 128, 'TRN', 'SAT'),
+])
+def test_qsoftmax_kernel_variants(B, T, L, table_round, exp_iq_mode):
+    """Every organisation of the fused softmax kernels (lanes per row, scores per lane, modes known at compile time or
+    not) against the oracle: outputs, EBOPs, input gradient, every quantizer's gradients and tracked state."""
+    from hgq2_b200 import routes
+    from hgq2_b200.config import QuantizerConfigScope
+    from hgq2_b200.layers import QSoftmax
+    from hgq2_b200.quantizer import QuantizerConfig
+
+    rng = np.random.default_rng(L + B)
+    w, a, t, l = scopes()
+    t2 = QuantizerConfigScope(place='table', b0=10, i0=1, round_mode=table_round)
+    with w, a, t, t2, l:
+        layer = QSoftmax(axis=-1, enable_oq=True, input_scaler=0.25, name=f'smv_{B}_{L}_{table_round}_{exp_iq_mode}',
+                         exp_iq_conf=QuantizerConfig(place='datalane', overflow_mode=exp_iq_mode, k0=0, i0=4, f0=6),
+                         inv_iq_conf=QuantizerConfig(place='datalane', k0=0, i0=7, f0=3))
+    x_np = (np.round(rng.standard_normal((B, 4, T, L)) * 3 * 64) / 64).astype(np.float32)
+    x = torch.from_numpy(x_np).cuda().requires_grad_()
+    layer(x.detach()[:2], training=False)
+    twin = OL.mirror_softmax(layer)
+    xc = torch.from_numpy(x_np).requires_grad_()
+    routes.reset()
+    with routes.strict_mode():
+        y = layer(x, training=True)
+    yc = twin(xc, training=True)
+    close(y, yc, 1e-5, 'softmax output')
+    assert layer.ebops == twin.total_ebops()
+    wgt = torch.from_numpy(rng.standard_normal(tuple(yc.shape)).astype(np.float32))
+    ((y * wgt.cuda()).sum() + sum(layer.losses)).backward()
+    ((yc * wgt).sum() + sum(twin.losses)).backward()
+    close(x.grad, xc.grad, 1e-4, 'dx')
+    for pq, oq, name in ((layer.oq, twin.oq, 'oq'), (layer.exp_table.iq, twin.exp_table.iq, 'exp.iq'),
+                         (layer.exp_table.oq, twin.exp_table.oq, 'exp.oq'), (layer.inv_table.iq, twin.inv_table.iq, 'inv.iq'),
+                         (layer.inv_table.oq, twin.inv_table.oq, 'inv.oq')):
+        compare_quantizer(pq, oq, name)
+    assert routes.counts['hgq_qsoftmax_fwd'] == 1 and routes.counts['hgq_qsoftmax_bwd'] == 1, dict(routes.counts)
+
+
+def test_qsoftmax_rows_of_64_from_a_16_byte_aligned_buffer():
+    """Scores that start on a 16-byte but not a 32-byte boundary take the 16-lanes-per-row organisation (the 8-lane one
+    moves 32 bytes per lane): same outputs and statistics bit for bit, gradients within the summation-order noise."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    gen = torch.Generator(device=dev).manual_seed(3)
+    B, rp, L = 13, 256, 64
+    n = B * rp * L
+    s = torch.round(torch.randn(n, device=dev, generator=gen) * 3 * 64) / 64
+    gy = torch.randn(n, device=dev, generator=gen)
+    hold = torch.empty(n + 8, device=dev)
+    s_off = hold[4:4 + n]
+    s_off.copy_(s)
+    assert s.data_ptr() % 32 == 0 and s_off.data_ptr() % 32 == 16
+    one = lambda v, dt=torch.float32: torch.full((1,), v, dtype=dt, device=dev)
+    k0 = one(0, torch.uint8)
+    f5 = torch.randint(4, 10, (rp * L,), device=dev, generator=gen).float()
+    quants = [(k0, one(4.0), one(6.0), 'RND', 'SAT'), (k0, one(1.0), one(9.0), 'RND', 'SAT'), (None, None, one(3.0), 'RND', 'NONE'),
+              (k0, one(1.0), one(9.0), 'RND', 'SAT'), (None, None, f5, 'RND', 'NONE')]
+    outs = []
+    for src in (s, s_off):
+        x = src.view(B, rp, L)
+        y, a3, a5, a1 = kernels.qsoftmax_fwd(x, quants, 0.25, 1e-7, rp, True, True, True)
+        ds, sc, df5, _ = kernels.qsoftmax_bwd(gy.view(B, rp, L), x, quants, 0.25, 1e-7, rp, False)
+        outs.append((y, a3, a5, a1, ds, sc, df5))
+    for j, name in enumerate(('y', 'amax3', 'amax5', 'amax1')):
+        assert torch.equal(outs[0][j], outs[1][j]), name
+    for j, name in ((4, 'ds'), (5, 'scalars'), (6, 'df5')):
+        close(outs[1][j], outs[0][j], 1e-5, name)
+
+
 def test_qmha_at_the_benchmark_shape():
     """QMultiHeadAttention(4 heads, key_dim 16) on [B, 64, 64]: projections on the fused dense kernels, Q K^T and P V (and
     the four products of their backward) on the per-head tensor-core kernel, the scores through the fused softmax."""
