@@ -21,6 +21,7 @@ ROUND_MODES = {'TRN': 0, 'RND': 1, 'RND_CONV': 2}
 OVERFLOW_MODES = {'NONE': 0, 'WRAP': 1, 'SAT': 2, 'SAT_SYM': 3}
 FLAG_TRAINING = 1
 FLAG_ZERO_NONPOS = 2
+FLAG_ABSMAX_ACCUMULATE = 4
 
 
 class HGQError(RuntimeError):

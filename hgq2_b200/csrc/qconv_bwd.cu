@@ -257,18 +257,33 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad(const CwParams P) {
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-// out[e] = sum over CTAs of part[cta * stride + offset + e]: eight elements per warp, four lanes per element walking the
-// partials, combined in a fixed order (double accumulation), so the result does not depend on scheduling
-__global__ void __launch_bounds__(kThreads) k_cw_stage2(const float *__restrict__ part, int64_t stride, int64_t offset,
-                                                       float *__restrict__ out, int64_t n, int nparts) {
-    const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
-    const int64_t e = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * 8 + j;
+// Element e of the per-CTA partial records [dWq | dbq] summed over the CTAs into its own output array, in double and in a
+// fixed order, so the result does not depend on scheduling.  A block owns eight consecutive elements; its 32 groups of
+// eight lanes walk the records 32 apart (about ten loads per thread, all in flight together: the launch is pure latency
+// on the critical path of a step).
+constexpr int kCwS2Elems = 8;
+__global__ void __launch_bounds__(kThreads) k_cw_stage2(const float *__restrict__ part, int64_t stride, float *__restrict__ dw,
+                                                       int64_t nw, float *__restrict__ db, int64_t nb, int nparts) {
+    __shared__ double red[kThreads / 32][kCwS2Elems];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane >> 3, j = lane & 7;
+    const int64_t e = (int64_t)blockIdx.x * kCwS2Elems + j;
+    const int64_t n = nw + nb;
     double acc = 0.0;
-    if (e < n)
-        for (int p = sub; p < nparts; p += 4) acc += (double)part[(int64_t)p * stride + offset + e];
+    if (e < n) {
+#pragma unroll 4
+        for (int p = warp * 4 + sub; p < nparts; p += kThreads / 8) acc += (double)part[(int64_t)p * stride + e];
+    }
     acc += __shfl_down_sync(0xffffffffu, acc, 16);
     acc += __shfl_down_sync(0xffffffffu, acc, 8);
-    if (sub == 0 && e < n) out[e] = (float)acc;
+    if (sub == 0) red[warp][j] = acc;
+    __syncthreads();
+    if (threadIdx.x < kCwS2Elems && e < n) {
+        double a = 0.0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) a += red[w][threadIdx.x];
+        if (e < nw) dw[e] = (float)a;
+        else db[e - nw] = (float)a;
+    }
 }
 
 
@@ -630,13 +645,9 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
         }
         if (int e = check_launch()) return e;
         const int64_t nw = (int64_t)K * N;
-        k_cw_stage2<<<(unsigned)((nw + 63) / 64), kThreads, 0, st>>>(q.part, stride, 0, dwq, nw, gs.grid);
-        if (int e = check_launch()) return e;
-        if (dbq != nullptr) {
-            k_cw_stage2<<<(unsigned)((N + 63) / 64), kThreads, 0, st>>>(q.part, stride, nw, dbq, N, gs.grid);
-            if (int e = check_launch()) return e;
-        }
-        return HGQ_OK;
+        const int64_t nb1 = dbq != nullptr ? N : 0;
+        k_cw_stage2<<<(unsigned)((nw + nb1 + kCwS2Elems - 1) / kCwS2Elems), kThreads, 0, st>>>(q.part, stride, dwq, nw, dbq, nb1, gs.grid);
+        return check_launch();
     }
     CwGeom g;
     if (int e = cw_geom(B, H, W, C, KH, KW, N, OH, OW, g)) return e;
@@ -652,11 +663,7 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
     k_qconv_wgrad<<<g.grid, kCwThreads, g.smem, st>>>(p);
     if (int e = check_launch()) return e;
     const int64_t nw = (int64_t)K * N;
-    k_cw_stage2<<<(unsigned)((nw + 63) / 64), kThreads, 0, st>>>(p.part, stride, 0, dwq, nw, g.grid);
-    if (int e = check_launch()) return e;
-    if (dbq != nullptr) {
-        k_cw_stage2<<<(unsigned)((N + 63) / 64), kThreads, 0, st>>>(p.part, stride, nw, dbq, N, g.grid);
-        if (int e = check_launch()) return e;
-    }
-    return HGQ_OK;
+    const int64_t nb = dbq != nullptr ? N : 0;
+    k_cw_stage2<<<(unsigned)((nw + nb + kCwS2Elems - 1) / kCwS2Elems), kThreads, 0, st>>>(p.part, stride, dwq, nw, dbq, nb, g.grid);
+    return check_launch();
 }

@@ -50,6 +50,7 @@ struct QdParams {
     const float *bq;     // [N] or nullptr
     float *y;            // [M, N]
     unsigned *amax_part; // [gridDim.x, rows_period * K] abs-max partials, or nullptr
+    int amax_direct;     // amax_part is the [rows_period * K] result itself: merge by atomic max
     unsigned *status;
     int64_t M;
     int K, N, Kpad, Npad;
@@ -484,8 +485,15 @@ __global__ void __launch_bounds__(kQdThreads) k_qdense_fwd(const QdParams P) {
             __syncthreads();
         }
         const int table = P.rows_period * K;
-        unsigned *dst = P.amax_part + (int64_t)blockIdx.x * table;
-        for (int e = tid; e < table; e += kQdThreads) dst[e] = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
+        if (P.amax_direct) {
+            for (int e = tid; e < table; e += kQdThreads) {
+                const unsigned v = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
+                if (v != 0u) atomicMax(P.amax_part + e, v);
+            }
+        } else {
+            unsigned *dst = P.amax_part + (int64_t)blockIdx.x * table;
+            for (int e = tid; e < table; e += kQdThreads) dst[e] = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
+        }
     }
     tc::fence_before_sync();
     __syncthreads();
@@ -503,8 +511,8 @@ __global__ void __launch_bounds__(kThreads) k_amax_stage2(const unsigned *__rest
 }
 
 int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round_mode, const float *wq, const float *bq,
-                     int activation, float *y, unsigned *amax_part, int64_t M, int K, int N, int Kpad, int Npad, int Kt,
-                     unsigned *status, cudaStream_t st, int *grid);
+                     int activation, float *y, unsigned *amax_part, int amax_direct, int64_t M, int K, int N, int Kpad, int Npad,
+                     int Kt, unsigned *status, cudaStream_t st, int *grid);
 
 // HGQ_QDENSE_WS=0 in the environment keeps every call on the general kernel (for comparisons).
 static bool ws_enabled() {
@@ -567,7 +575,8 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
     if (x == nullptr || wq == nullptr || y == nullptr) return HGQ_ERR_NULL;
     if (round_mode < 0 || round_mode > 2 || overflow_mode < 0 || overflow_mode > 3) return HGQ_ERR_MODE;
     if (activation != ACT_NONE && activation != ACT_RELU) return HGQ_ERR_MODE;
-    if (flags & ~(HGQ_FLAG_TRAINING | HGQ_FLAG_ZERO_NONPOS)) return HGQ_ERR_MODE;
+    if (flags & ~(HGQ_FLAG_TRAINING | HGQ_FLAG_ZERO_NONPOS | HGQ_FLAG_ABSMAX_ACCUMULATE)) return HGQ_ERR_MODE;
+    const bool direct = (flags & HGQ_FLAG_ABSMAX_ACCUMULATE) != 0 && absmax != nullptr;
     int om = overflow_mode;
     if (om == OM_WRAP && (flags & HGQ_FLAG_TRAINING)) om = OM_NONE;
     const int zero = (flags & HGQ_FLAG_ZERO_NONPOS) ? 1 : 0;
@@ -576,11 +585,12 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
     if (absmax != nullptr && qf == nullptr) return HGQ_ERR_NULL;
     QdGeom g;
     if (int e = qd_geom(M, K, N, rows_period, absmax != nullptr, (qf != nullptr) && (om == OM_NONE), g)) return e;
-    const size_t need = absmax ? (size_t)g.grid * rows_period * K * sizeof(unsigned) : 0;
-    if (absmax && (workspace == nullptr || workspace_bytes < need)) return HGQ_ERR_WORKSPACE;
+    const size_t need = (absmax && !direct) ? (size_t)g.grid * rows_period * K * sizeof(unsigned) : 0;
+    if (need && (workspace == nullptr || workspace_bytes < need)) return HGQ_ERR_WORKSPACE;
     QdParams p;
     p.x = x; p.qk = qk; p.qi = qi; p.qf = qf; p.wq = wq; p.bq = bq; p.y = y;
-    p.amax_part = absmax ? (unsigned *)workspace : nullptr;
+    p.amax_part = absmax ? (direct ? (unsigned *)absmax : (unsigned *)workspace) : nullptr;
+    p.amax_direct = direct ? 1 : 0;
     p.status = status;
     p.M = M; p.K = K; p.N = N; p.Kpad = g.Kpad; p.Npad = g.Npad; p.Kt = g.Kt;
     p.rows_period = rows_period; p.rm = round_mode; p.om = om; p.act = activation; p.zero = zero;
@@ -592,12 +602,12 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
     if (fastq && ws_enabled()) {
         // the common training case has a warp-specialised kernel of its own
         int ws_grid = 0;
-        const int r = qdense_ws_launch(x, qf, rows_period, round_mode, wq, bq, activation, y, p.amax_part, M, K, N, g.Kpad,
-                                       g.Npad, g.Kt, status, st, &ws_grid);
+        const int r = qdense_ws_launch(x, qf, rows_period, round_mode, wq, bq, activation, y, p.amax_part, p.amax_direct, M, K, N,
+                                       g.Kpad, g.Npad, g.Kt, status, st, &ws_grid);
         if (r < 0) return -r;
         if (r == 1) {
             if (int e = check_launch()) return e;
-            if (absmax) {
+            if (absmax && !direct) {
                 const int table = rows_period * K;
                 k_amax_stage2<<<(table + kThreads - 1) / kThreads, kThreads, 0, st>>>((const unsigned *)workspace, absmax, table, ws_grid);
                 return check_launch();
@@ -639,7 +649,7 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
     }
 #undef HGQ_QD_LAUNCH
     if (int e = check_launch()) return e;
-    if (absmax) {
+    if (absmax && !direct) {
         const int table = rows_period * K;
         k_amax_stage2<<<(table + kThreads - 1) / kThreads, kThreads, 0, st>>>((const unsigned *)workspace, absmax, table, g.grid);
         return check_launch();

@@ -459,22 +459,33 @@ __global__ void __launch_bounds__(kQbThreads) k_qdense_bwd(const QbParams P) {
 }
 
 // Sum of the per-CTA partials, in double and in a fixed order: element e of the partial vector [dWq | dbq | df] goes to
-// its own output array.  Eight elements per warp, four lanes per element walking the partials.
+// its own output array.  A block owns eight consecutive elements; its 32 groups of eight lanes (four per warp) walk the
+// partial records 32 apart, so that a few hundred records cost about ten loads per thread, all in flight together (the
+// launch sits on the critical path of a step and is pure latency).
+constexpr int kQbS2Elems = 8;
 __global__ void __launch_bounds__(kThreads) k_qb_stage2(const float *__restrict__ part, int64_t stride, int nparts,
                                                        float *__restrict__ dw, int64_t nw, float *__restrict__ db, int64_t nb,
                                                        float *__restrict__ df, int64_t nf) {
-    const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
-    const int64_t e = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * 8 + j;
+    __shared__ double red[kThreads / 32][kQbS2Elems];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane >> 3, j = lane & 7;
+    const int64_t e = (int64_t)blockIdx.x * kQbS2Elems + j;
     const int64_t n = nw + nb + nf;
     double acc = 0.0;
-    if (e < n)
-        for (int p = sub; p < nparts; p += 4) acc += (double)part[(int64_t)p * stride + e];
+    if (e < n) {
+#pragma unroll 4
+        for (int p = warp * 4 + sub; p < nparts; p += kThreads / 8) acc += (double)part[(int64_t)p * stride + e];
+    }
     acc += __shfl_down_sync(0xffffffffu, acc, 16);
     acc += __shfl_down_sync(0xffffffffu, acc, 8);
-    if (sub == 0 && e < n) {
-        if (e < nw) dw[e] = (float)acc;
-        else if (e < nw + nb) { if (db != nullptr) db[e - nw] = (float)acc; }
-        else if (df != nullptr) df[e - nw - nb] = (float)acc;
+    if (sub == 0) red[warp][j] = acc;
+    __syncthreads();
+    if (threadIdx.x < kQbS2Elems && e < n) {
+        double a = 0.0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) a += red[w][threadIdx.x];
+        if (e < nw) dw[e] = (float)a;
+        else if (e < nw + nb) { if (db != nullptr) db[e - nw] = (float)a; }
+        else if (df != nullptr) df[e - nw - nb] = (float)a;
     }
 }
 
@@ -555,7 +566,7 @@ extern "C" int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const floa
         if (r < 0) return -r;
         if (r == 1) {
             if (int e = check_launch()) return e;
-            k_qb_stage2<<<(unsigned)((g.part_stride + 63) / 64), kThreads, 0, (cudaStream_t)stream>>>(
+            k_qb_stage2<<<(unsigned)((g.part_stride + kQbS2Elems - 1) / kQbS2Elems), kThreads, 0, (cudaStream_t)stream>>>(
                 (const float *)workspace, g.part_stride, records, dwq, nw_, dbq, N, df, df != nullptr ? nf_ : 0);
             return check_launch();
         }
@@ -581,7 +592,7 @@ extern "C" int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const floa
     }
     if (int e = check_launch()) return e;
     const int64_t nw = (int64_t)K * N, nf = (int64_t)rows_period * K;
-    k_qb_stage2<<<(unsigned)((g.part_stride + 63) / 64), kThreads, 0, st>>>(p.part, g.part_stride, g.grid, dwq, nw, dbq, N,
+    k_qb_stage2<<<(unsigned)((g.part_stride + kQbS2Elems - 1) / kQbS2Elems), kThreads, 0, st>>>(p.part, g.part_stride, g.grid, dwq, nw, dbq, N,
                                                                            df, df != nullptr ? nf : 0);
     if (int e = check_launch()) return e;
     return HGQ_OK;

@@ -57,6 +57,7 @@ struct WsParams {
     const float *x, *qf, *wq, *bq;
     float *y;
     unsigned *amax_part;  // [gridDim.x, rows_period * K] abs-max partials, or nullptr
+    int amax_direct;      // amax_part is the [rows_period * K] result itself: merge by atomic max
     unsigned *status;
     int64_t M, num_tiles;
     int K, N, Kpad, Npad, Kt, rows_period;
@@ -408,8 +409,15 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kWsProd) : "memory");
             const int table = P.rows_period * K;
-            unsigned *dst = P.amax_part + (int64_t)blockIdx.x * table;
-            for (int e = tid; e < table; e += kWsProd) dst[e] = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
+            if (P.amax_direct) {
+                for (int e = tid; e < table; e += kWsProd) {
+                    const unsigned v = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
+                    if (v != 0u) atomicMax(P.amax_part + e, v);
+                }
+            } else {
+                unsigned *dst = P.amax_part + (int64_t)blockIdx.x * table;
+                for (int e = tid; e < table; e += kWsProd) dst[e] = __float_as_uint(amax_t[(e / K) * Ks + (e % K)]);
+            }
         }
     } else if (warp == kWsIssueWarp) {
         // ================================ tensor-core issue ==========================================================
@@ -657,8 +665,8 @@ static bool ws_make_tmap(CUtensorMap *map, const float *x, int64_t M, int K) {
 // Launches the warp-specialised kernel when it covers the call; returns 1 with the grid size in *grid, 0 when the call is
 // not covered (the caller then takes the general kernel), or a negative CUDA error code.
 int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round_mode, const float *wq, const float *bq,
-                     int activation, float *y, unsigned *amax_part, int64_t M, int K, int N, int Kpad, int Npad, int Kt,
-                     unsigned *status, cudaStream_t st, int *grid) {
+                     int activation, float *y, unsigned *amax_part, int amax_direct, int64_t M, int K, int N, int Kpad, int Npad,
+                     int Kt, unsigned *status, cudaStream_t st, int *grid) {
     if (qf == nullptr || K % 4 != 0 || !aligned(x, 16) || !aligned(y, 4)) return 0;
     if (2 * Npad > 512) return 0;
     // Warp split: 8 producer and 8 epilogue warps.  Measured on the particle-layer shape (ms per launch): 8/8 0.53,
@@ -685,7 +693,7 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
     }
     if (smem > 227 * 1024) return 0;
     WsParams p;
-    p.x = x; p.qf = qf; p.wq = wq; p.bq = bq; p.y = y; p.amax_part = amax_part; p.status = status;
+    p.x = x; p.qf = qf; p.wq = wq; p.bq = bq; p.y = y; p.amax_part = amax_part; p.amax_direct = amax_direct; p.status = status;
     p.M = M; p.num_tiles = (M + kWsTileM - 1) / kWsTileM;
     p.K = K; p.N = N; p.Kpad = Kpad; p.Npad = Npad; p.Kt = Kt; p.rows_period = rows_period;
     p.rm = round_mode; p.act = activation; p.depth = depth;

@@ -231,7 +231,8 @@ class _Dense(_Node):
         x = x.contiguous()
         rm = self.iq.q.round_mode
         y, _ = kernels.qdense_fwd(x, None, None, self.iq.F.view(P, K), P, rm, 'NONE', True, False, self.wq.view(K, N),
-                                  self.bias_q, 'relu' if self.relu else None, True, absmax_out=self.iq.absmax)
+                                  self.bias_q, 'relu' if self.relu else None, True, absmax_out=self.iq.absmax,
+                                  absmax_accumulate=True)  # the step zeroed the statistics of every quantizer at its start
         self.x, self.y = x, (y if (self.relu or self.oq is not None) else None)
         out_shape = (x.shape[0],) + self.out_tail
         if self.oq is not None:
@@ -594,9 +595,11 @@ class Engine:
         dev = self.dev
         total = sum((s.n + 3) // 4 * 4 for s in self.slots)
         self.tables = torch.zeros(3 * total, dtype=torch.float32, device=dev)
-        self.tgrads = torch.zeros(3 * total, dtype=torch.float32, device=dev)
         n_abs = sum((s.n + 3) // 4 * 4 for s in self.slots if s.tracked_act)
-        self.absmax = torch.zeros(max(n_abs, 1), dtype=torch.float32, device=dev)
+        # table gradients and abs-max statistics share one buffer: one memset at the start of a step clears both
+        self._cleared = torch.zeros(3 * total + max(n_abs, 1), dtype=torch.float32, device=dev)
+        self.tgrads = self._cleared[:3 * total]
+        self.absmax = self._cleared[3 * total:]
         self.qweights = torch.zeros(max(self._wfloats, 1), dtype=torch.float32, device=dev)
         self.dqweights = torch.zeros(max(self._wfloats, 1), dtype=torch.float32, device=dev)
         self.eb_loss = torch.zeros(max(self._n_eb, 1), dtype=torch.float32, device=dev)
@@ -673,7 +676,7 @@ class Engine:
         side = self._side
         n_slots, n_weights = len(self.slots), len(self._weights)
         with torch.no_grad():
-            self.tgrads.zero_()
+            self._cleared.zero_()
             kernels.tables_forward(self._slot_descs, n_slots, self._max_slot)
             kernels.weights_forward(self._weight_descs, n_weights, self._max_weight, self._slot_descs)
             h = x

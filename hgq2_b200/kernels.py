@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import FLAG_TRAINING, FLAG_ZERO_NONPOS, OVERFLOW_MODES, ROUND_MODES, check, lib, ptr, require_cuda, stream_handle
+from ._lib import FLAG_ABSMAX_ACCUMULATE, FLAG_TRAINING, FLAG_ZERO_NONPOS, OVERFLOW_MODES, ROUND_MODES, check, lib, ptr, require_cuda, stream_handle
 
 _workspaces: dict[tuple[int, int, int], torch.Tensor] = {}
 
@@ -243,8 +243,9 @@ def qdense_supported(M: int, K: int, N: int, rows_period: int) -> bool:
 
 
 def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: str, training: bool, zero_nonpos: bool,
-               wq, bq, activation: str | None, want_absmax: bool, absmax_out=None):
-    """Fused y = act(iq(x) @ wq + bq); x is treated as [M, K] with K = wq.shape[0].  Returns (y [M, N], absmax or None)."""
+               wq, bq, activation: str | None, want_absmax: bool, absmax_out=None, absmax_accumulate: bool = False):
+    """Fused y = act(iq(x) @ wq + bq); x is treated as [M, K] with K = wq.shape[0].  Returns (y [M, N], absmax or None).
+    With ``absmax_accumulate`` the statistic is merged into ``absmax_out`` by atomic max (the caller zeroed it)."""
     require_cuda(x, qk, qi, qf, wq, bq)
     rm, om = _modes(round_mode, overflow_mode)
     x = x.contiguous()
@@ -256,9 +257,10 @@ def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: 
     wq = wq.contiguous()
     y = torch.empty((M, N), dtype=torch.float32, device=x.device)
     absmax = (absmax_out if absmax_out is not None else torch.empty(rows_period * K, dtype=torch.float32, device=x.device)) if want_absmax else None
-    ws = workspace(lib().hgq_qdense_fwd_workspace(M, K, N, rows_period), x.device, slot=1) if want_absmax else None
+    accumulate = want_absmax and absmax_accumulate and absmax_out is not None
+    ws = workspace(lib().hgq_qdense_fwd_workspace(M, K, N, rows_period), x.device, slot=1) if (want_absmax and not accumulate) else None
     act = {None: 0, 'relu': 1}[activation]
-    flags = (FLAG_TRAINING if training else 0) | (FLAG_ZERO_NONPOS if zero_nonpos else 0)
+    flags = (FLAG_TRAINING if training else 0) | (FLAG_ZERO_NONPOS if zero_nonpos else 0) | (FLAG_ABSMAX_ACCUMULATE if accumulate else 0)
     with torch.cuda.device(x.device):
         st = lib().hgq_qdense_fwd(
             ptr(x), ptr(qk), ptr(qi), ptr(qf), rows_period, rm, om, flags, ptr(wq), ptr(bq), act, ptr(y), ptr(absmax), M, K, N,

@@ -62,6 +62,7 @@ enum hgq_overflow_mode {
 /* flags (bit-or) */
 #define HGQ_FLAG_TRAINING 1u       /* training=True: WRAP leaves the rounded value unwrapped     */
 #define HGQ_FLAG_ZERO_NONPOS 2u    /* eval-only: y = 0 where k+i+f <= 0 (fixed_point_quantizer.py:148-149) */
+#define HGQ_FLAG_ABSMAX_ACCUMULATE 4u /* hgq_qdense_fwd: absmax = max(absmax, statistic) instead of being overwritten */
 
 /* ---- library ------------------------------------------------------------------------------ */
 
@@ -163,7 +164,9 @@ size_t hgq_qdense_fwd_workspace(int64_t M, int K, int N, int rows_period);
  *   mode is NONE, or WRAP with HGQ_FLAG_TRAINING); wq [K, N] and bq [N] (may be NULL) already quantised;
  *   activation 0 none, 1 relu; y [M, N].
  *   absmax (may be NULL): [rows_period, K] floats receiving max over rows of |round(x, f)| (the statistic
- *   of x_to_bw_absmax, quantizer/internal/base.py:185-186); needs `workspace`.
+ *   of x_to_bw_absmax, quantizer/internal/base.py:185-186); needs `workspace`.  With HGQ_FLAG_ABSMAX_ACCUMULATE the
+ *   statistic is merged into the caller's buffer by atomic max (the caller zeroes it once for all layers of a step): no
+ *   workspace and no second launch.
  *   status (may be NULL): device word; bit 0 is set if a bounded device-side wait gave up.
  *
  * The contraction runs on the tensor cores with every operand split exactly into bf16 terms and fp32
