@@ -14,11 +14,22 @@
 // two bf16 terms (exact up to 16 significant bits: the quantised projections and probabilities; gradients are rounded
 // at 2^-17 relative) and stored as no-swizzle core matrices: K-major where the contraction index is contiguous in memory,
 // MN-major where the row / column index is.  HBM-bound: 4 (2 L D + L L) bytes per head and product.
+// Raw operands reach the CTA in one of two ways (template parameter TMA): every thread loads its own 32-byte pieces, or
+// (kind 0) the copy engine fetches the tile's two boxes (tiled bulk-tensor copies from tensor maps over this GPU's x and y,
+// completion counted on an mbarrier) into a raw buffer that the threads convert from; the copies of tile t + 1 are issued
+// as soon as tile t has been converted, so they run under its products and its write-out.  Measured on 8192 x 4 heads:
+// kind 0 0.212 -> 0.193 ms; kinds 1 and 2, whose 32 KB raw box leaves room for two or three CTAs per SM instead of four,
+// 0.245 -> 0.270 and 0.266 -> 0.265 ms, so they keep the per-thread loads.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "hgq_common.cuh"
 #include "tc05.cuh"
+#include "tmap.cuh"
 
 namespace hgq {
 
@@ -42,10 +53,8 @@ __device__ __forceinline__ void at_split2(float v0, float v1, uint32_t &hi, uint
     lo = *reinterpret_cast<const uint32_t *>(&l2);
 }
 
-// eight consecutive floats -> one 16-byte row of a core matrix in each of the two term planes
-__device__ __forceinline__ int at_put8(const float *src, unsigned char *hi_plane, unsigned char *lo_plane, int off) {
-    float v[8];
-    ldcs8(src, v);  // one 32-byte sector per thread and instruction; every operand element is read once per product
+// eight floats -> one 16-byte row of a core matrix in each of the two term planes
+__device__ __forceinline__ int at_cvt8(const float (&v)[8], unsigned char *hi_plane, unsigned char *lo_plane, int off) {
     uint32_t hi[4], lo[4];
     at_split2(v[0], v[1], hi[0], lo[0]);
     at_split2(v[2], v[3], hi[1], lo[1]);
@@ -56,8 +65,22 @@ __device__ __forceinline__ int at_put8(const float *src, unsigned char *hi_plane
     return ((lo[0] | lo[1] | lo[2] | lo[3]) & 0x7fff7fffu) != 0;
 }
 
-template <int KIND>
-__global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
+// eight consecutive floats from the raw buffer in shared memory (SH, 32-byte aligned) or from global memory
+template <bool SH>
+__device__ __forceinline__ int at_put8(const float *src, unsigned char *hi_plane, unsigned char *lo_plane, int off) {
+    float v[8];
+    if (SH) {
+        const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        ldcs8(src, v);  // one 32-byte sector per thread and instruction; every operand element is read once per product
+    }
+    return at_cvt8(v, hi_plane, lo_plane, off);
+}
+
+template <int KIND, bool TMA>
+__global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, const __grid_constant__ CUtensorMap map_x,
+                                                          const __grid_constant__ CUtensorMap map_y) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int L = kAtL;
     const int D = P.D, H = P.H, DG = D >> 3;
@@ -68,14 +91,22 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
     const int b_term = Nn * Ka * 2;              // B of one head
     unsigned char *A = smem;                     // [2 terms]
     unsigned char *Bm = A + 2 * a_term;          // [2 heads][2 terms]
-    uint64_t *bar = reinterpret_cast<uint64_t *>(Bm + 4 * b_term);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+    // raw boxes (TMA): x and y are [64, 2 D] floats each; sizes are multiples of 128 B
+    static_assert(!TMA || KIND == 0, "bulk tensor copies are used for kind 0 only");
+    const int rawx_bytes = TMA ? L * 2 * D * 4 : 0;
+    const int rawy_bytes = TMA ? L * 2 * D * 4 : 0;
+    float *RX = reinterpret_cast<float *>(Bm + 4 * b_term);
+    float *RY = reinterpret_cast<float *>(Bm + 4 * b_term + rawx_bytes);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(Bm + 4 * b_term + rawx_bytes + rawy_bytes);
+    uint64_t *full = bar + 1;  // TMA: the raw boxes of the next tile have landed
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 2);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < 2 * Nn) tmem_cols <<= 1;
     if (tid == 0) {
         tc::mbar_init(bar, 2);  // one issuing thread per head commits to it
+        tc::mbar_init(full, 1); // the expect_tx arrival of the thread that issues the copies (+ their bytes)
         tc::mbar_init_fence();
     }
     if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
@@ -88,15 +119,39 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
     const int pairs = H >> 1;
     const int64_t LL = (int64_t)L * L, row_shd = (int64_t)H * D;
 
-    uint32_t phase = 0;
+    // the two boxes of a tile: x and y at (column, row) = (h0 D, b L) of [B L, H D].  h0 is even and D a multiple of 16:
+    // the column offsets are multiples of 128 bytes.
+    auto fetch = [&](int64_t t) {
+        const int64_t tb = t / pairs;
+        const int th0 = (int)(t - tb * pairs) * 2;
+        tma::expect_tx(full, (uint32_t)(rawx_bytes + rawy_bytes));
+        tma::load_2d(tc::smem_u32(RX), &map_x, th0 * D, (int)(tb * L), full);
+        tma::load_2d(tc::smem_u32(RY), &map_y, th0 * D, (int)(tb * L), full);
+    };
+    if (TMA && tid == 0 && (int64_t)blockIdx.x < P.num_tiles) fetch(blockIdx.x);
+
+    uint32_t phase = 0, full_phase = 0;
     bool ok = true;
+    bool pending = TMA && (int64_t)blockIdx.x < P.num_tiles;  // copies issued whose arrival nobody has waited for yet
     for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
         const int64_t b = tile / pairs;
         const int h0 = (int)(tile - b * pairs) * 2;
-        const float *x_shd = P.x + b * L * row_shd + (int64_t)h0 * D;   // kind 0: x[b, 0, h0, 0]
-        const float *x_hts = P.x + (b * H + h0) * LL;                   // kinds 1, 2: x[b, h0, 0, 0]
-        const float *y_shd = P.y + b * L * row_shd + (int64_t)h0 * D;
+        // TMA: the tile's rows in the raw buffers (row pitch 2 D floats)
+        const float *x_shd = TMA ? RX : P.x + b * L * row_shd + (int64_t)h0 * D;   // kind 0: x[b, 0, h0, 0]
+        const float *x_hts = TMA ? RX : P.x + (b * H + h0) * LL;                   // kinds 1, 2: x[b, h0, 0, 0]
+        const float *y_shd = TMA ? RY : P.y + b * L * row_shd + (int64_t)h0 * D;
+        const int64_t pitch_x = TMA ? 2 * D : row_shd, pitch_y = pitch_x;
         int lo_a = 0, lo_b = 0;
+        if (TMA) {
+            const bool got = tc::mbar_wait(full, full_phase);
+            if (!__syncthreads_and(got ? 1 : 0)) {
+                if (tid == 0 && P.status) atomicOr(P.status, 1u);
+                ok = false;
+                break;
+            }
+            full_phase ^= 1u;
+            pending = false;
+        }
         // ---- A operand: both heads ------------------------------------------------------------------------------------------
         if (KIND == 0) {
             // rows (hh, t), contraction d: K-major, core (row group, d group); unit = (t, hh, d group): a row of the pair is
@@ -104,20 +159,20 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
                 const int dg = u % DG, hh = (u / DG) & 1, t = u / (2 * DG);
                 const int row = hh * 64 + t;
-                lo_a |= at_put8(x_shd + t * row_shd + hh * D + dg * 8, A, A + a_term, ((row >> 3) * DG + dg) * 128 + (row & 7) * 16);
+                lo_a |= at_put8<TMA>(x_shd + t * pitch_x + hh * D + dg * 8, A, A + a_term, ((row >> 3) * DG + dg) * 128 + (row & 7) * 16);
             }
         } else if (KIND == 1) {
             // rows (hh, t), contraction s: K-major, core (row group, s group): a row is 64 contiguous floats
             for (int u = tid; u < 128 * 8; u += kAtThreads) {
                 const int sg = u & 7, row = u >> 3;
-                lo_a |= at_put8(x_hts + (int64_t)row * L + sg * 8, A, A + a_term, ((row >> 3) * 8 + sg) * 128 + (row & 7) * 16);
+                lo_a |= at_put8<TMA>(x_hts + (int64_t)row * L + sg * 8, A, A + a_term, ((row >> 3) * 8 + sg) * 128 + (row & 7) * 16);
             }
         } else {
             // rows m = (hh, s), contraction t: MN-major, core (t group, m group) = 8 t x 8 m; a row t of a head is 64 contiguous s
             for (int u = tid; u < 128 * 8; u += kAtThreads) {
                 const int sg = u & 7, t = (u >> 3) & 63, hh = u >> 9;
                 const int mg = hh * 8 + sg;
-                lo_a |= at_put8(x_hts + hh * LL + (int64_t)t * L + sg * 8, A, A + a_term, ((t >> 3) * 16 + mg) * 128 + (t & 7) * 16);
+                lo_a |= at_put8<TMA>(x_hts + hh * LL + (int64_t)t * L + sg * 8, A, A + a_term, ((t >> 3) * 16 + mg) * 128 + (t & 7) * 16);
             }
         }
         // ---- B operands: one per head -----------------------------------------------------------------------------------------
@@ -126,19 +181,24 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
                 const int dg = u % DG, hh = (u / DG) & 1, s = u / (2 * DG);
                 unsigned char *base = Bm + hh * 2 * b_term;
-                lo_b |= at_put8(y_shd + s * row_shd + hh * D + dg * 8, base, base + b_term, ((s >> 3) * DG + dg) * 128 + (s & 7) * 16);
+                lo_b |= at_put8<TMA>(y_shd + s * pitch_y + hh * D + dg * 8, base, base + b_term, ((s >> 3) * DG + dg) * 128 + (s & 7) * 16);
             }
         } else {
             // columns d, contraction r (s or t): MN-major, core (r group, d group) = 8 r x 8 d
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
                 const int dg = u % DG, hh = (u / DG) & 1, r = u / (2 * DG);
                 unsigned char *base = Bm + hh * 2 * b_term;
-                lo_b |= at_put8(y_shd + r * row_shd + hh * D + dg * 8, base, base + b_term, ((r >> 3) * DG + dg) * 128 + (r & 7) * 16);
+                lo_b |= at_put8<TMA>(y_shd + r * pitch_y + hh * D + dg * 8, base, base + b_term, ((r >> 3) * DG + dg) * 128 + (r & 7) * 16);
             }
         }
         tc::fence_smem_to_async();
         const int n_a = __syncthreads_or(lo_a) ? 2 : 1;
         const int n_b = __syncthreads_or(lo_b) ? 2 : 1;
+        // every thread is done with the raw buffers: the next tile's boxes may land while this one is multiplied and written
+        if (TMA && tile + gridDim.x < P.num_tiles) {
+            if (tid == 0) fetch(tile + gridDim.x);
+            pending = true;
+        }
         // ---- one issuing thread per head ------------------------------------------------------------------------------------------
         if (lane == 0 && warp < 2) {
             tc::fence_after_sync();
@@ -197,14 +257,27 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P) {
         tc::fence_before_sync();
         __syncthreads();
     }
+    // a wait gave up while copies were still on their way: give them (bounded) time to land before the CTA's shared
+    // memory is handed to another CTA
+    if (TMA && !ok && pending) (void)tc::mbar_wait(full, full_phase);
     tc::fence_before_sync();
     __syncthreads();
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-static size_t at_smem(int kind, int D) {
+static size_t at_smem(int kind, int D, bool tma) {
     const int Ka = kind == 0 ? D : kAtL, Nn = kind == 0 ? kAtL : D;
-    return 2 * (size_t)128 * Ka * 2 + 4 * (size_t)Nn * Ka * 2 + 64;
+    const size_t raw = tma ? 2 * (size_t)kAtL * 2 * D * 4 : 0;  // the raw boxes of x and y (kind 0)
+    return 2 * (size_t)128 * Ka * 2 + 4 * (size_t)Nn * Ka * 2 + raw + 64;
+}
+
+// HGQ_ATTN_TMA=0 in the environment keeps the per-thread loads (for comparisons).
+static bool at_tma_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("HGQ_ATTN_TMA");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
 }
 
 }  // namespace hgq
@@ -225,26 +298,32 @@ extern "C" int hgq_attn_heads_matmul(int kind, const float *x, const float *y, f
     p.x = x; p.y = y; p.out = out; p.status = status;
     p.B = B; p.H = H; p.D = D;
     p.num_tiles = B * (H / 2);
-    const size_t smem = at_smem(kind, D);
+    // kind 0: tensor maps over this GPU's x and y alone, [B L, H D] with boxes [64, 2 D]
+    CUtensorMap map_x, map_y;
+    memset(&map_x, 0, sizeof(map_x));
+    memset(&map_y, 0, sizeof(map_y));
+    const int64_t rows_shd = B * L;
+    const bool tma = kind == 0 && at_tma_enabled() && rows_shd < ((int64_t)1 << 31) &&
+                     tma::make_map_2d(&map_x, x, rows_shd, (int64_t)H * D, (int64_t)H * D, 2 * D, kAtL) &&
+                     tma::make_map_2d(&map_y, y, rows_shd, (int64_t)H * D, (int64_t)H * D, 2 * D, kAtL);
+    const size_t smem = at_smem(kind, D, tma);
     int per_sm = (int)((228 * 1024) / (smem + 1024));
-    const int cap = 4;  // measured optimum for all three kinds (3 and 5 resident CTAs are both slower)
+    const int cap = 4;  // measured optimum for all three kinds with per-thread loads (3 and 5 resident CTAs are both slower)
     if (per_sm > cap) per_sm = cap;
+    if (per_sm < 1) return HGQ_ERR_SIZE;
     int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > p.num_tiles) grid = p.num_tiles;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t ce;
-    if (kind == 0) {
-        ce = cudaFuncSetAttribute(k_attn_heads<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (ce != cudaSuccess) return (int)ce;
-        k_attn_heads<0><<<(unsigned)grid, kAtThreads, smem, st>>>(p);
-    } else if (kind == 1) {
-        ce = cudaFuncSetAttribute(k_attn_heads<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (ce != cudaSuccess) return (int)ce;
-        k_attn_heads<1><<<(unsigned)grid, kAtThreads, smem, st>>>(p);
-    } else {
-        ce = cudaFuncSetAttribute(k_attn_heads<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (ce != cudaSuccess) return (int)ce;
-        k_attn_heads<2><<<(unsigned)grid, kAtThreads, smem, st>>>(p);
-    }
+    cudaError_t ce = cudaSuccess;
+#define HGQ_AT_LAUNCH(KIND_, TMA_)                                                                                          \
+    do {                                                                                                                   \
+        ce = cudaFuncSetAttribute(k_attn_heads<KIND_, TMA_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        if (ce != cudaSuccess) return (int)ce;                                                                             \
+        k_attn_heads<KIND_, TMA_><<<(unsigned)grid, kAtThreads, smem, st>>>(p, map_x, map_y);                              \
+    } while (0)
+    if (kind == 0) { if (tma) HGQ_AT_LAUNCH(0, true); else HGQ_AT_LAUNCH(0, false); }
+    else if (kind == 1) HGQ_AT_LAUNCH(1, false);
+    else HGQ_AT_LAUNCH(2, false);
+#undef HGQ_AT_LAUNCH
     return check_launch();
 }

@@ -31,6 +31,28 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(autouse=True)
+def reproducible_initializers(monkeypatch):
+    """Initializers built without a seed draw from consecutive fixed seeds (restarted for every test) instead of from OS
+    entropy, so that a test sees the same weights in every run and in every test order."""
+    import copy
+    import itertools
+
+    from hgq2_b200 import backend
+
+    seeds = itertools.count(20240)
+    for cls in (backend.GlorotUniform, backend.RandomNormal):
+        original = cls.__call__
+
+        def call(self, *args, _original=original, **kwargs):
+            if self.seed is None:
+                self = copy.copy(self)
+                self.seed = next(seeds)
+            return _original(self, *args, **kwargs)
+
+        monkeypatch.setattr(cls, '__call__', call)
+
+
 @pytest.fixture(scope='session')
 def golden_dir():
     return ROOT / 'tests' / 'golden'
