@@ -14,6 +14,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "hgq_common.cuh"
 #include "tc05.cuh"
 
@@ -305,8 +307,12 @@ struct CsParams {
     FastDiv div_img, div_row, div_cg;  // by Hp * Wp, by Wp and by the number of channel groups
 };
 
-template <bool VEC_C>  // see k_qconv_s1: scalar image loads live in their own instantiation
-__global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P) {
+// VEC_C: see k_qconv_s1 (scalar image loads live in their own instantiation).  NT threads per CTA: 256 when three CTAs
+// fit an SM; when tensor memory or shared memory leave room for fewer, the CTA is made wider instead (512 / 1024 threads),
+// so that the staging loops -- latency-bound global loads -- still have 24 to 32 warps per SM behind them (layer 2 of the
+// small CNN ran one 8-warp CTA per SM: 12 % of the warp slots, 0.226 ms; see the profile summary).
+template <bool VEC_C, int NT>
+__global__ void __launch_bounds__(NT) k_qconv_wgrad_s1(const CsParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int Np = P.Np, ncg = P.ncg, ng = P.ng, Pt = P.Pt, npx = P.npx, N = P.N;
     const int cg_bytes = npx * 16, img_term = ncg * cg_bytes;
@@ -314,7 +320,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
     unsigned char *IMG = smem;
     unsigned char *GS = IMG + 2 * img_term;
     float *red = reinterpret_cast<float *>(GS + 2 * g_term);           // [256][8] bias-gradient partials
-    uint64_t *bar = reinterpret_cast<uint64_t *>(red + kCwThreads * 8);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(red + NT * 8);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -339,7 +345,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
     const bool relu = P.y != nullptr;
     const int n_units_x = npx * ncg, n_units_g = Pt * ng;
     const int ng_shift = 31 - __clz(ng);
-    const int my_g = tid % ng;  // kCwThreads is a multiple of ng: a thread always stages the same 8 output channels
+    const int my_g = tid % ng;  // NT is a multiple of ng: a thread always stages the same 8 output channels
     float db_r[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) db_r[j] = 0.f;
@@ -350,12 +356,12 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
         const int64_t q0 = tile * Pt;
         int lo_any = 0;
         // ---- image pixels q0 .. q0 + npx ------------------------------------------------------------------------------------
-        for (int u0 = tid; u0 < n_units_x; u0 += 4 * kCwThreads) {
+        for (int u0 = tid; u0 < n_units_x; u0 += 4 * NT) {
             float4 v[4][2];
             int dst[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int u = u0 + i * kCwThreads;
+                const int u = u0 + i * NT;
                 v[i][0] = v[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                 dst[i] = -1;
                 if (u < n_units_x) {
@@ -398,7 +404,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
             }
         }
         // ---- G = dY (* relu mask) at the output positions, zero elsewhere; masked gradient out -----------------------------------
-        for (int u = tid; u < n_units_g; u += kCwThreads) {
+        for (int u = tid; u < n_units_g; u += NT) {
             const int p = u >> ng_shift;  // ng is a power of two; u % ng == my_g
             const int64_t q = q0 + p;
             float g[8];
@@ -479,10 +485,10 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
     float *pw = P.part + (int64_t)blockIdx.x * ((int64_t)(K + 1) * N);
     if (ok) {
         tc::fence_after_sync();
-        const int qlane = (warp & 3) * 32, half = warp >> 2;
+        const int qlane = (warp & 3) * 32, half = (warp >> 2) & 1;
         const int ncol = Np >> 1;
         const int m = qlane + lane, kw = m >> 3, c8 = m & 7;  // accumulator row = (horizontal shift, channel in group)
-        for (int kh = 0; kh < P.KH; ++kh)
+        for (int kh = 0; kh < (warp < 8 ? P.KH : 0); ++kh)  // eight warps read the accumulators out
             for (int cg = 0; cg < ncg; ++cg) {
                 const int c = cg * 8 + c8;
                 const bool live = kw < P.KW && c < P.C;
@@ -503,7 +509,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
                 }
             }
     } else {
-        for (int e = tid; e < K * N; e += kCwThreads) pw[e] = 0.f;
+        for (int e = tid; e < K * N; e += NT) pw[e] = 0.f;
     }
     // bias gradient: threads with the same channel group are summed in a fixed order
     __syncthreads();
@@ -513,7 +519,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
     if (tid < ng * 8) {
         const int g = tid >> 3, j = tid & 7;
         float a = 0.f;
-        for (int t = g; t < kCwThreads; t += ng) a = __fadd_rn(a, red[t * 8 + j]);
+        for (int t = g; t < NT; t += ng) a = __fadd_rn(a, red[t * 8 + j]);
         if (g * 8 + j < N) pw[(int64_t)K * N + g * 8 + j] = a;
     }
     tc::fence_before_sync();
@@ -522,7 +528,7 @@ __global__ void __launch_bounds__(kCwThreads) k_qconv_wgrad_s1(const CsParams P)
 }
 
 struct CsGeom {
-    int Np, Hp, Wp, ncg, ng, Pt, npx, grid, stack;
+    int Np, Hp, Wp, ncg, ng, Pt, npx, grid, stack, nt;
     size_t smem;
     int64_t Q, tiles;
 };
@@ -559,6 +565,16 @@ static int cs_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH
     while (tm < KH * g.ncg * g.Np * (g.stack ? 2 : 1)) tm <<= 1;
     if (per_sm * tm > 512) per_sm = 512 / tm;
     if (per_sm < 1) return HGQ_ERR_SIZE;
+    // fewer than three resident CTAs: wider CTAs (the bias-gradient scratch grows with the thread count)
+    g.nt = kCwThreads;
+    const int want = per_sm == 1 ? 1024 : (per_sm == 2 ? 512 : kCwThreads);
+    if (want > kCwThreads) {
+        const size_t sm2 = g.smem + (size_t)(want - kCwThreads) * 32;
+        if (sm2 <= 226 * 1024 && (int)((228 * 1024) / (sm2 + 1024)) >= per_sm) {
+            g.nt = want;
+            g.smem = sm2;
+        }
+    }
     int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > g.tiles) grid = g.tiles;
     g.grid = (int)grid;
@@ -633,16 +649,23 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
         q.div_img = make_fastdiv((uint32_t)(gs.Hp * gs.Wp));
         q.div_row = make_fastdiv((uint32_t)gs.Wp);
         q.div_cg = make_fastdiv((uint32_t)gs.ncg);
-        cudaError_t ce;
+        cudaError_t ce = cudaSuccess;
+#define HGQ_CS_LAUNCH(VEC_, NT_)                                                                                             \
+    do {                                                                                                                    \
+        ce = cudaFuncSetAttribute(k_qconv_wgrad_s1<VEC_, NT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);  \
+        if (ce != cudaSuccess) return (int)ce;                                                                              \
+        k_qconv_wgrad_s1<VEC_, NT_><<<gs.grid, NT_, gs.smem, st>>>(q);                                                      \
+    } while (0)
         if (C % 4 == 0) {
-            ce = cudaFuncSetAttribute(k_qconv_wgrad_s1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);
-            if (ce != cudaSuccess) return (int)ce;
-            k_qconv_wgrad_s1<true><<<gs.grid, kCwThreads, gs.smem, st>>>(q);
+            if (gs.nt == 1024) HGQ_CS_LAUNCH(true, 1024);
+            else if (gs.nt == 512) HGQ_CS_LAUNCH(true, 512);
+            else HGQ_CS_LAUNCH(true, 256);
         } else {
-            ce = cudaFuncSetAttribute(k_qconv_wgrad_s1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gs.smem);
-            if (ce != cudaSuccess) return (int)ce;
-            k_qconv_wgrad_s1<false><<<gs.grid, kCwThreads, gs.smem, st>>>(q);
+            if (gs.nt == 1024) HGQ_CS_LAUNCH(false, 1024);
+            else if (gs.nt == 512) HGQ_CS_LAUNCH(false, 512);
+            else HGQ_CS_LAUNCH(false, 256);
         }
+#undef HGQ_CS_LAUNCH
         if (int e = check_launch()) return e;
         const int64_t nw = (int64_t)K * N;
         const int64_t nb1 = dbq != nullptr ? N : 0;

@@ -244,8 +244,10 @@ class _Dense(_Node):
         K, N, P = self.K, self.N, self.P
         M = self.x.numel() // K
         if self.oq is not None:
-            g, _, _ = kernels.quantize_bwd(g.contiguous().view(M, N), self.y, None, None, self.oq.F.view(-1), self.oq.q.round_mode,
-                                           'NONE', want_dx=True, want_di=False, out_df=self.oq.dF.view(-1))
+            # a rounding-only quantizer passes the gradient through unchanged: only its df is computed, nothing is copied
+            g = g.contiguous().view(M, N)
+            kernels.quantize_bwd(g, self.y, None, None, self.oq.F.view(-1), self.oq.q.round_mode, 'NONE', want_dx=False,
+                                 want_di=False, out_df=self.oq.dF.view(-1))
         gy_repeat = 1
         if (g.dim() == 3 and g.stride(1) == 0 and g.stride(2) == 1 and g.stride(0) == N and g.size(1) > 1 and M < (1 << 31)):
             gy_repeat, g = g.size(1), g[:, 0, :]  # the gradient of a sum over axis 1: one stored row per sample
@@ -329,10 +331,11 @@ class _Conv(_Node):
         wt = self.wq.view(KH, KW, C, N).flip(0, 1).permute(0, 1, 3, 2).reshape(KH * KW * N, C)
         dxq = kernels.qconv2d_fwd(gm, wt, None, None, KH, KW, (H, W), (1, 1), self.dil,
                                   ((KH - 1) * self.dil[0] - self.pad_tl[0], (KW - 1) * self.dil[1] - self.pad_tl[1]))
-        dx, _, _ = kernels.quantize_bwd(dxq, self.x, None, None, self.iq.F.view(-1), self.iq.q.round_mode, 'NONE', want_dx=need_dx,
-                                        want_di=False, out_df=self.iq.dF.view(-1))
+        # the rounding-only input quantizer passes dxq through unchanged: only its df is computed
+        kernels.quantize_bwd(dxq, self.x, None, None, self.iq.F.view(-1), self.iq.q.round_mode, 'NONE', want_dx=False,
+                             want_di=False, out_df=self.iq.dF.view(-1))
         self.x = self.xq = self.y = None
-        return dx
+        return dxq if need_dx else None
 
     def ebops(self, eng):
         if self.eb_index is None:
@@ -469,8 +472,9 @@ class _Attention(_Node):
         q, k, v, p = self.saved
         B = q.shape[0]
         if self.oq is not None:
-            g, _, _ = kernels.quantize_bwd(g.contiguous(), self.y_pre, None, None, self.oq.F.view(-1), self.oq.q.round_mode, 'NONE',
-                                           want_dx=True, want_di=False, out_df=self.oq.dF.view(-1))
+            g = g.contiguous()
+            kernels.quantize_bwd(g, self.y_pre, None, None, self.oq.F.view(-1), self.oq.q.round_mode, 'NONE', want_dx=False,
+                                 want_di=False, out_df=self.oq.dF.view(-1))
             self.y_pre = None
         go = self.o.backward(g).contiguous()
         dp = kernels.attn_heads_matmul(0, go, v, B, T, H, D)
