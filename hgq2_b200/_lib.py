@@ -109,6 +109,12 @@ SIGNATURES: dict[str, tuple] = {
         + [c_void_p] * 7,
     ),
     'hgq_adam_step': (c_int, [c_void_p] * 7 + [c_int64] + [c_float] * 5 + [c_void_p, c_void_p]),
+    'hgq_peer_exchange_bytes': (c_size_t, [c_int64]),
+    'hgq_peer_buffer_create': (c_int, [c_size_t, c_void_p, c_void_p]),
+    'hgq_peer_buffer_open': (c_int, [c_void_p, c_void_p]),
+    'hgq_peer_buffer_close': (c_int, [c_void_p]),
+    'hgq_peer_buffer_destroy': (c_int, [c_void_p]),
+    'hgq_adam_step_peers': (c_int, [c_void_p] * 7 + [c_int64] + [c_float] * 4 + [c_void_p, c_void_p, c_int, c_int, c_uint, c_void_p, c_void_p]),
     'hgq_tables_forward': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
     'hgq_tables_track_bits': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
     'hgq_tables_backward': (c_int, [c_void_p, c_int, c_int64, c_void_p]),

@@ -113,6 +113,80 @@ class FusedAdam:
             )
         _lib.check(st, 'hgq_adam_step')
 
+    def step_peers(self, peers: 'PeerExchange') -> None:
+        """The update from the MEAN of the ranks' gradient buckets, read over peer memory inside the optimizer kernel
+        (``hgq_adam_step_peers``).  ``state.grads`` keeps this rank's local gradients."""
+        from . import kernels
+
+        s = self.state
+        _lib.require_cuda(s.params)
+        with torch.cuda.device(s.params.device):
+            st = _lib.lib().hgq_adam_step_peers(
+                s.params.data_ptr(), s.grads.data_ptr(), self.m.data_ptr(), self.v.data_ptr(), s.lo.data_ptr(),
+                s.hi.data_ptr(), s.l1.data_ptr(), s.n, self.lr, self.b1, self.b2, self.eps, self.step_count.data_ptr(),
+                peers.ptrs, peers.world, peers.rank, peers.max_polls, kernels.status_word(s.params.device).data_ptr(),
+                _lib.stream_handle(),
+            )
+        _lib.check(st, 'hgq_adam_step_peers')
+
+
+class PeerExchange:
+    """This rank's gradient exchange buffer and its mappings of the other ranks' buffers (CUDA IPC over NVLink), for
+    ``FusedAdam.step_peers``: the gradient sum over the ranks and the optimizer update as one kernel per rank, with plain
+    peer loads instead of an NCCL all-reduce.  One node, one process per GPU.  ``PeerExchange.create`` returns None when
+    some rank cannot map some other rank's buffer (the ranks then agree to keep the NCCL all-reduce)."""
+
+    def __init__(self, own, ptrs, opened, world, rank, device):
+        self.own, self.ptrs, self.opened = own, ptrs, opened
+        self.world, self.rank, self.device = world, rank, device
+        self.max_polls = int(os.environ.get('HGQ_PEER_MAX_POLLS', str(1 << 25)))  # a few seconds of polling at most
+
+    @classmethod
+    def create(cls, dp: 'DataParallel', n: int, device: torch.device):
+        import ctypes
+
+        L = _lib.lib()
+        world, rank = dp.world, dp.rank
+        own = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        ok = 1
+        with torch.cuda.device(device):
+            st = L.hgq_peer_buffer_create(L.hgq_peer_exchange_bytes(n), ctypes.byref(own), handle)
+            if st != 0:
+                ok, own = 0, ctypes.c_void_p()
+            mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8, device=device)
+            gathered = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(gathered, mine, group=dp.group)
+            ptrs = (ctypes.c_void_p * world)()
+            opened = []
+            for r, h in enumerate(gathered):
+                if r == rank:
+                    ptrs[r] = own.value
+                    continue
+                raw = (ctypes.c_ubyte * 64)(*h.cpu().tolist())
+                p = ctypes.c_void_p()
+                if ok and L.hgq_peer_buffer_open(raw, ctypes.byref(p)) == 0:
+                    ptrs[r] = p.value
+                    opened.append(p.value)
+                else:
+                    ok = 0
+            agreed = torch.tensor([ok], dtype=torch.int32, device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=dp.group)
+            self = cls(own.value, ptrs, opened, world, rank, device)
+            if int(agreed.item()) == 0:
+                self.close()
+                return None
+            return self
+
+    def close(self) -> None:
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            for p in self.opened:
+                L.hgq_peer_buffer_close(p)
+            if self.own:
+                L.hgq_peer_buffer_destroy(self.own)
+        self.opened, self.own = [], None
+
 
 def shard_batch(n: int, rank: int, world: int) -> slice:
     """Contiguous, equal shard of a batch of n samples (n must divide evenly so per-rank means average correctly)."""
@@ -214,6 +288,12 @@ class Trainer:
                 if engine is True:
                     raise
                 self.engine_refusal = str(why)
+        # gradient exchange over peer memory inside the optimizer kernel (one node, NCCL process group on GPUs);
+        # HGQ_PEER_EXCHANGE=0 keeps the NCCL all-reduce
+        self.peers = None
+        if (dp is not None and dp.world > 1 and self.state.params.is_cuda and dist.get_backend(dp.group) == 'nccl'
+                and os.environ.get('HGQ_PEER_EXCHANGE', '1') != '0'):
+            self.peers = PeerExchange.create(dp, self.state.n, self.state.params.device)
         self._graphs = []      # captured steps, one per set of static input buffers
         self._sbuf = []        # the static (x, y) buffers the graphs read
         self._next_buf = 0
@@ -246,8 +326,11 @@ class Trainer:
         if self.dp is not None:
             with self.dp:
                 task, total = self.forward_backward(x, y)
-            self.dp.sync_gradients(self.state.grads, average=False)
-            self.opt.step(grad_scale=1.0 / self.dp.world)  # the mean over the ranks, folded into the optimizer kernel
+            if self.peers is not None:
+                self.opt.step_peers(self.peers)  # gradient sum over peer memory and update in one kernel
+            else:
+                self.dp.sync_gradients(self.state.grads, average=False)
+                self.opt.step(grad_scale=1.0 / self.dp.world)  # the mean over the ranks, folded into the optimizer kernel
         else:
             task, total = self.forward_backward(x, y)
             self.opt.step()

@@ -371,6 +371,32 @@ int hgq_adam_step(float *w, const float *g, float *m, float *v, const float *lo,
                   const float *l1, int64_t n, float lr, float beta1, float beta2, float eps,
                   float grad_scale, long long *step, void *stream);
 
+/* ---- gradient exchange over peer memory, fused with the optimizer update ------------------------ */
+
+/*
+ * The data-parallel tail of a step on one node (one process per GPU) as one kernel per rank: every rank publishes its
+ * gradient bucket in a buffer its peers have mapped, waits (bounded) for theirs, adds the buckets in rank order and applies
+ * hgq_adam_step's update with grad_scale = 1 / world.  No reference counterpart in the HGQ2 tree: it stands in for the
+ * gradient all-reduce of Keras' distribution strategy followed by optimizer.apply (see hgq_adam_step).  Plain peer loads
+ * over NVLink; no multicast, no collective library.
+ *
+ * hgq_peer_exchange_bytes(n): size of one rank's exchange buffer for a bucket of n floats.
+ * hgq_peer_buffer_create: cudaMalloc + zero fill on the current device; writes the 64-byte CUDA IPC handle that the other
+ *   processes pass to hgq_peer_buffer_open (which maps the buffer and enables peer access).  close / destroy undo them.
+ * hgq_adam_step_peers: peer_bufs is a HOST array of `world` device pointers (entry `rank` = this rank's own buffer, the
+ *   others as returned by hgq_peer_buffer_open); every rank must call it once per step with the same n, in the same step
+ *   order, each on its own GPU.  max_polls bounds every wait (about 0.1-0.2 us per poll); a wait that runs out sets bit 1
+ *   of *status (may be NULL) and leaves that part of the parameters untouched.  `g` is left as it was (the local gradients).
+ */
+size_t hgq_peer_exchange_bytes(int64_t n);
+int hgq_peer_buffer_create(size_t bytes, void **dev_ptr, void *ipc_handle_64);
+int hgq_peer_buffer_open(const void *ipc_handle_64, void **dev_ptr);
+int hgq_peer_buffer_close(void *dev_ptr);
+int hgq_peer_buffer_destroy(void *dev_ptr);
+int hgq_adam_step_peers(float *w, const float *g, float *m, float *v, const float *lo, const float *hi,
+                        const float *l1, int64_t n, float lr, float beta1, float beta2, float eps, long long *step,
+                        void *const *peer_bufs, int world, int rank, unsigned max_polls, unsigned *status, void *stream);
+
 /* ---- batched parameter-side work of a training step ------------------------------------------ */
 
 /*

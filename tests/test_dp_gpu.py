@@ -29,7 +29,12 @@ def run(builder, X, Y, dp):
     tr = Trainer(model, F.cross_entropy, dp=dp)
     n = X.shape[0]
     sl = shard_batch(n, rank, world) if dp is not None else slice(None)
+    want_peers = dp is not None and os.environ.get('HGQ_PEER_EXCHANGE', '1') != '0'
+    assert (tr.peers is not None) == want_peers, (tr.peers, want_peers)  # gradient exchange inside the optimizer kernel, or NCCL
     losses = [float(tr.step(X[sl], Y[sl])) for _ in range(3)]
+    tr.capture(X[sl], Y[sl], warmup=1)  # then the same step as a CUDA graph: one more eager step, two replays
+    losses += [float(tr.step(X[sl], Y[sl])) for _ in range(2)]
+    tr.check_status(wait=True)
     state = [(v.path, v.value.detach().clone()) for v in model.non_trainable_variables]
     return losses, tr.state.params.clone(), state, [int(l.ebops.item()) for l in model.layers if hasattr(l, '_ebops')]
 
@@ -57,7 +62,10 @@ dist.destroy_process_group()
 '''
 
 
-def test_two_rank_data_parallel_matches_single_rank(tmp_path):
+@pytest.mark.parametrize('peer_exchange', ['1', '0'])
+def test_two_rank_data_parallel_matches_single_rank(tmp_path, peer_exchange):
+    """peer_exchange '1': the gradient sum over peer memory inside the optimizer kernel (the default on one node);
+    '0': NCCL all-reduce followed by the optimizer kernel."""
     if torch.cuda.device_count() < 2:
         pytest.skip('needs 2 GPUs')
     script = tmp_path / 'dp_worker.py'
@@ -65,7 +73,7 @@ def test_two_rank_data_parallel_matches_single_rank(tmp_path):
     with socket.socket() as s:
         s.bind(('127.0.0.1', 0))
         port = s.getsockname()[1]
-    env = dict(os.environ, HGQ_ROOT=str(ROOT), NCCL_NVLS_ENABLE='0')
+    env = dict(os.environ, HGQ_ROOT=str(ROOT), NCCL_NVLS_ENABLE='0', HGQ_PEER_EXCHANGE=peer_exchange)
     r = subprocess.run([sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node=2', '--master-addr', '127.0.0.1',
                         '--master-port', str(port), str(script)], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0 and r.stdout.count('DP_OK') == 2, r.stdout[-2000:] + r.stderr[-4000:]
