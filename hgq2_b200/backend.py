@@ -67,7 +67,8 @@ class Constant(Initializer):
         self.value = value
 
     def __call__(self, shape, dtype=torch.float32, device=None):
-        return torch.full(tuple(shape), float(self.value), dtype=torch.float32, device=device).to(dtype)
+        # built on the host and copied over: a variable's initial value costs no kernel launch on the device
+        return torch.full(tuple(shape), float(self.value), dtype=torch.float32).to(dtype).to(device)
 
     def get_config(self):
         return {'value': self.value}

@@ -150,11 +150,15 @@ extern "C" int hgq_peer_buffer_create(size_t bytes, void **dev_ptr, void *ipc_ha
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
     void *p = nullptr;
     cudaError_t e = cudaMalloc(&p, bytes);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        cudaGetLastError();  // the failure is reported through the return value, not left behind for the next launch check
+        return (int)e;
+    }
     e = cudaMemset(p, 0, bytes);
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t *>(ipc_handle_64), p);
     if (e != cudaSuccess) {
         cudaFree(p);
+        cudaGetLastError();
         return (int)e;
     }
     *dev_ptr = p;
@@ -167,7 +171,10 @@ extern "C" int hgq_peer_buffer_open(const void *ipc_handle_64, void **dev_ptr) {
     memcpy(&h, ipc_handle_64, sizeof(h));
     void *p = nullptr;
     const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        cudaGetLastError();  // e.g. a peer on another node or without peer access: the caller falls back to NCCL
+        return (int)e;
+    }
     *dev_ptr = p;
     return HGQ_OK;
 }

@@ -44,15 +44,21 @@ class FlatState:
             self.offsets.append(off)
             off += (n + 3) // 4 * 4
         self.n = off
-        self.params = torch.zeros(self.n, dtype=torch.float32, device=dev)
+        # one concatenation instead of a copy per variable (padding pieces are slices of one small zero tensor)
+        pad = torch.zeros(3, dtype=torch.float32, device=dev)
+        pieces = []
+        for v, n in zip(self.variables, sizes):
+            pieces.append(v.value.detach().reshape(-1).to(torch.float32))
+            if (-n) % 4:
+                pieces.append(pad[:(-n) % 4])
+        self.params = torch.cat(pieces)
+        assert self.params.numel() == self.n
         self.grads = torch.zeros(self.n, dtype=torch.float32, device=dev)
         lo = torch.full((self.n,), -math.inf, dtype=torch.float32)
         hi = torch.full((self.n,), math.inf, dtype=torch.float32)
         l1 = torch.zeros(self.n, dtype=torch.float32)
         for v, o, n in zip(self.variables, self.offsets, sizes):
-            view = self.params[o:o + n].view(v.value.shape)
-            view.copy_(v.value.detach())
-            v.value.data = view
+            v.value.data = self.params[o:o + n].view(v.value.shape)
             v.value.grad = self.grads[o:o + n].view(v.value.shape)
             c = v.constraint
             if c is None:
