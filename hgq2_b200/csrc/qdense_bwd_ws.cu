@@ -136,7 +136,6 @@ template <bool CONV, int CGN, int CGK, bool RELU, bool TMA>
 __global__ void __launch_bounds__(kBwThreads + (TMA ? 32 : 0), 1) k_qdense_bwd_ws(const BwParams P, const __grid_constant__ CUtensorMap map_g,
                                                                                  const __grid_constant__ CUtensorMap map_y,
                                                                                  const __grid_constant__ CUtensorMap map_x) {
-    constexpr int kThreadsAll = kBwThreads + (TMA ? 32 : 0);
     constexpr int Np = CGN * 8, Kp = CGK * 8;
     constexpr int ITG = CGN / 2, ITX = CGK / 2;  // units (8 rows x 8 columns) a producer thread converts per tile
     constexpr int UNITS = ITG + ITX;
@@ -182,18 +181,50 @@ __global__ void __launch_bounds__(kBwThreads + (TMA ? 32 : 0), 1) k_qdense_bwd_w
         *abort_word = 0;
         tc::mbar_init_fence();
     }
+    // The loader warp (TMA variant) takes no part in the conversions below: once the barriers exist it has the copy engine
+    // fetch the CTA's first tile, so that the copies fly while the other warps convert the weights (on a launch of one
+    // tile per CTA -- small batches -- that is a microsecond or more of the launch's length).
+    constexpr int kSetupThreads = kBwThreads;  // the last warp is the loader
+    constexpr int IBG = (CGN >= 4 ? 128 : 64), IBX = (CGK >= 4 ? 128 : 64);  // bytes per row of a raw box
+    auto fetch_g = [&](int64_t tile) {
+        const uint32_t raw_u = tc::smem_u32(raw);
+        const uint32_t rawy_u = raw_u + 128 * Np * 4;
+        const int g_boxes = (N + 31) / 32;  // a column half that lies past N is not fetched
+        const int row0 = (int)(tile * kBwTileM);
+        const int R = P.g_box_rows;  // 128 unless dY repeats rows
+        const int grow0 = (P.gy_repeat > 1) ? (int)(tile * kBwTileM / P.gy_repeat) : row0;
+        bw_expect_tx(rawg_full, (uint32_t)(g_boxes * IBG * (R + (RELU ? 128 : 0))));
+        for (int b = 0; b < g_boxes; ++b) {
+            bw_tma_load_2d(raw_u + b * R * IBG, &map_g, b * 32, grow0, rawg_full);
+            if (RELU) bw_tma_load_2d(rawy_u + b * 128 * IBG, &map_y, b * 32, row0, rawg_full);
+        }
+    };
+    auto fetch_x = [&](int64_t tile) {
+        const uint32_t rawx_u = tc::smem_u32(raw) + 128 * Np * 4 * (RELU ? 2 : 1);
+        const int x_boxes = (K + 31) / 32;
+        bw_expect_tx(rawx_full, (uint32_t)(x_boxes * 128 * IBX));
+        for (int b = 0; b < x_boxes; ++b) bw_tma_load_2d(rawx_u + b * 128 * IBX, &map_x, b * 32, (int)(tile * kBwTileM), rawx_full);
+    };
+    const bool is_loader = TMA && warp == kBwLoadWarp;
+    if (TMA) {
+        __syncthreads();  // the barriers are initialised
+        if (is_loader && lane == 0 && (int64_t)blockIdx.x < P.num_tiles) {
+            fetch_g(blockIdx.x);
+            fetch_x(blockIdx.x);
+        }
+    }
     if (warp == kBwIssueWarp) tc::tmem_alloc(tmem_slot, tmem_cols);
-    if (has_q)
-        for (int e = tid; e < P.rows_period * P.Kt; e += kThreadsAll) {
+    if (has_q && !is_loader)
+        for (int e = tid; e < P.rows_period * P.Kt; e += kSetupThreads) {
             const int pr = e / P.Kt, k = e % P.Kt;
             const int fi = (k < K) ? __float2int_rn(__ldg(P.qf + pr * K + k)) : 0;
             etab[pr * Ke + k] = (unsigned char)(max(-126, min(127, fi)) + 127);
         }
     // the xq^T operand: column groups that no conversion unit writes (k >= Kp of either term) stay zero for ever
-    for (int e = tid; e < kBwXBytes / 16; e += kThreadsAll) reinterpret_cast<uint4 *>(X)[e] = make_uint4(0, 0, 0, 0);
+    for (int e = tid; e < kBwXBytes / 16 && !is_loader; e += kSetupThreads) reinterpret_cast<uint4 *>(X)[e] = make_uint4(0, 0, 0, 0);
     // weights as the B operand of MMA1: rows k (the product's N index), contraction n; core (k/8, n/8)
     int w_lo = 0, w_lo2 = 0;
-    for (int e = tid; e < Kp * Np; e += kThreadsAll) {
+    for (int e = tid; e < Kp * Np && !is_loader; e += kSetupThreads) {
         const int n = e % Np, k = e / Np;
         const float w = (k < K && n < N) ? __ldg(P.wq + (int64_t)k * N + n) : 0.f;
         __nv_bfloat16 h, l, l2;
@@ -512,37 +543,22 @@ __global__ void __launch_bounds__(kBwThreads + (TMA ? 32 : 0), 1) k_qdense_bwd_w
         // Keeps one raw tile in flight per stream: as soon as every producer warp has taken its units of dY / y (of x) out
         // of the buffer, the copy engine fetches the next tile's into it.  The whole warp walks the loop (it stays
         // converged for the tear-down barrier); lane 0 issues.
-        constexpr int IBG = (CGN >= 4 ? 128 : 64), IBX = (CGK >= 4 ? 128 : 64);
-        constexpr int g_stream_bytes = 128 * Np * 4, x_stream_bytes = 128 * Kp * 4;
-        const uint32_t raw_u = tc::smem_u32(raw);
-        const uint32_t rawy_u = raw_u + g_stream_bytes, rawx_u = raw_u + g_stream_bytes * (RELU ? 2 : 1);
-        const int g_boxes = (N + 31) / 32, x_boxes = (K + 31) / 32;  // a column half that lies past N / K is not fetched
+        // (the first tile's copies were issued during the set-up)
         uint32_t n = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x, ++n) {
-            const int row0 = (int)(tile * kBwTileM);
-            if (n > 0) {
+            if (n == 0) continue;
+            {
                 const bool w = bw_wait(rawg_empty, (n - 1) & 1u, abort_word);
                 if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
             }
-            if (lane == 0) {
-                const int R = P.g_box_rows;  // 128 unless dY repeats rows
-                const int grow0 = (P.gy_repeat > 1) ? (int)(tile * kBwTileM / P.gy_repeat) : row0;
-                bw_expect_tx(rawg_full, (uint32_t)(g_boxes * IBG * (R + (RELU ? 128 : 0))));
-                for (int b = 0; b < g_boxes; ++b) {
-                    bw_tma_load_2d(raw_u + b * R * IBG, &map_g, b * 32, grow0, rawg_full);
-                    if (RELU) bw_tma_load_2d(rawy_u + b * 128 * IBG, &map_y, b * 32, row0, rawg_full);
-                }
-            }
+            if (lane == 0) fetch_g(tile);
             __syncwarp();
-            if (n > 0) {
+            {
                 const bool w = bw_wait(rawx_empty, (n - 1) & 1u, abort_word);
                 if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
             }
-            if (lane == 0) {
-                bw_expect_tx(rawx_full, (uint32_t)(x_boxes * 128 * IBX));
-                for (int b = 0; b < x_boxes; ++b) bw_tma_load_2d(rawx_u + b * 128 * IBX, &map_x, b * 32, row0, rawx_full);
-            }
+            if (lane == 0) fetch_x(tile);
             __syncwarp();
         }
         if (!ok) {

@@ -141,7 +141,6 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
                                                                                        const __grid_constant__ CUtensorMap tmap_y) {
     constexpr int kWsProdWarps = NPW, kWsProd = NPW * 32, kWsEpiWarps = EW, kWsIssueWarp = NPW + EW;
     constexpr int kWsLoadWarp = NPW + EW + 1;  // TMA only
-    constexpr int kWsThreads = (NPW + EW + 1 + (TMA ? 1 : 0)) * 32;
     constexpr int ITS = 32 / NPW;       // 8-row groups a producer thread converts per slab
     constexpr int ROWSTEP = NPW * 4;    // their distance in rows
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -192,21 +191,43 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
             if (P.status) atomicOr(P.status, kWsTimeout);
         }
     }
+    // The loader warp (TMA variant) takes no part in the conversions below: once the barriers exist it has the copy engine
+    // fetch the CTA's first `depth` slabs, so that the copies fly while the other warps convert the weights (on a launch of
+    // one tile per CTA -- small batches -- that is a microsecond or more of the launch's length).
+    constexpr int kSetupThreads = (NPW + EW + 1) * 32;  // the last warp is the loader
+    const int n_chunks = (Kpad + kWsKC - 1) / kWsKC;
+    auto fetch_slab = [&](int64_t tile, int ch, uint32_t rb) {
+        const int c0 = ch * kWsKC;
+        const int halves = (K - c0 > 32) ? 2 : 1;  // a column half that lies past K is not fetched at all
+        ws_expect_tx(raw_full + rb, (uint32_t)(halves * (kWsFetchBytes / 2)));
+        const uint32_t dst = tc::smem_u32(fetch) + rb * kWsFetchBytes;
+        for (int hcol = 0; hcol < halves; ++hcol)
+            ws_tma_load_2d(dst + hcol * (kWsFetchBytes / 2), &tmap, c0 + hcol * 32, (int)(tile * kWsTileM), raw_full + rb);
+    };
+    const bool is_loader = TMA && warp == kWsLoadWarp;
+    if (TMA) {
+        __syncthreads();  // the barriers are initialised, the abort word is set
+        if (is_loader && lane == 0 && *reinterpret_cast<volatile int *>(abort_word) == 0) {
+            uint32_t n = 0;
+            for (int64_t tile = blockIdx.x; tile < P.num_tiles && n < (uint32_t)P.depth; tile += gridDim.x)
+                for (int ch = 0; ch < n_chunks && n < (uint32_t)P.depth; ++ch, ++n) fetch_slab(tile, ch, P.depth == 2 ? (n & 1u) : 0u);
+        }
+    }
     if (warp == kWsIssueWarp) tc::tmem_alloc(tmem_slot, tmem_cols);
-    for (int e = tid; e < Npad; e += kWsThreads) bias_s[e] = (P.bq != nullptr && e < N) ? __ldg(P.bq + e) : 0.f;
-    for (int e = tid; e < amax_elems; e += kWsThreads) amax_t[e] = 0.f;
-    for (int e = tid; e < P.rows_period * P.Kt; e += kWsThreads) {
+    for (int e = tid; e < Npad && !is_loader; e += kSetupThreads) bias_s[e] = (P.bq != nullptr && e < N) ? __ldg(P.bq + e) : 0.f;
+    for (int e = tid; e < amax_elems && !is_loader; e += kSetupThreads) amax_t[e] = 0.f;
+    for (int e = tid; e < P.rows_period * P.Kt && !is_loader; e += kSetupThreads) {
         const int pr = e / P.Kt, k = e % P.Kt;
         const int fi = (k < K) ? __float2int_rn(__ldg(P.qf + pr * K + k)) : 0;
         etab[pr * Ke + k] = (unsigned char)(max(-126, min(127, fi)) + 127);
     }
     // the third-term buffers hold zeros until a tile needs them
     for (int s = 0; s < 2; ++s)
-        for (int e = tid; e < kWsTermBytes / 16; e += kWsThreads)
+        for (int e = tid; e < kWsTermBytes / 16 && !is_loader; e += kSetupThreads)
             reinterpret_cast<uint4 *>(A + s * kWsStageBytes + 2 * kWsTermBytes)[e] = make_uint4(0, 0, 0, 0);
     // weights: fp32 [K, N] -> up to three bf16 terms, K-major core matrices: (n/8, k/8) -> 128-byte block
     int w_lo = 0, w_lo2 = 0;
-    for (int e = tid; e < Kpad * Npad; e += kWsThreads) {
+    for (int e = tid; e < Kpad * Npad && !is_loader; e += kSetupThreads) {
         const int n = e % Npad, k = e / Npad;
         const float w = (k < K && n < N) ? __ldg(P.wq + (int64_t)k * N + n) : 0.f;
         __nv_bfloat16 h, l, l2;
@@ -226,7 +247,6 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const int n_chunks = (Kpad + kWsKC - 1) / kWsKC;
 
     if (warp < kWsProdWarps) {
         // ================================ producers ==================================================================
@@ -474,18 +494,10 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
         for (int64_t tile = blockIdx.x; tile < P.num_tiles && ok; tile += gridDim.x) {
             for (int ch = 0; ch < n_chunks && ok; ++ch, ++n) {
                 const uint32_t rb = depth == 2 ? (n & 1u) : 0u, ruse = depth == 2 ? (n >> 1) : n;
-                if (ruse > 0) {
-                    const bool w = ws_wait(raw_empty + rb, (ruse - 1) & 1u, abort_word);
-                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
-                }
-                if (lane == 0) {
-                    const int c0 = ch * kWsKC;
-                    const int halves = (K - c0 > 32) ? 2 : 1;  // a column half that lies past K is not fetched at all
-                    ws_expect_tx(raw_full + rb, (uint32_t)(halves * (kWsFetchBytes / 2)));
-                    const uint32_t dst = fetch_base + rb * kWsFetchBytes;
-                    for (int hcol = 0; hcol < halves; ++hcol)
-                        ws_tma_load_2d(dst + hcol * (kWsFetchBytes / 2), &tmap, c0 + hcol * 32, (int)(tile * kWsTileM), raw_full + rb);
-                }
+                if (ruse == 0) continue;  // the first `depth` slabs were requested during the set-up
+                const bool w = ws_wait(raw_empty + rb, (ruse - 1) & 1u, abort_word);
+                if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                if (lane == 0) fetch_slab(tile, ch, rb);
                 __syncwarp();
             }
         }

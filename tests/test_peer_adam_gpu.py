@@ -121,3 +121,20 @@ def test_argument_errors():
     assert L.hgq_peer_buffer_create(0, None, None) == -1
     assert L.hgq_adam_step_peers(None, None, None, None, None, None, None, 16, 1e-3, 0.9, 0.999, 1e-7, None, None, 2, 0, 10, None,
                                  None) == -1
+
+
+def test_a_handle_that_cannot_be_opened_is_an_error_code_not_a_sticky_failure():
+    """A rank that cannot map a peer's buffer (here: a handle of zeros) gets an error code -- the trainer then keeps the NCCL
+    route -- and the next kernel launch check of the library is clean."""
+    from hgq2_b200 import _lib, kernels
+
+    L = _lib.lib()
+    torch.cuda.set_device(0)
+    bogus = (ctypes.c_ubyte * 64)()
+    p = ctypes.c_void_p()
+    assert L.hgq_peer_buffer_open(bogus, ctypes.byref(p)) != 0
+    x = torch.randn(1024, device='cuda')
+    f = torch.full((1024,), 4.0, device='cuda')
+    y = kernels.quantize_fwd(x, None, None, f, 'RND', 'NONE', training=True)
+    y = y[0] if isinstance(y, tuple) else y
+    assert torch.equal(y, torch.floor(x * 16 + 0.5) / 16)
