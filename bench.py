@@ -526,7 +526,8 @@ def run_qdense(args):
     f = torch.full((rp, K), 6.0, device=dev)
     w = (torch.randint(-128, 128, (K, N), device=dev, generator=gen).float() / 64.0)
     b = torch.zeros(N, device=dev)
-    fn = lambda: kernels.qdense_fwd(x, None, None, f, rp, 'RND', 'WRAP', True, False, w, b, 'relu', True)
+    # --pool-rows P: the kernel also sums y over groups of P consecutive rows (the particle tagger's sum over particles)
+    fn = lambda: kernels.qdense_fwd(x, None, None, f, rp, 'RND', 'WRAP', True, False, w, b, 'relu', True, pool_rows=args.pool_rows)
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
@@ -540,7 +541,7 @@ def run_qdense(args):
     ms = a.elapsed_time(bb) / args.steps
     peak, kind = measured_peaks()
     gbs = 4.0 * (K + N) * M / (ms * 1e-3) / 1e9
-    print(json.dumps({'kernel': 'k_qdense_fwd', 'M': M, 'K': K, 'N': N, 'rows_period': rp, 'ms': round(ms, 4),
+    print(json.dumps({'kernel': 'k_qdense_fwd', 'M': M, 'K': K, 'N': N, 'rows_period': rp, 'pool_rows': args.pool_rows, 'ms': round(ms, 4),
                       'achieved_GBs': round(gbs, 1), 'peak_GBs': peak, 'frac': round(gbs / peak, 4), 'peak_source': kind,
                       'tflops': round(2.0 * M * K * N / (ms * 1e-3) / 1e12, 2)}), flush=True)
 
@@ -756,6 +757,7 @@ def main():
     ap.add_argument('--k', type=int, default=64)
     ap.add_argument('--n', type=int, default=64)
     ap.add_argument('--rows-period', type=int, default=64)
+    ap.add_argument('--pool-rows', type=int, default=0, help="--workload qdense: also produce the sums over groups of this many rows")
     args = ap.parse_args()
     globals()['TOTAL_ELEMS'] = args.elements
     if args.workload == 'qdense':

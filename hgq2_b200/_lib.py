@@ -58,6 +58,12 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_uint, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
          c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    'hgq_qdense_fwd_pooled_supported': (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int]),
+    'hgq_qdense_fwd_pooled': (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_uint, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+         c_void_p, c_int, c_float, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
     'hgq_qdense_bwd_workspace': (c_size_t, [c_int64, c_int, c_int, c_int]),
     'hgq_qdense_bwd': (
         c_int,

@@ -511,8 +511,11 @@ __global__ void __launch_bounds__(kThreads) k_amax_stage2(const unsigned *__rest
 }
 
 int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round_mode, const float *wq, const float *bq,
-                     int activation, float *y, unsigned *amax_part, int amax_direct, int64_t M, int K, int N, int Kpad, int Npad,
-                     int Kt, unsigned *status, cudaStream_t st, int *grid);
+                     int activation, float *y, unsigned *amax_part, int amax_direct, float *pool_out, int pool_rows,
+                     float pool_scale, int64_t M, int K, int N, int Kpad, int Npad, int Kt, unsigned *status, cudaStream_t st,
+                     int *grid);
+
+bool qdense_ws_pool_supported(int64_t M, int K, int N, int Kpad, int Npad, int Kt, int rows_period, int pool_rows, bool want_amax);
 
 // HGQ_QDENSE_WS=0 in the environment keeps every call on the general kernel (for comparisons).
 static bool ws_enabled() {
@@ -568,10 +571,25 @@ extern "C" size_t hgq_qdense_fwd_workspace(int64_t M, int K, int N, int rows_per
     return (size_t)num_sms() * 4 * rows_period * K * sizeof(unsigned);  // room for the largest grid any variant launches
 }
 
+extern "C" int hgq_qdense_fwd_pooled_supported(int64_t M, int K, int N, int rows_period, int pool_rows, int want_absmax) {
+    QdGeom g;
+    if (qd_geom(M, K, N, rows_period, want_absmax != 0, true, g) != HGQ_OK || !ws_enabled()) return 0;
+    return qdense_ws_pool_supported(M, K, N, g.Kpad, g.Npad, g.Kt, rows_period, pool_rows, want_absmax != 0) ? 1 : 0;
+}
+
 extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi, const float *qf, int rows_period,
                               int round_mode, int overflow_mode, unsigned flags, const float *wq, const float *bq,
                               int activation, float *y, float *absmax, int64_t M, int K, int N, void *workspace,
                               size_t workspace_bytes, unsigned *status, void *stream) {
+    return hgq_qdense_fwd_pooled(x, qk, qi, qf, rows_period, round_mode, overflow_mode, flags, wq, bq, activation, y, absmax, nullptr,
+                                 0, 0.f, M, K, N, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int hgq_qdense_fwd_pooled(const float *x, const uint8_t *qk, const float *qi, const float *qf, int rows_period,
+                                     int round_mode, int overflow_mode, unsigned flags, const float *wq, const float *bq,
+                                     int activation, float *y, float *absmax, float *pool_out, int pool_rows, float pool_scale,
+                                     int64_t M, int K, int N, void *workspace, size_t workspace_bytes, unsigned *status,
+                                     void *stream) {
     if (x == nullptr || wq == nullptr || y == nullptr) return HGQ_ERR_NULL;
     if (round_mode < 0 || round_mode > 2 || overflow_mode < 0 || overflow_mode > 3) return HGQ_ERR_MODE;
     if (activation != ACT_NONE && activation != ACT_RELU) return HGQ_ERR_MODE;
@@ -602,8 +620,8 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
     if (fastq && ws_enabled()) {
         // the common training case has a warp-specialised kernel of its own
         int ws_grid = 0;
-        const int r = qdense_ws_launch(x, qf, rows_period, round_mode, wq, bq, activation, y, p.amax_part, p.amax_direct, M, K, N,
-                                       g.Kpad, g.Npad, g.Kt, status, st, &ws_grid);
+        const int r = qdense_ws_launch(x, qf, rows_period, round_mode, wq, bq, activation, y, p.amax_part, p.amax_direct, pool_out,
+                                       pool_rows, pool_scale, M, K, N, g.Kpad, g.Npad, g.Kt, status, st, &ws_grid);
         if (r < 0) return -r;
         if (r == 1) {
             if (int e = check_launch()) return e;
@@ -615,6 +633,7 @@ extern "C" int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi
             return HGQ_OK;
         }
     }
+    if (pool_out != nullptr) return HGQ_ERR_SIZE;  // row-group sums exist in the warp-specialised kernel's bulk-store path only
     int amax_mode = AMAX_NONE;
     if (absmax) {
         if (!fastq) amax_mode = AMAX_ATOMIC;

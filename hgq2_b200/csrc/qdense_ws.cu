@@ -64,6 +64,9 @@ struct WsParams {
     int rm, act;
     int depth;            // raw slabs in flight ahead of the conversion: 1 or 2
     int tma_store;        // the epilogue hands finished 128 x 32 blocks to the copy engine (tiled bulk-tensor stores)
+    float *pool_out;      // [M / pool_rows, N]: pool_scale * (sum of y over every group of pool_rows consecutive rows), or nullptr
+    int pool_rows;        // 32, 64 or 128 (bulk-store path only)
+    float pool_scale;
 };
 
 __device__ __forceinline__ void ws_arrive(uint64_t *bar) {
@@ -168,6 +171,7 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(full + 12);
     int *dirty3 = reinterpret_cast<int *>(tmem_slot + 1);  // per stage: some tile needed the third term (sticky)
     int *abort_word = dirty3 + 2;
+    float *pool_s = reinterpret_cast<float *>(abort_word + 2);  // row-group sums only: [2 column parts][4 warps][32] floats
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = P.K, N = P.N, Kpad = P.Kpad, Npad = P.Npad;
@@ -566,6 +570,36 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
                     tc::fence_smem_to_async();
                     asm volatile("bar.sync %0, 128;" ::"r"(3 + part) : "memory");
                     if (leader) ws_tma_store_2d(&tmap_y, c0, (int)(tile * kWsTileM), tc::smem_u32(box));
+                    // Sum over groups of pool_rows consecutive rows (the reduction over an axis that follows the layer), from
+                    // the finished block while the copy engine reads it.  lane = column; every warp adds its own 32 rows
+                    // (four interleaved partial sums, combined as (a0 + a1) + (a2 + a3): a fixed order; one row of the block
+                    // per load: 32 lanes read 32 different words of a 128-byte row, whatever the chunk swizzle).  Groups of 64
+                    // or 128 rows: the warps of a group leave their sums in shared memory, meet at a named barrier, and the
+                    // group's first warp adds them in ascending row order.  Groups never straddle the end of y (M is a
+                    // multiple of pool_rows), so a group is written iff its first row exists.
+                    if (P.pool_out != nullptr) {
+                        float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int rr = 0; rr < 32; ++rr) {
+                            const int r = q * 32 + rr;
+                            a4[rr & 3] = __fadd_rn(a4[rr & 3], *reinterpret_cast<const float *>(box + r * 128 + ((((lane >> 2) ^ (r & 7)) << 4) | ((lane & 3) << 2))));
+                        }
+                        float sum = __fadd_rn(__fadd_rn(a4[0], a4[1]), __fadd_rn(a4[2], a4[3]));
+                        const int wpg = P.pool_rows >> 5;  // warps per group: 1, 2 or 4
+                        if (wpg > 1) {
+                            float *slot = pool_s + part * 128;
+                            slot[q * 32 + lane] = sum;
+                            if (wpg == 2) asm volatile("bar.sync %0, 64;" ::"r"(5 + part * 2 + (q >> 1)) : "memory");
+                            else asm volatile("bar.sync %0, 128;" ::"r"(3 + part) : "memory");
+                            if ((q & (wpg - 1)) == 0) {
+                                sum = slot[q * 32 + lane];
+                                for (int k2 = 1; k2 < wpg; ++k2) sum = __fadd_rn(sum, slot[(q + k2) * 32 + lane]);
+                            }
+                        }
+                        const int64_t grow = tile * kWsTileM + q * 32;
+                        if ((q & (wpg - 1)) == 0 && grow < P.M && c0 + lane < N)
+                            P.pool_out[(grow / P.pool_rows) * N + c0 + lane] = __fmul_rn(sum, P.pool_scale);
+                    }
                     continue;
                 }
 #pragma unroll
@@ -674,36 +708,57 @@ static bool ws_make_tmap(CUtensorMap *map, const float *x, int64_t M, int K) {
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Launches the warp-specialised kernel when it covers the call; returns 1 with the grid size in *grid, 0 when the call is
-// not covered (the caller then takes the general kernel), or a negative CUDA error code.
-int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round_mode, const float *wq, const float *bq,
-                     int activation, float *y, unsigned *amax_part, int amax_direct, int64_t M, int K, int N, int Kpad, int Npad,
-                     int Kt, unsigned *status, cudaStream_t st, int *grid) {
-    if (qf == nullptr || K % 4 != 0 || !aligned(x, 16) || !aligned(y, 4)) return 0;
-    if (2 * Npad > 512) return 0;
-    // Warp split: 8 producer and 8 epilogue warps.  Measured on the particle-layer shape (ms per launch): 8/8 0.53,
-    // 16/8 0.63, 8/4 0.77, 16/4 0.80 -- more producer warps cost registers and add per-warp overhead, fewer epilogue warps
-    // fall behind.
-    constexpr int npw = 8, ew = 8;
-    const bool want_amax = amax_part != nullptr;
+// Warp split: 8 producer and 8 epilogue warps.  Measured on the particle-layer shape (ms per launch): 8/8 0.53, 16/8 0.63,
+// 8/4 0.77, 16/4 0.80 -- more producer warps cost registers and add per-warp overhead, fewer epilogue warps fall behind.
+constexpr int kWsNpw = 8, kWsEw = 8;
+
+// Abs-max bookkeeping mode, raw slabs in flight and shared-memory size of a launch; false when the kernel does not cover it.
+static bool ws_plan(int Kpad, int Npad, int Kt, int rows_period, bool want_amax, int &amax_mode, int &depth, size_t &smem) {
+    if (2 * Npad > 512) return false;
     const bool one_slab = Kpad <= kWsKC;
-    const int rowstep = npw * 4;
-    int depth = 2;
-    int amax_mode = WS_AMAX_NONE;
+    const int rowstep = kWsNpw * 4;
+    depth = 2;
+    amax_mode = WS_AMAX_NONE;
     if (want_amax) {
         const bool plain_ok = (rows_period % rowstep == 0) && (kWsTileM % rows_period == 0);
         if (one_slab && rowstep % rows_period == 0) amax_mode = WS_AMAX_REGS1;
         else if (one_slab && (2 * rowstep) % rows_period == 0 && (size_t)rows_period * (Kt + 4) * 4 <= kWsFetchBytes) amax_mode = WS_AMAX_REGS2;
         else if (plain_ok) amax_mode = WS_AMAX_PLAIN;
-        else return 0;
+        else return false;
     }
     const bool amax_table = amax_mode == WS_AMAX_PLAIN;
-    size_t smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth, ew);
+    smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth, kWsEw);
     if (smem > 227 * 1024) {
         depth = 1;
-        smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth, ew);
+        smem = qdense_ws_smem(Kpad, Npad, Kt, rows_period, amax_table, depth, kWsEw);
     }
-    if (smem > 227 * 1024) return 0;
+    return smem + 1024 <= 227 * 1024;  // + room to start the carve on a 1 KB boundary
+}
+
+// Whether a forward call with these sizes can also produce the sums over groups of pool_rows consecutive rows (pointer
+// alignment aside: x, y 16-byte aligned).
+bool qdense_ws_pool_supported(int64_t M, int K, int N, int Kpad, int Npad, int Kt, int rows_period, int pool_rows, bool want_amax) {
+    if (K % 4 != 0 || N % 4 != 0 || Npad / (kWsEw / 4) < 32 || M <= 0 || M >= ((int64_t)1 << 31)) return false;
+    if ((pool_rows != 32 && pool_rows != 64 && pool_rows != 128) || M % pool_rows != 0) return false;
+    if (!ws_tma_store_enabled() || encode_tiled_fn() == nullptr) return false;
+    int amax_mode, depth;
+    size_t smem;
+    return ws_plan(Kpad, Npad, Kt, rows_period, want_amax, amax_mode, depth, smem);
+}
+
+// Launches the warp-specialised kernel when it covers the call; returns 1 with the grid size in *grid, 0 when the call is
+// not covered (the caller then takes the general kernel), or a negative CUDA error code.
+int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round_mode, const float *wq, const float *bq,
+                     int activation, float *y, unsigned *amax_part, int amax_direct, float *pool_out, int pool_rows,
+                     float pool_scale, int64_t M, int K, int N, int Kpad, int Npad, int Kt, unsigned *status, cudaStream_t st,
+                     int *grid) {
+    if (qf == nullptr || K % 4 != 0 || !aligned(x, 16) || !aligned(y, 4)) return 0;
+    if (pool_out != nullptr && ((pool_rows != 32 && pool_rows != 64 && pool_rows != 128) || M % pool_rows != 0)) return 0;
+    constexpr int npw = kWsNpw, ew = kWsEw;
+    const bool want_amax = amax_part != nullptr;
+    int depth = 2, amax_mode = WS_AMAX_NONE;
+    size_t smem = 0;
+    if (!ws_plan(Kpad, Npad, Kt, rows_period, want_amax, amax_mode, depth, smem)) return 0;
     WsParams p;
     p.x = x; p.qf = qf; p.wq = wq; p.bq = bq; p.y = y; p.amax_part = amax_part; p.amax_direct = amax_direct; p.status = status;
     p.M = M; p.num_tiles = (M + kWsTileM - 1) / kWsTileM;
@@ -721,6 +776,9 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
     const bool tstore = ws_tma_store_enabled() && N % 4 == 0 && aligned(y, 16) && Npad / (ew / 4) >= 32 && M < ((int64_t)1 << 31) &&
                         ws_make_tmap(&tmap_y, y, M, N);
     p.tma_store = tstore ? 1 : 0;
+    if (pool_out != nullptr && !tstore) return 0;  // the row-group sums are taken from the blocks of the bulk-store path
+    p.pool_out = pool_out; p.pool_rows = pool_rows; p.pool_scale = pool_scale;
+    if (pool_out != nullptr) smem += 1024;  // the warps' partial sums
     smem += 1024;  // room to start the carve on a 1 KB boundary whatever the base of dynamic shared memory is
     if (smem > 227 * 1024) return 0;
 #define HGQ_WS_LAUNCH1(CV, AM, PW, EWW, TM)                                                                                      \

@@ -121,9 +121,13 @@ class _Reduce(_Node):
 
     def __init__(self, mean):
         self.mean = mean
+        self.ready = None  # the result, when the layer before produced it in its own kernel (see _Dense.pool)
 
     def forward(self, x):
         self.in_shape = x.shape
+        if self.ready is not None:
+            out, self.ready = self.ready, None
+            return out
         return x.mean(dim=1) if self.mean else x.sum(dim=1)
 
     def backward(self, g, need_dx=True):
@@ -214,12 +218,15 @@ class _Dense(_Node):
             _require(self.oq.n == int(np.prod(self.out_tail)), f'{layer.name}: output bitwidth table is not per activation')
             self.oq.tracked_act = True
         self.eb_index = eng.new_ebops_term() if layer.enable_ebops else None
+        self.pool = None        # the _Reduce node that follows, when it sums this layer's output over its P rows per sample
+        self._pool_ok = {}      # batch -> whether the forward kernel can produce that sum itself
 
     def check(self, batch):
         K, N, P = self.K, self.N, self.P
         M = batch * P
         if not (kernels.qdense_supported(M, K, N, P) and kernels.qdense_bwd_supported(M, K, N, P)):
             raise Unsupported(f'{self.layer.name}: M={M} K={K} N={N} period={P} outside the fused kernels')
+        self._pool_ok[batch] = self.pool is not None and kernels.qdense_pooled_supported(M, K, N, P, P)
 
     def post_allocate(self, eng):
         self.wq, self.dwq = self.wq.t, self.dwq.t
@@ -230,9 +237,16 @@ class _Dense(_Node):
         K, N, P = self.K, self.N, self.P
         x = x.contiguous()
         rm = self.iq.q.round_mode
-        y, _ = kernels.qdense_fwd(x, None, None, self.iq.F.view(P, K), P, rm, 'NONE', True, False, self.wq.view(K, N),
-                                  self.bias_q, 'relu' if self.relu else None, True, absmax_out=self.iq.absmax,
-                                  absmax_accumulate=True)  # the step zeroed the statistics of every quantizer at its start
+        if self._pool_ok.get(x.shape[0], False):
+            # the reduction over the P rows of a sample that follows the layer, taken from the finished blocks on chip
+            y, _, pooled = kernels.qdense_fwd(x, None, None, self.iq.F.view(P, K), P, rm, 'NONE', True, False, self.wq.view(K, N),
+                                              self.bias_q, 'relu' if self.relu else None, True, absmax_out=self.iq.absmax,
+                                              absmax_accumulate=True, pool_rows=P, pool_scale=(1.0 / P) if self.pool.mean else 1.0)
+            self.pool.ready = pooled
+        else:
+            y, _ = kernels.qdense_fwd(x, None, None, self.iq.F.view(P, K), P, rm, 'NONE', True, False, self.wq.view(K, N),
+                                      self.bias_q, 'relu' if self.relu else None, True, absmax_out=self.iq.absmax,
+                                      absmax_accumulate=True)  # the step zeroed the statistics of every quantizer at its start
         self.x, self.y = x, (y if (self.relu or self.oq is not None) else None)
         out_shape = (x.shape[0],) + self.out_tail
         if self.oq is not None:
@@ -534,6 +548,10 @@ class Engine:
             node, shape = self._make_node(layer, shape)
             self.nodes.append(node)
         _require(self.slots, 'no quantised layer')
+        # a dense layer followed by a sum / mean over its row axis hands the reduction to its own forward kernel
+        for a, b in zip(self.nodes, self.nodes[1:]):
+            if isinstance(a, _Dense) and isinstance(b, _Reduce) and a.oq is None and len(a.out_tail) == 2 and a.out_tail[0] == a.P:
+                a.pool = b
         self._allocate()
         for node in self.nodes:
             node.post_allocate(self)

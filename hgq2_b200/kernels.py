@@ -243,9 +243,12 @@ def qdense_supported(M: int, K: int, N: int, rows_period: int) -> bool:
 
 
 def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: str, training: bool, zero_nonpos: bool,
-               wq, bq, activation: str | None, want_absmax: bool, absmax_out=None, absmax_accumulate: bool = False):
+               wq, bq, activation: str | None, want_absmax: bool, absmax_out=None, absmax_accumulate: bool = False,
+               pool_rows: int = 0, pool_scale: float = 1.0):
     """Fused y = act(iq(x) @ wq + bq); x is treated as [M, K] with K = wq.shape[0].  Returns (y [M, N], absmax or None).
-    With ``absmax_accumulate`` the statistic is merged into ``absmax_out`` by atomic max (the caller zeroed it)."""
+    With ``absmax_accumulate`` the statistic is merged into ``absmax_out`` by atomic max (the caller zeroed it).
+    With ``pool_rows`` > 0 a third value is returned: ``pool_scale`` times the sum of y over every group of ``pool_rows``
+    consecutive rows, [M / pool_rows, N] (shapes for which ``qdense_pooled_supported`` is true)."""
     require_cuda(x, qk, qi, qf, wq, bq)
     rm, om = _modes(round_mode, overflow_mode)
     x = x.contiguous()
@@ -261,13 +264,27 @@ def qdense_fwd(x, qk, qi, qf, rows_period: int, round_mode: str, overflow_mode: 
     ws = workspace(lib().hgq_qdense_fwd_workspace(M, K, N, rows_period), x.device, slot=1) if (want_absmax and not accumulate) else None
     act = {None: 0, 'relu': 1}[activation]
     flags = (FLAG_TRAINING if training else 0) | (FLAG_ZERO_NONPOS if zero_nonpos else 0) | (FLAG_ABSMAX_ACCUMULATE if accumulate else 0)
+    pooled = torch.empty((M // pool_rows, N), dtype=torch.float32, device=x.device) if pool_rows else None
     with torch.cuda.device(x.device):
-        st = lib().hgq_qdense_fwd(
-            ptr(x), ptr(qk), ptr(qi), ptr(qf), rows_period, rm, om, flags, ptr(wq), ptr(bq), act, ptr(y), ptr(absmax), M, K, N,
-            ptr(ws), ws.numel() if ws is not None else 0, ptr(status_word(x.device)), stream_handle(),
-        )
-    check(st, 'hgq_qdense_fwd')
+        if pool_rows:
+            st = lib().hgq_qdense_fwd_pooled(
+                ptr(x), ptr(qk), ptr(qi), ptr(qf), rows_period, rm, om, flags, ptr(wq), ptr(bq), act, ptr(y), ptr(absmax),
+                ptr(pooled), pool_rows, float(pool_scale), M, K, N, ptr(ws), ws.numel() if ws is not None else 0,
+                ptr(status_word(x.device)), stream_handle(),
+            )
+        else:
+            st = lib().hgq_qdense_fwd(
+                ptr(x), ptr(qk), ptr(qi), ptr(qf), rows_period, rm, om, flags, ptr(wq), ptr(bq), act, ptr(y), ptr(absmax), M, K, N,
+                ptr(ws), ws.numel() if ws is not None else 0, ptr(status_word(x.device)), stream_handle(),
+            )
+    check(st, 'hgq_qdense_fwd_pooled' if pool_rows else 'hgq_qdense_fwd')
+    if pool_rows:
+        return y, absmax, pooled
     return y, absmax
+
+
+def qdense_pooled_supported(M: int, K: int, N: int, rows_period: int, pool_rows: int, want_absmax: bool = True) -> bool:
+    return bool(lib().hgq_qdense_fwd_pooled_supported(M, K, N, rows_period, pool_rows, int(want_absmax)))
 
 
 _QB_KBLOCK = 64  # input columns one backward launch covers

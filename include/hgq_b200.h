@@ -179,6 +179,22 @@ int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi, const flo
                    size_t workspace_bytes, unsigned *status, void *stream);
 
 /*
+ * hgq_qdense_fwd that also returns the sum of y over every group of pool_rows consecutive rows, times pool_scale:
+ * pool_out [M / pool_rows, N].  Stands in for a layer followed by a reduction over the axis its rows run along, e.g.
+ * `QEinsumDense('bpc,cd->bpd')` followed by `ops.sum(x, axis=1)` / `ops.mean(x, axis=1)` with pool_rows = p (the particle-set
+ * models of the reference's examples): the reduction reads the finished blocks on chip instead of reading y back from memory.
+ * y is written as usual (the backward pass needs it).  Rows of a group are added in ascending order.
+ * Covered: the training-mode case on the warp-specialised kernel with bulk stores (input quantizer that only rounds, K and N
+ * multiples of 4, N >= 33, pool_rows 32, 64 or 128 dividing M); hgq_qdense_fwd_pooled_supported says whether a shape is
+ * (HGQ_ERR_SIZE otherwise; pool_out == NULL makes the call plain hgq_qdense_fwd).
+ */
+int hgq_qdense_fwd_pooled_supported(int64_t M, int K, int N, int rows_period, int pool_rows, int want_absmax);
+int hgq_qdense_fwd_pooled(const float *x, const uint8_t *qk, const float *qi, const float *qf, int rows_period,
+                          int round_mode, int overflow_mode, unsigned flags, const float *wq, const float *bq,
+                          int activation, float *y, float *absmax, float *pool_out, int pool_rows, float pool_scale,
+                          int64_t M, int K, int N, void *workspace, size_t workspace_bytes, unsigned *status, void *stream);
+
+/*
  * Scratch bytes hgq_qdense_bwd needs (0 if the shape is not supported by the fused backward).
  */
 size_t hgq_qdense_bwd_workspace(int64_t M, int K, int N, int rows_period);

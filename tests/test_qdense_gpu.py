@@ -51,6 +51,36 @@ def test_fused_dense_forward(M, K, N, rows_period, rm, om, training):
         assert torch.equal(amax.cpu().view(rows_period, K), ar), 'absmax'
 
 
+@pytest.mark.parametrize('M,K,N,pool_rows,rows_period', [
+    (64 * 301, 16, 64, 64, 64),    # the particle layers: 64 particles per sample; the last tile holds one sample
+    (64 * 300, 64, 64, 64, 64),
+    (32 * 77, 32, 64, 32, 32),     # a group per epilogue warp
+    (128 * 9, 64, 128, 128, 1),    # a group per tile, two column pieces per epilogue warp
+    (64 * 10, 64, 36, 64, 64),     # padded output columns
+])
+def test_fused_dense_forward_with_row_group_sums(M, K, N, pool_rows, rows_period):
+    """hgq_qdense_fwd_pooled: the sums over groups of consecutive rows come out of the forward kernel and equal the sums
+    of the y it writes (exactly for quantised operands: every partial sum is exact in fp32), scaled as asked."""
+    from hgq2_b200 import kernels
+
+    assert kernels.qdense_pooled_supported(M, K, N, rows_period, pool_rows)
+    assert not kernels.qdense_pooled_supported(M + 4, K, N, rows_period, pool_rows)  # groups must tile the rows
+    rng = np.random.default_rng(M + N)
+    x = torch.from_numpy((rng.standard_normal((M, K)) * 3).astype(np.float32)).cuda()
+    f = torch.from_numpy(rng.integers(1, 7, (rows_period, K)).astype(np.float32)).cuda()
+    w = torch.from_numpy(np.round(rng.uniform(-2, 2, (K, N)) * 64) / 64).float().cuda()
+    b = torch.from_numpy(np.round(rng.standard_normal(N) * 16) / 16).float().cuda()
+    for act, scale in ((None, 1.0), ('relu', 1.0 / pool_rows)):
+        y0, a0 = kernels.qdense_fwd(x, None, None, f, rows_period, 'RND', 'WRAP', True, False, w, b, act, True)
+        y, a, pooled = kernels.qdense_fwd(x, None, None, f, rows_period, 'RND', 'WRAP', True, False, w, b, act, True,
+                                          pool_rows=pool_rows, pool_scale=scale)
+        kernels.check_status(y.device)
+        assert torch.equal(y, y0) and torch.equal(a, a0)
+        want = y.view(M // pool_rows, pool_rows, N).double().sum(dim=1) * scale
+        assert pooled.shape == (M // pool_rows, N)
+        assert torch.equal(pooled.double(), want), float((pooled.double() - want).abs().max())
+
+
 def test_fused_dense_is_exact_for_wide_values():
     # operands that need two and three bf16 terms: 14-bit activations, 12- and 20-bit weights
     from hgq2_b200 import kernels
