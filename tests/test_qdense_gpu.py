@@ -61,10 +61,17 @@ def test_fused_dense_forward(M, K, N, rows_period, rm, om, training):
 def test_fused_dense_forward_with_row_group_sums(M, K, N, pool_rows, rows_period):
     """hgq_qdense_fwd_pooled: the sums over groups of consecutive rows come out of the forward kernel and equal the sums
     of the y it writes (exactly for quantised operands: every partial sum is exact in fp32), scaled as asked."""
+    import os
+
     from hgq2_b200 import kernels
 
-    assert kernels.qdense_pooled_supported(M, K, N, rows_period, pool_rows)
+    # the sums are taken from the blocks of the warp-specialised kernel's bulk-store path: with that path switched off in
+    # the environment (the child-process runs below) the query must say no, and callers keep their separate reduction
+    on = os.environ.get('HGQ_QDENSE_WS', '1') != '0' and os.environ.get('HGQ_QDENSE_TMA_STORE', '1') != '0'
+    assert kernels.qdense_pooled_supported(M, K, N, rows_period, pool_rows) == on
     assert not kernels.qdense_pooled_supported(M + 4, K, N, rows_period, pool_rows)  # groups must tile the rows
+    if not on:
+        return
     rng = np.random.default_rng(M + N)
     x = torch.from_numpy((rng.standard_normal((M, K)) * 3).astype(np.float32)).cuda()
     f = torch.from_numpy(rng.integers(1, 7, (rows_period, K)).astype(np.float32)).cuda()
