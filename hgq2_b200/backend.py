@@ -508,21 +508,27 @@ def _snake(name: str) -> str:
     return ''.join(out)
 
 
+# The process group the batch statistics of ``moments(..., synchronized=True)`` are averaged over: the group of the active
+# ``train.DataParallel`` (set while its context is entered), else the default group.
+moments_group = None
+
+
 def moments(x: torch.Tensor, axes, keepdims: bool = False, synchronized: bool = False):
     """Mean and variance over ``axes`` the way keras.ops.moments computes them on the torch backend
-    (Var = E[x^2] - E[x]^2).  ``synchronized``: average both statistics over the ranks of the default process group
-    (equal shard sizes), differentiably -- the torch backend of Keras refuses this flag; data-parallel training here
-    supports it."""
+    (Var = E[x^2] - E[x]^2).  ``synchronized``: average both statistics over the ranks of the active data-parallel group
+    (``moments_group``; the default process group when none is active; equal shard sizes), differentiably -- the torch
+    backend of Keras refuses this flag; data-parallel training here supports it."""
     axes = tuple(axes) if not isinstance(axes, int) else (axes,)
     mean = torch.mean(x, dim=axes, keepdim=True)
     mean_sq = torch.mean(torch.square(x), dim=axes, keepdim=True)
     if synchronized:
         import torch.distributed as dist
 
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(moments_group) > 1:
             import torch.distributed.nn.functional as dfn
 
-            stats = dfn.all_reduce(torch.cat([mean.reshape(-1), mean_sq.reshape(-1)])) / dist.get_world_size()
+            stats = dfn.all_reduce(torch.cat([mean.reshape(-1), mean_sq.reshape(-1)]), group=moments_group)
+            stats = stats / dist.get_world_size(moments_group)
             mean, mean_sq = stats[:mean.numel()].view_as(mean), stats[mean.numel():].view_as(mean_sq)
     variance = mean_sq - torch.square(mean)
     if not keepdims:

@@ -231,12 +231,17 @@ class DataParallel:
         return absmax
 
     def __enter__(self):
-        self._prev = _fpq.absmax_sync_hook
+        from . import backend
+
+        self._prev = (_fpq.absmax_sync_hook, backend.moments_group)
         _fpq.absmax_sync_hook = self.absmax_sync
+        backend.moments_group = self.group  # synchronized batch statistics are averaged over this group's ranks
         return self
 
     def __exit__(self, *exc):
-        _fpq.absmax_sync_hook = self._prev
+        from . import backend
+
+        _fpq.absmax_sync_hook, backend.moments_group = self._prev
 
 
 class _SoftmaxXentFn(torch.autograd.Function):
