@@ -51,7 +51,9 @@ constexpr unsigned kWsTimeout = 1u;                  // status bit, same meaning
 //          through a table in shared memory (atomic max on the bit patterns) when the CTA is done
 //   PLAIN  period 64 or 128, several K slabs: rows that share a table entry fall to the same thread, plain
 //          read-modify-write of the table in shared memory
-enum : int { WS_AMAX_NONE = 0, WS_AMAX_REGS1 = 1, WS_AMAX_PLAIN = 2, WS_AMAX_REGS2 = 3 };
+//   REGS2X2  as REGS2 for TWO K slabs (K up to 128): a second set of registers holds the maxima of the second slab's
+//          columns; the merge table has no row padding so that 64 x 128 entries fit the (single) raw-slab buffer
+enum : int { WS_AMAX_NONE = 0, WS_AMAX_REGS1 = 1, WS_AMAX_PLAIN = 2, WS_AMAX_REGS2 = 3, WS_AMAX_REGS2X2 = 4 };
 
 struct WsParams {
     const float *x, *qf, *wq, *bq;
@@ -159,10 +161,10 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
     const int Ke = P.Kt + 8;  // row stride of the exponent table: 8-byte reads of 8 rows hit 8 bank pairs
     const int tab_bytes = (P.rows_period * Ke + 15) / 16 * 16;
     unsigned char *etab = reinterpret_cast<unsigned char *>(bias_s + P.Npad);
-    const int Ks = P.Kt + 4;  // abs-max table row: 16-byte accesses of 8 rows hit 8 bank groups
+    const int Ks = (AMAX == WS_AMAX_REGS2X2) ? P.Kt : P.Kt + 4;  // abs-max table row: 16-byte accesses of 8 rows hit 8 bank groups
     // PLAIN keeps the abs-max table beside the exponent table; the register modes merge through the raw-slab slots, which
     // are idle by then
-    constexpr bool amax_regs = (AMAX == WS_AMAX_REGS1 || AMAX == WS_AMAX_REGS2);
+    constexpr bool amax_regs = (AMAX == WS_AMAX_REGS1 || AMAX == WS_AMAX_REGS2 || AMAX == WS_AMAX_REGS2X2);
     const int amax_elems = (AMAX == WS_AMAX_PLAIN) ? P.rows_period * Ks : 0;
     float *amax_t = amax_regs ? reinterpret_cast<float *>(fetch) : reinterpret_cast<float *>(etab + tab_bytes);
     uint64_t *full = reinterpret_cast<uint64_t *>(etab + tab_bytes + amax_elems * 4);
@@ -297,9 +299,9 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
         const bool rp_pow2 = (rp & (rp - 1)) == 0;
         uint32_t base_pr = (uint32_t)(((int64_t)blockIdx.x * kWsTileM) % P.rows_period);
         const uint32_t step_pr = (uint32_t)(((int64_t)gridDim.x * kWsTileM) % P.rows_period);
-        float amax_r[2][8];
+        float amax_r[2][8], amax_x[2][8];  // amax_x: the second K slab (REGS2X2)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) amax_r[0][j] = amax_r[1][j] = 0.f;
+        for (int j = 0; j < 8; ++j) amax_r[0][j] = amax_r[1][j] = amax_x[0][j] = amax_x[1][j] = 0.f;
 
         uint32_t n = 0;  // slabs produced so far
         bool ok = true;
@@ -364,7 +366,16 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
                                                   : floorf(__fmaf_rn(xv[it][j], __uint_as_float(sbits), rbias));
                             xv[it][j] = __fmul_rn(q, __uint_as_float(0x7F000000u - sbits));  // * 2^-f
                         }
-                        if (AMAX == WS_AMAX_REGS1 || AMAX == WS_AMAX_REGS2) {
+                        if (AMAX == WS_AMAX_REGS2X2) {
+                            const int ri = it & 1;
+                            if (ch == 0) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) amax_r[ri][j] = fmaxf(amax_r[ri][j], fabsf(xv[it][j]));
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) amax_x[ri][j] = fmaxf(amax_x[ri][j], fabsf(xv[it][j]));
+                            }
+                        } else if (AMAX == WS_AMAX_REGS1 || AMAX == WS_AMAX_REGS2) {
                             const int ri = (AMAX == WS_AMAX_REGS2) ? (it & 1) : 0;  // REGS2: the table row alternates with it
 #pragma unroll
                             for (int j = 0; j < 8; ++j) amax_r[ri][j] = fmaxf(amax_r[ri][j], fabsf(xv[it][j]));
@@ -424,11 +435,17 @@ __global__ void __launch_bounds__((NPW + EW + 1 + (TMA ? 1 : 0)) * 32, 1) k_qden
                 for (int e = tid; e < P.rows_period * Ks; e += kWsProd) amax_t[e] = 0.f;
                 asm volatile("bar.sync 1, %0;" ::"n"(kWsProd) : "memory");
 #pragma unroll
-                for (int ri = 0; ri < (AMAX == WS_AMAX_REGS2 ? 2 : 1); ++ri) {
+                for (int ri = 0; ri < ((AMAX == WS_AMAX_REGS2 || AMAX == WS_AMAX_REGS2X2) ? 2 : 1); ++ri) {
                     const int pr = (ri * ROWSTEP + (warp >> 1) * 8 + r8) % P.rows_period;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         if (kg * 8 + j < K) atomicMax(reinterpret_cast<unsigned *>(amax_t) + pr * Ks + kg * 8 + j, __float_as_uint(amax_r[ri][j]));
+                    if (AMAX == WS_AMAX_REGS2X2) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (kWsKC + kg * 8 + j < K)
+                                atomicMax(reinterpret_cast<unsigned *>(amax_t) + pr * Ks + kWsKC + kg * 8 + j, __float_as_uint(amax_x[ri][j]));
+                    }
                 }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kWsProd) : "memory");
@@ -723,6 +740,8 @@ static bool ws_plan(int Kpad, int Npad, int Kt, int rows_period, bool want_amax,
         const bool plain_ok = (rows_period % rowstep == 0) && (kWsTileM % rows_period == 0);
         if (one_slab && rowstep % rows_period == 0) amax_mode = WS_AMAX_REGS1;
         else if (one_slab && (2 * rowstep) % rows_period == 0 && (size_t)rows_period * (Kt + 4) * 4 <= kWsFetchBytes) amax_mode = WS_AMAX_REGS2;
+        else if (Kpad > kWsKC && Kpad <= 2 * kWsKC && (2 * rowstep) % rows_period == 0 && (size_t)rows_period * Kt * 4 <= kWsFetchBytes)
+            amax_mode = WS_AMAX_REGS2X2;
         else if (plain_ok) amax_mode = WS_AMAX_PLAIN;
         else return false;
     }
@@ -798,6 +817,7 @@ int qdense_ws_launch(const float *x, const float *qf, int rows_period, int round
         case WS_AMAX_NONE: HGQ_WS_LAUNCH(CV, WS_AMAX_NONE, PW, EWW); break;           \
         case WS_AMAX_REGS1: HGQ_WS_LAUNCH(CV, WS_AMAX_REGS1, PW, EWW); break;         \
         case WS_AMAX_REGS2: HGQ_WS_LAUNCH(CV, WS_AMAX_REGS2, PW, EWW); break;         \
+        case WS_AMAX_REGS2X2: HGQ_WS_LAUNCH(CV, WS_AMAX_REGS2X2, PW, EWW); break;     \
         default: HGQ_WS_LAUNCH(CV, WS_AMAX_PLAIN, PW, EWW); break;                    \
     }
     if (round_mode == RM_RND_CONV) { HGQ_WS_MODES(true, npw, ew) } else { HGQ_WS_MODES(false, npw, ew) }
