@@ -75,6 +75,12 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
          c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    'hgq_qdense_bwd_accumulate_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    'hgq_qdense_bwd_accumulate': (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
+         c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
     'hgq_qsoftmax_fwd': (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p,

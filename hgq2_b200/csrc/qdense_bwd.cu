@@ -490,8 +490,9 @@ __global__ void __launch_bounds__(kThreads) k_qb_stage2(const float *__restrict_
 }
 
 int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const float *x, int64_t ldx, const float *qf,
-                         int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *part, bool want_df,
-                         int64_t M, int K, int N, unsigned *status, cudaStream_t st, int *records);
+                         int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, int dx_accumulate, float *part,
+                         bool want_df, int64_t M, int K, int N, unsigned *status, cudaStream_t st, int *records);
+bool qdense_bwd_ws_covers(int K, int N, int rows_period, bool relu, bool has_q);
 
 // HGQ_QDENSE_BWD_WS=0 in the environment keeps every call on the general kernel (for comparisons).
 static bool bwd_ws_enabled() {
@@ -548,6 +549,18 @@ extern "C" int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const floa
                                       int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *dwq,
                                       float *dbq, float *df, int64_t M, int K, int N, void *workspace, size_t workspace_bytes,
                                       unsigned *status, void *stream) {
+    return hgq_qdense_bwd_accumulate(gy, gy_repeat, y, x, ldx, qf, rows_period, round_mode, wq, dx, lddx, 0, dwq, dbq, df, M, K, N,
+                                     workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int hgq_qdense_bwd_accumulate_supported(int K, int N, int rows_period, int relu, int has_quantizer) {
+    return (bwd_ws_enabled() && qdense_bwd_ws_covers(K, N, rows_period, relu != 0, has_quantizer != 0)) ? 1 : 0;
+}
+
+extern "C" int hgq_qdense_bwd_accumulate(const float *gy, int gy_repeat, const float *y, const float *x, int64_t ldx, const float *qf,
+                                         int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, int dx_accumulate,
+                                         float *dwq, float *dbq, float *df, int64_t M, int K, int N, void *workspace,
+                                         size_t workspace_bytes, unsigned *status, void *stream) {
     if (gy == nullptr || x == nullptr || wq == nullptr || dwq == nullptr) return HGQ_ERR_NULL;
     if (ldx < K || (dx != nullptr && lddx < K)) return HGQ_ERR_SIZE;
     if (gy_repeat < 1 || (gy_repeat > 1 && M >= ((int64_t)1 << 31))) return HGQ_ERR_SIZE;
@@ -561,8 +574,8 @@ extern "C" int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const floa
     const int64_t nw_ = (int64_t)K * N, nf_ = (int64_t)rows_period * K;
     if (bwd_ws_enabled()) {
         int records = 0;
-        const int r = qdense_bwd_ws_launch(gy, gy_repeat, y, x, ldx, qf, rows_period, round_mode, wq, dx, lddx, (float *)workspace,
-                                           df != nullptr, M, K, N, status, (cudaStream_t)stream, &records);
+        const int r = qdense_bwd_ws_launch(gy, gy_repeat, y, x, ldx, qf, rows_period, round_mode, wq, dx, lddx, dx_accumulate,
+                                           (float *)workspace, df != nullptr, M, K, N, status, (cudaStream_t)stream, &records);
         if (r < 0) return -r;
         if (r == 1) {
             if (int e = check_launch()) return e;
@@ -571,6 +584,7 @@ extern "C" int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const floa
             return check_launch();
         }
     }
+    if (dx_accumulate && dx != nullptr) return HGQ_ERR_SIZE;  // only the warp-specialised kernel adds into dx
     QbParams p;
     p.gy = gy; p.y = y; p.x = x; p.qf = qf; p.wq = wq; p.dx = dx;
     p.part = (float *)workspace;

@@ -52,6 +52,7 @@ constexpr unsigned kBwTimeout = 1u;
 struct BwParams {
     const float *gy, *y, *x, *qf, *wq;
     float *dx;
+    int dx_accumulate;  // dx += dXq instead of dx = dXq (several layers that read the same input add their gradients up)
     float *part;        // two records per CTA: [(K+1) x N] dWq|dbq, then [rows_period x K] df
     unsigned *status;
     int64_t M, num_tiles, ldx, lddx;
@@ -645,7 +646,14 @@ __global__ void __launch_bounds__(kBwThreads + (TMA ? 32 : 0), 1) k_qdense_bwd_w
                         acc_df[i * 4 + j] = fmaf(d, os[j], acc_df[i * 4 + j]);
                     }
                 }
-                if (store_dx && ROWS_IT * i < rows_left) __stcs(reinterpret_cast<float4 *>(dx_my + i * dx_it), o);
+                if (store_dx && ROWS_IT * i < rows_left) {
+                    float4 out = o;
+                    if (P.dx_accumulate) {
+                        const float4 old = __ldcs(reinterpret_cast<const float4 *>(dx_my + i * dx_it));
+                        out.x = __fadd_rn(old.x, o.x); out.y = __fadd_rn(old.y, o.y); out.z = __fadd_rn(old.z, o.z); out.w = __fadd_rn(old.w, o.w);
+                    }
+                    __stcs(reinterpret_cast<float4 *>(dx_my + i * dx_it), out);
+                }
             }
             __syncwarp();  // the transposition buffer is reused by the next tile
         }
@@ -759,9 +767,17 @@ static bool bw_make_tmap(CUtensorMap *map, const float *base, int64_t rows, int 
 
 // Launches the warp-specialised backward when it covers the call: returns 1 with the number of partial records in
 // *records, 0 when the call is not covered (the caller takes the general kernel), or a negative CUDA error code.
+// Shapes the warp-specialised backward covers (pointer alignment aside).
+bool qdense_bwd_ws_covers(int K, int N, int rows_period, bool relu, bool has_q) {
+    const int Kp = (K + 15) / 16 * 16, Np = (N + 15) / 16 * 16, Kt = (K + 7) / 8 * 8;
+    auto pow2_16_64 = [](int v) { return v == 16 || v == 32 || v == 64; };
+    if (!pow2_16_64(Kp) || !pow2_16_64(Np) || K % 4 != 0 || N % 4 != 0 || rows_period <= 0 || kBwTileM % rows_period != 0) return false;
+    return qdense_bwd_ws_smem(Kp, Np, Kt, rows_period, relu, has_q) <= 227 * 1024;
+}
+
 int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const float *x, int64_t ldx, const float *qf,
-                         int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *part, bool want_df,
-                         int64_t M, int K, int N, unsigned *status, cudaStream_t st, int *records) {
+                         int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, int dx_accumulate, float *part,
+                         bool want_df, int64_t M, int K, int N, unsigned *status, cudaStream_t st, int *records) {
     const int Kp = (K + 15) / 16 * 16, Np = (N + 15) / 16 * 16, Kt = (K + 7) / 8 * 8;
     auto pow2_16_64 = [](int v) { return v == 16 || v == 32 || v == 64; };
     if (!pow2_16_64(Kp) || !pow2_16_64(Np) || K % 4 != 0 || N % 4 != 0) return 0;
@@ -771,7 +787,7 @@ int qdense_bwd_ws_launch(const float *gy, int gy_repeat, const float *y, const f
     const size_t smem = qdense_bwd_ws_smem(Kp, Np, Kt, rows_period, y != nullptr, qf != nullptr);
     if (smem > 227 * 1024) return 0;
     BwParams p;
-    p.gy = gy; p.y = y; p.x = x; p.qf = qf; p.wq = wq; p.dx = dx; p.part = part; p.status = status;
+    p.gy = gy; p.y = y; p.x = x; p.qf = qf; p.wq = wq; p.dx = dx; p.dx_accumulate = dx_accumulate; p.part = part; p.status = status;
     p.M = M; p.num_tiles = (M + kBwTileM - 1) / kBwTileM; p.ldx = ldx; p.lddx = (dx != nullptr) ? lddx : K;
     p.K = K; p.N = N; p.Kp = Kp; p.Np = Np; p.Kt = Kt;
     p.rows_period = rows_period; p.rm = round_mode; p.relu = (y != nullptr) ? 1 : 0; p.want_df = want_df ? 1 : 0;

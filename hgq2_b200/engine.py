@@ -254,7 +254,8 @@ class _Dense(_Node):
                                      want_absmax=True, absmax_out=self.oq.absmax)[0]
         return y.view(out_shape)
 
-    def backward(self, g, need_dx=True):
+    def backward(self, g, need_dx=True, dx_into=None):
+        """``dx_into``: a tensor of the input's shape that the input gradient is added to (see ``accumulates``)."""
         K, N, P = self.K, self.N, self.P
         M = self.x.numel() // K
         if self.oq is not None:
@@ -270,10 +271,14 @@ class _Dense(_Node):
         dx, _, _, _ = kernels.qdense_bwd(g, self.y if self.relu else None, self.x, self.iq.F.view(-1), P, self.iq.q.round_mode,
                                          self.wq.view(K, N), want_dx=need_dx, want_db=self.dbq is not None, want_df=True,
                                          gy_repeat=gy_repeat, out_dwq=self.dwq.view(K, N), out_dbq=self.dbq,
-                                         out_df=self.iq.dF.view(-1))
+                                         out_df=self.iq.dF.view(-1), dx_into=dx_into if need_dx else None)
         x_shape = self.x.shape
         self.x = self.y = None
         return dx.view(x_shape) if dx is not None else None
+
+    def accumulates(self) -> bool:
+        """Whether this layer's backward kernel can add its input gradient to an existing tensor."""
+        return kernels.qdense_bwd_accumulates(self.K, self.N, self.P, self.relu)
 
     def ebops(self, eng):
         if self.eb_index is None:
@@ -497,12 +502,18 @@ class _Attention(_Node):
         dq = kernels.attn_heads_matmul(1, ds, k, B, T, H, D)
         dk = kernels.attn_heads_matmul(2, ds, q, B, T, H, D)
         self.saved = None
+        # the three projections read the same input: the key and value backward kernels add their input gradients to the
+        # query's in place (where the kernel covers the shape; two separate additions otherwise)
         dx = self.q.backward(dq, need_dx)
-        dxk = self.k.backward(dk, need_dx)
-        dxv = self.v.backward(dv, need_dx)
+        dxk = self.k.backward(dk, need_dx, dx_into=dx if (need_dx and self.k.accumulates()) else None)
+        dxv = self.v.backward(dv, need_dx, dx_into=dx if (need_dx and self.v.accumulates()) else None)
         if not need_dx:
             return None
-        return dx.add_(dxk).add_(dxv)
+        if dxk.data_ptr() != dx.data_ptr():
+            dx.add_(dxk)
+        if dxv.data_ptr() != dx.data_ptr():
+            dx.add_(dxv)
+        return dx
 
     def ebops(self, eng):
         for d in (self.q, self.k, self.v, self.o):

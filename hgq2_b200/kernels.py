@@ -301,10 +301,11 @@ def qdense_bwd_supported(M: int, K: int, N: int, rows_period: int) -> bool:
 
 
 def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: bool, want_db: bool, want_df: bool,
-               gy_repeat: int = 1, out_dwq=None, out_dbq=None, out_df=None):
+               gy_repeat: int = 1, out_dwq=None, out_dbq=None, out_df=None, dx_into=None):
     """Fused backward of qdense_fwd (rounding-only input quantizer or none).  gy/y are [M, N], x [M, K]; with
     ``gy_repeat`` > 1, gy is [M / gy_repeat, N] and each of its rows serves gy_repeat consecutive rows.
-    Returns (dx or None, dwq, dbq or None, df or None)."""
+    Returns (dx or None, dwq, dbq or None, df or None).
+    ``dx_into``: an [M, K] tensor the input gradient is ADDED to (and returned as dx); see ``qdense_bwd_accumulates``."""
     require_cuda(gy, y, x, qf, wq)
     rm = ROUND_MODES[round_mode.upper()]
     gy, x, wq = gy.contiguous(), x.contiguous(), wq.contiguous()
@@ -313,7 +314,7 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
     M = x.numel() // K
     dev = x.device
     want_df = want_df and qf is not None
-    dx = torch.empty((M, K), dtype=torch.float32, device=dev) if want_dx else None
+    dx = (dx_into.view(M, K) if dx_into is not None else torch.empty((M, K), dtype=torch.float32, device=dev)) if want_dx else None
     dwq = out_dwq if out_dwq is not None else torch.empty((K, N), dtype=torch.float32, device=dev)
     dbq = (out_dbq if out_dbq is not None else torch.empty(N, dtype=torch.float32, device=dev)) if want_db else None
     direct_df = want_df and out_df is not None and K <= _QB_KBLOCK  # one launch: the kernel writes the caller's table
@@ -326,11 +327,18 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
             qf_b = None if qf2 is None else qf2[:, k0:k0 + kb].contiguous()
             df_b = (out_df if direct_df else torch.empty(rows_period * kb, dtype=torch.float32, device=dev)) if want_df else None
             ws = workspace(lib().hgq_qdense_bwd_workspace(M, kb, N, rows_period), dev, slot=2)
-            st = lib().hgq_qdense_bwd_strided(
-                ptr(gy), gy_repeat, ptr(y), x2.data_ptr() + 4 * k0, K, ptr(qf_b), rows_period, rm, wq.data_ptr() + 4 * k0 * N,
-                (dx.data_ptr() + 4 * k0) if dx is not None else None, K, dwq.data_ptr() + 4 * k0 * N,
-                ptr(dbq) if k0 == 0 else None, ptr(df_b), M, kb, N, ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
-            check(st, 'hgq_qdense_bwd_strided')
+            if dx_into is not None and want_dx:
+                st = lib().hgq_qdense_bwd_accumulate(
+                    ptr(gy), gy_repeat, ptr(y), x2.data_ptr() + 4 * k0, K, ptr(qf_b), rows_period, rm, wq.data_ptr() + 4 * k0 * N,
+                    dx.data_ptr() + 4 * k0, K, 1, dwq.data_ptr() + 4 * k0 * N, ptr(dbq) if k0 == 0 else None, ptr(df_b), M, kb, N,
+                    ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
+                check(st, 'hgq_qdense_bwd_accumulate')
+            else:
+                st = lib().hgq_qdense_bwd_strided(
+                    ptr(gy), gy_repeat, ptr(y), x2.data_ptr() + 4 * k0, K, ptr(qf_b), rows_period, rm, wq.data_ptr() + 4 * k0 * N,
+                    (dx.data_ptr() + 4 * k0) if dx is not None else None, K, dwq.data_ptr() + 4 * k0 * N,
+                    ptr(dbq) if k0 == 0 else None, ptr(df_b), M, kb, N, ptr(ws), ws.numel(), ptr(status_word(dev)), stream_handle())
+                check(st, 'hgq_qdense_bwd_strided')
             if want_df:
                 dfs.append(df_b.view(rows_period, kb))
     df = None
@@ -343,6 +351,11 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
         else:
             df = (dfs[0] if len(dfs) == 1 else torch.cat(dfs, dim=1)).reshape(-1)
     return dx, dwq, dbq, df
+
+
+def qdense_bwd_accumulates(K: int, N: int, rows_period: int, relu: bool, has_quantizer: bool = True) -> bool:
+    """Whether ``qdense_bwd(..., dx_into=...)`` is available for a layer of this shape."""
+    return K <= _QB_KBLOCK and bool(lib().hgq_qdense_bwd_accumulate_supported(K, N, rows_period, int(relu), int(has_quantizer)))
 
 
 def _quant_arrays(quants):

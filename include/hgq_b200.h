@@ -224,6 +224,15 @@ int hgq_qdense_bwd_strided(const float *gy, int gy_repeat, const float *y, const
                            int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, float *dwq,
                            float *dbq, float *df, int64_t M, int K, int N, void *workspace, size_t workspace_bytes,
                            unsigned *status, void *stream);
+/* The same with dx += (instead of =) when dx_accumulate is non-zero: layers that read the same input (the query, key and value
+ * projections of an attention layer) add their input gradients up in place instead of through separate passes over
+ * three tensors.  Covered by the warp-specialised kernel only: hgq_qdense_bwd_accumulate_supported says whether a shape is
+ * (relu: y is given; has_quantizer: qf is given); HGQ_ERR_SIZE otherwise. */
+int hgq_qdense_bwd_accumulate_supported(int K, int N, int rows_period, int relu, int has_quantizer);
+int hgq_qdense_bwd_accumulate(const float *gy, int gy_repeat, const float *y, const float *x, int64_t ldx, const float *qf,
+                              int rows_period, int round_mode, const float *wq, float *dx, int64_t lddx, int dx_accumulate,
+                              float *dwq, float *dbq, float *df, int64_t M, int K, int N, void *workspace, size_t workspace_bytes,
+                              unsigned *status, void *stream);
 
 /* ---- K4: quantised softmax ------------------------------------------------------------------ */
 

@@ -273,6 +273,35 @@ def test_warp_specialised_backward_shapes(M, K, N, rows_period, relu, want_dx):
     assert rel(df.view(rows_period, K), dfr) <= 5e-5
 
 
+@pytest.mark.parametrize('M,K,N,rows_period,relu', [(128 * 40 + 17, 64, 64, 64, False), (4096, 16, 64, 1, True), (777, 32, 16, 4, True)])
+def test_backward_adds_its_input_gradient_in_place(M, K, N, rows_period, relu):
+    """hgq_qdense_bwd_accumulate: dx += the layer's input gradient (what layers that share an input need), every other
+    output as without the flag."""
+    import os
+
+    from hgq2_b200 import kernels
+
+    on = os.environ.get('HGQ_QDENSE_BWD_WS', '1') != '0'
+    assert kernels.qdense_bwd_accumulates(K, N, rows_period, relu) == on
+    assert not kernels.qdense_bwd_accumulates(K, 10, rows_period, relu)  # widths the warp-specialised kernel does not cover
+    if not on:
+        return
+    gen = torch.Generator(device='cuda').manual_seed(M)
+    x = torch.randn(M, K, device='cuda', generator=gen) * 2
+    f = torch.randint(2, 7, (rows_period, K), device='cuda', generator=gen).float()
+    w = torch.randint(-64, 64, (K, N), device='cuda', generator=gen).float() / 32
+    y = torch.randn(M, N, device='cuda', generator=gen) if relu else None
+    gy = torch.randn(M, N, device='cuda', generator=gen)
+    dx, dw, db, df = (t.clone() for t in kernels.qdense_bwd(gy, y, x, f.view(-1), rows_period, 'RND', w, True, True, True))
+    base = torch.randn(M, K, device='cuda', generator=gen)
+    acc = base.clone()
+    dx2, dw2, db2, df2 = kernels.qdense_bwd(gy, y, x, f.view(-1), rows_period, 'RND', w, True, True, True, dx_into=acc)
+    kernels.check_status(x.device)
+    assert dx2.data_ptr() == acc.data_ptr()
+    assert torch.equal(acc, base + dx)
+    assert torch.equal(dw2, dw) and torch.equal(db2, db) and torch.equal(df2, df)
+
+
 def test_general_backward_kernel_on_the_same_cases():
     # HGQ_QDENSE_BWD_WS=0 (read once per process) keeps every backward call on the general kernel: the backward cases
     # above run again in a child process so that both kernels stay covered by the same references

@@ -105,6 +105,46 @@ def test_transformer_block_steps():
     run_steps(lambda beta0: workloads.transformer_block(seq=16, d_model=32, heads=2, beta0=beta0), x, y, steps=2, engine=None)
 
 
+def _attention_behind_a_dense_layer(beta0=1e-5):
+    """QDense 64 -> 64, then QMultiHeadAttention(4 heads, key_dim 16) on [B, 64, 64], mean over the sequence, QDense -> 5:
+    the attention layer is not the first one, so its three input projections must hand an input gradient back."""
+    from hgq2_b200 import workloads as W
+    from hgq2_b200.backend import Lambda, Sequential
+    from hgq2_b200.config import QuantizerConfigScope
+    from hgq2_b200.layers import QDense, QMultiHeadAttention
+    from hgq2_b200.quantizer import QuantizerConfig
+
+    w, a, l = W._scopes(4, 8, beta0)
+    t = QuantizerConfigScope(place='table', b0=10, i0=1)
+    with w, a, t, l:
+        layers = W._seeded([
+            QDense(64, activation='relu'),
+            QMultiHeadAttention(4, 16,
+                                softmax_exp_iq_conf=QuantizerConfig(place='datalane', overflow_mode='SAT', k0=0, i0=4, f0=6),
+                                softmax_inv_iq_conf=QuantizerConfig(place='datalane', k0=0, i0=7, f0=3)),
+            Lambda(lambda x: x.mean(dim=1), name='mean_sequence'),
+            QDense(5),
+        ])
+    model = Sequential(layers, name='attention_behind_dense')
+    model.input_shape = (64, 64)
+    model.weight_bits = (4, 8)
+    return model
+
+
+def test_attention_layer_that_is_not_the_first_layer():
+    """The key and value projections' backward kernels add their input gradients to the query projection's in place
+    (hgq_qdense_bwd_accumulate); loss, EBOPs, gradients and updates against the oracle as for the other models."""
+    from hgq2_b200 import routes
+
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((8, 64, 64)).astype(np.float32)
+    y = np.random.default_rng(2).integers(0, 5, 8)
+    routes.reset()
+    with routes.strict_mode():
+        run_steps(_attention_behind_a_dense_layer, x, y, steps=2, engine=True)
+    assert routes.counts['hgq_qdense_bwd_accumulate'] == 2 * 2, dict(routes.counts)
+
+
 def test_adam_kernel_matches_keras_rule():
     from hgq2_b200 import _lib
 
