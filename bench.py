@@ -712,10 +712,10 @@ def run_qsoftmax(args):
     gy = torch.randn(B, 4, 64, L, device=dev, generator=gen)
     one = lambda v, dt=torch.float32: torch.full((1,), v, dtype=dt, device=dev)
     k0, k1 = one(0, torch.uint8), one(1, torch.uint8)
-    # the modes of the transformer block's layer in training: saturating table index and table outputs, the two WRAP
-    # quantizers only round
-    quants = [(k0, one(4.0), one(6.0), 'RND', 'SAT'), (k0, one(1.0), one(9.0), 'RND', 'SAT'), (None, None, one(3.0), 'RND', 'NONE'),
-              (k0, one(1.0), one(9.0), 'RND', 'SAT'), (None, None, torch.full((rp * L,), 8.0, device=dev), 'RND', 'NONE')]
+    # the modes of the transformer block's layer in training: saturating table index, table outputs that saturate and round
+    # half-even (what the layer forces them to), the two WRAP quantizers only round
+    quants = [(k0, one(4.0), one(6.0), 'RND', 'SAT'), (k0, one(1.0), one(9.0), 'RND_CONV', 'SAT'), (None, None, one(3.0), 'RND', 'NONE'),
+              (k0, one(1.0), one(9.0), 'RND_CONV', 'SAT'), (None, None, torch.full((rp * L,), 8.0, device=dev), 'RND', 'NONE')]
     fwd = lambda: kernels.qsoftmax_fwd(s, quants, 0.25, 1e-7, rp, True, True)
     bwd = lambda: kernels.qsoftmax_bwd(gy, s, quants, 0.25, 1e-7, rp, False)
     peak, kind = measured_peaks()

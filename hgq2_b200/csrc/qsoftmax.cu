@@ -90,17 +90,17 @@ __device__ __forceinline__ QC load_q(const SQuant &q) {
 }
 
 // Mode knowledge at compile time.  CL: 0 = the quantizer only rounds, 1 = it clips, 2 = decided at run time (launch-uniform
-// flag).  FL: every quantizer rounds by floor(x 2^f + bias) (RND: bias 1/2, TRN: bias 0); otherwise round-half-even is
-// selected at run time.
-template <bool FL>
+// flag).  RD: 0 = it rounds by floor(x 2^f + bias) (RND: bias 1/2, TRN: bias 0), 1 = round-half-even, 2 = decided at run
+// time.
+template <int RD>
 __device__ __forceinline__ float qc_round(float x, const QC &c) {
     const float xs = __fmul_rn(x, c.s);
-    const float q = (!FL && c.conv) ? rintf(xs) : floorf(__fadd_rn(xs, c.rbias));
+    const float q = (RD == 1 || (RD == 2 && c.conv)) ? rintf(xs) : floorf(__fadd_rn(xs, c.rbias));
     return __fmul_rn(q, c.inv);
 }
-template <int CL, bool FL>
+template <int CL, int RD>
 __device__ __forceinline__ float qc_fwd(float x, const QC &c, float &rounded) {
-    rounded = qc_round<FL>(x, c);
+    rounded = qc_round<RD>(x, c);
     if (CL == 0) return rounded;
     return clipf(rounded, c.lo, c.hi);  // +-inf bounds when a run-time quantizer only rounds
 }
@@ -126,16 +126,17 @@ __device__ __forceinline__ void qc_bwd_r(float g, float x, float xq, const QC &c
     df = __fadd_rn(pass ? df_r : 0.f, __fmul_rn(c.sym ? m : ghi, c.cf));
 }
 
-// Kernel variants: 0 = every mode decided at run time; 1 / 2 = the training set-up of the layer (every quantizer rounds
-// by floor; the two table outputs Q2 and Q4 saturate; Q3 and Q5, WRAP quantizers, only round), with Q1 only rounding (1)
-// or saturating (2).
+// Kernel variants: 0 = every mode decided at run time; 1 .. 4 = the training set-up of the layer: Q1, Q3, Q5 round by
+// floor, the two table outputs Q2 and Q4 saturate, Q3 and Q5 (WRAP quantizers) only round; Q1 only rounds (1, 3) or
+// saturates (2, 4); the table outputs round by floor (1, 2) or half-even (3, 4: what the layer forces them to).
 template <int V> struct Modes {
-    static constexpr bool FL = V != 0;
-    static constexpr int C1 = V == 0 ? 2 : (V == 2 ? 1 : 0);
+    static constexpr int C1 = V == 0 ? 2 : ((V == 2 || V == 4) ? 1 : 0);
     static constexpr int C2 = V == 0 ? 2 : 1;
     static constexpr int C3 = V == 0 ? 2 : 0;
     static constexpr int C4 = C2;
     static constexpr int C5 = C3;
+    static constexpr int RA = V == 0 ? 2 : 0;                  // rounding of Q1, Q3, Q5
+    static constexpr int RT = V == 0 ? 2 : (V >= 3 ? 1 : 0);   // rounding of the table outputs Q2, Q4
 };
 
 template <int VE>
@@ -203,15 +204,15 @@ __device__ __forceinline__ void chain_fwd(const SmParams &P, const QC &q1, const
     float part = 0.f;
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
-        const float a = qc_fwd<Mo::C1, Mo::FL>(__fsub_rn(m, s[j]), q1, ra[j]);
+        const float a = qc_fwd<Mo::C1, Mo::RA>(__fsub_rn(m, s[j]), q1, ra[j]);
         e[j] = expf(__fmul_rn(-a, P.scaler));
-        b[j] = qc_fwd<Mo::C2, Mo::FL>(e[j], q2, rb[j]);
+        b[j] = qc_fwd<Mo::C2, Mo::RT>(e[j], q2, rb[j]);
         part = __fadd_rn(part, b[j]);
     }
     S = row_sum<LPR>(part);
-    const float t = qc_fwd<Mo::C3, Mo::FL>(S, q3, t_rounded);
+    const float t = qc_fwd<Mo::C3, Mo::RA>(S, q3, t_rounded);
     v = __fdiv_rn(1.f, __fadd_rn(t, P.eps));
-    u = qc_fwd<Mo::C4, Mo::FL>(v, q4, u_rounded);
+    u = qc_fwd<Mo::C4, Mo::RT>(v, q4, u_rounded);
 }
 
 template <int VE>
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(kSmWarps * 32, VE == 8 ? 3 : 1) k_qsoftmax_fwd
             for (int j = 0; j < VE; ++j) {
                 float r;
                 am1 = fmaxf(am1, fabsf(ra[j]));
-                y[j] = qc_fwd<Mo::C5, Mo::FL>(__fmul_rn(b[j], u), q5[j], r);
+                y[j] = qc_fwd<Mo::C5, Mo::RA>(__fmul_rn(b[j], u), q5[j], r);
                 am5[j] = fmaxf(am5[j], fabsf(r));
             }
             store_row<VE>(P.y + row * L, rl, y);
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(kSmWarps * 32, VE == 8 ? 2 : 4) k_qsoftmax_bwd
         for (int j = 0; j < VE; ++j) {
             float gz, di, df;
             const float z = __fmul_rn(b[j], u);
-            qc_bwd_r<Mo::C5>(g[j], z, qc_round<Mo::FL>(z, q5[j]), q5[j], gz, di, df);
+            qc_bwd_r<Mo::C5>(g[j], z, qc_round<Mo::RA>(z, q5[j]), q5[j], gz, di, df);
             adf5[j] = __fadd_rn(adf5[j], df);
             if (Mo::C5 != 0) adi5[j] = __fadd_rn(adi5[j], di);
             gb[j] = __fmul_rn(gz, u);
@@ -437,12 +438,15 @@ static int sm_check(const SmParams &p, int64_t R) {
 
 // Kernel variant of a launch (see Modes<>): 1 / 2 when the modes are those of the layer in training, else 0.
 static int sm_variant(const SmParams &p) {
-    const SQuant *qs[4] = {&p.q1, &p.q2, &p.q3, &p.q4};
-    for (const SQuant *q : qs)
-        if (q->rm == RM_RND_CONV) return 0;
-    if (p.rm5 == RM_RND_CONV) return 0;
+    static const bool general_only = [] {  // HGQ_QSOFTMAX_GENERAL=1: every launch on the run-time variant (for comparisons)
+        const char *v = getenv("HGQ_QSOFTMAX_GENERAL");
+        return v != nullptr && v[0] == '1';
+    }();
+    if (general_only) return 0;
+    if (p.q1.rm == RM_RND_CONV || p.q3.rm == RM_RND_CONV || p.rm5 == RM_RND_CONV) return 0;
+    if ((p.q2.rm == RM_RND_CONV) != (p.q4.rm == RM_RND_CONV)) return 0;
     if (p.q2.om == OM_NONE || p.q4.om == OM_NONE || p.q3.om != OM_NONE || p.om5 != OM_NONE) return 0;
-    return p.q1.om == OM_NONE ? 1 : 2;
+    return (p.q1.om == OM_NONE ? 1 : 2) + (p.q2.rm == RM_RND_CONV ? 2 : 0);
 }
 
 // Lanes per row of 64 scores: 8 (eight scores per lane, four rows per warp) unless HGQ_QSOFTMAX_LANES in the environment says
@@ -465,6 +469,8 @@ static bool sm_aligned32(const SmParams &p) { return aligned(p.s, 32) && aligned
         switch (sm_variant(p)) {                                                          \
             case 1: KERN<__VA_ARGS__, 1><<<grid, kSmWarps * 32, 0, st>>>(p); break;       \
             case 2: KERN<__VA_ARGS__, 2><<<grid, kSmWarps * 32, 0, st>>>(p); break;       \
+            case 3: KERN<__VA_ARGS__, 3><<<grid, kSmWarps * 32, 0, st>>>(p); break;       \
+            case 4: KERN<__VA_ARGS__, 4><<<grid, kSmWarps * 32, 0, st>>>(p); break;       \
             default: KERN<__VA_ARGS__, 0><<<grid, kSmWarps * 32, 0, st>>>(p); break;      \
         }                                                                                 \
     } while (0)

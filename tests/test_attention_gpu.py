@@ -124,13 +124,14 @@ def test_per_head_attention_products(B, H, D):
 
 def test_per_thread_loads_and_wider_softmax_rows_on_the_same_cases():
     # HGQ_ATTN_TMA=0 (read once per process) keeps the per-head products on per-thread loads instead of bulk tensor copies,
-    # HGQ_QSOFTMAX_LANES=32 keeps a whole warp on every row of 64 scores: the cases of this file and the softmax cases at
-    # the benchmark shape run again in a child process, so that both organisations stay covered by the same references
+    # HGQ_QSOFTMAX_LANES=32 keeps a whole warp on every row of 64 scores, HGQ_QSOFTMAX_GENERAL=1 keeps the softmax kernels on
+    # the variant that decides every mode at run time: the cases of this file and the softmax cases at the benchmark shape
+    # run again in a child process, so that both organisations stay covered by the same references
     import os
     import subprocess
     import sys
 
-    env = dict(os.environ, HGQ_ATTN_TMA='0', HGQ_QSOFTMAX_LANES='32')
+    env = dict(os.environ, HGQ_ATTN_TMA='0', HGQ_QSOFTMAX_LANES='32', HGQ_QSOFTMAX_GENERAL='1')
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, '-m', 'pytest', os.path.join(root, 'tests', 'test_attention_gpu.py'),
                         os.path.join(root, 'tests', 'test_benchmark_shapes_gpu.py'), '-q', '-x', '-m', 'gpu',

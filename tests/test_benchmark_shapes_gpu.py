@@ -163,6 +163,32 @@ def test_qsoftmax_rows_of_64_from_a_16_byte_aligned_buffer():
         close(outs[1][j], outs[0][j], 1e-5, name)
 
 
+def test_qsoftmax_compile_time_variants_agree():
+    """The kernel variants with the modes known at compile time against one another: a table index quantizer that saturates
+    at a range nothing reaches (variants 2 / 4) must give the bits of one that only rounds (variants 1 / 3), for table
+    outputs that round by floor and half-even."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    gen = torch.Generator(device=dev).manual_seed(5)
+    B, rp, L = 9, 256, 64
+    s = (torch.round(torch.randn(B, rp, L, device=dev, generator=gen) * 3 * 64) / 64)
+    gy = torch.randn(B, rp, L, device=dev, generator=gen)
+    one = lambda v, dt=torch.float32: torch.full((1,), v, dtype=dt, device=dev)
+    k0 = one(0, torch.uint8)
+    f5 = torch.randint(4, 10, (rp * L,), device=dev, generator=gen).float()
+    for table_round in ('RND', 'RND_CONV'):
+        outs = []
+        for q1 in ((None, None, one(6.0), 'RND', 'NONE'), (k0, one(20.0), one(6.0), 'RND', 'SAT')):
+            quants = [q1, (k0, one(1.0), one(9.0), table_round, 'SAT'), (None, None, one(3.0), 'RND', 'NONE'),
+                      (k0, one(1.0), one(9.0), table_round, 'SAT'), (None, None, f5, 'RND', 'NONE')]
+            y, a3, a5, a1 = kernels.qsoftmax_fwd(s, quants, 0.25, 1e-7, rp, True, True, True)
+            ds, sc, df5, _ = kernels.qsoftmax_bwd(gy, s, quants, 0.25, 1e-7, rp, False)
+            outs.append((y.clone(), a3.clone(), a5.clone(), a1.clone(), ds.clone(), sc.clone(), df5.clone()))
+        for j, name in enumerate(('y', 'amax3', 'amax5', 'amax1', 'ds', 'scalars', 'df5')):
+            assert torch.equal(outs[0][j], outs[1][j]), (table_round, name)
+
+
 def test_qmha_at_the_benchmark_shape():
     """QMultiHeadAttention(4 heads, key_dim 16) on [B, 64, 64]: projections on the fused dense kernels, Q K^T and P V (and
     the four products of their backward) on the per-head tensor-core kernel, the scores through the fused softmax."""
