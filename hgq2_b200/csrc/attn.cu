@@ -33,6 +33,9 @@
 
 namespace hgq {
 
+int attn_ws_launch(int kind, const float *x, const float *y, float *out, int64_t B, int L, int H, int D, unsigned *status,
+                   cudaStream_t st);
+
 constexpr int kAtThreads = 256;
 constexpr int kAtL = 64;
 
@@ -157,20 +160,27 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, con
             // rows (hh, t), contraction d: K-major, core (row group, d group); unit = (t, hh, d group): a row of the pair is
             // 2 D contiguous floats in memory
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
-                const int dg = u % DG, hh = (u / DG) & 1, t = u / (2 * DG);
+                int dg, hh, t;
+                if (TMA) { dg = u % DG; hh = (u / DG) & 1; t = u / (2 * DG); }  // raw box in shared memory: contiguous reads
+                else {  // the 8 lanes of a quarter-warp take the 8 rows of one core matrix: their 16-byte stores fill 128
+                        // contiguous bytes instead of hitting one bank group 8 times
+                    const int r8 = u & 7, v = u >> 3, rg = v / DG;
+                    dg = v - rg * DG; hh = rg >> 3; t = (rg & 7) * 8 + r8;
+                }
                 const int row = hh * 64 + t;
                 lo_a |= at_put8<TMA>(x_shd + t * pitch_x + hh * D + dg * 8, A, A + a_term, ((row >> 3) * DG + dg) * 128 + (row & 7) * 16);
             }
         } else if (KIND == 1) {
             // rows (hh, t), contraction s: K-major, core (row group, s group): a row is 64 contiguous floats
             for (int u = tid; u < 128 * 8; u += kAtThreads) {
-                const int sg = u & 7, row = u >> 3;
+                const int r8 = u & 7, sg = (u >> 3) & 7, row = (u >> 6) * 8 + r8;  // a quarter-warp = the 8 rows of one core matrix
                 lo_a |= at_put8<TMA>(x_hts + (int64_t)row * L + sg * 8, A, A + a_term, ((row >> 3) * 8 + sg) * 128 + (row & 7) * 16);
             }
         } else {
             // rows m = (hh, s), contraction t: MN-major, core (t group, m group) = 8 t x 8 m; a row t of a head is 64 contiguous s
             for (int u = tid; u < 128 * 8; u += kAtThreads) {
-                const int sg = u & 7, t = (u >> 3) & 63, hh = u >> 9;
+                const int r8 = u & 7, sg = (u >> 3) & 7, rg = u >> 6;  // a quarter-warp = the 8 positions t of one core matrix
+                const int hh = rg >> 3, t = (rg & 7) * 8 + r8;
                 const int mg = hh * 8 + sg;
                 lo_a |= at_put8<TMA>(x_hts + hh * LL + (int64_t)t * L + sg * 8, A, A + a_term, ((t >> 3) * 16 + mg) * 128 + (t & 7) * 16);
             }
@@ -179,14 +189,20 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, con
         if (KIND == 0) {
             // rows s (the product's columns), contraction d: K-major, core (s group, d group)
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
-                const int dg = u % DG, hh = (u / DG) & 1, s = u / (2 * DG);
+                int dg, hh, s;
+                if (TMA) { dg = u % DG; hh = (u / DG) & 1; s = u / (2 * DG); }
+                else {
+                    const int r8 = u & 7, v = u >> 3;
+                    dg = v % DG; hh = (v / DG) & 1; s = (v / (2 * DG)) * 8 + r8;
+                }
                 unsigned char *base = Bm + hh * 2 * b_term;
                 lo_b |= at_put8<TMA>(y_shd + s * pitch_y + hh * D + dg * 8, base, base + b_term, ((s >> 3) * DG + dg) * 128 + (s & 7) * 16);
             }
         } else {
             // columns d, contraction r (s or t): MN-major, core (r group, d group) = 8 r x 8 d
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
-                const int dg = u % DG, hh = (u / DG) & 1, r = u / (2 * DG);
+                const int r8 = u & 7, v = u >> 3;
+                const int dg = v % DG, hh = (v / DG) & 1, r = (v / (2 * DG)) * 8 + r8;
                 unsigned char *base = Bm + hh * 2 * b_term;
                 lo_b |= at_put8<TMA>(y_shd + r * pitch_y + hh * D + dg * 8, base, base + b_term, ((r >> 3) * DG + dg) * 128 + (r & 7) * 16);
             }
@@ -294,6 +310,11 @@ extern "C" int hgq_attn_heads_matmul(int kind, const float *x, const float *y, f
     if (kind < 0 || kind > 2) return HGQ_ERR_MODE;
     if (!hgq_attn_heads_supported(B, L, H, D)) return HGQ_ERR_SIZE;
     if (!aligned(x, 32) || !aligned(y, 32) || !aligned(out, 32)) return HGQ_ERR_ALIGN;  // 256-bit accesses
+    {
+        const int r = attn_ws_launch(kind, x, y, out, B, L, H, D, status, (cudaStream_t)stream);
+        if (r < 0) return -r;
+        if (r == 1) return check_launch();
+    }
     AtParams p;
     p.x = x; p.y = y; p.out = out; p.status = status;
     p.B = B; p.H = H; p.D = D;

@@ -32,9 +32,10 @@ static inline EncodeTiledFn encode_tiled_fn() {
 
 // A map over a row-major fp32 matrix [rows, cols] (row stride ld floats): boxes of box_rows x box_cols floats, rows of a
 // box contiguous in shared memory (no swizzle), zeros outside the matrix.  base 16-byte aligned, ld and box_cols
-// multiples of 4, box_cols and box_rows <= 256.
+// multiples of 4, box_cols and box_rows <= 256.  swizzle128: box_cols = 32 (128-byte rows); the 16-byte chunk c of row r
+// lands at chunk c ^ (r & 7) of its row, and the destination must start on a 1 KB boundary.
 static inline bool make_map_2d(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int64_t ld, int box_cols,
-                               int box_rows) {
+                               int box_rows, bool swizzle128 = false) {
     const EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr || base == nullptr) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -42,7 +43,8 @@ static inline bool make_map_2d(CUtensorMap *map, const float *base, int64_t rows
     const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+               swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 #ifdef __CUDACC__

@@ -122,19 +122,25 @@ def test_per_head_attention_products(B, H, D):
     assert float((g.cpu().double() - ref).abs().max()) <= 3e-5 * float(ref.abs().max())
 
 
-def test_per_thread_loads_and_wider_softmax_rows_on_the_same_cases():
-    # HGQ_ATTN_TMA=0 (read once per process) keeps the per-head products on per-thread loads instead of bulk tensor copies,
-    # HGQ_QSOFTMAX_LANES=32 keeps a whole warp on every row of 64 scores, HGQ_QSOFTMAX_GENERAL=1 keeps the softmax kernels on
-    # the variant that decides every mode at run time: the cases of this file and the softmax cases at the benchmark shape
-    # run again in a child process, so that both organisations stay covered by the same references
+@pytest.mark.parametrize('switches', [
+    # the general per-head kernel with per-thread loads, a whole warp per softmax row, softmax modes decided at run time
+    dict(HGQ_ATTN_WS='0', HGQ_ATTN_TMA='0', HGQ_QSOFTMAX_LANES='32', HGQ_QSOFTMAX_GENERAL='1'),
+    # the general per-head kernel with Q K^T's raw boxes from the copy engine (the default for that product) for all products
+    dict(HGQ_ATTN_WS='0'),
+    # the warp-specialised per-head kernel for Q K^T too (by default it takes the other two kinds of product)
+    dict(HGQ_ATTN_WS='2'),
+])
+def test_other_kernel_organisations_on_the_same_cases(switches):
+    # the switches are read once per process: the cases of this file and the attention / softmax cases at the benchmark
+    # shape run again in a child process, so that every organisation stays covered by the same references
     import os
     import subprocess
     import sys
 
-    env = dict(os.environ, HGQ_ATTN_TMA='0', HGQ_QSOFTMAX_LANES='32', HGQ_QSOFTMAX_GENERAL='1')
+    env = dict(os.environ, **switches)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, '-m', 'pytest', os.path.join(root, 'tests', 'test_attention_gpu.py'),
                         os.path.join(root, 'tests', 'test_benchmark_shapes_gpu.py'), '-q', '-x', '-m', 'gpu',
-                        '-k', '(softmax or qmha or per_head) and not per_thread_loads', '-p', 'no:cacheprovider'],
+                        '-k', '(softmax or qmha or per_head) and not other_kernel_organisations', '-p', 'no:cacheprovider'],
                        cwd=root, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
