@@ -10,7 +10,7 @@
 // CTA c of the kernel (the same grid on every rank)
 //   1. copies chunk c of its own gradients into its own slot, fences, and publishes the step number in the chunk's flag;
 //   2. waits -- a bounded number of polls with a sleep between them -- until the same flag of every peer shows the step number
-//      (plain peer loads over NVLink: no multicast, no NVLS, no collective library);
+//      (plain peer loads over NVLink: no switch-side reduction, no collective library);
 //   3. adds the chunk over the ranks in rank order (the same order on every rank, so all ranks compute bit-identical sums
 //      and their parameters never drift apart) and applies the update to its own copy of the parameters.
 // Two slots are enough: a rank can only write slot t & 1 again at step t + 2, after it has seen every peer's flag of step

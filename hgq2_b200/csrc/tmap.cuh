@@ -1,6 +1,6 @@
 // Tiled bulk-tensor copies (TMA) over this GPU's own memory: host-side tensor-map encoding through the runtime's driver
-// entry point query (the library does not link against libcuda), and the device-side copy instructions.  No copy here
-// uses cluster multicast.
+// entry point query (the library does not link against libcuda), and the device-side copy instructions.  Every copy here
+// is issued by one CTA for its own shared memory.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

@@ -403,7 +403,7 @@ int hgq_adam_step(float *w, const float *g, float *m, float *v, const float *lo,
  * gradient bucket in a buffer its peers have mapped, waits (bounded) for theirs, adds the buckets in rank order and applies
  * hgq_adam_step's update with grad_scale = 1 / world.  No reference counterpart in the HGQ2 tree: it stands in for the
  * gradient all-reduce of Keras' distribution strategy followed by optimizer.apply (see hgq_adam_step).  Plain peer loads
- * over NVLink; no multicast, no collective library.
+ * over NVLink; no switch-side reduction, no collective library.
  *
  * hgq_peer_exchange_bytes(n): size of one rank's exchange buffer for a bucket of n floats.
  * hgq_peer_buffer_create: cudaMalloc + zero fill on the current device; writes the 64-byte CUDA IPC handle that the other
