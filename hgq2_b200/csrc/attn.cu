@@ -81,10 +81,23 @@ __device__ __forceinline__ int at_put8(const float *src, unsigned char *hi_plane
     return at_cvt8(v, hi_plane, lo_plane, off);
 }
 
+// eight floats (row r, float columns fc .. fc + 7) of a [64, 2 D] raw tensor that the copy engine delivered as boxes of 32
+// columns x 64 rows with the 128-byte swizzle: 16-byte chunk c of a row sits at chunk position c ^ (r & 7)
+__device__ __forceinline__ int at_put8_swz(const unsigned char *raw, int r, int fc, unsigned char *hi_plane, unsigned char *lo_plane, int off) {
+    const unsigned char *row = raw + (fc >> 5) * kAtL * 128 + r * 128;
+    const int c0 = (fc & 31) >> 2;
+    const float4 a = *reinterpret_cast<const float4 *>(row + ((c0 ^ (r & 7)) << 4));
+    const float4 b = *reinterpret_cast<const float4 *>(row + (((c0 + 1) ^ (r & 7)) << 4));
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    return at_cvt8(v, hi_plane, lo_plane, off);
+}
+
 template <int KIND, bool TMA>
 __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, const __grid_constant__ CUtensorMap map_x,
                                                           const __grid_constant__ CUtensorMap map_y) {
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    // the swizzled raw boxes (TMA) need 1 KB aligned destinations whatever the base of dynamic shared memory is
+    unsigned char *smem = TMA ? smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u) : smem_raw;
     constexpr int L = kAtL;
     const int D = P.D, H = P.H, DG = D >> 3;
     // operand geometry
@@ -94,7 +107,8 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, con
     const int b_term = Nn * Ka * 2;              // B of one head
     unsigned char *A = smem;                     // [2 terms]
     unsigned char *Bm = A + 2 * a_term;          // [2 heads][2 terms]
-    // raw boxes (TMA): x and y are [64, 2 D] floats each; sizes are multiples of 128 B
+    // raw boxes (TMA): x and y are [64, 2 D] floats each, fetched as boxes of 32 columns with the 128-byte swizzle (one
+    // box for D = 16, two for D = 32); every size is a multiple of 1 KB
     static_assert(!TMA || KIND == 0, "bulk tensor copies are used for kind 0 only");
     const int rawx_bytes = TMA ? L * 2 * D * 4 : 0;
     const int rawy_bytes = TMA ? L * 2 * D * 4 : 0;
@@ -128,8 +142,10 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, con
         const int64_t tb = t / pairs;
         const int th0 = (int)(t - tb * pairs) * 2;
         tma::expect_tx(full, (uint32_t)(rawx_bytes + rawy_bytes));
-        tma::load_2d(tc::smem_u32(RX), &map_x, th0 * D, (int)(tb * L), full);
-        tma::load_2d(tc::smem_u32(RY), &map_y, th0 * D, (int)(tb * L), full);
+        for (int j = 0; j < ((2 * D) >> 5); ++j) {
+            tma::load_2d(tc::smem_u32(RX) + j * L * 128, &map_x, th0 * D + 32 * j, (int)(tb * L), full);
+            tma::load_2d(tc::smem_u32(RY) + j * L * 128, &map_y, th0 * D + 32 * j, (int)(tb * L), full);
+        }
     };
     if (TMA && tid == 0 && (int64_t)blockIdx.x < P.num_tiles) fetch(blockIdx.x);
 
@@ -160,15 +176,14 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, con
             // rows (hh, t), contraction d: K-major, core (row group, d group); unit = (t, hh, d group): a row of the pair is
             // 2 D contiguous floats in memory
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
-                int dg, hh, t;
-                if (TMA) { dg = u % DG; hh = (u / DG) & 1; t = u / (2 * DG); }  // raw box in shared memory: contiguous reads
-                else {  // the 8 lanes of a quarter-warp take the 8 rows of one core matrix: their 16-byte stores fill 128
-                        // contiguous bytes instead of hitting one bank group 8 times
-                    const int r8 = u & 7, v = u >> 3, rg = v / DG;
-                    dg = v - rg * DG; hh = rg >> 3; t = (rg & 7) * 8 + r8;
-                }
+                // the 8 lanes of a quarter-warp take the 8 rows of one core matrix: their 16-byte stores fill 128 contiguous
+                // bytes instead of hitting one bank group 8 times (and, with the raw box in shared memory, their reads of the
+                // swizzled rows hit 8 different chunk positions)
+                const int r8 = u & 7, v = u >> 3, rg = v / DG;
+                const int dg = v - rg * DG, hh = rg >> 3, t = (rg & 7) * 8 + r8;
                 const int row = hh * 64 + t;
-                lo_a |= at_put8<TMA>(x_shd + t * pitch_x + hh * D + dg * 8, A, A + a_term, ((row >> 3) * DG + dg) * 128 + (row & 7) * 16);
+                if (TMA) lo_a |= at_put8_swz(reinterpret_cast<const unsigned char *>(RX), t, hh * D + dg * 8, A, A + a_term, ((row >> 3) * DG + dg) * 128 + (row & 7) * 16);
+                else lo_a |= at_put8<false>(x_shd + t * pitch_x + hh * D + dg * 8, A, A + a_term, ((row >> 3) * DG + dg) * 128 + (row & 7) * 16);
             }
         } else if (KIND == 1) {
             // rows (hh, t), contraction s: K-major, core (row group, s group): a row is 64 contiguous floats
@@ -189,14 +204,11 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, con
         if (KIND == 0) {
             // rows s (the product's columns), contraction d: K-major, core (s group, d group)
             for (int u = tid; u < 128 * DG; u += kAtThreads) {
-                int dg, hh, s;
-                if (TMA) { dg = u % DG; hh = (u / DG) & 1; s = u / (2 * DG); }
-                else {
-                    const int r8 = u & 7, v = u >> 3;
-                    dg = v % DG; hh = (v / DG) & 1; s = (v / (2 * DG)) * 8 + r8;
-                }
+                const int r8 = u & 7, v = u >> 3;
+                const int dg = v % DG, hh = (v / DG) & 1, s = (v / (2 * DG)) * 8 + r8;
                 unsigned char *base = Bm + hh * 2 * b_term;
-                lo_b |= at_put8<TMA>(y_shd + s * pitch_y + hh * D + dg * 8, base, base + b_term, ((s >> 3) * DG + dg) * 128 + (s & 7) * 16);
+                if (TMA) lo_b |= at_put8_swz(reinterpret_cast<const unsigned char *>(RY), s, hh * D + dg * 8, base, base + b_term, ((s >> 3) * DG + dg) * 128 + (s & 7) * 16);
+                else lo_b |= at_put8<false>(y_shd + s * pitch_y + hh * D + dg * 8, base, base + b_term, ((s >> 3) * DG + dg) * 128 + (s & 7) * 16);
             }
         } else {
             // columns d, contraction r (s or t): MN-major, core (r group, d group) = 8 r x 8 d
@@ -284,7 +296,7 @@ __global__ void __launch_bounds__(kAtThreads) k_attn_heads(const AtParams P, con
 static size_t at_smem(int kind, int D, bool tma) {
     const int Ka = kind == 0 ? D : kAtL, Nn = kind == 0 ? kAtL : D;
     const size_t raw = tma ? 2 * (size_t)kAtL * 2 * D * 4 : 0;  // the raw boxes of x and y (kind 0)
-    return 2 * (size_t)128 * Ka * 2 + 4 * (size_t)Nn * Ka * 2 + raw + 64;
+    return 2 * (size_t)128 * Ka * 2 + 4 * (size_t)Nn * Ka * 2 + raw + 64 + (tma ? 1024 : 0);  // + room to align the carve to 1 KB
 }
 
 // HGQ_ATTN_TMA=0 in the environment keeps the per-thread loads (for comparisons).
@@ -325,8 +337,8 @@ extern "C" int hgq_attn_heads_matmul(int kind, const float *x, const float *y, f
     memset(&map_y, 0, sizeof(map_y));
     const int64_t rows_shd = B * L;
     const bool tma = kind == 0 && at_tma_enabled() && rows_shd < ((int64_t)1 << 31) &&
-                     tma::make_map_2d(&map_x, x, rows_shd, (int64_t)H * D, (int64_t)H * D, 2 * D, kAtL) &&
-                     tma::make_map_2d(&map_y, y, rows_shd, (int64_t)H * D, (int64_t)H * D, 2 * D, kAtL);
+                     tma::make_map_2d(&map_x, x, rows_shd, (int64_t)H * D, (int64_t)H * D, 32, kAtL, true) &&
+                     tma::make_map_2d(&map_y, y, rows_shd, (int64_t)H * D, (int64_t)H * D, 32, kAtL, true);
     const size_t smem = at_smem(kind, D, tma);
     int per_sm = (int)((228 * 1024) / (smem + 1024));
     const int cap = 4;  // measured optimum for all three kinds with per-thread loads (3 and 5 resident CTAs are both slower)
