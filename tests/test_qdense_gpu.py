@@ -152,6 +152,7 @@ def test_fused_dense_no_input_quantizer_and_limits():
 @pytest.mark.parametrize('M,K,N,rows_period', [
     (1000, 16, 64, 1), (128 * 21 + 5, 64, 64, 64), (4096, 64, 32, 1), (513, 32, 5, 1), (300, 24, 16, 8), (640, 64, 128, 32),
     (129, 27, 10, 1), (7, 16, 64, 1), (60000, 64, 64, 64), (2000, 48, 40, 2), (3000, 128, 64, 64), (700, 96, 32, 1),
+    (128 * 50 + 9, 64, 128, 64),  # 128 outputs: two calls over column slices of dY and y
 ])
 @pytest.mark.parametrize('rm,relu,quant', [('RND', True, True), ('TRN', False, True), ('RND_CONV', True, True), ('RND', True, False)])
 def test_fused_dense_backward(M, K, N, rows_period, rm, relu, quant):
