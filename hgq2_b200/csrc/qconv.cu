@@ -38,6 +38,7 @@ struct ClParams {
     int64_t Q, num_tiles;      // padded positions of the whole batch; tiles of Pt positions
     int H, W, C, N, Np, OH, OW, Hp, Wp, KH, KW, dh, dw, pt, pl;
     int ncg, nsteps, MB, npx;  // channel groups, MMA K-steps, 128-row blocks per tile, staged pixels per tile
+    int cgb;                   // bytes from one channel group's pixels to the next (see cl_group_pad)
     int act;
     FastDiv div_img, div_row, div_cg;  // by Hp * Wp, by Wp and by the number of channel groups
 };
@@ -58,11 +59,11 @@ __global__ void __launch_bounds__(kClThreads, VEC_C ? 4 : 3) k_qconv_s1(const Cl
     extern __shared__ __align__(128) unsigned char smem[];
     const int Np = P.Np, ncg = P.ncg, nsteps = P.nsteps, MB = P.MB, npx = P.npx;
     const int Pt = MB * 128;
-    const int cg_bytes = npx * 16;                 // one channel group of one term
+    const int cg_bytes = P.cgb;                    // one channel group of one term: npx pixels of 16 bytes, padded
     const int img_term_bytes = ncg * cg_bytes;
     const int w_step_bytes = Np * 32;              // one K = 16 step of the weights: Np rows x 16 bf16
     const int w_term_bytes = nsteps * w_step_bytes;
-    unsigned char *IMG = smem;                                          // [2 terms][ncg][npx] x 16 B
+    unsigned char *IMG = smem;                                          // [2 terms][ncg] x cg_bytes
     unsigned char *WT = IMG + 2 * img_term_bytes;                       // [2 terms][nsteps][Np/8][2 halves] x 128 B
     int2 *steps = reinterpret_cast<int2 *>(WT + 2 * w_term_bytes);      // per step: A start offset, A leading offset
     float *bias_s = reinterpret_cast<float *>(steps + nsteps);
@@ -93,19 +94,27 @@ __global__ void __launch_bounds__(kClThreads, VEC_C ? 4 : 3) k_qconv_s1(const Cl
         steps[s] = make_int2(off0, lbo);
     }
     for (int e = tid; e < Np; e += kClThreads) bias_s[e] = (P.bq != nullptr && e < P.N) ? __ldg(P.bq + e) : 0.f;
-    // weights -> two bf16 terms; element (n, octet o, j): step o/2, half o&1
+    // weights -> two bf16 terms; a thread converts the eight channels of (output channel n, octet o): step o/2, half o&1.
+    // Eight loads in flight per thread and one 16-byte store per term: the conversion of a 288 x 64 kernel is 9 rounds
+    // per CTA, and the eight threads of a quarter-warp fill the eight rows of one core matrix (no bank conflict).
     int w_lo = 0;
-    for (int e = tid; e < nsteps * 16 * Np; e += kClThreads) {
-        const int n = e % Np, kk = e / Np;           // kk = step * 16 + half * 8 + j
-        const int o = kk >> 3, j = kk & 7;
-        const int cg = o / T, t = o - cg * T, c = cg * 8 + j;
-        const float w = (o < n_oct && c < P.C && n < P.N) ? __ldg(P.wq + ((int64_t)t * P.C + c) * P.N + n) : 0.f;
-        uint32_t hi, lo;
-        cl_split2(w, 0.f, hi, lo);
-        const int off = (kk >> 4) * w_step_bytes + ((n >> 3) * 2 + ((kk >> 3) & 1)) * 128 + (n & 7) * 16 + j * 2;
-        *reinterpret_cast<unsigned short *>(WT + off) = (unsigned short)(hi & 0xffffu);
-        *reinterpret_cast<unsigned short *>(WT + w_term_bytes + off) = (unsigned short)(lo & 0xffffu);
-        w_lo |= (lo & 0x7fffu) != 0;
+    const int np_shift = 31 - __clz(Np);  // Np is a power of two
+    for (int e = tid; e < nsteps * 2 * Np; e += kClThreads) {
+        const int n = e & (Np - 1), o = e >> np_shift;
+        const int cg = o / T, t = o - cg * T;
+        float w8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = cg * 8 + j;
+            w8[j] = (o < n_oct && c < P.C && n < P.N) ? __ldg(P.wq + ((int64_t)t * P.C + c) * P.N + n) : 0.f;
+        }
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cl_split2(w8[2 * j], w8[2 * j + 1], hi[j], lo[j]);
+        const int off = (o >> 1) * w_step_bytes + ((n >> 3) * 2 + (o & 1)) * 128 + (n & 7) * 16;
+        *reinterpret_cast<uint4 *>(WT + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4 *>(WT + w_term_bytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        w_lo |= ((lo[0] | lo[1] | lo[2] | lo[3]) & 0x7fff7fffu) != 0;
     }
     const int n_w = __syncthreads_or(w_lo) ? 2 : 1;
     tc::fence_smem_to_async();
@@ -244,15 +253,21 @@ __global__ void __launch_bounds__(kClThreads, VEC_C ? 4 : 3) k_qconv_s1(const Cl
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
+// Padding between the pixel arrays of consecutive channel groups.  The staging threads of a quarter-warp hold consecutive
+// (pixel, group) units: 8 / groups pixels of every group.  With group arrays a multiple of 128 bytes apart their 16-byte
+// stores would fall on the same banks (2-, 4- or 8-way conflicts); a stride of 128 / groups bytes modulo 128 lets the
+// eight stores tile the 32 banks.  Descriptors address windows in 16-byte units, so any multiple of 16 is a legal stride.
+int cl_group_pad(int groups) { return groups >= 8 ? 16 : groups >= 4 ? 32 : groups >= 2 ? 64 : 0; }
+
 struct ClGeom {
-    int Np, Hp, Wp, ncg, nsteps, MB, npx, grid;
+    int Np, Hp, Wp, ncg, nsteps, MB, npx, cgb, grid;
     size_t smem;
     int64_t Q, tiles;
 };
 
 static size_t cl_smem(int MB, int halo, int ncg, int nsteps, int Np, int &npx) {
     npx = (MB * 128 + halo + 7) / 8 * 8;
-    return 2 * (size_t)ncg * npx * 16 + 2 * (size_t)nsteps * Np * 32 + (size_t)nsteps * 8 + (size_t)Np * 4 + 64;
+    return 2 * (size_t)ncg * (npx * 16 + cl_group_pad(ncg)) + 2 * (size_t)nsteps * Np * 32 + (size_t)nsteps * 8 + (size_t)Np * 4 + 64;
 }
 
 static int cl_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH, int OW, int dh, int dw, ClGeom &g) {
@@ -275,12 +290,13 @@ static int cl_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH
         const size_t sm = cl_smem(mb, halo, g.ncg, g.nsteps, g.Np, npx);
         if (sm <= 72 * 1024 || mb == 1) {
             g.MB = mb; g.npx = npx; g.smem = sm;
+            g.cgb = npx * 16 + cl_group_pad(g.ncg);
             break;
         }
     }
     if (g.MB == 0 || g.smem > 226 * 1024) return HGQ_ERR_SIZE;
     // window offsets must fit the descriptor's 14-bit (x 16 bytes) leading-dimension field
-    if ((size_t)g.ncg * g.npx * 16 >= (1u << 18)) return HGQ_ERR_SIZE;
+    if ((size_t)g.ncg * g.cgb >= (1u << 18)) return HGQ_ERR_SIZE;
     g.tiles = (g.Q + g.MB * 128 - 1) / (g.MB * 128);
     int per_sm = (int)((228 * 1024) / (g.smem + 1024));
     if (per_sm > 4) per_sm = 4;
@@ -326,7 +342,7 @@ extern "C" int hgq_qconv2d_fwd(const float *x, int64_t B, int H, int W, int C, c
     p.Q = g.Q; p.num_tiles = g.tiles;
     p.H = H; p.W = W; p.C = C; p.N = N; p.Np = g.Np; p.OH = OH; p.OW = OW; p.Hp = g.Hp; p.Wp = g.Wp;
     p.KH = KH; p.KW = KW; p.dh = dil_h; p.dw = dil_w; p.pt = pad_top; p.pl = pad_left;
-    p.ncg = g.ncg; p.nsteps = g.nsteps; p.MB = g.MB; p.npx = g.npx; p.act = activation;
+    p.ncg = g.ncg; p.nsteps = g.nsteps; p.MB = g.MB; p.npx = g.npx; p.cgb = g.cgb; p.act = activation;
     p.div_img = make_fastdiv((uint32_t)(g.Hp * g.Wp));
     p.div_row = make_fastdiv((uint32_t)g.Wp);
     p.div_cg = make_fastdiv((uint32_t)g.ncg);

@@ -21,6 +21,8 @@
 
 namespace hgq {
 
+int cl_group_pad(int groups);  // qconv.cu: padding between the pixel arrays of consecutive channel groups
+
 constexpr int kCwThreads = 256;
 constexpr int kCwTileM = 128;
 constexpr int kCwXTermBytes = 128 * 128 * 2;
@@ -304,6 +306,7 @@ struct CsParams {
     int64_t Q, num_tiles;
     int H, W, C, N, Np, OH, OW, Hp, Wp, KH, KW, dh, dw, pt, pl;
     int ncg, ng, Pt, npx, stack;
+    int cgb, ggb;  // bytes between the pixel arrays of consecutive channel groups of the image / of G (padded: cl_group_pad)
     FastDiv div_img, div_row, div_cg;  // by Hp * Wp, by Wp and by the number of channel groups
 };
 
@@ -315,8 +318,8 @@ template <bool VEC_C, int NT>
 __global__ void __launch_bounds__(NT) k_qconv_wgrad_s1(const CsParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int Np = P.Np, ncg = P.ncg, ng = P.ng, Pt = P.Pt, npx = P.npx, N = P.N;
-    const int cg_bytes = npx * 16, img_term = ncg * cg_bytes;
-    const int gg_bytes = Pt * 16, g_term = ng * gg_bytes;
+    const int cg_bytes = P.cgb, img_term = ncg * cg_bytes;
+    const int gg_bytes = P.ggb, g_term = ng * gg_bytes;
     unsigned char *IMG = smem;
     unsigned char *GS = IMG + 2 * img_term;
     float *red = reinterpret_cast<float *>(GS + 2 * g_term);           // [256][8] bias-gradient partials
@@ -549,7 +552,8 @@ static int cs_geom(int64_t B, int H, int W, int C, int KH, int KW, int N, int OH
     g.Pt = 0;
     for (int pt = 512; pt >= 128; pt >>= 1) {
         const int npx = (pt + reach + 7) / 8 * 8;
-        const size_t sm = 2 * (size_t)g.ncg * npx * 16 + 2 * (size_t)g.ng * pt * 16 + (size_t)kCwThreads * 32 + 64;
+        const size_t sm = 2 * (size_t)g.ncg * (npx * 16 + cl_group_pad(g.ncg)) + 2 * (size_t)g.ng * (pt * 16 + cl_group_pad(g.ng)) +
+                          (size_t)kCwThreads * 32 + 64;
         if (sm <= 100 * 1024 || pt == 128) {
             g.Pt = pt; g.npx = npx; g.smem = sm;
             break;
@@ -646,6 +650,7 @@ extern "C" int hgq_qconv2d_wgrad(const float *x, const float *gy, const float *y
         q.H = H; q.W = W; q.C = C; q.N = N; q.Np = gs.Np; q.OH = OH; q.OW = OW; q.Hp = gs.Hp; q.Wp = gs.Wp;
         q.KH = KH; q.KW = KW; q.dh = dil_h; q.dw = dil_w; q.pt = pad_top; q.pl = pad_left;
         q.ncg = gs.ncg; q.ng = gs.ng; q.Pt = gs.Pt; q.npx = gs.npx; q.stack = gs.stack;
+        q.cgb = gs.npx * 16 + cl_group_pad(gs.ncg); q.ggb = gs.Pt * 16 + cl_group_pad(gs.ng);
         q.div_img = make_fastdiv((uint32_t)(gs.Hp * gs.Wp));
         q.div_row = make_fastdiv((uint32_t)gs.Wp);
         q.div_cg = make_fastdiv((uint32_t)gs.ncg);
