@@ -293,7 +293,8 @@ class _Dense(_Node):
 
 
 class _Conv(_Node):
-    """QConv2D on the implicit-GEMM kernels (unit stride), its input quantizer as a rounding pass of its own."""
+    """QConv2D / QConv1D on the implicit-GEMM kernels (unit stride), its input quantizer as a rounding pass of its own.  A
+    1-D layer is an image of one row: [B, W, C] activations are [B, 1, W, C] in memory as they stand."""
 
     def __init__(self, eng, layer, in_shape):
         self.layer = layer
@@ -301,10 +302,16 @@ class _Conv(_Node):
         _require(layer.enable_iq and not (layer.enable_oq and not layer.__output_quantizer_handled__), f'{layer.name}: iq / oq set-up')
         _require(tuple(layer.strides) == (1, 1), f'{layer.name}: strided convolution')
         self.relu = layer._activation_spec == 'relu'
-        _, H, W, C = in_shape
-        KH, KW, _, N = layer._kernel.shape
+        self.one_d = layer.rank == 1
+        if self.one_d:
+            (_, W, C), H = in_shape, 1
+            (KW, _, N), KH = layer._kernel.shape, 1
+            self.out = (1, 1) + tuple(layer.compute_output_shape((1, W, C))[1:])
+        else:
+            _, H, W, C = in_shape
+            KH, KW, _, N = layer._kernel.shape
+            self.out = layer.compute_output_shape((1, H, W, C))
         self.geom = (H, W, C, KH, KW, N)
-        self.out = layer.compute_output_shape((1, H, W, C))
         (pt, _), (pl, _) = layer._pads(H, W)
         self.pad_tl, self.dil = (pt, pl), tuple(layer.dilation_rate)
         self.iq = eng.slot(layer.iq, 'act')
@@ -333,18 +340,19 @@ class _Conv(_Node):
 
     def forward(self, x):
         H, W, C, KH, KW, N = self.geom
-        x = x.contiguous()
+        x = x.contiguous().view(-1, H, W, C)
         _, OH, OW, _ = self.out
         xq = kernels.quantize_fwd(x, None, None, self.iq.F.view(-1), self.iq.q.round_mode, 'NONE', training=True,
                                   want_absmax=True, absmax_out=self.iq.absmax)[0]
         y = kernels.qconv2d_fwd(xq, self.wq.view(KH * KW * C, N), self.bias_q, 'relu' if self.relu else None, KH, KW, (OH, OW),
                                 (1, 1), self.dil, self.pad_tl)
         self.x, self.xq, self.y = x, xq, (y if self.relu else None)
-        return y
+        return y.view(-1, OW, N) if self.one_d else y
 
     def backward(self, g, need_dx=True):
         H, W, C, KH, KW, N = self.geom
-        gm, _, _ = kernels.qconv2d_wgrad(self.xq, g.contiguous(), self.y, KH, KW, (1, 1), self.dil, self.pad_tl, self.dbq is not None,
+        _, OH, OW, _ = self.out
+        gm, _, _ = kernels.qconv2d_wgrad(self.xq, g.contiguous().view(-1, OH, OW, N), self.y, KH, KW, (1, 1), self.dil, self.pad_tl, self.dbq is not None,
                                          out_dwq=self.dwq.view(KH * KW * C, N), out_dbq=self.dbq)
         # the input gradient is the same convolution kernel over the masked gradient with the flipped, transposed kernel
         wt = self.wq.view(KH, KW, C, N).flip(0, 1).permute(0, 1, 3, 2).reshape(KH * KW * N, C)
@@ -354,7 +362,9 @@ class _Conv(_Node):
         kernels.quantize_bwd(dxq, self.x, None, None, self.iq.F.view(-1), self.iq.q.round_mode, 'NONE', want_dx=False,
                              want_di=False, out_df=self.iq.dF.view(-1))
         self.x = self.xq = self.y = None
-        return dxq if need_dx else None
+        if not need_dx:
+            return None
+        return dxq.view(-1, W, C) if self.one_d else dxq
 
     def ebops(self, eng):
         if self.eb_index is None:

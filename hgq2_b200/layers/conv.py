@@ -1,4 +1,5 @@
-"""QConv2D: act(conv2d(iq(x), kq(W)) + bq(b)) with EBOPs (mirror of src/hgq/layers/conv.py, rank 2, channels_last)."""
+"""QConv2D / QConv1D: act(conv(iq(x), kq(W)) + bq(b)) with EBOPs (mirror of src/hgq/layers/conv.py, ranks 2 and 1,
+channels_last)."""
 
 from __future__ import annotations
 
@@ -109,7 +110,7 @@ class QConv2D(QLayerBaseSingleInput):
     def build(self, input_shape):
         # kernel and bias before the base classes' beta / ebops: the reference's variable order
         c = int(input_shape[-1])
-        self._kernel = self.add_weight(name='kernel', shape=self.kernel_size + (c, self.filters),
+        self._kernel = self.add_weight(name='kernel', shape=self._kernel_shape(c),
                                        initializer=self.kernel_initializer, regularizer=self.kernel_regularizer,
                                        constraint=self.kernel_constraint)
         if self.use_bias:
@@ -122,11 +123,17 @@ class QConv2D(QLayerBaseSingleInput):
         if self.use_bias:
             self.bq.build(tuple(self._bias.shape))
             self.bq.built = True
-        self._built_hw = (int(input_shape[1]), int(input_shape[2]))
+        self._built_hw = self._image_hw(input_shape)
         out = self.compute_output_shape(input_shape)
         self.n_parallel = prod(int(d) for d in out[1:-1])
         if self.parallelization_factor <= 0:
             self.parallelization_factor = self.n_parallel
+
+    def _kernel_shape(self, channels):
+        return self.kernel_size + (channels, self.filters)
+
+    def _image_hw(self, input_shape):
+        return (int(input_shape[1]), int(input_shape[2]))
 
     def convolution_op(self, inputs, kernel):
         """channels_last 2-D convolution through the library (shapes the implicit-GEMM kernels do not cover)."""
@@ -153,10 +160,14 @@ class QConv2D(QLayerBaseSingleInput):
         if self.enable_iq:
             inputs = self.iq(inputs, training=training)
         qkernel, qbias = take_prepared(self) or self.prepare_params()
+        return self._contract(inputs, qkernel, qbias)
+
+    def _contract(self, inputs, qkernel, qbias):
+        """act(conv(inputs, qkernel) + qbias) on quantised operands: [B, H, W, C] image, [KH, KW, C, N] kernel."""
         fused = fused_conv2d_call(self, inputs, qkernel, qbias)
         if fused is not None:
             return fused
-        routes.fallback('cudnn.conv2d', f'QConv2D {self.name}')
+        routes.fallback('cudnn.conv2d', f'{type(self).__name__} {self.name}')
         outputs = self.convolution_op(inputs, qkernel)
         if self.use_bias:
             outputs = outputs + qbias.reshape(1, 1, 1, self.filters)
@@ -196,3 +207,64 @@ class QConv2D(QLayerBaseSingleInput):
         if self.bias is None:
             return None
         return self.bq(self._bias.value)
+
+
+class QConv1D(QConv2D):
+    """act(conv1d(iq(x), kq(W)) + bq(b)) on [batch, steps, channels] inputs (QConv1D of src/hgq/layers/conv.py:127-174; the
+    call and the EBOPs are QBaseConv's, conv.py:72-102): QConv2D's kernels on an image of one row.  The kernel variable has the
+    reference's shape [kernel_size, channels, filters].  padding: 'valid', 'same' or 'causal' (kernel_size - 1 dilated steps of
+    zeros in front, none behind, as keras' Conv1D)."""
+
+    rank = 1
+
+    def __init__(self, filters, kernel_size, strides=1, padding='valid', data_format=None, dilation_rate=1, **kwargs):
+        def one(v):
+            return int(v[0]) if isinstance(v, (tuple, list)) else int(v)
+
+        causal = padding == 'causal'
+        super().__init__(filters, (1, one(kernel_size)), strides=(1, one(strides)), padding='valid' if causal else padding,
+                         data_format=data_format, dilation_rate=(1, one(dilation_rate)), **kwargs)
+        if causal:
+            self.padding = 'causal'
+
+    def _pads(self, h, w):
+        if self.padding == 'causal':
+            return (0, 0), ((self.kernel_size[1] - 1) * self.dilation_rate[1], 0)
+        return super()._pads(h, w)
+
+    def _kernel_shape(self, channels):
+        return (self.kernel_size[1], channels, self.filters)
+
+    def _image_hw(self, input_shape):
+        return (1, int(input_shape[1]))
+
+    def compute_output_shape(self, input_shape):
+        if len(input_shape) == 4:  # the one-row image the 2-D kernels see
+            return super().compute_output_shape(input_shape)
+        b, w, c = input_shape
+        out = super().compute_output_shape((b, 1, w, c))
+        return (out[0], out[2], out[3])
+
+    def call(self, inputs, training=None):
+        if self.enable_iq:
+            inputs = self.iq(inputs, training=training)
+        qkernel, qbias = take_prepared(self) or self.prepare_params()
+        return self._contract(inputs.unsqueeze(1), qkernel.unsqueeze(0), qbias).squeeze(1)
+
+    def _compute_ebops(self, shape):
+        shape = tuple(shape)
+        _, w, _ = shape
+        bw_inp = self.iq.bits_(shape)[0].unsqueeze(0)
+        bw_ker = self.kq.bits_(tuple(self._kernel.shape)).unsqueeze(0)
+        bw_bias = self.bq.bits_(tuple(self._bias.shape)) if self.bq is not None else None
+        (pt, _), (pl, _) = self._pads(1, w)
+        out = self.compute_output_shape(shape)
+        size = float(prod(shape[:-1]) * self.filters)
+        return EbopsConv2dFn.apply(bw_inp, bw_ker, bw_bias, (1, out[1]), self.strides, self.dilation_rate, (pt, pl),
+                                   size, self.parallelization_factor / self.n_parallel, 1.0)
+
+    def get_config(self):
+        config = super().get_config()
+        config.update({'kernel_size': (self.kernel_size[1],), 'strides': (self.strides[1],),
+                       'dilation_rate': (self.dilation_rate[1],)})
+        return config

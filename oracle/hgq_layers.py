@@ -312,6 +312,26 @@ class OracleQConv2D(OracleQLayer):
         return ebops
 
 
+class OracleQConv1D(OracleQConv2D):
+    """QConv1D (layers/conv.py:127-174; call and EBOPs of QBaseConv, conv.py:72-102), channels_last: [B, W, C] inputs,
+    [KW, C, N] kernel.  `pads` = (left, right); 'causal' is (dilation (KW - 1), 0)."""
+
+    def conv(self, x, w):
+        pl, pr = self.pads
+        x = x.permute(0, 2, 1)
+        if pl or pr:
+            x = F.pad(x, (pl, pr))
+        return F.conv1d(x, w.permute(2, 1, 0), stride=self.strides, dilation=self.dilation).permute(0, 2, 1)
+
+    def call(self, x, training):
+        if self.iq is not None:
+            x = self.iq(x, training)
+        y = self.conv(x, self.kq(self.kernel, training))
+        if self.bias is not None:
+            y = y + self.bq(self.bias, training).reshape(1, 1, -1)
+        return self._act(y)
+
+
 # ---- building an oracle twin of a product object (reads variables by their reference names) ----
 def _np(v):
     return v.value.detach().cpu()
@@ -335,7 +355,7 @@ def mirror_quantizer(q):
 
 
 def mirror_layer(layer):
-    """Oracle twin of a built hgq2_b200 QDense / QEinsumDense / QConv2D."""
+    """Oracle twin of a built hgq2_b200 QDense / QEinsumDense / QConv2D / QConv1D."""
     name = type(layer).__name__
     common = dict(
         iq=mirror_quantizer(layer.iq) if layer.enable_iq else None, kq=mirror_quantizer(layer.kq),
@@ -353,6 +373,10 @@ def mirror_layer(layer):
     if name == 'QConv2D':
         h, w = layer._built_hw
         return OracleQConv2D(kernel, bias, layer.strides, layer.dilation_rate, layer._pads(h, w), layer.n_parallel,
+                             layer.parallelization_factor, **common)
+    if name == 'QConv1D':
+        _, w = layer._built_hw
+        return OracleQConv1D(kernel, bias, layer.strides[1], layer.dilation_rate[1], layer._pads(1, w)[1], layer.n_parallel,
                              layer.parallelization_factor, **common)
     raise NotImplementedError(name)
 

@@ -39,7 +39,7 @@ def mirror_model(model):
     out = []
     for layer in model.layers:
         name = type(layer).__name__
-        if name in ('QDense', 'QEinsumDense', 'QConv2D'):
+        if name in ('QDense', 'QEinsumDense', 'QConv2D', 'QConv1D'):
             out.append(OL.mirror_layer(layer))
         elif name == 'QMultiHeadAttention':
             out.append(OL.mirror_mha(layer))

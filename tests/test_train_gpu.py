@@ -95,6 +95,39 @@ def test_small_cnn_steps(engine):
     run_steps(workloads.small_cnn, x, y, steps=2, engine=engine)
 
 
+def _conv1d_net(beta0=1e-5):
+    """Two causal / valid QConv1D layers (the second dilated) on [B, 24, 8] sequences, Flatten (160 features), QDense -> 5."""
+    from hgq2_b200 import workloads as W
+    from hgq2_b200.backend import Flatten, Sequential
+    from hgq2_b200.layers import QConv1D, QDense
+
+    w, a, l = W._scopes(3, 6, beta0)
+    with w, a, l:
+        layers = W._seeded([
+            QConv1D(16, 5, padding='causal', activation='relu'),
+            QConv1D(8, 3, dilation_rate=2, activation='relu'),
+            Flatten(), QDense(5),
+        ])
+    model = Sequential(layers, name='conv1d_net')
+    model.input_shape = (24, 8)
+    model.weight_bits = (3, 8)
+    return model
+
+
+@pytest.mark.parametrize('engine', [True, False])
+def test_conv1d_net_steps(engine):
+    """QConv1D layers in a full QAT step: the static step plan runs them on the 2-D implicit-GEMM kernels as images of one
+    row (engine=True: the plan must cover the model, no library convolution)."""
+    from hgq2_b200 import routes
+
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((64, 24, 8)).astype(np.float32)
+    y = np.random.default_rng(6).integers(0, 5, 64)
+    routes.reset()
+    run_steps(_conv1d_net, x, y, steps=2, engine=engine)
+    assert not routes.fallbacks(), routes.fallbacks()
+
+
 def test_transformer_block_steps():
     # sequence 16: outside the per-head attention kernel, so this model takes the autograd path (torch.einsum products)
     from hgq2_b200 import workloads
