@@ -1,11 +1,14 @@
 """Properties that need no oracle, checked at the benchmark's FULL sizes (where the CPU oracle would take minutes): the
-quantizer sweep's 2^28 elements, the particle layer's 4.19 M rows, the transformer's 134 M attention scores.
+quantizer sweep's 2^28 elements, the particle layer's 4.19 M rows, the transformer's 134 M attention scores and its other
+per-head products at batch 8192, the three convolution layers of the small CNN at batch 4096.
 
 * idempotence and range membership of the quantizer; its backward passes the gradient or zero;
 * shard invariance: a contiguous shard of the input gives the same bits as the same slice of the full result (what the
   multi-GPU sweep and the data-parallel step rely on), and reductions over the batch are the reductions of the shards;
 * exact homogeneity under scaling by powers of two (weights and bias x 2 => outputs x 2; upstream gradient x 2 => every
-  gradient x 2), which holds bit for bit in binary floating point when nothing over- or underflows.
+  gradient x 2), which holds bit for bit in binary floating point when nothing over- or underflows;
+* sampled outputs against the definition evaluated in float64 on the GPU (exact equality where the operands lie on grids
+  coarse enough for fp32 sums to be exact).
 """
 
 import pytest
@@ -142,3 +145,92 @@ def test_attention_scores_at_134_million():
     del dsa
     ds2, sc2, df52, _ = K.qsoftmax_bwd(g * 2, s, quants, 0.25, 1e-7, rp, False)
     assert torch.equal(ds2, ds * 2) and torch.equal(sc2, sc * 2) and torch.equal(df52, df5 * 2)
+
+
+@pytest.mark.parametrize('H,C,N', [(32, 4, 16), (15, 16, 32), (6, 32, 64)])
+def test_convolution_layers_at_batch_4096(H, C, N):
+    """The three layers of the small CNN at the benchmark batch: forward, input gradient and weight gradient.
+    Operands on coarse binary grids make every product and sum exact in fp32, so sampled outputs must EQUAL a float64
+    evaluation of the definition, and shards / sums of shards must equal the whole bit for bit."""
+    from hgq2_b200 import kernels as K
+
+    B, OH = 4096, H - 2
+    gen = torch.Generator(device='cuda').manual_seed(H)
+    x = torch.randint(0, 32, (B, H, H, C), device='cuda', generator=gen).float() / 32          # 5-bit activations
+    w = torch.randint(-64, 64, (3, 3, C, N), device='cuda', generator=gen).float() / 64        # 7-bit weights
+    b = torch.randint(-8, 8, (N,), device='cuda', generator=gen).float() / 8
+    y = K.qconv2d_fwd(x, w.reshape(-1, N), b, 'relu', 3, 3, (OH, OH), (1, 1), (1, 1), (0, 0))
+    K.check_status(x.device)
+    assert y.shape == (B, OH, OH, N)
+    # sampled output pixels against the definition in float64
+    n_s = 4096
+    bi = torch.randint(0, B, (n_s,), device='cuda', generator=gen)
+    oy = torch.randint(0, OH, (n_s,), device='cuda', generator=gen)
+    ox = torch.randint(0, OH, (n_s,), device='cuda', generator=gen)
+    dy, dx_ = torch.meshgrid(torch.arange(3, device='cuda'), torch.arange(3, device='cuda'), indexing='ij')
+    patches = x[bi[:, None, None], oy[:, None, None] + dy, ox[:, None, None] + dx_]             # [n_s, 3, 3, C]
+    ref = torch.einsum('sklc,klcn->sn', patches.double(), w.double()) + b.double()
+    assert torch.equal(y[bi, oy, ox].double(), ref.clamp_min(0))
+    # shard invariance
+    h = B // 2
+    assert torch.equal(K.qconv2d_fwd(x[h:].contiguous(), w.reshape(-1, N), b, 'relu', 3, 3, (OH, OH), (1, 1), (1, 1), (0, 0)), y[h:])
+    # backward on an upstream gradient with 6 significant bits: masked gradient, weight / bias / input gradients
+    gy = torch.randint(-32, 32, (B, OH, OH, N), device='cuda', generator=gen).float() / 32
+    gm, dw, db = K.qconv2d_wgrad(x, gy, y, 3, 3, (1, 1), (1, 1), (0, 0), True)
+    gm, dw, db = gm.clone(), dw.clone(), db.clone()
+    K.check_status(x.device)
+    assert torch.equal(gm, gy * (y > 0))
+    assert torch.equal(db, gm.double().sum(dim=(0, 1, 2)).float())  # exact partial sums, one rounding to fp32 at the end
+    _, dwa, dba = (t.clone() for t in K.qconv2d_wgrad(x[:h].contiguous(), gy[:h].contiguous(), y[:h].contiguous(), 3, 3, (1, 1),
+                                                      (1, 1), (0, 0), True))
+    _, dwb, dbb = K.qconv2d_wgrad(x[h:].contiguous(), gy[h:].contiguous(), y[h:].contiguous(), 3, 3, (1, 1), (1, 1), (0, 0), True)
+    # sums of up to 3.7 M exact products exceed 24 bits: the whole and the sum of the shards agree to fp32 rounding
+    err = float((dw - (dwa + dwb)).abs().max() / dw.abs().max())
+    assert err <= 2e-6, err
+    # one tap of the weight gradient against the definition in float64 (tap (1, 2))
+    ref_tap = torch.einsum('bijc,bijn->cn', x[:, 1:1 + OH, 2:2 + OH].double(), gm.double())
+    err = float((dw.view(3, 3, C, N)[1, 2].double() - ref_tap).abs().max() / ref_tap.abs().max())
+    assert err <= 2e-6, err
+    wt = w.flip(0, 1).permute(0, 1, 3, 2).reshape(9 * N, C).contiguous()
+    dxg = K.qconv2d_fwd(gm, wt, None, None, 3, 3, (H, H), (1, 1), (1, 1), (2, 2))
+    K.check_status(x.device)
+    iy = torch.randint(0, H, (n_s,), device='cuda', generator=gen)
+    ix = torch.randint(0, H, (n_s,), device='cuda', generator=gen)
+    gp = torch.nn.functional.pad(gm, (0, 0, 2, 2, 2, 2))                                         # zeros around the gradient
+    gpatch = gp[bi[:, None, None], iy[:, None, None] + 2 - dy, ix[:, None, None] + 2 - dx_]      # g[y - kh, x - kw]
+    refx = torch.einsum('skln,klcn->sc', gpatch.double(), w.double())
+    assert torch.equal(dxg[bi, iy, ix].double(), refx)
+    assert torch.equal(K.qconv2d_fwd(gm[h:].contiguous(), wt, None, None, 3, 3, (H, H), (1, 1), (1, 1), (2, 2)), dxg[h:])
+
+
+def test_attention_products_at_batch_8192():
+    """context = P V, dQ = dS K and dV = P^T dO at the transformer's full batch: sampled heads against float64, shards and
+    exact doubling."""
+    from hgq2_b200 import kernels as K
+
+    B, H, L, D = 8192, 4, 64, 16
+    gen = torch.Generator(device='cuda').manual_seed(3)
+    v = torch.randint(-512, 512, (B, L, H, D), device='cuda', generator=gen).float() / 64       # 10-bit projections
+    p = torch.randint(0, 256, (B, H, L, L), device='cuda', generator=gen).float() / 256         # 8-bit probabilities
+    g = torch.randn(B, H, L, L, device='cuda', generator=gen)
+    sb = torch.randint(0, B, (64,), device='cuda', generator=gen)
+    h = B // 2
+    ctx = K.attn_heads_matmul(1, p, v, B, L, H, D)                                               # [B, L, H, D]
+    K.check_status(v.device)
+    ref = torch.einsum('bhts,bshd->bthd', p[sb].double(), v[sb].double())
+    assert torch.equal(ctx[sb].double(), ref)  # 8-bit x 10-bit products, 64 terms: exact in fp32
+    assert torch.equal(K.attn_heads_matmul(1, p[h:], v[h:], h, L, H, D), ctx[h:])
+    assert torch.equal(K.attn_heads_matmul(1, p, v * 2, B, L, H, D), ctx * 2)
+    dq = K.attn_heads_matmul(1, g, v, B, L, H, D)                                                # fp32 left operand
+    ref = torch.einsum('bhts,bshd->bthd', g[sb].double(), v[sb].double())
+    err = float((dq[sb].double() - ref).abs().max() / ref.abs().max())
+    assert err <= 2e-5, err  # two bf16 terms of the gradient: 16 significant bits
+    assert torch.equal(K.attn_heads_matmul(1, g[h:], v[h:], h, L, H, D), dq[h:])
+    assert torch.equal(K.attn_heads_matmul(1, g * 2, v, B, L, H, D), dq * 2)
+    dv = K.attn_heads_matmul(2, g, v, B, L, H, D)                                                # G^T V: [B, L, H, D]
+    K.check_status(v.device)
+    ref = torch.einsum('bhts,bthd->bshd', g[sb].double(), v[sb].double())
+    err = float((dv[sb].double() - ref).abs().max() / ref.abs().max())
+    assert err <= 2e-5, err
+    assert torch.equal(K.attn_heads_matmul(2, g[h:], v[h:], h, L, H, D), dv[h:])
+    assert torch.equal(K.attn_heads_matmul(2, g * 2, v, B, L, H, D), dv * 2)
