@@ -264,7 +264,7 @@ def fused_conv2d_call(layer, xq, qkernel, qbias):
     if act_spec not in (None, 'relu'):
         return None
     if tuple(layer.strides) != (1, 1):
-        return None  # the input gradient is written as a stride-1 convolution over the output gradient
+        return strided_conv2d_call(layer, xq, qkernel, qbias, act_spec)
     B, H, W, C = xq.shape
     KH, KW, _, N = qkernel.shape
     (pt, _), (pl, _) = layer._pads(H, W)
@@ -274,6 +274,34 @@ def fused_conv2d_call(layer, xq, qkernel, qbias):
     if cp is None:
         return None
     return QConv2dFusedFn.apply(xq, qkernel, qbias, act_spec, tuple(layer.strides), dil, (pt, pl), (OH, OW), cp)
+
+
+def strided_conv2d_call(layer, xq, qkernel, qbias, act_spec):
+    """A strided convolution as a unit-stride one (space to depth), so that forward, input gradient and weight gradient all run
+    on the unit-stride implicit-GEMM kernels: the zero-padded image is regrouped into blocks of sh x sw pixels whose pixels
+    become channels, x'[b, i, j, (a, e, c)] = x[b, i sh + a, j sw + e, c], and the kernel likewise,
+    w'[p, q, (a, e, c), n] = w[p sh + a, q sw + e, c, n] (zero where p sh + a >= KH or q sw + e >= KW); then
+    y[b, oy, ox] = sum_{p, q} x'[b, oy + p, ox + q] . w'[p, q].  The regrouping is a copy made by torch (autograd maps the
+    gradients back through it); the contraction is QConv2dFusedFn.  None when the regrouped shape is not covered."""
+    sh, sw = (int(v) for v in layer.strides)
+    if tuple(layer.dilation_rate) != (1, 1):
+        return None
+    B, H, W, C = xq.shape
+    KH, KW, _, N = qkernel.shape
+    (pt, pb), (pl, pr) = layer._pads(H, W)
+    _, OH, OW, _ = layer.compute_output_shape(tuple(xq.shape))
+    KHs, KWs = -(-KH // sh), -(-KW // sw)
+    Hs, Ws = OH + KHs - 1, OW + KWs - 1          # blocks the outputs reach
+    Cs = sh * sw * C
+    cp = conv_padding_channels(B, Hs, Ws, Cs, KHs, KWs, N, OH, OW, (1, 1))
+    if cp is None:
+        return None
+    # image: pad (or crop rows / columns no output reads) to Hs sh x Ws sw, then blocks -> channels
+    x = torch.nn.functional.pad(xq, (0, 0, pl, Ws * sw - W - pl, pt, Hs * sh - H - pt))
+    x = x.reshape(B, Hs, sh, Ws, sw, C).permute(0, 1, 3, 2, 4, 5).reshape(B, Hs, Ws, Cs)
+    w = torch.nn.functional.pad(qkernel, (0, 0, 0, 0, 0, KWs * sw - KW, 0, KHs * sh - KH))
+    w = w.reshape(KHs, sh, KWs, sw, C, N).permute(0, 2, 1, 3, 4, 5).reshape(KHs, KWs, Cs, N)
+    return QConv2dFusedFn.apply(x, w, qbias, act_spec, (1, 1), (1, 1), (0, 0), (OH, OW), cp)
 
 
 class AttnScoresFn(torch.autograd.Function):

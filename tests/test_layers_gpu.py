@@ -240,3 +240,31 @@ def test_qconv1d_takes_the_fused_route():
     run_pair(layer, x, rng)
     assert _lib.lib().hgq_launch_count() - before >= 6
     assert not routes.fallbacks(), routes.fallbacks()
+
+
+@pytest.mark.parametrize('q_type,overflow_mode,round_mode', [('kbi', 'WRAP', 'RND'), ('kif', 'SAT', 'TRN')])
+@pytest.mark.parametrize('padding', ['valid', 'same'])
+@pytest.mark.parametrize('conv_params', [
+    # the parameter sets of the reference's own QConv2D test (tests/test_conv.py:66-73) on its 6 x 6 x 2 inputs and on larger ones
+    {'kernel_size': (1, 1), 'strides': (3, 5), 'parallelization_factor': -1},
+    {'kernel_size': (3, 3), 'strides': (1, 1), 'parallelization_factor': -1},
+    {'kernel_size': (3, 2), 'strides': (1, 3), 'parallelization_factor': 1},
+    {'kernel_size': (2, 3), 'strides': (4, 2), 'parallelization_factor': 1},
+])
+@pytest.mark.parametrize('in_shape', [(6, 6, 2), (17, 19, 4)])
+def test_qconv2d_strided_takes_the_fused_route(q_type, overflow_mode, round_mode, padding, conv_params, in_shape):
+    """Strided convolutions run on the unit-stride tensor-core kernels after a space-to-depth regrouping: no library
+    convolution, and the same parity bounds as everything else."""
+    from hgq2_b200 import routes
+    from hgq2_b200.layers import QConv2D
+
+    rng = np.random.default_rng(13)
+    sw, sa, sl = make_scopes(q_type, overflow_mode, round_mode, True)
+    with sw, sa, sl:
+        layer = QConv2D(4, padding=padding, activation='relu', **conv_params)
+    x = grid_input(rng, (32,) + in_shape)
+    layer(torch.from_numpy(x[:2]).cuda(), training=False)
+    perturb(layer, rng, True)
+    routes.reset()
+    run_pair(layer, x, rng)
+    assert not routes.fallbacks(), routes.fallbacks()
