@@ -263,6 +263,18 @@ def fused_conv2d_call(layer, xq, qkernel, qbias):
     act_spec = getattr(layer, '_activation_spec', None)
     if act_spec not in (None, 'relu'):
         return None
+    n_filters = qkernel.shape[-1]
+    if n_filters % 4 != 0:
+        # the kernels write output pixels as 16-byte pieces: filters of zeros make up the count and are cut off afterwards
+        extra = (-n_filters) % 4
+        qkernel = torch.nn.functional.pad(qkernel, (0, extra))
+        qbias = None if qbias is None else torch.nn.functional.pad(qbias, (0, extra))
+        y = _fused_conv2d(layer, xq, qkernel, qbias, act_spec)
+        return None if y is None else y[..., :n_filters]
+    return _fused_conv2d(layer, xq, qkernel, qbias, act_spec)
+
+
+def _fused_conv2d(layer, xq, qkernel, qbias, act_spec):
     if tuple(layer.strides) != (1, 1):
         return strided_conv2d_call(layer, xq, qkernel, qbias, act_spec)
     B, H, W, C = xq.shape

@@ -290,7 +290,7 @@ class OracleQConv2D(OracleQLayer):
         x = x.permute(0, 3, 1, 2)
         if pt or pb or pl or pr:
             x = F.pad(x, (pl, pr, pt, pb))
-        return F.conv2d(x, w.permute(3, 2, 0, 1), stride=self.strides, dilation=self.dilation).permute(0, 2, 3, 1)
+        return F.conv2d(x, w.permute(3, 2, 0, 1).contiguous(), stride=self.strides, dilation=self.dilation).permute(0, 2, 3, 1)
 
     def call(self, x, training):
         if self.iq is not None:
@@ -321,7 +321,7 @@ class OracleQConv1D(OracleQConv2D):
         x = x.permute(0, 2, 1)
         if pl or pr:
             x = F.pad(x, (pl, pr))
-        return F.conv1d(x, w.permute(2, 1, 0), stride=self.strides, dilation=self.dilation).permute(0, 2, 1)
+        return F.conv1d(x, w.permute(2, 1, 0).contiguous(), stride=self.strides, dilation=self.dilation).permute(0, 2, 1)
 
     def call(self, x, training):
         if self.iq is not None:

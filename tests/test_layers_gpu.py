@@ -137,7 +137,7 @@ def test_qeinsum_dense(q_type, overflow_mode, round_mode, equation, in_shape, ou
 
 @pytest.mark.parametrize('q_type,overflow_mode,round_mode', [('kbi', 'WRAP', 'RND'), ('kif', 'SAT', 'TRN'), ('kbi', 'SAT', 'RND')])
 @pytest.mark.parametrize('padding,strides', [('valid', 1), ('same', 1), ('valid', 2), ('same', 2)])
-@pytest.mark.parametrize('filters', [5, 8])  # 8: the implicit-GEMM tensor-core kernels at stride 1; 5: the library path
+@pytest.mark.parametrize('filters', [5, 8])  # 5: filters of zeros make up a multiple of four
 def test_qconv2d(q_type, overflow_mode, round_mode, padding, strides, filters):
     from hgq2_b200.layers import QConv2D
 
@@ -251,8 +251,8 @@ def test_qconv1d_takes_the_fused_route():
     {'kernel_size': (3, 2), 'strides': (1, 3), 'parallelization_factor': 1},
     {'kernel_size': (2, 3), 'strides': (4, 2), 'parallelization_factor': 1},
 ])
-@pytest.mark.parametrize('in_shape', [(6, 6, 2), (17, 19, 4)])
-def test_qconv2d_strided_takes_the_fused_route(q_type, overflow_mode, round_mode, padding, conv_params, in_shape):
+@pytest.mark.parametrize('in_shape,filters', [((6, 6, 2), 4), ((17, 19, 4), 4), ((6, 6, 2), 1), ((9, 10, 3), 5)])
+def test_qconv2d_strided_takes_the_fused_route(q_type, overflow_mode, round_mode, padding, conv_params, in_shape, filters):
     """Strided convolutions run on the unit-stride tensor-core kernels after a space-to-depth regrouping: no library
     convolution, and the same parity bounds as everything else."""
     from hgq2_b200 import routes
@@ -261,7 +261,7 @@ def test_qconv2d_strided_takes_the_fused_route(q_type, overflow_mode, round_mode
     rng = np.random.default_rng(13)
     sw, sa, sl = make_scopes(q_type, overflow_mode, round_mode, True)
     with sw, sa, sl:
-        layer = QConv2D(4, padding=padding, activation='relu', **conv_params)
+        layer = QConv2D(filters, padding=padding, activation='relu', **conv_params)
     x = grid_input(rng, (32,) + in_shape)
     layer(torch.from_numpy(x[:2]).cuda(), training=False)
     perturb(layer, rng, True)
