@@ -10,7 +10,8 @@
 // tracking needs (fixed_point_quantizer.py:405-413) is a side output, so the activations are read once and
 // the quantised activations never touch HBM.
 //
-// Shapes are skinny (K, N <= 256) so the kernel is HBM-bound: 4 (K + N) bytes per row.  A persistent CTA
+// Shapes are skinny (N <= 128; K as far as the three weight terms, 6 K N bytes, fit shared memory beside the tile buffers:
+// 256 inputs at 64 outputs, 1500 at 16) so the kernel is HBM-bound: 4 (K + N) bytes per row.  A persistent CTA
 // keeps the whole quantised weight matrix in shared memory as bf16 and streams 128-row tiles:
 //   all threads   load a 128 x 64 fp32 slab with 128-bit loads, quantise it in registers, split every value
 //                 exactly into up to three bf16 terms (3 x 8 significant bits = the 24 of fp32) and store
@@ -532,7 +533,7 @@ struct QdGeom {
     int64_t tiles;
 };
 
-static int qd_geom(int64_t M, int K, int N, int rows_period, bool want_amax, bool fastq, QdGeom &g, int kmax = 256) {
+static int qd_geom(int64_t M, int K, int N, int rows_period, bool want_amax, bool fastq, QdGeom &g, int kmax = 4096) {
     if (M <= 0 || K <= 0 || N <= 0 || rows_period <= 0) return HGQ_ERR_SIZE;
     if (K > kmax || N > 128) return HGQ_ERR_SIZE;
     if (want_amax && (int64_t)rows_period * K > kQdMaxTable) return HGQ_ERR_SIZE;

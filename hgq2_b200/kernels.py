@@ -295,8 +295,9 @@ def qdense_bwd_supported(M: int, K: int, N: int, rows_period: int) -> bool:
         return False
     if K <= _QB_KBLOCK:
         return lib().hgq_qdense_bwd_workspace(M, K, N, rows_period) > 0
-    # wider layers run as one launch per block of 64 input columns
-    return K % 4 == 0 and K <= 4 * _QB_KBLOCK and all(
+    # wider layers run as one launch per block of 64 input columns (each re-reads dY and y: meant for layers whose outputs are
+    # few, such as a classifier head behind a Flatten)
+    return K % 4 == 0 and K <= 64 * _QB_KBLOCK and all(
         lib().hgq_qdense_bwd_workspace(M, min(_QB_KBLOCK, K - k0), N, rows_period) > 0 for k0 in range(0, K, _QB_KBLOCK))
 
 

@@ -171,7 +171,8 @@ size_t hgq_qdense_fwd_workspace(int64_t M, int K, int N, int rows_period);
  *
  * The contraction runs on the tensor cores with every operand split exactly into bf16 terms and fp32
  * accumulation, so y equals the fp32 result whenever that is exact, and is within fp32 rounding otherwise.
- * Limits: K <= 256, N <= 128, rows_period * K <= 8192 when absmax is requested.
+ * Limits: N <= 128; K as far as the three bf16 weight terms (6 K Npad bytes) fit shared memory beside the tile buffers
+ * (256 at 64 outputs, about 1500 at 16; HGQ_ERR_SIZE beyond); rows_period * K <= 8192 when absmax is requested.
  */
 int hgq_qdense_fwd(const float *x, const uint8_t *qk, const float *qi, const float *qf, int rows_period,
                    int round_mode, int overflow_mode, unsigned flags, const float *wq, const float *bq,

@@ -71,6 +71,13 @@ def run_pair(layer, x_np, rng, check_eval=True):
     w = torch.from_numpy(rng.standard_normal(tuple(yc.shape)).astype(np.float32))
     loss = (y * w.cuda()).sum() / x.shape[0] + sum(layer.losses)
     lossc = (yc * w).sum() / x.shape[0] + sum(twin.losses)
+    # the bitwidth regularisers (MonoL1: l1 * sum of the variable) are part of the product layer's losses
+    for qname, tq in twin.quantizers().items():
+        pq = getattr(layer, qname).quantizer
+        for vname, leaf in tq.trainable_leaves().items():
+            reg = getattr(pq, '_' + vname).regularizer
+            if reg is not None:
+                lossc = lossc + reg.l1 * leaf.sum()
     # the loss is a sum of signed terms that largely cancel: its fp32 summation error is relative to sum |terms|
     rel_close(loss, lossc, 1e-5, 'loss', scale=float((yc.detach() * w).abs().sum() / x.shape[0] + abs(float(lossc.detach()))))
     # EBOPs: exact integer
@@ -263,6 +270,25 @@ def test_qconv2d_strided_takes_the_fused_route(q_type, overflow_mode, round_mode
     with sw, sa, sl:
         layer = QConv2D(filters, padding=padding, activation='relu', **conv_params)
     x = grid_input(rng, (32,) + in_shape)
+    layer(torch.from_numpy(x[:2]).cuda(), training=False)
+    perturb(layer, rng, True)
+    routes.reset()
+    run_pair(layer, x, rng)
+    assert not routes.fallbacks(), routes.fallbacks()
+
+
+@pytest.mark.parametrize('features,units', [(784, 10), (1152, 16), (320, 64)])
+def test_wide_qdense_takes_the_fused_route(features, units):
+    """A classifier head behind a Flatten (hundreds of inputs, few outputs): forward in one launch with the whole kernel in shared
+    memory, backward as one launch per block of 64 inputs; no library matmul."""
+    from hgq2_b200 import routes
+    from hgq2_b200.layers import QDense
+
+    rng = np.random.default_rng(21)
+    sw, sa, sl = make_scopes('kif', 'WRAP', 'RND', True)
+    with sw, sa, sl:
+        layer = QDense(units, activation='relu')
+    x = grid_input(rng, (256, features))
     layer(torch.from_numpy(x[:2]).cuda(), training=False)
     perturb(layer, rng, True)
     routes.reset()

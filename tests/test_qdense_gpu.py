@@ -29,6 +29,7 @@ def _ref(x, k, i, f, rm, om, training, w, b, act, rows_period):
 @pytest.mark.parametrize('M,K,N,rows_period', [
     (1000, 16, 64, 1), (128 * 37 + 5, 64, 64, 64), (4096, 64, 32, 1), (513, 32, 5, 1), (300, 27, 16, 1),
     (2048, 128, 64, 64), (640, 64, 128, 8), (129, 64, 10, 3), (7, 16, 64, 1), (50000, 64, 64, 1), (3000, 144, 32, 1),
+    (300, 1152, 12, 1), (500, 784, 32, 1),  # a classifier head behind a Flatten
 ])
 @pytest.mark.parametrize('rm,om,training', [('RND', 'WRAP', True), ('TRN', 'SAT', True), ('RND', 'WRAP', False)])
 def test_fused_dense_forward(M, K, N, rows_period, rm, om, training):
@@ -143,16 +144,19 @@ def test_fused_dense_no_input_quantizer_and_limits():
     kernels.check_status(y.device)
     yr = x.double() @ w.double()
     assert float((y.cpu().double() - yr).abs().max() / yr.abs().max()) <= 1e-6  # full-width operands: fp32 rounding of the sum
-    assert not kernels.qdense_supported(100, 300, 64, 1)
+    # limits: at most 128 outputs; inputs as far as the weight terms fit shared memory beside the tile buffers
+    assert kernels.qdense_supported(100, 300, 64, 1) and kernels.qdense_supported(100, 1152, 16, 1)
+    assert not kernels.qdense_supported(100, 600, 64, 1)
     assert not kernels.qdense_supported(100, 64, 200, 1)
     L = _lib.lib()
-    assert L.hgq_qdense_fwd(1, None, None, None, 1, 1, 1, 0, 1, None, 0, 1, None, 100, 300, 64, None, 0, None, None) == -2
+    assert L.hgq_qdense_fwd(1, None, None, None, 1, 1, 1, 0, 1, None, 0, 1, None, 100, 600, 64, None, 0, None, None) == -2
 
 
 @pytest.mark.parametrize('M,K,N,rows_period', [
     (1000, 16, 64, 1), (128 * 21 + 5, 64, 64, 64), (4096, 64, 32, 1), (513, 32, 5, 1), (300, 24, 16, 8), (640, 64, 128, 32),
     (129, 27, 10, 1), (7, 16, 64, 1), (60000, 64, 64, 64), (2000, 48, 40, 2), (3000, 128, 64, 64), (700, 96, 32, 1),
-    (128 * 50 + 9, 64, 128, 64),  # 128 outputs: two calls over column slices of dY and y
+    (128 * 50 + 9, 64, 128, 64),  # 128 outputs
+    (300, 1152, 12, 1), (500, 784, 32, 1),  # a classifier head behind a Flatten: 18 / 13 blocks of 64 inputs
 ])
 @pytest.mark.parametrize('rm,relu,quant', [('RND', True, True), ('TRN', False, True), ('RND_CONV', True, True), ('RND', True, False)])
 def test_fused_dense_backward(M, K, N, rows_period, rm, relu, quant):
