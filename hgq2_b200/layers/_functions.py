@@ -94,6 +94,25 @@ class QDenseFusedFn(torch.autograd.Function):
                 df = df.view(f.shape)
             di = torch.zeros_like(i) if (need_i and i is not None) else None
             return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None, None
+        if fused_bwd_enabled and need_w and kernels.qdense_bwd_supported(x.numel() // K, K, N, 1):
+            # an input quantizer that clips (SAT / SAT_SYM, or WRAP outside training): the quantised activations are formed by
+            # the quantizer kernel, the three products run on the fused backward kernel as for a layer without input
+            # quantizer, and the quantizer's surrogate backward turns dXq into dx and the bitwidth gradients
+            x2 = x.reshape(-1, K)
+            xq = kernels.quantize_fwd(x2, k, i, f, rm, om, training=training, zero_nonpos=zero)
+            want_dxq = bool(need_x or need_f or need_i)
+            dxq, dwq, dbq, _ = kernels.qdense_bwd(gy, y if activation == 'relu' else None, xq, None, 1, rm, wq, want_dx=want_dxq,
+                                                  want_db=has_bias and need_b, want_df=False, gy_repeat=gy_repeat)
+            dx = di = df = None
+            if want_dxq:
+                om_b = 'NONE' if (om == 'WRAP' and training) else om
+                dx, di, df = kernels.quantize_bwd(dxq, x2, k, i, f, rm, om_b, want_dx=need_x,
+                                                  want_di=bool(need_i) and om_b in ('SAT', 'SAT_SYM'))
+                if need_i and di is None and i is not None:
+                    di = torch.zeros_like(i)
+                if dx is not None:
+                    dx = dx.view(x.shape)
+            return dx, dwq, dbq, None, di, df, None, None, None, None, None, None, None, None
         routes.fallback('cuBLAS backward of a dense layer', f'M={x.numel() // K} K={K} N={N} period={rows_period} {rm}/{om}')
         if gy_repeat > 1:
             gy = gy.unsqueeze(1).expand(-1, gy_repeat, -1)

@@ -119,7 +119,11 @@ def test_qdense(q_type, overflow_mode, round_mode, parallel_io):
     x = grid_input(rng, (500, 12))
     layer(torch.from_numpy(x[:2]).cuda(), training=False)
     perturb(layer, rng, parallel_io)
+    from hgq2_b200 import routes
+
+    routes.reset()
     run_pair(layer, x, rng)
+    assert not routes.fallbacks(), routes.fallbacks()  # saturating input quantizers included: no library GEMM in the backward
 
 
 @pytest.mark.parametrize('q_type,overflow_mode,round_mode', [('kbi', 'WRAP', 'RND'), ('kif', 'SAT', 'TRN')])
