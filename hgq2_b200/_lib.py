@@ -127,6 +127,10 @@ SIGNATURES: dict[str, tuple] = {
     'hgq_peer_buffer_close': (c_int, [c_void_p]),
     'hgq_peer_buffer_destroy': (c_int, [c_void_p]),
     'hgq_adam_step_peers': (c_int, [c_void_p] * 7 + [c_int64] + [c_float] * 4 + [c_void_p, c_void_p, c_int, c_int, c_uint, c_void_p, c_void_p]),
+    'hgq_dense_chain_supported': (c_int, [c_int, c_void_p]),
+    'hgq_dense_chain_workspace': (c_size_t, [c_int64, c_int, c_void_p]),
+    'hgq_dense_chain_fwd': (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
+    'hgq_dense_chain_bwd': (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     'hgq_tables_forward': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
     'hgq_tables_track_bits': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
     'hgq_tables_backward': (c_int, [c_void_p, c_int, c_int64, c_void_p]),
@@ -149,6 +153,14 @@ class SlotDesc(ctypes.Structure):
                 ('absmax', c_void_p), ('decay', c_void_p), ('n', c_int64), ('kind', ctypes.c_int32), ('om', ctypes.c_int32),
                 ('rm', ctypes.c_int32), ('symmetric', ctypes.c_int32), ('tracked_weight', ctypes.c_int32), ('i_lo', c_float),
                 ('i_hi', c_float)]
+
+
+class ChainLayer(ctypes.Structure):
+    """hgq_chain_layer of include/hgq_b200.h."""
+
+    _fields_ = [('K', ctypes.c_int32), ('N', ctypes.c_int32), ('relu', ctypes.c_int32), ('round_mode', ctypes.c_int32),
+                ('qf', c_void_p), ('wq', c_void_p), ('bq', c_void_p), ('y', c_void_p), ('absmax', c_void_p), ('dwq', c_void_p),
+                ('dbq', c_void_p), ('df', c_void_p)]
 
 
 class WeightDesc(ctypes.Structure):

@@ -354,6 +354,49 @@ def qdense_bwd(gy, y, x, qf, rows_period: int, round_mode: str, wq, want_dx: boo
     return dx, dwq, dbq, df
 
 
+def dense_chain_layers(specs):
+    """A host array of hgq_chain_layer from dicts with the keys K, N, relu, round_mode and the tensors qf, wq, bq, y, absmax,
+    dwq, dbq, df (None where absent)."""
+    arr = (_lib.ChainLayer * len(specs))()
+    for a, s in zip(arr, specs):
+        a.K, a.N, a.relu, a.round_mode = int(s['K']), int(s['N']), int(bool(s['relu'])), ROUND_MODES[s['round_mode'].upper()]
+        for name in ('qf', 'wq', 'bq', 'y', 'absmax', 'dwq', 'dbq', 'df'):
+            t = s.get(name)
+            setattr(a, name, None if t is None else t.data_ptr())
+    return arr
+
+
+def dense_chain_supported(widths) -> bool:
+    """Whether a stack of dense layers with these widths (inputs of the first layer, then every layer's outputs) fits the
+    single-launch kernels."""
+    if len(widths) < 2 or len(widths) - 1 > 8:
+        return False
+    arr = (_lib.ChainLayer * (len(widths) - 1))()
+    for a, k, n in zip(arr, widths[:-1], widths[1:]):
+        a.K, a.N = int(k), int(n)
+    return bool(lib().hgq_dense_chain_supported(len(arr), arr))
+
+
+def dense_chain_fwd(x, layers, n_layers: int) -> None:
+    """Forward of the stack described by ``layers`` (see dense_chain_layers) on x [M, K0]: fills every layer's y."""
+    require_cuda(x)
+    M = x.shape[0]
+    with torch.cuda.device(x.device):
+        check(lib().hgq_dense_chain_fwd(ptr(x), M, n_layers, layers, stream_handle()), 'hgq_dense_chain_fwd')
+
+
+def dense_chain_bwd(gy, x, dx, layers, n_layers: int) -> None:
+    """Backward of the stack: fills dwq / dbq / df of every layer and dx (when not None)."""
+    require_cuda(gy, x, dx)
+    M = x.shape[0]
+    ws = workspace(lib().hgq_dense_chain_workspace(M, n_layers, layers), x.device, slot=6)
+    if ws is None:
+        raise _lib.HGQError(-2, 'hgq_dense_chain_bwd: unsupported stack')
+    with torch.cuda.device(x.device):
+        check(lib().hgq_dense_chain_bwd(ptr(gy), ptr(x), ptr(dx), M, n_layers, layers, ptr(ws), ws.numel(), stream_handle()),
+              'hgq_dense_chain_bwd')
+
+
 def qdense_bwd_accumulates(K: int, N: int, rows_period: int, relu: bool, has_quantizer: bool = True) -> bool:
     """Whether ``qdense_bwd(..., dx_into=...)`` is available for a layer of this shape."""
     return K <= _QB_KBLOCK and bool(lib().hgq_qdense_bwd_accumulate_supported(K, N, rows_period, int(relu), int(has_quantizer)))

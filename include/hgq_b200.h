@@ -499,6 +499,51 @@ int hgq_weights_forward(const hgq_weight_desc *weights, int n_weights, int64_t m
 int hgq_weights_backward(const hgq_weight_desc *weights, int n_weights, int64_t max_n, const hgq_slot_desc *slots,
                          void *stream);
 
+/* ---- a stack of small dense layers in one launch --------------------------------------------- */
+
+#define HGQ_CHAIN_MAX_LAYERS 8
+
+/*
+ * One layer of the stack: y = act(round_f(x) @ wq + bq) (QDense.call, src/hgq/layers/core/dense.py:60-68, with the
+ * training-mode WRAP input quantizer, which only rounds: fixed_point_quantizer.py:403-424).  1 <= K, N <= 64 and the K of a
+ * layer equals the N of the one before.  All pointers are device pointers.
+ */
+typedef struct {
+    int K, N;          /* inputs and outputs */
+    int relu;          /* 1: ReLU, 0: no activation */
+    int round_mode;    /* HGQ_ROUND_* of the input quantizer */
+    const float *qf;   /* [K] fractional bits of the input quantizer (integer-valued) */
+    const float *wq;   /* [K, N] quantised kernel */
+    const float *bq;   /* [N] quantised bias, or NULL */
+    float *y;          /* [M, N] the layer's output: written by the forward, read by the backward */
+    float *absmax;     /* forward: [K] abs-max of the rounded inputs, merged by atomic max into what is there
+                          (the caller clears it once per step), or NULL */
+    float *dwq;        /* backward outputs: [K, N] */
+    float *dbq;        /*                   [N] or NULL */
+    float *df;         /*                   [K] gradient of the fractional bits, or NULL */
+} hgq_chain_layer;
+
+/* 1 when the stack fits the kernels (layer count, widths, shared memory), else 0. */
+int hgq_dense_chain_supported(int n_layers, const hgq_chain_layer *layers);
+
+/* Scratch bytes hgq_dense_chain_bwd needs (0 when the stack is not supported). */
+size_t hgq_dense_chain_workspace(int64_t M, int n_layers, const hgq_chain_layer *layers);
+
+/*
+ * Forward of the whole stack on x [M, K of layer 0] in ONE launch: the activations of a 128-row tile stay in shared memory
+ * from layer to layer, every layer's output is also written to its `y`.  `layers` is a host array.  The arithmetic is fp32
+ * fused multiply-add on the CUDA cores (layers this small are bound by launch and dependency latencies, not by throughput).
+ */
+int hgq_dense_chain_fwd(const float *x, int64_t M, int n_layers, const hgq_chain_layer *layers, void *stream);
+
+/*
+ * Backward of the stack: gy [M, N of the last layer] is the gradient of its output; x and every layer's `y` are the
+ * forward's.  Writes dwq / dbq / df of every layer (the ReLU mask is y > 0) and, when dx != NULL, the gradient of x.
+ * Two launches: the stack, then a fixed-order reduction of the per-block partial sums (results do not depend on scheduling).
+ */
+int hgq_dense_chain_bwd(const float *gy, const float *x, float *dx, int64_t M, int n_layers, const hgq_chain_layer *layers,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- standalone quantizer on host buffers ------------------------------------------------- */
 
 /*
