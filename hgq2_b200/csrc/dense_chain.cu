@@ -22,24 +22,26 @@
 
 namespace hgq {
 
-constexpr int kMcThreads = 256;
+constexpr int kMcThreads = 512;
 constexpr int kMcRows = 128;      // rows of a tile
 constexpr int kMcWidth = 64;      // largest layer width
-constexpr int kMcLd = 68;         // row stride (floats) of an activation tile in shared memory: 16-byte aligned rows
+constexpr int kMcLd = 68;         // row stride (floats) of an activation tile in shared memory: 16-byte aligned rows, room for a
+                                  // 65th column (the ones that turn the bias gradient into a row of the weight gradient)
 constexpr int kMcMaxLayers = HGQ_CHAIN_MAX_LAYERS;
 
 struct McLayer {
     const float *qf, *wq, *bq;
     float *y, *absmax, *dwq, *dbq, *df;
     int K, N, relu, rm;
-    int part_off;  // offset (floats) of this layer's [dWq | dbq | df] record inside a block's partial record
+    int part_off;  // offset (floats) of this layer's [dWq (K x N) | dbq (N) | df (K)] record inside a block's partial record
+    int w_off;     // offset (floats) of this layer's weights inside the shared-memory weight area (forward: [K][Nw], backward: [N][Kw])
 };
 
 struct McParams {
     const float *x, *gy;
     float *dx, *part;
     int64_t M, tiles;
-    int n, part_stride;
+    int n, part_stride, w_total;
     McLayer L[kMcMaxLayers];
 };
 
@@ -50,7 +52,7 @@ __device__ __forceinline__ float mc_round(float v, float s, float inv, int rm) {
 }
 
 // Output tile of a product with `groups` groups of four output columns: thread t takes column group t % groups and the rows
-// slot, slot + slots, ... of the tile (slots = 256 / groups threads per column group, at most 8 rows each for groups <= 16).
+// (or inputs) slot, slot + slots, ... (slots = threads / groups per column group).
 struct McMap {
     int groups, slots, cg, slot;
     bool active;
@@ -64,102 +66,178 @@ __device__ __forceinline__ McMap mc_map(int width, int tid) {
     m.active = m.slot < m.slots;
     return m;
 }
+constexpr int kMcRowsPerThread = 4;  // 128 rows over at least 32 slots (at most 16 column groups)
+constexpr int kMcInputsPerThread = 3;  // 65 inputs over at least 32 slots
+
+// f(r, c) for every element of a [128, width] tile.  When the thread count is a multiple of the width a thread stays in one
+// column and walks rows a fixed step apart (no division per element: these loops, not the products, were most of the
+// instructions of a first version); otherwise elements are dealt out in order.
+template <class F>
+__device__ __forceinline__ void mc_foreach(int width, int tid, F f) {
+    if (kMcThreads % width == 0) {
+        const int c = tid % width, step = kMcThreads / width;
+#pragma unroll 4
+        for (int r = tid / width; r < kMcRows; r += step) f(r, c);
+    } else {
+        for (int e = tid; e < kMcRows * width; e += kMcThreads) {
+            const int r = e / width;
+            f(r, e - r * width);
+        }
+    }
+}
+
+// a tile of a row-major [M, width] matrix into shared memory (rows beyond the matrix read as zero)
+__device__ __forceinline__ void mc_load_tile(float *dst, const float *src, int64_t row0, int rows_here, int width, int tid) {
+    if ((width & 3) == 0 && aligned(src, 16)) {
+        const float4 *s4 = reinterpret_cast<const float4 *>(src + row0 * width);
+        const int w4 = width >> 2;
+        mc_foreach(w4, tid, [&](int r, int c) {
+            const float4 v = (r < rows_here) ? __ldcs(s4 + r * w4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(dst + r * kMcLd + c * 4) = v;
+        });
+    } else {
+        const float *s1 = src + row0 * width;
+        mc_foreach(width, tid, [&](int r, int c) { dst[r * kMcLd + c] = (r < rows_here) ? __ldcs(s1 + r * width + c) : 0.f; });
+    }
+}
+
+// zero where the layer's output was not positive (the ReLU mask of the gradient)
+__device__ __forceinline__ void mc_relu_mask(float *g, const float *y, int64_t row0, int rows_here, int width, int tid) {
+    if ((width & 3) == 0 && aligned(y, 16)) {
+        const float4 *y4 = reinterpret_cast<const float4 *>(y + row0 * width);
+        const int w4 = width >> 2;
+        mc_foreach(w4, tid, [&](int r, int c) {
+            if (r < rows_here) {
+                const float4 v = __ldcs(y4 + r * w4 + c);
+                float4 *gp = reinterpret_cast<float4 *>(g + r * kMcLd + c * 4);
+                float4 t = *gp;
+                t.x = v.x > 0.f ? t.x : 0.f; t.y = v.y > 0.f ? t.y : 0.f; t.z = v.z > 0.f ? t.z : 0.f; t.w = v.w > 0.f ? t.w : 0.f;
+                *gp = t;
+            }
+        });
+    } else {
+        const float *y1 = y + row0 * width;
+        mc_foreach(width, tid, [&](int r, int c) {
+            if (r < rows_here && !(__ldcs(y1 + r * width + c) > 0.f)) g[r * kMcLd + c] = 0.f;
+        });
+    }
+}
+
+// acc[j][0..3] = sum_i A[row_j][i] * B[i][4 cg .. 4 cg + 3] for the JN rows slot, slot + slots, ... of this thread: A is an
+// activation tile (row stride kMcLd), B a weight matrix with row stride ldb.  Rows beyond the tile are clamped (computed,
+// not stored by the callers), so the loop has no predicate; JN is the number of rows a thread really has (1, 2 or 4).
+template <int JN>
+__device__ __forceinline__ void mc_rows_product(const float *A, const float *B, int ldb, int depth, const McMap &m, float (&acc)[4][4]) {
+    const float *ap[JN];
+#pragma unroll
+    for (int j = 0; j < JN; ++j) ap[j] = A + min(m.slot + j * m.slots, kMcRows - 1) * kMcLd;
+    const float *bp = B + m.cg * 4;
+#pragma unroll 4
+    for (int i = 0; i < depth; ++i) {
+        const float4 b4 = *reinterpret_cast<const float4 *>(bp + i * ldb);
+#pragma unroll
+        for (int j = 0; j < JN; ++j) {
+            const float a = ap[j][i];
+            acc[j][0] = __fmaf_rn(a, b4.x, acc[j][0]);
+            acc[j][1] = __fmaf_rn(a, b4.y, acc[j][1]);
+            acc[j][2] = __fmaf_rn(a, b4.z, acc[j][2]);
+            acc[j][3] = __fmaf_rn(a, b4.w, acc[j][3]);
+        }
+    }
+}
+__device__ __forceinline__ void mc_rows_product_any(const float *A, const float *B, int ldb, int depth, const McMap &m, float (&acc)[4][4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+    const int jn = (kMcRows + m.slots - 1) / m.slots;  // 4 (16 column groups), 2 or 3 (5 .. 15), 1 (at most 4)
+    if (jn <= 1) mc_rows_product<1>(A, B, ldb, depth, m, acc);
+    else if (jn == 2) mc_rows_product<2>(A, B, ldb, depth, m, acc);
+    else mc_rows_product<4>(A, B, ldb, depth, m, acc);
+}
 
 // ---- forward --------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kMcThreads) k_dense_chain_fwd(const McParams P) {
     extern __shared__ __align__(16) float smem_f[];
     float *buf0 = smem_f;                                   // [128][68] activations entering the current layer
     float *buf1 = buf0 + kMcRows * kMcLd;                   // [128][68] activations leaving it
-    float *W = buf1 + kMcRows * kMcLd;                      // [K][Nw] weights, Nw = 4 * groups, zero beyond N
-    float *bias = W + kMcWidth * kMcWidth;                  // [64]
-    float *sc = bias + kMcWidth;                            // [64] 2^f
-    float *isc = sc + kMcWidth;                             // [64] 2^-f
-    unsigned *colmax = reinterpret_cast<unsigned *>(isc + kMcWidth);  // [64] bits of the column maxima of |xq|
+    float *bias = buf1 + kMcRows * kMcLd;                   // [layers][64]
+    float *sc = bias + kMcMaxLayers * kMcWidth;             // [layers][64] 2^f
+    float *isc = sc + kMcMaxLayers * kMcWidth;              // [layers][64] 2^-f
+    unsigned *colmax = reinterpret_cast<unsigned *>(isc + kMcMaxLayers * kMcWidth);  // [layers][64] bits of max |xq| per column
+    float *Wall = reinterpret_cast<float *>(colmax + kMcMaxLayers * kMcWidth);       // every layer's [K][Nw], zero beyond N
     const int tid = threadIdx.x;
+
+    // every layer's weights, bias and scales once per block
+    for (int l = 0; l < P.n; ++l) {
+        const McLayer &Ly = P.L[l];
+        const int K = Ly.K, N = Ly.N, Nw = ((N + 3) >> 2) * 4;
+        float *W = Wall + Ly.w_off;
+        for (int e = tid; e < K * Nw; e += kMcThreads) {
+            const int k = e / Nw, n = e - k * Nw;
+            W[e] = (n < N) ? __ldg(Ly.wq + k * N + n) : 0.f;
+        }
+        if (tid < kMcWidth) {
+            bias[l * kMcWidth + tid] = (Ly.bq != nullptr && tid < N) ? __ldg(Ly.bq + tid) : 0.f;
+            const int fi = (tid < K) ? __float2int_rn(__ldg(Ly.qf + tid)) : 0;
+            sc[l * kMcWidth + tid] = pow2i(fi);
+            isc[l * kMcWidth + tid] = pow2i(-fi);
+            colmax[l * kMcWidth + tid] = 0u;
+        }
+    }
+    __syncthreads();
 
     for (int64_t tile = blockIdx.x; tile < P.tiles; tile += gridDim.x) {
         const int64_t row0 = tile * kMcRows;
         const int rows_here = (int)((P.M - row0) < kMcRows ? (P.M - row0) : kMcRows);
         float *in = buf0, *out = buf1;
-        {   // the tile of the first layer's input
-            const int K0 = P.L[0].K;
-            for (int e = tid; e < kMcRows * K0; e += kMcThreads) {
-                const int r = e / K0, k = e - r * K0;
-                in[r * kMcLd + k] = (r < rows_here) ? __ldcs(P.x + (row0 + r) * K0 + k) : 0.f;
-            }
-        }
+        mc_load_tile(in, P.x, row0, rows_here, P.L[0].K, tid);
+        __syncthreads();
         for (int l = 0; l < P.n; ++l) {
             const McLayer &Ly = P.L[l];
             const int K = Ly.K, N = Ly.N;
             const McMap m = mc_map(N, tid);
             const int Nw = m.groups * 4;
-            for (int e = tid; e < K * Nw; e += kMcThreads) {
-                const int k = e / Nw, n = e - k * Nw;
-                W[e] = (n < N) ? __ldg(Ly.wq + k * N + n) : 0.f;
-            }
-            if (tid < kMcWidth) {
-                bias[tid] = (Ly.bq != nullptr && tid < N) ? __ldg(Ly.bq + tid) : 0.f;
-                const int fi = (tid < K) ? __float2int_rn(__ldg(Ly.qf + tid)) : 0;
-                sc[tid] = pow2i(fi);
-                isc[tid] = pow2i(-fi);
-                colmax[tid] = 0u;
-            }
-            __syncthreads();
+            const float *W = Wall + Ly.w_off;
+            const float *sc_l = sc + l * kMcWidth, *isc_l = isc + l * kMcWidth;
             // input quantizer in place, column maxima of the rounded values over the rows that exist
             if (kMcThreads % K == 0) {  // a thread stays in one column
                 const int k = tid % K;
-                const float s = sc[k], inv = isc[k];
+                const float s = sc_l[k], inv = isc_l[k];
                 float mx = 0.f;
+#pragma unroll 4
                 for (int r = tid / K; r < kMcRows; r += kMcThreads / K) {
                     const float q = mc_round(in[r * kMcLd + k], s, inv, Ly.rm);
                     in[r * kMcLd + k] = q;
                     if (r < rows_here) mx = fmaxf(mx, fabsf(q));
                 }
-                if (Ly.absmax != nullptr) atomicMax(colmax + k, __float_as_uint(mx));
+                if (Ly.absmax != nullptr) atomicMax(colmax + l * kMcWidth + k, __float_as_uint(mx));
             } else {
                 for (int e = tid; e < kMcRows * K; e += kMcThreads) {
                     const int r = e / K, k = e - r * K;
-                    const float q = mc_round(in[r * kMcLd + k], sc[k], isc[k], Ly.rm);
+                    const float q = mc_round(in[r * kMcLd + k], sc_l[k], isc_l[k], Ly.rm);
                     in[r * kMcLd + k] = q;
-                    if (Ly.absmax != nullptr && r < rows_here) atomicMax(colmax + k, __float_as_uint(fabsf(q)));
+                    if (Ly.absmax != nullptr && r < rows_here) atomicMax(colmax + l * kMcWidth + k, __float_as_uint(fabsf(q)));
                 }
             }
             __syncthreads();
-            if (Ly.absmax != nullptr && tid < K) atomicMax(reinterpret_cast<unsigned *>(Ly.absmax) + tid, colmax[tid]);
             // y = act(xq @ W + b): rows slot + j * slots of column group cg
-            if (m.active) {
-                float acc[8][4];
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
-                const float *arow = in + m.slot * kMcLd;
-                const int rstep = m.slots * kMcLd;
-                for (int k = 0; k < K; ++k) {
-                    const float4 w4 = *reinterpret_cast<const float4 *>(W + k * Nw + m.cg * 4);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (m.slot + j * m.slots < kMcRows) {
-                            const float a = arow[j * rstep + k];
-                            acc[j][0] = __fmaf_rn(a, w4.x, acc[j][0]);
-                            acc[j][1] = __fmaf_rn(a, w4.y, acc[j][1]);
-                            acc[j][2] = __fmaf_rn(a, w4.z, acc[j][2]);
-                            acc[j][3] = __fmaf_rn(a, w4.w, acc[j][3]);
-                        }
-                    }
-                }
+            if (m.active && m.slot < kMcRows) {
+                float acc[kMcRowsPerThread][4];
+                mc_rows_product_any(in, Wall + Ly.w_off, Nw, K, m, acc);
                 const float lo = Ly.relu ? 0.f : -INFINITY;
                 const int n0 = m.cg * 4;
+                const float4 b4 = *reinterpret_cast<const float4 *>(bias + l * kMcWidth + n0);
                 const bool vec = (N % 4 == 0) && aligned(Ly.y, 16);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < kMcRowsPerThread; ++j) {
                     const int r = m.slot + j * m.slots;
                     if (r < kMcRows) {
                         float4 o;
-                        o.x = fmaxf(__fadd_rn(acc[j][0], bias[n0]), lo);
-                        o.y = fmaxf(__fadd_rn(acc[j][1], bias[n0 + 1]), lo);
-                        o.z = fmaxf(__fadd_rn(acc[j][2], bias[n0 + 2]), lo);
-                        o.w = fmaxf(__fadd_rn(acc[j][3], bias[n0 + 3]), lo);
+                        o.x = fmaxf(__fadd_rn(acc[j][0], b4.x), lo);
+                        o.y = fmaxf(__fadd_rn(acc[j][1], b4.y), lo);
+                        o.z = fmaxf(__fadd_rn(acc[j][2], b4.z), lo);
+                        o.w = fmaxf(__fadd_rn(acc[j][3], b4.w), lo);
                         *reinterpret_cast<float4 *>(out + r * kMcLd + n0) = o;
                         if (r < rows_here) {
                             float *dst = Ly.y + (row0 + r) * N + n0;
@@ -179,6 +257,11 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_fwd(const McParams P
             float *t = in; in = out; out = t;
         }
     }
+    // the block's column maxima into the callers' statistics
+    for (int e = tid; e < P.n * kMcWidth; e += kMcThreads) {
+        const int l = e / kMcWidth, k = e - l * kMcWidth;
+        if (k < P.L[l].K && P.L[l].absmax != nullptr) atomicMax(reinterpret_cast<unsigned *>(P.L[l].absmax) + k, colmax[e]);
+    }
 }
 
 // ---- backward -------------------------------------------------------------------------------------------------------------
@@ -186,28 +269,37 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
     extern __shared__ __align__(16) float smem_f[];
     float *G = smem_f;                                      // [128][68] gradient entering the current layer (its output side)
     float *D = G + kMcRows * kMcLd;                         // [128][68] gradient leaving it (dXq)
-    float *XQ = D + kMcRows * kMcLd;                        // [128][68] rounded inputs
-    float *ER = XQ + kMcRows * kMcLd;                       // [128][68] -ln2 (xq - x)
-    float *WT = ER + kMcRows * kMcLd;                       // [N][Kw] transposed weights, Kw = 4 * groups of K
-    float *red = WT + kMcWidth * kMcWidth;                  // [256][4] per-thread df partials
-    float *sc = red + kMcThreads * 4;                       // [64], [64]
-    float *isc = sc + kMcWidth;
-    float *acc_s = isc + kMcWidth;                          // per layer [dWq (K x N) | dbq (N) | df (K)] sums over this block's tiles
+    float *XQ = D + kMcRows * kMcLd;                        // [128][68] rounded inputs, a column of ones behind them
+    float *XR = XQ + kMcRows * kMcLd;                       // [128][68] inputs as stored
+    float *red = XR + kMcRows * kMcLd;                      // [512] partial df sums
+    float *scratch = red + kMcThreads;                      // [512][4] partial weight-gradient sums of the row splits
+    float *sc = scratch + kMcThreads * 4;                   // [layers][64], [layers][64]
+    float *isc = sc + kMcMaxLayers * kMcWidth;
+    float *acc_s = isc + kMcMaxLayers * kMcWidth;           // per layer [dWq | dbq | df] sums over this block's tiles
+    float *WTall = acc_s + ((P.part_stride + 3) & ~3);      // every layer's transposed weights [N][Kw], zero beyond K
     const int tid = threadIdx.x;
 
     for (int e = tid; e < P.part_stride; e += kMcThreads) acc_s[e] = 0.f;
+    for (int l = 0; l < P.n; ++l) {
+        const McLayer &Ly = P.L[l];
+        const int K = Ly.K, N = Ly.N, Kw = ((K + 3) >> 2) * 4;
+        float *WT = WTall + Ly.w_off;
+        for (int e = tid; e < Kw * N; e += kMcThreads) {  // coalesced over n in memory, transposed into shared memory
+            const int k = e / N, n = e - k * N;
+            WT[n * Kw + k] = (k < K) ? __ldg(Ly.wq + k * N + n) : 0.f;
+        }
+        if (tid < kMcWidth) {
+            const int fi = (tid < K) ? __float2int_rn(__ldg(Ly.qf + tid)) : 0;
+            sc[l * kMcWidth + tid] = pow2i(fi);
+            isc[l * kMcWidth + tid] = pow2i(-fi);
+        }
+    }
     __syncthreads();
 
     for (int64_t tile = blockIdx.x; tile < P.tiles; tile += gridDim.x) {
         const int64_t row0 = tile * kMcRows;
         const int rows_here = (int)((P.M - row0) < kMcRows ? (P.M - row0) : kMcRows);
-        {
-            const int NL = P.L[P.n - 1].N;
-            for (int e = tid; e < kMcRows * NL; e += kMcThreads) {
-                const int r = e / NL, n = e - r * NL;
-                G[r * kMcLd + n] = (r < rows_here) ? __ldcs(P.gy + (row0 + r) * NL + n) : 0.f;
-            }
-        }
+        mc_load_tile(G, P.gy, row0, rows_here, P.L[P.n - 1].N, tid);
         float *g_in = G, *g_out = D;
         for (int l = P.n - 1; l >= 0; --l) {
             const McLayer &Ly = P.L[l];
@@ -215,74 +307,31 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
             const McMap mk = mc_map(K, tid);    // dXq tile: column groups over k
             const McMap mn = mc_map(N, tid);    // dWq tile: column groups over n
             const int Kw = mk.groups * 4, Nw = mn.groups * 4;
+            const float *WT = WTall + Ly.w_off;
+            const float *sc_l = sc + l * kMcWidth, *isc_l = isc + l * kMcWidth;
             float *a_l = acc_s + Ly.part_off;
-            __syncthreads();  // the previous layer's readers of WT / XQ / ER / red are done
-            if (tid < kMcWidth) {
-                const int fi = (tid < K) ? __float2int_rn(__ldg(Ly.qf + tid)) : 0;
-                sc[tid] = pow2i(fi);
-                isc[tid] = pow2i(-fi);
-            }
-            for (int e = tid; e < N * Kw; e += kMcThreads) {  // coalesced over n in memory, transposed into shared memory
-                const int k = e / N, n = e - k * N;
-                if (k < Kw) WT[n * Kw + k] = (k < K) ? __ldg(Ly.wq + k * N + n) : 0.f;
-            }
-            if (Ly.relu) {
-                for (int e = tid; e < kMcRows * N; e += kMcThreads) {
-                    const int r = e / N, n = e - r * N;
-                    if (r < rows_here && !(__ldcs(Ly.y + (row0 + r) * N + n) > 0.f)) g_in[r * kMcLd + n] = 0.f;
-                }
-            }
-            // zero the padding columns the float4 reads of the dWq product touch
-            if (Nw != N)
+            __syncthreads();  // the tile's gradient is in place; the previous layer's readers of XQ / XR / red are done
+            // this layer's inputs (as stored, rounded, and a column of ones), the ReLU mask on the gradient
+            mc_load_tile(XR, (l == 0) ? P.x : P.L[l - 1].y, row0, rows_here, K, tid);
+            if (Ly.relu) mc_relu_mask(g_in, Ly.y, row0, rows_here, N, tid);
+            if (Nw != N)  // the padding columns the float4 reads of the dWq product touch
                 for (int e = tid; e < kMcRows * (Nw - N); e += kMcThreads) {
                     const int r = e / (Nw - N), n = N + (e - r * (Nw - N));
                     g_in[r * kMcLd + n] = 0.f;
                 }
-            __syncthreads();  // sc / isc
-            {
-                const float *xl = (l == 0) ? P.x : P.L[l - 1].y;
-                for (int e = tid; e < kMcRows * K; e += kMcThreads) {
-                    const int r = e / K, k = e - r * K;
-                    const float v = (r < rows_here) ? __ldcs(xl + (row0 + r) * K + k) : 0.f;
-                    const float q = mc_round(v, sc[k], isc[k], Ly.rm);
-                    XQ[r * kMcLd + k] = q;
-                    ER[r * kMcLd + k] = __fmul_rn(__fsub_rn(q, v), -kLn2);
-                }
-            }
             __syncthreads();
-            // ---- dXq = G @ W^T, and the df terms of this thread's elements -------------------------------------------------
-            float dfp[4] = {0.f, 0.f, 0.f, 0.f};
-            if (mk.active) {
-                float acc[8][4];
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
-                const float *grow = g_in + mk.slot * kMcLd;
-                const int rstep = mk.slots * kMcLd;
-                for (int n = 0; n < N; ++n) {
-                    const float4 w4 = *reinterpret_cast<const float4 *>(WT + n * Kw + mk.cg * 4);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (mk.slot + j * mk.slots < kMcRows) {
-                            const float g = grow[j * rstep + n];
-                            acc[j][0] = __fmaf_rn(g, w4.x, acc[j][0]);
-                            acc[j][1] = __fmaf_rn(g, w4.y, acc[j][1]);
-                            acc[j][2] = __fmaf_rn(g, w4.z, acc[j][2]);
-                            acc[j][3] = __fmaf_rn(g, w4.w, acc[j][3]);
-                        }
-                    }
-                }
+            mc_foreach(K, tid, [&](int r, int k) { XQ[r * kMcLd + k] = mc_round(XR[r * kMcLd + k], sc_l[k], isc_l[k], Ly.rm); });
+            if (tid < kMcRows) XQ[tid * kMcLd + K] = 1.f;
+            __syncthreads();
+            // ---- dXq = G @ W^T ------------------------------------------------------------------------------------------------
+            if (mk.active && mk.slot < kMcRows) {
+                float acc[kMcRowsPerThread][4];
+                mc_rows_product_any(g_in, WT, Kw, N, mk, acc);
                 const int k0 = mk.cg * 4;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < kMcRowsPerThread; ++j) {
                     const int r = mk.slot + j * mk.slots;
                     if (r < kMcRows) {
-                        const float4 er = *reinterpret_cast<const float4 *>(ER + r * kMcLd + k0);
-                        dfp[0] = __fmaf_rn(er.x, acc[j][0], dfp[0]);
-                        dfp[1] = __fmaf_rn(er.y, acc[j][1], dfp[1]);
-                        dfp[2] = __fmaf_rn(er.z, acc[j][2], dfp[2]);
-                        dfp[3] = __fmaf_rn(er.w, acc[j][3], dfp[3]);
                         *reinterpret_cast<float4 *>(g_out + r * kMcLd + k0) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
                         if (l == 0 && P.dx != nullptr && r < rows_here) {
 #pragma unroll
@@ -292,33 +341,56 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
                     }
                 }
             }
-            *reinterpret_cast<float4 *>(red + tid * 4) = make_float4(dfp[0], dfp[1], dfp[2], dfp[3]);
-            // ---- dWq += xq^T @ G: thread t takes column group t % groups(N) and the inputs slot, slot + slots, ... ------------
-            if (mn.active) {
-                float acc[4][4];
+            // ---- [dWq; dbq] += [xq 1]^T @ G (the column of ones behind xq makes row K the bias gradient) -------------------------
+            // A unit is (input k, group of four outputs): its four sums run over the 128 rows.  Layers with fewer units than
+            // threads split the rows among `splits` threads per unit (combined below in a fixed order); wider layers give a
+            // thread up to three inputs of one column group.
+            const int units = (K + 1) * mn.groups;
+            const int splits = units < kMcThreads ? kMcThreads / units : 1;
+            const int rps = (kMcRows + splits - 1) / splits;  // rows per split
+            if (units < kMcThreads) {
+                if (tid < units * splits) {
+                    const int unit = tid % units, sp = tid / units;
+                    const int k = unit / mn.groups, cg = unit - k * mn.groups;
+                    const int r0 = sp * rps, r1 = min(kMcRows, r0 + rps);
+                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                    const float *xp = XQ + k, *gq = g_in + cg * 4;
+#pragma unroll 4
+                    for (int r = r0; r < r1; ++r) {
+                        const float4 g4 = *reinterpret_cast<const float4 *>(gq + r * kMcLd);
+                        const float xv = xp[r * kMcLd];
+                        a0 = __fmaf_rn(xv, g4.x, a0); a1 = __fmaf_rn(xv, g4.y, a1);
+                        a2 = __fmaf_rn(xv, g4.z, a2); a3 = __fmaf_rn(xv, g4.w, a3);
+                    }
+                    *reinterpret_cast<float4 *>(scratch + tid * 4) = make_float4(a0, a1, a2, a3);
+                }
+            } else if (mn.active) {
+                float acc[kMcInputsPerThread][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < kMcInputsPerThread; ++j)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
-                const int kpt = (K + mn.slots - 1) / mn.slots;  // inputs per thread: at most 4 (64 inputs, 16 slots)
-                for (int r = 0; r < kMcRows; ++r) {
-                    const float4 g4 = *reinterpret_cast<const float4 *>(g_in + r * kMcLd + mn.cg * 4);
+                // inputs beyond the layer's are clamped to the column of ones (computed, not stored)
+                const float *xp[kMcInputsPerThread];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int k = mn.slot + j * mn.slots;
-                        if (j < kpt && k < K) {
-                            const float xv = XQ[r * kMcLd + k];
-                            acc[j][0] = __fmaf_rn(xv, g4.x, acc[j][0]);
-                            acc[j][1] = __fmaf_rn(xv, g4.y, acc[j][1]);
-                            acc[j][2] = __fmaf_rn(xv, g4.z, acc[j][2]);
-                            acc[j][3] = __fmaf_rn(xv, g4.w, acc[j][3]);
-                        }
+                for (int j = 0; j < kMcInputsPerThread; ++j) xp[j] = XQ + min(mn.slot + j * mn.slots, K);
+                const float *gq = g_in + mn.cg * 4;
+#pragma unroll 4
+                for (int r = 0; r < kMcRows; ++r) {
+                    const float4 g4 = *reinterpret_cast<const float4 *>(gq + r * kMcLd);
+#pragma unroll
+                    for (int j = 0; j < kMcInputsPerThread; ++j) {
+                        const float xv = xp[j][r * kMcLd];
+                        acc[j][0] = __fmaf_rn(xv, g4.x, acc[j][0]);
+                        acc[j][1] = __fmaf_rn(xv, g4.y, acc[j][1]);
+                        acc[j][2] = __fmaf_rn(xv, g4.z, acc[j][2]);
+                        acc[j][3] = __fmaf_rn(xv, g4.w, acc[j][3]);
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < kMcInputsPerThread; ++j) {
                     const int k = mn.slot + j * mn.slots;
-                    if (j < kpt && k < K) {
+                    if (k <= K) {  // row K of the record is dbq
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             const int n = mn.cg * 4 + c;
@@ -327,18 +399,37 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
                     }
                 }
             }
-            // dbq += column sums of G (fixed order over the rows)
-            if (tid < N) {
+            __syncthreads();  // dXq complete
+            // ---- df[k] += sum_r -ln2 (xq - x) dXq: thread t takes column t % K and the rows t / K, t / K + subsets, ... --------
+            const int subsets = kMcThreads / K;
+            if (tid < subsets * K) {
+                const int k = tid % K;
                 float s = 0.f;
-                for (int r = 0; r < kMcRows; ++r) s = __fadd_rn(s, g_in[r * kMcLd + tid]);
-                a_l[K * N + tid] = __fadd_rn(a_l[K * N + tid], s);
+                for (int r = tid / K; r < kMcRows; r += subsets) {
+                    const float er = __fmul_rn(__fsub_rn(XQ[r * kMcLd + k], XR[r * kMcLd + k]), -kLn2);
+                    s = __fmaf_rn(er, g_out[r * kMcLd + k], s);
+                }
+                red[tid] = s;
             }
-            __syncthreads();  // red complete
-            if (tid < K) {   // df[k]: the partials of the threads that hold column k, in slot order
-                const int cg = tid >> 2, c = tid & 3;
+            __syncthreads();
+            if (tid < K) {
                 float s = 0.f;
-                for (int slot = 0; slot < mk.slots; ++slot) s = __fadd_rn(s, red[(slot * mk.groups + cg) * 4 + c]);
+                for (int sub = 0; sub < subsets; ++sub) s = __fadd_rn(s, red[sub * K + tid]);
                 a_l[K * N + N + tid] = __fadd_rn(a_l[K * N + N + tid], s);
+            }
+            if (units < kMcThreads && tid < units) {  // the row splits of this unit, in order
+                const int k = tid / mn.groups, cg = tid - k * mn.groups;
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp = 0; sp < splits; ++sp) {
+                    const float4 v = *reinterpret_cast<const float4 *>(scratch + (sp * units + tid) * 4);
+                    t.x = __fadd_rn(t.x, v.x); t.y = __fadd_rn(t.y, v.y); t.z = __fadd_rn(t.z, v.z); t.w = __fadd_rn(t.w, v.w);
+                }
+                const float tv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int n = cg * 4 + c;
+                    if (n < N) a_l[k * N + n] = __fadd_rn(a_l[k * N + n], tv[c]);
+                }
             }
             float *t = g_in; g_in = g_out; g_out = t;
         }
@@ -380,30 +471,47 @@ __global__ void __launch_bounds__(kThreads) k_dense_chain_stage2(const McParams 
     }
 }
 
-static size_t mc_fwd_smem() { return (size_t)(2 * kMcRows * kMcLd + kMcWidth * kMcWidth + 4 * kMcWidth) * sizeof(float); }
-static size_t mc_bwd_smem(int part_stride) {
-    return (size_t)(4 * kMcRows * kMcLd + kMcWidth * kMcWidth + kMcThreads * 4 + 2 * kMcWidth + part_stride) * sizeof(float);
+static size_t mc_fwd_smem(int w_total) {
+    return (size_t)(2 * kMcRows * kMcLd + 4 * kMcMaxLayers * kMcWidth + w_total) * sizeof(float);
+}
+static size_t mc_bwd_smem(int part_stride, int w_total) {
+    return (size_t)(4 * kMcRows * kMcLd + 5 * kMcThreads + 2 * kMcMaxLayers * kMcWidth + ((part_stride + 3) & ~3) + w_total) * sizeof(float);
 }
 
-static int mc_fill(int n_layers, const hgq_chain_layer *layers, bool backward, McParams &p) {
+// widths, record offsets and the shared-memory weight area of a stack; HGQ_OK when both kernels fit
+static int mc_plan(int n_layers, const hgq_chain_layer *layers, bool backward, McParams &p) {
     if (layers == nullptr) return HGQ_ERR_NULL;
     if (n_layers < 1 || n_layers > kMcMaxLayers) return HGQ_ERR_SIZE;
-    int off = 0;
+    int off = 0, wf = 0, wb = 0;
     for (int l = 0; l < n_layers; ++l) {
         const hgq_chain_layer &s = layers[l];
         if (s.K < 1 || s.K > kMcWidth || s.N < 1 || s.N > kMcWidth) return HGQ_ERR_SIZE;
         if (l > 0 && s.K != layers[l - 1].N) return HGQ_ERR_SIZE;
+        McLayer &d = p.L[l];
+        d.K = s.K; d.N = s.N; d.part_off = off;
+        d.w_off = backward ? wb : wf;
+        off += s.K * s.N + s.N + s.K;
+        wf += s.K * ((s.N + 3) / 4 * 4);
+        wb += s.N * ((s.K + 3) / 4 * 4);
+    }
+    p.n = n_layers;
+    p.part_stride = off;
+    p.w_total = backward ? wb : wf;
+    if (mc_fwd_smem(wf) > 226 * 1024 || mc_bwd_smem(off, wb) > 226 * 1024) return HGQ_ERR_SIZE;
+    return HGQ_OK;
+}
+
+static int mc_fill(int n_layers, const hgq_chain_layer *layers, bool backward, McParams &p) {
+    if (int e = mc_plan(n_layers, layers, backward, p)) return e;
+    for (int l = 0; l < n_layers; ++l) {
+        const hgq_chain_layer &s = layers[l];
         if (s.round_mode < 0 || s.round_mode > 2) return HGQ_ERR_MODE;
         if (s.qf == nullptr || s.wq == nullptr || s.y == nullptr) return HGQ_ERR_NULL;
         if (backward && s.dwq == nullptr) return HGQ_ERR_NULL;
         McLayer &d = p.L[l];
         d.qf = s.qf; d.wq = s.wq; d.bq = s.bq; d.y = s.y; d.absmax = s.absmax; d.dwq = s.dwq; d.dbq = s.dbq; d.df = s.df;
-        d.K = s.K; d.N = s.N; d.relu = s.relu ? 1 : 0; d.rm = s.round_mode; d.part_off = off;
-        off += s.K * s.N + s.N + s.K;
+        d.relu = s.relu ? 1 : 0; d.rm = s.round_mode;
     }
-    p.n = n_layers;
-    p.part_stride = off;
-    if (mc_bwd_smem(off) > 226 * 1024) return HGQ_ERR_SIZE;
     return HGQ_OK;
 }
 
@@ -414,14 +522,8 @@ static int mc_grid(int64_t tiles) { return (int)(tiles < num_sms() ? tiles : num
 using namespace hgq;
 
 extern "C" int hgq_dense_chain_supported(int n_layers, const hgq_chain_layer *layers) {
-    if (layers == nullptr || n_layers < 1 || n_layers > kMcMaxLayers) return 0;
-    int off = 0;
-    for (int l = 0; l < n_layers; ++l) {
-        if (layers[l].K < 1 || layers[l].K > kMcWidth || layers[l].N < 1 || layers[l].N > kMcWidth) return 0;
-        if (l > 0 && layers[l].K != layers[l - 1].N) return 0;
-        off += layers[l].K * layers[l].N + layers[l].N + layers[l].K;
-    }
-    return mc_bwd_smem(off) <= 226 * 1024 ? 1 : 0;
+    McParams p;
+    return mc_plan(n_layers, layers, true, p) == HGQ_OK ? 1 : 0;
 }
 
 extern "C" size_t hgq_dense_chain_workspace(int64_t M, int n_layers, const hgq_chain_layer *layers) {
@@ -437,7 +539,7 @@ extern "C" int hgq_dense_chain_fwd(const float *x, int64_t M, int n_layers, cons
     McParams p;
     if (int e = mc_fill(n_layers, layers, false, p)) return e;
     p.x = x; p.gy = nullptr; p.dx = nullptr; p.part = nullptr; p.M = M; p.tiles = (M + kMcRows - 1) / kMcRows;
-    const size_t smem = mc_fwd_smem();
+    const size_t smem = mc_fwd_smem(p.w_total);
     cudaError_t ce = cudaFuncSetAttribute(k_dense_chain_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
     k_dense_chain_fwd<<<mc_grid(p.tiles), kMcThreads, smem, (cudaStream_t)stream>>>(p);
@@ -455,7 +557,7 @@ extern "C" int hgq_dense_chain_bwd(const float *gy, const float *x, float *dx, i
     if (workspace == nullptr || workspace_bytes < (size_t)grid * p.part_stride * sizeof(float)) return HGQ_ERR_WORKSPACE;
     if (!aligned(workspace, 16)) return HGQ_ERR_ALIGN;
     p.part = (float *)workspace;
-    const size_t smem = mc_bwd_smem(p.part_stride);
+    const size_t smem = mc_bwd_smem(p.part_stride, p.w_total);
     cudaError_t ce = cudaFuncSetAttribute(k_dense_chain_bwd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
     cudaStream_t st = (cudaStream_t)stream;

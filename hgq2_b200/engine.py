@@ -26,6 +26,7 @@ the autograd path: the same kernels run on the same operands.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 
 import numpy as np
@@ -290,6 +291,68 @@ class _Dense(_Node):
                             None if self.bq is None else self.bq.BITS.view(-1), out_size, scale, layer._beta.value,
                             out=(layer._ebops.value, eng.eb_loss[self.eb_index], self.iq.dBITS.view(self.P, self.K),
                                  self.kq.dBITS.view(self.K, self.N), None if self.bq is None else self.bq.dBITS.view(-1)))
+
+
+class _DenseChain(_Node):
+    """Consecutive QDense layers with one row per sample, at most 64 inputs and outputs each and no output quantizer, run as
+    ONE forward and ONE backward launch for batches of at most one 128-row tile per SM (hgq_dense_chain_fwd / _bwd: the
+    activations of a tile stay in shared memory from layer to layer).  On the tensor-core kernels every layer of such a batch
+    is a launch that walks its whole chain of dependent latencies for a single tile.  Larger batches keep the per-layer
+    tensor-core kernels, which are bound by memory there and faster than fp32 FMAs."""
+
+    def __init__(self, nodes):
+        self.nodes = nodes
+        self._use = {}
+        self._keep = None
+
+    @staticmethod
+    def chainable(node) -> bool:
+        return (isinstance(node, _Dense) and node.P == 1 and node.n_con == 1 and len(node.out_tail) == 1 and node.oq is None
+                and node.pool is None and node.K <= 64 and node.N <= 64)
+
+    def check(self, batch):
+        for n in self.nodes:
+            n.check(batch)
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        self._use[batch] = (os.environ.get('HGQ_DENSE_CHAIN', '1') != '0' and batch <= 128 * sms
+                            and kernels.dense_chain_supported([self.nodes[0].K] + [n.N for n in self.nodes]))
+
+    def post_allocate(self, eng):
+        for n in self.nodes:
+            n.post_allocate(eng)
+
+    def forward(self, x):
+        if not self._use.get(x.shape[0], False):
+            for n in self.nodes:
+                x = n.forward(x)
+            return x
+        x = x.contiguous()
+        M = x.shape[0]
+        specs = []
+        for n in self.nodes:
+            specs.append(dict(K=n.K, N=n.N, relu=n.relu, round_mode=n.iq.q.round_mode, qf=n.iq.F.view(-1), wq=n.wq.view(n.K, n.N),
+                              bq=n.bias_q, y=torch.empty((M, n.N), dtype=torch.float32, device=x.device), absmax=n.iq.absmax,
+                              dwq=n.dwq.view(n.K, n.N), dbq=n.dbq, df=n.iq.dF.view(-1)))
+        layers = kernels.dense_chain_layers(specs)
+        kernels.dense_chain_fwd(x, layers, len(specs))
+        self._keep = (x, layers, specs)  # the descriptor array holds raw addresses: the tensors stay alive until the backward
+        return specs[-1]['y']
+
+    def backward(self, g, need_dx=True):
+        if self._keep is None:
+            for j in range(len(self.nodes) - 1, -1, -1):
+                g = self.nodes[j].backward(g, need_dx=need_dx or j > 0)
+            return g
+        x, layers, specs = self._keep
+        self._keep = None
+        g = g.contiguous()
+        dx = torch.empty_like(x) if need_dx else None
+        kernels.dense_chain_bwd(g, x, dx, layers, len(specs))
+        return dx
+
+    def ebops(self, eng):
+        for n in self.nodes:
+            n.ebops(eng)
 
 
 class _Conv(_Node):
@@ -573,6 +636,16 @@ class Engine:
         for a, b in zip(self.nodes, self.nodes[1:]):
             if isinstance(a, _Dense) and isinstance(b, _Reduce) and a.oq is None and len(a.out_tail) == 2 and a.out_tail[0] == a.P:
                 a.pool = b
+        # runs of small dense layers become one node (one forward and one backward launch for the whole run)
+        merged: list[_Node] = []
+        for node in self.nodes:
+            if _DenseChain.chainable(node) and merged and isinstance(merged[-1], (_Dense, _DenseChain)) and \
+                    _DenseChain.chainable(merged[-1].nodes[-1] if isinstance(merged[-1], _DenseChain) else merged[-1]):
+                last = merged.pop()
+                merged.append(_DenseChain((last.nodes if isinstance(last, _DenseChain) else [last]) + [node]))
+            else:
+                merged.append(node)
+        self.nodes = merged
         self._allocate()
         for node in self.nodes:
             node.post_allocate(self)
