@@ -23,10 +23,9 @@
 namespace hgq {
 
 constexpr int kMcThreads = 512;
-constexpr int kMcRows = 128;      // rows of a tile
+constexpr int kMcRows = 128;      // most rows of a tile (the shared-memory buffers are this tall)
 constexpr int kMcWidth = 64;      // largest layer width
-constexpr int kMcLd = 68;         // row stride (floats) of an activation tile in shared memory: 16-byte aligned rows, room for a
-                                  // 65th column (the ones that turn the bias gradient into a row of the weight gradient)
+constexpr int kMcLd = 68;         // row stride (floats) of an activation tile in shared memory: 16-byte aligned rows
 constexpr int kMcMaxLayers = HGQ_CHAIN_MAX_LAYERS;
 
 struct McLayer {
@@ -42,8 +41,40 @@ struct McParams {
     float *dx, *part;
     int64_t M, tiles;
     int n, part_stride, w_total;
+    int R;  // rows of a tile: as few as spread the batch over every SM (a multiple of 8, at most 128)
     McLayer L[kMcMaxLayers];
 };
+
+// 4-byte asynchronous copy global -> shared (zero when `valid` is false): a thread issues all of its copies and waits once,
+// so the loads of every layer's weights overlap instead of each loop iteration waiting for its own
+__device__ __forceinline__ void mc_cp4(float *dst, const float *src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mc_cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Phase timing of block 0 (stand-alone profiling builds only): time since the previous mark, added to slot i.
+#ifdef HGQ_MC_PROF
+__device__ unsigned long long g_mc_prof[32];
+__device__ __forceinline__ unsigned long long mc_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define MC_DECL unsigned long long mc_t0 = mc_now()
+#define MC_MARK(i)                                           \
+    do {                                                     \
+        if (blockIdx.x == 0 && threadIdx.x == 0) {           \
+            const unsigned long long mc_t = mc_now();        \
+            g_mc_prof[i] += mc_t - mc_t0;                    \
+            mc_t0 = mc_t;                                    \
+        }                                                    \
+    } while (0)
+#else
+#define MC_DECL
+#define MC_MARK(i)
+#endif
 
 __device__ __forceinline__ float mc_round(float v, float s, float inv, int rm) {
     const float xs = __fmul_rn(v, s);
@@ -57,29 +88,30 @@ struct McMap {
     int groups, slots, cg, slot;
     bool active;
 };
-__device__ __forceinline__ McMap mc_map(int width, int tid) {
+__device__ __forceinline__ McMap mc_map(int R, int width, int tid) {
     McMap m;
     m.groups = (width + 3) >> 2;
-    m.slots = kMcThreads / m.groups;
+    // four rows per thread wherever the tile has that many: a 16-byte shared-memory load occupies the load unit for four
+    // cycles, so a thread with a single row (one 16-byte and one 4-byte load per four FMAs) would be bound by it
+    m.slots = min(kMcThreads / m.groups, (R + 3) >> 2);
     m.cg = tid % m.groups;
     m.slot = tid / m.groups;
     m.active = m.slot < m.slots;
     return m;
 }
 constexpr int kMcRowsPerThread = 4;  // 128 rows over at least 32 slots (at most 16 column groups)
-constexpr int kMcInputsPerThread = 3;  // 65 inputs over at least 32 slots
 
 // f(r, c) for every element of a [128, width] tile.  When the thread count is a multiple of the width a thread stays in one
 // column and walks rows a fixed step apart (no division per element: these loops, not the products, were most of the
 // instructions of a first version); otherwise elements are dealt out in order.
 template <class F>
-__device__ __forceinline__ void mc_foreach(int width, int tid, F f) {
+__device__ __forceinline__ void mc_foreach(int R, int width, int tid, F f) {
     if (kMcThreads % width == 0) {
         const int c = tid % width, step = kMcThreads / width;
 #pragma unroll 4
-        for (int r = tid / width; r < kMcRows; r += step) f(r, c);
+        for (int r = tid / width; r < R; r += step) f(r, c);
     } else {
-        for (int e = tid; e < kMcRows * width; e += kMcThreads) {
+        for (int e = tid; e < R * width; e += kMcThreads) {
             const int r = e / width;
             f(r, e - r * width);
         }
@@ -87,26 +119,26 @@ __device__ __forceinline__ void mc_foreach(int width, int tid, F f) {
 }
 
 // a tile of a row-major [M, width] matrix into shared memory (rows beyond the matrix read as zero)
-__device__ __forceinline__ void mc_load_tile(float *dst, const float *src, int64_t row0, int rows_here, int width, int tid) {
+__device__ __forceinline__ void mc_load_tile(int R, float *dst, const float *src, int64_t row0, int rows_here, int width, int tid) {
     if ((width & 3) == 0 && aligned(src, 16)) {
         const float4 *s4 = reinterpret_cast<const float4 *>(src + row0 * width);
         const int w4 = width >> 2;
-        mc_foreach(w4, tid, [&](int r, int c) {
+        mc_foreach(R, w4, tid, [&](int r, int c) {
             const float4 v = (r < rows_here) ? __ldcs(s4 + r * w4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             *reinterpret_cast<float4 *>(dst + r * kMcLd + c * 4) = v;
         });
     } else {
         const float *s1 = src + row0 * width;
-        mc_foreach(width, tid, [&](int r, int c) { dst[r * kMcLd + c] = (r < rows_here) ? __ldcs(s1 + r * width + c) : 0.f; });
+        mc_foreach(R, width, tid, [&](int r, int c) { dst[r * kMcLd + c] = (r < rows_here) ? __ldcs(s1 + r * width + c) : 0.f; });
     }
 }
 
 // zero where the layer's output was not positive (the ReLU mask of the gradient)
-__device__ __forceinline__ void mc_relu_mask(float *g, const float *y, int64_t row0, int rows_here, int width, int tid) {
+__device__ __forceinline__ void mc_relu_mask(int R, float *g, const float *y, int64_t row0, int rows_here, int width, int tid) {
     if ((width & 3) == 0 && aligned(y, 16)) {
         const float4 *y4 = reinterpret_cast<const float4 *>(y + row0 * width);
         const int w4 = width >> 2;
-        mc_foreach(w4, tid, [&](int r, int c) {
+        mc_foreach(R, w4, tid, [&](int r, int c) {
             if (r < rows_here) {
                 const float4 v = __ldcs(y4 + r * w4 + c);
                 float4 *gp = reinterpret_cast<float4 *>(g + r * kMcLd + c * 4);
@@ -117,7 +149,7 @@ __device__ __forceinline__ void mc_relu_mask(float *g, const float *y, int64_t r
         });
     } else {
         const float *y1 = y + row0 * width;
-        mc_foreach(width, tid, [&](int r, int c) {
+        mc_foreach(R, width, tid, [&](int r, int c) {
             if (r < rows_here && !(__ldcs(y1 + r * width + c) > 0.f)) g[r * kMcLd + c] = 0.f;
         });
     }
@@ -127,10 +159,10 @@ __device__ __forceinline__ void mc_relu_mask(float *g, const float *y, int64_t r
 // activation tile (row stride kMcLd), B a weight matrix with row stride ldb.  Rows beyond the tile are clamped (computed,
 // not stored by the callers), so the loop has no predicate; JN is the number of rows a thread really has (1, 2 or 4).
 template <int JN>
-__device__ __forceinline__ void mc_rows_product(const float *A, const float *B, int ldb, int depth, const McMap &m, float (&acc)[4][4]) {
+__device__ __forceinline__ void mc_rows_product(int R, const float *A, const float *B, int ldb, int depth, const McMap &m, float (&acc)[4][4]) {
     const float *ap[JN];
 #pragma unroll
-    for (int j = 0; j < JN; ++j) ap[j] = A + min(m.slot + j * m.slots, kMcRows - 1) * kMcLd;
+    for (int j = 0; j < JN; ++j) ap[j] = A + min(m.slot + j * m.slots, R - 1) * kMcLd;
     const float *bp = B + m.cg * 4;
 #pragma unroll 4
     for (int i = 0; i < depth; ++i) {
@@ -145,15 +177,15 @@ __device__ __forceinline__ void mc_rows_product(const float *A, const float *B, 
         }
     }
 }
-__device__ __forceinline__ void mc_rows_product_any(const float *A, const float *B, int ldb, int depth, const McMap &m, float (&acc)[4][4]) {
+__device__ __forceinline__ void mc_rows_product_any(int R, const float *A, const float *B, int ldb, int depth, const McMap &m, float (&acc)[4][4]) {
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
-    const int jn = (kMcRows + m.slots - 1) / m.slots;  // 4 (16 column groups), 2 or 3 (5 .. 15), 1 (at most 4)
-    if (jn <= 1) mc_rows_product<1>(A, B, ldb, depth, m, acc);
-    else if (jn == 2) mc_rows_product<2>(A, B, ldb, depth, m, acc);
-    else mc_rows_product<4>(A, B, ldb, depth, m, acc);
+    const int jn = (R + m.slots - 1) / m.slots;  // 4 unless the tile is shorter than four rows per slot
+    if (jn <= 1) mc_rows_product<1>(R, A, B, ldb, depth, m, acc);
+    else if (jn == 2) mc_rows_product<2>(R, A, B, ldb, depth, m, acc);
+    else mc_rows_product<4>(R, A, B, ldb, depth, m, acc);
 }
 
 // ---- forward --------------------------------------------------------------------------------------------------------------
@@ -166,7 +198,8 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_fwd(const McParams P
     float *isc = sc + kMcMaxLayers * kMcWidth;              // [layers][64] 2^-f
     unsigned *colmax = reinterpret_cast<unsigned *>(isc + kMcMaxLayers * kMcWidth);  // [layers][64] bits of max |xq| per column
     float *Wall = reinterpret_cast<float *>(colmax + kMcMaxLayers * kMcWidth);       // every layer's [K][Nw], zero beyond N
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, R = P.R;
+    MC_DECL;
 
     // every layer's weights, bias and scales once per block
     for (int l = 0; l < P.n; ++l) {
@@ -175,7 +208,7 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_fwd(const McParams P
         float *W = Wall + Ly.w_off;
         for (int e = tid; e < K * Nw; e += kMcThreads) {
             const int k = e / Nw, n = e - k * Nw;
-            W[e] = (n < N) ? __ldg(Ly.wq + k * N + n) : 0.f;
+            mc_cp4(W + e, Ly.wq + k * N + min(n, N - 1), n < N);
         }
         if (tid < kMcWidth) {
             bias[l * kMcWidth + tid] = (Ly.bq != nullptr && tid < N) ? __ldg(Ly.bq + tid) : 0.f;
@@ -185,60 +218,74 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_fwd(const McParams P
             colmax[l * kMcWidth + tid] = 0u;
         }
     }
+    mc_cp_wait();
     __syncthreads();
+    MC_MARK(0);
 
     for (int64_t tile = blockIdx.x; tile < P.tiles; tile += gridDim.x) {
-        const int64_t row0 = tile * kMcRows;
-        const int rows_here = (int)((P.M - row0) < kMcRows ? (P.M - row0) : kMcRows);
+        const int64_t row0 = tile * R;
+        const int rows_here = (int)((P.M - row0) < R ? (P.M - row0) : R);
         float *in = buf0, *out = buf1;
-        mc_load_tile(in, P.x, row0, rows_here, P.L[0].K, tid);
+        {   // the tile of x, rounded by the first layer's input quantizer on its way into shared memory
+            const McLayer &L0 = P.L[0];
+            const int K0 = L0.K;
+            const float *x0 = P.x + row0 * K0;
+            const bool track = L0.absmax != nullptr, one_column = (kMcThreads % K0 == 0);  // one_column: see mc_foreach
+            float mx = 0.f;
+            mc_foreach(R, K0, tid, [&](int r, int k) {
+                const float v = (r < rows_here) ? __ldcs(x0 + r * K0 + k) : 0.f;
+                const float q = mc_round(v, sc[k], isc[k], L0.rm);
+                in[r * kMcLd + k] = q;
+                if (track && r < rows_here) {
+                    if (one_column) mx = fmaxf(mx, fabsf(q));
+                    else atomicMax(colmax + k, __float_as_uint(fabsf(q)));
+                }
+            });
+            if (track && one_column) atomicMax(colmax + tid % K0, __float_as_uint(mx));
+        }
         __syncthreads();
+        MC_MARK(1);
         for (int l = 0; l < P.n; ++l) {
             const McLayer &Ly = P.L[l];
             const int K = Ly.K, N = Ly.N;
-            const McMap m = mc_map(N, tid);
+            const McMap m = mc_map(R, N, tid);
             const int Nw = m.groups * 4;
-            const float *W = Wall + Ly.w_off;
-            const float *sc_l = sc + l * kMcWidth, *isc_l = isc + l * kMcWidth;
-            // input quantizer in place, column maxima of the rounded values over the rows that exist
-            if (kMcThreads % K == 0) {  // a thread stays in one column
-                const int k = tid % K;
-                const float s = sc_l[k], inv = isc_l[k];
-                float mx = 0.f;
-#pragma unroll 4
-                for (int r = tid / K; r < kMcRows; r += kMcThreads / K) {
-                    const float q = mc_round(in[r * kMcLd + k], s, inv, Ly.rm);
-                    in[r * kMcLd + k] = q;
-                    if (r < rows_here) mx = fmaxf(mx, fabsf(q));
-                }
-                if (Ly.absmax != nullptr) atomicMax(colmax + l * kMcWidth + k, __float_as_uint(mx));
-            } else {
-                for (int e = tid; e < kMcRows * K; e += kMcThreads) {
-                    const int r = e / K, k = e - r * K;
-                    const float q = mc_round(in[r * kMcLd + k], sc_l[k], isc_l[k], Ly.rm);
-                    in[r * kMcLd + k] = q;
-                    if (Ly.absmax != nullptr && r < rows_here) atomicMax(colmax + l * kMcWidth + k, __float_as_uint(fabsf(q)));
-                }
-            }
-            __syncthreads();
             // y = act(xq @ W + b): rows slot + j * slots of column group cg
-            if (m.active && m.slot < kMcRows) {
+            if (m.active && m.slot < R) {
                 float acc[kMcRowsPerThread][4];
-                mc_rows_product_any(in, Wall + Ly.w_off, Nw, K, m, acc);
+                mc_rows_product_any(R, in, Wall + Ly.w_off, Nw, K, m, acc);
+                MC_MARK(4);
                 const float lo = Ly.relu ? 0.f : -INFINITY;
                 const int n0 = m.cg * 4;
                 const float4 b4 = *reinterpret_cast<const float4 *>(bias + l * kMcWidth + n0);
                 const bool vec = (N % 4 == 0) && aligned(Ly.y, 16);
+                // the next layer's input quantizer is applied here, on the way into shared memory (the value as computed
+                // goes to memory for the backward)
+                const bool more = l + 1 < P.n;
+                const int ln = more ? l + 1 : l;
+                const float4 s4 = *reinterpret_cast<const float4 *>(sc + ln * kMcWidth + n0);
+                const float4 i4 = *reinterpret_cast<const float4 *>(isc + ln * kMcWidth + n0);
+                const int rm_n = P.L[ln].rm;
+                float mx[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int j = 0; j < kMcRowsPerThread; ++j) {
                     const int r = m.slot + j * m.slots;
-                    if (r < kMcRows) {
+                    if (r < R) {
                         float4 o;
                         o.x = fmaxf(__fadd_rn(acc[j][0], b4.x), lo);
                         o.y = fmaxf(__fadd_rn(acc[j][1], b4.y), lo);
                         o.z = fmaxf(__fadd_rn(acc[j][2], b4.z), lo);
                         o.w = fmaxf(__fadd_rn(acc[j][3], b4.w), lo);
-                        *reinterpret_cast<float4 *>(out + r * kMcLd + n0) = o;
+                        if (more) {
+                            float4 q;
+                            q.x = mc_round(o.x, s4.x, i4.x, rm_n); q.y = mc_round(o.y, s4.y, i4.y, rm_n);
+                            q.z = mc_round(o.z, s4.z, i4.z, rm_n); q.w = mc_round(o.w, s4.w, i4.w, rm_n);
+                            *reinterpret_cast<float4 *>(out + r * kMcLd + n0) = q;
+                            if (r < rows_here) {
+                                mx[0] = fmaxf(mx[0], fabsf(q.x)); mx[1] = fmaxf(mx[1], fabsf(q.y));
+                                mx[2] = fmaxf(mx[2], fabsf(q.z)); mx[3] = fmaxf(mx[3], fabsf(q.w));
+                            }
+                        }
                         if (r < rows_here) {
                             float *dst = Ly.y + (row0 + r) * N + n0;
                             if (vec) {
@@ -252,8 +299,15 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_fwd(const McParams P
                         }
                     }
                 }
+                if (more && P.L[ln].absmax != nullptr) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (n0 + c < N) atomicMax(colmax + ln * kMcWidth + n0 + c, __float_as_uint(mx[c]));
+                }
+                MC_MARK(5);
             }
             __syncthreads();
+            MC_MARK(3);
             float *t = in; in = out; out = t;
         }
     }
@@ -269,15 +323,17 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
     extern __shared__ __align__(16) float smem_f[];
     float *G = smem_f;                                      // [128][68] gradient entering the current layer (its output side)
     float *D = G + kMcRows * kMcLd;                         // [128][68] gradient leaving it (dXq)
-    float *XQ = D + kMcRows * kMcLd;                        // [128][68] rounded inputs, a column of ones behind them
+    float *XQ = D + kMcRows * kMcLd;                        // [128][68] rounded inputs
     float *XR = XQ + kMcRows * kMcLd;                       // [128][68] inputs as stored
     float *red = XR + kMcRows * kMcLd;                      // [512] partial df sums
-    float *scratch = red + kMcThreads;                      // [512][4] partial weight-gradient sums of the row splits
-    float *sc = scratch + kMcThreads * 4;                   // [layers][64], [layers][64]
+    float *red_b = red + kMcThreads;                        // [512] partial bias-gradient sums
+    float *scratch = red_b + kMcThreads;                    // [512][16] partial weight-gradient sums of the row splits
+    float *sc = scratch + kMcThreads * 16;                   // [layers][64], [layers][64]
     float *isc = sc + kMcMaxLayers * kMcWidth;
     float *acc_s = isc + kMcMaxLayers * kMcWidth;           // per layer [dWq | dbq | df] sums over this block's tiles
     float *WTall = acc_s + ((P.part_stride + 3) & ~3);      // every layer's transposed weights [N][Kw], zero beyond K
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, R = P.R;
+    MC_DECL;
 
     for (int e = tid; e < P.part_stride; e += kMcThreads) acc_s[e] = 0.f;
     for (int l = 0; l < P.n; ++l) {
@@ -286,7 +342,7 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
         float *WT = WTall + Ly.w_off;
         for (int e = tid; e < Kw * N; e += kMcThreads) {  // coalesced over n in memory, transposed into shared memory
             const int k = e / N, n = e - k * N;
-            WT[n * Kw + k] = (k < K) ? __ldg(Ly.wq + k * N + n) : 0.f;
+            mc_cp4(WT + n * Kw + k, Ly.wq + min(k, K - 1) * N + n, k < K);
         }
         if (tid < kMcWidth) {
             const int fi = (tid < K) ? __float2int_rn(__ldg(Ly.qf + tid)) : 0;
@@ -294,44 +350,75 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
             isc[l * kMcWidth + tid] = pow2i(-fi);
         }
     }
+    mc_cp_wait();
     __syncthreads();
+    MC_MARK(0);
 
     for (int64_t tile = blockIdx.x; tile < P.tiles; tile += gridDim.x) {
-        const int64_t row0 = tile * kMcRows;
-        const int rows_here = (int)((P.M - row0) < kMcRows ? (P.M - row0) : kMcRows);
-        mc_load_tile(G, P.gy, row0, rows_here, P.L[P.n - 1].N, tid);
+        const int64_t row0 = tile * R;
+        const int rows_here = (int)((P.M - row0) < R ? (P.M - row0) : R);
+        mc_load_tile(R, G, P.gy, row0, rows_here, P.L[P.n - 1].N, tid);
+        if (P.L[P.n - 1].relu) {  // the mask of the last layer comes from its stored output; the others' from shared memory
+            __syncthreads();
+            mc_relu_mask(R, G, P.L[P.n - 1].y, row0, rows_here, P.L[P.n - 1].N, tid);
+        }
         float *g_in = G, *g_out = D;
+        __syncthreads();  // the tile's gradient is in place
         for (int l = P.n - 1; l >= 0; --l) {
             const McLayer &Ly = P.L[l];
             const int K = Ly.K, N = Ly.N;
-            const McMap mk = mc_map(K, tid);    // dXq tile: column groups over k
-            const McMap mn = mc_map(N, tid);    // dWq tile: column groups over n
-            const int Kw = mk.groups * 4, Nw = mn.groups * 4;
+            const McMap mk = mc_map(R, K, tid);    // dXq tile: column groups over k
+            const int n_groups = (N + 3) >> 2;
+            const int Kw = mk.groups * 4, Nw = n_groups * 4;
             const float *WT = WTall + Ly.w_off;
             const float *sc_l = sc + l * kMcWidth, *isc_l = isc + l * kMcWidth;
             float *a_l = acc_s + Ly.part_off;
-            __syncthreads();  // the tile's gradient is in place; the previous layer's readers of XQ / XR / red are done
-            // this layer's inputs (as stored, rounded, and a column of ones), the ReLU mask on the gradient
-            mc_load_tile(XR, (l == 0) ? P.x : P.L[l - 1].y, row0, rows_here, K, tid);
-            if (Ly.relu) mc_relu_mask(g_in, Ly.y, row0, rows_here, N, tid);
+            // (no barrier here: the sums that end a layer touch only the block's records and the scratch areas, which the
+            // next layer writes after its own load barrier)
+            MC_MARK(1);
+            // this layer's inputs as stored and rounded
+            {
+                const float *xl = ((l == 0) ? P.x : P.L[l - 1].y) + row0 * K;
+                if ((K & 3) == 0 && aligned(xl, 16)) {  // 16 bytes per load: the whole tile is in flight at once
+                    const int w4 = K >> 2;
+                    mc_foreach(R, w4, tid, [&](int r, int c) {
+                        const float4 v = (r < rows_here) ? __ldcs(reinterpret_cast<const float4 *>(xl + r * K) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        const float4 s4 = *reinterpret_cast<const float4 *>(sc_l + c * 4), i4 = *reinterpret_cast<const float4 *>(isc_l + c * 4);
+                        *reinterpret_cast<float4 *>(XR + r * kMcLd + c * 4) = v;
+                        *reinterpret_cast<float4 *>(XQ + r * kMcLd + c * 4) =
+                            make_float4(mc_round(v.x, s4.x, i4.x, Ly.rm), mc_round(v.y, s4.y, i4.y, Ly.rm), mc_round(v.z, s4.z, i4.z, Ly.rm),
+                                        mc_round(v.w, s4.w, i4.w, Ly.rm));
+                    });
+                } else {
+                    mc_foreach(R, K, tid, [&](int r, int k) {
+                        const float v = (r < rows_here) ? __ldcs(xl + r * K + k) : 0.f;
+                        XR[r * kMcLd + k] = v;
+                        XQ[r * kMcLd + k] = mc_round(v, sc_l[k], isc_l[k], Ly.rm);
+                    });
+                    if (Kw != K)  // the padding columns the 16-byte reads of the dWq product touch
+                        for (int e = tid; e < R * (Kw - K); e += kMcThreads) {
+                            const int r = e / (Kw - K), k = K + (e - r * (Kw - K));
+                            XQ[r * kMcLd + k] = 0.f;
+                        }
+                }
+            }
             if (Nw != N)  // the padding columns the float4 reads of the dWq product touch
-                for (int e = tid; e < kMcRows * (Nw - N); e += kMcThreads) {
+                for (int e = tid; e < R * (Nw - N); e += kMcThreads) {
                     const int r = e / (Nw - N), n = N + (e - r * (Nw - N));
                     g_in[r * kMcLd + n] = 0.f;
                 }
             __syncthreads();
-            mc_foreach(K, tid, [&](int r, int k) { XQ[r * kMcLd + k] = mc_round(XR[r * kMcLd + k], sc_l[k], isc_l[k], Ly.rm); });
-            if (tid < kMcRows) XQ[tid * kMcLd + K] = 1.f;
-            __syncthreads();
+            MC_MARK(2);
+            MC_MARK(3);
             // ---- dXq = G @ W^T ------------------------------------------------------------------------------------------------
-            if (mk.active && mk.slot < kMcRows) {
+            if (mk.active && mk.slot < R) {
                 float acc[kMcRowsPerThread][4];
-                mc_rows_product_any(g_in, WT, Kw, N, mk, acc);
+                mc_rows_product_any(R, g_in, WT, Kw, N, mk, acc);
                 const int k0 = mk.cg * 4;
 #pragma unroll
                 for (int j = 0; j < kMcRowsPerThread; ++j) {
                     const int r = mk.slot + j * mk.slots;
-                    if (r < kMcRows) {
+                    if (r < R) {
                         *reinterpret_cast<float4 *>(g_out + r * kMcLd + k0) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
                         if (l == 0 && P.dx != nullptr && r < rows_here) {
 #pragma unroll
@@ -341,103 +428,94 @@ __global__ void __launch_bounds__(kMcThreads) k_dense_chain_bwd(const McParams P
                     }
                 }
             }
-            // ---- [dWq; dbq] += [xq 1]^T @ G (the column of ones behind xq makes row K the bias gradient) -------------------------
-            // A unit is (input k, group of four outputs): its four sums run over the 128 rows.  Layers with fewer units than
-            // threads split the rows among `splits` threads per unit (combined below in a fixed order); wider layers give a
-            // thread up to three inputs of one column group.
-            const int units = (K + 1) * mn.groups;
-            const int splits = units < kMcThreads ? kMcThreads / units : 1;
-            const int rps = (kMcRows + splits - 1) / splits;  // rows per split
-            if (units < kMcThreads) {
-                if (tid < units * splits) {
-                    const int unit = tid % units, sp = tid / units;
-                    const int k = unit / mn.groups, cg = unit - k * mn.groups;
-                    const int r0 = sp * rps, r1 = min(kMcRows, r0 + rps);
-                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-                    const float *xp = XQ + k, *gq = g_in + cg * 4;
+            MC_MARK(4);
+            // ---- dWq += xq^T @ G ---------------------------------------------------------------------------------------------------
+            // A unit is (four inputs, four outputs): its sixteen sums run over the rows, two 16-byte loads per sixteen FMAs.
+            // There are far fewer units than threads, so the rows of a unit are split among `splits` threads (partial sums to
+            // shared memory, combined below in a fixed order).
+            const int units = mk.groups * n_groups;
+            const int splits = max(1, min(kMcThreads / units, R >> 3));  // at least eight rows per split
+            const int rps = (R + splits - 1) / splits;  // rows per split
+            if (tid < units * splits) {
+                const int unit = tid % units, sp = tid / units;
+                const int kg = unit / n_groups, cg = unit - kg * n_groups;
+                const int r0 = sp * rps, r1 = min(R, r0 + rps);
+                float a[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) a[i][c] = 0.f;
+                const float *xp = XQ + kg * 4, *gq = g_in + cg * 4;
 #pragma unroll 4
-                    for (int r = r0; r < r1; ++r) {
-                        const float4 g4 = *reinterpret_cast<const float4 *>(gq + r * kMcLd);
-                        const float xv = xp[r * kMcLd];
-                        a0 = __fmaf_rn(xv, g4.x, a0); a1 = __fmaf_rn(xv, g4.y, a1);
-                        a2 = __fmaf_rn(xv, g4.z, a2); a3 = __fmaf_rn(xv, g4.w, a3);
-                    }
-                    *reinterpret_cast<float4 *>(scratch + tid * 4) = make_float4(a0, a1, a2, a3);
-                }
-            } else if (mn.active) {
-                float acc[kMcInputsPerThread][4];
-#pragma unroll
-                for (int j = 0; j < kMcInputsPerThread; ++j)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
-                // inputs beyond the layer's are clamped to the column of ones (computed, not stored)
-                const float *xp[kMcInputsPerThread];
-#pragma unroll
-                for (int j = 0; j < kMcInputsPerThread; ++j) xp[j] = XQ + min(mn.slot + j * mn.slots, K);
-                const float *gq = g_in + mn.cg * 4;
-#pragma unroll 4
-                for (int r = 0; r < kMcRows; ++r) {
+                for (int r = r0; r < r1; ++r) {
                     const float4 g4 = *reinterpret_cast<const float4 *>(gq + r * kMcLd);
+                    const float4 x4 = *reinterpret_cast<const float4 *>(xp + r * kMcLd);
+                    const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
 #pragma unroll
-                    for (int j = 0; j < kMcInputsPerThread; ++j) {
-                        const float xv = xp[j][r * kMcLd];
-                        acc[j][0] = __fmaf_rn(xv, g4.x, acc[j][0]);
-                        acc[j][1] = __fmaf_rn(xv, g4.y, acc[j][1]);
-                        acc[j][2] = __fmaf_rn(xv, g4.z, acc[j][2]);
-                        acc[j][3] = __fmaf_rn(xv, g4.w, acc[j][3]);
+                    for (int i = 0; i < 4; ++i) {
+                        a[i][0] = __fmaf_rn(xv[i], g4.x, a[i][0]); a[i][1] = __fmaf_rn(xv[i], g4.y, a[i][1]);
+                        a[i][2] = __fmaf_rn(xv[i], g4.z, a[i][2]); a[i][3] = __fmaf_rn(xv[i], g4.w, a[i][3]);
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < kMcInputsPerThread; ++j) {
-                    const int k = mn.slot + j * mn.slots;
-                    if (k <= K) {  // row K of the record is dbq
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int n = mn.cg * 4 + c;
-                            if (n < N) a_l[k * N + n] = __fadd_rn(a_l[k * N + n], acc[j][c]);
-                        }
-                    }
-                }
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<float4 *>(scratch + (tid * 4 + i) * 4) = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
             }
             __syncthreads();  // dXq complete
+            MC_MARK(5);
             // ---- df[k] += sum_r -ln2 (xq - x) dXq: thread t takes column t % K and the rows t / K, t / K + subsets, ... --------
             const int subsets = kMcThreads / K;
             if (tid < subsets * K) {
                 const int k = tid % K;
                 float s = 0.f;
-                for (int r = tid / K; r < kMcRows; r += subsets) {
-                    const float er = __fmul_rn(__fsub_rn(XQ[r * kMcLd + k], XR[r * kMcLd + k]), -kLn2);
-                    s = __fmaf_rn(er, g_out[r * kMcLd + k], s);
+                const bool mask_below = l > 0 && P.L[l - 1].relu;
+#pragma unroll 4
+                for (int r = tid / K; r < R; r += subsets) {
+                    const float xv = XR[r * kMcLd + k], d = g_out[r * kMcLd + k];
+                    const float er = __fmul_rn(__fsub_rn(XQ[r * kMcLd + k], xv), -kLn2);
+                    s = __fmaf_rn(er, d, s);
+                    // the layer below wrote xv as its output: its ReLU passes the gradient where that was positive
+                    if (mask_below && !(xv > 0.f)) g_out[r * kMcLd + k] = 0.f;
                 }
                 red[tid] = s;
             }
+            // ---- dbq += column sums of G: thread t takes column t % N and the rows t / N, t / N + subsets_b, ... --------------------
+            const int subsets_b = kMcThreads / N;
+            if (tid < subsets_b * N) {
+                const int n = tid % N;
+                float s = 0.f;
+#pragma unroll 4
+                for (int r = tid / N; r < R; r += subsets_b) s = __fadd_rn(s, g_in[r * kMcLd + n]);
+                red_b[tid] = s;
+            }
             __syncthreads();
+            MC_MARK(6);
             if (tid < K) {
                 float s = 0.f;
                 for (int sub = 0; sub < subsets; ++sub) s = __fadd_rn(s, red[sub * K + tid]);
                 a_l[K * N + N + tid] = __fadd_rn(a_l[K * N + N + tid], s);
             }
-            if (units < kMcThreads && tid < units) {  // the row splits of this unit, in order
-                const int k = tid / mn.groups, cg = tid - k * mn.groups;
-                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int sp = 0; sp < splits; ++sp) {
-                    const float4 v = *reinterpret_cast<const float4 *>(scratch + (sp * units + tid) * 4);
-                    t.x = __fadd_rn(t.x, v.x); t.y = __fadd_rn(t.y, v.y); t.z = __fadd_rn(t.z, v.z); t.w = __fadd_rn(t.w, v.w);
-                }
-                const float tv[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int n = cg * 4 + c;
-                    if (n < N) a_l[k * N + n] = __fadd_rn(a_l[k * N + n], tv[c]);
-                }
+            if (tid < N) {
+                float s = 0.f;
+                for (int sub = 0; sub < subsets_b; ++sub) s = __fadd_rn(s, red_b[sub * N + tid]);
+                a_l[K * N + tid] = __fadd_rn(a_l[K * N + tid], s);
+            }
+            for (int e = tid; e < K * N; e += kMcThreads) {  // the row splits of every weight, in order
+                const int k = e / N, n = e - k * N;
+                const int unit = (k >> 2) * n_groups + (n >> 2), off = (k & 3) * 4 + (n & 3);
+                float t = 0.f;
+                for (int sp = 0; sp < splits; ++sp) t = __fadd_rn(t, scratch[(sp * units + unit) * 16 + off]);
+                a_l[e] = __fadd_rn(a_l[e], t);
             }
             float *t = g_in; g_in = g_out; g_out = t;
         }
         __syncthreads();
     }
     __syncthreads();
+    MC_MARK(7);
     float *pb = P.part + (int64_t)blockIdx.x * P.part_stride;
     for (int e = tid; e < P.part_stride; e += kMcThreads) pb[e] = acc_s[e];
+    MC_MARK(8);
 }
 
 // Sums the blocks' partial records in a fixed order (in double) and scatters element e of the record to the layer output it
@@ -475,7 +553,7 @@ static size_t mc_fwd_smem(int w_total) {
     return (size_t)(2 * kMcRows * kMcLd + 4 * kMcMaxLayers * kMcWidth + w_total) * sizeof(float);
 }
 static size_t mc_bwd_smem(int part_stride, int w_total) {
-    return (size_t)(4 * kMcRows * kMcLd + 5 * kMcThreads + 2 * kMcMaxLayers * kMcWidth + ((part_stride + 3) & ~3) + w_total) * sizeof(float);
+    return (size_t)(4 * kMcRows * kMcLd + 18 * kMcThreads + 2 * kMcMaxLayers * kMcWidth + ((part_stride + 3) & ~3) + w_total) * sizeof(float);
 }
 
 // widths, record offsets and the shared-memory weight area of a stack; HGQ_OK when both kernels fit
@@ -517,6 +595,14 @@ static int mc_fill(int n_layers, const hgq_chain_layer *layers, bool backward, M
 
 static int mc_grid(int64_t tiles) { return (int)(tiles < num_sms() ? tiles : num_sms()); }
 
+// rows per tile: as few as give every SM a tile (a multiple of 8), at most 128
+static void mc_tiles(int64_t M, McParams &p) {
+    int64_t r = (M + num_sms() - 1) / num_sms();
+    r = (r + 7) / 8 * 8;
+    p.R = (int)(r < 8 ? 8 : (r > kMcRows ? kMcRows : r));
+    p.tiles = (M + p.R - 1) / p.R;
+}
+
 }  // namespace hgq
 
 using namespace hgq;
@@ -538,7 +624,8 @@ extern "C" int hgq_dense_chain_fwd(const float *x, int64_t M, int n_layers, cons
     if (M <= 0) return HGQ_ERR_SIZE;
     McParams p;
     if (int e = mc_fill(n_layers, layers, false, p)) return e;
-    p.x = x; p.gy = nullptr; p.dx = nullptr; p.part = nullptr; p.M = M; p.tiles = (M + kMcRows - 1) / kMcRows;
+    p.x = x; p.gy = nullptr; p.dx = nullptr; p.part = nullptr; p.M = M;
+    mc_tiles(M, p);
     const size_t smem = mc_fwd_smem(p.w_total);
     cudaError_t ce = cudaFuncSetAttribute(k_dense_chain_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
@@ -552,7 +639,8 @@ extern "C" int hgq_dense_chain_bwd(const float *gy, const float *x, float *dx, i
     if (M <= 0) return HGQ_ERR_SIZE;
     McParams p;
     if (int e = mc_fill(n_layers, layers, true, p)) return e;
-    p.x = x; p.gy = gy; p.dx = dx; p.M = M; p.tiles = (M + kMcRows - 1) / kMcRows;
+    p.x = x; p.gy = gy; p.dx = dx; p.M = M;
+    mc_tiles(M, p);
     const int grid = mc_grid(p.tiles);
     if (workspace == nullptr || workspace_bytes < (size_t)grid * p.part_stride * sizeof(float)) return HGQ_ERR_WORKSPACE;
     if (!aligned(workspace, 16)) return HGQ_ERR_ALIGN;
