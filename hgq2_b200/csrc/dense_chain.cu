@@ -91,9 +91,11 @@ struct McMap {
 __device__ __forceinline__ McMap mc_map(int R, int width, int tid) {
     McMap m;
     m.groups = (width + 3) >> 2;
-    // four rows per thread wherever the tile has that many: a 16-byte shared-memory load occupies the load unit for four
-    // cycles, so a thread with a single row (one 16-byte and one 4-byte load per four FMAs) would be bound by it
-    m.slots = min(kMcThreads / m.groups, (R + 3) >> 2);
+    // several rows per thread: a 16-byte shared-memory load occupies the load unit for four cycles, so a thread with a single
+    // row (one 16-byte and one 4-byte load per four FMAs) would be bound by it.  Four rows for wide outputs; two for narrow
+    // ones, where four would leave most warps waiting at the barrier behind a few.
+    const int rows_per_thread = m.groups >= 12 ? 4 : 2;
+    m.slots = min(kMcThreads / m.groups, (R + rows_per_thread - 1) / rows_per_thread);
     m.cg = tid % m.groups;
     m.slot = tid / m.groups;
     m.active = m.slot < m.slots;
