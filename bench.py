@@ -578,6 +578,43 @@ def run_qdense_bwd(args):
                       'achieved_GBs': round(gbs, 1), 'peak_GBs': peak, 'frac': round(gbs / peak, 4), 'peak_source': kind}), flush=True)
 
 
+def run_dense_chain(args):
+    """Kernel-level benchmark of the single-launch dense stack (hgq_dense_chain_fwd / _bwd) on the jet-tagger MLP's layers:
+    16 -> 64 -> 32 -> 32 -> 5, ReLU on the first three, batch 16384 (--batch).  Activations are L2-resident at this size; the
+    figures are microseconds per launch, not bandwidth."""
+    from hgq2_b200 import kernels
+
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    M = args.batch or 16384
+    widths, relus = (16, 64, 32, 32, 5), (True, True, True, False)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(M, widths[0], device=dev, generator=gen) * 2
+    specs = []
+    for K, N, relu in zip(widths[:-1], widths[1:], relus):
+        specs.append(dict(K=K, N=N, relu=relu, round_mode='RND', qf=torch.randint(2, 7, (K,), device=dev, generator=gen).float(),
+                          wq=torch.randint(-48, 48, (K, N), device=dev, generator=gen).float() / 32,
+                          bq=torch.randint(-16, 16, (N,), device=dev, generator=gen).float() / 16,
+                          y=torch.empty(M, N, device=dev), absmax=torch.zeros(K, device=dev), dwq=torch.empty(K, N, device=dev),
+                          dbq=torch.empty(N, device=dev), df=torch.empty(K, device=dev)))
+    layers = kernels.dense_chain_layers(specs)
+    gy = torch.randn(M, widths[-1], device=dev, generator=gen)
+    out = {'kernel': 'k_dense_chain', 'widths': list(widths), 'batch': M}
+    for name, fn in (('forward', lambda: kernels.dense_chain_fwd(x, layers, len(specs))),
+                     ('backward', lambda: kernels.dense_chain_bwd(gy, x, None, layers, len(specs)))):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = {'us': round(a.elapsed_time(b) / args.steps * 1e3, 2)}
+    print(json.dumps(out), flush=True)
+
+
 def run_qconv(args):
     """Kernel-level benchmark of the three convolution passes (forward, input gradient, weight gradient) on one layer of
     the small CNN (--layer 1..3: 32x32x4 -> 16, 15x15x16 -> 32, 6x6x32 -> 64 filters, 3x3 'valid', ReLU).
@@ -750,7 +787,7 @@ def main():
                     help='total elements of the sweep (default 2^28; smaller values are for profiler captures)')
     ap.add_argument('--model', default='particle_tagger', help='model of --workload qat')
     ap.add_argument('--batch', type=int, default=0, help='batch of --workload qat (0 = the benchmark batch)')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'bcast', 'qdense', 'qdense_bwd', 'qsoftmax', 'qconv', 'attn', 'qat'],
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'bcast', 'qdense', 'qdense_bwd', 'qsoftmax', 'qconv', 'attn', 'dense_chain', 'qat'],
                     help="'qdense' times the fused dense forward kernel alone (for profiler captures)")
     ap.add_argument('--layer', type=int, default=1, choices=[1, 2, 3], help='convolution layer of --workload qconv')
     ap.add_argument('--rows', type=int, default=1 << 22)
@@ -768,6 +805,9 @@ def main():
         return run_qdense_bwd(args)
     if args.workload == 'bcast':
         return run_bcast(args)
+    if args.workload == 'dense_chain':
+        run_dense_chain(args)
+        return
     if args.workload == 'qconv':
         return run_qconv(args)
     if args.workload == 'attn':
