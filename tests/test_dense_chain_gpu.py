@@ -52,6 +52,7 @@ def _rel(a, b):
     ((64, 64), (True,), 129),
     ((3, 7, 64, 1), (True, False, True), 50),
     ((8, 8, 8, 8, 8, 8, 8, 8, 8), (True,) * 8, 300),            # eight layers
+    ((16, 64, 32, 5), (True, True, False), 128 * 300 + 5),      # more tiles than SMs: a block walks several, ragged last tile
 ])
 @pytest.mark.parametrize('rm', ['RND', 'TRN', 'RND_CONV'])
 def test_dense_chain_forward_and_backward(widths, relus, M, rm):
