@@ -53,6 +53,30 @@ def test_argument_errors_need_no_gpu(built_lib):
     assert L.hgq_quantize_bwd_workspace(1 << 20, 64) > 0
 
 
+def test_dense_stack_limits_need_no_gpu(built_lib):
+    """hgq_dense_chain_supported / _workspace are host arithmetic: layer count, widths, shared-memory budget."""
+    from hgq2_b200._lib import ChainLayer
+
+    def stack(widths):
+        arr = (ChainLayer * (len(widths) - 1))()
+        for a, k, n in zip(arr, widths[:-1], widths[1:]):
+            a.K, a.N = k, n
+        return len(arr), arr
+
+    L = built_lib
+    assert L.hgq_dense_chain_supported(*stack((16, 64, 32, 32, 5))) == 1
+    assert L.hgq_dense_chain_supported(*stack((16, 65))) == 0          # a layer wider than 64
+    assert L.hgq_dense_chain_supported(*stack((16, 64, 32, 5)[:1] + (64, 31, 5))) == 1
+    assert L.hgq_dense_chain_supported(*stack((8,) * 10)) == 0         # nine layers
+    assert L.hgq_dense_chain_supported(*stack((64,) * 9)) == 0         # eight 64 x 64 layers: weights and records exceed shared memory
+    n, arr = stack((16, 64, 32, 32, 5))
+    assert L.hgq_dense_chain_workspace(16384, n, arr) >= 128 * (16 * 64 + 64 + 16) * 4
+    assert L.hgq_dense_chain_workspace(0, n, arr) == 0
+    assert L.hgq_dense_chain_fwd(None, 16, n, arr, None) == -1         # null input: refused before any CUDA call
+    arr[1].K = 63                                                       # widths that do not chain
+    assert L.hgq_dense_chain_supported(n, arr) == 0
+
+
 def test_product_path_has_no_cpu_fallback():
     import torch
 
@@ -70,17 +94,17 @@ def test_package_never_imports_the_oracle():
 
 
 def test_descriptor_structs_match_the_header(tmp_path):
-    """hgq_slot_desc / hgq_weight_desc as the C compiler lays them out equal their ctypes mirrors field by field."""
+    """hgq_slot_desc / hgq_weight_desc / hgq_chain_layer as the C compiler lays them out equal their ctypes mirrors field by field."""
     import ctypes
     import shutil
     import subprocess
 
-    from hgq2_b200._lib import SlotDesc, WeightDesc
+    from hgq2_b200._lib import ChainLayer, SlotDesc, WeightDesc
 
     gcc = shutil.which('gcc')
     if gcc is None:
         pytest.skip('no C compiler')
-    fields = [('hgq_slot_desc', SlotDesc), ('hgq_weight_desc', WeightDesc)]
+    fields = [('hgq_slot_desc', SlotDesc), ('hgq_weight_desc', WeightDesc), ('hgq_chain_layer', ChainLayer)]
     body = ''.join(f'printf("%zu\\n", sizeof({c}));' + ''.join(f'printf("%zu\\n", offsetof({c}, {name}));' for name, _ in s._fields_)
                    for c, s in fields)
     src = tmp_path / 'layout.c'
