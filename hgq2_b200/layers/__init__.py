@@ -6,11 +6,13 @@ from .core import QBatchNormDense, QDense, QEinsumDense, QLayerBase, QLayerBaseM
 from .einsum_dense_batchnorm import QEinsumDenseBatchnorm
 from .ops import QAdd, QAveragePow2, QMaximum, QMeanPow2, QMinimum, QMultiply, QSubtract, QSum
 from .pooling import (
+    QAveragePooling1D,
     QAveragePooling2D,
     QGlobalAveragePooling1D,
     QGlobalAveragePooling2D,
     QGlobalMaxPooling1D,
     QGlobalMaxPooling2D,
+    QMaxPooling1D,
     QMaxPooling2D,
 )
 from .softmax import QSoftmax
@@ -18,6 +20,6 @@ from .softmax import QSoftmax
 __all__ = [
     'QDense', 'QEinsumDense', 'QConv1D', 'QConv2D', 'QSoftmax', 'QUnaryFunctionLUT', 'QMultiHeadAttention', 'QLayerBase',
     'QLayerBaseSingleInput', 'QLayerBaseMultiInputs', 'QSum', 'QMeanPow2', 'QAdd', 'QAveragePow2', 'QSubtract', 'QMultiply',
-    'QMaximum', 'QMinimum', 'QMaxPooling2D', 'QAveragePooling2D', 'QGlobalAveragePooling1D', 'QGlobalAveragePooling2D',
+    'QMaximum', 'QMinimum', 'QMaxPooling1D', 'QAveragePooling1D', 'QMaxPooling2D', 'QAveragePooling2D', 'QGlobalAveragePooling1D', 'QGlobalAveragePooling2D',
     'QGlobalMaxPooling1D', 'QGlobalMaxPooling2D', 'QBatchNormalization', 'QBatchNormDense', 'QEinsumDenseBatchnorm',
 ]

@@ -77,6 +77,38 @@ class QAveragePooling2D(_Windowed2D):
         return y.permute(0, 2, 3, 1)
 
 
+class _Windowed1D(QBasePooling):
+    """[batch, steps, channels] inputs: the 2-D pooling of an image of one row."""
+
+    def __init__(self, pool_size, strides=None, padding='valid', data_format=None, name=None,
+                 iq_conf: QuantizerConfig | None = None, oq_conf: QuantizerConfig | None = None, **kwargs):
+        if padding != 'valid':
+            raise NotImplementedError("only padding='valid' is supported")
+        one = lambda v: int(v[0]) if isinstance(v, (tuple, list)) else int(v)  # noqa: E731
+        self.pool_size = (1, one(pool_size))
+        self.strides = self.pool_size if strides is None else (1, one(strides))
+        self.padding = padding
+        super().__init__(data_format=data_format, name=name, iq_conf=iq_conf, oq_conf=oq_conf, **kwargs)
+
+    def compute_output_shape(self, input_shape):
+        b, w, c = input_shape
+        return (b, (w - self.pool_size[1]) // self.strides[1] + 1, c)
+
+
+class QMaxPooling1D(_Windowed1D):
+    """pooling.py:122-143, on the max-pooling kernels of the 2-D layer."""
+
+    def _pool(self, inputs):
+        return MaxPooling2D.call(self, inputs.unsqueeze(1)).squeeze(1)
+
+
+class QAveragePooling1D(_Windowed1D):
+    """pooling.py:50-71."""
+
+    def _pool(self, inputs):
+        return F.avg_pool1d(inputs.permute(0, 2, 1), self.pool_size[1], self.strides[1]).permute(0, 2, 1)
+
+
 class _Global(QBasePooling):
     def __init__(self, data_format=None, keepdims=False, iq_conf: QuantizerConfig | None = None,
                  oq_conf: QuantizerConfig | None = None, **kwargs):

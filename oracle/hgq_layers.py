@@ -613,6 +613,8 @@ def mirror_op_layer(layer):
     pools = {
         'QMaxPooling2D': lambda l: (lambda t: F.max_pool2d(t.permute(0, 3, 1, 2), l.pool_size, l.strides).permute(0, 2, 3, 1)),
         'QAveragePooling2D': lambda l: (lambda t: F.avg_pool2d(t.permute(0, 3, 1, 2), l.pool_size, l.strides).permute(0, 2, 3, 1)),
+        'QMaxPooling1D': lambda l: (lambda t: F.max_pool1d(t.permute(0, 2, 1), l.pool_size[1], l.strides[1]).permute(0, 2, 1)),
+        'QAveragePooling1D': lambda l: (lambda t: F.avg_pool1d(t.permute(0, 2, 1), l.pool_size[1], l.strides[1]).permute(0, 2, 1)),
         'QGlobalAveragePooling1D': lambda l: (lambda t: t.mean(dim=1, keepdim=l.keepdims)),
         'QGlobalAveragePooling2D': lambda l: (lambda t: t.mean(dim=(1, 2), keepdim=l.keepdims)),
         'QGlobalMaxPooling1D': lambda l: (lambda t: t.amax(dim=1, keepdim=l.keepdims)),

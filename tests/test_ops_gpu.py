@@ -54,6 +54,9 @@ SINGLE = [
     ('QMeanPow2', dict(axes=1), (50, 16, 7)),
     ('QMaxPooling2D', dict(pool_size=2), (30, 9, 8, 8)),
     ('QAveragePooling2D', dict(pool_size=2), (30, 8, 8, 5)),
+    ('QMaxPooling1D', dict(pool_size=2), (30, 9, 8)),
+    ('QMaxPooling1D', dict(pool_size=3, strides=2), (30, 11, 5)),
+    ('QAveragePooling1D', dict(pool_size=2), (30, 8, 5)),
     ('QGlobalAveragePooling1D', dict(), (40, 8, 6)),
     ('QGlobalAveragePooling2D', dict(keepdims=True), (30, 4, 4, 6)),
     ('QGlobalMaxPooling1D', dict(), (40, 8, 6)),
