@@ -115,6 +115,7 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_double, c_double, c_void_p] + [c_void_p] * 7,
     ),
+    'hgq_ebops_dense_batch': (c_int, [c_void_p, c_int, c_void_p]),
     'hgq_ebops_conv2d': (
         c_int,
         [c_void_p, c_int, c_int, c_int, c_void_p] + [c_int] * 11 + [c_void_p, c_int64, c_double, c_double, c_double, c_void_p]
@@ -153,6 +154,15 @@ class SlotDesc(ctypes.Structure):
                 ('absmax', c_void_p), ('decay', c_void_p), ('n', c_int64), ('kind', ctypes.c_int32), ('om', ctypes.c_int32),
                 ('rm', ctypes.c_int32), ('symmetric', ctypes.c_int32), ('tracked_weight', ctypes.c_int32), ('i_lo', c_float),
                 ('i_hi', c_float)]
+
+
+class EbopsDenseDesc(ctypes.Structure):
+    """hgq_ebops_dense_desc of include/hgq_b200.h."""
+
+    _fields_ = [('bw_in', c_void_p), ('P', c_int64), ('K', c_int64), ('bw_w', c_void_p), ('N', c_int64), ('bw_bias', c_void_p),
+                ('n_bias', c_int64), ('out_size', ctypes.c_double), ('scale', ctypes.c_double), ('beta', c_void_p),
+                ('ebops', c_void_p), ('ebops_f', c_void_p), ('loss', c_void_p), ('d_bw_in', c_void_p), ('d_bw_w', c_void_p),
+                ('d_bw_bias', c_void_p)]
 
 
 class ChainLayer(ctypes.Structure):

@@ -75,10 +75,9 @@ __device__ void finish(long long total, const float *bw_bias, int64_t n_bias, do
 }
 
 // bw_in [P, K], bw_w [K, N]
-__global__ void __launch_bounds__(kEbThreads) k_ebops_dense(const float *__restrict__ bw_in, int64_t P, int64_t K,
-                                                            const float *__restrict__ bw_w, int64_t N,
-                                                            const float *__restrict__ bw_bias, int64_t n_bias,
-                                                            double out_size, double scale, const float *__restrict__ beta_p, EbopsOut o) {
+__device__ __forceinline__ void ebops_dense_body(const float *__restrict__ bw_in, int64_t P, int64_t K, const float *__restrict__ bw_w,
+                                                 int64_t N, const float *__restrict__ bw_bias, int64_t n_bias, double out_size,
+                                                 double scale, const float *__restrict__ beta_p, const EbopsOut &o) {
     const float beta = *beta_p;
     extern __shared__ long long sm[];
     long long *A = sm, *B = sm + K, *scratch = sm + 2 * K;
@@ -104,6 +103,24 @@ __global__ void __launch_bounds__(kEbThreads) k_ebops_dense(const float *__restr
     if (o.d_w)
         for (int64_t e = threadIdx.x; e < K * N; e += blockDim.x) o.d_w[e] = gs * (float)A[e / N];
     finish(total, bw_bias, n_bias, out_size, scale, scale, beta, o, scratch);
+}
+
+__global__ void __launch_bounds__(kEbThreads) k_ebops_dense(const float *__restrict__ bw_in, int64_t P, int64_t K,
+                                                            const float *__restrict__ bw_w, int64_t N,
+                                                            const float *__restrict__ bw_bias, int64_t n_bias,
+                                                            double out_size, double scale, const float *__restrict__ beta_p, EbopsOut o) {
+    ebops_dense_body(bw_in, P, K, bw_w, N, bw_bias, n_bias, out_size, scale, beta_p, o);
+}
+
+// Several dense layers in one launch: block b takes layer b (the layers are independent and each is one block's work, so a
+// step's EBOPs terms cost one launch latency instead of one per layer).
+struct EbBatch {
+    hgq_ebops_dense_desc d[HGQ_EBOPS_BATCH_MAX];
+};
+__global__ void __launch_bounds__(kEbThreads) k_ebops_dense_batch(const EbBatch B) {
+    const hgq_ebops_dense_desc &d = B.d[blockIdx.x];
+    EbopsOut o{d.ebops, d.ebops_f, d.loss, d.d_bw_in, d.d_bw_w, d.d_bw_bias};
+    ebops_dense_body(d.bw_in, d.P, d.K, d.bw_w, d.N, d.bw_bias, d.n_bias, d.out_size, d.scale, d.beta, o);
 }
 
 // bw_in [H, W, C] (channels last), bw_w [KH, KW, C, N]; output position (oh, ow) reads input
@@ -182,6 +199,28 @@ extern "C" int hgq_ebops_dense(const float *bw_in, int64_t P, int64_t K, const f
     }
     k_ebops_dense<<<1, kEbThreads, smem, (cudaStream_t)stream>>>(bw_in, P, K, bw_w, N, bw_bias, n_bias, out_size, scale,
                                                                  beta, o);
+    return check_launch();
+}
+
+extern "C" int hgq_ebops_dense_batch(const hgq_ebops_dense_desc *descs, int n, void *stream) {
+    if (descs == nullptr) return HGQ_ERR_NULL;
+    if (n < 1 || n > HGQ_EBOPS_BATCH_MAX) return HGQ_ERR_SIZE;
+    EbBatch b;
+    int64_t kmax = 0;
+    for (int i = 0; i < n; ++i) {
+        const hgq_ebops_dense_desc &d = descs[i];
+        if (d.P <= 0 || d.K <= 0 || d.N <= 0 || d.n_bias < 0 || d.K > kEbMaxK) return HGQ_ERR_SIZE;
+        if (d.bw_in == nullptr || d.bw_w == nullptr || d.beta == nullptr || (d.n_bias > 0 && d.bw_bias == nullptr)) return HGQ_ERR_NULL;
+        b.d[i] = d;
+        if (d.K > kmax) kmax = d.K;
+    }
+    const size_t smem = (size_t)(2 * kmax + 32) * sizeof(long long);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k_ebops_dense_batch, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)((2 * kEbMaxK + 32) * sizeof(long long)));
+        if (e != cudaSuccess) return (int)e;
+    }
+    k_ebops_dense_batch<<<n, kEbThreads, smem, (cudaStream_t)stream>>>(b);
     return check_launch();
 }
 

@@ -96,8 +96,9 @@ class _Node:
     def backward(self, g, need_dx=True):
         raise NotImplementedError
 
-    def ebops(self, eng):
-        """Queue this node's EBOPs kernels (second stream, after the tables hold the tracked bits)."""
+    def ebops(self, eng, dense_items):
+        """Queue this node's EBOPs kernels (second stream, after the tables hold the tracked bits); dense layers append
+        their term to ``dense_items`` instead, and the engine launches those together."""
 
     def autograd_ebops(self):
         """EBOPs terms computed through torch on the BITS leaves (layers without a direct kernel); returns loss terms."""
@@ -281,16 +282,16 @@ class _Dense(_Node):
         """Whether this layer's backward kernel can add its input gradient to an existing tensor."""
         return kernels.qdense_bwd_accumulates(self.K, self.N, self.P, self.relu)
 
-    def ebops(self, eng):
+    def ebops(self, eng, dense_items):
         if self.eb_index is None:
             return
         layer = self.layer
         out_size = float(self.P * self.N) if not isinstance(layer, QEinsumDense) else float(np.prod(layer.full_output_shape[1:]))
         scale = layer.parallelization_factor / layer.n_parallel * layer.ebops_factor
-        kernels.ebops_dense(self.iq.BITS.view(self.P, self.K), self.kq.BITS.view(self.K, self.N),
+        dense_items.append((self.iq.BITS.view(self.P, self.K), self.kq.BITS.view(self.K, self.N),
                             None if self.bq is None else self.bq.BITS.view(-1), out_size, scale, layer._beta.value,
-                            out=(layer._ebops.value, eng.eb_loss[self.eb_index], self.iq.dBITS.view(self.P, self.K),
-                                 self.kq.dBITS.view(self.K, self.N), None if self.bq is None else self.bq.dBITS.view(-1)))
+                            (layer._ebops.value, eng.eb_loss[self.eb_index], self.iq.dBITS.view(self.P, self.K),
+                             self.kq.dBITS.view(self.K, self.N), None if self.bq is None else self.bq.dBITS.view(-1))))
 
 
 class _DenseChain(_Node):
@@ -350,9 +351,9 @@ class _DenseChain(_Node):
         kernels.dense_chain_bwd(g, x, dx, layers, len(specs))
         return dx
 
-    def ebops(self, eng):
+    def ebops(self, eng, dense_items):
         for n in self.nodes:
-            n.ebops(eng)
+            n.ebops(eng, dense_items)
 
 
 class _Conv(_Node):
@@ -429,7 +430,7 @@ class _Conv(_Node):
             return None
         return dxq.view(-1, W, C) if self.one_d else dxq
 
-    def ebops(self, eng):
+    def ebops(self, eng, dense_items):
         if self.eb_index is None:
             return
         H, W, C, KH, KW, N = self.geom
@@ -588,9 +589,9 @@ class _Attention(_Node):
             dx.add_(dxv)
         return dx
 
-    def ebops(self, eng):
+    def ebops(self, eng, dense_items):
         for d in (self.q, self.k, self.v, self.o):
-            d.ebops(eng)
+            d.ebops(eng, dense_items)
 
     def autograd_ebops(self):
         """The terms without a kernel of their own (the two activation-activation products, the softmax and its two
@@ -804,8 +805,11 @@ class Engine:
                 if self.dp is not None and self.dp.world > 1 and self.absmax.numel() > 1:
                     self.dp.absmax_sync(self.absmax)
                 kernels.tables_track_bits(self._slot_descs, n_slots, self._max_slot)
+                dense_items = []
                 for node in self.nodes:
-                    node.ebops(self)
+                    node.ebops(self, dense_items)
+                if dense_items:  # every dense layer's term in one launch
+                    kernels.ebops_dense_batch(dense_items)
                 eb_total = self.eb_loss.sum() if self._n_eb else None
                 with torch.enable_grad():
                     self._install_bits(True)

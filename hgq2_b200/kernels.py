@@ -188,6 +188,31 @@ def ebops_dense(bw_in, bw_w, bw_bias, out_size: float, scale: float, beta, want_
     return e_u, e_f, loss, d_in, d_w, d_b
 
 
+EBOPS_BATCH_MAX = 16
+
+
+def ebops_dense_batch(items) -> None:
+    """K3 for several dense layers in one launch per 16 layers.  ``items``: tuples (bw_in [P, K], bw_w [K, N], bw_bias or None,
+    out_size, scale, beta, out) with ``out`` = (ebops_u32, loss, d_in, d_w, d_bias) destinations as for ``ebops_dense``."""
+    for start in range(0, len(items), EBOPS_BATCH_MAX):
+        chunk = items[start:start + EBOPS_BATCH_MAX]
+        arr = (_lib.EbopsDenseDesc * len(chunk))()
+        keep = []
+        for a, (bw_in, bw_w, bw_bias, out_size, scale, beta, out) in zip(arr, chunk):
+            require_cuda(bw_in, bw_w, bw_bias, beta)
+            bw_in, bw_w = bw_in.contiguous(), bw_w.contiguous()
+            bw_bias = None if bw_bias is None else bw_bias.contiguous()
+            keep.append((bw_in, bw_w, bw_bias))
+            e_u, loss, d_in, d_w, d_b = out
+            a.bw_in, (a.P, a.K), a.bw_w, a.N = bw_in.data_ptr(), bw_in.shape, bw_w.data_ptr(), bw_w.shape[1]
+            a.bw_bias, a.n_bias = (None, 0) if bw_bias is None else (bw_bias.data_ptr(), bw_bias.numel())
+            a.out_size, a.scale, a.beta = float(out_size), float(scale), beta.data_ptr()
+            for name, t in (('ebops', e_u), ('ebops_f', None), ('loss', loss), ('d_bw_in', d_in), ('d_bw_w', d_w), ('d_bw_bias', d_b)):
+                setattr(a, name, None if t is None else t.data_ptr())
+        with torch.cuda.device(chunk[0][0].device):
+            check(lib().hgq_ebops_dense_batch(arr, len(chunk), stream_handle()), 'hgq_ebops_dense_batch')
+
+
 def ebops_conv2d(bw_in, bw_w, bw_bias, out_hw, strides, dilation, pad_tl, out_size: float, scale_main: float,
                  scale_bias: float, beta, want_grads: bool = True, out=None):
     """K3 for a channels-last conv2d.  bw_in [H, W, C], bw_w [KH, KW, C, N]."""

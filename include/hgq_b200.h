@@ -368,6 +368,26 @@ int hgq_ebops_dense(const float *bw_in, int64_t P, int64_t K, const float *bw_w,
                     float *d_bw_w, float *d_bw_bias, void *stream);
 
 /*
+ * hgq_ebops_dense for up to HGQ_EBOPS_BATCH_MAX layers in ONE launch (a block per layer): the terms of a step's dense
+ * layers cost one launch latency instead of one per layer.  `descs` is a host array; the fields are hgq_ebops_dense's
+ * arguments.
+ */
+#define HGQ_EBOPS_BATCH_MAX 16
+typedef struct {
+    const float *bw_in;
+    int64_t P, K;
+    const float *bw_w;
+    int64_t N;
+    const float *bw_bias;
+    int64_t n_bias;
+    double out_size, scale;
+    const float *beta;
+    uint32_t *ebops;
+    float *ebops_f, *loss, *d_bw_in, *d_bw_w, *d_bw_bias;
+} hgq_ebops_dense_desc;
+int hgq_ebops_dense_batch(const hgq_ebops_dense_desc *descs, int n, void *stream);
+
+/*
  * EBOPs of a channels-last 2-D convolution: sum(conv(bw_in, bw_w)) * scale_main +
  * mean(bw_bias) * out_size * scale_bias (layers/conv.py:91-102).  bw_in [H, W, C],
  * bw_w [KH, KW, C, N]; (OH, OW) is the output size, pad_top / pad_left the implicit zero padding

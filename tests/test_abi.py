@@ -99,12 +99,13 @@ def test_descriptor_structs_match_the_header(tmp_path):
     import shutil
     import subprocess
 
-    from hgq2_b200._lib import ChainLayer, SlotDesc, WeightDesc
+    from hgq2_b200._lib import ChainLayer, EbopsDenseDesc, SlotDesc, WeightDesc
 
     gcc = shutil.which('gcc')
     if gcc is None:
         pytest.skip('no C compiler')
-    fields = [('hgq_slot_desc', SlotDesc), ('hgq_weight_desc', WeightDesc), ('hgq_chain_layer', ChainLayer)]
+    fields = [('hgq_slot_desc', SlotDesc), ('hgq_weight_desc', WeightDesc), ('hgq_chain_layer', ChainLayer),
+              ('hgq_ebops_dense_desc', EbopsDenseDesc)]
     body = ''.join(f'printf("%zu\\n", sizeof({c}));' + ''.join(f'printf("%zu\\n", offsetof({c}, {name}));' for name, _ in s._fields_)
                    for c, s in fields)
     src = tmp_path / 'layout.c'
