@@ -307,6 +307,25 @@ def _fused_conv2d(layer, xq, qkernel, qbias, act_spec):
     return QConv2dFusedFn.apply(xq, qkernel, qbias, act_spec, tuple(layer.strides), dil, (pt, pl), (OH, OW), cp)
 
 
+def space_to_depth_operands(x, kernel, pad_tl, strides, out_hw):
+    """The operands of the unit-stride 'valid' convolution that equals conv(x, kernel) with the given strides and top / left
+    zero padding on its first out_hw outputs: x [B, H, W, C] -> [B, OH + KH' - 1, OW + KW' - 1, sh sw C] and kernel
+    [KH, KW, C, N] -> [KH', KW', sh sw C, N] with KH' = ceil(KH / sh), KW' = ceil(KW / sw) (see strided_conv2d_call).  Plain
+    tensor algebra: differentiable, and the same on any device."""
+    (pt, pl), (sh, sw), (OH, OW) = pad_tl, strides, out_hw
+    B, H, W, C = x.shape
+    KH, KW, _, N = kernel.shape
+    KHs, KWs = -(-KH // sh), -(-KW // sw)
+    Hs, Ws = OH + KHs - 1, OW + KWs - 1          # blocks the outputs reach
+    Cs = sh * sw * C
+    # image: pad (or crop rows / columns no output reads) to Hs sh x Ws sw, then blocks -> channels
+    x = torch.nn.functional.pad(x, (0, 0, pl, Ws * sw - W - pl, pt, Hs * sh - H - pt))
+    x = x.reshape(B, Hs, sh, Ws, sw, C).permute(0, 1, 3, 2, 4, 5).reshape(B, Hs, Ws, Cs)
+    w = torch.nn.functional.pad(kernel, (0, 0, 0, 0, 0, KWs * sw - KW, 0, KHs * sh - KH))
+    w = w.reshape(KHs, sh, KWs, sw, C, N).permute(0, 2, 1, 3, 4, 5).reshape(KHs, KWs, Cs, N)
+    return x, w
+
+
 def strided_conv2d_call(layer, xq, qkernel, qbias, act_spec):
     """A strided convolution as a unit-stride one (space to depth), so that forward, input gradient and weight gradient all run
     on the unit-stride implicit-GEMM kernels: the zero-padded image is regrouped into blocks of sh x sw pixels whose pixels
@@ -319,19 +338,13 @@ def strided_conv2d_call(layer, xq, qkernel, qbias, act_spec):
         return None
     B, H, W, C = xq.shape
     KH, KW, _, N = qkernel.shape
-    (pt, pb), (pl, pr) = layer._pads(H, W)
+    (pt, _), (pl, _) = layer._pads(H, W)
     _, OH, OW, _ = layer.compute_output_shape(tuple(xq.shape))
     KHs, KWs = -(-KH // sh), -(-KW // sw)
-    Hs, Ws = OH + KHs - 1, OW + KWs - 1          # blocks the outputs reach
-    Cs = sh * sw * C
-    cp = conv_padding_channels(B, Hs, Ws, Cs, KHs, KWs, N, OH, OW, (1, 1))
+    cp = conv_padding_channels(B, OH + KHs - 1, OW + KWs - 1, sh * sw * C, KHs, KWs, N, OH, OW, (1, 1))
     if cp is None:
         return None
-    # image: pad (or crop rows / columns no output reads) to Hs sh x Ws sw, then blocks -> channels
-    x = torch.nn.functional.pad(xq, (0, 0, pl, Ws * sw - W - pl, pt, Hs * sh - H - pt))
-    x = x.reshape(B, Hs, sh, Ws, sw, C).permute(0, 1, 3, 2, 4, 5).reshape(B, Hs, Ws, Cs)
-    w = torch.nn.functional.pad(qkernel, (0, 0, 0, 0, 0, KWs * sw - KW, 0, KHs * sh - KH))
-    w = w.reshape(KHs, sh, KWs, sw, C, N).permute(0, 2, 1, 3, 4, 5).reshape(KHs, KWs, Cs, N)
+    x, w = space_to_depth_operands(xq, qkernel, (pt, pl), (sh, sw), (OH, OW))
     return QConv2dFusedFn.apply(x, w, qbias, act_spec, (1, 1), (1, 1), (0, 0), (OH, OW), cp)
 
 
